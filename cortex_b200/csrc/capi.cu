@@ -1,0 +1,244 @@
+// Device / stream / buffer / event half of the C ABI: the B200 counterpart of
+// the reference's CudaDriver / CudaDevice / CudaStream records
+// (src/cortex/compute/cuda/driver.clj:725-733, 849-1045).
+#include "common.cuh"
+#include <stdarg.h>
+#include <string.h>
+#include <new>
+
+static thread_local char g_err[1024] = "";
+
+void cb200_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cb200_cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
+  cb200_set_error("CUDA error %d (%s) in %s at %s:%d", (int)e, cudaGetErrorString(e), what, file, line);
+  return e == cudaErrorMemoryAllocation ? CB200_ERR_NOMEM : CB200_ERR_CUDA;
+}
+
+int cb200_check_dims(const cb200_dims* d, const char* what) {
+  if (!d) { cb200_set_error("%s: null dimensions", what); return CB200_ERR_INVALID; }
+  for (int i = 0; i < 5; ++i) {
+    if (d->rev_shape[i] < 1) {
+      cb200_set_error("%s: rev_shape[%d] = %d must be >= 1", what, i, d->rev_shape[i]);
+      return CB200_ERR_INVALID;
+    }
+    if (d->rev_strides[i] < 0) {
+      cb200_set_error("%s: rev_strides[%d] = %d must be >= 0", what, i, d->rev_strides[i]);
+      return CB200_ERR_INVALID;
+    }
+  }
+  return CB200_OK;
+}
+
+int cb200_scratch(cb200_stream* s, size_t bytes, void** out) {
+  if (bytes > s->scratch_bytes) {
+    DeviceGuard g(s->device);
+    if (s->scratch) {
+      CB_CUDA(cudaStreamSynchronize(s->stream));
+      CB_CUDA(cudaFree(s->scratch));
+      s->scratch = nullptr;
+      s->scratch_bytes = 0;
+    }
+    size_t want = (bytes + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
+    CB_CUDA(cudaMalloc(&s->scratch, want));
+    s->scratch_bytes = want;
+  }
+  *out = s->scratch;
+  return CB200_OK;
+}
+
+extern "C" {
+
+const char* cb200_last_error(void) { return g_err; }
+
+int cb200_unsupported(const char* method_name) {
+  cb200_set_error("%s is outside the dense-inference path of this backend", method_name ? method_name : "?");
+  return CB200_ERR_UNSUPPORTED;
+}
+
+int cb200_device_count(int* count) {
+  CB_REQUIRE(count, "device_count: null out pointer");
+  CB_CUDA(cudaGetDeviceCount(count));
+  return CB200_OK;
+}
+
+int cb200_device_info(int device, char* name, int name_len, int* sm_count, int* cc_major, int* cc_minor) {
+  cudaDeviceProp p;
+  CB_CUDA(cudaGetDeviceProperties(&p, device));
+  if (name && name_len > 0) { strncpy(name, p.name, name_len - 1); name[name_len - 1] = 0; }
+  if (sm_count) *sm_count = p.multiProcessorCount;
+  if (cc_major) *cc_major = p.major;
+  if (cc_minor) *cc_minor = p.minor;
+  return CB200_OK;
+}
+
+int cb200_mem_info(int device, size_t* free_bytes, size_t* total_bytes) {
+  DeviceGuard g(device);
+  CB_REQUIRE(g.ok, "mem_info: cannot select device %d", device);
+  size_t f = 0, t = 0;
+  CB_CUDA(cudaMemGetInfo(&f, &t));
+  if (free_bytes) *free_bytes = f;
+  if (total_bytes) *total_bytes = t;
+  return CB200_OK;
+}
+
+int cb200_stream_create(int device, cb200_stream** out) {
+  CB_REQUIRE(out, "stream_create: null out pointer");
+  DeviceGuard g(device);
+  CB_REQUIRE(g.ok, "stream_create: cannot select device %d", device);
+  cb200_stream* s = new (std::nothrow) cb200_stream();
+  if (!s) { cb200_set_error("stream_create: out of host memory"); return CB200_ERR_NOMEM; }
+  s->device = device;
+  s->scratch = nullptr;
+  s->scratch_bytes = 0;
+  s->launches.store(0);
+  cudaError_t e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&s->status_dev, 2 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(s->status_dev, 0, 2 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&s->status_host, 2 * sizeof(int));
+  if (e != cudaSuccess) { delete s; return cb200_cuda_fail(e, "stream_create", __FILE__, __LINE__); }
+  s->status_host[0] = s->status_host[1] = 0;
+  *out = s;
+  return CB200_OK;
+}
+
+int cb200_stream_destroy(cb200_stream* s) {
+  if (!s) return CB200_OK;
+  DeviceGuard g(s->device);
+  cudaStreamSynchronize(s->stream);
+  if (s->scratch) cudaFree(s->scratch);
+  cudaFree(s->status_dev);
+  cudaFreeHost(s->status_host);
+  cudaStreamDestroy(s->stream);
+  delete s;
+  return CB200_OK;
+}
+
+void* cb200_stream_native(cb200_stream* s) { return s ? (void*)s->stream : nullptr; }
+int cb200_stream_device(cb200_stream* s) { return s ? s->device : -1; }
+int64_t cb200_launch_count(cb200_stream* s) { return s ? s->launches.load() : 0; }
+
+int cb200_stream_status(cb200_stream* s, int* code, int* detail) {
+  CB_REQUIRE(s, "stream_status: null stream");
+  DeviceGuard g(s->device);
+  CB_CUDA(cudaMemcpyAsync(s->status_host, s->status_dev, 2 * sizeof(int), cudaMemcpyDeviceToHost, s->stream));
+  CB_CUDA(cudaMemsetAsync(s->status_dev, 0, 2 * sizeof(int), s->stream));
+  CB_CUDA(cudaStreamSynchronize(s->stream));
+  if (code) *code = s->status_host[0];
+  if (detail) *detail = s->status_host[1];
+  return CB200_OK;
+}
+
+int cb200_malloc(int device, size_t bytes, void** out) {
+  CB_REQUIRE(out, "malloc: null out pointer");
+  DeviceGuard g(device);
+  CB_REQUIRE(g.ok, "malloc: cannot select device %d", device);
+  CB_CUDA(cudaMalloc(out, bytes ? bytes : 1));
+  return CB200_OK;
+}
+
+int cb200_free(int device, void* ptr) {
+  if (!ptr) return CB200_OK;
+  DeviceGuard g(device);
+  CB_CUDA(cudaFree(ptr));
+  return CB200_OK;
+}
+
+int cb200_host_alloc(size_t bytes, void** out) {
+  CB_REQUIRE(out, "host_alloc: null out pointer");
+  CB_CUDA(cudaMallocHost(out, bytes ? bytes : 1));
+  return CB200_OK;
+}
+
+int cb200_host_free(void* ptr) {
+  if (!ptr) return CB200_OK;
+  CB_CUDA(cudaFreeHost(ptr));
+  return CB200_OK;
+}
+
+int cb200_memcpy_h2d(cb200_stream* s, void* dst, const void* src, size_t bytes) {
+  CB_REQUIRE(s && (bytes == 0 || (dst && src)), "memcpy_h2d: null argument");
+  DeviceGuard g(s->device);
+  CB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, s->stream));
+  return CB200_OK;
+}
+
+int cb200_memcpy_d2h(cb200_stream* s, void* dst, const void* src, size_t bytes) {
+  CB_REQUIRE(s && (bytes == 0 || (dst && src)), "memcpy_d2h: null argument");
+  DeviceGuard g(s->device);
+  CB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, s->stream));
+  return CB200_OK;
+}
+
+int cb200_memcpy_d2d(cb200_stream* s, void* dst, const void* src, size_t bytes) {
+  CB_REQUIRE(s && (bytes == 0 || (dst && src)), "memcpy_d2d: null argument");
+  DeviceGuard g(s->device);
+  CB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s->stream));
+  return CB200_OK;
+}
+
+int cb200_event_record(cb200_stream* s, int timing, cb200_event** out) {
+  CB_REQUIRE(s && out, "event_record: null argument");
+  DeviceGuard g(s->device);
+  cb200_event* e = new (std::nothrow) cb200_event();
+  if (!e) { cb200_set_error("event_record: out of host memory"); return CB200_ERR_NOMEM; }
+  e->device = s->device;
+  e->stream = s;
+  cudaError_t err = cudaEventCreateWithFlags(&e->ev, timing ? cudaEventDefault : cudaEventDisableTiming);
+  if (err == cudaSuccess) err = cudaEventRecord(e->ev, s->stream);
+  if (err != cudaSuccess) { delete e; return cb200_cuda_fail(err, "event_record", __FILE__, __LINE__); }
+  *out = e;
+  return CB200_OK;
+}
+
+int cb200_stream_wait_event(cb200_stream* s, cb200_event* e) {
+  CB_REQUIRE(s && e, "stream_wait_event: null argument");
+  DeviceGuard g(s->device);
+  CB_CUDA(cudaStreamWaitEvent(s->stream, e->ev, 0));
+  return CB200_OK;
+}
+
+int cb200_event_wait(cb200_event* e) {
+  CB_REQUIRE(e, "event_wait: null event");
+  DeviceGuard g(e->device);
+  CB_CUDA(cudaEventSynchronize(e->ev));
+  return CB200_OK;
+}
+
+int cb200_event_elapsed_ms(cb200_event* start, cb200_event* stop, float* ms) {
+  CB_REQUIRE(start && stop && ms, "event_elapsed_ms: null argument");
+  DeviceGuard g(start->device);
+  CB_CUDA(cudaEventElapsedTime(ms, start->ev, stop->ev));
+  return CB200_OK;
+}
+
+int cb200_event_destroy(cb200_event* e) {
+  if (!e) return CB200_OK;
+  DeviceGuard g(e->device);
+  cudaEventDestroy(e->ev);
+  delete e;
+  return CB200_OK;
+}
+
+int cb200_stream_sync(cb200_stream* s) {
+  CB_REQUIRE(s, "stream_sync: null stream");
+  DeviceGuard g(s->device);
+  CB_CUDA(cudaStreamSynchronize(s->stream));
+  int code = 0, detail = 0;
+  int rc = cb200_stream_status(s, &code, &detail);
+  if (rc != CB200_OK) return rc;
+  if (code != 0) {
+    cb200_set_error("device-side status %d (detail %d): a bounded wait ran out or a kernel rejected its arguments",
+                    code, detail);
+    return code == CB200_ERR_TIMEOUT ? CB200_ERR_TIMEOUT : CB200_ERR_CUDA;
+  }
+  return CB200_OK;
+}
+
+}  // extern "C"

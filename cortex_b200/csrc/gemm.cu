@@ -1,0 +1,168 @@
+// gemm! entry points (src/cortex/tensor/math.clj:106-115) and the plain SIMT
+// kernel that takes the shapes the tensor-core kernels do not (pointers or
+// pitches that TMA cannot address, K = 0).
+#include "common.cuh"
+#include <math.h>
+
+int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
+                             const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
+                             float beta, const float* bias, int act, int store_mode, int hw, int flags);
+bool cb200_gemm_tf32x3_eligible(const float* A, long long lda, const float* B, long long ldb, int M, int N, int K);
+int cb200_gemm_f64_launch(cb200_stream* s, double* C, long long ldc, int trans_a, int trans_b, double alpha,
+                          const double* A, int M, int K, long long lda, const double* B, int N, long long ldb,
+                          double beta, const double* bias, int act);
+
+namespace {
+
+template <typename T> __device__ __forceinline__ T act_apply(T v, int act) {
+  switch (act) {
+    case CB200_ACT_RELU: return v > (T)0 ? v : (T)0;
+    case CB200_ACT_TANH: return (T)tanh((double)v);
+    case CB200_ACT_LOGISTIC: return (T)(1.0 / (1.0 + exp(-(double)v)));
+  }
+  return v;
+}
+
+// 64x64 tile, 16x16 threads, 4x4 per thread.  Element (m,k) of op(A) is
+// A[m*sam + k*sak]; element (k,n) of op(B) is B[k*sbk + n*sbn].
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm_simt(T* C, long long ldc, const T* A, long long sam, long long sak, const T* B, long long sbk, long long sbn,
+          int M, int N, int K, T alpha, T beta, const T* bias, int act) {
+  __shared__ T As[16][64 + 1];
+  __shared__ T Bs[16][64 + 1];
+  const int t = threadIdx.x, tx = t % 16, ty = t / 16;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  T acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = (T)0;
+  for (int k0 = 0; k0 < K; k0 += 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int k, m;
+      if (sak == 1) { k = t % 16; m = t / 16 + 16 * i; } else { m = t % 64; k = t / 64 + 4 * i; }
+      T v = (T)0;
+      if (m0 + m < M && k0 + k < K) v = A[(long long)(m0 + m) * sam + (long long)(k0 + k) * sak];
+      As[k][m] = v;
+      int kb, n;
+      if (sbn == 1) { n = t % 64; kb = t / 64 + 4 * i; } else { kb = t % 16; n = t / 16 + 16 * i; }
+      T w = (T)0;
+      if (n0 + n < N && k0 + kb < K) w = B[(long long)(k0 + kb) * sbk + (long long)(n0 + n) * sbn];
+      Bs[kb][n] = w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      T a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty + 16 * i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[k][tx + 16 * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int m = m0 + ty + 16 * i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int n = n0 + tx + 16 * j;
+      if (n >= N) continue;
+      T* c = C + (long long)m * ldc + n;
+      T o = alpha * acc[i][j];
+      if (beta != (T)0) o += beta * (*c);
+      if (bias) o += bias[n];
+      *c = act_apply<T>(o, act);
+    }
+  }
+}
+
+template <typename T>
+int launch_simt(cb200_stream* s, T* C, long long ldc, int ta, int tb, T alpha, const T* A, int M, int K, long long lda,
+                const T* B, int N, long long ldb, T beta, const T* bias, int act) {
+  DeviceGuard guard(s->device);
+  dim3 grid((N + 63) / 64, (M + 63) / 64);
+  long long sam = ta ? 1 : lda, sak = ta ? lda : 1;
+  long long sbk = tb ? 1 : ldb, sbn = tb ? ldb : 1;
+  gemm_simt<T><<<grid, 256, 0, s->stream>>>(C, ldc, A, sam, sak, B, sbk, sbn, M, N, K, alpha, beta, bias, act);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha, const void* A,
+              int64_t a_rows, int64_t a_cols, int64_t lda, const void* B, int64_t b_cols, int64_t ldb, double beta,
+              const void* bias, int act) {
+  CB_REQUIRE(s && C && A && B, "gemm: null argument");
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "gemm! is only defined for float and double tensors");
+  CB_REQUIRE(a_rows >= 0 && a_cols >= 0 && b_cols >= 0, "gemm: negative extent");
+  CB_REQUIRE(a_rows <= 2147483647LL && a_cols <= 2147483647LL && b_cols <= 2147483647LL, "gemm: extent over 2^31-1");
+  const int M = (int)a_rows, K = (int)a_cols, N = (int)b_cols;
+  CB_REQUIRE(ldc >= N, "gemm: ldc %lld smaller than N %d", (long long)ldc, N);
+  CB_REQUIRE(lda >= (trans_a ? M : K), "gemm: lda %lld smaller than the stored row of A", (long long)lda);
+  CB_REQUIRE(ldb >= (trans_b ? K : N), "gemm: ldb %lld smaller than the stored row of B", (long long)ldb);
+  CB_REQUIRE(act >= CB200_ACT_NONE && act <= CB200_ACT_LOGISTIC, "gemm: unknown activation %d", act);
+  if (M == 0 || N == 0) return CB200_OK;
+  if (dtype == CB200_FLOAT) {
+    const float* a = (const float*)A;
+    const float* b = (const float*)B;
+    if (cb200_gemm_tf32x3_eligible(a, lda, b, ldb, M, N, K))
+      return cb200_gemm_tf32x3_launch(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb,
+                                      (float)beta, (const float*)bias, act, 0, 1, 0);
+    return launch_simt<float>(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb, (float)beta,
+                              (const float*)bias, act);
+  }
+  if (K >= 1)
+    return cb200_gemm_f64_launch(s, (double*)C, ldc, trans_a, trans_b, alpha, (const double*)A, M, K, lda,
+                                 (const double*)B, N, ldb, beta, (const double*)bias, act);
+  return launch_simt<double>(s, (double*)C, ldc, trans_a, trans_b, alpha, (const double*)A, M, K, lda, (const double*)B,
+                             N, ldb, beta, (const double*)bias, act);
+}
+
+}  // namespace
+
+// used by conv.cu when the weight pitch is not addressable by TMA
+int cb200_gemm_simt_f32_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
+                               const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
+                               float beta) {
+  return launch_simt<float>(s, C, ldc, trans_a, trans_b, alpha, A, M, K, lda, B, N, ldb, beta, nullptr, 0);
+}
+
+extern "C" {
+
+int cb200_gemm(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha, const void* A,
+               int64_t a_rows, int64_t a_cols, int64_t lda, const void* B, int64_t b_cols, int64_t ldb, double beta) {
+  return gemm_impl(s, dtype, C, ldc, trans_a, trans_b, alpha, A, a_rows, a_cols, lda, B, b_cols, ldb, beta, nullptr,
+                   CB200_ACT_NONE);
+}
+
+int cb200_gemm_bias_act(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha,
+                        const void* A, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B, int64_t b_cols,
+                        int64_t ldb, double beta, const void* bias, int act) {
+  return gemm_impl(s, dtype, C, ldc, trans_a, trans_b, alpha, A, a_rows, a_cols, lda, B, b_cols, ldb, beta, bias, act);
+}
+
+// Test hooks (not part of the public header): force a specific fp32 kernel.
+//   which = 0: SIMT kernel; 1: tensor-core kernel with `flags` (1 = single tf32 term,
+//   2 = keep the raw fp32 tile as the hi operand)
+int cb200_gemm_f32_variant(cb200_stream* s, int which, int flags, void* C, int64_t ldc, int trans_a, int trans_b,
+                           double alpha, const void* A, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B,
+                           int64_t b_cols, int64_t ldb, double beta) {
+  CB_REQUIRE(s && C && A && B, "gemm_f32_variant: null argument");
+  const int M = (int)a_rows, K = (int)a_cols, N = (int)b_cols;
+  if (which == 0)
+    return launch_simt<float>(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, (const float*)A, M, K, lda,
+                              (const float*)B, N, ldb, (float)beta, nullptr, 0);
+  CB_REQUIRE(cb200_gemm_tf32x3_eligible((const float*)A, lda, (const float*)B, ldb, M, N, K),
+             "gemm_f32_variant: operands are not addressable by TMA");
+  return cb200_gemm_tf32x3_launch(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, (const float*)A, M, K, lda,
+                                  (const float*)B, N, ldb, (float)beta, nullptr, 0, 0, 1, flags);
+}
+
+}  // extern "C"

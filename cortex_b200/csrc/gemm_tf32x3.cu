@@ -1,0 +1,383 @@
+// fp32 gemm! on the 5th-generation tensor cores: C = alpha*op(A)*op(B) + beta*C
+// (+ bias row, + activation), fp32 in / fp32 out, computed as a 3xTF32 split:
+//   x = hi + lo,  hi = tf32(x), lo = tf32(x - hi)
+//   A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi      (fp32 accumulation in TMEM)
+// Replaces cublasSgemm_v2 of the reference backend
+// (src/cortex/compute/cuda/tensor_math.clj:127-154, 633-649).
+//
+// One CTA computes a 128 x BN tile of C.  Warp roles:
+//   warps 0-7  split the raw fp32 tiles that TMA delivered into hi (in place) and
+//              lo (second buffer) inside shared memory, then run the epilogue
+//   warp  8    TMA producer (one lane)
+//   warp  9    allocates TMEM, issues tcgen05.mma (one lane), frees TMEM
+// Per k-block (32 fp32 = one 128-byte swizzle row) and pipeline stage:
+//   empty[s] -> TMA -> full[s] -> split -> conv[s] -> 12 x tcgen05.mma -> commit -> empty[s]
+// All four transpose combinations run on the tensor cores: a non-transposed A /
+// transposed B is K-major in memory; the other two are MN-major and use the
+// MN-major form of the shared-memory descriptor with 32x32 TMA boxes.
+// Operand tiles outside the matrix are zero-filled by TMA, so any M, N, K works;
+// pointers must be 16-byte aligned and row pitches a multiple of 4 elements
+// (the host falls back to gemm_simt otherwise).
+#include "common.cuh"
+#include "sm100.cuh"
+#include <mutex>
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                 // fp32 elements per k-block = 128 bytes
+constexpr int A_TILE = BM * BK * 4;    // 16 KiB
+constexpr int NUM_CONV_WARPS = 8;
+constexpr int NUM_THREADS = (NUM_CONV_WARPS + 2) * 32;
+
+enum { STORE_ROW_MAJOR = 0, STORE_NCHW = 1 };
+enum { FLAG_ONE_TERM = 1, FLAG_KEEP_RAW_HI = 2 };
+
+struct GemmParams {
+  float* C;
+  long long ldc;
+  int M, N, K;
+  float alpha, beta;
+  const float* bias;   // [N] or null
+  int act;
+  int a_mn_major, b_mn_major;
+  int store_mode;
+  int hw;              // STORE_NCHW: pixels per image; C[(m / hw) * N * hw + n * hw + m % hw]
+  int flags;
+  int* status;
+};
+
+template <int BN> struct TileCfg {
+  static constexpr int B_TILE = BN * BK * 4;
+  static constexpr int RAW = A_TILE + B_TILE;
+  static constexpr int STAGE = 2 * RAW;
+  static constexpr int STAGES = (BN == 256) ? 2 : ((BN == 128) ? 3 : 4);
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case CB200_ACT_RELU: return v > 0.f ? v : 0.f;
+    case CB200_ACT_TANH: return tanhf(v);
+    case CB200_ACT_LOGISTIC: return 1.f / (1.f + expf(-v));
+  }
+  return v;
+}
+
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi_bits, uint32_t& lo_bits) {
+  uint32_t hb = cvt_rna_tf32(x);
+  if ((hb & 0x7f800000u) == 0x7f800000u) {
+    // rounding overflowed, or x is not finite: fall back to truncation / canonical NaN
+    hb = (x != x) ? 0x7fc00000u : (__float_as_uint(x) & 0xffffe000u);
+  }
+  float lo = ((hb & 0x7f800000u) == 0x7f800000u) ? 0.f : x - __uint_as_float(hb);
+  hi_bits = hb;
+  lo_bits = cvt_rna_tf32(lo);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  typedef TileCfg<BN> Cfg;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::STAGE);
+  // bars[0..S) full, [S..2S) conv, [2S..3S) empty, [3S] accumulator ready
+  uint32_t* tmem_slot = (uint32_t*)(bars + 3 * STAGES + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
+  const int m0 = tile_m * BM, n0 = tile_n * BN;
+  const int nkb = (p.K + BK - 1) / BK;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_full = smem_u32(bars), bar_conv = smem_u32(bars + STAGES), bar_empty = smem_u32(bars + 2 * STAGES),
+                 bar_acc = smem_u32(bars + 3 * STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_conv + 8 * s, NUM_CONV_WARPS * 32);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == NUM_CONV_WARPS + 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == NUM_CONV_WARPS && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == NUM_CONV_WARPS) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES, ph = (i / STAGES) & 1;
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 100 + s)) break;
+        const uint32_t full = bar_full + 8 * s;
+        const uint32_t a_dst = smem_base + s * Cfg::STAGE, b_dst = a_dst + A_TILE;
+        const int k0 = i * BK;
+        mbar_arrive_expect_tx(full, Cfg::RAW);
+        if (!p.a_mn_major) {
+          tma_load_2d(a_dst, &tmA, k0, m0, full);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BM / 32; ++j) tma_load_2d(a_dst + j * 4096, &tmA, m0 + 32 * j, k0, full);
+        }
+        if (!p.b_mn_major) {
+          tma_load_2d(b_dst, &tmB, k0, n0, full);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &tmB, n0 + 32 * j, k0, full);
+        }
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        // let copies already issued land before this CTA gives its shared memory back
+        for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+          for (int it = 0; it < (1 << 16); ++it)
+            if (mbar_try_wait(bar_full + 8 * (i % STAGES), (i / STAGES) & 1)) break;
+      }
+    }
+  } else if (warp == NUM_CONV_WARPS + 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_tf32(BM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? 4096u : 16u, b_lbo = p.b_mn_major ? 4096u : 16u;
+      const uint32_t a_kstep = p.a_mn_major ? 1024u : 32u, b_kstep = p.b_mn_major ? 1024u : 32u;
+      uint32_t accumulate = 0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES, ph = (i / STAGES) & 1;
+        if (!mbar_wait(bar_conv + 8 * s, ph, abort_flag, p.status, 200 + s)) break;
+        tc_fence_after();
+        const uint32_t a_hi = smem_base + s * Cfg::STAGE, b_hi = a_hi + A_TILE;
+        const uint32_t a_lo = a_hi + Cfg::RAW, b_lo = b_hi + Cfg::RAW;
+#pragma unroll
+        for (int kk = 0; kk < BK / 8; ++kk) {
+          const uint64_t dah = make_smem_desc(a_hi + kk * a_kstep, a_lbo, 1024);
+          const uint64_t dbh = make_smem_desc(b_hi + kk * b_kstep, b_lbo, 1024);
+          if (!(p.flags & FLAG_ONE_TERM)) {
+            const uint64_t dal = make_smem_desc(a_lo + kk * a_kstep, a_lbo, 1024);
+            const uint64_t dbl = make_smem_desc(b_lo + kk * b_kstep, b_lbo, 1024);
+            mma_tf32_ss(tmem_base, dal, dbh, idesc, accumulate);   // small terms first
+            mma_tf32_ss(tmem_base, dah, dbl, idesc, 1);
+            accumulate = 1;
+          }
+          mma_tf32_ss(tmem_base, dah, dbh, idesc, accumulate);
+          accumulate = 1;
+        }
+        mma_commit(bar_empty + 8 * s);
+      }
+      mma_commit(bar_acc);
+      if (*abort_flag) {
+        // every MMA issued must have retired before TMEM is freed
+        for (int it = 0; it < (1 << 16); ++it)
+          if (mbar_try_wait(bar_acc, 0)) break;
+      }
+    }
+  } else {
+    // ------------------- hi/lo split, then epilogue (warps 0-7) ---------------
+    const int tid = threadIdx.x;
+    bool ok = true;
+    for (int i = 0; i < nkb; ++i) {
+      const int s = i % STAGES, ph = (i / STAGES) & 1;
+      if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 300 + s)) { ok = false; break; }
+      uint8_t* hi = smem + s * Cfg::STAGE;
+      uint8_t* lo = hi + Cfg::RAW;
+      if (!(p.flags & FLAG_ONE_TERM)) {
+#pragma unroll
+        for (int c = 0; c < Cfg::RAW / 16 / (NUM_CONV_WARPS * 32); ++c) {
+          const int off = (tid + c * NUM_CONV_WARPS * 32) * 16;
+          float4 v = *reinterpret_cast<const float4*>(hi + off);
+          uint4 h, l;
+          split_tf32(v.x, h.x, l.x);
+          split_tf32(v.y, h.y, l.y);
+          split_tf32(v.z, h.z, l.z);
+          split_tf32(v.w, h.w, l.w);
+          if (!(p.flags & FLAG_KEEP_RAW_HI)) *reinterpret_cast<uint4*>(hi + off) = h;
+          *reinterpret_cast<uint4*>(lo + off) = l;
+        }
+        fence_proxy_async_smem();
+      }
+      mbar_arrive(bar_conv + 8 * s);
+    }
+    if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 400);
+    ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
+    tc_fence_after();
+    if (ok) {
+      const int q = warp & 3, half = warp >> 2;
+      const int m = m0 + q * 32 + lane;
+      constexpr int COLS_PER_HALF = BN / 2;
+      constexpr int CHUNK = COLS_PER_HALF < 32 ? COLS_PER_HALF : 32;
+      static_assert(CHUNK == 32, "BN must be >= 64");
+      const bool vec_ok = p.store_mode == STORE_ROW_MAJOR && (p.ldc % 4) == 0 && (((uintptr_t)p.C) & 15) == 0;
+#pragma unroll 1
+      for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
+        const int col0 = half * COLS_PER_HALF + cc * 32;
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
+        tmem_ld_wait();
+        const int nb = n0 + col0;
+        if (m < p.M && nb < p.N) {
+          if (p.store_mode == STORE_ROW_MAJOR) {
+            float* crow = p.C + (long long)m * p.ldc + nb;
+            if (vec_ok && nb + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o;
+                o.x = p.alpha * __uint_as_float(r[j]);
+                o.y = p.alpha * __uint_as_float(r[j + 1]);
+                o.z = p.alpha * __uint_as_float(r[j + 2]);
+                o.w = p.alpha * __uint_as_float(r[j + 3]);
+                if (p.beta != 0.f) {
+                  float4 c = *reinterpret_cast<const float4*>(crow + j);
+                  o.x += p.beta * c.x; o.y += p.beta * c.y; o.z += p.beta * c.z; o.w += p.beta * c.w;
+                }
+                if (p.bias) {
+                  float4 b = *reinterpret_cast<const float4*>(p.bias + nb + j);
+                  o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                }
+                if (p.act) { o.x = apply_act(o.x, p.act); o.y = apply_act(o.y, p.act); o.z = apply_act(o.z, p.act); o.w = apply_act(o.w, p.act); }
+                *reinterpret_cast<float4*>(crow + j) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (nb + j < p.N) {
+                  float o = p.alpha * __uint_as_float(r[j]);
+                  if (p.beta != 0.f) o += p.beta * crow[j];
+                  if (p.bias) o += p.bias[nb + j];
+                  crow[j] = apply_act(o, p.act);
+                }
+              }
+            }
+          } else {
+            const long long img = m / p.hw, pix = m % p.hw;
+            float* cbase = p.C + img * (long long)p.N * p.hw + pix;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (nb + j < p.N) {
+                float* cp = cbase + (long long)(nb + j) * p.hw;
+                float o = p.alpha * __uint_as_float(r[j]);
+                if (p.beta != 0.f) o += p.beta * (*cp);
+                if (p.bias) o += p.bias[nb + j];
+                *cp = apply_act(o, p.act);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == NUM_CONV_WARPS + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------ host side -------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)f;
+  });
+  return fn;
+}
+
+// fp32 matrix [rows][cols] with row pitch ld (elements); box = {box_cols, box_rows}, 128-byte swizzle
+int make_tmap(CUtensorMap* tm, const float* base, long long rows, long long cols, long long ld, int box_cols,
+              int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    cb200_set_error("cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld box %dx%d)", (int)r, rows, cols,
+                    ld, box_cols, box_rows);
+    return CB200_ERR_CUDA;
+  }
+  return CB200_OK;
+}
+
+template <int BN>
+int launch_tile(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p) {
+  typedef TileCfg<BN> Cfg;
+  static std::once_flag once[64];
+  int dev = s->device;
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[dev & 63], [&] {
+    attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  });
+  if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
+  long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  gemm_tf32x3_kernel<BN><<<(unsigned)tiles, NUM_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmB, p);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+}  // namespace
+
+// Shared with conv.cu.  A: op(A) is M x K; B: op(B) is K x N.
+int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
+                             const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
+                             float beta, const float* bias, int act, int store_mode, int hw, int flags) {
+  DeviceGuard guard(s->device);
+  GemmParams p;
+  p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta; p.bias = bias; p.act = act;
+  p.a_mn_major = trans_a ? 1 : 0;   // op(A)[m][k] = A[k][m]: M is the contiguous axis
+  p.b_mn_major = trans_b ? 0 : 1;   // op(B)[k][n] = B[k][n]: N is the contiguous axis
+  p.store_mode = store_mode; p.hw = hw > 0 ? hw : 1; p.flags = flags; p.status = s->status_dev;
+  const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!p.a_mn_major) rc = make_tmap(&tmA, A, M, K, lda, BK, BM);
+  else rc = make_tmap(&tmA, A, K, M, lda, 32, BK);
+  if (rc) return rc;
+  if (!p.b_mn_major) rc = make_tmap(&tmB, B, N, K, ldb, BK, BN);
+  else rc = make_tmap(&tmB, B, K, N, ldb, 32, BK);
+  if (rc) return rc;
+  if (BN == 256) return launch_tile<256>(s, tmA, tmB, p);
+  if (BN == 128) return launch_tile<128>(s, tmA, tmB, p);
+  return launch_tile<64>(s, tmA, tmB, p);
+}
+
+bool cb200_gemm_tf32x3_eligible(const float* A, long long lda, const float* B, long long ldb, int M, int N, int K) {
+  if (M < 1 || N < 1 || K < 1) return false;
+  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return false;
+  if ((lda % 4) || (ldb % 4)) return false;
+  return true;
+}

@@ -1,0 +1,449 @@
+// unary-reduce!, softmax! and the fused bias+ReLU+row-statistics pass.
+//
+// The reference runs one thread per output row with a serial loop over the row
+// (resources/tensor_unary_reduce.cu:38-88): adjacent threads are a whole row
+// apart.  Here a row whose fastest dimension is contiguous is read by one warp
+// (short rows) or one CTA (long rows) with coalesced loads, several loads in
+// flight per thread, and combined with warp shuffles.  HBM-bound: algorithmic
+// bytes = input read once + output written once.
+//
+// Arithmetic follows the reference CPU backend
+// (src/cortex/compute/cpu/tensor_math.clj:588-629, 1037-1103): fp32 rows are
+// accumulated in double and rounded once; integer rows in 64-bit.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+template <typename A> __device__ __forceinline__ A shfl_down_any(A v, int delta);
+template <> __device__ __forceinline__ double shfl_down_any<double>(double v, int delta) {
+  return __shfl_down_sync(0xffffffffu, v, delta);
+}
+template <> __device__ __forceinline__ long long shfl_down_any<long long>(long long v, int delta) {
+  return __shfl_down_sync(0xffffffffu, v, delta);
+}
+template <> __device__ __forceinline__ float shfl_down_any<float>(float v, int delta) {
+  return __shfl_down_sync(0xffffffffu, v, delta);
+}
+
+// clojure.core/max and min on primitives: NaN-propagating for doubles
+__device__ __forceinline__ double clj_max(double a, double b) { return (a != a) ? a : ((b != b) ? b : (a > b ? a : b)); }
+__device__ __forceinline__ double clj_min(double a, double b) { return (a != a) ? a : ((b != b) ? b : (a < b ? a : b)); }
+__device__ __forceinline__ float clj_max(float a, float b) { return (a != a) ? a : ((b != b) ? b : (a > b ? a : b)); }
+__device__ __forceinline__ long long clj_max(long long a, long long b) { return a > b ? a : b; }
+__device__ __forceinline__ long long clj_min(long long a, long long b) { return a < b ? a : b; }
+
+template <typename A> __device__ __forceinline__ A red_identity(int op);
+template <> __device__ __forceinline__ double red_identity<double>(int op) {
+  return op == CB200_RMAX ? -INFINITY : (op == CB200_RMIN ? INFINITY : 0.0);
+}
+template <> __device__ __forceinline__ long long red_identity<long long>(int op) {
+  return op == CB200_RMAX ? (-9223372036854775807LL - 1) : (op == CB200_RMIN ? 9223372036854775807LL : 0);
+}
+
+template <typename A>
+__device__ __forceinline__ A red_elem(int op, A v) {
+  return (op == CB200_RMAGNITUDE || op == CB200_RMAGNITUDE_SQ) ? (A)(v * v) : v;
+}
+template <typename A>
+__device__ __forceinline__ A red_combine(int op, A a, A b) {
+  if (op == CB200_RMAX) return clj_max(a, b);
+  if (op == CB200_RMIN) return clj_min(a, b);
+  return (A)(a + b);
+}
+
+template <typename T>
+__device__ __forceinline__ T red_finish(int op, typename acc_of<T>::type acc, long long len) {
+  typedef typename acc_of<T>::type A;
+  if (op == CB200_RMEAN) {
+    // (/ sum n): double division for floating views, truncating for integer views
+    return store_as<T>::from((A)(acc / (A)len));
+  }
+  if (op == CB200_RMAGNITUDE) return store_as<T>::from(sqrt((double)acc));
+  return store_as<T>::from(acc);
+}
+
+template <typename A, int NWARPS>
+__device__ __forceinline__ A block_combine(int op, A v, A* smem) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v = red_combine(op, v, shfl_down_any<A>(v, d));
+  if (NWARPS == 1) return v;
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    v = lane < NWARPS ? smem[lane] : red_identity<A>(op);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = red_combine(op, v, shfl_down_any<A>(v, d));
+  }
+  return v;  // valid in thread 0
+}
+
+// One CTA (NWARPS = 8) or one warp (NWARPS = 1, 8 rows per CTA) per row.
+template <typename T, int NWARPS>
+__global__ void __launch_bounds__(256)
+reduce_rows(T* out, const T* in, Operand oo, Operand oi, Geometry go, Geometry gi, long long n_rows, int len, int op,
+            typename acc_of<T>::type alpha) {
+  typedef typename acc_of<T>::type A;
+  __shared__ A smem[8];
+  const int rows_per_block = NWARPS == 1 ? 8 : 1;
+  const int tid = NWARPS == 1 ? (threadIdx.x & 31) : threadIdx.x;
+  const int nthreads = NWARPS == 1 ? 32 : 256;
+  for (long long r0 = (long long)blockIdx.x * rows_per_block; r0 < n_rows; r0 += (long long)gridDim.x * rows_per_block) {
+    long long r = NWARPS == 1 ? r0 + (threadIdx.x >> 5) : r0;
+    A acc = red_identity<A>(op);
+    if (r < n_rows) {
+      const T* row = in + operand_offset(oi, gi, r * len);
+      int j = tid;
+      // 4 independent loads in flight per thread
+      for (; j + 3 * nthreads < len; j += 4 * nthreads) {
+        T v0 = row[j], v1 = row[j + nthreads], v2 = row[j + 2 * nthreads], v3 = row[j + 3 * nthreads];
+        acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v0)));
+        acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v1)));
+        acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v2)));
+        acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v3)));
+      }
+      for (; j < len; j += nthreads) acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)row[j])));
+    }
+    acc = block_combine<A, NWARPS>(op, acc, smem);
+    if (tid == 0 && r < n_rows) out[operand_offset(oo, go, r)] = red_finish<T>(op, acc, len);
+  }
+}
+
+// 16-byte vector variant for aligned contiguous rows (len % VEC == 0)
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) RVec { T v[VEC]; };
+
+template <typename T, int NWARPS>
+__global__ void __launch_bounds__(256)
+reduce_rows_vec(T* out, const T* in, Operand oo, Operand oi, Geometry go, Geometry gi, long long n_rows, int len,
+                int op, typename acc_of<T>::type alpha) {
+  typedef typename acc_of<T>::type A;
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ A smem[8];
+  const int rows_per_block = NWARPS == 1 ? 8 : 1;
+  const int tid = NWARPS == 1 ? (threadIdx.x & 31) : threadIdx.x;
+  const int nthreads = NWARPS == 1 ? 32 : 256;
+  const int nvec = len / VEC;
+  for (long long r0 = (long long)blockIdx.x * rows_per_block; r0 < n_rows; r0 += (long long)gridDim.x * rows_per_block) {
+    long long r = NWARPS == 1 ? r0 + (threadIdx.x >> 5) : r0;
+    A acc = red_identity<A>(op);
+    if (r < n_rows) {
+      const RVec<T, VEC>* row = reinterpret_cast<const RVec<T, VEC>*>(in + operand_offset(oi, gi, r * len));
+      int j = tid;
+      for (; j + 3 * nthreads < nvec; j += 4 * nthreads) {
+        RVec<T, VEC> v0 = row[j], v1 = row[j + nthreads], v2 = row[j + 2 * nthreads], v3 = row[j + 3 * nthreads];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v0.v[k])));
+          acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v1.v[k])));
+          acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v2.v[k])));
+          acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v3.v[k])));
+        }
+      }
+      for (; j < nvec; j += nthreads) {
+        RVec<T, VEC> v0 = row[j];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v0.v[k])));
+      }
+    }
+    acc = block_combine<A, NWARPS>(op, acc, smem);
+    if (tid == 0 && r < n_rows) out[operand_offset(oo, go, r)] = red_finish<T>(op, acc, len);
+  }
+}
+
+// Any layout: the reference's own shape, one thread per output element.
+template <typename T>
+__global__ void __launch_bounds__(256)
+reduce_generic(T* out, const T* in, Operand oo, Operand oi, Geometry go, Geometry gi, long long n_rows, int len, int op,
+               typename acc_of<T>::type alpha) {
+  typedef typename acc_of<T>::type A;
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < n_rows;
+       r += (long long)gridDim.x * blockDim.x) {
+    A acc = red_elem(op, (A)(alpha * (A)in[operand_offset(oi, gi, r * len)]));
+    for (int j = 1; j < len; ++j)
+      acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)in[operand_offset(oi, gi, r * len + j)])));
+    out[operand_offset(oo, go, r)] = red_finish<T>(op, acc, len);
+  }
+}
+
+void geometry_of(Geometry& g, const Operand& o) {
+  g.ndims = 1;
+  for (int d = 0; d < 5; ++d) { g.max_shape[d] = o.shape[d]; if (o.shape[d] > 1) g.ndims = d + 1; }
+}
+
+// ------------------------------ softmax -------------------------------------
+// Row r of a [rows, C] view with element stride cs inside the row and the row
+// base given by (r / inner) * outer_stride + (r % inner) * inner_stride:
+//   eltwise: inner = 1, outer_stride = row pitch, cs = 1
+//   spatial [N, C, E] over C: inner = E, outer_stride = N-stride, inner_stride = E-stride, cs = C-stride
+// Steps as softmax-impl (cpu/tensor_math.clj:1037-1088): m = max; e = exp(x - m)
+// rounded to the element type; s = sum of the rounded e in double, rounded;
+// y = e / s in the element type.
+template <typename T> __device__ __forceinline__ T sm_exp(T x, T m);
+template <> __device__ __forceinline__ float sm_exp<float>(float x, float m) {
+  return expf((float)((double)x - (double)m));
+}
+template <> __device__ __forceinline__ double sm_exp<double>(double x, double m) { return exp(x - m); }
+
+struct SoftmaxGeom {
+  long long rows;
+  int C;
+  long long inner;
+  long long in_outer, in_inner, in_cs;
+  long long out_outer, out_inner, out_cs;
+};
+
+// One warp (NWARPS = 1) or CTA (NWARPS = 8) per row; the row lives in registers
+// (PER values per thread), so x is read once and y written once.
+template <typename T, int NWARPS, int PER>
+__global__ void __launch_bounds__(256)
+softmax_rows(T* out, const T* in, SoftmaxGeom g) {
+  __shared__ double smem[8];
+  __shared__ double bcast;
+  const int rows_per_block = NWARPS == 1 ? 8 : 1;
+  const int tid = NWARPS == 1 ? (threadIdx.x & 31) : threadIdx.x;
+  const int nthreads = NWARPS == 1 ? 32 : 256;
+  for (long long r0 = (long long)blockIdx.x * rows_per_block; r0 < g.rows; r0 += (long long)gridDim.x * rows_per_block) {
+    long long r = NWARPS == 1 ? r0 + (threadIdx.x >> 5) : r0;
+    bool live = r < g.rows;
+    long long rr = live ? r : 0;
+    const T* x = in + (rr / g.inner) * g.in_outer + (rr % g.inner) * g.in_inner;
+    T* y = out + (rr / g.inner) * g.out_outer + (rr % g.inner) * g.out_inner;
+    T v[PER];
+    double m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      int j = tid + k * nthreads;
+      if (live && j < g.C) { v[k] = x[(long long)j * g.in_cs]; m = clj_max(m, (double)v[k]); }
+    }
+    m = block_combine<double, NWARPS>(CB200_RMAX, m, smem);
+    if (NWARPS == 1) m = __shfl_sync(0xffffffffu, m, 0);
+    else { if (threadIdx.x == 0) bcast = m; __syncthreads(); m = bcast; }
+    T mt = (T)m;
+    double s = 0.0;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      int j = tid + k * nthreads;
+      if (live && j < g.C) { v[k] = sm_exp<T>(v[k], mt); s += (double)v[k]; }
+    }
+    s = block_combine<double, NWARPS>(CB200_RSUM, s, smem);
+    if (NWARPS == 1) s = __shfl_sync(0xffffffffu, s, 0);
+    else { __syncthreads(); if (threadIdx.x == 0) bcast = s; __syncthreads(); s = bcast; }
+    T st = (T)s;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      int j = tid + k * nthreads;
+      if (live && j < g.C) y[(long long)j * g.out_cs] = v[k] / st;
+    }
+    if (NWARPS != 1) __syncthreads();
+  }
+}
+
+// Rows too long for registers, or strided inner axis (spatial): one thread per
+// row, three passes.  Adjacent threads take adjacent `inner` positions, which
+// is the contiguous axis of a [N, C, E] tensor.
+template <typename T>
+__global__ void __launch_bounds__(256)
+softmax_generic(T* out, const T* in, SoftmaxGeom g) {
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < g.rows;
+       r += (long long)gridDim.x * blockDim.x) {
+    const T* x = in + (r / g.inner) * g.in_outer + (r % g.inner) * g.in_inner;
+    T* y = out + (r / g.inner) * g.out_outer + (r % g.inner) * g.out_inner;
+    double m = (double)x[0];
+    for (int j = 1; j < g.C; ++j) m = clj_max(m, (double)x[(long long)j * g.in_cs]);
+    T mt = (T)m;
+    double s = 0.0;
+    for (int j = 0; j < g.C; ++j) {
+      T e = sm_exp<T>(x[(long long)j * g.in_cs], mt);
+      y[(long long)j * g.out_cs] = e;
+      s = j == 0 ? (double)e : s + (double)e;
+    }
+    T st = (T)s;
+    for (int j = 0; j < g.C; ++j) y[(long long)j * g.out_cs] = y[(long long)j * g.out_cs] / st;
+  }
+}
+
+template <typename T>
+int launch_softmax(cb200_stream* s, T* out, const T* in, const SoftmaxGeom& g) {
+  if (g.rows <= 0 || g.C <= 0) return CB200_OK;
+  DeviceGuard guard(s->device);
+  long long cap = (long long)s->sm_count * 16;
+  if (g.in_cs == 1 && g.out_cs == 1 && g.C <= 32 * 32) {
+    long long blocks = (g.rows + 7) / 8;
+    if (blocks > cap) blocks = cap;
+    if (g.C <= 32 * 4) softmax_rows<T, 1, 4><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    else if (g.C <= 32 * 16) softmax_rows<T, 1, 16><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    else softmax_rows<T, 1, 32><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+  } else if (g.in_cs == 1 && g.out_cs == 1 && g.C <= 256 * 32) {
+    long long blocks = g.rows < cap ? g.rows : cap;
+    if (g.C <= 256 * 8) softmax_rows<T, 8, 8><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    else if (g.C <= 256 * 16) softmax_rows<T, 8, 16><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    else softmax_rows<T, 8, 32><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+  } else {
+    long long blocks = (g.rows + 255) / 256;
+    if (blocks > cap) blocks = cap;
+    softmax_generic<T><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+  }
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+// ---------------------- fused bias + ReLU + row max / sum --------------------
+// One CTA per row, row in registers: X read once, Y written once.
+template <typename T, int PER>
+__global__ void __launch_bounds__(256)
+bias_relu_rowstats_k(T* Y, long long ldy, const T* X, long long ldx, const T* bias, long long rows, int cols,
+                     T* rowmax, T* rowsum) {
+  __shared__ double smem[8];
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* x = X + r * ldx;
+    T* y = Y + r * ldy;
+    double mx = -INFINITY, sum = 0.0;
+    T v[PER];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      int j = threadIdx.x + k * 256;
+      if (j < cols) v[k] = x[j];
+    }
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      int j = threadIdx.x + k * 256;
+      if (j < cols) {
+        T t = (T)((double)v[k] + (double)bias[j]);   // binary-op! :+ , rounded to the element type
+        double td = (double)t;
+        T o = (T)(td > 0.0 ? td : 0.0);              // binary-op! :max with scalar 0
+        y[j] = o;
+        mx = clj_max(mx, (double)o);
+        sum += (double)o;
+      }
+    }
+    mx = block_combine<double, 8>(CB200_RMAX, mx, smem);
+    if (threadIdx.x == 0 && rowmax) rowmax[r] = (T)mx;
+    sum = block_combine<double, 8>(CB200_RSUM, sum, smem);
+    if (threadIdx.x == 0 && rowsum) rowsum[r] = (T)sum;
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int cb200_unary_reduce(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, double alpha,
+                       const void* in, const cb200_dims* in_dims, int op) {
+  CB_REQUIRE(s && out && out_dims && in && in_dims, "unary_reduce: null argument");
+  CB_REQUIRE(op >= CB200_RMAX && op <= CB200_RMAGNITUDE_SQ, "unary_reduce: unknown op %d", op);
+  int rc = cb200_check_dims(out_dims, "unary_reduce out");
+  if (rc) return rc;
+  rc = cb200_check_dims(in_dims, "unary_reduce in");
+  if (rc) return rc;
+  Operand oo, oi;
+  operand_from_dims(oo, out_dims);
+  operand_from_dims(oi, in_dims);
+  Geometry go, gi;
+  geometry_of(go, oo);
+  geometry_of(gi, oi);
+  long long n_out = 1, n_in = 1;
+  for (int d = 0; d < 5; ++d) { n_out *= oo.shape[d]; n_in *= oi.shape[d]; }
+  CB_REQUIRE(n_out > 0 && n_in % n_out == 0, "unary_reduce: output element count %lld does not divide input count %lld",
+             n_out, n_in);
+  long long len_ll = n_in / n_out;   // iter-amount, cpu/tensor_math.clj:641-643
+  CB_REQUIRE(len_ll >= 1 && len_ll <= 2147483647LL, "unary_reduce: bad row length");
+  int len = (int)len_ll;
+  DeviceGuard guard(s->device);
+  bool contiguous = !oi.index[0] && oi.shape[0] == len && (oi.stride[0] == 1 || len == 1);
+  long long cap = (long long)s->sm_count * 16;
+  CB_DISPATCH_DTYPE(dtype, T, {
+    typedef typename acc_of<T>::type A;
+    A a = scalar_as<T>(alpha);
+    constexpr int VEC = 16 / sizeof(T);
+    if (contiguous) {
+      bool vec = (len % VEC) == 0 && ((uintptr_t)in % 16) == 0;
+      for (int d = 1; d < gi.ndims && vec; ++d) if (oi.shape[d] > 1 && (oi.stride[d] % VEC) != 0) vec = false;
+      if ((size_t)len * sizeof(T) >= 2048) {
+        long long blocks = n_out < cap ? n_out : cap;
+        if (vec) reduce_rows_vec<T, 8><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
+        else reduce_rows<T, 8><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
+      } else {
+        long long blocks = (n_out + 7) / 8;
+        if (blocks > cap) blocks = cap;
+        if (vec) reduce_rows_vec<T, 1><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
+        else reduce_rows<T, 1><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
+      }
+    } else {
+      long long blocks = (n_out + 255) / 256;
+      if (blocks > cap) blocks = cap;
+      reduce_generic<T><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
+    }
+    CB_LAUNCH_CHECK(s);
+  });
+  return CB200_OK;
+}
+
+static int softmax_entry(cb200_stream* s, int dtype, void* out, const cb200_dims* od, const void* in,
+                         const cb200_dims* id, int spatial) {
+  CB_REQUIRE(s && out && od && in && id, "softmax: null argument");
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "softmax is only defined for float and double tensors");
+  int rc = cb200_check_dims(od, "softmax out");
+  if (rc) return rc;
+  rc = cb200_check_dims(id, "softmax in");
+  if (rc) return rc;
+  for (int d = 0; d < 5; ++d) {
+    CB_REQUIRE(!od->index[d] && !id->index[d], "softmax: index arrays are not supported");
+    CB_REQUIRE(od->rev_shape[d] == id->rev_shape[d], "softmax: input and output shapes differ");
+  }
+  SoftmaxGeom g;
+  if (!spatial) {
+    // [rows, C]; anything above dim 1 must be trivial (softmax! passes as-batch-matrix views)
+    for (int d = 2; d < 5; ++d) CB_REQUIRE(id->rev_shape[d] == 1, "softmax_eltwise expects a 2-d view");
+    g.rows = id->rev_shape[1]; g.C = id->rev_shape[0]; g.inner = 1;
+    g.in_outer = id->rev_strides[1]; g.in_inner = 0; g.in_cs = id->rev_strides[0];
+    g.out_outer = od->rev_strides[1]; g.out_inner = 0; g.out_cs = od->rev_strides[0];
+  } else {
+    // [N, C, E]: softmax over C for every (n, e)
+    for (int d = 3; d < 5; ++d) CB_REQUIRE(id->rev_shape[d] == 1, "softmax_spatial expects a 3-d view");
+    long long N = id->rev_shape[2], E = id->rev_shape[0];
+    g.rows = N * E; g.C = id->rev_shape[1]; g.inner = E;
+    g.in_outer = id->rev_strides[2]; g.in_inner = id->rev_strides[0]; g.in_cs = id->rev_strides[1];
+    g.out_outer = od->rev_strides[2]; g.out_inner = od->rev_strides[0]; g.out_cs = od->rev_strides[1];
+  }
+  if (g.C == 1) { g.in_cs = 1; g.out_cs = 1; }
+  if (dtype == CB200_FLOAT) return launch_softmax<float>(s, (float*)out, (const float*)in, g);
+  return launch_softmax<double>(s, (double*)out, (const double*)in, g);
+}
+
+int cb200_softmax_eltwise(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, const void* in,
+                          const cb200_dims* in_dims) {
+  return softmax_entry(s, dtype, out, out_dims, in, in_dims, 0);
+}
+
+int cb200_softmax_spatial(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, const void* in,
+                          const cb200_dims* in_dims) {
+  return softmax_entry(s, dtype, out, out_dims, in, in_dims, 1);
+}
+
+int cb200_bias_relu_rowstats(cb200_stream* s, int dtype, void* Y, int64_t ldy, const void* X, int64_t ldx,
+                             const void* bias, int64_t rows, int64_t cols, void* rowmax, void* rowsum) {
+  CB_REQUIRE(s && Y && X && bias, "bias_relu_rowstats: null argument");
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "bias_relu_rowstats: float and double only");
+  CB_REQUIRE(rows >= 0 && cols >= 1 && cols <= 256 * 32, "bias_relu_rowstats: cols must be in [1, 8192]");
+  CB_REQUIRE(ldx >= cols && ldy >= cols, "bias_relu_rowstats: row pitch smaller than the row");
+  if (rows == 0) return CB200_OK;
+  DeviceGuard guard(s->device);
+  long long cap = (long long)s->sm_count * 16;
+  unsigned blocks = (unsigned)(rows < cap ? rows : cap);
+#define CB_BRS(T)                                                                                          \
+  do {                                                                                                     \
+    if (cols <= 256 * 8) bias_relu_rowstats_k<T, 8><<<blocks, 256, 0, s->stream>>>((T*)Y, ldy, (const T*)X, ldx, (const T*)bias, rows, (int)cols, (T*)rowmax, (T*)rowsum); \
+    else if (cols <= 256 * 16) bias_relu_rowstats_k<T, 16><<<blocks, 256, 0, s->stream>>>((T*)Y, ldy, (const T*)X, ldx, (const T*)bias, rows, (int)cols, (T*)rowmax, (T*)rowsum); \
+    else bias_relu_rowstats_k<T, 32><<<blocks, 256, 0, s->stream>>>((T*)Y, ldy, (const T*)X, ldx, (const T*)bias, rows, (int)cols, (T*)rowmax, (T*)rowsum); \
+  } while (0)
+  if (dtype == CB200_FLOAT) CB_BRS(float); else CB_BRS(double);
+#undef CB_BRS
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+}  // extern "C"

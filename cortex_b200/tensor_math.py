@@ -1,0 +1,145 @@
+"""TensorMath protocol methods (src/cortex/tensor/math.clj:11-252) marshalled onto
+a C ABI.
+
+``CTensorMath`` is a mixin for a stream class that provides
+``_tm(name, *c_args)`` -- "call entry point <prefix><name> for this stream".
+Method names, argument order and meaning are the protocol's; buffers are
+objects with ``.ptr`` / ``.dtype`` and dimensions are the dicts of
+``cortex_b200.dimensions``.
+"""
+import ctypes as C
+
+from . import dimensions as dims_mod
+from ._lib import ACTIVATIONS, BINARY_OPS, DTYPE_CODE, REDUCE_OPS, UNARY_OPS, ConvDesc, Dims
+
+
+def _index_pointer(tensor):
+    if tensor.get_datatype() != "int":
+        raise TypeError("Index buffers must be integer tensors")
+    return tensor.buffer.ptr
+
+
+def wire(dimensions):
+    """dimensions->cuda (src/cortex/compute/cuda/tensor_math.clj:34-51) as a C struct."""
+    rev_shape, rev_strides, ptrs = dims_mod.to_wire(dimensions, _index_pointer)
+    d = Dims()
+    for i in range(5):
+        d.rev_shape[i] = rev_shape[i]
+        d.rev_strides[i] = rev_strides[i]
+        d.index[i] = ptrs[i] or None
+    return d
+
+
+def conv_desc_struct(desc):
+    return ConvDesc(desc["out-channels"], desc["in-channels"], desc["kernel-width"], desc["kernel-height"],
+                    desc["pad-x"], desc["pad-y"], desc["stride-x"], desc["stride-y"])
+
+
+class CTensorMath:
+    def assign_constant(self, buffer, dimensions, value, n_elems):
+        self._tm("assign_constant", DTYPE_CODE[buffer.dtype], buffer.ptr, C.byref(wire(dimensions)), float(value),
+                 int(n_elems))
+
+    def assign(self, dest, dest_dims, src, src_dims, n_elems):
+        self._tm("assign", DTYPE_CODE[dest.dtype], dest.ptr, C.byref(wire(dest_dims)), DTYPE_CODE[src.dtype], src.ptr,
+                 C.byref(wire(src_dims)), int(n_elems))
+
+    def unary_accum(self, dest, dest_dims, alpha, op, n_elems):
+        self._tm("unary_accum", DTYPE_CODE[dest.dtype], dest.ptr, C.byref(wire(dest_dims)), float(alpha),
+                 UNARY_OPS[op], int(n_elems))
+
+    def unary_op(self, dest, dest_dims, x, x_dims, alpha, op, n_elems):
+        self._tm("unary_op", DTYPE_CODE[dest.dtype], dest.ptr, C.byref(wire(dest_dims)), x.ptr, C.byref(wire(x_dims)),
+                 float(alpha), UNARY_OPS[op], int(n_elems))
+
+    def binary_accum_constant(self, dest, dest_dims, dest_alpha, scalar, n_elems, op, reverse_operands):
+        self._tm("binary_accum_constant", DTYPE_CODE[dest.dtype], dest.ptr, C.byref(wire(dest_dims)),
+                 float(dest_alpha), float(scalar), int(n_elems), BINARY_OPS[op], 1 if reverse_operands else 0)
+
+    def binary_op_constant(self, dest, dest_dims, x, x_dims, x_alpha, scalar, n_elems, op, reverse_operands):
+        self._tm("binary_op_constant", DTYPE_CODE[dest.dtype], dest.ptr, C.byref(wire(dest_dims)), x.ptr,
+                 C.byref(wire(x_dims)), float(x_alpha), float(scalar), int(n_elems), BINARY_OPS[op],
+                 1 if reverse_operands else 0)
+
+    def binary_accum(self, dest, dest_dims, dest_alpha, y, y_dims, y_alpha, n_elems, op, reverse_operands,
+                     dest_requires_cas):
+        self._tm("binary_accum", DTYPE_CODE[dest.dtype], dest.ptr, C.byref(wire(dest_dims)), float(dest_alpha),
+                 y.ptr, C.byref(wire(y_dims)), float(y_alpha), int(n_elems), BINARY_OPS[op],
+                 1 if reverse_operands else 0, 1 if dest_requires_cas else 0)
+
+    def binary_op(self, dest, dest_dims, x, x_dims, x_alpha, y, y_dims, y_alpha, n_elems, op):
+        self._tm("binary_op", DTYPE_CODE[dest.dtype], dest.ptr, C.byref(wire(dest_dims)), x.ptr,
+                 C.byref(wire(x_dims)), float(x_alpha), y.ptr, C.byref(wire(y_dims)), float(y_alpha), int(n_elems),
+                 BINARY_OPS[op])
+
+    def unary_reduce(self, output, output_dims, input_alpha, input, input_dims, op):
+        self._tm("unary_reduce", DTYPE_CODE[output.dtype], output.ptr, C.byref(wire(output_dims)), float(input_alpha),
+                 input.ptr, C.byref(wire(input_dims)), REDUCE_OPS[op])
+
+    def gemm(self, c, c_colstride, trans_a, trans_b, alpha, a, a_row_count, a_col_count, a_colstride, b, b_col_count,
+             b_colstride, beta):
+        self._tm("gemm", DTYPE_CODE[c.dtype], c.ptr, int(c_colstride), 1 if trans_a else 0, 1 if trans_b else 0,
+                 float(alpha), a.ptr, int(a_row_count), int(a_col_count), int(a_colstride), b.ptr, int(b_col_count),
+                 int(b_colstride), float(beta))
+
+    def softmax_eltwise(self, output, output_dims, input, input_dims):
+        self._tm("softmax_eltwise", DTYPE_CODE[output.dtype], output.ptr, C.byref(wire(output_dims)), input.ptr,
+                 C.byref(wire(input_dims)))
+
+    def softmax_spatial(self, output, output_dims, input, input_dims):
+        self._tm("softmax_spatial", DTYPE_CODE[output.dtype], output.ptr, C.byref(wire(output_dims)), input.ptr,
+                 C.byref(wire(input_dims)))
+
+    def convolution_descriptor(self, datatype, out_channels, in_channels, kern_width, kern_height, pad_x, pad_y,
+                               stride_x, stride_y):
+        return None   # nothing to create on the device
+
+    def choose_convolution_algorithms(self, conv_descriptor, input_width, input_height, output_width, output_height,
+                                      batch_size, max_ideal_workspace_size, use_defaults):
+        n = C.c_int64()
+        self._tm_nostream("convolution_workspace_size", C.byref(conv_desc_struct(conv_descriptor)), int(input_width),
+                          int(input_height), int(output_width), int(output_height), int(batch_size), C.byref(n))
+        return {"workspace-size": n.value}
+
+    def convolution_forward(self, output, output_dims, output_alpha, input, input_dims, weights, weight_dims,
+                            workspace, workspace_ecount, conv_descriptor, algorithms):
+        self._tm("convolution_forward", DTYPE_CODE[output.dtype], output.ptr, C.byref(wire(output_dims)),
+                 float(output_alpha), input.ptr, C.byref(wire(input_dims)), weights.ptr, C.byref(wire(weight_dims)),
+                 workspace.ptr if workspace is not None else None, int(workspace_ecount),
+                 C.byref(conv_desc_struct(conv_descriptor)))
+
+    # --- fused extras (no protocol counterpart) ----------------------------------
+    def gemm_bias_act(self, c, c_colstride, trans_a, trans_b, alpha, a, a_row_count, a_col_count, a_colstride, b,
+                      b_col_count, b_colstride, beta, bias, act):
+        self._tm("gemm_bias_act", DTYPE_CODE[c.dtype], c.ptr, int(c_colstride), 1 if trans_a else 0,
+                 1 if trans_b else 0, float(alpha), a.ptr, int(a_row_count), int(a_col_count), int(a_colstride),
+                 b.ptr, int(b_col_count), int(b_colstride), float(beta), bias.ptr if bias is not None else None,
+                 ACTIVATIONS[act])
+
+    def bias_relu_rowstats(self, y, ldy, x, ldx, bias, rows, cols, rowmax, rowsum):
+        self._tm("bias_relu_rowstats", DTYPE_CODE[y.dtype], y.ptr, int(ldy), x.ptr, int(ldx), bias.ptr, int(rows),
+                 int(cols), rowmax.ptr if rowmax is not None else None, rowsum.ptr if rowsum is not None else None)
+
+    def _tm_nostream(self, name, *args):
+        from ._lib import call
+        return call("cb200_" + name, *args)
+
+    # --- protocol methods outside the dense-inference path -----------------------
+    def _unsupported(self, name):
+        from ._lib import call
+        call("cb200_unsupported", name.encode())
+
+    def ternary_op(self, *a):
+        self._unsupported("ternary-op!")
+
+    def gemv(self, *a):
+        self._unsupported("gemv!")
+
+    def batch_normalize_eltwise(self, *a):
+        self._unsupported("batch-normalize-eltwise!")
+
+    def pooling_forward(self, *a):
+        self._unsupported("pooling-forward!")
+
+    def rand(self, *a):
+        self._unsupported("rand!")

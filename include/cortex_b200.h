@@ -1,0 +1,226 @@
+/*
+ * cortex_b200 -- C ABI of the B200 (sm_100a) compute backend for cortex's
+ * dense-layer hot path.
+ *
+ * Every entry point mirrors one method of the reference's backend protocols:
+ *   - operator boundary:  cortex.tensor.math/TensorMath   (src/cortex/tensor/math.clj:11-252)
+ *   - device boundary:    cortex.compute.driver protocols (src/cortex/compute/driver.clj:46-203)
+ * The argument order and meaning follow the protocol method named in each
+ * comment, so a Clojure (JNA / JavaCPP) shim is a 1:1 forwarder.
+ *
+ * Conventions
+ *   - Every function returns 0 on success, a CB200_ERR_* code otherwise;
+ *     cb200_last_error() returns a thread-local message for the last failure.
+ *   - Buffers are raw device pointers.  Offsets/sub-buffers are pointer
+ *     arithmetic done by the caller (as src/cortex/compute/cuda/driver.clj:465-506).
+ *   - Scalars travel as double and are cast to the element type of the
+ *     destination before use (drv/dtype-cast, src/cortex/compute/cuda/tensor_math.clj:293).
+ *   - Nothing here aborts the process or traps on the device.
+ *   - The stream handle carries its device; there is no process-global
+ *     "current device / current stream" state, so N host threads x N streams
+ *     are safe (src/cortex/verify/nn/train.clj:211-236 is the usage model).
+ */
+#ifndef CORTEX_B200_H
+#define CORTEX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enumerations (numbered as the reference's wire format) ------------- */
+
+/* resources/datatypes.h:81-92, src/cortex/compute/cuda/driver.clj:354-367 */
+enum cb200_dtype {
+  CB200_BYTE = 0, CB200_SHORT = 1, CB200_INT = 2, CB200_LONG = 3,
+  CB200_FLOAT = 4, CB200_DOUBLE = 5
+};
+
+/* src/cortex/compute/cuda/tensor_math.clj:54-72, resources/operations.h:27-45 */
+enum cb200_binary_op {
+  CB200_ADD = 0, CB200_SUB = 1, CB200_MUL = 2, CB200_DIV = 3, CB200_MIN = 4,
+  CB200_MAX = 5, CB200_BIT_AND = 6, CB200_BIT_XOR = 7, CB200_EQ = 8,
+  CB200_GT = 9, CB200_GE = 10, CB200_LT = 11, CB200_LE = 12
+};
+
+/* src/cortex/compute/cuda/tensor_math.clj:75-92, resources/operations.h:88-102 */
+enum cb200_unary_op {
+  CB200_FLOOR = 0, CB200_CEIL = 1, CB200_ROUND = 2, CB200_NEG = 3,
+  CB200_TANH = 4, CB200_LOGISTIC = 5, CB200_EXP = 6, CB200_SQRT = 7,
+  CB200_NOOP = 8
+};
+
+/* src/cortex/compute/cuda/tensor_math.clj:624-630, resources/tensor_unary_reduce.cu:9-20 */
+enum cb200_reduce_op {
+  CB200_RMAX = 0, CB200_RMIN = 1, CB200_RSUM = 2, CB200_RMEAN = 3,
+  CB200_RMAGNITUDE = 4, CB200_RMAGNITUDE_SQ = 5
+};
+
+/* epilogue activations of the fused extras (no protocol counterpart) */
+enum cb200_act { CB200_ACT_NONE = 0, CB200_ACT_RELU = 1, CB200_ACT_TANH = 2, CB200_ACT_LOGISTIC = 3 };
+
+enum cb200_status {
+  CB200_OK = 0,
+  CB200_ERR_INVALID = 1,      /* bad argument / descriptor            */
+  CB200_ERR_UNSUPPORTED = 2,  /* protocol method outside the hot path */
+  CB200_ERR_CUDA = 3,         /* CUDA runtime / driver error          */
+  CB200_ERR_TIMEOUT = 4,      /* a bounded device-side wait ran out   */
+  CB200_ERR_NOMEM = 5
+};
+
+/* ---- tensor descriptor ---------------------------------------------------
+ * Wire format of one operand: what dimensions->cuda builds
+ * (src/cortex/compute/cuda/tensor_math.clj:34-51) and what
+ * resources/index_system.h:16-41 consumes: shape and strides reversed
+ * (fastest-changing dimension first), padded to 5 with shape 1 and the
+ * outermost stride, plus one optional int32 index array per dimension
+ * (NULL = direct).  When index[d] is set, rev_shape[d] is the number of
+ * entries of that index array.                                              */
+typedef struct cb200_dims {
+  int32_t rev_shape[5];
+  int32_t rev_strides[5];
+  const int32_t* index[5];
+} cb200_dims;
+
+/* convolution-descriptor fields (src/cortex/tensor.clj:1322-1348) */
+typedef struct cb200_conv_desc {
+  int32_t out_channels, in_channels;
+  int32_t kernel_width, kernel_height;
+  int32_t pad_x, pad_y;
+  int32_t stride_x, stride_y;
+} cb200_conv_desc;
+
+typedef struct cb200_stream cb200_stream;  /* device + CUDA stream + status word */
+typedef struct cb200_event cb200_event;
+
+/* ---- errors -------------------------------------------------------------- */
+/* check-cuda-error: src/cortex/compute/cuda/driver.clj:40-49 */
+const char* cb200_last_error(void);
+
+/* ---- PDriver / PDevice (src/cortex/compute/driver.clj:46-61, 74-84) ------ */
+/* get-devices */
+int cb200_device_count(int* count);
+int cb200_device_info(int device, char* name, int name_len, int* sm_count,
+                      int* cc_major, int* cc_minor);
+/* memory-info-impl */
+int cb200_mem_info(int device, size_t* free_bytes, size_t* total_bytes);
+/* create-stream-impl */
+int cb200_stream_create(int device, cb200_stream** out);
+int cb200_stream_destroy(cb200_stream* s);
+/* raw cudaStream_t of the stream (for NCCL / interop), as void* */
+void* cb200_stream_native(cb200_stream* s);
+int cb200_stream_device(cb200_stream* s);
+/* allocate-device-buffer-impl */
+int cb200_malloc(int device, size_t bytes, void** out);
+int cb200_free(int device, void* ptr);
+/* allocate-host-buffer-impl (page-locked: src/cortex/compute/cuda/driver.clj:522-542) */
+int cb200_host_alloc(size_t bytes, void** out);
+int cb200_host_free(void* ptr);
+
+/* ---- PStream / PEvent (src/cortex/compute/driver.clj:180-203) ------------ */
+/* copy-host->device / copy-device->host / copy-device->device (sizes in bytes) */
+int cb200_memcpy_h2d(cb200_stream* s, void* dst_dev, const void* src_host, size_t bytes);
+int cb200_memcpy_d2h(cb200_stream* s, void* dst_host, const void* src_dev, size_t bytes);
+int cb200_memcpy_d2d(cb200_stream* s, void* dst_dev, const void* src_dev, size_t bytes);
+/* memset [stream device-buffer device-offset elem-val elem-count] */
+int cb200_memset(cb200_stream* s, int dtype, void* buf, int64_t elem_offset,
+                 double value, int64_t n_elems);
+/* create-event: records an event on the stream.  timing != 0 keeps timestamps
+ * (the reference creates its events with cudaEventDisableTiming,
+ * src/cortex/compute/cuda/driver.clj:935-940; timing is an addition). */
+int cb200_event_record(cb200_stream* s, int timing, cb200_event** out);
+/* sync-event: make `s` wait for the event */
+int cb200_stream_wait_event(cb200_stream* s, cb200_event* e);
+/* wait-for-event: block the host; also surfaces asynchronous kernel errors
+ * (CUDA errors and bounded-wait timeouts recorded in the stream's status word) */
+int cb200_event_wait(cb200_event* e);
+int cb200_event_elapsed_ms(cb200_event* start, cb200_event* stop, float* ms);
+int cb200_event_destroy(cb200_event* e);
+/* sync-stream (driver.clj:206-211) */
+int cb200_stream_sync(cb200_stream* s);
+
+/* ---- TensorMath (src/cortex/tensor/math.clj) ------------------------------ */
+/* assign-constant! :14 */
+int cb200_assign_constant(cb200_stream* s, int dtype, void* buf, const cb200_dims* dims,
+                          double value, int64_t n_elems);
+/* assign! :16-24 (marshals between any two dtypes) */
+int cb200_assign(cb200_stream* s, int dest_dtype, void* dest, const cb200_dims* dest_dims,
+                 int src_dtype, const void* src, const cb200_dims* src_dims, int64_t n_elems);
+/* unary-accum! :26-28   dest = op(alpha*dest) */
+int cb200_unary_accum(cb200_stream* s, int dtype, void* dest, const cb200_dims* dest_dims,
+                      double alpha, int op, int64_t n_elems);
+/* unary-op! :30-33      dest = op(alpha*x) */
+int cb200_unary_op(cb200_stream* s, int dtype, void* dest, const cb200_dims* dest_dims,
+                   const void* x, const cb200_dims* x_dims, double alpha, int op, int64_t n_elems);
+/* binary-accum-constant! :35-40   dest = (alpha*dest) op scalar   (reversed when rev_ops) */
+int cb200_binary_accum_constant(cb200_stream* s, int dtype, void* dest, const cb200_dims* dest_dims,
+                                double dest_alpha, double scalar, int64_t n_elems, int op, int rev_ops);
+/* binary-op-constant! :42-48      dest = (alpha*x) op scalar */
+int cb200_binary_op_constant(cb200_stream* s, int dtype, void* dest, const cb200_dims* dest_dims,
+                             const void* x, const cb200_dims* x_dims, double x_alpha,
+                             double scalar, int64_t n_elems, int op, int rev_ops);
+/* binary-accum! :50-61            dest = (alpha*dest) op (beta*y); requires_cas when several
+ * element indexes land on one dest address (dest smaller than the op, or indexed) */
+int cb200_binary_accum(cb200_stream* s, int dtype, void* dest, const cb200_dims* dest_dims,
+                       double dest_alpha, const void* y, const cb200_dims* y_dims, double y_alpha,
+                       int64_t n_elems, int op, int rev_ops, int requires_cas);
+/* binary-op! :63-69               dest = (alpha*x) op (beta*y) */
+int cb200_binary_op(cb200_stream* s, int dtype, void* dest, const cb200_dims* dest_dims,
+                    const void* x, const cb200_dims* x_dims, double x_alpha,
+                    const void* y, const cb200_dims* y_dims, double y_alpha,
+                    int64_t n_elems, int op);
+/* unary-reduce! :100-104          out[..., 0] = reduce_j (alpha * in[..., j]) */
+int cb200_unary_reduce(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims,
+                       double alpha, const void* in, const cb200_dims* in_dims, int op);
+/* gemm! :106-115   C = alpha*op(A)*op(B) + beta*C, row-major, ld* = row pitch in elements.
+ * a_rows/a_cols are those of op(A) (M, K); b_cols is that of op(B) (N). float and double only. */
+int cb200_gemm(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b,
+               double alpha, const void* A, int64_t a_rows, int64_t a_cols, int64_t lda,
+               const void* B, int64_t b_cols, int64_t ldb, double beta);
+/* softmax-eltwise! :177-179 / softmax-spatial! :181-183 */
+int cb200_softmax_eltwise(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims,
+                          const void* in, const cb200_dims* in_dims);
+int cb200_softmax_spatial(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims,
+                          const void* in, const cb200_dims* in_dims);
+/* choose-convolution-algorithms :191-195 -> workspace element count (this backend needs none
+ * and reports 1 so that callers can still allocate a non-empty tensor) */
+int cb200_convolution_workspace_size(const cb200_conv_desc* desc, int in_w, int in_h,
+                                     int out_w, int out_h, int batch, int64_t* n_elems);
+/* convolution-forward! :197-203   NCHW cross-correlation:
+ * out = conv(in, w) + out_alpha * out ; workspace may be NULL */
+int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims,
+                              double out_alpha, const void* in, const cb200_dims* in_dims,
+                              const void* w, const cb200_dims* w_dims,
+                              void* workspace, int64_t workspace_ecount,
+                              const cb200_conv_desc* desc);
+
+/* Protocol methods outside the dense-inference path return CB200_ERR_UNSUPPORTED:
+ * ternary-op*, gemv!, batch-normalize-*, activation-gradient!, convolution-backward-*,
+ * pooling-*, rand!, lrn-* (src/cortex/tensor/math.clj:71-98, 116-175, 205-250). */
+int cb200_unsupported(const char* method_name);
+
+/* ---- fused extras (no counterpart in the protocol) -------------------------
+ * What nn-backend/biased-multiply! + the following ActivationLayer issue as three
+ * calls (src/cortex/compute/nn/backend.clj:98-112, src/cortex/compute/nn/layers.clj:91-103):
+ *   C = act(alpha*op(A)*op(B) + beta*C + bias)   bias: [N] broadcast over rows, or NULL */
+int cb200_gemm_bias_act(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b,
+                        double alpha, const void* A, int64_t a_rows, int64_t a_cols, int64_t lda,
+                        const void* B, int64_t b_cols, int64_t ldb, double beta,
+                        const void* bias, int act);
+/* One pass over X[rows, cols] (pitch ldx): Y = max(X + bias, 0), rowmax[r] = max_j Y[r,j],
+ * rowsum[r] = sum_j Y[r,j].  float/double.  Y may alias X; rowmax/rowsum may be NULL. */
+int cb200_bias_relu_rowstats(cb200_stream* s, int dtype, void* Y, int64_t ldy, const void* X,
+                             int64_t ldx, const void* bias, int64_t rows, int64_t cols,
+                             void* rowmax, void* rowsum);
+
+/* number of kernels this library has launched on the stream since creation */
+int64_t cb200_launch_count(cb200_stream* s);
+/* read and clear the stream's device-side status word (0 = clean) */
+int cb200_stream_status(cb200_stream* s, int* code, int* detail);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CORTEX_B200_H */

@@ -1,0 +1,465 @@
+/*
+ * oracle.c -- TEST INFRASTRUCTURE, not product code.
+ *
+ * A plain-C restatement, on host memory, of the reference CPU backend's
+ * algorithm for the dense-inference hot path
+ * (src/cortex/compute/cpu/tensor_math.clj of originrose/cortex).  Only tests/,
+ * the smoke check and the cpu_baseline / reference arms of bench.py may load
+ * it; the product (cortex_b200/) never does.
+ *
+ * Parity pin: every function here is checked against the literal expected
+ * vectors of the reference's own verification suite
+ * (src/cortex/verify/tensor.clj, src/cortex/verify/nn/layers.clj), transcribed
+ * in tests/verify_tensor.py.  The reference itself (Clojure/JVM) cannot run in
+ * this environment, and its GEMM arithmetic lives in an un-vendored dependency
+ * (com.github.fommil.netlib/all 1.1.2, BLAS sgemm/dgemm): orc_gemm restates the
+ * published reference-BLAS loop nest; rounding-level parity of large GEMMs is
+ * unpinned by the reference (its tests use small integers).
+ *
+ * Arithmetic rules restated (file:line are the reference's):
+ *  - float views are widened to double for *, +, max ... and rounded once by
+ *    the final cast (datatype->cast-fn, cpu/driver.clj:149-157; uses at
+ *    cpu/tensor_math.clj:259-262, 446-450); integer views are widened to long,
+ *    wrap, and are narrowed by truncation (unchecked math).
+ *  - double -> integer narrowing saturates, NaN -> 0 (JVM d2i / d2l).
+ *  - scalars are cast to the element type first (cpu/tensor_math.clj:145, 233).
+ *  - reductions fold left to right in the accumulator type (:588-629).
+ *  - softmax: max, exp(x - max) stored in the element type, sum of the stored
+ *    values in double, in-place divide in the element type (:1037-1088).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+typedef struct orc_dims {
+  int32_t rev_shape[5];
+  int32_t rev_strides[5];
+  const int32_t* index[5];
+} orc_dims;
+
+typedef struct orc_conv_desc {
+  int32_t out_channels, in_channels, kernel_width, kernel_height, pad_x, pad_y, stride_x, stride_y;
+} orc_conv_desc;
+
+enum { T_BYTE = 0, T_SHORT, T_INT, T_LONG, T_FLOAT, T_DOUBLE };
+enum { B_ADD = 0, B_SUB, B_MUL, B_DIV, B_MIN, B_MAX, B_AND, B_XOR, B_EQ, B_GT, B_GE, B_LT, B_LE };
+enum { U_FLOOR = 0, U_CEIL, U_ROUND, U_NEG, U_TANH, U_LOGISTIC, U_EXP, U_SQRT, U_NOOP };
+enum { R_MAX = 0, R_MIN, R_SUM, R_MEAN, R_MAG, R_MAGSQ };
+
+/* ---- JVM narrowing ---------------------------------------------------------- */
+static int32_t d2i(double v) {
+  if (v != v) return 0;
+  if (v >= 2147483647.0) return INT32_MAX;
+  if (v <= -2147483648.0) return INT32_MIN;
+  return (int32_t)v;
+}
+static int64_t d2l(double v) {
+  if (v != v) return 0;
+  if (v >= 9223372036854775807.0) return INT64_MAX;
+  if (v <= -9223372036854775808.0) return INT64_MIN;
+  return (int64_t)v;
+}
+static int64_t jvm_round(double a) { /* Math/round: floor(a + 1/2), exact */
+  if (a != a) return 0;
+  double r = floor(a);
+  if (a - r >= 0.5) r += 1.0;
+  return d2l(r);
+}
+
+/* ---- index system (src/cortex/tensor/dimensions.clj:226-277) ------------------ */
+static void max_shape_of(int32_t* mx, const orc_dims* a, const orc_dims* b, const orc_dims* c) {
+  for (int d = 0; d < 5; ++d) {
+    int32_t m = a->rev_shape[d];
+    if (b && b->rev_shape[d] > m) m = b->rev_shape[d];
+    if (c && c->rev_shape[d] > m) m = c->rev_shape[d];
+    mx[d] = m;
+  }
+}
+static int64_t addr_of(const orc_dims* o, const int32_t* mx, int64_t arg) {
+  int64_t off = 0;
+  for (int d = 0; d < 5; ++d) {
+    int64_t idx = arg % o->rev_shape[d];
+    if (o->index[d]) idx = o->index[d][idx];
+    off += (int64_t)o->rev_strides[d] * idx;
+    arg /= mx[d];
+  }
+  return off;
+}
+/* SimpleElemIdxToAddr fast path (cpu/tensor_math.clj:90-97): direct, dense, shape == max-shape */
+static int is_simple(const orc_dims* o, const int32_t* mx) {
+  int64_t e = 1;
+  for (int d = 0; d < 5; ++d) {
+    if (o->index[d] || o->rev_shape[d] != mx[d]) return 0;
+    if (o->rev_shape[d] > 1 && o->rev_strides[d] != e) return 0;
+    e *= o->rev_shape[d];
+  }
+  return 1;
+}
+#define ADDR(o, simple, mx, i) ((simple) ? (i) : addr_of((o), (mx), (i)))
+
+/* ---- per-type accumulator views ------------------------------------------------- */
+/* integer element types compute in int64 (wrapping), floating ones in double */
+#define FOR_INT_TYPES(X) X(T_BYTE, int8_t) X(T_SHORT, int16_t) X(T_INT, int32_t) X(T_LONG, int64_t)
+#define FOR_FLT_TYPES(X) X(T_FLOAT, float) X(T_DOUBLE, double)
+
+static int64_t wrap_mul(int64_t a, int64_t b) { return (int64_t)((uint64_t)a * (uint64_t)b); }
+static int64_t wrap_add(int64_t a, int64_t b) { return (int64_t)((uint64_t)a + (uint64_t)b); }
+static int64_t wrap_sub(int64_t a, int64_t b) { return (int64_t)((uint64_t)a - (uint64_t)b); }
+
+static double bin_d(int op, double a, double b) { /* perform-operation-impl, cpu/tensor_math.clj:278-308 */
+  switch (op) {
+    case B_ADD: return a + b;
+    case B_SUB: return a - b;
+    case B_MUL: return a * b;
+    case B_DIV: return a / b;
+    case B_MAX: return a > b ? a : b;
+    case B_MIN: return a > b ? b : a;
+    case B_AND: return (double)(d2i(a) & d2i(b));
+    case B_XOR: return (double)(d2i(a) ^ d2i(b));
+    case B_EQ: return a == b;
+    case B_GT: return a > b;
+    case B_GE: return a >= b;
+    case B_LT: return a < b;
+    case B_LE: return a <= b;
+  }
+  return 0;
+}
+static int64_t bin_l(int op, int64_t a, int64_t b) {
+  switch (op) {
+    case B_ADD: return wrap_add(a, b);
+    case B_SUB: return wrap_sub(a, b);
+    case B_MUL: return wrap_mul(a, b);
+    case B_DIV: /* (/ long long) is an exact Ratio, truncated toward zero by the cast; /0 throws in the reference */
+      if (b == 0) return 0;
+      if (b == -1) return wrap_sub(0, a);
+      return a / b;
+    case B_MAX: return a > b ? a : b;
+    case B_MIN: return a > b ? b : a;
+    case B_AND: return (int64_t)((int32_t)a & (int32_t)b);
+    case B_XOR: return (int64_t)((int32_t)a ^ (int32_t)b);
+    case B_EQ: return a == b;
+    case B_GT: return a > b;
+    case B_GE: return a >= b;
+    case B_LT: return a < b;
+    case B_LE: return a <= b;
+  }
+  return 0;
+}
+
+/* store helpers: value in accumulator type -> element type */
+#define ST_float_d(v) ((float)(v))
+#define ST_double_d(v) ((double)(v))
+#define ST_int8_t_d(v) ((int8_t)d2i(v))
+#define ST_int16_t_d(v) ((int16_t)d2i(v))
+#define ST_int32_t_d(v) (d2i(v))
+#define ST_int64_t_d(v) (d2l(v))
+#define ST_float_l(v) ((float)(v))
+#define ST_double_l(v) ((double)(v))
+#define ST_int8_t_l(v) ((int8_t)(v))
+#define ST_int16_t_l(v) ((int16_t)(v))
+#define ST_int32_t_l(v) ((int32_t)(v))
+#define ST_int64_t_l(v) ((int64_t)(v))
+
+/* scalar cast to the element type, returned in the accumulator type */
+#define SCALAR_float(v) ((double)(float)(v))
+#define SCALAR_double(v) ((double)(v))
+#define SCALAR_int8_t(v) ((int64_t)(int8_t)d2i(v))
+#define SCALAR_int16_t(v) ((int64_t)(int16_t)d2i(v))
+#define SCALAR_int32_t(v) ((int64_t)d2i(v))
+#define SCALAR_int64_t(v) (d2l(v))
+
+/* ---- assign ------------------------------------------------------------------------ */
+int orc_memset(int dtype, void* buf, int64_t off, double value, int64_t n) {
+  switch (dtype) {
+#define X(code, T) case code: { T* p = (T*)buf + off; T v = ST_##T##_d(value); for (int64_t i = 0; i < n; ++i) p[i] = v; return 0; }
+    FOR_INT_TYPES(X) FOR_FLT_TYPES(X)
+#undef X
+  }
+  return 1;
+}
+
+int orc_assign_constant(int dtype, void* buf, const orc_dims* dims, double value, int64_t n) {
+  int32_t mx[5];
+  max_shape_of(mx, dims, NULL, NULL);
+  int s = is_simple(dims, mx);
+  switch (dtype) {
+#define X(code, T) case code: { T* p = (T*)buf; T v = ST_##T##_d(value); \
+    _Pragma("omp parallel for") for (int64_t i = 0; i < n; ++i) p[ADDR(dims, s, mx, i)] = v; return 0; }
+    FOR_INT_TYPES(X) FOR_FLT_TYPES(X)
+#undef X
+  }
+  return 1;
+}
+
+/* marshalling assign: (datatype->cast-fn lhs (v-aget src ...)), cpu/tensor_math.clj:180-197 */
+#define ASSIGN_INNER_FROM_INT(TD, TS) { const TS* sp = (const TS*)src; TD* dp = (TD*)dest; \
+    _Pragma("omp parallel for") for (int64_t i = 0; i < n; ++i) { int64_t v = (int64_t)sp[ADDR(sd, ss, mx, i)]; dp[ADDR(dd, ds, mx, i)] = ST_##TD##_l(v); } return 0; }
+#define ASSIGN_INNER_FROM_FLT(TD, TS) { const TS* sp = (const TS*)src; TD* dp = (TD*)dest; \
+    _Pragma("omp parallel for") for (int64_t i = 0; i < n; ++i) { double v = (double)sp[ADDR(sd, ss, mx, i)]; dp[ADDR(dd, ds, mx, i)] = ST_##TD##_d(v); } return 0; }
+
+#define ASSIGN_DEST_SWITCH(INNER, TS) switch (ddt) { \
+    case T_BYTE: INNER(int8_t, TS) case T_SHORT: INNER(int16_t, TS) case T_INT: INNER(int32_t, TS) \
+    case T_LONG: INNER(int64_t, TS) case T_FLOAT: INNER(float, TS) case T_DOUBLE: INNER(double, TS) } break;
+
+int orc_assign(int ddt, void* dest, const orc_dims* dd, int sdt, const void* src, const orc_dims* sd, int64_t n) {
+  int32_t mx[5];
+  max_shape_of(mx, dd, sd, NULL);
+  int ds = is_simple(dd, mx), ss = is_simple(sd, mx);
+  switch (sdt) {
+    case T_BYTE: ASSIGN_DEST_SWITCH(ASSIGN_INNER_FROM_INT, int8_t)
+    case T_SHORT: ASSIGN_DEST_SWITCH(ASSIGN_INNER_FROM_INT, int16_t)
+    case T_INT: ASSIGN_DEST_SWITCH(ASSIGN_INNER_FROM_INT, int32_t)
+    case T_LONG: ASSIGN_DEST_SWITCH(ASSIGN_INNER_FROM_INT, int64_t)
+    case T_FLOAT: ASSIGN_DEST_SWITCH(ASSIGN_INNER_FROM_FLT, float)
+    case T_DOUBLE: ASSIGN_DEST_SWITCH(ASSIGN_INNER_FROM_FLT, double)
+  }
+  return 1;
+}
+
+/* ---- unary (cpu/tensor_math.clj:211-262) ------------------------------------------------ */
+#define UNARY_BODY_FLT(T) { const T* xp = (const T*)x; T* dp = (T*)dest; double a = SCALAR_##T(alpha); \
+  PAR for (int64_t i = 0; i < n; ++i) { double v = (double)xp[ADDR(xd, xs, mx, i)] * a; T r; \
+    switch (op) { case U_FLOOR: r = ST_##T##_d(floor(v)); break; case U_CEIL: r = ST_##T##_d(ceil(v)); break; \
+      case U_ROUND: r = ST_##T##_l(jvm_round(v)); break; case U_NEG: r = ST_##T##_d(-v); break; \
+      case U_TANH: r = ST_##T##_d(tanh(v)); break; case U_LOGISTIC: r = ST_##T##_d(1.0 / (1.0 + exp(-v))); break; \
+      case U_EXP: r = ST_##T##_d(exp(v)); break; case U_SQRT: r = ST_##T##_d(sqrt(v)); break; default: r = ST_##T##_d(v); } \
+    dp[ADDR(dd, ds, mx, i)] = r; } return 0; }
+#define UNARY_BODY_INT(T) { const T* xp = (const T*)x; T* dp = (T*)dest; int64_t a = SCALAR_##T(alpha); \
+  PAR for (int64_t i = 0; i < n; ++i) { int64_t lv = wrap_mul((int64_t)xp[ADDR(xd, xs, mx, i)], a); double v = (double)lv; T r; \
+    switch (op) { case U_FLOOR: r = ST_##T##_d(floor(v)); break; case U_CEIL: r = ST_##T##_d(ceil(v)); break; \
+      case U_ROUND: r = ST_##T##_l(jvm_round(v)); break; case U_NEG: r = ST_##T##_l(wrap_sub(0, lv)); break; \
+      case U_TANH: r = ST_##T##_d(tanh(v)); break; case U_LOGISTIC: r = ST_##T##_d(1.0 / (1.0 + exp(-(double)lv))); break; \
+      case U_EXP: r = ST_##T##_d(exp(v)); break; case U_SQRT: r = ST_##T##_d(sqrt(v)); break; default: r = ST_##T##_d(v); } \
+    dp[ADDR(dd, ds, mx, i)] = r; } return 0; }
+
+static int unary_impl(int dtype, void* dest, const orc_dims* dd, const void* x, const orc_dims* xd, double alpha,
+                      int op, int64_t n, int serial) {
+  int32_t mx[5];
+  max_shape_of(mx, dd, xd, NULL);
+  int ds = is_simple(dd, mx), xs = is_simple(xd, mx);
+  if (serial) {
+#define PAR
+    switch (dtype) {
+      case T_BYTE: UNARY_BODY_INT(int8_t) case T_SHORT: UNARY_BODY_INT(int16_t) case T_INT: UNARY_BODY_INT(int32_t)
+      case T_LONG: UNARY_BODY_INT(int64_t) case T_FLOAT: UNARY_BODY_FLT(float) case T_DOUBLE: UNARY_BODY_FLT(double)
+    }
+#undef PAR
+  } else {
+#define PAR _Pragma("omp parallel for")
+    switch (dtype) {
+      case T_BYTE: UNARY_BODY_INT(int8_t) case T_SHORT: UNARY_BODY_INT(int16_t) case T_INT: UNARY_BODY_INT(int32_t)
+      case T_LONG: UNARY_BODY_INT(int64_t) case T_FLOAT: UNARY_BODY_FLT(float) case T_DOUBLE: UNARY_BODY_FLT(double)
+    }
+#undef PAR
+  }
+  return 1;
+}
+int orc_unary_op(int dtype, void* dest, const orc_dims* dd, const void* x, const orc_dims* xd, double alpha, int op,
+                 int64_t n) {
+  return unary_impl(dtype, dest, dd, x, xd, alpha, op, n, 0);
+}
+/* unary-accum! is a serial c-for in the reference (cpu/tensor_math.clj:226-241) */
+int orc_unary_accum(int dtype, void* dest, const orc_dims* dd, double alpha, int op, int64_t n) {
+  return unary_impl(dtype, dest, dd, dest, dd, alpha, op, n, 1);
+}
+
+/* ---- binary (cpu/tensor_math.clj:311-462) ------------------------------------------------ */
+/* mode: y_is_scalar -> second operand is `scalar`; rev -> operands swapped */
+#define BIN_BODY(T, ACC, BINF, SUF) { const T* xp = (const T*)x; const T* yp = (const T*)y; T* dp = (T*)dest; \
+  ACC xa_ = SCALAR_##T(xa); ACC ya_ = SCALAR_##T(ya); ACC sc = SCALAR_##T(scalar); \
+  PAR for (int64_t i = 0; i < n; ++i) { \
+    int64_t da = ADDR(dd, ds, mx, i); \
+    ACC a = MUL_##SUF((ACC)xp[x_is_dest ? da : ADDR(xd, xs, mx, i)], xa_); \
+    ACC b = y_is_scalar ? sc : MUL_##SUF((ACC)yp[ADDR(yd, ys, mx, i)], ya_); \
+    ACC r = rev ? BINF(op, b, a) : BINF(op, a, b); \
+    dp[da] = ST_##T##_##SUF(r); } return 0; }
+#define MUL_d(a, b) ((a) * (b))
+#define MUL_l(a, b) wrap_mul((a), (b))
+
+static int binary_impl(int dtype, void* dest, const orc_dims* dd, const void* x, const orc_dims* xd, double xa,
+                       const void* y, const orc_dims* yd, double ya, double scalar, int y_is_scalar, int x_is_dest,
+                       int rev, int op, int64_t n, int serial) {
+  int32_t mx[5];
+  max_shape_of(mx, dd, x_is_dest ? NULL : xd, y_is_scalar ? NULL : yd);
+  int ds = is_simple(dd, mx), xs = x_is_dest ? ds : is_simple(xd, mx), ys = y_is_scalar ? 1 : is_simple(yd, mx);
+  if (y_is_scalar) { y = x; yd = xd; }
+  if (serial) {
+#define PAR
+    switch (dtype) {
+      case T_BYTE: BIN_BODY(int8_t, int64_t, bin_l, l) case T_SHORT: BIN_BODY(int16_t, int64_t, bin_l, l)
+      case T_INT: BIN_BODY(int32_t, int64_t, bin_l, l) case T_LONG: BIN_BODY(int64_t, int64_t, bin_l, l)
+      case T_FLOAT: BIN_BODY(float, double, bin_d, d) case T_DOUBLE: BIN_BODY(double, double, bin_d, d)
+    }
+#undef PAR
+  } else {
+#define PAR _Pragma("omp parallel for")
+    switch (dtype) {
+      case T_BYTE: BIN_BODY(int8_t, int64_t, bin_l, l) case T_SHORT: BIN_BODY(int16_t, int64_t, bin_l, l)
+      case T_INT: BIN_BODY(int32_t, int64_t, bin_l, l) case T_LONG: BIN_BODY(int64_t, int64_t, bin_l, l)
+      case T_FLOAT: BIN_BODY(float, double, bin_d, d) case T_DOUBLE: BIN_BODY(double, double, bin_d, d)
+    }
+#undef PAR
+  }
+  return 1;
+}
+
+int orc_binary_op(int dtype, void* dest, const orc_dims* dd, const void* x, const orc_dims* xd, double xa,
+                  const void* y, const orc_dims* yd, double ya, int64_t n, int op) {
+  return binary_impl(dtype, dest, dd, x, xd, xa, y, yd, ya, 0, 0, 0, 0, op, n, 0);
+}
+int orc_binary_op_constant(int dtype, void* dest, const orc_dims* dd, const void* x, const orc_dims* xd, double xa,
+                           double scalar, int64_t n, int op, int rev) {
+  return binary_impl(dtype, dest, dd, x, xd, xa, NULL, NULL, 0, scalar, 1, 0, rev, op, n, 0);
+}
+/* the accum forms are serial c-for loops in the reference: repeated dest addresses fold in index order */
+int orc_binary_accum_constant(int dtype, void* dest, const orc_dims* dd, double da, double scalar, int64_t n, int op,
+                              int rev) {
+  return binary_impl(dtype, dest, dd, dest, dd, da, NULL, NULL, 0, scalar, 1, 1, rev, op, n, 1);
+}
+int orc_binary_accum(int dtype, void* dest, const orc_dims* dd, double da, const void* y, const orc_dims* yd, double ya,
+                     int64_t n, int op, int rev, int requires_cas) {
+  (void)requires_cas;
+  return binary_impl(dtype, dest, dd, dest, dd, da, y, yd, ya, 0, 0, 1, rev, op, n, 1);
+}
+
+/* ---- unary-reduce (cpu/tensor_math.clj:588-663) ------------------------------------------- */
+static double clj_max_d(double a, double b) { return (a != a) ? a : ((b != b) ? b : (a > b ? a : b)); }
+static double clj_min_d(double a, double b) { return (a != a) ? a : ((b != b) ? b : (a < b ? a : b)); }
+
+#define REDUCE_BODY_FLT(T) { const T* ip = (const T*)in; T* op_ = (T*)out; double a = SCALAR_##T(alpha); \
+  _Pragma("omp parallel for") for (int64_t r = 0; r < n_out; ++r) { int64_t s0 = r * len; \
+    double v = a * (double)ip[ADDR(id, is, imx, s0)]; double acc = (op == R_MAG || op == R_MAGSQ) ? v * v : v; \
+    for (int64_t j = 1; j < len; ++j) { v = a * (double)ip[ADDR(id, is, imx, s0 + j)]; \
+      switch (op) { case R_MAX: acc = clj_max_d(acc, v); break; case R_MIN: acc = clj_min_d(acc, v); break; \
+        case R_MAG: case R_MAGSQ: acc += v * v; break; default: acc += v; } } \
+    if (op == R_MEAN) acc = acc / (double)len; if (op == R_MAG) acc = sqrt(acc); \
+    op_[ADDR(od, os, omx, r)] = ST_##T##_d(acc); } return 0; }
+#define REDUCE_BODY_INT(T) { const T* ip = (const T*)in; T* op_ = (T*)out; int64_t a = SCALAR_##T(alpha); \
+  _Pragma("omp parallel for") for (int64_t r = 0; r < n_out; ++r) { int64_t s0 = r * len; \
+    int64_t v = wrap_mul(a, (int64_t)ip[ADDR(id, is, imx, s0)]); int64_t acc = (op == R_MAG || op == R_MAGSQ) ? wrap_mul(v, v) : v; \
+    for (int64_t j = 1; j < len; ++j) { v = wrap_mul(a, (int64_t)ip[ADDR(id, is, imx, s0 + j)]); \
+      switch (op) { case R_MAX: acc = acc > v ? acc : v; break; case R_MIN: acc = acc < v ? acc : v; break; \
+        case R_MAG: case R_MAGSQ: acc = wrap_add(acc, wrap_mul(v, v)); break; default: acc = wrap_add(acc, v); } } \
+    if (op == R_MEAN) { op_[ADDR(od, os, omx, r)] = ST_##T##_l(acc / len); } \
+    else if (op == R_MAG) { op_[ADDR(od, os, omx, r)] = ST_##T##_d(sqrt((double)acc)); } \
+    else { op_[ADDR(od, os, omx, r)] = ST_##T##_l(acc); } } return 0; }
+
+int orc_unary_reduce(int dtype, void* out, const orc_dims* od, double alpha, const void* in, const orc_dims* id, int op) {
+  int32_t omx[5], imx[5];
+  max_shape_of(omx, od, NULL, NULL);
+  max_shape_of(imx, id, NULL, NULL);
+  int os = is_simple(od, omx), is = is_simple(id, imx);
+  int64_t n_out = 1, n_in = 1;
+  for (int d = 0; d < 5; ++d) { n_out *= od->rev_shape[d]; n_in *= id->rev_shape[d]; }
+  if (n_out <= 0) return 1;
+  int64_t len = n_in / n_out;   /* iter-amount */
+  if (len < 1) return 1;
+  switch (dtype) {
+    case T_BYTE: REDUCE_BODY_INT(int8_t) case T_SHORT: REDUCE_BODY_INT(int16_t) case T_INT: REDUCE_BODY_INT(int32_t)
+    case T_LONG: REDUCE_BODY_INT(int64_t) case T_FLOAT: REDUCE_BODY_FLT(float) case T_DOUBLE: REDUCE_BODY_FLT(double)
+  }
+  return 1;
+}
+
+/* ---- gemm: reference-BLAS xGEMM loop nest behind col->row-gemm -------------------------------
+ * (cpu/tensor_math.clj:672-699, compute/math_util.clj:17-27).  Row-major C[M,N] with pitches. */
+#define GEMM_BODY(T) { const T* a = (const T*)A; const T* b = (const T*)B; T* c = (T*)C; T al = (T)alpha, be = (T)beta; \
+  _Pragma("omp parallel for") for (int64_t m = 0; m < M; ++m) { for (int64_t n = 0; n < N; ++n) { T acc = (T)0; \
+      for (int64_t k = 0; k < K; ++k) { T av = ta ? a[k * lda + m] : a[m * lda + k]; T bv = tb ? b[n * ldb + k] : b[k * ldb + n]; acc += av * bv; } \
+      T* cp = c + m * ldc + n; *cp = (be == (T)0) ? al * acc : al * acc + be * (*cp); } } return 0; }
+int orc_gemm(int dtype, void* C, int64_t ldc, int ta, int tb, double alpha, const void* A, int64_t M, int64_t K,
+             int64_t lda, const void* B, int64_t N, int64_t ldb, double beta) {
+  if (dtype == T_FLOAT) GEMM_BODY(float)
+  if (dtype == T_DOUBLE) GEMM_BODY(double)
+  return 1;
+}
+
+/* ---- softmax (cpu/tensor_math.clj:1037-1103) --------------------------------------------------- */
+#define SOFTMAX_BODY(T) { const T* ip = (const T*)in; T* op_ = (T*)out; \
+  _Pragma("omp parallel for") for (int64_t r = 0; r < rows; ++r) { \
+    const T* x = ip + (r / inner) * in_outer + (r % inner) * in_inner; T* y = op_ + (r / inner) * out_outer + (r % inner) * out_inner; \
+    double mxv = (double)x[0]; for (int64_t j = 1; j < C; ++j) mxv = clj_max_d(mxv, (double)x[j * in_cs]); \
+    T mt = (T)mxv; \
+    for (int64_t j = 0; j < C; ++j) y[j * out_cs] = (T)exp((double)x[j * in_cs] - (double)mt); \
+    double s = (double)y[0]; for (int64_t j = 1; j < C; ++j) s += (double)y[j * out_cs]; \
+    T st = (T)s; for (int64_t j = 0; j < C; ++j) y[j * out_cs] = y[j * out_cs] / st; } return 0; }
+
+static int softmax_impl(int dtype, void* out, const orc_dims* od, const void* in, const orc_dims* id, int spatial) {
+  int64_t rows, C, inner, in_outer, in_inner, in_cs, out_outer, out_inner, out_cs;
+  if (!spatial) {
+    rows = id->rev_shape[1]; C = id->rev_shape[0]; inner = 1;
+    in_outer = id->rev_strides[1]; in_inner = 0; in_cs = id->rev_strides[0];
+    out_outer = od->rev_strides[1]; out_inner = 0; out_cs = od->rev_strides[0];
+  } else { /* [N, C, E] transposed to [N, E, C] (cpu/tensor_math.clj:1097-1103) */
+    int64_t Nn = id->rev_shape[2], E = id->rev_shape[0];
+    rows = Nn * E; C = id->rev_shape[1]; inner = E;
+    in_outer = id->rev_strides[2]; in_inner = id->rev_strides[0]; in_cs = id->rev_strides[1];
+    out_outer = od->rev_strides[2]; out_inner = od->rev_strides[0]; out_cs = od->rev_strides[1];
+  }
+  if (dtype == T_FLOAT) SOFTMAX_BODY(float)
+  if (dtype == T_DOUBLE) SOFTMAX_BODY(double)
+  return 1;
+}
+int orc_softmax_eltwise(int dtype, void* out, const orc_dims* od, const void* in, const orc_dims* id) {
+  return softmax_impl(dtype, out, od, in, id, 0);
+}
+int orc_softmax_spatial(int dtype, void* out, const orc_dims* od, const void* in, const orc_dims* id) {
+  return softmax_impl(dtype, out, od, in, id, 1);
+}
+
+/* ---- convolution forward: per image im2col + gemm ------------------------------------------------
+ * (cpu/tensor_math.clj:1118-1131, 1682-1714; loop nest of src/cortex/nn/impl.clj:8-90) */
+#define IM2COL_BODY(T) { const T* ip = (const T*)in_img; T* cp = (T*)cols; \
+  for (int c = 0; c < cin; ++c) for (int oy = 0; oy < out_h; ++oy) for (int ox = 0; ox < out_w; ++ox) { \
+    int rel_y = oy * d->stride_y - d->pad_y, rel_x = ox * d->stride_x - d->pad_x; \
+    for (int ky = 0; ky < kh; ++ky) for (int kx = 0; kx < kw; ++kx) { int iy = rel_y + ky, ix = rel_x + kx; \
+      int valid = ix >= 0 && ix < in_w && iy >= 0 && iy < in_h; \
+      cp[(int64_t)(oy * out_w + ox) * kcols + c * kh * kw + ky * kw + kx] = valid ? ip[((int64_t)c * in_h + iy) * in_w + ix] : (T)0; } } }
+
+int orc_convolution_forward(int dtype, void* out, const orc_dims* od, double out_alpha, const void* in,
+                            const orc_dims* id, const void* w, const orc_dims* wd, void* workspace,
+                            int64_t workspace_ecount, const orc_conv_desc* d) {
+  (void)wd; (void)workspace; (void)workspace_ecount;
+  int batch = id->rev_shape[3], cin = id->rev_shape[2], in_h = id->rev_shape[1], in_w = id->rev_shape[0];
+  int cout = od->rev_shape[2], out_h = od->rev_shape[1], out_w = od->rev_shape[0];
+  int kh = d->kernel_height, kw = d->kernel_width;
+  int64_t kcols = (int64_t)cin * kh * kw, hw = (int64_t)out_h * out_w;
+  size_t es = dtype == T_FLOAT ? 4 : 8;
+  if (dtype != T_FLOAT && dtype != T_DOUBLE) return 1;
+  int rc = 0;
+#pragma omp parallel for
+  for (int n = 0; n < batch; ++n) {
+    void* cols = malloc((size_t)hw * kcols * es);
+    const char* in_img = (const char*)in + (size_t)n * cin * in_h * in_w * es;
+    if (dtype == T_FLOAT) IM2COL_BODY(float) else IM2COL_BODY(double)
+    /* gemm!(out_n[C_out, hw], false, true, 1.0, W[C_out, K], cols[hw, K], out_alpha) */
+    char* out_img = (char*)out + (size_t)n * cout * hw * es;
+    if (dtype == T_FLOAT) {
+      const float* W = (const float*)w; const float* cl = (const float*)cols; float* o = (float*)out_img; float be = (float)out_alpha;
+      for (int64_t co = 0; co < cout; ++co) for (int64_t p = 0; p < hw; ++p) { float acc = 0.f;
+        for (int64_t k = 0; k < kcols; ++k) acc += W[co * kcols + k] * cl[p * kcols + k];
+        o[co * hw + p] = (be == 0.f) ? acc : acc + be * o[co * hw + p]; }
+    } else {
+      const double* W = (const double*)w; const double* cl = (const double*)cols; double* o = (double*)out_img;
+      for (int64_t co = 0; co < cout; ++co) for (int64_t p = 0; p < hw; ++p) { double acc = 0.0;
+        for (int64_t k = 0; k < kcols; ++k) acc += W[co * kcols + k] * cl[p * kcols + k];
+        o[co * hw + p] = (out_alpha == 0.0) ? acc : acc + out_alpha * o[co * hw + p]; }
+    }
+    free(cols);
+  }
+  return rc;
+}
+
+/* ---- fused extras, as the unfused reference sequence ------------------------------------------------ */
+int orc_bias_relu_rowstats(int dtype, void* Y, int64_t ldy, const void* X, int64_t ldx, const void* bias, int64_t rows,
+                           int64_t cols, void* rowmax, void* rowsum) {
+#define BRS(T) { const T* x = (const T*)X; const T* b = (const T*)bias; T* y = (T*)Y; T* rm = (T*)rowmax; T* rs = (T*)rowsum; \
+  _Pragma("omp parallel for") for (int64_t r = 0; r < rows; ++r) { double mx = 0, sum = 0; \
+    for (int64_t j = 0; j < cols; ++j) { T t = (T)((double)x[r * ldx + j] + (double)b[j]); double td = (double)t; \
+      T o = (T)(td > 0.0 ? td : 0.0); y[r * ldy + j] = o; mx = j == 0 ? (double)o : clj_max_d(mx, (double)o); sum = j == 0 ? (double)o : sum + (double)o; } \
+    if (rm) rm[r] = (T)mx; if (rs) rs[r] = (T)sum; } return 0; }
+  if (dtype == T_FLOAT) BRS(float)
+  if (dtype == T_DOUBLE) BRS(double)
+  return 1;
+}

@@ -1,0 +1,175 @@
+"""Seeded parity cases shared by the CPU suite (oracle vs plain numpy) and the GPU
+suite (B200 vs oracle).  Inputs follow the benchmark configurations: same
+distributions and seeds, sizes scaled down where noted so that the oracle
+finishes in seconds.  Each case builds its inputs with numpy, runs the SAME
+tensor-API calls on whatever backend is bound, and returns host arrays."""
+import numpy as np
+
+from cortex_b200 import nn
+from cortex_b200 import tensor as ct
+from cortex_b200.dimensions import ALL
+
+NP = {"float": np.float32, "double": np.float64, "int": np.int32, "long": np.int64}
+TOL = {"float": 1e-4, "double": 1e-12}
+
+
+def rel_err(got, ref):
+    """abs(got - ref) / max(abs(ref), rms(ref)), the parity measure used for fp results."""
+    ref = np.asarray(ref, np.float64)
+    got = np.asarray(got, np.float64).reshape(ref.shape)
+    rms = float(np.sqrt(np.mean(ref ** 2))) or 1.0
+    return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), rms))) if ref.size else 0.0
+
+
+def gemm_case(datatype, m, n, k, trans_a, trans_b, alpha, beta, pitch_pad=0, offset=0, seed=201):
+    """C = alpha*op(A)*op(B) + beta*C on [rows, cols] windows of larger backing buffers
+    (row pitch = cols + pitch_pad, window origin (offset, offset)): config 2's shape at any size."""
+    rng = np.random.default_rng(seed)
+    dt = NP[datatype]
+
+    def backing(rows, cols):
+        full = rng.standard_normal((rows + offset, cols + pitch_pad + offset)).astype(dt)
+        return full
+
+    a_shape = (k, m) if trans_a else (m, k)
+    b_shape = (n, k) if trans_b else (k, n)
+    A_full, B_full, C_full = backing(*a_shape), backing(*b_shape), backing(m, n)
+
+    def run():
+        ta, tb, tc = ct.to_tensor(A_full, datatype), ct.to_tensor(B_full, datatype), ct.to_tensor(C_full, datatype)
+        va = ct.submatrix(ta, offset, a_shape[0], offset, a_shape[1])
+        vb = ct.submatrix(tb, offset, b_shape[0], offset, b_shape[1])
+        vc = ct.submatrix(tc, offset, m, offset, n)
+        ct.gemm(vc, trans_a, trans_b, alpha, va, vb, beta)
+        return ct.to_array(tc)      # whole backing buffer: the frame around the window must be untouched
+
+    def reference():
+        A = A_full[offset:offset + a_shape[0], offset:offset + a_shape[1]].astype(np.float64)
+        B = B_full[offset:offset + b_shape[0], offset:offset + b_shape[1]].astype(np.float64)
+        opa, opb = (A.T if trans_a else A), (B.T if trans_b else B)
+        out = C_full.astype(np.float64).copy()
+        out[offset:offset + m, offset:offset + n] = alpha * (opa @ opb) + beta * out[offset:offset + m, offset:offset + n]
+        return out
+
+    return run, reference
+
+
+def eltwise_case(datatype, rows, cols, seed=301):
+    """Config 3: X + bias (out of place and in place), ReLU, row max / sum, softmax and its decomposition."""
+    rng = np.random.default_rng(seed)
+    dt = NP[datatype]
+    X = rng.standard_normal((rows, cols)).astype(dt)
+    bias = (np.random.default_rng(seed + 1).standard_normal((1, cols)) * 0.1).astype(dt)
+
+    def run():
+        x, b = ct.to_tensor(X, datatype), ct.to_tensor(bias, datatype)
+        y = ct.new_tensor([rows, cols], datatype)
+        ct.binary_op(y, 1.0, x, 1.0, b, "+")                      # out of place, row broadcast
+        biased = ct.to_array(y)
+        x2 = ct.to_tensor(X, datatype)
+        ct.binary_op(x2, 1.0, x2, 1.0, ct.in_place_reshape(b, [cols]), "+")   # in place, bias as [cols]
+        biased_inplace = ct.to_array(x2)
+        r = ct.new_tensor([rows, cols], datatype)
+        ct.binary_op(r, 1.0, y, 1.0, 0, "max")                    # ReLU
+        relu = ct.to_array(r)
+        mx, sm = ct.new_tensor([rows, 1], datatype), ct.new_tensor([rows, 1], datatype)
+        ct.unary_reduce(mx, 1.0, r, "max")
+        ct.unary_reduce(sm, 1.0, r, "sum")
+        s = ct.new_tensor([rows, cols], datatype)
+        ct.softmax(s, y)
+        # decomposed softmax: max -> subtract (column broadcast) -> exp -> sum -> divide
+        m2 = ct.new_tensor([rows, 1], datatype)
+        ct.unary_reduce(m2, 1.0, y, "max")
+        d = ct.new_tensor([rows, cols], datatype)
+        ct.binary_op(d, 1.0, y, 1.0, m2, "-")
+        ct.unary_op(d, 1.0, d, "exp")
+        s2 = ct.new_tensor([rows, 1], datatype)
+        ct.unary_reduce(s2, 1.0, d, "sum")
+        ct.binary_op(d, 1.0, d, 1.0, s2, "/")
+        return {"biased": biased, "biased_inplace": biased_inplace, "relu": relu, "rowmax": ct.to_array(mx),
+                "rowsum": ct.to_array(sm), "softmax": ct.to_array(s), "softmax_decomposed": ct.to_array(d)}
+
+    return run
+
+
+def gather_case(datatype, src_rows, n_idx, cols, seed=303):
+    """Config 3's index gather: dest[i, :] = M[idx[i], :] through select + assign!; bit-exact."""
+    rng = np.random.default_rng(seed)
+    idx = rng.integers(0, src_rows, size=n_idx, dtype=np.int32)
+    if datatype in ("int", "long"):
+        info = np.iinfo(NP[datatype])
+        M = np.random.default_rng(seed + 1).integers(info.min, info.max, size=(src_rows, cols), dtype=NP[datatype],
+                                                      endpoint=True)
+    else:
+        M = np.random.default_rng(seed + 1).standard_normal((src_rows, cols)).astype(NP[datatype])
+
+    def run():
+        m = ct.to_tensor(M, datatype)
+        it = ct.to_tensor(idx, "int")
+        dest = ct.new_tensor([n_idx, cols], datatype)
+        ct.assign(dest, ct.select(m, it, ALL))
+        return ct.to_array(dest)
+
+    return run, lambda: M[idx]
+
+
+def mlp_case(datatype, batch, widths, seed=101, fused=False, bias_scale=0.0):
+    """Configs 1 and 5: dense layers with ReLU, softmax head.  widths = [in, h1, ..., out]."""
+    dt = NP[datatype]
+    X = np.random.default_rng(seed).random((batch, widths[0])).astype(dt)
+    Ws, bs = [], []
+    for i in range(len(widths) - 1):
+        fan_in = widths[i]
+        Ws.append((np.random.default_rng(seed + 1 + i).standard_normal((widths[i + 1], fan_in))
+                   * np.sqrt(2.0 / fan_in)).astype(dt))
+        bs.append((np.random.default_rng(seed + 50 + i).standard_normal(widths[i + 1]) * bias_scale).astype(dt))
+
+    def run():
+        layers = []
+        for i, (w, b) in enumerate(zip(Ws, bs)):
+            act = "softmax" if i == len(Ws) - 1 else "relu"
+            layers.append((ct.to_tensor(w, datatype), ct.to_tensor(b, datatype), act))
+        net = nn.MLP(layers, fused=fused)
+        return ct.to_array(net.infer(ct.to_tensor(X, datatype)))
+
+    def reference():
+        h = X.astype(np.float64)
+        for i, (w, b) in enumerate(zip(Ws, bs)):
+            h = h @ w.astype(np.float64).T + b.astype(np.float64)
+            if i < len(Ws) - 1:
+                h = np.maximum(h, 0.0)
+        e = np.exp(h - h.max(axis=1, keepdims=True))
+        return e / e.sum(axis=1, keepdims=True)
+
+    return run, reference
+
+
+def conv_case(datatype, batch, cin, hw, cout, k=3, pad=1, stride=1, seed=401, bias_scale=0.0):
+    """Config 4: NCHW conv + bias + ReLU."""
+    dt = NP[datatype]
+    X = np.random.default_rng(seed).standard_normal((batch, cin, hw, hw)).astype(dt)
+    W = (np.random.default_rng(seed + 1).standard_normal((cout, cin * k * k)) * np.sqrt(2.0 / (cin * k * k))).astype(dt)
+    b = (np.random.default_rng(seed + 2).standard_normal(cout) * bias_scale).astype(dt)
+    out_hw = (hw + 2 * pad - k) // stride + 1
+
+    def run():
+        layer = nn.Convolution(ct.to_tensor(W, datatype), ct.to_tensor(b, datatype), (k, k), (pad, pad),
+                               (stride, stride), cin, cout, datatype)
+        out = ct.new_tensor([batch, cout, out_hw, out_hw], datatype)
+        layer.forward(ct.to_tensor(X, datatype), out)
+        nn.relu(out, out)
+        return ct.to_array(out)
+
+    def reference():
+        xp = np.zeros((batch, cin, hw + 2 * pad, hw + 2 * pad), np.float64)
+        xp[:, :, pad:pad + hw, pad:pad + hw] = X
+        cols = np.empty((batch, out_hw * out_hw, cin, k, k), np.float64)
+        for ky in range(k):
+            for kx in range(k):
+                patch = xp[:, :, ky:ky + stride * out_hw:stride, kx:kx + stride * out_hw:stride]
+                cols[:, :, :, ky, kx] = patch.reshape(batch, cin, -1).transpose(0, 2, 1)
+        out = np.einsum("ok,npk->nop", W.astype(np.float64), cols.reshape(batch, out_hw * out_hw, -1))
+        out = out + b.astype(np.float64)[None, :, None]
+        return np.maximum(out, 0.0).reshape(batch, cout, out_hw, out_hw)
+
+    return run, reference

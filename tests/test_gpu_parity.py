@@ -1,0 +1,121 @@
+"""B200 kernels against the CPU oracle on seeded, configuration-shaped inputs,
+through the C ABI.  Tolerances are the ones the backend is specified to:
+bit-exact for integer / copy work, max rel err <= 1e-4 (fp32) and <= 1e-12
+(fp64), error measured as abs(gpu - ref) / max(abs(ref), rms(ref))."""
+import numpy as np
+import pytest
+
+import parity_cases as pc
+from cortex_b200 import tensor as ct
+
+pytestmark = pytest.mark.gpu
+
+
+def _on(driver, datatype, fn):
+    stream = driver.default_device().create_stream()
+    with ct.with_stream(stream), ct.with_datatype(datatype):
+        out = fn()
+    stream.sync()
+    return out
+
+
+GEMM_SHAPES = [
+    # m, n, k, pitch_pad, offset
+    (3, 3, 3, 0, 0),          # the reference's own literal size
+    (128, 256, 32, 0, 0),     # exactly one tile, one k-block
+    (128, 256, 96, 0, 0),
+    (200, 136, 100, 0, 0),    # ragged in every dimension
+    (130, 10, 500, 2, 0),     # MLP tail; pitch not a multiple of 4 -> SIMT kernel for fp32
+    (257, 300, 129, 4, 4),    # pitched window at (4,4): pitch multiple of 4, 16-byte aligned origin
+    (64, 64, 64, 8, 3),       # window origin not 16-byte aligned
+    (512, 384, 1024, 128, 64),
+]
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)],
+                         ids=["NN", "NT", "TN", "TT"])
+@pytest.mark.parametrize("shape", GEMM_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_gemm_matches_oracle(b200_driver, oracle_driver, datatype, ta, tb, shape):
+    m, n, k, pad, off = shape
+    for alpha, beta in ((1.5, 0.5), (1.0, 0.0), (1.0, 1.0)):
+        run, ref64 = pc.gemm_case(datatype, m, n, k, ta, tb, alpha, beta, pad, off)
+        gpu = _on(b200_driver, datatype, run)
+        cpu = _on(oracle_driver, datatype, run)
+        assert pc.rel_err(gpu, cpu) <= pc.TOL[datatype], (alpha, beta)
+        assert pc.rel_err(gpu, ref64()) <= pc.TOL[datatype], (alpha, beta)
+
+
+def test_gemm_beta_zero_ignores_nan_in_c(b200_driver):
+    """BLAS semantics: with beta = 0, C is overwritten without being read."""
+    rng = np.random.default_rng(5)
+    A = rng.standard_normal((128, 64)).astype(np.float32)
+    B = rng.standard_normal((64, 64)).astype(np.float32)
+
+    def run():
+        c = ct.to_tensor(np.full((128, 64), np.nan, np.float32), "float")
+        ct.gemm(c, False, True, 1.0, ct.to_tensor(A, "float"), ct.to_tensor(B, "float"), 0.0)
+        return ct.to_array(c)
+
+    out = _on(b200_driver, "float", run).reshape(128, 64)
+    assert np.isfinite(out).all()
+    assert pc.rel_err(out, A.astype(np.float64) @ B.astype(np.float64).T) <= 1e-4
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
+@pytest.mark.parametrize("rows,cols", [(64, 96), (257, 1000), (512, 4096), (33, 10), (16, 9000)])
+def test_eltwise_reduce_softmax(b200_driver, oracle_driver, datatype, rows, cols):
+    case = pc.eltwise_case(datatype, rows, cols)
+    gpu, cpu = _on(b200_driver, datatype, case), _on(oracle_driver, datatype, case)
+    for key in ("biased", "biased_inplace", "relu", "rowmax"):
+        assert np.array_equal(gpu[key], cpu[key]), key          # one rounding of an exact double result: bit-exact
+    for key in ("rowsum", "softmax", "softmax_decomposed"):
+        assert pc.rel_err(gpu[key], cpu[key]) <= pc.TOL[datatype], key
+
+
+@pytest.mark.parametrize("datatype", ["int", "long", "float", "double"])
+def test_gather_bit_exact(b200_driver, oracle_driver, datatype):
+    for (src_rows, n_idx, cols) in ((100, 57, 24), (1024, 512, 4096), (50, 31, 7)):
+        run, ref = pc.gather_case(datatype, src_rows, n_idx, cols)
+        gpu = _on(b200_driver, datatype, run)
+        assert np.array_equal(gpu.reshape(n_idx, cols), ref())
+        assert np.array_equal(gpu, _on(oracle_driver, datatype, run))
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
+@pytest.mark.parametrize("fused", [False, True], ids=["unfused", "fused"])
+def test_mlp_matches_oracle(b200_driver, oracle_driver, datatype, fused):
+    for batch, widths in ((128, [784, 500, 10]), (256, [1024, 1024, 1024, 1000])):
+        run_gpu, ref = pc.mlp_case(datatype, batch, widths, fused=fused, bias_scale=0.1)
+        run_cpu, _ = pc.mlp_case(datatype, batch, widths, fused=False, bias_scale=0.1)
+        gpu, cpu = _on(b200_driver, datatype, run_gpu), _on(oracle_driver, datatype, run_cpu)
+        assert pc.rel_err(gpu, cpu) <= pc.TOL[datatype]
+        assert pc.rel_err(gpu, ref()) <= pc.TOL[datatype]
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
+def test_conv_matches_oracle(b200_driver, oracle_driver, datatype):
+    for args in (dict(batch=2, cin=4, hw=9, cout=5), dict(batch=2, cin=3, hw=8, cout=4, k=2, pad=0, stride=2),
+                 dict(batch=4, cin=64, hw=28, cout=64)):
+        run, ref = pc.conv_case(datatype, bias_scale=0.1, **args)
+        gpu, cpu = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
+        assert pc.rel_err(gpu, cpu) <= pc.TOL[datatype]
+        assert pc.rel_err(gpu, ref()) <= pc.TOL[datatype]
+
+
+def test_fused_bias_relu_rowstats(b200_driver, oracle_driver):
+    rng = np.random.default_rng(9)
+    for dt, npdt in (("float", np.float32), ("double", np.float64)):
+        X = rng.standard_normal((300, 4096)).astype(npdt)
+        b = (rng.standard_normal(4096) * 0.1).astype(npdt)
+
+        def run():
+            stream = ct.check_stream()
+            x, bias = ct.to_tensor(X, dt), ct.to_tensor(b, dt)
+            y, mx, sm = ct.new_tensor([300, 4096], dt), ct.new_tensor([300], dt), ct.new_tensor([300], dt)
+            stream.bias_relu_rowstats(y.buffer, 4096, x.buffer, 4096, bias.buffer, 300, 4096, mx.buffer, sm.buffer)
+            return ct.to_array(y), ct.to_array(mx), ct.to_array(sm)
+
+        g, c = _on(b200_driver, dt, run), _on(oracle_driver, dt, run)
+        assert np.array_equal(g[0], c[0]) and np.array_equal(g[1], c[1])
+        assert pc.rel_err(g[2], c[2]) <= pc.TOL[dt]

@@ -1,0 +1,433 @@
+"""Backend-agnostic verification functions of the tensor API.
+
+Transcribed from the reference's own verification namespace
+(src/cortex/verify/tensor.clj): same inputs, same literal expected vectors.
+Each function takes ``(driver, datatype)`` and is instantiated once per backend
+(CPU oracle in the CPU suite, B200 in the ``gpu`` suite), which is how the
+reference stamps out its CPU and CUDA tests
+(test/clj/cortex/compute/{cpu,cuda}/tensor_test.clj).
+"""
+import contextlib
+import math
+
+import numpy as np
+
+from cortex_b200 import dimensions as ct_dims
+from cortex_b200 import tensor as ct
+from cortex_b200.dimensions import ALL
+
+ALL_DTYPES = ["byte", "short", "int", "long", "float", "double"]
+CAS_DTYPES = ["int", "long", "float", "double"]
+FLOAT_DTYPES = ["float", "double"]
+INT_LONG = ["int", "long"]
+
+
+@contextlib.contextmanager
+def tensor_context(driver, datatype):
+    stream = driver.default_device().create_stream()
+    with ct.with_stream(stream), ct.with_datatype(datatype):
+        yield stream
+    stream.sync()
+
+
+def _eq(expected, actual, tol=0.0):
+    expected = np.asarray(expected, dtype=np.float64).reshape(-1)
+    actual = np.asarray(actual, dtype=np.float64).reshape(-1)
+    assert expected.shape == actual.shape, (expected.shape, actual.shape)
+    if tol == 0.0:
+        assert np.array_equal(expected, actual), (expected, actual)
+    else:
+        assert np.allclose(expected, actual, rtol=0, atol=tol), (expected, actual)
+
+
+def _part(seq, n):
+    seq = list(seq)
+    return [seq[i:i + n] for i in range(0, len(seq), n)]
+
+
+def assign_constant(driver, datatype):
+    """verify/tensor.clj:20-42"""
+    with tensor_context(driver, datatype):
+        tensor = ct.to_tensor(_part(range(9), 3))
+        assert tensor.ecount() == 9
+        _eq(range(9), ct.to_double_array(tensor))
+        ct.assign(tensor, 1)
+        _eq([1] * 9, ct.to_double_array(tensor))
+        rows, columns = ct.rows(tensor), ct.columns(tensor)
+        for row in rows:
+            ct.assign(row, 2)
+        _eq([2] * 9, ct.to_double_array(tensor))
+        c1, c2, c3 = columns
+        ct.assign(c1, 1)
+        ct.assign(c2, 2)
+        ct.assign(c3, 3)
+        _eq([1, 2, 3] * 3, ct.to_double_array(tensor))
+
+
+def assign_marshal(driver, datatype):
+    """verify/tensor.clj:45-57"""
+    with tensor_context(driver, datatype):
+        tensor = ct.to_tensor(_part(range(9), 3))
+        intermediate = ct.new_tensor([3, 3], datatype="int")
+        final = ct.new_tensor([3, 3], datatype="double")
+        ct.assign(intermediate, tensor)
+        ct.assign(final, intermediate)
+        _eq(range(9), ct.to_double_array(final))
+
+
+def unary_op(driver, datatype):
+    """verify/tensor.clj:60-80"""
+    with tensor_context(driver, datatype):
+        tens_a = ct.to_tensor(_part(range(9), 3))
+        tens_b = ct.to_tensor(_part([1] * 9, 3))
+        a = float(ct.dtype_cast(2.5, datatype))
+        ct.unary_op(tens_b, 2.5, tens_a, "ceil")
+        _eq([math.ceil(v * a) for v in range(9)], ct.to_double_array(tens_b))
+        ct.unary_op(tens_b, 1.0, tens_b, "-")
+        _eq([-math.ceil(v * a) for v in range(9)], ct.to_double_array(tens_b))
+        src = [0, 1, 2, 3, 4]
+        tens_src, tens_b = ct.to_tensor(src), ct.to_tensor(src)
+        tol = 1e-6 if datatype == "float" else 0.0   # fp32 views evaluate exp in single precision on the device
+        ct.unary_op(tens_b, 1.0, tens_src, "exp")
+        _eq([_cast(math.exp(v), datatype) for v in src], ct.to_double_array(tens_b), tol * math.exp(4))
+        ct.unary_op(tens_b, 1.0, tens_src, "sqrt")
+        _eq([_cast(math.sqrt(v), datatype) for v in src], ct.to_double_array(tens_b))
+
+
+def _cast(v, datatype):
+    if datatype == "double":
+        return float(v)
+    if datatype == "float":
+        return float(np.float32(v))
+    return int(v)
+
+
+def channel_op(driver, datatype):
+    """verify/tensor.clj:83-94"""
+    with tensor_context(driver, datatype):
+        tens_a = ct.to_tensor(np.arange(18).reshape(2, 3, 3))
+        tens_chan = ct.in_place_reshape(ct.to_tensor(range(3)), [3, 1])
+        tens_result = ct.new_tensor([2, 3, 3])
+        ct.binary_op(tens_result, 1.0, tens_a, 1.0, tens_chan, "*")
+        _eq([0.0, 0.0, 0.0, 3.0, 4.0, 5.0, 12.0, 14.0, 16.0, 0.0, 0.0, 0.0, 12.0, 13.0, 14.0, 30.0, 32.0, 34.0],
+            ct.to_double_array(tens_result))
+
+
+def binary_constant_op(driver, datatype):
+    """verify/tensor.clj:97-126"""
+    with tensor_context(driver, datatype):
+        tens_a = ct.to_tensor(_part(range(9), 3))
+        tens_b = ct.to_tensor(_part([1] * 9, 3))
+        if datatype != "byte":
+            ct.binary_op(tens_b, 2.0, tens_a, 3.0, 4.0, "*")
+            _eq([24 * v for v in range(9)], ct.to_double_array(tens_b))
+        ct.binary_op(tens_b, 2.0, tens_a, 3.0, 4.0, "+")
+        _eq([12 + 2 * v for v in range(9)], ct.to_double_array(tens_b))
+        # reversed operands
+        ct.binary_op(tens_b, 3.0, 4.0, 2.0, tens_a, "-")
+        _eq([12 - 2 * v for v in range(9)], ct.to_double_array(tens_b))
+        ct.assign(tens_b, 1.0)
+        _eq([1] * 9, ct.to_double_array(tens_b))
+        # accumulation
+        ct.binary_op(tens_b, 1.0, tens_b, 1.0, 1.0, "+")
+        _eq([2] * 9, ct.to_double_array(tens_b))
+
+
+def binary_op(driver, datatype):
+    """verify/tensor.clj:129-249"""
+    with tensor_context(driver, datatype):
+        tens_a = ct.to_tensor(_part(range(9), 3))
+        tens_b = ct.to_tensor(_part([2] * 9, 3))
+        tens_c = ct.to_tensor(_part([10] * 9, 3))
+        ct.binary_op(tens_c, 2.0, tens_a, 2.0, tens_b, "*")
+        _eq([2 * 2 * 2 * v for v in range(9)], ct.to_double_array(tens_c))
+        ct.binary_op(tens_b, 1.0, tens_c, 2.0, tens_a, "-")
+        _eq([0.0, 6.0, 12.0, 18.0, 24.0, 30.0, 36.0, 42.0, 48.0], ct.to_double_array(tens_b))
+        # destination is one of the operands
+        ct.binary_op(tens_c, 1.0, tens_c, 2.0, tens_a, "-")
+        _eq([0.0, 6.0, 12.0, 18.0, 24.0, 30.0, 36.0, 42.0, 48.0], ct.to_double_array(tens_c))
+        if datatype in CAS_DTYPES:
+            # destination smaller than the operation: broadcast-accumulate (needs the CAS form)
+            tens_c_small = ct.subvector(tens_c, 0, length=3)
+            sub = lambda nth: [row[nth] for row in _part(range(9), 3)]
+            c_data = list(ct.to_double_array(tens_c))
+            ct.binary_op(tens_c_small, 1.0, tens_c_small, 2.0, tens_a, "-")
+            _eq([c_data[i] - sum(2.0 * v for v in sub(i)) for i in range(3)], ct.to_double_array(tens_c_small))
+            c_data = list(ct.to_double_array(tens_c_small))
+            ct.binary_op(tens_c_small, 2.0, tens_a, 1.0, tens_c_small, "+")
+            _eq([c_data[i] + sum(2.0 * v for v in sub(i)) for i in range(3)], ct.to_double_array(tens_c_small))
+        if datatype in FLOAT_DTYPES:
+            n_batches, n_channels, img_dim = 3, 5, 4
+            rng = np.random.default_rng(7)
+            big = rng.random((n_batches, n_channels, img_dim, img_dim))
+            sums = big.sum(axis=(0, 2, 3))
+            big_m = ct.to_tensor(big)
+            test_vec = ct.in_place_reshape(ct.new_tensor([n_channels]), [n_channels, 1, 1])
+            ct.binary_op(test_vec, 1.0, test_vec, 1.0, big_m, "+")
+            _eq(sums, ct.to_double_array(test_vec), 1e-4)
+        tens_a4 = ct.to_tensor([_part(range(9), 3)] * 4)
+        result = ct.new_tensor(tens_a4.shape())
+        ct.binary_op(result, 1.0, tens_a4, 1.0, 5, "eq")
+        _eq([1 if int(v) == 5 else 0 for v in ct.to_double_array(tens_a4)], ct.to_double_array(result))
+        # bias add over [4 3 3]
+        tens_z = ct.new_tensor([4, 3, 3])
+        bias = ct.in_place_reshape(ct.to_tensor([1, 2, 3, 4]), [4, 1, 1])
+        ct.binary_op(tens_z, 1.0, tens_z, 1.0, bias, "+")
+        _eq([v for b in [1, 2, 3, 4] for v in [b] * 9], ct.to_double_array(tens_z))
+        if datatype in CAS_DTYPES:
+            # bias gradient: sum over everything but the channel
+            tens_g = ct.to_tensor([np.full((3, 3), v) for v in [1, 2, 3, 4]])
+            bias_g = ct.in_place_reshape(ct.new_tensor([4]), [4, 1, 1])
+            ct.binary_op(bias_g, 1.0, tens_g, 1.0, bias_g, "+")
+            _eq([9, 18, 27, 36], ct.to_double_array(bias_g))
+        tens_1, tens_2 = ct.to_tensor([1, 1, 0, 0]), ct.to_tensor([-1, 1, 2, -2])
+        result = ct.new_tensor(tens_2.shape())
+        for op, expected in ((">", [1, 0, 0, 1]), (">=", [1, 1, 0, 1]), ("<", [0, 0, 1, 0]), ("<=", [0, 1, 1, 0])):
+            ct.binary_op(result, 1.0, tens_1, 1.0, tens_2, op)
+            _eq(expected, ct.to_double_array(result))
+        tens_1, tens_2 = ct.to_tensor([1, 1, 0, 0]), ct.to_tensor([1, 1, 1, 1])
+        result = ct.new_tensor(tens_2.shape())
+        ct.binary_op(result, 1.0, tens_1, 1.0, tens_2, "bit-xor")
+        _eq([0, 0, 1, 1], ct.to_double_array(result))
+
+
+def gemm(driver, datatype):
+    """verify/tensor.clj:252-284 -- also checks sub-matrix views"""
+    with tensor_context(driver, datatype):
+        tens_a = ct.to_tensor(_part(range(9), 3))
+        tens_b = ct.to_tensor(_part([2] * 9, 3))
+        tens_c = ct.to_tensor(_part([10] * 9, 3))
+        ct.gemm(tens_c, False, False, 1, tens_a, tens_b, 1)
+        _eq([16.0, 16.0, 16.0, 34.0, 34.0, 34.0, 52.0, 52.0, 52.0], ct.to_double_array(tens_c))
+        ct.gemm(tens_c, False, False, 1, tens_a, tens_b, 0)
+        _eq([6.0, 6.0, 6.0, 24.0, 24.0, 24.0, 42.0, 42.0, 42.0], ct.to_double_array(tens_c))
+        ct.gemm(tens_c, True, False, 1, tens_a, tens_b, 0)
+        _eq([18.0, 18.0, 18.0, 24.0, 24.0, 24.0, 30.0, 30.0, 30.0], ct.to_double_array(tens_c))
+        sa, sb = ct.submatrix(tens_a, 0, 2, 0, 2), ct.submatrix(tens_b, 0, 2, 0, 2)
+        sc = ct.submatrix(tens_c, 0, 2, 0, 2)
+        ct.gemm(sc, False, False, 1, sa, sb, 0)
+        _eq([2, 2, 14, 14], ct.to_double_array(sc))
+        _eq([2.0, 2.0, 18.0, 14.0, 14.0, 24.0, 30.0, 30.0, 30.0], ct.to_double_array(tens_c))
+        sa, sb = ct.submatrix(tens_a, 1, 2, 1, 2), ct.submatrix(tens_b, 0, 2, 0, 2)
+        sc = ct.submatrix(tens_c, 1, 2, 1, 2)
+        ct.gemm(sc, False, False, 1, sa, sb, 1)
+        _eq([32, 42, 60, 60], ct.to_double_array(sc))
+        _eq([2.0, 2.0, 18.0, 14.0, 32.0, 42.0, 30.0, 60.0, 60.0], ct.to_double_array(tens_c))
+
+
+def activation_forward(driver, datatype):
+    """verify/tensor.clj:532-554"""
+    with tensor_context(driver, datatype):
+        inp = ct.to_tensor(range(-4, 8))
+        out = ct.new_tensor([12])
+        ct.unary_op(out, 1.0, inp, "logistic")
+        _eq([0.01798620996209156, 0.04742587317756678, 0.11920292202211755, 0.2689414213699951, 0.5,
+             0.7310585786300049, 0.8807970779778823, 0.9525741268224334, 0.9820137900379085, 0.9933071490757153,
+             0.9975273768433653, 0.9990889488055994], ct.to_double_array(out), 1e-4)
+        ct.unary_op(out, 1.0, inp, "tanh")
+        _eq([-0.999329299739067, -0.9950547536867305, -0.9640275800758169, -0.7615941559557649, 0.0,
+             0.7615941559557649, 0.9640275800758169, 0.9950547536867305, 0.999329299739067, 0.9999092042625951,
+             0.9999877116507956, 0.9999983369439447], ct.to_double_array(out), 1e-4)
+        ct.binary_op(out, 1.0, inp, 0, 0, "max")
+        _eq([0.0, 0.0, 0.0, 0.0, 0.0, 1.0, 2.0, 3.0, 4.0, 5.0, 6.0, 7.0], ct.to_double_array(out))
+
+
+SOFTMAX_1234 = [0.03205860328008499, 0.08714431874203256, 0.2368828180899101, 0.6439142598879722]
+
+
+def softmax(driver, datatype):
+    """verify/tensor.clj:577-620"""
+    with tensor_context(driver, datatype):
+        inp = ct.to_tensor([[1, 2, 3, 4]] * 10)
+        out = ct.new_tensor([10, 4])
+        ct.softmax(out, inp)
+        _eq(SOFTMAX_1234 * 10, ct.to_double_array(out), 1e-4)
+        img_dim = 4
+        inp = ct.to_tensor([[[v] * (img_dim * img_dim) for v in [1, 2, 3, 4]]])
+        out = ct.new_tensor([1, 4, img_dim * img_dim])
+        ct.softmax(out, inp)
+        _eq([v for s in SOFTMAX_1234 for v in [s] * (img_dim * img_dim)], ct.to_double_array(out), 1e-4)
+        # strided (non-contiguous) columns, in place
+        pred = ct.to_tensor([list(range(10))] * 5)
+        sel = ct.select(pred, ALL, list(range(2, 10)))
+        test_tensor = ct.to_tensor(range(2, 10))
+        answer = ct.softmax(test_tensor, test_tensor)
+        ct.softmax(sel, sel)
+        _eq(([0, 1] + list(ct.to_double_array(answer))) * 5, ct.to_double_array(pred))
+
+
+def unary_reduce(driver, datatype):
+    """verify/tensor.clj:648-665"""
+    with tensor_context(driver, datatype):
+        dest = ct.new_tensor([10, 1])
+        src_data = [0, 3, 5, 2, 1, 9, 5, 7, 7, 2]
+        src = ct.to_tensor([src_data] * 10)
+        ct.unary_reduce(dest, 2.0, src, "max")
+        _eq([18] * 10, ct.to_double_array(dest))
+        ct.unary_reduce(dest, 1.0, src, "sum")
+        _eq([sum(src_data)] * 10, ct.to_double_array(dest))
+        ct.unary_reduce(dest, 1.0, src, "mean")
+        _eq([_cast(sum(src_data) / len(src_data), datatype)] * 10, ct.to_double_array(dest))
+
+
+def transpose(driver, datatype):
+    """verify/tensor.clj:668-684"""
+    with tensor_context(driver, datatype):
+        img_dim = 4
+        img = ct.to_tensor(np.tile(np.array([1, 2, 3]), (img_dim, img_dim, 1)))
+        planar = ct.transpose(img, [2, 0, 1])
+        rgb = ct.transpose(planar, [1, 2, 0])
+        n = img_dim * img_dim
+        _eq([1] * n + [2] * n + [3] * n, ct.to_double_array(planar))
+        _eq([1, 2, 3] * n, ct.to_double_array(rgb))
+
+
+def mask(driver, datatype):
+    """verify/tensor.clj:687-717 (int and long only)"""
+    with tensor_context(driver, datatype):
+        rgba = 1 + (2 << 8) + (3 << 16) + (255 << 24)
+        if datatype == "int":
+            rgba -= 1 << 32   # the reference builds it from (int ...) values: wraps to a negative int
+        img_dim = 4
+        img = ct.to_tensor(np.full((img_dim, img_dim), rgba, dtype=np.int64))
+        mask_t = ct.in_place_reshape(ct.to_tensor([0xFF, 0xFF << 8, 0xFF << 16]), [3, 1, 1])
+        div_t = ct.in_place_reshape(ct.to_tensor([1, 1 << 8, 1 << 16]), [3, 1, 1])
+        result = ct.new_tensor([3, img_dim, img_dim])
+        ct.binary_op(result, 1.0, img, 1.0, mask_t, "bit-and")
+        ct.binary_op(result, 1.0, result, 1.0, div_t, "/")
+        n = img_dim * img_dim
+        _eq([1] * n + [2] * n + [3] * n, ct.to_double_array(result))
+
+
+def select(driver, datatype):
+    """verify/tensor.clj:720-782"""
+    with tensor_context(driver, datatype):
+        mat = ct.to_tensor([_part(range(9), 3)] * 2)
+        s = ct.select(mat, ALL, ALL, [1, 2])
+        _eq([1, 2, 4, 5, 7, 8] * 2, ct.to_double_array(s))
+        assert s.shape() == [2, 3, 2]
+        s = ct.select(mat, ALL, ALL, [2])
+        _eq([2, 5, 8] * 2, ct.to_double_array(s))
+        assert s.shape() == [2, 3, 1]
+        s = ct.select(mat, ALL, ALL, 2)
+        _eq([2, 5, 8] * 2, ct.to_double_array(s))
+        assert s.shape() == [2, 3] and not ct.dense(s)
+        s = ct.select(mat, ALL, [1, 2], ALL)
+        _eq([3, 4, 5, 6, 7, 8] * 2, ct.to_double_array(s))
+        assert s.shape() == [2, 2, 3] and not ct.dense(s)
+        s = ct.select(mat, ALL, [2], ALL)
+        _eq([6, 7, 8] * 2, ct.to_double_array(s))
+        assert s.shape() == [2, 1, 3] and not ct.dense(s)
+        s = ct.select(mat, ALL, 0, ALL)
+        _eq([0, 1, 2] * 2, ct.to_double_array(s))
+        assert s.shape() == [2, 3] and not ct.dense(s)
+        s = ct.select(mat, [1], [1], ALL)
+        _eq([3, 4, 5], ct.to_double_array(s))
+        assert s.shape() == [1, 1, 3] and ct.dense(s)
+        s = ct.select(mat, 1, 1, ALL)
+        _eq([3, 4, 5], ct.to_double_array(s))
+        assert s.shape() == [3] and ct.dense(s)
+        s = ct.select(mat, 1, ALL, 2)
+        _eq([2, 5, 8], ct.to_double_array(s))
+        assert s.shape() == [3] and not ct.dense(s)
+
+
+def select_transpose_interaction(driver, datatype):
+    """verify/tensor.clj:785-805"""
+    with tensor_context(driver, datatype):
+        img_dim = 4
+        mat = ct.to_tensor(np.tile(np.array([1, 2, 3]), (img_dim, img_dim, 1)))
+        planar = ct.transpose(mat, [2, 0, 1])
+        n = img_dim * img_dim
+        r, g, b = (ct.select(planar, c, ALL, ALL) for c in range(3))
+        _eq([1] * n, ct.to_double_array(r))
+        _eq([2] * n, ct.to_double_array(g))
+        _eq([3] * n, ct.to_double_array(b))
+        bgr = ct.new_tensor([img_dim, img_dim, 3])
+        planes = ct.transpose(bgr, [2, 0, 1])
+        ct.assign(ct.select(planes, 0, ALL, ALL), b)
+        ct.assign(ct.select(planes, 1, ALL, ALL), g)
+        ct.assign(ct.select(planes, 2, ALL, ALL), r)
+        _eq([3, 2, 1] * n, ct.to_double_array(bgr))
+
+
+CONV_EXPECTED = [25062.0, 25692.0, 27582.0, 28212.0, 62646.0, 64572.0, 70350.0, 72276.0, 100230.0, 103452.0, 113118.0,
+                 116340.0, 65382.0, 66012.0, 67902.0, 68532.0, 185910.0, 187836.0, 193614.0, 195540.0, 306438.0,
+                 309660.0, 319326.0, 322548.0, 105702.0, 106332.0, 108222.0, 108852.0, 309174.0, 311100.0, 316878.0,
+                 318804.0, 512646.0, 515868.0, 525534.0, 528756.0]
+
+
+def convolution_operator(driver, datatype):
+    """verify/tensor.clj:808-849 (forward part)"""
+    with tensor_context(driver, datatype):
+        batch, cin, cout, dim = 3, 4, 3, 4
+        inp = ct.to_tensor(np.arange(dim * dim * batch * cin).reshape(batch, cin, dim, dim))
+        desc = ct.convolution_descriptor(datatype, cout, cin, 3, 3, 0, 0, 1, 1)
+        od = ct.get_convolution_output_dimensions(desc, dim, dim)
+        out = ct.new_tensor([batch, cout, od["output-height"], od["output-width"]])
+        algorithms = ct.choose_convolution_algorithms(desc, dim, dim, batch, 1000)
+        workspace = ct.new_tensor([int(algorithms["workspace-size"])])
+        weights = ct.to_tensor(np.arange(cout * 3 * 3 * cin).reshape(cout, 3 * 3 * cin))
+        ct.assign(out, 1)   # pre-existing contents must not leak through out_alpha = 0
+        ct.convolution_forward(out, 0.0, inp, weights, workspace, desc, algorithms)
+        tol = 0.0 if datatype == "double" else 0.5   # exact in fp64; fp32 results reach 5e5 (ulp 0.03)
+        _eq(CONV_EXPECTED, ct.to_double_array(out), tol)
+
+
+def indexed_tensor(driver, datatype):
+    """verify/tensor.clj:1147-1199"""
+    with tensor_context(driver, datatype):
+        mat = ct.to_tensor([_part(range(9), 3)] * 2)
+        index = ct.to_tensor([1, 2, 1, 2, 1, 2], datatype="int")
+        sel = ct.select(mat, ALL, ALL, index)
+        assert not ct_dims.access_increasing(sel.dimensions)
+        assert sel.shape() == [2, 3, 6]
+        _eq([1, 2, 1, 2, 1, 2, 4, 5, 4, 5, 4, 5, 7, 8, 7, 8, 7, 8] * 2, ct.to_double_array(sel))
+        # the center-loss pattern: gather rows, then scatter-accumulate through the same index
+        centers = ct.select(mat, 0, ct.to_tensor([0, 1, 0, 2, 1], datatype="int"), ALL)
+        batch_data = ct.new_tensor([5, 3])
+        ct.assign(batch_data, centers)
+        _eq([0, 1, 2, 3, 4, 5, 0, 1, 2, 6, 7, 8, 3, 4, 5], ct.to_double_array(batch_data))
+        if datatype in CAS_DTYPES:
+            ct.binary_op(centers, 1.0, batch_data, 1.0, centers, "+")
+            _eq([0, 3, 6, 9, 12, 15, 0, 3, 6, 12, 14, 16, 9, 12, 15], ct.to_double_array(centers))
+        # broadcasting with several indexes in one tensor
+        mat2 = ct.to_tensor(_part(range(9), 3))
+        sel2 = ct.select(mat2, ct.to_tensor([0, 1, 1, 2], datatype="int"), ct.to_tensor([2, 1, 0], datatype="int"))
+        dest = ct.new_tensor([8, 6])
+        ct.assign(dest, sel2)
+        rows = [[2, 1, 0], [2, 1, 0], [5, 4, 3], [5, 4, 3], [5, 4, 3], [5, 4, 3], [8, 7, 6], [8, 7, 6]] * 2
+        _eq([v for r in rows for v in r], ct.to_double_array(dest))
+
+
+def magnitude_and_mag_squared(driver, datatype):
+    """verify/tensor.clj:1202-1228"""
+    with tensor_context(driver, datatype):
+        n = 10
+        src_data = np.arange(n * n).reshape(n, n)
+        src = ct.to_tensor(src_data)
+        dst = ct.new_tensor([n, 1])
+        ct.unary_reduce(dst, 1.0, src, "magnitude-squared")
+        _eq((src_data.astype(np.float64) ** 2).sum(axis=1), ct.to_double_array(dst), 1e-4)
+        ct.unary_reduce(dst, 1.0, src, "magnitude")
+        expected = np.sqrt((src_data.astype(np.float64) ** 2).sum(axis=1))
+        tol = 1e-4 if datatype in FLOAT_DTYPES else 1.0   # integer views store the truncated square root
+        _eq(expected if datatype in FLOAT_DTYPES else np.floor(expected), ct.to_double_array(dst), tol)
+
+
+# how the reference instantiates them (test/clj/cortex/compute/cpu/tensor_test.clj:17-119)
+CASES = [
+    (assign_constant, ALL_DTYPES), (assign_marshal, ALL_DTYPES), (unary_op, ALL_DTYPES), (channel_op, ALL_DTYPES),
+    (binary_constant_op, ALL_DTYPES), (binary_op, ALL_DTYPES), (gemm, FLOAT_DTYPES),
+    (activation_forward, FLOAT_DTYPES), (softmax, FLOAT_DTYPES), (unary_reduce, ALL_DTYPES), (transpose, ALL_DTYPES),
+    (mask, INT_LONG), (select, ALL_DTYPES), (select_transpose_interaction, ALL_DTYPES),
+    (convolution_operator, FLOAT_DTYPES), (indexed_tensor, ALL_DTYPES), (magnitude_and_mag_squared, FLOAT_DTYPES),
+]
+
+
+def case_params():
+    return [(fn, dt) for fn, dts in CASES for dt in dts]
+
+
+def case_id(param):
+    return param.__name__ if callable(param) else str(param)
