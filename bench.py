@@ -1,0 +1,412 @@
+#!/usr/bin/env python
+"""bench.py -- headline benchmark of the B200 backend.
+
+Workload (the configuration the multi-GPU half of the headline metric is quoted
+on): wide MLP batch inference, fp32, batch 65536 x 4096 -> 4 x (linear
+4096->4096 + ReLU) -> linear 4096->1000 + softmax, He-normal weights from fixed
+seeds, zero biases, batch-sharded over the GPUs with replicated weights (strong
+scaling on the same 65536 rows).  One step = one forward pass over this rank's
+shard.  `value` = samples/s with the shard resident in HBM; `e2e` = the same
+pass through the host-buffer pipeline (pinned host input -> H2D -> layers ->
+D2H of the probabilities, every step).  The other half of the headline metric,
+the standalone 4096^3 fp32 gemm!, and the HBM-bound elementwise / reduce kernels
+are reported in the `gemm_4096` / `eltwise` objects of the same line (N=1 only).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BATCH, WIDTH, CLASSES, HIDDEN_LAYERS = 65536, 4096, 1000, 4
+SEED_X, SEED_W = 501, 502
+FLOPS_PER_SAMPLE = 2.0 * (HIDDEN_LAYERS * WIDTH * WIDTH + WIDTH * CLASSES)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_burst": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def make_weights():
+    ws = []
+    for i in range(HIDDEN_LAYERS + 1):
+        out = WIDTH if i < HIDDEN_LAYERS else CLASSES
+        w = np.random.default_rng(SEED_W + i).standard_normal((out, WIDTH), dtype=np.float32)
+        w *= np.float32(np.sqrt(2.0 / WIDTH))
+        ws.append(w)
+    return ws
+
+
+def make_input(lo, hi):
+    """Rows [lo, hi) of the seeded N(0,1) batch, generated in 4096-row blocks so that any
+    sharding sees the same global matrix."""
+    out = np.empty((hi - lo, WIDTH), np.float32)
+    blk = 4096
+    for b0 in range(lo // blk * blk, hi, blk):
+        rows = np.random.default_rng([SEED_X, b0 // blk]).standard_normal((blk, WIDTH), dtype=np.float32)
+        s, e = max(lo, b0), min(hi, b0 + blk)
+        out[s - lo:e - lo] = rows[s - b0:e - b0]
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while a timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # under load = the upper half of the samples (the sampler also sees the idle edges)
+        sm_sorted = sorted(sm)
+        return {"sm_mhz": float(np.median(sm_sorted)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------
+# reference arm: the CPU oracle (restatement of the reference's CPU backend) on host cores
+# --------------------------------------------------------------------------------------
+
+def cpu_forward_rate(sample_rows, weights, repeats=1):
+    """samples/s of the oracle MLP forward (bias assign!, gemm! NT beta=1, ReLU binary-op!, softmax!)
+    on `sample_rows` rows of the workload."""
+    from cortex_b200 import nn
+    from cortex_b200 import tensor as ct
+    from oracle.cpu_backend import OracleDriver
+    drv = OracleDriver()
+    stream = drv.default_device().create_stream()
+    x = make_input(0, sample_rows)
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        layers = []
+        for i, w in enumerate(weights):
+            act = "softmax" if i == len(weights) - 1 else "relu"
+            layers.append((ct.to_tensor(w), ct.to_tensor(np.zeros(w.shape[0], np.float32)), act))
+        net = nn.MLP(layers, fused=False)
+        xt = ct.to_tensor(x)
+        net.infer(xt)   # touch buffers once
+        t0 = time.perf_counter()
+        for _ in range(repeats):
+            net.infer(xt)
+        dt = (time.perf_counter() - t0) / repeats
+    return sample_rows / dt, dt
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    weights = make_weights()
+    sample = 2048
+    cores = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_forward_rate(sample, weights)
+    t0 = time.perf_counter()
+    rates = [cpu_forward_rate(sample, weights)[0] for _ in range(args.steps)]
+    total = time.perf_counter() - t0
+    value = float(np.mean(rates))
+    line = {
+        "impl": "reference", "metric": "wide_mlp_inference_samples_per_s", "value": value, "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * sample / value,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "wide_mlp 65536x4096 -> 4x(4096+ReLU) -> 1000+softmax, fp32 (CPU: %d-row sample per step)" % sample},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "port",
+                         "sample": "%d rows of the 65536-row batch per step; oracle elementwise/softmax in C (OpenMP), "
+                                   "gemm! through OpenBLAS sgemm; the reference itself is Clojure/JVM and cannot run here" % sample},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": total,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# B200 arm
+# --------------------------------------------------------------------------------------
+
+def time_region(stream, fn, iters):
+    e0 = stream.create_event(timing=True)
+    for _ in range(iters):
+        fn()
+    e1 = stream.create_event(timing=True)
+    e1.wait_for_event()
+    stream.sync()
+    return e1.elapsed_ms_since(e0) / iters
+
+
+def bench_gemm_4096(drv, dev, peaks):
+    """Config 2 in brief: C = 1.5*A*B^T + 0.5*C, 4096^3 fp32, all four transposes."""
+    from cortex_b200 import tensor as ct
+    stream = dev.create_stream()
+    rng = np.random.default_rng(201)
+    out = {}
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        A = ct.to_tensor(rng.standard_normal((4096, 4096), dtype=np.float32))
+        B = ct.to_tensor(rng.standard_normal((4096, 4096), dtype=np.float32))
+        Cm = ct.to_tensor(rng.standard_normal((4096, 4096), dtype=np.float32))
+        for name, ta, tb in (("NT", False, True), ("NN", False, False), ("TN", True, False), ("TT", True, True)):
+            for _ in range(3):
+                ct.gemm(Cm, ta, tb, 1.5, A, B, 0.5)
+            ms = time_region(stream, lambda: ct.gemm(Cm, ta, tb, 1.5, A, B, 0.5), 10)
+            out[name] = round(2.0 * 4096 ** 3 / ms / 1e9, 1)
+    peak = peaks["bf16_burst"] / 2.0 / 3.0
+    best = max(out.values())
+    return {"tflops": out, "roofline_peak_tflops": round(peak, 1), "frac_of_%s" % peaks["source"]: round(out["NT"] / peak, 3),
+            "note": "peak = bf16 burst / 2 (tf32) / 3 (3xTF32); work counted as 2*M*N*K", "best": best}
+
+
+def bench_eltwise(drv, dev, peaks):
+    """Config 3 in brief: GB/s of the HBM-bound kernels on [8192, 4096] fp32, rotating 4 buffer sets."""
+    from cortex_b200 import tensor as ct
+    from cortex_b200.dimensions import ALL
+    stream = dev.create_stream()
+    rows, cols, sets = 8192, 4096, 4
+    rng = np.random.default_rng(301)
+    res = {}
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        xs = [ct.to_tensor(rng.standard_normal((rows, cols), dtype=np.float32)) for _ in range(sets)]
+        ys = [ct.new_tensor([rows, cols]) for _ in range(sets)]
+        bias = ct.to_tensor((rng.standard_normal((1, cols)) * 0.1).astype(np.float32))
+        stat = [ct.new_tensor([rows, 1]) for _ in range(sets)]
+        idx = ct.to_tensor(rng.integers(0, rows, size=rows, dtype=np.int32), datatype="int")
+        state = {"i": 0}
+
+        def rot():
+            state["i"] = (state["i"] + 1) % sets
+            return state["i"]
+
+        cases = {
+            "bias_add": (lambda i: ct.binary_op(ys[i], 1.0, xs[i], 1.0, bias, "+"), 2 * rows * cols * 4 + cols * 4),
+            "relu": (lambda i: ct.binary_op(ys[i], 1.0, xs[i], 1.0, 0, "max"), 2 * rows * cols * 4),
+            "reduce_max": (lambda i: ct.unary_reduce(stat[i], 1.0, xs[i], "max"), rows * cols * 4 + rows * 4),
+            "reduce_sum": (lambda i: ct.unary_reduce(stat[i], 1.0, xs[i], "sum"), rows * cols * 4 + rows * 4),
+            "softmax": (lambda i: ct.softmax(ys[i], xs[i]), 2 * rows * cols * 4),
+            "gather_rows": (lambda i: ct.assign(ys[i], ct.select(xs[i], idx, ALL)), 2 * rows * cols * 4 + rows * 4),
+            "fused_bias_relu_rowstats": (lambda i: stream.bias_relu_rowstats(ys[i].buffer, cols, xs[i].buffer, cols,
+                                                                            bias.buffer, rows, cols, stat[i].buffer,
+                                                                            stat[(i + 1) % sets].buffer),
+                                         2 * rows * cols * 4 + cols * 4 + 2 * rows * 4),
+        }
+        for name, (fn, nbytes) in cases.items():
+            for _ in range(3):
+                fn(rot())
+            ms = time_region(stream, lambda: fn(rot()), 20)
+            gbs = nbytes / ms / 1e6
+            res[name] = {"gbs": round(gbs, 0), "frac_of_%s_hbm" % peaks["source"]: round(gbs / peaks["hbm_gbs"], 3)}
+    return res
+
+
+def run_b200(args, rank, world, local_rank):
+    import torch  # plumbing only: rendezvous, barrier, max-over-ranks
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+    from cortex_b200 import dimensions as dims
+    from cortex_b200 import nn
+    from cortex_b200 import tensor as ct
+    from cortex_b200.driver import driver
+    from cortex_b200.parallel import shard_bounds
+    from cortex_b200.pipeline import BatchPipeline
+
+    peaks = measured_peaks()
+    drv = driver()
+    dev = drv.get_devices()[local_rank]
+    stream = dev.create_stream()
+    lo, hi = shard_bounds(BATCH, world, rank)
+    rows = hi - lo
+    weights = make_weights()
+    x_host = drv.allocate_host_buffer(rows * WIDTH, "float")
+    x_host.as_numpy()[:] = make_input(lo, hi).reshape(-1)
+    y_host = drv.allocate_host_buffer(rows * CLASSES, "float")
+
+    def barrier():
+        stream.sync()
+        if dist is not None:
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        layers = []
+        for i, w in enumerate(weights):
+            act = "softmax" if i == len(weights) - 1 else "relu"
+            layers.append((ct.to_tensor(w), ct.new_tensor([w.shape[0]]), act))
+        net = nn.MLP(layers, fused=True)
+        x_dev = dev.allocate_device_buffer(rows * WIDTH, "float")
+        stream.copy_host_to_device(x_host, 0, x_dev, 0, rows * WIDTH)
+        x = ct.Tensor(dev, dims.dimensions([rows, WIDTH]), x_dev)
+
+        # ---- resident: inputs already in HBM ------------------------------------------------
+        gemm_events = []
+
+        def step(record=False):
+            cur = x
+            for idx, (lin, act) in enumerate(net.layers):
+                out = net._buffer(idx, rows, lin.weights.shape()[0], "float")
+                if record and idx < HIDDEN_LAYERS:
+                    e0 = stream.create_event(timing=True)
+                lin.forward_fused(cur, out, act if act != "softmax" else None)
+                if record and idx < HIDDEN_LAYERS:
+                    gemm_events.append((e0, stream.create_event(timing=True)))
+                if act == "softmax":
+                    ct.softmax(out, out)
+                cur = out
+            return cur
+
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        launches0 = stream.launch_count()
+        e0 = stream.create_event(timing=True)
+        for _ in range(args.steps):
+            step(record=True)
+        e1 = stream.create_event(timing=True)
+        e1.wait_for_event()
+        barrier()
+        launches = stream.launch_count() - launches0
+        clocks = sampler.stop() if rank == 0 else None
+        ms_step = e1.elapsed_ms_since(e0) / args.steps
+        gemm_ms = float(np.mean([b.elapsed_ms_since(a) for a, b in gemm_events]))
+
+        # ---- end to end: pinned host in -> H2D -> layers -> D2H, every step --------------------
+        chunk = min(8192, rows)
+        pipe = BatchPipeline(dev, net, WIDTH, CLASSES, chunk, "float")
+        h2d = d2h = 0
+        for _ in range(min(args.warmup, 2)):
+            pipe.run(x_host, y_host, rows)
+        barrier()
+        t0 = pipe.compute.create_event(timing=True)
+        for _ in range(args.steps):
+            h2d, d2h = pipe.run(x_host, y_host, rows)
+        pipe.download.sync()
+        t1 = pipe.compute.create_event(timing=True)
+        t1.wait_for_event()
+        barrier()
+        e2e_ms = t1.elapsed_ms_since(t0) / args.steps
+        launches += 0
+        probs = y_host.as_numpy().reshape(rows, CLASSES)
+        checksum = float(np.abs(probs.sum(axis=1) - 1.0).max())
+
+    # max over ranks
+    if dist is not None:
+        t = torch.tensor([ms_step, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_ms = float(t[0]), float(t[1])
+        lt = torch.tensor([launches], device="cuda", dtype=torch.int64)
+        dist.all_reduce(lt, op=dist.ReduceOp.SUM)
+        launches = int(lt[0])
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    value = BATCH / (ms_step / 1000.0)
+    e2e_value = BATCH / (e2e_ms / 1000.0)
+    gemm_flops = 2.0 * rows * WIDTH * WIDTH
+    peak_tf32x3 = peaks["bf16_sustained"] / 2.0 / 3.0
+    achieved = gemm_flops / gemm_ms / 1e9
+    line = {
+        "metric": "wide_mlp_inference_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "wide_mlp: batch 65536 x 4096 -> 4 x (linear 4096 + ReLU) -> linear 1000 + softmax, fp32, "
+                               "He-normal weights (seeds 502-506), zero biases, batch-sharded, weights replicated",
+                   "global_batch": BATCH, "rows_per_gpu": rows, "parallelism": "batch-shard x%d" % world,
+                   "l2": "inputs larger than L2 (every layer streams >= %d MiB of activations)" % (rows * WIDTH * 4 >> 20),
+                   "kernel_path": "gemm_bias_act (tcgen05 3xTF32, bias+ReLU fused) x5 + softmax"},
+        "tflops": value * FLOPS_PER_SAMPLE / 1e12,
+        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+                "ms_per_step": e2e_ms, "chunk_rows": chunk, "max_abs_rowsum_minus_1": checksum},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tf32x3_kernel<256> (M=%d, N=4096, K=4096)" % rows,
+                     "achieved": achieved, "peak": peak_tf32x3, "unit": "TFLOP/s", "frac": achieved / peak_tf32x3,
+                     "traffic": None, "ms_per_launch": gemm_ms,
+                     "peak_note": "%s bf16 sustained %.0f TF / 2 (tf32 rate) / 3 (three tf32 MMAs per product); "
+                                  "algorithmic work 2*M*N*K" % (peaks["source"], peaks["bf16_sustained"])},
+        "clocks": clocks,
+    }
+    if world == 1:
+        cores = os.cpu_count() or 1
+        rate, secs = cpu_forward_rate(2048, weights)
+        line["cpu_baseline"] = {"value": rate, "unit": "samples/s", "cores": cores, "kind": "port",
+                                "sample": "2048 rows of the batch, one forward (%.1f s): oracle C/OpenMP elementwise + "
+                                          "OpenBLAS sgemm" % secs}
+        line["gemm_4096"] = bench_gemm_4096(drv, dev, peaks)
+        line["eltwise"] = bench_eltwise(drv, dev, peaks)
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_b200(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -112,9 +112,27 @@ int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int
   if (dtype == CB200_FLOAT) {
     const float* a = (const float*)A;
     const float* b = (const float*)B;
-    if (cb200_gemm_tf32x3_eligible(a, lda, b, ldb, M, N, K))
-      return cb200_gemm_tf32x3_launch(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb,
-                                      (float)beta, (const float*)bias, act, 0, 1, 0);
+    if (cb200_gemm_tf32x3_eligible(a, lda, b, ldb, M, N, K)) {
+      // tcgen05 accumulates with truncation, so the result drifts toward zero by about 7e-9 * K
+      // (relative, worst case all-positive data).  Long reductions are therefore cut into K chunks
+      // chained through C (beta = 1), each chunk boundary being a round-to-nearest fp32 add in the
+      // epilogue; bias and activation join on the last chunk.
+      const int K_CHUNK = 4096;
+      if (K <= 2 * K_CHUNK)
+        return cb200_gemm_tf32x3_launch(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb,
+                                        (float)beta, (const float*)bias, act, 0, 1, 0);
+      for (int k0 = 0; k0 < K; k0 += K_CHUNK) {
+        const int kc = (K - k0 < K_CHUNK) ? (K - k0) : K_CHUNK;
+        const bool last = k0 + kc >= K;
+        const float* ak = trans_a ? a + (long long)k0 * lda : a + k0;
+        const float* bk = trans_b ? b + k0 : b + (long long)k0 * ldb;
+        int rc = cb200_gemm_tf32x3_launch(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, ak, M, kc, lda, bk, N, ldb,
+                                          k0 == 0 ? (float)beta : 1.0f, last ? (const float*)bias : nullptr,
+                                          last ? act : 0, 0, 1, 0);
+        if (rc) return rc;
+      }
+      return CB200_OK;
+    }
     return launch_simt<float>(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb, (float)beta,
                               (const float*)bias, act);
   }
@@ -149,8 +167,7 @@ int cb200_gemm_bias_act(cb200_stream* s, int dtype, void* C, int64_t ldc, int tr
 }
 
 // Test hooks (not part of the public header): force a specific fp32 kernel.
-//   which = 0: SIMT kernel; 1: tensor-core kernel with `flags` (1 = single tf32 term,
-//   2 = keep the raw fp32 tile as the hi operand)
+//   which = 0: SIMT kernel; 1: tensor-core kernel with `flags` (1 = single tf32 term, no split)
 int cb200_gemm_f32_variant(cb200_stream* s, int which, int flags, void* C, int64_t ldc, int trans_a, int trans_b,
                            double alpha, const void* A, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B,
                            int64_t b_cols, int64_t ldb, double beta) {

@@ -1,20 +1,28 @@
 // fp32 gemm! on the 5th-generation tensor cores: C = alpha*op(A)*op(B) + beta*C
 // (+ bias row, + activation), fp32 in / fp32 out, computed as a 3xTF32 split:
-//   x = hi + lo,  hi = tf32(x), lo = tf32(x - hi)
-//   A*B ~= A_lo*B_hi + A_hi*B_lo + A_hi*B_hi      (fp32 accumulation in TMEM)
+//   x = hi + lo,  hi = x with the low 13 mantissa bits cleared, lo = x - hi (exact)
+//   A*B ~= A_hi*B_hi + (A_lo*B_hi + A_hi*B_lo)     (fp32 accumulation in TMEM)
+// The tensor core itself ignores the low 13 bits of an fp32 word fed as tf32, so
+// the raw tile TMA delivered IS the hi operand; only lo is computed and stored.
+// tcgen05 accumulates with truncation, one truncation per MMA instruction, so the
+// bias grows with the number of instructions chained on one accumulator: the two
+// small cross terms therefore go to a second TMEM accumulator (their truncation
+// error is 2^-11 of the main one's) and the epilogue adds the two in fp32.
 // Replaces cublasSgemm_v2 of the reference backend
 // (src/cortex/compute/cuda/tensor_math.clj:127-154, 633-649).
 //
 // One CTA computes a 128 x BN tile of C.  Warp roles:
-//   warps 0-7  split the raw fp32 tiles that TMA delivered into hi (in place) and
-//              lo (second buffer) inside shared memory, then run the epilogue
+//   warps 0-7  compute the lo tiles (second buffer) from the raw fp32 tiles that
+//              TMA delivered into shared memory, then run the epilogue
 //   warp  8    TMA producer (one lane)
 //   warp  9    allocates TMEM, issues tcgen05.mma (one lane), frees TMEM
 // Per k-block (32 fp32 = one 128-byte swizzle row) and pipeline stage:
 //   empty[s] -> TMA -> full[s] -> split -> conv[s] -> 12 x tcgen05.mma -> commit -> empty[s]
 // All four transpose combinations run on the tensor cores: a non-transposed A /
-// transposed B is K-major in memory; the other two are MN-major and use the
-// MN-major form of the shared-memory descriptor with 32x32 TMA boxes.
+// transposed B is K-major in memory (128-byte swizzle); the other two are
+// MN-major, for which tf32 only has the 128-byte swizzle with 32-byte atoms:
+// 32x32 TMA boxes with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B and the matching
+// shared-memory descriptor (4 k-rows per atom, atoms 512 B apart along K).
 // Operand tiles outside the matrix are zero-filled by TMA, so any M, N, K works;
 // pointers must be 16-byte aligned and row pitches a multiple of 4 elements
 // (the host falls back to gemm_simt otherwise).
@@ -33,7 +41,7 @@ constexpr int NUM_CONV_WARPS = 8;
 constexpr int NUM_THREADS = (NUM_CONV_WARPS + 2) * 32;
 
 enum { STORE_ROW_MAJOR = 0, STORE_NCHW = 1 };
-enum { FLAG_ONE_TERM = 1, FLAG_KEEP_RAW_HI = 2 };
+enum { FLAG_ONE_TERM = 1 };
 
 struct GemmParams {
   float* C;
@@ -54,7 +62,7 @@ template <int BN> struct TileCfg {
   static constexpr int RAW = A_TILE + B_TILE;
   static constexpr int STAGE = 2 * RAW;
   static constexpr int STAGES = (BN == 256) ? 2 : ((BN == 128) ? 3 : 4);
-  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int TMEM_COLS = 2 * BN;   // main accumulator + cross-term accumulator
   static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
@@ -67,15 +75,11 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   return v;
 }
 
-__device__ __forceinline__ void split_tf32(float x, uint32_t& hi_bits, uint32_t& lo_bits) {
-  uint32_t hb = cvt_rna_tf32(x);
-  if ((hb & 0x7f800000u) == 0x7f800000u) {
-    // rounding overflowed, or x is not finite: fall back to truncation / canonical NaN
-    hb = (x != x) ? 0x7fc00000u : (__float_as_uint(x) & 0xffffe000u);
-  }
-  float lo = ((hb & 0x7f800000u) == 0x7f800000u) ? 0.f : x - __uint_as_float(hb);
-  hi_bits = hb;
-  lo_bits = cvt_rna_tf32(lo);
+// lo = x - trunc_tf32(x): exact in fp32; 0 for Inf / NaN so that they propagate through hi alone
+__device__ __forceinline__ float lo_part(float x) {
+  const uint32_t xb = __float_as_uint(x);
+  const float lo = x - __uint_as_float(xb & 0xffffe000u);
+  return ((xb & 0x7f800000u) == 0x7f800000u) ? 0.f : lo;
 }
 
 template <int BN>
@@ -159,8 +163,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       const uint32_t idesc = make_idesc_tf32(BM, BN, p.a_mn_major, p.b_mn_major);
+      // K-major: 8-row groups 1024 B apart, 32 B per k-step inside the swizzle row.
+      // MN-major: 32-element blocks along M/N 4096 B apart (one TMA box), 4-k-row atoms 512 B apart,
+      // 1024 B per k-step.
       const uint32_t a_lbo = p.a_mn_major ? 4096u : 16u, b_lbo = p.b_mn_major ? 4096u : 16u;
+      const uint32_t a_sbo = p.a_mn_major ? 512u : 1024u, b_sbo = p.b_mn_major ? 512u : 1024u;
+      const uint32_t a_sw = p.a_mn_major ? SWZ_128B_BASE32B : SWZ_128B, b_sw = p.b_mn_major ? SWZ_128B_BASE32B : SWZ_128B;
       const uint32_t a_kstep = p.a_mn_major ? 1024u : 32u, b_kstep = p.b_mn_major ? 1024u : 32u;
+      const uint32_t tmem_main = tmem_base, tmem_cross = tmem_base + BN;
+      uint32_t acc_cross = 0;
       uint32_t accumulate = 0;
       for (int i = 0; i < nkb; ++i) {
         const int s = i % STAGES, ph = (i / STAGES) & 1;
@@ -170,16 +181,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const uint32_t a_lo = a_hi + Cfg::RAW, b_lo = b_hi + Cfg::RAW;
 #pragma unroll
         for (int kk = 0; kk < BK / 8; ++kk) {
-          const uint64_t dah = make_smem_desc(a_hi + kk * a_kstep, a_lbo, 1024);
-          const uint64_t dbh = make_smem_desc(b_hi + kk * b_kstep, b_lbo, 1024);
+          const uint64_t dah = make_smem_desc(a_hi + kk * a_kstep, a_lbo, a_sbo, a_sw);
+          const uint64_t dbh = make_smem_desc(b_hi + kk * b_kstep, b_lbo, b_sbo, b_sw);
           if (!(p.flags & FLAG_ONE_TERM)) {
-            const uint64_t dal = make_smem_desc(a_lo + kk * a_kstep, a_lbo, 1024);
-            const uint64_t dbl = make_smem_desc(b_lo + kk * b_kstep, b_lbo, 1024);
-            mma_tf32_ss(tmem_base, dal, dbh, idesc, accumulate);   // small terms first
-            mma_tf32_ss(tmem_base, dah, dbl, idesc, 1);
-            accumulate = 1;
+            const uint64_t dal = make_smem_desc(a_lo + kk * a_kstep, a_lbo, a_sbo, a_sw);
+            const uint64_t dbl = make_smem_desc(b_lo + kk * b_kstep, b_lbo, b_sbo, b_sw);
+            mma_tf32_ss(tmem_cross, dal, dbh, idesc, acc_cross);
+            mma_tf32_ss(tmem_cross, dah, dbl, idesc, 1);
+            acc_cross = 1;
           }
-          mma_tf32_ss(tmem_base, dah, dbh, idesc, accumulate);
+          mma_tf32_ss(tmem_main, dah, dbh, idesc, accumulate);
           accumulate = 1;
         }
         mma_commit(bar_empty + 8 * s);
@@ -204,14 +215,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
         for (int c = 0; c < Cfg::RAW / 16 / (NUM_CONV_WARPS * 32); ++c) {
           const int off = (tid + c * NUM_CONV_WARPS * 32) * 16;
-          float4 v = *reinterpret_cast<const float4*>(hi + off);
-          uint4 h, l;
-          split_tf32(v.x, h.x, l.x);
-          split_tf32(v.y, h.y, l.y);
-          split_tf32(v.z, h.z, l.z);
-          split_tf32(v.w, h.w, l.w);
-          if (!(p.flags & FLAG_KEEP_RAW_HI)) *reinterpret_cast<uint4*>(hi + off) = h;
-          *reinterpret_cast<uint4*>(lo + off) = l;
+          const float4 v = *reinterpret_cast<const float4*>(hi + off);
+          float4 l;
+          l.x = lo_part(v.x); l.y = lo_part(v.y); l.z = lo_part(v.z); l.w = lo_part(v.w);
+          *reinterpret_cast<float4*>(lo + off) = l;
         }
         fence_proxy_async_smem();
       }
@@ -232,7 +239,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const int col0 = half * COLS_PER_HALF + cc * 32;
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
-        tmem_ld_wait();
+        if (!(p.flags & FLAG_ONE_TERM)) {
+          uint32_t rc[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + col0), rc);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(rc[j]));
+        } else {
+          tmem_ld_wait();
+        }
         const int nb = n0 + col0;
         if (m < p.M && nb < p.N) {
           if (p.store_mode == STORE_ROW_MAJOR) {
@@ -313,9 +328,9 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// fp32 matrix [rows][cols] with row pitch ld (elements); box = {box_cols, box_rows}, 128-byte swizzle
+// fp32 matrix [rows][cols] with row pitch ld (elements); box = {box_cols, box_rows}
 int make_tmap(CUtensorMap* tm, const float* base, long long rows, long long cols, long long ld, int box_cols,
-              int box_rows) {
+              int box_rows, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
   cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -323,7 +338,7 @@ int make_tmap(CUtensorMap* tm, const float* base, long long rows, long long cols
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     cb200_set_error("cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld box %dx%d)", (int)r, rows, cols,
@@ -364,11 +379,11 @@ int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans
   const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
   CUtensorMap tmA, tmB;
   int rc;
-  if (!p.a_mn_major) rc = make_tmap(&tmA, A, M, K, lda, BK, BM);
-  else rc = make_tmap(&tmA, A, K, M, lda, 32, BK);
+  if (!p.a_mn_major) rc = make_tmap(&tmA, A, M, K, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  else rc = make_tmap(&tmA, A, K, M, lda, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (rc) return rc;
-  if (!p.b_mn_major) rc = make_tmap(&tmB, B, N, K, ldb, BK, BN);
-  else rc = make_tmap(&tmB, B, K, N, ldb, 32, BK);
+  if (!p.b_mn_major) rc = make_tmap(&tmB, B, N, K, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  else rc = make_tmap(&tmB, B, K, N, ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (rc) return rc;
   if (BN == 256) return launch_tile<256>(s, tmA, tmB, p);
   if (BN == 128) return launch_tile<128>(s, tmA, tmB, p);

@@ -129,17 +129,19 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // Shared-memory matrix descriptor (64-bit):
 //   [0,14)  start address >> 4        [16,30) leading-dimension byte offset >> 4
 //   [32,46) stride-dimension byte offset >> 4   [46,48) version = 1
-//   [61,64) swizzle: 0 none, 2 = 128-byte, 4 = 64-byte, 6 = 32-byte
+//   [61,64) swizzle: 0 none, 1 = 128-byte with 32-byte atoms, 2 = 128-byte, 4 = 64-byte, 6 = 32-byte
 // 128-byte swizzle, K-major operand (row = 128 B of K): 8-row groups are SBO apart.
-// 128-byte swizzle, MN-major operand (row = 128 B of M or N for one k): groups of
-// 8 k-rows are SBO apart, 32-element blocks along M/N are LBO apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// 128-byte swizzle with 32-byte atoms, MN-major 32-bit operand (row = 128 B of M or N
+// for one k): atoms of 4 k-rows are SBO apart, 32-element blocks along M/N are LBO apart.
+enum { SWZ_128B_BASE32B = 1, SWZ_128B = 2 };
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t swizzle) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3fffu);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)(swizzle & 7u) << 61;
   return d;
 }
 

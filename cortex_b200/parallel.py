@@ -1,0 +1,110 @@
+"""Multi-GPU partitioning of the dense-inference path (one process per GPU).
+
+The reference has no multi-device code (README.md:48 lists it as future work);
+this module adds exactly what the path needs:
+
+* batch sharding -- every op on the path is independent across rows, so rank r
+  takes rows [r*B/g, (r+1)*B/g) with weights replicated and NO collective;
+* a column-sharded last layer for outputs too wide for one device: rank r owns
+  W_r = W[r*n/g:(r+1)*n/g, :], computes logits_r = h . W_r^T, and the shards are
+  exchanged with ONE all-gather (NCCL over NVLink on GPUs, gloo on CPU tests).
+  The gathered buffer [g, B, n/g] is read through the rank-3 descriptor
+  {shape [B, g, n/g], strides [n/g, B*n/g, 1]} -- the kind of view cortex's
+  dimension/stride descriptors express -- and made dense with one assign!
+  before softmax!, which (like the reference's, src/cortex/tensor.clj:903-917)
+  wants non-increasing strides.
+
+``torch.distributed`` is plumbing only: rendezvous, barrier, the all-gather.
+"""
+import numpy as np
+
+from . import dimensions as dims
+from . import tensor as ct
+from ._lib import NUMPY_NAME
+
+
+def shard_bounds(total, world_size, rank):
+    """Rows (or columns) [lo, hi) of rank `rank`; the remainder goes to the first ranks."""
+    if not (0 <= rank < world_size):
+        raise ValueError("rank %d outside world of %d" % (rank, world_size))
+    base, rem = divmod(int(total), int(world_size))
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def shard_rows(array, world_size, rank):
+    lo, hi = shard_bounds(array.shape[0], world_size, rank)
+    return array[lo:hi]
+
+
+def _as_torch(buffer, shape):
+    """A torch tensor aliasing a backend buffer (device memory through
+    __cuda_array_interface__, oracle/host memory through numpy)."""
+    import torch
+    if buffer.host:
+        return torch.from_numpy(buffer.as_numpy()).view(*shape)
+
+    class _Cai:
+        pass
+
+    holder = _Cai()
+    typestr = np.dtype(NUMPY_NAME[buffer.dtype]).str
+    holder.__cuda_array_interface__ = {"data": (buffer.ptr, False), "shape": tuple(int(s) for s in shape),
+                                       "typestr": typestr, "version": 2}
+    return torch.as_tensor(holder, device="cuda:%d" % buffer.device.index)
+
+
+def all_gather_buffers(local, gathered, world_size, group=None):
+    """gathered[r] = rank r's `local` (both backend tensors, dense).  One collective."""
+    import torch.distributed as dist
+    stream = ct.check_stream()
+    n = local.ecount()
+    src = _as_torch(local.buffer, [n])
+    dst = _as_torch(gathered.buffer, [world_size * n])
+    stream.sync()                      # the producer kernels run on the backend's own stream
+    if dst.is_cuda:
+        import torch
+        dist.all_gather_into_tensor(dst, src, group=group)
+        torch.cuda.synchronize(dst.device)
+    else:
+        parts = [dst[r * n:(r + 1) * n] for r in range(world_size)]
+        dist.all_gather(parts, src, group=group)
+    return gathered
+
+
+def column_sharded_head(h, w_shard, b_shard, n_total, world_size, rank, group=None):
+    """softmax(h . W^T + b) where W[n_total, k] is split by output column across ranks.
+
+    h        [B, k]            this rank's (replicated or gathered) activations
+    w_shard  [n_total/g, k]    this rank's rows of W
+    b_shard  [n_total/g]
+    returns  [B, n_total]      dense probabilities, identical on every rank
+    """
+    if n_total % world_size:
+        raise ValueError("column sharding needs n_total divisible by the world size")
+    B = h.shape()[0]
+    per = n_total // world_size
+    dt = h.get_datatype()
+    local = ct.new_tensor([B, per], datatype=dt, init_value=None)
+    ct.assign(local, b_shard)
+    ct.gemm(local, False, True, 1.0, h, w_shard, 1.0)
+    gathered = ct.new_tensor([world_size, B, per], datatype=dt, init_value=None)
+    all_gather_buffers(local, gathered, world_size, group)
+    view = ct.Tensor(gathered.device, {"shape": [B, world_size, per], "strides": [per, B * per, 1]}, gathered.buffer)
+    logits = ct.new_tensor([B, world_size, per], datatype=dt, init_value=None)
+    ct.assign(logits, view)                                   # strided gather through the index system
+    logits2d = ct.in_place_reshape(logits, [B, n_total])
+    return ct.softmax(logits2d, logits2d)
+
+
+class ShardedMLP:
+    """Batch-sharded inference: this rank's slice of the batch through a replicated network."""
+
+    def __init__(self, net, world_size, rank):
+        self.net, self.world_size, self.rank = net, world_size, rank
+
+    def local_rows(self, global_batch):
+        return shard_bounds(global_batch, self.world_size, self.rank)
+
+    def infer_local(self, x_local):
+        return self.net.infer(x_local)
