@@ -397,7 +397,16 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise"],
+                    help="mlp = the benchmark; gemm4096 / eltwise = the small single-purpose runs used for ncu captures")
     args = ap.parse_args()
+    if args.case != "mlp":
+        from cortex_b200.driver import driver
+        drv = driver()
+        dev = drv.default_device()
+        fn = bench_gemm_4096 if args.case == "gemm4096" else bench_eltwise
+        print(json.dumps({args.case: fn(drv, dev, measured_peaks())}), flush=True)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

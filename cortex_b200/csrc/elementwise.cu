@@ -137,6 +137,50 @@ struct UnaryF {
   __device__ __forceinline__ T operator()(T x, T) const { return unary_apply<T>(op, (A)((A)x * alpha)); }
 };
 
+// float views: a float*float product is exact in double and every basic operation on two
+// floats gives the same result whether it is rounded once from double or done in single
+// precision (53 >= 2*24 + 2), so with alpha == 1 the whole op runs in fp32, bit-identically,
+// and stays clear of the slow f32<->f64 conversion pipe.
+__device__ __forceinline__ float bin_apply_f32(int op, float a, float b) {
+  switch (op) {
+    case CB200_ADD: return a + b;
+    case CB200_SUB: return a - b;
+    case CB200_MUL: return a * b;
+    case CB200_DIV: return __fdiv_rn(a, b);
+    case CB200_MAX: return a > b ? a : b;
+    case CB200_MIN: return a > b ? b : a;
+    case CB200_EQ: return a == b ? 1.f : 0.f;
+    case CB200_GT: return a > b ? 1.f : 0.f;
+    case CB200_GE: return a >= b ? 1.f : 0.f;
+    case CB200_LT: return a < b ? 1.f : 0.f;
+    case CB200_LE: return a <= b ? 1.f : 0.f;
+  }
+  return (float)bin_apply(op, (double)a, (double)b);
+}
+
+template <>
+struct UnaryF<float> {
+  static const int NIN = 1;
+  typedef float TX;
+  int op;
+  double alpha;
+  __device__ __forceinline__ float operator()(float x, float) const {
+    if (alpha == 1.0) {
+      switch (op) {
+        case CB200_FLOOR: return floorf(x);
+        case CB200_CEIL: return ceilf(x);
+        case CB200_NEG: return -x;
+        case CB200_TANH: return tanhf(x);
+        case CB200_LOGISTIC: return 1.0f / (1.0f + expf(-x));
+        case CB200_EXP: return expf(x);
+        case CB200_SQRT: return __fsqrt_rn(x);
+        case CB200_NOOP: return x;
+      }
+    }
+    return unary_apply<float>(op, (double)x * alpha);
+  }
+};
+
 template <typename T>
 struct BinaryConstF {
   static const int NIN = 1;
@@ -149,6 +193,23 @@ struct BinaryConstF {
     A a = (A)x * alpha;
     A r = rev ? bin_apply(op, scalar, a) : bin_apply(op, a, scalar);
     return store_as<T>::from(r);
+  }
+};
+
+template <>
+struct BinaryConstF<float> {
+  static const int NIN = 1;
+  typedef float TX;
+  int op;
+  int rev;
+  double alpha, scalar;   // scalar was cast to float first, so (float)scalar is exact
+  __device__ __forceinline__ float operator()(float x, float) const {
+    if (alpha == 1.0) {
+      const float sc = (float)scalar;
+      return rev ? bin_apply_f32(op, sc, x) : bin_apply_f32(op, x, sc);
+    }
+    double a = (double)x * alpha;
+    return (float)(rev ? bin_apply(op, scalar, a) : bin_apply(op, a, scalar));
   }
 };
 
@@ -167,22 +228,39 @@ struct BinaryF {
   }
 };
 
+template <>
+struct BinaryF<float> {
+  static const int NIN = 2;
+  typedef float TX;
+  int op;
+  int rev;
+  double xa, ya;
+  __device__ __forceinline__ float operator()(float x, float y) const {
+    if (xa == 1.0 && ya == 1.0) return rev ? bin_apply_f32(op, y, x) : bin_apply_f32(op, x, y);
+    if (xa == 1.0 && ya == -1.0 && op == CB200_ADD) return rev ? (-y) + x : x - y;   // binary-op! :- arrives as :+ with -beta
+    double a = (double)x * xa, b = (double)y * ya;
+    return (float)(rev ? bin_apply(op, b, a) : bin_apply(op, a, b));
+  }
+};
+
 // ------------------------------ kernels -------------------------------------
 
 template <typename T, int N>
 struct alignas(sizeof(T) * N) Vec { T v[N]; };
 
+// Element counts are 32-bit, as in the reference (int n_elems in every kernel), so the
+// index arithmetic below stays in 32-bit registers.
 struct FlatMode {   // address of element i:  kind 0: i   1: i % ec   2: ((i / amt) % ec) * stride
   int kind;
   int stride;
-  long long ec;
-  long long amt;
+  unsigned ec;
+  unsigned amt;
 };
 
 template <typename T, int VEC>
-__device__ __forceinline__ void flat_load(const T* p, const FlatMode& m, long long i0, bool vec_ok, T (&out)[VEC]) {
+__device__ __forceinline__ void flat_load(const T* p, const FlatMode& m, unsigned i0, bool vec_ok, T (&out)[VEC]) {
   if (m.kind == 0 || m.kind == 1) {
-    long long a = m.kind == 0 ? i0 : (i0 % m.ec);
+    unsigned a = m.kind == 0 ? i0 : (i0 % m.ec);
     if (vec_ok) {
       Vec<T, VEC> v = *reinterpret_cast<const Vec<T, VEC>*>(p + a);
 #pragma unroll
@@ -193,12 +271,12 @@ __device__ __forceinline__ void flat_load(const T* p, const FlatMode& m, long lo
     }
   } else {
     if (vec_ok) {
-      T v = p[((i0 / m.amt) % m.ec) * m.stride];
+      T v = p[(size_t)((i0 / m.amt) % m.ec) * m.stride];
 #pragma unroll
       for (int k = 0; k < VEC; ++k) out[k] = v;
     } else {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) out[k] = p[(((i0 + k) / m.amt) % m.ec) * m.stride];
+      for (int k = 0; k < VEC; ++k) out[k] = p[(size_t)(((i0 + k) / m.amt) % m.ec) * m.stride];
     }
   }
 }
@@ -209,14 +287,14 @@ __device__ __forceinline__ void flat_load(const T* p, const FlatMode& m, long lo
 template <typename TD, typename F, int VEC, int UNROLL>
 __global__ void __launch_bounds__(256)
 ew_flat(TD* dest, const typename F::TX* x, const typename F::TX* y,
-        FlatMode mx, FlatMode my, int xv, int yv, long long n, F f) {
+        FlatMode mx, FlatMode my, int xv, int yv, unsigned n, F f) {
   typedef typename F::TX TX;
-  const long long n_vec = n / VEC;
-  const long long base = ((long long)blockIdx.x * UNROLL) * blockDim.x + threadIdx.x;
+  const unsigned n_vec = n / VEC;
+  const unsigned base = (blockIdx.x * UNROLL) * blockDim.x + threadIdx.x;
   TX xs[UNROLL][VEC], ys[UNROLL][VEC];
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
-    long long c = base + (long long)u * blockDim.x;
+    unsigned c = base + u * blockDim.x;
     if (c < n_vec) {
       if (F::NIN >= 1) flat_load<TX, VEC>(x, mx, c * VEC, xv != 0, xs[u]);
       if (F::NIN >= 2) flat_load<TX, VEC>(y, my, c * VEC, yv != 0, ys[u]);
@@ -224,17 +302,17 @@ ew_flat(TD* dest, const typename F::TX* x, const typename F::TX* y,
   }
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
-    long long c = base + (long long)u * blockDim.x;
+    unsigned c = base + u * blockDim.x;
     if (c < n_vec) {
       Vec<TD, VEC> o;
 #pragma unroll
       for (int k = 0; k < VEC; ++k)
         o.v[k] = f(F::NIN >= 1 ? xs[u][k] : TX(), F::NIN >= 2 ? ys[u][k] : TX());
-      *reinterpret_cast<Vec<TD, VEC>*>(dest + c * VEC) = o;
+      *reinterpret_cast<Vec<TD, VEC>*>(dest + (size_t)c * VEC) = o;
     }
   }
   // scalar tail
-  long long t = n_vec * VEC + base;
+  unsigned t = n_vec * VEC + base;
   if (blockIdx.x == 0 && t < n) {
     TX xe = TX(), ye = TX();
     if (F::NIN >= 1) { TX tmp[1]; flat_load<TX, 1>(x, mx, t, false, tmp); xe = tmp[0]; }
@@ -375,13 +453,13 @@ bool flat_mode(const Operand& o, const Geometry& g, FlatMode& m) {
   if (suffix) {
     bool full = true;
     for (int d = last + 1; d < 5; ++d) if (g.max_shape[d] != 1) full = false;
-    m.kind = full ? 0 : 1; m.ec = ec; m.amt = 1; m.stride = 1;
+    m.kind = full ? 0 : 1; m.ec = (unsigned)ec; m.amt = 1; m.stride = 1;
     return true;
   }
   if (nontrivial == 1 && o.shape[last] == g.max_shape[last]) {
     long long amt = 1;
     for (int d = 0; d < last; ++d) amt *= g.max_shape[d];
-    m.kind = 2; m.ec = o.shape[last]; m.amt = amt; m.stride = o.stride[last];
+    m.kind = 2; m.ec = (unsigned)o.shape[last]; m.amt = (unsigned)amt; m.stride = o.stride[last];
     return true;
   }
   return false;
@@ -416,6 +494,7 @@ int launch_map(cb200_stream* s, TD* dest, const cb200_dims* dd, const typename F
                const typename F::TX* y, const cb200_dims* yd, long long n, const F& f) {
   typedef typename F::TX TX;
   if (n <= 0) return CB200_OK;
+  CB_REQUIRE(n <= 2147483647LL, "element count %lld exceeds the 32-bit index range of the tensor protocol", n);
   Operand ops[3];
   operand_from_dims(ops[0], dd);
   int n_ops = 1;
@@ -444,7 +523,7 @@ int launch_map(cb200_stream* s, TD* dest, const cb200_dims* dd, const typename F
     long long n_vec = n / VEC;
     long long blocks = (n_vec + 256 * UNROLL - 1) / (256 * UNROLL);
     if (blocks < 1) blocks = 1;
-    ew_flat<TD, F, VEC, UNROLL><<<(unsigned)blocks, 256, 0, s->stream>>>(dest, x, y, mx, my, xv, yv, n, f);
+    ew_flat<TD, F, VEC, UNROLL><<<(unsigned)blocks, 256, 0, s->stream>>>(dest, x, y, mx, my, xv, yv, (unsigned)n, f);
     CB_LAUNCH_CHECK(s);
     return CB200_OK;
   }

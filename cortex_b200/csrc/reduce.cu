@@ -111,43 +111,61 @@ reduce_rows(T* out, const T* in, Operand oo, Operand oi, Geometry go, Geometry g
   }
 }
 
-// 16-byte vector variant for aligned contiguous rows (len % VEC == 0)
+// 16-byte vector variant for aligned contiguous rows (len % VEC == 0): 8 independent
+// 16-byte loads in flight per thread.  FAST (float rows, max / min, alpha == 1) compares
+// in fp32 -- exact, and it avoids one f32->f64 conversion per element.
 template <typename T, int VEC>
 struct alignas(sizeof(T) * VEC) RVec { T v[VEC]; };
 
-template <typename T, int NWARPS>
+template <typename T, typename A, bool FAST>
+__device__ __forceinline__ void red_vec_accum(int op, A& acc, float& facc, const RVec<T, 16 / sizeof(T)>& v, A alpha,
+                                              bool unit) {
+  constexpr int VEC = 16 / sizeof(T);
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    if (FAST) {
+      float f = (float)v.v[k];
+      facc = op == CB200_RMAX ? clj_max(facc, f) : ((facc != facc) ? facc : ((f != f) ? f : (facc < f ? facc : f)));
+    } else {
+      A e = unit ? (A)v.v[k] : (A)(alpha * (A)v.v[k]);
+      acc = red_combine(op, acc, red_elem(op, e));
+    }
+  }
+}
+
+template <typename T, int NWARPS, bool FAST>
 __global__ void __launch_bounds__(256)
 reduce_rows_vec(T* out, const T* in, Operand oo, Operand oi, Geometry go, Geometry gi, long long n_rows, int len,
                 int op, typename acc_of<T>::type alpha) {
   typedef typename acc_of<T>::type A;
   constexpr int VEC = 16 / sizeof(T);
+  constexpr int U = 8;
   __shared__ A smem[8];
   const int rows_per_block = NWARPS == 1 ? 8 : 1;
   const int tid = NWARPS == 1 ? (threadIdx.x & 31) : threadIdx.x;
   const int nthreads = NWARPS == 1 ? 32 : 256;
   const int nvec = len / VEC;
+  const bool unit = alpha == (A)1;
   for (long long r0 = (long long)blockIdx.x * rows_per_block; r0 < n_rows; r0 += (long long)gridDim.x * rows_per_block) {
     long long r = NWARPS == 1 ? r0 + (threadIdx.x >> 5) : r0;
     A acc = red_identity<A>(op);
+    float facc = op == CB200_RMAX ? -INFINITY : INFINITY;
     if (r < n_rows) {
       const RVec<T, VEC>* row = reinterpret_cast<const RVec<T, VEC>*>(in + operand_offset(oi, gi, r * len));
       int j = tid;
-      for (; j + 3 * nthreads < nvec; j += 4 * nthreads) {
-        RVec<T, VEC> v0 = row[j], v1 = row[j + nthreads], v2 = row[j + 2 * nthreads], v3 = row[j + 3 * nthreads];
+      for (; j + (U - 1) * nthreads < nvec; j += U * nthreads) {
+        RVec<T, VEC> v[U];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-          acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v0.v[k])));
-          acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v1.v[k])));
-          acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v2.v[k])));
-          acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v3.v[k])));
-        }
+        for (int u = 0; u < U; ++u) v[u] = row[j + u * nthreads];
+#pragma unroll
+        for (int u = 0; u < U; ++u) red_vec_accum<T, A, FAST>(op, acc, facc, v[u], alpha, unit);
       }
       for (; j < nvec; j += nthreads) {
         RVec<T, VEC> v0 = row[j];
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) acc = red_combine(op, acc, red_elem(op, (A)(alpha * (A)v0.v[k])));
+        red_vec_accum<T, A, FAST>(op, acc, facc, v0, alpha, unit);
       }
     }
+    if (FAST) acc = (A)facc;
     acc = block_combine<A, NWARPS>(op, acc, smem);
     if (tid == 0 && r < n_rows) out[operand_offset(oo, go, r)] = red_finish<T>(op, acc, len);
   }
@@ -181,11 +199,17 @@ void geometry_of(Geometry& g, const Operand& o) {
 // Steps as softmax-impl (cpu/tensor_math.clj:1037-1088): m = max; e = exp(x - m)
 // rounded to the element type; s = sum of the rounded e in double, rounded;
 // y = e / s in the element type.
+// fp32 rows: x - m in fp32 equals the double difference rounded once; the exponential is the
+// hardware ex2 path (|rel err| ~ 1e-6 on the terms that matter), the row sum is a per-thread
+// fp32 partial combined in double, and the divide is a multiply by the reciprocal: all within
+// the 1e-4 parity bound, and the kernel stays on the HBM roofline.  fp64 rows follow the
+// reference arithmetic exactly up to summation order.
 template <typename T> __device__ __forceinline__ T sm_exp(T x, T m);
-template <> __device__ __forceinline__ float sm_exp<float>(float x, float m) {
-  return expf((float)((double)x - (double)m));
-}
+template <> __device__ __forceinline__ float sm_exp<float>(float x, float m) { return __expf(x - m); }
 template <> __device__ __forceinline__ double sm_exp<double>(double x, double m) { return exp(x - m); }
+template <typename T> __device__ __forceinline__ T sm_norm(T e, T s, T inv);
+template <> __device__ __forceinline__ float sm_norm<float>(float e, float, float inv) { return e * inv; }
+template <> __device__ __forceinline__ double sm_norm<double>(double e, double s, double) { return e / s; }
 
 struct SoftmaxGeom {
   long long rows;
@@ -212,30 +236,36 @@ softmax_rows(T* out, const T* in, SoftmaxGeom g) {
     const T* x = in + (rr / g.inner) * g.in_outer + (rr % g.inner) * g.in_inner;
     T* y = out + (rr / g.inner) * g.out_outer + (rr % g.inner) * g.out_inner;
     T v[PER];
-    double m = -INFINITY;
+    T mloc = -INFINITY;
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
       int j = tid + k * nthreads;
-      if (live && j < g.C) { v[k] = x[(long long)j * g.in_cs]; m = clj_max(m, (double)v[k]); }
+      if (live && j < g.C) v[k] = x[(long long)j * g.in_cs];
     }
-    m = block_combine<double, NWARPS>(CB200_RMAX, m, smem);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      int j = tid + k * nthreads;
+      if (live && j < g.C) mloc = (mloc != mloc) ? mloc : ((v[k] != v[k]) ? v[k] : (mloc > v[k] ? mloc : v[k]));
+    }
+    double m = block_combine<double, NWARPS>(CB200_RMAX, (double)mloc, smem);
     if (NWARPS == 1) m = __shfl_sync(0xffffffffu, m, 0);
     else { if (threadIdx.x == 0) bcast = m; __syncthreads(); m = bcast; }
     T mt = (T)m;
-    double s = 0.0;
+    T sloc = (T)0;
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
       int j = tid + k * nthreads;
-      if (live && j < g.C) { v[k] = sm_exp<T>(v[k], mt); s += (double)v[k]; }
+      if (live && j < g.C) { v[k] = sm_exp<T>(v[k], mt); sloc += v[k]; }
     }
-    s = block_combine<double, NWARPS>(CB200_RSUM, s, smem);
+    double s = block_combine<double, NWARPS>(CB200_RSUM, (double)sloc, smem);
     if (NWARPS == 1) s = __shfl_sync(0xffffffffu, s, 0);
     else { __syncthreads(); if (threadIdx.x == 0) bcast = s; __syncthreads(); s = bcast; }
-    T st = (T)s;
+    const T st = (T)s;
+    const T inv = (T)1 / st;
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
       int j = tid + k * nthreads;
-      if (live && j < g.C) y[(long long)j * g.out_cs] = v[k] / st;
+      if (live && j < g.C) y[(long long)j * g.out_cs] = sm_norm<T>(v[k], st, inv);
     }
     if (NWARPS != 1) __syncthreads();
   }
@@ -300,7 +330,7 @@ bias_relu_rowstats_k(T* Y, long long ldy, const T* X, long long ldx, const T* bi
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
     const T* x = X + r * ldx;
     T* y = Y + r * ldy;
-    double mx = -INFINITY, sum = 0.0;
+    T mx = -INFINITY, sum = (T)0;
     T v[PER];
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
@@ -311,18 +341,17 @@ bias_relu_rowstats_k(T* Y, long long ldy, const T* X, long long ldx, const T* bi
     for (int k = 0; k < PER; ++k) {
       int j = threadIdx.x + k * 256;
       if (j < cols) {
-        T t = (T)((double)v[k] + (double)bias[j]);   // binary-op! :+ , rounded to the element type
-        double td = (double)t;
-        T o = (T)(td > 0.0 ? td : 0.0);              // binary-op! :max with scalar 0
+        T t = v[k] + bias[j];          // binary-op! :+ (same value as the double sum rounded once)
+        T o = t > (T)0 ? t : (T)0;     // binary-op! :max with scalar 0
         y[j] = o;
-        mx = clj_max(mx, (double)o);
-        sum += (double)o;
+        mx = (mx != mx) ? mx : ((o != o) ? o : (mx > o ? mx : o));
+        sum += o;                      // per-thread partial in the element type, combined in double
       }
     }
-    mx = block_combine<double, 8>(CB200_RMAX, mx, smem);
-    if (threadIdx.x == 0 && rowmax) rowmax[r] = (T)mx;
-    sum = block_combine<double, 8>(CB200_RSUM, sum, smem);
-    if (threadIdx.x == 0 && rowsum) rowsum[r] = (T)sum;
+    double mxd = block_combine<double, 8>(CB200_RMAX, (double)mx, smem);
+    if (threadIdx.x == 0 && rowmax) rowmax[r] = (T)mxd;
+    double sumd = block_combine<double, 8>(CB200_RSUM, (double)sum, smem);
+    if (threadIdx.x == 0 && rowsum) rowsum[r] = (T)sumd;
     __syncthreads();
   }
 }
@@ -362,14 +391,19 @@ int cb200_unary_reduce(cb200_stream* s, int dtype, void* out, const cb200_dims* 
     if (contiguous) {
       bool vec = (len % VEC) == 0 && ((uintptr_t)in % 16) == 0;
       for (int d = 1; d < gi.ndims && vec; ++d) if (oi.shape[d] > 1 && (oi.stride[d] % VEC) != 0) vec = false;
-      if ((size_t)len * sizeof(T) >= 2048) {
+      // one warp per row while there are enough rows to occupy every SM, one CTA per row otherwise
+      const bool cta_per_row = (size_t)len * sizeof(T) >= 2048 && n_out < (long long)s->sm_count * 32;
+      const bool fast = sizeof(T) == 4 && dtype == CB200_FLOAT && (op == CB200_RMAX || op == CB200_RMIN) && a == (A)1;
+      if (cta_per_row) {
         long long blocks = n_out < cap ? n_out : cap;
-        if (vec) reduce_rows_vec<T, 8><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
+        if (vec && fast) reduce_rows_vec<T, 8, true><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
+        else if (vec) reduce_rows_vec<T, 8, false><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
         else reduce_rows<T, 8><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
       } else {
         long long blocks = (n_out + 7) / 8;
         if (blocks > cap) blocks = cap;
-        if (vec) reduce_rows_vec<T, 1><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
+        if (vec && fast) reduce_rows_vec<T, 1, true><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
+        else if (vec) reduce_rows_vec<T, 1, false><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
         else reduce_rows<T, 1><<<(unsigned)blocks, 256, 0, s->stream>>>((T*)out, (const T*)in, oo, oi, go, gi, n_out, len, op, a);
       }
     } else {
