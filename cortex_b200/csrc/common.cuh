@@ -136,18 +136,22 @@ struct Geometry {
   int ndims;   // dimensions beyond ndims all have max_shape 1
 };
 
-__device__ __forceinline__ long long operand_offset(const Operand& o, const Geometry& g, long long i) {
+// Element indexes are 32-bit in the tensor protocol (int n_elems), so the divisions stay 32-bit;
+// only the resulting offset is widened.
+__device__ __forceinline__ long long operand_offset(const Operand& o, const Geometry& g, long long idx) {
+  unsigned i = (unsigned)idx;
   long long off = 0;
 #pragma unroll
   for (int d = 0; d < 5; ++d) {
     if (d < g.ndims) {
-      int m = g.max_shape[d];
-      int c = (int)(i % m);
-      i /= m;
-      int sh = o.shape[d];
+      unsigned m = (unsigned)g.max_shape[d];
+      unsigned q = i / m;
+      unsigned c = i - q * m;
+      i = q;
+      unsigned sh = (unsigned)o.shape[d];
       if (sh != m) c = c % sh;
-      if (o.index[d]) c = o.index[d][c];
-      off += (long long)o.stride[d] * c;
+      if (o.index[d]) c = (unsigned)o.index[d][c];
+      off += (long long)o.stride[d] * (long long)c;
     }
   }
   return off;

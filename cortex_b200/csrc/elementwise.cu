@@ -243,6 +243,33 @@ struct BinaryF<float> {
   }
 };
 
+// fp32, unit scale factors, operation fixed at compile time: what the dense layers issue
+// (bias add, ReLU as max with 0, softmax's subtract / divide).  Same values as the generic
+// functors above; the kernels they instantiate are a handful of instructions per element.
+template <int OP> __device__ __forceinline__ float f32_op(float a, float b);
+template <> __device__ __forceinline__ float f32_op<CB200_ADD>(float a, float b) { return a + b; }
+template <> __device__ __forceinline__ float f32_op<CB200_SUB>(float a, float b) { return a - b; }
+template <> __device__ __forceinline__ float f32_op<CB200_MUL>(float a, float b) { return a * b; }
+template <> __device__ __forceinline__ float f32_op<CB200_DIV>(float a, float b) { return __fdiv_rn(a, b); }
+template <> __device__ __forceinline__ float f32_op<CB200_MAX>(float a, float b) { return a > b ? a : b; }
+template <> __device__ __forceinline__ float f32_op<CB200_MIN>(float a, float b) { return a > b ? b : a; }
+
+template <int OP, int REV>
+struct FastBinaryF {
+  static const int NIN = 2;
+  typedef float TX;
+  __device__ __forceinline__ float operator()(float x, float y) const { return REV ? f32_op<OP>(y, x) : f32_op<OP>(x, y); }
+};
+template <int OP, int REV>
+struct FastBinaryConstF {
+  static const int NIN = 1;
+  typedef float TX;
+  float scalar;
+  __device__ __forceinline__ float operator()(float x, float) const {
+    return REV ? f32_op<OP>(scalar, x) : f32_op<OP>(x, scalar);
+  }
+};
+
 // ------------------------------ kernels -------------------------------------
 
 template <typename T, int N>
@@ -281,38 +308,41 @@ __device__ __forceinline__ void flat_load(const T* p, const FlatMode& m, unsigne
   }
 }
 
-// dest is dense and full-size.  n_vec = n / VEC full chunks; the tail is done
-// scalar by the last threads.  xv / yv say whether the input admits one vector
-// (or one broadcast scalar) access per chunk.
+// dest is dense and full-size.  n_vec = n / VEC full chunks; the tail is done scalar by the
+// first threads.  xv / yv say whether the input admits one vector (or one broadcast scalar)
+// access per chunk.  Grid-stride: the grid is sized to fill every SM once, each thread keeps
+// UNROLL independent 16-byte loads in flight per operand.
 template <typename TD, typename F, int VEC, int UNROLL>
 __global__ void __launch_bounds__(256)
 ew_flat(TD* dest, const typename F::TX* x, const typename F::TX* y,
         FlatMode mx, FlatMode my, int xv, int yv, unsigned n, F f) {
   typedef typename F::TX TX;
   const unsigned n_vec = n / VEC;
-  const unsigned base = (blockIdx.x * UNROLL) * blockDim.x + threadIdx.x;
-  TX xs[UNROLL][VEC], ys[UNROLL][VEC];
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned base = blockIdx.x * blockDim.x + threadIdx.x; base < n_vec; base += stride * UNROLL) {
+    TX xs[UNROLL][VEC], ys[UNROLL][VEC];
 #pragma unroll
-  for (int u = 0; u < UNROLL; ++u) {
-    unsigned c = base + u * blockDim.x;
-    if (c < n_vec) {
-      if (F::NIN >= 1) flat_load<TX, VEC>(x, mx, c * VEC, xv != 0, xs[u]);
-      if (F::NIN >= 2) flat_load<TX, VEC>(y, my, c * VEC, yv != 0, ys[u]);
+    for (int u = 0; u < UNROLL; ++u) {
+      unsigned c = base + u * stride;
+      if (c < n_vec) {
+        if (F::NIN >= 1) flat_load<TX, VEC>(x, mx, c * VEC, xv != 0, xs[u]);
+        if (F::NIN >= 2) flat_load<TX, VEC>(y, my, c * VEC, yv != 0, ys[u]);
+      }
     }
-  }
 #pragma unroll
-  for (int u = 0; u < UNROLL; ++u) {
-    unsigned c = base + u * blockDim.x;
-    if (c < n_vec) {
-      Vec<TD, VEC> o;
+    for (int u = 0; u < UNROLL; ++u) {
+      unsigned c = base + u * stride;
+      if (c < n_vec) {
+        Vec<TD, VEC> o;
 #pragma unroll
-      for (int k = 0; k < VEC; ++k)
-        o.v[k] = f(F::NIN >= 1 ? xs[u][k] : TX(), F::NIN >= 2 ? ys[u][k] : TX());
-      *reinterpret_cast<Vec<TD, VEC>*>(dest + (size_t)c * VEC) = o;
+        for (int k = 0; k < VEC; ++k)
+          o.v[k] = f(F::NIN >= 1 ? xs[u][k] : TX(), F::NIN >= 2 ? ys[u][k] : TX());
+        *reinterpret_cast<Vec<TD, VEC>*>(dest + (size_t)c * VEC) = o;
+      }
     }
   }
   // scalar tail
-  unsigned t = n_vec * VEC + base;
+  unsigned t = n_vec * VEC + threadIdx.x;
   if (blockIdx.x == 0 && t < n) {
     TX xe = TX(), ye = TX();
     if (F::NIN >= 1) { TX tmp[1]; flat_load<TX, 1>(x, mx, t, false, tmp); xe = tmp[0]; }
@@ -327,43 +357,59 @@ ew_flat(TD* dest, const typename F::TX* x, const typename F::TX* y,
 template <typename TD, typename F, int VEC>
 __global__ void __launch_bounds__(256)
 ew_rowvec(TD* dest, const typename F::TX* x, const typename F::TX* y,
-          Operand od, Operand ox, Operand oy, Geometry g, int x_row, int y_row, long long n_chunks, F f) {
+          Operand od, Operand ox, Operand oy, Geometry g, int x_row, int y_row, unsigned n_chunks, F f) {
   typedef typename F::TX TX;
-  const int chunks_per_row = g.max_shape[0] / VEC;
-  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks;
-       c += (long long)gridDim.x * blockDim.x) {
-    long long row = c / chunks_per_row;
-    int col = (int)(c - row * chunks_per_row) * VEC;
-    long long i = row * g.max_shape[0];
-    TX xs[VEC], ys[VEC];
-    if (F::NIN >= 1) {
-      const TX* p = x + operand_offset(ox, g, i);
-      if (x_row) {
-        Vec<TX, VEC> v = *reinterpret_cast<const Vec<TX, VEC>*>(p + col);
+  constexpr int UNROLL = 4;
+  const unsigned chunks_per_row = (unsigned)g.max_shape[0] / VEC;
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned base = blockIdx.x * blockDim.x + threadIdx.x; base < n_chunks; base += stride * UNROLL) {
+    TX xs[UNROLL][VEC], ys[UNROLL][VEC];
+    long long doff[UNROLL];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) xs[k] = v.v[k];
-      } else {
-        TX v = *p;
+    for (int u = 0; u < UNROLL; ++u) {
+      const unsigned c = base + u * stride;
+      if (c < n_chunks) {
+        const unsigned row = c / chunks_per_row;
+        const unsigned col = (c - row * chunks_per_row) * VEC;
+        const unsigned i = row * (unsigned)g.max_shape[0];
+        doff[u] = operand_offset(od, g, i) + col;
+        if (F::NIN >= 1) {
+          const TX* p = x + operand_offset(ox, g, i);
+          if (x_row) {
+            Vec<TX, VEC> v = *reinterpret_cast<const Vec<TX, VEC>*>(p + col);
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) xs[k] = v;
+            for (int k = 0; k < VEC; ++k) xs[u][k] = v.v[k];
+          } else {
+            TX v = *p;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) xs[u][k] = v;
+          }
+        }
+        if (F::NIN >= 2) {
+          const TX* p = y + operand_offset(oy, g, i);
+          if (y_row) {
+            Vec<TX, VEC> v = *reinterpret_cast<const Vec<TX, VEC>*>(p + col);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) ys[u][k] = v.v[k];
+          } else {
+            TX v = *p;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) ys[u][k] = v;
+          }
+        }
       }
     }
-    if (F::NIN >= 2) {
-      const TX* p = y + operand_offset(oy, g, i);
-      if (y_row) {
-        Vec<TX, VEC> v = *reinterpret_cast<const Vec<TX, VEC>*>(p + col);
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) ys[k] = v.v[k];
-      } else {
-        TX v = *p;
+    for (int u = 0; u < UNROLL; ++u) {
+      const unsigned c = base + u * stride;
+      if (c < n_chunks) {
+        Vec<TD, VEC> o;
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) ys[k] = v;
+        for (int k = 0; k < VEC; ++k)
+          o.v[k] = f(F::NIN >= 1 ? xs[u][k] : TX(), F::NIN >= 2 ? ys[u][k] : TX());
+        *reinterpret_cast<Vec<TD, VEC>*>(dest + doff[u]) = o;
       }
     }
-    Vec<TD, VEC> o;
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) o.v[k] = f(F::NIN >= 1 ? xs[k] : TX(), F::NIN >= 2 ? ys[k] : TX());
-    *reinterpret_cast<Vec<TD, VEC>*>(dest + operand_offset(od, g, i) + col) = o;
   }
 }
 
@@ -522,6 +568,8 @@ int launch_map(cb200_stream* s, TD* dest, const cb200_dims* dd, const typename F
     int xv = F::NIN >= 1 ? vec_ok(mx, x) : 1, yv = F::NIN >= 2 ? vec_ok(my, y) : 1;
     long long n_vec = n / VEC;
     long long blocks = (n_vec + 256 * UNROLL - 1) / (256 * UNROLL);
+    long long full = (long long)s->sm_count * 8;    // 2048 threads per SM
+    if (blocks > full) blocks = full;
     if (blocks < 1) blocks = 1;
     ew_flat<TD, F, VEC, UNROLL><<<(unsigned)blocks, 256, 0, s->stream>>>(dest, x, y, mx, my, xv, yv, (unsigned)n, f);
     CB_LAUNCH_CHECK(s);
@@ -536,8 +584,10 @@ int launch_map(cb200_stream* s, TD* dest, const cb200_dims* dd, const typename F
   for (int d = 0; d < 5; ++d) total *= g.max_shape[d];
   if (rv && n == total) {
     long long n_chunks = n / VEC;
-    ew_rowvec<TD, F, VEC><<<grid_for(s, n_chunks, 256), 256, 0, s->stream>>>(dest, x, y, ops[0], ops[1], ops[2], g,
-                                                                            xr, yr, n_chunks, f);
+    long long rblocks = (n_chunks + 1023) / 1024, rfull = (long long)s->sm_count * 8;
+    if (rblocks > rfull) rblocks = rfull;
+    ew_rowvec<TD, F, VEC><<<(unsigned)rblocks, 256, 0, s->stream>>>(dest, x, y, ops[0], ops[1], ops[2], g, xr, yr,
+                                                                    (unsigned)n_chunks, f);
     CB_LAUNCH_CHECK(s);
     return CB200_OK;
   }
@@ -559,6 +609,41 @@ int launch_accum_cas(cb200_stream* s, T* dest, const cb200_dims* dd, const T* y,
   DeviceGuard guard(s->device);
   ew_accum_cas<T><<<grid_for(s, n, 256), 256, 0, s->stream>>>(dest, y, ops[0], ops[1], g, n, f, has_y, fc);
   CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+// fp32 + unit scale factors + one of the six arithmetic ops -> compile-time-op kernels
+#define CB_FAST_OPS(X) X(CB200_ADD) X(CB200_SUB) X(CB200_MUL) X(CB200_DIV) X(CB200_MAX) X(CB200_MIN)
+
+int fast_binary_f32(cb200_stream* s, float* dest, const cb200_dims* dd, const float* x, const cb200_dims* xd,
+                    const float* y, const cb200_dims* yd, long long n, int op, int rev, bool* handled) {
+  *handled = true;
+  switch (op) {
+#define X(OPC)                                                                                                      \
+    case OPC:                                                                                                       \
+      if (rev) return launch_map<float, FastBinaryF<OPC, 1> >(s, dest, dd, x, xd, y, yd, n, FastBinaryF<OPC, 1>()); \
+      return launch_map<float, FastBinaryF<OPC, 0> >(s, dest, dd, x, xd, y, yd, n, FastBinaryF<OPC, 0>());
+    CB_FAST_OPS(X)
+#undef X
+  }
+  *handled = false;
+  return CB200_OK;
+}
+
+int fast_binary_const_f32(cb200_stream* s, float* dest, const cb200_dims* dd, const float* x, const cb200_dims* xd,
+                          float scalar, long long n, int op, int rev, bool* handled) {
+  *handled = true;
+  switch (op) {
+#define X(OPC)                                                                                              \
+    case OPC: {                                                                                             \
+      if (rev) { FastBinaryConstF<OPC, 1> f; f.scalar = scalar;                                             \
+        return launch_map<float, FastBinaryConstF<OPC, 1> >(s, dest, dd, x, xd, nullptr, nullptr, n, f); }  \
+      FastBinaryConstF<OPC, 0> f; f.scalar = scalar;                                                        \
+      return launch_map<float, FastBinaryConstF<OPC, 0> >(s, dest, dd, x, xd, nullptr, nullptr, n, f); }
+    CB_FAST_OPS(X)
+#undef X
+  }
+  *handled = false;
   return CB200_OK;
 }
 
@@ -655,6 +740,12 @@ int cb200_binary_op_constant(cb200_stream* s, int dtype, void* dest, const cb200
   if (rc) return rc;
   rc = cb200_check_dims(x_dims, "binary_op_constant x");
   if (rc) return rc;
+  if (dtype == CB200_FLOAT && (float)x_alpha == 1.0f) {
+    bool handled = false;
+    rc = fast_binary_const_f32(s, (float*)dest, dest_dims, (const float*)x, x_dims, (float)scalar, n_elems, op,
+                               rev_ops, &handled);
+    if (handled) return rc;
+  }
   CB_DISPATCH_DTYPE(dtype, T, {
     BinaryConstF<T> f; f.op = op; f.rev = rev_ops; f.alpha = scalar_as<T>(x_alpha); f.scalar = scalar_as<T>(scalar);
     return launch_map<T, BinaryConstF<T> >(s, (T*)dest, dest_dims, (const T*)x, x_dims, nullptr, nullptr, n_elems, f);
@@ -702,6 +793,13 @@ int cb200_binary_op(cb200_stream* s, int dtype, void* dest, const cb200_dims* de
   if (rc) return rc;
   rc = cb200_check_dims(y_dims, "binary_op y");
   if (rc) return rc;
+  if (dtype == CB200_FLOAT && (float)x_alpha == 1.0f && ((float)y_alpha == 1.0f || ((float)y_alpha == -1.0f && op == CB200_ADD))) {
+    // binary-op! :- reaches the backend as :+ with a negated beta (src/cortex/tensor.clj:774-778)
+    bool handled = false;
+    rc = fast_binary_f32(s, (float*)dest, dest_dims, (const float*)x, x_dims, (const float*)y, y_dims, n_elems,
+                         (float)y_alpha == -1.0f ? CB200_SUB : op, 0, &handled);
+    if (handled) return rc;
+  }
   CB_DISPATCH_DTYPE(dtype, T, {
     BinaryF<T> f; f.op = op; f.rev = 0; f.xa = scalar_as<T>(x_alpha); f.ya = scalar_as<T>(y_alpha);
     return launch_map<T, BinaryF<T> >(s, (T*)dest, dest_dims, (const T*)x, x_dims, (const T*)y, y_dims, n_elems, f);
@@ -737,6 +835,12 @@ int cb200_binary_accum(cb200_stream* s, int dtype, void* dest, const cb200_dims*
         cb200_set_error("binary_accum: compare-and-swap accumulation exists for int, long, float, double only");
         return CB200_ERR_INVALID;
     }
+  }
+  if (dtype == CB200_FLOAT && (float)dest_alpha == 1.0f && ((float)y_alpha == 1.0f || ((float)y_alpha == -1.0f && op == CB200_ADD && !rev_ops))) {
+    bool handled = false;
+    rc = fast_binary_f32(s, (float*)dest, dest_dims, (const float*)dest, dest_dims, (const float*)y, y_dims, n_elems,
+                         (float)y_alpha == -1.0f ? CB200_SUB : op, rev_ops, &handled);
+    if (handled) return rc;
   }
   CB_DISPATCH_DTYPE(dtype, T, {
     BinaryF<T> f; f.op = op; f.rev = rev_ops; f.xa = scalar_as<T>(dest_alpha); f.ya = scalar_as<T>(y_alpha);

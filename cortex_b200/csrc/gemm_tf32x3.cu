@@ -16,7 +16,7 @@
 //              TMA delivered into shared memory, then run the epilogue
 //   warp  8    TMA producer (one lane)
 //   warp  9    allocates TMEM, issues tcgen05.mma (one lane), frees TMEM
-// Per k-block (32 fp32 = one 128-byte swizzle row) and pipeline stage:
+// Per k-block (16 or 32 fp32 = one 64- or 128-byte swizzle row) and pipeline stage:
 //   empty[s] -> TMA -> full[s] -> split -> conv[s] -> 12 x tcgen05.mma -> commit -> empty[s]
 // All four transpose combinations run on the tensor cores: a non-transposed A /
 // transposed B is K-major in memory (128-byte swizzle); the other two are
@@ -35,13 +35,11 @@ using namespace sm100;
 namespace {
 
 constexpr int BM = 128;
-constexpr int BK = 32;                 // fp32 elements per k-block = 128 bytes
-constexpr int A_TILE = BM * BK * 4;    // 16 KiB
 constexpr int NUM_CONV_WARPS = 8;
 constexpr int NUM_THREADS = (NUM_CONV_WARPS + 2) * 32;
 
 enum { STORE_ROW_MAJOR = 0, STORE_NCHW = 1 };
-enum { FLAG_ONE_TERM = 1 };
+enum { FLAG_ONE_TERM = 1, FLAG_BK32 = 2 };
 
 struct GemmParams {
   float* C;
@@ -57,12 +55,16 @@ struct GemmParams {
   int* status;
 };
 
-template <int BN> struct TileCfg {
+// BK = fp32 elements per k-block: 32 (one 128-byte swizzle row per operand row) or 16 (64-byte
+// rows).  The smaller block halves the stage, which doubles the number of stages that fit and
+// lets the TMA latency + lo-tile pass of one stage hide behind more MMA work.
+template <int BN, int BK> struct TileCfg {
+  static constexpr int A_TILE = BM * BK * 4;
   static constexpr int B_TILE = BN * BK * 4;
   static constexpr int RAW = A_TILE + B_TILE;
-  static constexpr int STAGE = 2 * RAW;
-  static constexpr int STAGES = (BN == 256) ? 2 : ((BN == 128) ? 3 : 4);
-  static constexpr int TMEM_COLS = 2 * BN;   // main accumulator + cross-term accumulator
+  static constexpr int STAGE = 2 * RAW;                 // raw (= hi) tiles + lo tiles
+  static constexpr int STAGES = (196608 / STAGE) > 8 ? 8 : (196608 / STAGE);
+  static constexpr int TMEM_COLS = 2 * BN;              // main accumulator + cross-term accumulator
   static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
@@ -82,11 +84,13 @@ __device__ __forceinline__ float lo_part(float x) {
   return ((xb & 0x7f800000u) == 0x7f800000u) ? 0.f : lo;
 }
 
-template <int BN>
+template <int BN, int BK>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
-  typedef TileCfg<BN> Cfg;
+  typedef TileCfg<BN, BK> Cfg;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int A_TILE = Cfg::A_TILE;
+  constexpr int BOX = BK * 128;          // bytes of one 32 x BK MN-major TMA box
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::STAGE);
@@ -107,7 +111,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_conv + 8 * s, NUM_CONV_WARPS * 32);
+      mbar_init(bar_conv + 8 * s, NUM_CONV_WARPS);
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_acc, 1);
@@ -142,13 +146,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           tma_load_2d(a_dst, &tmA, k0, m0, full);
         } else {
 #pragma unroll
-          for (int j = 0; j < BM / 32; ++j) tma_load_2d(a_dst + j * 4096, &tmA, m0 + 32 * j, k0, full);
+          for (int j = 0; j < BM / 32; ++j) tma_load_2d(a_dst + j * BOX, &tmA, m0 + 32 * j, k0, full);
         }
         if (!p.b_mn_major) {
           tma_load_2d(b_dst, &tmB, k0, n0, full);
         } else {
 #pragma unroll
-          for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &tmB, n0 + 32 * j, k0, full);
+          for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * BOX, &tmB, n0 + 32 * j, k0, full);
         }
         issued = i + 1;
       }
@@ -163,12 +167,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       const uint32_t idesc = make_idesc_tf32(BM, BN, p.a_mn_major, p.b_mn_major);
-      // K-major: 8-row groups 1024 B apart, 32 B per k-step inside the swizzle row.
-      // MN-major: 32-element blocks along M/N 4096 B apart (one TMA box), 4-k-row atoms 512 B apart,
-      // 1024 B per k-step.
-      const uint32_t a_lbo = p.a_mn_major ? 4096u : 16u, b_lbo = p.b_mn_major ? 4096u : 16u;
-      const uint32_t a_sbo = p.a_mn_major ? 512u : 1024u, b_sbo = p.b_mn_major ? 512u : 1024u;
-      const uint32_t a_sw = p.a_mn_major ? SWZ_128B_BASE32B : SWZ_128B, b_sw = p.b_mn_major ? SWZ_128B_BASE32B : SWZ_128B;
+      // K-major: rows of BK*4 bytes (128- or 64-byte swizzle), 8-row groups 8*BK*4 B apart, 32 B per
+      // k-step inside the row.  MN-major: 32-element blocks along M/N one TMA box apart, 4-k-row
+      // atoms 512 B apart, 1024 B per k-step.
+      constexpr uint32_t K_SWZ = BK == 32 ? SWZ_128B : SWZ_64B;
+      constexpr uint32_t K_SBO = 8 * BK * 4;
+      const uint32_t a_lbo = p.a_mn_major ? (uint32_t)BOX : 16u, b_lbo = p.b_mn_major ? (uint32_t)BOX : 16u;
+      const uint32_t a_sbo = p.a_mn_major ? 512u : K_SBO, b_sbo = p.b_mn_major ? 512u : K_SBO;
+      const uint32_t a_sw = p.a_mn_major ? SWZ_128B_BASE32B : K_SWZ, b_sw = p.b_mn_major ? SWZ_128B_BASE32B : K_SWZ;
       const uint32_t a_kstep = p.a_mn_major ? 1024u : 32u, b_kstep = p.b_mn_major ? 1024u : 32u;
       const uint32_t tmem_main = tmem_base, tmem_cross = tmem_base + BN;
       uint32_t acc_cross = 0;
@@ -222,7 +228,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         fence_proxy_async_smem();
       }
-      mbar_arrive(bar_conv + 8 * s);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_conv + 8 * s);   // one arrive per warp
     }
     if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 400);
     ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
@@ -348,18 +355,18 @@ int make_tmap(CUtensorMap* tm, const float* base, long long rows, long long cols
   return CB200_OK;
 }
 
-template <int BN>
+template <int BN, int BK>
 int launch_tile(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p) {
-  typedef TileCfg<BN> Cfg;
+  typedef TileCfg<BN, BK> Cfg;
   static std::once_flag once[64];
   int dev = s->device;
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
   });
   if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
   long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  gemm_tf32x3_kernel<BN><<<(unsigned)tiles, NUM_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmB, p);
+  gemm_tf32x3_kernel<BN, BK><<<(unsigned)tiles, NUM_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmB, p);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
@@ -377,17 +384,24 @@ int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans
   p.b_mn_major = trans_b ? 0 : 1;   // op(B)[k][n] = B[k][n]: N is the contiguous axis
   p.store_mode = store_mode; p.hw = hw > 0 ? hw : 1; p.flags = flags; p.status = s->status_dev;
   const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  const int BK = (flags & FLAG_BK32) ? 32 : 16;
+  const CUtensorMapSwizzle kswz = BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap tmA, tmB;
   int rc;
-  if (!p.a_mn_major) rc = make_tmap(&tmA, A, M, K, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!p.a_mn_major) rc = make_tmap(&tmA, A, M, K, lda, BK, BM, kswz);
   else rc = make_tmap(&tmA, A, K, M, lda, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (rc) return rc;
-  if (!p.b_mn_major) rc = make_tmap(&tmB, B, N, K, ldb, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!p.b_mn_major) rc = make_tmap(&tmB, B, N, K, ldb, BK, BN, kswz);
   else rc = make_tmap(&tmB, B, K, N, ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (rc) return rc;
-  if (BN == 256) return launch_tile<256>(s, tmA, tmB, p);
-  if (BN == 128) return launch_tile<128>(s, tmA, tmB, p);
-  return launch_tile<64>(s, tmA, tmB, p);
+  if (BK == 32) {
+    if (BN == 256) return launch_tile<256, 32>(s, tmA, tmB, p);
+    if (BN == 128) return launch_tile<128, 32>(s, tmA, tmB, p);
+    return launch_tile<64, 32>(s, tmA, tmB, p);
+  }
+  if (BN == 256) return launch_tile<256, 16>(s, tmA, tmB, p);
+  if (BN == 128) return launch_tile<128, 16>(s, tmA, tmB, p);
+  return launch_tile<64, 16>(s, tmA, tmB, p);
 }
 
 bool cb200_gemm_tf32x3_eligible(const float* A, long long lda, const float* B, long long ldb, int M, int N, int K) {

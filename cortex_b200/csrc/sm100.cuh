@@ -133,7 +133,7 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // 128-byte swizzle, K-major operand (row = 128 B of K): 8-row groups are SBO apart.
 // 128-byte swizzle with 32-byte atoms, MN-major 32-bit operand (row = 128 B of M or N
 // for one k): atoms of 4 k-rows are SBO apart, 32-element blocks along M/N are LBO apart.
-enum { SWZ_128B_BASE32B = 1, SWZ_128B = 2 };
+enum { SWZ_128B_BASE32B = 1, SWZ_128B = 2, SWZ_64B = 4 };
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                                    uint32_t swizzle) {
   uint64_t d = 0;
