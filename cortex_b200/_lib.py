@@ -79,6 +79,7 @@ SIGNATURES = {
     "cb200_softmax_spatial": [_vp, _i, _vp, _pd, _vp, _pd],
     "cb200_convolution_workspace_size": [C.POINTER(ConvDesc), _i, _i, _i, _i, _i, C.POINTER(_i64)],
     "cb200_convolution_forward": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
+    "cb200_convolution_forward_static": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, C.POINTER(ConvDesc)],
     "cb200_unsupported": [C.c_char_p],
     "cb200_gemm_bias_act": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i],
     "cb200_bias_relu_rowstats": [_vp, _i, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp],

@@ -12,6 +12,7 @@
 // The unrolled matrix lives in the stream's scratch buffer, not in the caller's
 // workspace.
 #include "common.cuh"
+#include <mutex>
 
 int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
                              const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
@@ -129,6 +130,126 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
   CB_LAUNCH_CHECK(s);
   for (int n = 0; n < g.batch; ++n) {
     // per image, as the reference: out_n[C_out, hw] = W[C_out, K] * cols_n[hw, K]^T + out_alpha * out_n
+    rc = cb200_gemm_f64_launch(s, (double*)out + (long long)n * cout * hw, hw, 0, 1, 1.0, (const double*)w, cout,
+                               g.kcols, g.kcols, (const double*)cols + (long long)n * hw * g.ld, hw, g.ld, out_alpha,
+                               nullptr, 0);
+    if (rc) return rc;
+  }
+  return CB200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// convolution-forward! for callers that must not allocate.
+//
+// cb200_convolution_forward unrolls the input into a per-stream scratch buffer that it grows with
+// cudaMalloc on demand.  Some hosts of this library cannot tolerate that: a serving loop that has
+// handed all device memory to its own pool, a process that forbids the implicit device-wide
+// synchronisation of cudaMalloc / cudaFree on its latency path, or code that runs between two
+// points where allocation is simply not allowed.  This variant keeps the unrolled matrix in a
+// fixed array that is part of the library image instead.
+//
+//  * The array is CB200_STATIC_CONV_SCRATCH_BYTES (64 MiB) of device memory per GPU that loads the
+//    library, held until the process exits whether or not this entry point is ever called.
+//  * A problem whose unrolled matrix (batch*outH*outW rows x C_in*kH*kW columns, columns rounded up
+//    to 4) does not fit is rejected with CB200_ERR_INVALID and a message; nothing is launched.
+//  * The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
+//    that device current) and caches it.  Make that first call before any stream capture.
+//    No call allocates or frees device or host memory, directly or through a library.
+//  * All calls, on all streams of a device, share the one array, and it keeps the previous call's
+//    contents.  im2col rewrites every element of the region a call uses (padding columns included),
+//    so nothing needs clearing between calls; but two calls whose kernels overlap on the GPU
+//    (different streams, no event between them) race on it.  Serialise them.
+#define CB200_STATIC_CONV_SCRATCH_BYTES (64ull << 20)
+static __device__ __align__(256) unsigned char g_static_conv_scratch[CB200_STATIC_CONV_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_ptr[64] = {nullptr};
+
+// Device address of g_static_conv_scratch on `device` (which must be current).  In host code the
+// array's name is only a handle for the runtime, never a pointer a kernel may be given.
+int static_scratch_address(int device, void** out) {
+  CB_REQUIRE(device >= 0 && device < 64, "convolution_forward_static: device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[device]) {
+    void* p = nullptr;
+    CB_CUDA(cudaGetSymbolAddress(&p, g_static_conv_scratch));
+    CB_REQUIRE(p != nullptr, "convolution_forward_static: the static scratch array has no device address");
+    g_static_scratch_ptr[device] = p;
+  }
+  *out = g_static_scratch_ptr[device];
+  return CB200_OK;
+}
+}  // namespace
+
+int cb200_convolution_forward_static(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims,
+                                     double out_alpha, const void* in, const cb200_dims* in_dims, const void* w,
+                                     const cb200_dims* w_dims, const cb200_conv_desc* desc) {
+  CB_REQUIRE(s && out && out_dims && in && in_dims && w && w_dims && desc, "convolution_forward_static: null argument");
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE,
+             "convolution-forward! is only defined for float and double tensors");
+  ConvGeom g;
+  g.batch = in_dims->rev_shape[3]; g.cin = in_dims->rev_shape[2]; g.in_h = in_dims->rev_shape[1]; g.in_w = in_dims->rev_shape[0];
+  g.out_h = out_dims->rev_shape[1]; g.out_w = out_dims->rev_shape[0];
+  g.kh = desc->kernel_height; g.kw = desc->kernel_width;
+  g.pad_x = desc->pad_x; g.pad_y = desc->pad_y; g.stride_x = desc->stride_x; g.stride_y = desc->stride_y;
+  const int cout = out_dims->rev_shape[2];
+  CB_REQUIRE(in_dims->rev_shape[4] == 1 && out_dims->rev_shape[4] == 1, "convolution_forward_static: tensors must be 4-d");
+  CB_REQUIRE(g.cin == desc->in_channels && cout == desc->out_channels && out_dims->rev_shape[3] == g.batch,
+             "convolution_forward_static: tensor shapes do not match the descriptor");
+  CB_REQUIRE(g.kh >= 1 && g.kw >= 1 && g.stride_x >= 1 && g.stride_y >= 1 && g.pad_x >= 0 && g.pad_y >= 0,
+             "convolution_forward_static: bad descriptor");
+  CB_REQUIRE(g.out_w == (g.in_w + 2 * g.pad_x - g.kw) / g.stride_x + 1 &&
+             g.out_h == (g.in_h + 2 * g.pad_y - g.kh) / g.stride_y + 1,
+             "convolution_forward_static: output extent does not match floor((in + 2*pad - k)/stride) + 1");
+  for (int i = 0; i < 4; ++i)
+    CB_REQUIRE(!in_dims->index[i] && !out_dims->index[i], "Convolution arguments must be dense tensors");
+  long long e_in = 1, e_out = 1;
+  for (int i = 0; i < 4; ++i) {
+    CB_REQUIRE(in_dims->rev_shape[i] == 1 || in_dims->rev_strides[i] == e_in, "Convolution arguments must be dense tensors");
+    CB_REQUIRE(out_dims->rev_shape[i] == 1 || out_dims->rev_strides[i] == e_out, "Convolution arguments must be dense tensors");
+    e_in *= in_dims->rev_shape[i];
+    e_out *= out_dims->rev_shape[i];
+  }
+  g.kcols = g.cin * g.kh * g.kw;
+  g.ld = (g.kcols + 3) & ~3;
+  long long wec = 1;
+  for (int i = 0; i < 5; ++i) wec *= w_dims->rev_shape[i];
+  CB_REQUIRE(wec == (long long)cout * g.kcols, "Weight element count does not equal out-channels * kernel * in-channels");
+  const int hw = g.out_h * g.out_w;
+  const long long rows = (long long)g.batch * hw;
+  CB_REQUIRE(rows <= 2147483647LL, "convolution_forward_static: more than 2^31-1 output pixels");
+  if (rows == 0 || cout == 0) return CB200_OK;
+  const size_t es = dtype == CB200_FLOAT ? 4 : 8;
+  const long long total = rows * g.ld;
+  CB_REQUIRE((unsigned long long)total * es <= CB200_STATIC_CONV_SCRATCH_BYTES,
+             "convolution_forward_static: the unrolled input needs %lld bytes but the static scratch array holds %llu; "
+             "use cb200_convolution_forward (which allocates) for this size",
+             (long long)(total * (long long)es), (unsigned long long)CB200_STATIC_CONV_SCRATCH_BYTES);
+  DeviceGuard guard(s->device);
+  CB_REQUIRE(guard.ok, "convolution_forward_static: cannot select device %d", s->device);
+  void* cols = nullptr;
+  int rc = static_scratch_address(s->device, &cols);
+  if (rc) return rc;
+  long long blocks = (total + 255) / 256, cap = (long long)s->sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  if (dtype == CB200_FLOAT) {
+    im2col_kernel<float><<<(unsigned)blocks, 256, 0, s->stream>>>((float*)cols, (const float*)in, g, total);
+    CB_LAUNCH_CHECK(s);
+    if ((((uintptr_t)w) & 15) == 0 && (g.kcols % 4) == 0)
+      return cb200_gemm_tf32x3_launch(s, (float*)out, hw, 0, 1, 1.0f, (const float*)cols, (int)rows, g.kcols, g.ld,
+                                      (const float*)w, cout, g.kcols, (float)out_alpha, nullptr, 0, 1, hw, 0);
+    for (int n = 0; n < g.batch; ++n) {
+      rc = cb200_gemm_simt_f32_launch(s, (float*)out + (long long)n * cout * hw, hw, 0, 1, 1.0f, (const float*)w, cout,
+                                      g.kcols, g.kcols, (const float*)cols + (long long)n * hw * g.ld, hw, g.ld,
+                                      (float)out_alpha);
+      if (rc) return rc;
+    }
+    return CB200_OK;
+  }
+  im2col_kernel<double><<<(unsigned)blocks, 256, 0, s->stream>>>((double*)cols, (const double*)in, g, total);
+  CB_LAUNCH_CHECK(s);
+  for (int n = 0; n < g.batch; ++n) {
     rc = cb200_gemm_f64_launch(s, (double*)out + (long long)n * cout * hw, hw, 0, 1, 1.0, (const double*)w, cout,
                                g.kcols, g.kcols, (const double*)cols + (long long)n * hw * g.ld, hw, g.ld, out_alpha,
                                nullptr, 0);

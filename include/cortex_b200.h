@@ -196,6 +196,18 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
                               void* workspace, int64_t workspace_ecount,
                               const cb200_conv_desc* desc);
 
+/* convolution-forward! without any allocation.  No counterpart in the reference: cortex's backends
+ * take a caller-provided workspace tensor instead.  For hosts that cannot call cudaMalloc on this
+ * path (all device memory owned by their own pool, or no tolerance for the device-wide
+ * synchronisation an allocation implies): the unrolled input lives in a fixed 64 MiB device array
+ * that is part of the library image (one per GPU that loads the library, held until exit).
+ * Problems whose unrolled matrix batch*outH*outW x roundup4(C_in*kH*kW) elements exceeds 64 MiB are
+ * rejected with CB200_ERR_INVALID.  The first call on a device resolves the array's address - make
+ * it before any stream capture.  All calls share the array: calls that overlap on the GPU race. */
+int cb200_convolution_forward_static(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims,
+                                     double out_alpha, const void* in, const cb200_dims* in_dims,
+                                     const void* w, const cb200_dims* w_dims, const cb200_conv_desc* desc);
+
 /* Protocol methods outside the dense-inference path return CB200_ERR_UNSUPPORTED:
  * ternary-op*, gemv!, batch-normalize-*, activation-gradient!, convolution-backward-*,
  * pooling-*, rand!, lrn-* (src/cortex/tensor/math.clj:71-98, 116-175, 205-250). */
