@@ -65,7 +65,7 @@ def make_input(lo, hi):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while a timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms while a timed region runs."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -76,7 +76,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -172,7 +172,12 @@ def run_reference(args, rank, world):
 # B200 arm
 # --------------------------------------------------------------------------------------
 
-def time_region(stream, fn, iters):
+def time_region(stream, fn, iters, prime=None):
+    """Mean device time of `fn` over `iters` back-to-back calls, CUDA events on the launching stream.
+    `prime` enqueues a few milliseconds of unrelated work first, so that the host runs ahead of the
+    device and the timed launches are not spaced by host-side call overhead (short kernels only)."""
+    if prime is not None:
+        prime()
     e0 = stream.create_event(timing=True)
     for _ in range(iters):
         fn()
@@ -217,6 +222,15 @@ def bench_eltwise(drv, dev, peaks):
         bias = ct.to_tensor((rng.standard_normal((1, cols)) * 0.1).astype(np.float32))
         stat = [ct.new_tensor([rows, 1]) for _ in range(sets)]
         idx = ct.to_tensor(rng.integers(0, rows, size=rows, dtype=np.int32), datatype="int")
+        gathered = [ct.select(x, idx, ALL) for x in xs]      # descriptor views, built once
+        ga = ct.to_tensor(rng.standard_normal((4096, 4096), dtype=np.float32))
+        gb = ct.to_tensor(rng.standard_normal((4096, 4096), dtype=np.float32))
+        gc = ct.new_tensor([4096, 4096])
+
+        def prime():
+            for _ in range(4):
+                ct.gemm(gc, False, True, 1.0, ga, gb, 0.0)
+
         state = {"i": 0}
 
         def rot():
@@ -229,7 +243,7 @@ def bench_eltwise(drv, dev, peaks):
             "reduce_max": (lambda i: ct.unary_reduce(stat[i], 1.0, xs[i], "max"), rows * cols * 4 + rows * 4),
             "reduce_sum": (lambda i: ct.unary_reduce(stat[i], 1.0, xs[i], "sum"), rows * cols * 4 + rows * 4),
             "softmax": (lambda i: ct.softmax(ys[i], xs[i]), 2 * rows * cols * 4),
-            "gather_rows": (lambda i: ct.assign(ys[i], ct.select(xs[i], idx, ALL)), 2 * rows * cols * 4 + rows * 4),
+            "gather_rows": (lambda i: ct.assign(ys[i], gathered[i]), 2 * rows * cols * 4 + rows * 4),
             "fused_bias_relu_rowstats": (lambda i: stream.bias_relu_rowstats(ys[i].buffer, cols, xs[i].buffer, cols,
                                                                             bias.buffer, rows, cols, stat[i].buffer,
                                                                             stat[(i + 1) % sets].buffer),
@@ -238,9 +252,74 @@ def bench_eltwise(drv, dev, peaks):
         for name, (fn, nbytes) in cases.items():
             for _ in range(3):
                 fn(rot())
-            ms = time_region(stream, lambda: fn(rot()), 20)
+            ms = time_region(stream, lambda: fn(rot()), 20, prime)
             gbs = nbytes / ms / 1e6
             res[name] = {"gbs": round(gbs, 0), "frac_of_%s_hbm" % peaks["source"]: round(gbs / peaks["hbm_gbs"], 3)}
+    return res
+
+
+def bench_conv(drv, dev, peaks):
+    """Config 4 in brief: NCHW conv 64x64x56x56, 3x3 s1 p1, 64 output channels, + bias + ReLU, fp32."""
+    from cortex_b200 import nn
+    from cortex_b200 import tensor as ct
+    stream = dev.create_stream()
+    rng = np.random.default_rng(401)
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        x = ct.to_tensor(rng.standard_normal((64, 64, 56, 56), dtype=np.float32))
+        w = ct.to_tensor((rng.standard_normal((64, 576), dtype=np.float32) * np.float32(np.sqrt(2.0 / 576))))
+        b = ct.new_tensor([64])
+        out = ct.new_tensor([64, 64, 56, 56])
+        layer = nn.Convolution(w, b, (3, 3), (1, 1), (1, 1), 64, 64, "float")
+
+        def fwd():
+            layer.forward(x, out)
+            nn.relu(out, out)
+
+        for _ in range(3):
+            fwd()
+        ms = time_region(stream, fwd, 10)
+        conv_only = lambda: ct.convolution_forward(out, 0.0, x, w, layer.workspace, layer.desc, layer.algorithms)
+        ms_conv = time_region(stream, conv_only, 10)
+    flops = 2.0 * 64 * 64 * 3136 * 576
+    return {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "images_per_s": round(64 / ms * 1000.0, 0),
+            "conv_kernel_ms": round(ms_conv, 4), "conv_kernel_tflops": round(flops / ms_conv / 1e9, 1),
+            "note": "ms = conv + bias + ReLU (3 protocol calls); work = 2*64*64*3136*576"}
+
+
+def bench_gemm_f64(drv, dev):
+    """Config 2, fp64: 4096^3 DMMA gemm!, alpha 1.5 beta 0.5."""
+    from cortex_b200 import tensor as ct
+    stream = dev.create_stream()
+    rng = np.random.default_rng(201)
+    out = {}
+    with ct.with_stream(stream), ct.with_datatype("double"):
+        A = ct.to_tensor(rng.standard_normal((4096, 4096)))
+        B = ct.to_tensor(rng.standard_normal((4096, 4096)))
+        Cm = ct.to_tensor(rng.standard_normal((4096, 4096)))
+        for name, ta, tb in (("NT", False, True), ("NN", False, False)):
+            ct.gemm(Cm, ta, tb, 1.5, A, B, 0.5)
+            ms = time_region(stream, lambda: ct.gemm(Cm, ta, tb, 1.5, A, B, 0.5), 3)
+            out[name] = round(2.0 * 4096 ** 3 / ms / 1e9, 2)
+    return {"tflops": out}
+
+
+def bench_mlp_128(drv, dev):
+    """Config 1: MNIST-shaped MLP, batch 128 (launch-latency-bound; roofline fractions are not meaningful here)."""
+    from cortex_b200 import nn
+    from cortex_b200 import tensor as ct
+    stream = dev.create_stream()
+    res = {}
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        x = ct.to_tensor(np.random.default_rng(101).random((128, 784), dtype=np.float32))
+        w1 = ct.to_tensor((np.random.default_rng(102).standard_normal((500, 784)) * np.sqrt(2.0 / 784)).astype(np.float32))
+        w2 = ct.to_tensor((np.random.default_rng(103).standard_normal((10, 500)) * np.sqrt(2.0 / 500)).astype(np.float32))
+        b1, b2 = ct.new_tensor([500]), ct.new_tensor([10])
+        for label, fused in (("reference_call_sequence", False), ("fused", True)):
+            net = nn.MLP([(w1, b1, "relu"), (w2, b2, "softmax")], fused=fused)
+            for _ in range(5):
+                net.infer(x)
+            ms = time_region(stream, lambda: net.infer(x), 200)
+            res[label] = {"us_per_forward": round(ms * 1000.0, 1), "samples_per_s": round(128 / ms * 1000.0, 0)}
     return res
 
 
@@ -385,7 +464,10 @@ def run_b200(args, rank, world, local_rank):
                                 "sample": "2048 rows of the batch, one forward (%.1f s): oracle C/OpenMP elementwise + "
                                           "OpenBLAS sgemm" % secs}
         line["gemm_4096"] = bench_gemm_4096(drv, dev, peaks)
+        line["gemm_4096_f64"] = bench_gemm_f64(drv, dev)
         line["eltwise"] = bench_eltwise(drv, dev, peaks)
+        line["conv_64x64x56x56"] = bench_conv(drv, dev, peaks)
+        line["mlp_128x784_500_10"] = bench_mlp_128(drv, dev)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -397,15 +479,18 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise"],
+    ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128"],
                     help="mlp = the benchmark; gemm4096 / eltwise = the small single-purpose runs used for ncu captures")
     args = ap.parse_args()
     if args.case != "mlp":
         from cortex_b200.driver import driver
         drv = driver()
         dev = drv.default_device()
-        fn = bench_gemm_4096 if args.case == "gemm4096" else bench_eltwise
-        print(json.dumps({args.case: fn(drv, dev, measured_peaks())}), flush=True)
+        peaks = measured_peaks()
+        fns = {"gemm4096": lambda: bench_gemm_4096(drv, dev, peaks), "eltwise": lambda: bench_eltwise(drv, dev, peaks),
+               "conv": lambda: bench_conv(drv, dev, peaks), "gemm4096f64": lambda: bench_gemm_f64(drv, dev),
+               "mlp128": lambda: bench_mlp_128(drv, dev)}
+        print(json.dumps({args.case: fns[args.case]()}), flush=True)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

@@ -3,14 +3,18 @@
 //
 // Same decomposition as the reference CPU backend
 // (src/cortex/compute/cpu/tensor_math.clj:1118-1131, 1682-1714,
-//  src/cortex/nn/impl.clj:8-90): unroll the input into a
+//  src/cortex/nn/impl.clj:8-90): the input unrolled into a
 // [batch*outH*outW, C_in*kH*kW] matrix (column = c*kH*kW + ky*kW + kx, zeros in
-// the padding), then multiply by W[C_out, C_in*kH*kW] transposed.  Unlike the
-// reference, the whole batch is ONE GEMM with the output pixels as the M
-// dimension; the tensor-core epilogue scatters its [pixel, channel] tile
-// straight into NCHW (adjacent lanes = adjacent pixels, so stores coalesce).
-// The unrolled matrix lives in the stream's scratch buffer, not in the caller's
-// workspace.
+// the padding) times W[C_out, C_in*kH*kW] transposed.  Unlike the reference, the
+// whole batch is ONE GEMM with the output pixels as the M dimension and an
+// epilogue that scatters [pixel, channel] tiles straight into NCHW.
+//   fp32: conv_igemm.cu gathers the unrolled rows directly into the tensor-core
+//         operand tiles; nothing is materialised and no scratch memory is used.
+//         (Weights whose row length is not a multiple of 4, or an unaligned
+//         weight pointer, take the explicit path below with the SIMT GEMM.)
+//   fp64: explicit im2col into the stream's scratch buffer, then one DMMA GEMM
+//         per image as the reference does.
+// The caller's workspace tensor is not used by either.
 #include "common.cuh"
 #include <mutex>
 
@@ -23,6 +27,9 @@ int cb200_gemm_f64_launch(cb200_stream* s, double* C, long long ldc, int trans_a
 int cb200_gemm_simt_f32_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
                                const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
                                float beta);
+int cb200_conv_igemm_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
+                            int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
+                            int stride_x, int stride_y, float out_alpha);
 
 namespace {
 
@@ -37,12 +44,13 @@ __global__ void __launch_bounds__(256)
 im2col_kernel(T* cols, const T* in, ConvGeom g, long long total) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    int col = (int)(i % g.ld);
-    long long row = i / g.ld;
+    // rows < 2^31 and ld < 2^31 (checked by the caller): one 64-bit division, the rest 32-bit
+    const unsigned row = (unsigned)(i / (unsigned)g.ld);
+    const int col = (int)(i - (long long)row * g.ld);
     T v = (T)0;
     if (col < g.kcols) {
       int kx = col % g.kw, ky = (col / g.kw) % g.kh, c = col / (g.kw * g.kh);
-      int hw = g.out_h * g.out_w;
+      const unsigned hw = (unsigned)(g.out_h * g.out_w);
       int n = (int)(row / hw), p = (int)(row % hw);
       int oy = p / g.out_w, ox = p % g.out_w;
       int iy = oy * g.stride_y - g.pad_y + ky, ix = ox * g.stride_x - g.pad_x + kx;
@@ -102,6 +110,10 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
   const long long rows = (long long)g.batch * hw;
   CB_REQUIRE(rows <= 2147483647LL, "convolution_forward: more than 2^31-1 output pixels");
   if (rows == 0 || cout == 0) return CB200_OK;
+  if (dtype == CB200_FLOAT && (((uintptr_t)w) & 15) == 0 && (g.kcols % 4) == 0)
+    return cb200_conv_igemm_launch(s, (float*)out, (const float*)in, (const float*)w, g.batch, g.cin, g.in_h, g.in_w,
+                                   cout, g.out_h, g.out_w, g.kh, g.kw, g.pad_x, g.pad_y, g.stride_x, g.stride_y,
+                                   (float)out_alpha);
   const size_t es = dtype == CB200_FLOAT ? 4 : 8;
   const long long total = rows * g.ld;
   void* cols = nullptr;
@@ -113,11 +125,6 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
   if (dtype == CB200_FLOAT) {
     im2col_kernel<float><<<(unsigned)blocks, 256, 0, s->stream>>>((float*)cols, (const float*)in, g, total);
     CB_LAUNCH_CHECK(s);
-    if ((((uintptr_t)w) & 15) == 0 && (g.kcols % 4) == 0) {
-      // out[pixel, co] = cols[pixel, :] . W[co, :]   stored as NCHW
-      return cb200_gemm_tf32x3_launch(s, (float*)out, hw, 0, 1, 1.0f, (const float*)cols, (int)rows, g.kcols, g.ld,
-                                      (const float*)w, cout, g.kcols, (float)out_alpha, nullptr, 0, 1, hw, 0);
-    }
     for (int n = 0; n < g.batch; ++n) {
       rc = cb200_gemm_simt_f32_launch(s, (float*)out + (long long)n * cout * hw, hw, 0, 1, 1.0f, (const float*)w, cout,
                                       g.kcols, g.kcols, (const float*)cols + (long long)n * hw * g.ld, hw, g.ld,

@@ -1,0 +1,323 @@
+// fp32 convolution-forward! as an implicit GEMM on the tensor cores: the im2col
+// matrix of the reference CPU backend (src/cortex/compute/cpu/tensor_math.clj:1118-1131,
+// loop nest of src/cortex/nn/impl.clj:8-90; column k = c*kH*kW + ky*kW + kx, zeros in
+// the padding) is never materialised.  GEMM view:
+//   M = batch*outH*outW output pixels, N = C_out, K = C_in*kH*kW
+//   out[pixel, co] = sum_k im2col[pixel, k] * W[co, k]   (+ out_alpha * out)
+// The A operand (im2col rows) is gathered from the NCHW input straight into the
+// shared-memory tile the tensor core reads: for a fixed k, 32 consecutive pixels are
+// (mostly) consecutive floats in global memory, so A is staged MN-major (128-byte rows
+// of 32 pixels, 128-byte swizzle with 32-byte atoms) by 8 gather warps, one pixel per
+// lane: coalesced global loads, conflict-free shared stores.  The same warps write the
+// hi operand (the raw value) and the lo operand (x - trunc_tf32(x)) of the 3xTF32
+// split, and run the lo pass over the W tile that TMA delivers (K-major, 64-byte
+// swizzle).  MMA issue, TMEM accumulators (main + cross terms), bounded waits and the
+// NCHW-scatter epilogue are as in gemm_tf32x3.cu.
+#include "common.cuh"
+#include "sm100.cuh"
+#include <mutex>
+
+using namespace sm100;
+
+namespace {
+
+constexpr int CBM = 128;            // pixels per CTA tile
+constexpr int CBK = 16;             // k values per stage
+constexpr int GATHER_WARPS = 8;
+constexpr int CONV_THREADS = (GATHER_WARPS + 2) * 32;
+
+struct ConvParams {
+  const float* in;
+  float* out;
+  int batch, cin, in_h, in_w, out_h, out_w, kh, kw, pad_x, pad_y, stride_x, stride_y;
+  int cout, K, M;      // K = cin*kh*kw, M = batch*out_h*out_w
+  float out_alpha;
+  int* status;
+};
+
+template <int BN> struct ConvCfg {
+  static constexpr int A_TILE = CBM * CBK * 4;          // 8 KiB: 4 boxes of [16 k-rows][32 pixels]
+  static constexpr int B_TILE = BN * CBK * 4;
+  static constexpr int STAGE = 2 * (A_TILE + B_TILE);   // A_hi | B_hi | A_lo | B_lo
+  // BN = 64: 4 stages (~97 KB) so that two CTAs share an SM and one CTA's gather latency hides
+  // behind the other's; wider tiles take the whole SM.
+  static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
+  static constexpr int BUDGET = 196608 / CTAS_PER_SM;
+  static constexpr int STAGES = (BUDGET / STAGE) > 8 ? 8 : (BUDGET / STAGE);
+  // BN = 64: two (main, cross) accumulator pairs, one per k-step of a k-block, so that back-to-back
+  // MMAs do not form one dependency chain on a single accumulator; the epilogue adds them.
+  static constexpr int ACC_SETS = BN <= 64 ? 2 : 1;
+  static constexpr int TMEM_COLS = 2 * BN * ACC_SETS;
+  static constexpr int SMEM = STAGES * STAGE + 1024 + 256;
+};
+
+__device__ __forceinline__ float conv_lo_part(float x) {
+  const uint32_t xb = __float_as_uint(x);
+  const float lo = x - __uint_as_float(xb & 0xffffe000u);
+  return ((xb & 0x7f800000u) == 0x7f800000u) ? 0.f : lo;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(CONV_THREADS, ConvCfg<BN>::CTAS_PER_SM)
+conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
+  typedef ConvCfg<BN> Cfg;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int A_TILE = Cfg::A_TILE, B_TILE = Cfg::B_TILE, RAW = A_TILE + B_TILE;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::STAGE);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 3 * STAGES + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (p.cout + BN - 1) / BN;
+  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
+  const int m0 = tile_m * CBM, n0 = tile_n * BN;
+  const int nkb = (p.K + CBK - 1) / CBK;
+  const int hw = p.out_h * p.out_w;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_full = smem_u32(bars), bar_conv = smem_u32(bars + STAGES), bar_empty = smem_u32(bars + 2 * STAGES),
+                 bar_acc = smem_u32(bars + 3 * STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_conv + 8 * s, GATHER_WARPS);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == GATHER_WARPS + 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == GATHER_WARPS && lane == 0) tma_prefetch_desc(&tmW);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == GATHER_WARPS) {
+    // ---------------------------- TMA producer: W tiles ----------------------------
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES, ph = (i / STAGES) & 1;
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) break;
+        const uint32_t full = bar_full + 8 * s;
+        mbar_arrive_expect_tx(full, B_TILE);
+        tma_load_2d(smem_base + s * Cfg::STAGE + A_TILE, &tmW, i * CBK, n0, full);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+          for (int it = 0; it < (1 << 16); ++it)
+            if (mbar_try_wait(bar_full + 8 * (i % STAGES), (i / STAGES) & 1)) break;
+      }
+    }
+  } else if (warp == GATHER_WARPS + 1) {
+    // ---------------------------- MMA issuer ---------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_tf32(CBM, BN, 1 /*A: pixels contiguous*/, 0 /*W: K contiguous*/);
+      uint32_t accumulate[2] = {0, 0};
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES, ph = (i / STAGES) & 1;
+        if (!mbar_wait(bar_conv + 8 * s, ph, abort_flag, p.status, 600 + s)) break;
+        tc_fence_after();
+        const uint32_t a_hi = smem_base + s * Cfg::STAGE, b_hi = a_hi + A_TILE;
+        const uint32_t a_lo = a_hi + RAW, b_lo = b_hi + RAW;
+#pragma unroll
+        for (int kk = 0; kk < CBK / 8; ++kk) {
+          // A: 32-pixel boxes 2048 B apart, 4-k-row atoms 512 B apart, 1024 B per k-step
+          const uint64_t dah = make_smem_desc(a_hi + kk * 1024, 2048, 512, SWZ_128B_BASE32B);
+          const uint64_t dal = make_smem_desc(a_lo + kk * 1024, 2048, 512, SWZ_128B_BASE32B);
+          // W: 64-byte rows, 8-row groups 512 B apart, 32 B per k-step
+          const uint64_t dbh = make_smem_desc(b_hi + kk * 32, 16, 512, SWZ_64B);
+          const uint64_t dbl = make_smem_desc(b_lo + kk * 32, 16, 512, SWZ_64B);
+          const int set = Cfg::ACC_SETS == 2 ? kk : 0;
+          const uint32_t tmem_main = tmem_base + set * 2 * BN, tmem_cross = tmem_main + BN;
+          mma_tf32_ss(tmem_cross, dal, dbh, idesc, accumulate[set]);
+          mma_tf32_ss(tmem_main, dah, dbh, idesc, accumulate[set]);
+          mma_tf32_ss(tmem_cross, dah, dbl, idesc, 1);
+          accumulate[set] = 1;
+        }
+        mma_commit(bar_empty + 8 * s);
+      }
+      mma_commit(bar_acc);
+      if (*abort_flag) {
+        for (int it = 0; it < (1 << 16); ++it)
+          if (mbar_try_wait(bar_acc, 0)) break;
+      }
+    }
+  } else {
+    // -------------- im2col gather (hi + lo) and W lo pass, then epilogue (warps 0-7) --------------
+    const int tid = threadIdx.x;
+    const int pb = warp & 3, khalf = warp >> 2;      // 32-pixel block, which 8 of the 16 k-rows
+    const int m = m0 + pb * 32 + lane;
+    const bool m_ok = m < p.M;
+    const int img = m_ok ? m / hw : 0, pix = m_ok ? m % hw : 0;
+    const int oy = pix / p.out_w, ox = pix % p.out_w;
+    const int iy0 = oy * p.stride_y - p.pad_y, ix0 = ox * p.stride_x - p.pad_x;
+    const float* img_base = p.in + (long long)img * p.cin * p.in_h * p.in_w;
+    const int khkw = p.kh * p.kw;
+    // byte offset of this lane's element inside a k-row of its box, before the per-row swizzle
+    const uint32_t box_off = pb * 2048 + (lane & 7) * 4;
+    const uint32_t chunk = lane >> 3;
+    // im2col rows of k-block i for this lane's pixel, fetched one k-block ahead so that the
+    // global-load latency overlaps the shared-memory work of the current k-block
+    auto fetch = [&](int i, float (&v)[8]) {
+      const int k0 = i * CBK + khalf * 8;
+      int c = k0 / khkw, t = k0 - c * khkw;
+      int ky = t / p.kw, kx = t - ky * p.kw;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int iy = iy0 + ky, ix = ix0 + kx;
+        const bool valid = m_ok && (k0 + j) < p.K && iy >= 0 && iy < p.in_h && ix >= 0 && ix < p.in_w;
+        v[j] = valid ? __ldg(img_base + ((long long)c * p.in_h + iy) * p.in_w + ix) : 0.f;
+        if (++kx == p.kw) { kx = 0; if (++ky == p.kh) { ky = 0; ++c; } }
+      }
+    };
+    bool ok = true;
+    float vn[8];
+    if (nkb > 0) fetch(0, vn);
+    for (int i = 0; i < nkb; ++i) {
+      const int s = i % STAGES, ph = (i / STAGES) & 1;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = vn[j];
+      if (i + 1 < nkb) fetch(i + 1, vn);
+      // the stage is free once the MMAs that read it have retired
+      if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 700 + s)) { ok = false; break; }
+      uint8_t* a_hi = smem + s * Cfg::STAGE;
+      uint8_t* a_lo = a_hi + RAW;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t row = khalf * 8 + j;
+        const uint32_t off = box_off + row * 128 + ((chunk ^ (row & 3)) << 5);
+        *reinterpret_cast<float*>(a_hi + off) = v[j];
+        *reinterpret_cast<float*>(a_lo + off) = conv_lo_part(v[j]);
+      }
+      // W tile: lo pass once TMA has landed it
+      if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 800 + s)) { ok = false; break; }
+      uint8_t* b_hi = a_hi + A_TILE;
+      uint8_t* b_lo = b_hi + RAW;
+      for (int cidx = tid; cidx < B_TILE / 16; cidx += GATHER_WARPS * 32) {
+        const float4 w4 = *reinterpret_cast<const float4*>(b_hi + cidx * 16);
+        float4 l;
+        l.x = conv_lo_part(w4.x); l.y = conv_lo_part(w4.y); l.z = conv_lo_part(w4.z); l.w = conv_lo_part(w4.w);
+        *reinterpret_cast<float4*>(b_lo + cidx * 16) = l;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_conv + 8 * s);
+    }
+    if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 900);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    if (ok) {
+      const int q = warp & 3, half = warp >> 2;
+      const int em = m0 + q * 32 + lane;
+      constexpr int COLS_PER_HALF = BN / 2;
+      const long long eimg = em / hw, epix = em % hw;
+      float* obase = p.out + eimg * (long long)p.cout * hw + epix;
+#pragma unroll 1
+      for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
+        const int col0 = half * COLS_PER_HALF + cc * 32;
+        // sum of the (main, cross) accumulators of every set, one 32-column slab at a time
+        uint32_t r[32], t[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
+        tmem_ld_wait();
+#pragma unroll 1
+        for (int a = 1; a < 2 * Cfg::ACC_SETS; ++a) {
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + col0), t);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(t[j]));
+        }
+        const int nb = n0 + col0;
+        if (em < p.M) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (nb + j < p.cout) {
+              float* cp = obase + (long long)(nb + j) * hw;   // adjacent lanes = adjacent pixels: coalesced
+              float o = __uint_as_float(r[j]);
+              if (p.out_alpha != 0.f) o += p.out_alpha * (*cp);
+              *cp = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == GATHER_WARPS + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn conv_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)f;
+  });
+  return fn;
+}
+
+template <int BN>
+int launch_conv(cb200_stream* s, const CUtensorMap& tmW, const ConvParams& p) {
+  typedef ConvCfg<BN> Cfg;
+  static std::once_flag once[64];
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[s->device & 63], [&] {
+    attr_err = cudaFuncSetAttribute(conv_igemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  });
+  if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
+  long long tiles = (long long)((p.M + CBM - 1) / CBM) * ((p.cout + BN - 1) / BN);
+  conv_igemm_kernel<BN><<<(unsigned)tiles, CONV_THREADS, Cfg::SMEM, s->stream>>>(tmW, p);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+}  // namespace
+
+// Dense NCHW fp32 input/output, weights [cout][cin*kh*kw] with a 16-byte aligned base and
+// cin*kh*kw a multiple of 4 (checked by the caller).
+int cb200_conv_igemm_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
+                            int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
+                            int stride_x, int stride_y, float out_alpha) {
+  DeviceGuard guard(s->device);
+  ConvParams p;
+  p.in = in; p.out = out; p.batch = batch; p.cin = cin; p.in_h = in_h; p.in_w = in_w; p.out_h = out_h; p.out_w = out_w;
+  p.kh = kh; p.kw = kw; p.pad_x = pad_x; p.pad_y = pad_y; p.stride_x = stride_x; p.stride_y = stride_y;
+  p.cout = cout; p.K = cin * kh * kw; p.M = batch * out_h * out_w; p.out_alpha = out_alpha; p.status = s->status_dev;
+  const int BN = cout > 128 ? 256 : (cout > 64 ? 128 : 64);
+  EncodeTiledFn fn = conv_encode_fn();
+  if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
+  CUtensorMap tmW;
+  cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)cout};
+  cuuint64_t gstride[1] = {(cuuint64_t)p.K * 4};
+  cuuint32_t box[2] = {(cuuint32_t)CBK, (cuuint32_t)BN};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)w, gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { cb200_set_error("cuTensorMapEncodeTiled failed with %d for the weights", (int)r); return CB200_ERR_CUDA; }
+  if (BN == 256) return launch_conv<256>(s, tmW, p);
+  if (BN == 128) return launch_conv<128>(s, tmW, p);
+  return launch_conv<64>(s, tmW, p);
+}

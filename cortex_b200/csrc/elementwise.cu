@@ -254,11 +254,11 @@ template <> __device__ __forceinline__ float f32_op<CB200_DIV>(float a, float b)
 template <> __device__ __forceinline__ float f32_op<CB200_MAX>(float a, float b) { return a > b ? a : b; }
 template <> __device__ __forceinline__ float f32_op<CB200_MIN>(float a, float b) { return a > b ? b : a; }
 
-template <int OP, int REV>
+template <int OP>
 struct FastBinaryF {
   static const int NIN = 2;
   typedef float TX;
-  __device__ __forceinline__ float operator()(float x, float y) const { return REV ? f32_op<OP>(y, x) : f32_op<OP>(x, y); }
+  __device__ __forceinline__ float operator()(float x, float y) const { return f32_op<OP>(x, y); }
 };
 template <int OP, int REV>
 struct FastBinaryConstF {
@@ -413,6 +413,50 @@ ew_rowvec(TD* dest, const typename F::TX* x, const typename F::TX* y,
   }
 }
 
+// Same contract as ew_rowvec for long rows (>= 32 chunks): one warp per row.  The outer
+// addressing (index-array lookups included) is resolved once per row instead of once per
+// chunk, and each lane keeps 8 independent 16-byte loads in flight.
+template <typename TD, typename F, int VEC>
+__global__ void __launch_bounds__(256)
+ew_rowwarp(TD* dest, const typename F::TX* x, const typename F::TX* y,
+           Operand od, Operand ox, Operand oy, Geometry g, int x_row, int y_row, unsigned n_rows, F f) {
+  typedef typename F::TX TX;
+  constexpr int U = 8;
+  const unsigned lane = threadIdx.x & 31;
+  const unsigned chunks = (unsigned)g.max_shape[0] / VEC;
+  const unsigned warps = gridDim.x * (blockDim.x >> 5);
+  for (unsigned row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < n_rows; row += warps) {
+    const unsigned i = row * (unsigned)g.max_shape[0];
+    Vec<TD, VEC>* d = reinterpret_cast<Vec<TD, VEC>*>(dest + operand_offset(od, g, i));
+    const TX* xp = F::NIN >= 1 ? x + operand_offset(ox, g, i) : nullptr;
+    const TX* yp = F::NIN >= 2 ? y + operand_offset(oy, g, i) : nullptr;
+    const TX xb = (F::NIN >= 1 && !x_row) ? *xp : TX();
+    const TX yb = (F::NIN >= 2 && !y_row) ? *yp : TX();
+    for (unsigned c0 = lane; c0 < chunks; c0 += 32 * U) {
+      Vec<TX, VEC> xv[U], yv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned c = c0 + 32 * u;
+        if (c < chunks) {
+          if (F::NIN >= 1 && x_row) xv[u] = reinterpret_cast<const Vec<TX, VEC>*>(xp)[c];
+          if (F::NIN >= 2 && y_row) yv[u] = reinterpret_cast<const Vec<TX, VEC>*>(yp)[c];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const unsigned c = c0 + 32 * u;
+        if (c < chunks) {
+          Vec<TD, VEC> o;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k)
+            o.v[k] = f(F::NIN >= 1 ? (x_row ? xv[u].v[k] : xb) : TX(), F::NIN >= 2 ? (y_row ? yv[u].v[k] : yb) : TX());
+          d[c] = o;
+        }
+      }
+    }
+  }
+}
+
 template <typename TD, typename F>
 __global__ void __launch_bounds__(256)
 ew_generic(TD* dest, const typename F::TX* x, const typename F::TX* y,
@@ -533,9 +577,13 @@ int grid_for(cb200_stream* s, long long work_items, int per_block) {
 }
 
 template <int A, int B> struct max_of { static const int value = A > B ? A : B; };
+template <typename A, typename B> struct acc_same { static const bool value = false; };
+template <typename A> struct acc_same<A, A> { static const bool value = true; };
 
 // Launch one elementwise map.  x / y may be null when F::NIN says so.
-template <typename TD, typename F>
+// PATHS: 0 = general index-system kernel only (dtype-marshalling copies), 1 = + flat and
+// row-vector kernels, 2 = + warp-per-row kernel (what the dense layers and gathers hit).
+template <typename TD, typename F, int PATHS = 1>
 int launch_map(cb200_stream* s, TD* dest, const cb200_dims* dd, const typename F::TX* x, const cb200_dims* xd,
                const typename F::TX* y, const cb200_dims* yd, long long n, const F& f) {
   typedef typename F::TX TX;
@@ -551,45 +599,60 @@ int launch_map(cb200_stream* s, TD* dest, const cb200_dims* dd, const typename F
   make_geometry(g, ops, n_ops);
   DeviceGuard guard(s->device);
 
-  constexpr int ES = max_of<sizeof(TD), sizeof(TX)>::value;
-  constexpr int VEC = 16 / ES;
-  constexpr int UNROLL = 4;
+  if constexpr (PATHS >= 1) {
+    constexpr int ES = max_of<sizeof(TD), sizeof(TX)>::value;
+    constexpr int VEC = (16 / ES) > 4 ? 4 : (16 / ES);   // 16-byte accesses for 4- and 8-byte types
+    constexpr int UNROLL = 4;
 
-  FlatMode md, mx = {0, 1, 1, 1}, my = {0, 1, 1, 1};
-  bool flat = flat_mode(ops[0], g, md) && md.kind == 0 && aligned16(dest);
-  if (flat && F::NIN >= 1) flat = flat_mode(ops[1], g, mx);
-  if (flat && F::NIN >= 2) flat = flat_mode(ops[2], g, my);
-  if (flat) {
-    auto vec_ok = [&](const FlatMode& m, const void* p) -> int {
-      if (m.kind == 0) return ((uintptr_t)p % (sizeof(TX) * VEC)) == 0;
-      if (m.kind == 1) return (m.ec % VEC) == 0 && ((uintptr_t)p % (sizeof(TX) * VEC)) == 0;
-      return (m.amt % VEC) == 0;
-    };
-    int xv = F::NIN >= 1 ? vec_ok(mx, x) : 1, yv = F::NIN >= 2 ? vec_ok(my, y) : 1;
-    long long n_vec = n / VEC;
-    long long blocks = (n_vec + 256 * UNROLL - 1) / (256 * UNROLL);
-    long long full = (long long)s->sm_count * 8;    // 2048 threads per SM
-    if (blocks > full) blocks = full;
-    if (blocks < 1) blocks = 1;
-    ew_flat<TD, F, VEC, UNROLL><<<(unsigned)blocks, 256, 0, s->stream>>>(dest, x, y, mx, my, xv, yv, (unsigned)n, f);
-    CB_LAUNCH_CHECK(s);
-    return CB200_OK;
-  }
+    FlatMode md, mx = {0, 1, 1, 1}, my = {0, 1, 1, 1};
+    bool flat = flat_mode(ops[0], g, md) && md.kind == 0 && aligned16(dest);
+    if (flat && F::NIN >= 1) flat = flat_mode(ops[1], g, mx);
+    if (flat && F::NIN >= 2) flat = flat_mode(ops[2], g, my);
+    if (flat) {
+      auto vec_ok = [&](const FlatMode& m, const void* p) -> int {
+        if (m.kind == 0) return ((uintptr_t)p % (sizeof(TX) * VEC)) == 0;
+        if (m.kind == 1) return (m.ec % VEC) == 0 && ((uintptr_t)p % (sizeof(TX) * VEC)) == 0;
+        return (m.amt % VEC) == 0;
+      };
+      int xv = F::NIN >= 1 ? vec_ok(mx, x) : 1, yv = F::NIN >= 2 ? vec_ok(my, y) : 1;
+      long long n_vec = n / VEC;
+      long long blocks = (n_vec + 256 * UNROLL - 1) / (256 * UNROLL);
+      long long full = (long long)s->sm_count * 8;    // 2048 threads per SM
+      if (blocks > full) blocks = full;
+      if (blocks < 1) blocks = 1;
+      ew_flat<TD, F, VEC, UNROLL><<<(unsigned)blocks, 256, 0, s->stream>>>(dest, x, y, mx, my, xv, yv, (unsigned)n, f);
+      CB_LAUNCH_CHECK(s);
+      return CB200_OK;
+    }
 
-  int dr = 0, xr = 1, yr = 1;
-  bool rv = (g.max_shape[0] % VEC) == 0 && VEC > 1 && rowvec_ok(ops[0], g, dest, sizeof(TD), VEC, dr) && dr == 1;
-  if (rv && F::NIN >= 1) rv = rowvec_ok(ops[1], g, x, sizeof(TX), VEC, xr);
-  if (rv && F::NIN >= 2) rv = rowvec_ok(ops[2], g, y, sizeof(TX), VEC, yr);
-  long long total = 1;
-  for (int d = 0; d < 5; ++d) total *= g.max_shape[d];
-  if (rv && n == total) {
-    long long n_chunks = n / VEC;
-    long long rblocks = (n_chunks + 1023) / 1024, rfull = (long long)s->sm_count * 8;
-    if (rblocks > rfull) rblocks = rfull;
-    ew_rowvec<TD, F, VEC><<<(unsigned)rblocks, 256, 0, s->stream>>>(dest, x, y, ops[0], ops[1], ops[2], g, xr, yr,
-                                                                    (unsigned)n_chunks, f);
-    CB_LAUNCH_CHECK(s);
-    return CB200_OK;
+    if constexpr (VEC > 1) {
+      int dr = 0, xr = 1, yr = 1;
+      bool rv = (g.max_shape[0] % VEC) == 0 && rowvec_ok(ops[0], g, dest, sizeof(TD), VEC, dr) && dr == 1;
+      if (rv && F::NIN >= 1) rv = rowvec_ok(ops[1], g, x, sizeof(TX), VEC, xr);
+      if (rv && F::NIN >= 2) rv = rowvec_ok(ops[2], g, y, sizeof(TX), VEC, yr);
+      long long total = 1;
+      for (int d = 0; d < 5; ++d) total *= g.max_shape[d];
+      if (rv && n == total) {
+        const long long n_chunks = n / VEC;
+        const long long chunks_per_row = g.max_shape[0] / VEC, n_rows = n / g.max_shape[0];
+        if constexpr (PATHS >= 2) {
+          if (chunks_per_row >= 32 && n_rows >= (long long)s->sm_count * 8) {
+            long long wblocks = (n_rows + 7) / 8, wfull = (long long)s->sm_count * 8;
+            if (wblocks > wfull) wblocks = wfull;
+            ew_rowwarp<TD, F, VEC><<<(unsigned)wblocks, 256, 0, s->stream>>>(dest, x, y, ops[0], ops[1], ops[2], g, xr,
+                                                                           yr, (unsigned)n_rows, f);
+            CB_LAUNCH_CHECK(s);
+            return CB200_OK;
+          }
+        }
+        long long rblocks = (n_chunks + 1023) / 1024, rfull = (long long)s->sm_count * 8;
+        if (rblocks > rfull) rblocks = rfull;
+        ew_rowvec<TD, F, VEC><<<(unsigned)rblocks, 256, 0, s->stream>>>(dest, x, y, ops[0], ops[1], ops[2], g, xr, yr,
+                                                                        (unsigned)n_chunks, f);
+        CB_LAUNCH_CHECK(s);
+        return CB200_OK;
+      }
+    }
   }
 
   ew_generic<TD, F><<<grid_for(s, n, 256), 256, 0, s->stream>>>(dest, x, y, ops[0], ops[1], ops[2], g, n, f);
@@ -618,11 +681,10 @@ int launch_accum_cas(cb200_stream* s, T* dest, const cb200_dims* dd, const T* y,
 int fast_binary_f32(cb200_stream* s, float* dest, const cb200_dims* dd, const float* x, const cb200_dims* xd,
                     const float* y, const cb200_dims* yd, long long n, int op, int rev, bool* handled) {
   *handled = true;
+  if (rev) { const float* t = x; x = y; y = t; const cb200_dims* td = xd; xd = yd; yd = td; }
   switch (op) {
-#define X(OPC)                                                                                                      \
-    case OPC:                                                                                                       \
-      if (rev) return launch_map<float, FastBinaryF<OPC, 1> >(s, dest, dd, x, xd, y, yd, n, FastBinaryF<OPC, 1>()); \
-      return launch_map<float, FastBinaryF<OPC, 0> >(s, dest, dd, x, xd, y, yd, n, FastBinaryF<OPC, 0>());
+#define X(OPC) \
+    case OPC: return launch_map<float, FastBinaryF<OPC>, 2>(s, dest, dd, x, xd, y, yd, n, FastBinaryF<OPC>());
     CB_FAST_OPS(X)
 #undef X
   }
@@ -633,13 +695,16 @@ int fast_binary_f32(cb200_stream* s, float* dest, const cb200_dims* dd, const fl
 int fast_binary_const_f32(cb200_stream* s, float* dest, const cb200_dims* dd, const float* x, const cb200_dims* xd,
                           float scalar, long long n, int op, int rev, bool* handled) {
   *handled = true;
-  switch (op) {
-#define X(OPC)                                                                                              \
-    case OPC: {                                                                                             \
-      if (rev) { FastBinaryConstF<OPC, 1> f; f.scalar = scalar;                                             \
-        return launch_map<float, FastBinaryConstF<OPC, 1> >(s, dest, dd, x, xd, nullptr, nullptr, n, f); }  \
-      FastBinaryConstF<OPC, 0> f; f.scalar = scalar;                                                        \
-      return launch_map<float, FastBinaryConstF<OPC, 0> >(s, dest, dd, x, xd, nullptr, nullptr, n, f); }
+  if (rev && (op == CB200_SUB || op == CB200_DIV)) {
+    if (op == CB200_SUB) { FastBinaryConstF<CB200_SUB, 1> f; f.scalar = scalar;
+      return launch_map<float, FastBinaryConstF<CB200_SUB, 1>, 2>(s, dest, dd, x, xd, nullptr, nullptr, n, f); }
+    FastBinaryConstF<CB200_DIV, 1> f; f.scalar = scalar;
+    return launch_map<float, FastBinaryConstF<CB200_DIV, 1>, 2>(s, dest, dd, x, xd, nullptr, nullptr, n, f);
+  }
+  switch (op) {   // + * max min are symmetric: operand order does not matter
+#define X(OPC) \
+    case OPC: { FastBinaryConstF<OPC, 0> f; f.scalar = scalar; \
+      return launch_map<float, FastBinaryConstF<OPC, 0>, 2>(s, dest, dd, x, xd, nullptr, nullptr, n, f); }
     CB_FAST_OPS(X)
 #undef X
   }
@@ -704,8 +769,11 @@ int cb200_assign(cb200_stream* s, int dest_dtype, void* dest, const cb200_dims* 
   CB_DISPATCH_DTYPE(dest_dtype, TD, {
     CB_DISPATCH_DTYPE(src_dtype, TS, {
       AssignF<TD, TS> f;
-      return launch_map<TD, AssignF<TD, TS> >(s, (TD*)dest, dest_dims, (const TS*)src, src_dims, nullptr, nullptr,
-                                              n_elems, f);
+      // same-dtype copies (bias broadcast, row gathers, transposes) get every fast path;
+      // marshalling copies go through the general kernel
+      constexpr int paths = (sizeof(TD) == sizeof(TS) && acc_same<TD, TS>::value) ? 2 : 0;
+      return launch_map<TD, AssignF<TD, TS>, paths>(s, (TD*)dest, dest_dims, (const TS*)src, src_dims, nullptr,
+                                                    nullptr, n_elems, f);
     });
   });
   return CB200_OK;

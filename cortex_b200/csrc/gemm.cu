@@ -96,6 +96,14 @@ int launch_simt(cb200_stream* s, T* C, long long ldc, int ta, int tb, T alpha, c
   return CB200_OK;
 }
 
+// tensor-core fp32 path.  (A CTA-pair variant with tcgen05.mma.cta_group::2 and 256 x 256 tiles was
+// built and measured: correct, but 142 vs 210 TFLOP/s at 4096^3 -- the lo pass over shared memory
+// slows to 1000-2000 cycles per k-block while the pair's MMAs stream operands -- so single CTAs stay.)
+int tc_f32(cb200_stream* s, float* C, long long ldc, int ta, int tb, float alpha, const float* A, int M, int K,
+           long long lda, const float* B, int N, long long ldb, float beta, const float* bias, int act) {
+  return cb200_gemm_tf32x3_launch(s, C, ldc, ta, tb, alpha, A, M, K, lda, B, N, ldb, beta, bias, act, 0, 1, 0);
+}
+
 int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha, const void* A,
               int64_t a_rows, int64_t a_cols, int64_t lda, const void* B, int64_t b_cols, int64_t ldb, double beta,
               const void* bias, int act) {
@@ -119,16 +127,15 @@ int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int
       // epilogue; bias and activation join on the last chunk.
       const int K_CHUNK = 4096;
       if (K <= 2 * K_CHUNK)
-        return cb200_gemm_tf32x3_launch(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb,
-                                        (float)beta, (const float*)bias, act, 0, 1, 0);
+        return tc_f32(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb, (float)beta,
+                      (const float*)bias, act);
       for (int k0 = 0; k0 < K; k0 += K_CHUNK) {
         const int kc = (K - k0 < K_CHUNK) ? (K - k0) : K_CHUNK;
         const bool last = k0 + kc >= K;
         const float* ak = trans_a ? a + (long long)k0 * lda : a + k0;
         const float* bk = trans_b ? b + k0 : b + (long long)k0 * ldb;
-        int rc = cb200_gemm_tf32x3_launch(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, ak, M, kc, lda, bk, N, ldb,
-                                          k0 == 0 ? (float)beta : 1.0f, last ? (const float*)bias : nullptr,
-                                          last ? act : 0, 0, 1, 0);
+        int rc = tc_f32(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, ak, M, kc, lda, bk, N, ldb,
+                        k0 == 0 ? (float)beta : 1.0f, last ? (const float*)bias : nullptr, last ? act : 0);
         if (rc) return rc;
       }
       return CB200_OK;

@@ -26,11 +26,11 @@
 // Operand tiles outside the matrix are zero-filled by TMA, so any M, N, K works;
 // pointers must be 16-byte aligned and row pitches a multiple of 4 elements
 // (the host falls back to gemm_simt otherwise).
-#include "common.cuh"
-#include "sm100.cuh"
+#include "gemm3x_common.cuh"
 #include <mutex>
 
 using namespace sm100;
+using namespace gemm3x;
 
 namespace {
 
@@ -38,26 +38,9 @@ constexpr int BM = 128;
 constexpr int NUM_CONV_WARPS = 8;
 constexpr int NUM_THREADS = (NUM_CONV_WARPS + 2) * 32;
 
-enum { STORE_ROW_MAJOR = 0, STORE_NCHW = 1 };
-enum { FLAG_ONE_TERM = 1, FLAG_BK32 = 2 };
-
-struct GemmParams {
-  float* C;
-  long long ldc;
-  int M, N, K;
-  float alpha, beta;
-  const float* bias;   // [N] or null
-  int act;
-  int a_mn_major, b_mn_major;
-  int store_mode;
-  int hw;              // STORE_NCHW: pixels per image; C[(m / hw) * N * hw + n * hw + m % hw]
-  int flags;
-  int* status;
-};
-
-// BK = fp32 elements per k-block: 32 (one 128-byte swizzle row per operand row) or 16 (64-byte
-// rows).  The smaller block halves the stage, which doubles the number of stages that fit and
-// lets the TMA latency + lo-tile pass of one stage hide behind more MMA work.
+// BK = fp32 elements per k-block: 16 (64-byte swizzle rows).  Measured against 32 (128-byte rows,
+// 2 stages of 96 KB): the smaller block doubles the number of stages that fit, so the TMA latency
+// + lo-tile pass of one stage hides behind more MMA work (173 -> 207 TFLOP/s at 4096^3).
 template <int BN, int BK> struct TileCfg {
   static constexpr int A_TILE = BM * BK * 4;
   static constexpr int B_TILE = BN * BK * 4;
@@ -67,22 +50,6 @@ template <int BN, int BK> struct TileCfg {
   static constexpr int TMEM_COLS = 2 * BN;              // main accumulator + cross-term accumulator
   static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
-
-__device__ __forceinline__ float apply_act(float v, int act) {
-  switch (act) {
-    case CB200_ACT_RELU: return v > 0.f ? v : 0.f;
-    case CB200_ACT_TANH: return tanhf(v);
-    case CB200_ACT_LOGISTIC: return 1.f / (1.f + expf(-v));
-  }
-  return v;
-}
-
-// lo = x - trunc_tf32(x): exact in fp32; 0 for Inf / NaN so that they propagate through hi alone
-__device__ __forceinline__ float lo_part(float x) {
-  const uint32_t xb = __float_as_uint(x);
-  const float lo = x - __uint_as_float(xb & 0xffffe000u);
-  return ((xb & 0x7f800000u) == 0x7f800000u) ? 0.f : lo;
-}
 
 template <int BN, int BK>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -235,76 +202,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
     tc_fence_after();
     if (ok) {
-      const int q = warp & 3, half = warp >> 2;
-      const int m = m0 + q * 32 + lane;
-      constexpr int COLS_PER_HALF = BN / 2;
-      constexpr int CHUNK = COLS_PER_HALF < 32 ? COLS_PER_HALF : 32;
-      static_assert(CHUNK == 32, "BN must be >= 64");
-      const bool vec_ok = p.store_mode == STORE_ROW_MAJOR && (p.ldc % 4) == 0 && (((uintptr_t)p.C) & 15) == 0;
-#pragma unroll 1
-      for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
-        const int col0 = half * COLS_PER_HALF + cc * 32;
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
-        if (!(p.flags & FLAG_ONE_TERM)) {
-          uint32_t rc[32];
-          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + col0), rc);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(rc[j]));
-        } else {
-          tmem_ld_wait();
-        }
-        const int nb = n0 + col0;
-        if (m < p.M && nb < p.N) {
-          if (p.store_mode == STORE_ROW_MAJOR) {
-            float* crow = p.C + (long long)m * p.ldc + nb;
-            if (vec_ok && nb + 32 <= p.N) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o;
-                o.x = p.alpha * __uint_as_float(r[j]);
-                o.y = p.alpha * __uint_as_float(r[j + 1]);
-                o.z = p.alpha * __uint_as_float(r[j + 2]);
-                o.w = p.alpha * __uint_as_float(r[j + 3]);
-                if (p.beta != 0.f) {
-                  float4 c = *reinterpret_cast<const float4*>(crow + j);
-                  o.x += p.beta * c.x; o.y += p.beta * c.y; o.z += p.beta * c.z; o.w += p.beta * c.w;
-                }
-                if (p.bias) {
-                  float4 b = *reinterpret_cast<const float4*>(p.bias + nb + j);
-                  o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
-                }
-                if (p.act) { o.x = apply_act(o.x, p.act); o.y = apply_act(o.y, p.act); o.z = apply_act(o.z, p.act); o.w = apply_act(o.w, p.act); }
-                *reinterpret_cast<float4*>(crow + j) = o;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (nb + j < p.N) {
-                  float o = p.alpha * __uint_as_float(r[j]);
-                  if (p.beta != 0.f) o += p.beta * crow[j];
-                  if (p.bias) o += p.bias[nb + j];
-                  crow[j] = apply_act(o, p.act);
-                }
-              }
-            }
-          } else {
-            const long long img = m / p.hw, pix = m % p.hw;
-            float* cbase = p.C + img * (long long)p.N * p.hw + pix;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (nb + j < p.N) {
-                float* cp = cbase + (long long)(nb + j) * p.hw;
-                float o = p.alpha * __uint_as_float(r[j]);
-                if (p.beta != 0.f) o += p.beta * (*cp);
-                if (p.bias) o += p.bias[nb + j];
-                *cp = apply_act(o, p.act);
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile<BN>(p, tmem_base, m0, n0, warp, lane);
     }
   }
 
@@ -384,8 +282,8 @@ int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans
   p.b_mn_major = trans_b ? 0 : 1;   // op(B)[k][n] = B[k][n]: N is the contiguous axis
   p.store_mode = store_mode; p.hw = hw > 0 ? hw : 1; p.flags = flags; p.status = s->status_dev;
   const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
-  const int BK = (flags & FLAG_BK32) ? 32 : 16;
-  const CUtensorMapSwizzle kswz = BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  constexpr int BK = 16;
+  const CUtensorMapSwizzle kswz = CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap tmA, tmB;
   int rc;
   if (!p.a_mn_major) rc = make_tmap(&tmA, A, M, K, lda, BK, BM, kswz);
@@ -394,11 +292,6 @@ int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans
   if (!p.b_mn_major) rc = make_tmap(&tmB, B, N, K, ldb, BK, BN, kswz);
   else rc = make_tmap(&tmB, B, K, N, ldb, 32, BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
   if (rc) return rc;
-  if (BK == 32) {
-    if (BN == 256) return launch_tile<256, 32>(s, tmA, tmB, p);
-    if (BN == 128) return launch_tile<128, 32>(s, tmA, tmB, p);
-    return launch_tile<64, 32>(s, tmA, tmB, p);
-  }
   if (BN == 256) return launch_tile<256, 16>(s, tmA, tmB, p);
   if (BN == 128) return launch_tile<128, 16>(s, tmA, tmB, p);
   return launch_tile<64, 16>(s, tmA, tmB, p);

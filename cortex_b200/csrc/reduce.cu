@@ -220,15 +220,29 @@ struct SoftmaxGeom {
 };
 
 // One warp (NWARPS = 1) or CTA (NWARPS = 8) per row; the row lives in registers
-// (PER values per thread), so x is read once and y written once.
-template <typename T, int NWARPS, int PER>
+// (PER values per thread), so x is read once and y written once.  VEC = 4 moves the row
+// with 16-byte accesses (contiguous, aligned rows whose length is a multiple of 4).
+template <int NWARPS>
+__device__ __forceinline__ double block_all_reduce(int op, double v, double* slots) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v = red_combine(op, v, __shfl_xor_sync(0xffffffffu, v, d));
+  if (NWARPS == 1) return v;
+  if ((threadIdx.x & 31) == 0) slots[threadIdx.x >> 5] = v;
+  __syncthreads();
+  double r = slots[0];
+#pragma unroll
+  for (int w = 1; w < NWARPS; ++w) r = red_combine(op, r, slots[w]);
+  return r;
+}
+
+template <typename T, int NWARPS, int PER, int VEC>
 __global__ void __launch_bounds__(256)
 softmax_rows(T* out, const T* in, SoftmaxGeom g) {
-  __shared__ double smem[8];
-  __shared__ double bcast;
+  __shared__ double slots_a[8], slots_b[8];
   const int rows_per_block = NWARPS == 1 ? 8 : 1;
   const int tid = NWARPS == 1 ? (threadIdx.x & 31) : threadIdx.x;
   const int nthreads = NWARPS == 1 ? 32 : 256;
+  constexpr int NV = PER / VEC;
   for (long long r0 = (long long)blockIdx.x * rows_per_block; r0 < g.rows; r0 += (long long)gridDim.x * rows_per_block) {
     long long r = NWARPS == 1 ? r0 + (threadIdx.x >> 5) : r0;
     bool live = r < g.rows;
@@ -236,38 +250,56 @@ softmax_rows(T* out, const T* in, SoftmaxGeom g) {
     const T* x = in + (rr / g.inner) * g.in_outer + (rr % g.inner) * g.in_inner;
     T* y = out + (rr / g.inner) * g.out_outer + (rr % g.inner) * g.out_inner;
     T v[PER];
+    // element k of chunk c sits at column (tid + c * nthreads) * VEC + k
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+      const int j = (tid + c * nthreads) * VEC;
+      if (VEC == 1) {
+        if (live && j < g.C) v[c] = x[(long long)j * g.in_cs];
+      } else if (live && j < g.C) {
+        RVec<T, VEC> t = *reinterpret_cast<const RVec<T, VEC>*>(x + j);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[c * VEC + k] = t.v[k];
+      }
+    }
     T mloc = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < PER; ++k) {
-      int j = tid + k * nthreads;
-      if (live && j < g.C) v[k] = x[(long long)j * g.in_cs];
-    }
+    for (int c = 0; c < NV; ++c) {
+      const int j = (tid + c * nthreads) * VEC;
+      if (live && j < g.C) {
 #pragma unroll
-    for (int k = 0; k < PER; ++k) {
-      int j = tid + k * nthreads;
-      if (live && j < g.C) mloc = (mloc != mloc) ? mloc : ((v[k] != v[k]) ? v[k] : (mloc > v[k] ? mloc : v[k]));
+        for (int k = 0; k < VEC; ++k) {
+          const T e = v[c * VEC + k];
+          mloc = (mloc != mloc) ? mloc : ((e != e) ? e : (mloc > e ? mloc : e));
+        }
+      }
     }
-    double m = block_combine<double, NWARPS>(CB200_RMAX, (double)mloc, smem);
-    if (NWARPS == 1) m = __shfl_sync(0xffffffffu, m, 0);
-    else { if (threadIdx.x == 0) bcast = m; __syncthreads(); m = bcast; }
-    T mt = (T)m;
+    const T mt = (T)block_all_reduce<NWARPS>(CB200_RMAX, (double)mloc, slots_a);
     T sloc = (T)0;
 #pragma unroll
-    for (int k = 0; k < PER; ++k) {
-      int j = tid + k * nthreads;
-      if (live && j < g.C) { v[k] = sm_exp<T>(v[k], mt); sloc += v[k]; }
+    for (int c = 0; c < NV; ++c) {
+      const int j = (tid + c * nthreads) * VEC;
+      if (live && j < g.C) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { v[c * VEC + k] = sm_exp<T>(v[c * VEC + k], mt); sloc += v[c * VEC + k]; }
+      }
     }
-    double s = block_combine<double, NWARPS>(CB200_RSUM, (double)sloc, smem);
-    if (NWARPS == 1) s = __shfl_sync(0xffffffffu, s, 0);
-    else { __syncthreads(); if (threadIdx.x == 0) bcast = s; __syncthreads(); s = bcast; }
+    const double s = block_all_reduce<NWARPS>(CB200_RSUM, (double)sloc, slots_b);
     const T st = (T)s;
     const T inv = (T)1 / st;
 #pragma unroll
-    for (int k = 0; k < PER; ++k) {
-      int j = tid + k * nthreads;
-      if (live && j < g.C) y[(long long)j * g.out_cs] = sm_norm<T>(v[k], st, inv);
+    for (int c = 0; c < NV; ++c) {
+      const int j = (tid + c * nthreads) * VEC;
+      if (VEC == 1) {
+        if (live && j < g.C) y[(long long)j * g.out_cs] = sm_norm<T>(v[c], st, inv);
+      } else if (live && j < g.C) {
+        RVec<T, VEC> t;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) t.v[k] = sm_norm<T>(v[c * VEC + k], st, inv);
+        *reinterpret_cast<RVec<T, VEC>*>(y + j) = t;
+      }
     }
-    if (NWARPS != 1) __syncthreads();
+    if (NWARPS != 1) __syncthreads();   // slots are reused by the next row
   }
 }
 
@@ -300,17 +332,34 @@ int launch_softmax(cb200_stream* s, T* out, const T* in, const SoftmaxGeom& g) {
   if (g.rows <= 0 || g.C <= 0) return CB200_OK;
   DeviceGuard guard(s->device);
   long long cap = (long long)s->sm_count * 16;
+  constexpr int V = 16 / sizeof(T);
+  // 16-byte accesses need aligned rows: base, row pitch and length all multiples of V elements
+  const bool vec = g.in_cs == 1 && g.out_cs == 1 && (g.C % V) == 0 && ((uintptr_t)in % 16) == 0 &&
+                   ((uintptr_t)out % 16) == 0 && (g.in_outer % V) == 0 && (g.out_outer % V) == 0 &&
+                   (g.in_inner % V) == 0 && (g.out_inner % V) == 0;
   if (g.in_cs == 1 && g.out_cs == 1 && g.C <= 32 * 32) {
     long long blocks = (g.rows + 7) / 8;
     if (blocks > cap) blocks = cap;
-    if (g.C <= 32 * 4) softmax_rows<T, 1, 4><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
-    else if (g.C <= 32 * 16) softmax_rows<T, 1, 16><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
-    else softmax_rows<T, 1, 32><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    if (g.C <= 32 * 4) softmax_rows<T, 1, 4, 1><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    else if (g.C <= 32 * 16) {
+      if (vec) softmax_rows<T, 1, 16, V><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+      else softmax_rows<T, 1, 16, 1><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    } else {
+      if (vec) softmax_rows<T, 1, 32, V><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+      else softmax_rows<T, 1, 32, 1><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    }
   } else if (g.in_cs == 1 && g.out_cs == 1 && g.C <= 256 * 32) {
     long long blocks = g.rows < cap ? g.rows : cap;
-    if (g.C <= 256 * 8) softmax_rows<T, 8, 8><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
-    else if (g.C <= 256 * 16) softmax_rows<T, 8, 16><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
-    else softmax_rows<T, 8, 32><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    if (g.C <= 256 * 8) {
+      if (vec) softmax_rows<T, 8, 8, V><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+      else softmax_rows<T, 8, 8, 1><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    } else if (g.C <= 256 * 16) {
+      if (vec) softmax_rows<T, 8, 16, V><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+      else softmax_rows<T, 8, 16, 1><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    } else {
+      if (vec) softmax_rows<T, 8, 32, V><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+      else softmax_rows<T, 8, 32, 1><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g);
+    }
   } else {
     long long blocks = (g.rows + 255) / 256;
     if (blocks > cap) blocks = cap;
