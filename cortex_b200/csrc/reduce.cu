@@ -370,38 +370,54 @@ int launch_softmax(cb200_stream* s, T* out, const T* in, const SoftmaxGeom& g) {
 }
 
 // ---------------------- fused bias + ReLU + row max / sum --------------------
-// One CTA per row, row in registers: X read once, Y written once.
-template <typename T, int PER>
+// One CTA per row, row in registers: X read once, Y written once.  VEC = 16 / sizeof(T) moves the
+// row with 16-byte accesses when base pointers, pitches and the row length allow.
+template <typename T, int PER, int VEC>
 __global__ void __launch_bounds__(256)
 bias_relu_rowstats_k(T* Y, long long ldy, const T* X, long long ldx, const T* bias, long long rows, int cols,
                      T* rowmax, T* rowsum) {
-  __shared__ double smem[8];
+  __shared__ double slots_a[8], slots_b[8];
+  constexpr int NV = PER / VEC;
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
     const T* x = X + r * ldx;
     T* y = Y + r * ldy;
     T mx = -INFINITY, sum = (T)0;
-    T v[PER];
+    T v[PER], bv[PER];
 #pragma unroll
-    for (int k = 0; k < PER; ++k) {
-      int j = threadIdx.x + k * 256;
-      if (j < cols) v[k] = x[j];
-    }
-#pragma unroll
-    for (int k = 0; k < PER; ++k) {
-      int j = threadIdx.x + k * 256;
+    for (int c = 0; c < NV; ++c) {
+      const int j = (threadIdx.x + c * 256) * VEC;
       if (j < cols) {
-        T t = v[k] + bias[j];          // binary-op! :+ (same value as the double sum rounded once)
-        T o = t > (T)0 ? t : (T)0;     // binary-op! :max with scalar 0
-        y[j] = o;
-        mx = (mx != mx) ? mx : ((o != o) ? o : (mx > o ? mx : o));
-        sum += o;                      // per-thread partial in the element type, combined in double
+        if (VEC == 1) { v[c] = x[j]; bv[c] = bias[j]; }
+        else {
+          RVec<T, VEC> t = *reinterpret_cast<const RVec<T, VEC>*>(x + j);
+          RVec<T, VEC> tb = *reinterpret_cast<const RVec<T, VEC>*>(bias + j);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) { v[c * VEC + k] = t.v[k]; bv[c * VEC + k] = tb.v[k]; }
+        }
       }
     }
-    double mxd = block_combine<double, 8>(CB200_RMAX, (double)mx, smem);
+#pragma unroll
+    for (int c = 0; c < NV; ++c) {
+      const int j = (threadIdx.x + c * 256) * VEC;
+      if (j < cols) {
+        RVec<T, VEC> o;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          const T t = v[c * VEC + k] + bv[c * VEC + k];   // binary-op! :+ (same value as the double sum rounded once)
+          const T e = t > (T)0 ? t : (T)0;                // binary-op! :max with scalar 0
+          o.v[k] = e;
+          mx = (mx != mx) ? mx : ((e != e) ? e : (mx > e ? mx : e));
+          sum += e;                                       // per-thread partial in the element type, combined in double
+        }
+        if (VEC == 1) y[j] = o.v[0];
+        else *reinterpret_cast<RVec<T, VEC>*>(y + j) = o;
+      }
+    }
+    const double mxd = block_all_reduce<8>(CB200_RMAX, (double)mx, slots_a);
+    const double sumd = block_all_reduce<8>(CB200_RSUM, (double)sum, slots_b);
     if (threadIdx.x == 0 && rowmax) rowmax[r] = (T)mxd;
-    double sumd = block_combine<double, 8>(CB200_RSUM, (double)sum, smem);
     if (threadIdx.x == 0 && rowsum) rowsum[r] = (T)sumd;
-    __syncthreads();
+    __syncthreads();   // slots are reused by the next row
   }
 }
 
@@ -517,14 +533,22 @@ int cb200_bias_relu_rowstats(cb200_stream* s, int dtype, void* Y, int64_t ldy, c
   DeviceGuard guard(s->device);
   long long cap = (long long)s->sm_count * 16;
   unsigned blocks = (unsigned)(rows < cap ? rows : cap);
+#define CB_BRS_ARGS(T) (T*)Y, ldy, (const T*)X, ldx, (const T*)bias, rows, (int)cols, (T*)rowmax, (T*)rowsum
 #define CB_BRS(T)                                                                                          \
   do {                                                                                                     \
-    if (cols <= 256 * 8) bias_relu_rowstats_k<T, 8><<<blocks, 256, 0, s->stream>>>((T*)Y, ldy, (const T*)X, ldx, (const T*)bias, rows, (int)cols, (T*)rowmax, (T*)rowsum); \
-    else if (cols <= 256 * 16) bias_relu_rowstats_k<T, 16><<<blocks, 256, 0, s->stream>>>((T*)Y, ldy, (const T*)X, ldx, (const T*)bias, rows, (int)cols, (T*)rowmax, (T*)rowsum); \
-    else bias_relu_rowstats_k<T, 32><<<blocks, 256, 0, s->stream>>>((T*)Y, ldy, (const T*)X, ldx, (const T*)bias, rows, (int)cols, (T*)rowmax, (T*)rowsum); \
+    constexpr int V = 16 / sizeof(T);                                                                      \
+    const bool vec = (cols % V) == 0 && (ldx % V) == 0 && (ldy % V) == 0 && ((uintptr_t)X % 16) == 0 &&    \
+                     ((uintptr_t)Y % 16) == 0 && ((uintptr_t)bias % 16) == 0;                              \
+    if (cols <= 256 * 8) { if (vec) bias_relu_rowstats_k<T, 8, V><<<blocks, 256, 0, s->stream>>>(CB_BRS_ARGS(T)); \
+                           else bias_relu_rowstats_k<T, 8, 1><<<blocks, 256, 0, s->stream>>>(CB_BRS_ARGS(T)); }  \
+    else if (cols <= 256 * 16) { if (vec) bias_relu_rowstats_k<T, 16, V><<<blocks, 256, 0, s->stream>>>(CB_BRS_ARGS(T)); \
+                                 else bias_relu_rowstats_k<T, 16, 1><<<blocks, 256, 0, s->stream>>>(CB_BRS_ARGS(T)); } \
+    else { if (vec) bias_relu_rowstats_k<T, 32, V><<<blocks, 256, 0, s->stream>>>(CB_BRS_ARGS(T));          \
+           else bias_relu_rowstats_k<T, 32, 1><<<blocks, 256, 0, s->stream>>>(CB_BRS_ARGS(T)); }            \
   } while (0)
   if (dtype == CB200_FLOAT) CB_BRS(float); else CB_BRS(double);
 #undef CB_BRS
+#undef CB_BRS_ARGS
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
