@@ -48,7 +48,7 @@ template <int BN> struct ConvCfg {
   // MMAs do not form one dependency chain on a single accumulator; the epilogue adds them.
   static constexpr int ACC_SETS = BN <= 64 ? 2 : 1;
   static constexpr int TMEM_COLS = 2 * BN * ACC_SETS;
-  static constexpr int SMEM = STAGES * STAGE + 1024 + 256;
+  static constexpr int SMEM = STAGES * STAGE + 1024 + 512;   // alignment slack + barriers and the tap table
 };
 
 __device__ __forceinline__ float conv_lo_part(float x) {
@@ -68,6 +68,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
   uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::STAGE);
   uint32_t* tmem_slot = (uint32_t*)(bars + 3 * STAGES + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* tap_off = (int*)(bars + 32);      // [kh*kw <= 32] input offset ky*W + kx of each filter tap
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (p.cout + BN - 1) / BN;
@@ -90,6 +91,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
     *abort_flag = 0;
     mbar_fence_init();
   }
+  if (threadIdx.x < 32 && (int)threadIdx.x < p.kh * p.kw)
+    tap_off[threadIdx.x] = ((int)threadIdx.x / p.kw) * p.in_w + ((int)threadIdx.x % p.kw);
   if (warp == GATHER_WARPS + 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish();
@@ -168,9 +171,33 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
     const uint32_t chunk = lane >> 3;
     // im2col rows of k-block i for this lane's pixel, fetched one k-block ahead so that the
     // global-load latency overlaps the shared-memory work of the current k-block
+    // Filters with at most 32 taps (3x3, 5x5): which taps fall inside the image is a per-pixel bit
+    // mask computed once, and a tap's input offset comes from a small shared table, so that one
+    // gathered element costs a handful of instructions.
+    const bool tap_table = khkw <= 32;
+    uint32_t tap_valid = 0;
+    if (tap_table && m_ok) {
+      for (int t = 0; t < khkw; ++t) {
+        const int iy = iy0 + t / p.kw, ix = ix0 + t % p.kw;
+        if (iy >= 0 && iy < p.in_h && ix >= 0 && ix < p.in_w) tap_valid |= 1u << t;
+      }
+    }
+    const int in_hw = p.in_h * p.in_w;
+    const int pix_off = iy0 * p.in_w + ix0;
     auto fetch = [&](int i, float (&v)[8]) {
       const int k0 = i * CBK + khalf * 8;
       int c = k0 / khkw, t = k0 - c * khkw;
+      if (tap_table) {
+        const float* cb = img_base + (long long)c * in_hw + pix_off;
+        const int kleft = p.K - k0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const bool valid = ((tap_valid >> t) & 1u) && j < kleft;
+          v[j] = valid ? __ldg(cb + tap_off[t]) : 0.f;
+          if (++t == khkw) { t = 0; cb += in_hw; }
+        }
+        return;
+      }
       int ky = t / p.kw, kx = t - ky * p.kw;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
