@@ -65,7 +65,7 @@ def make_input(lo, hi):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 50 ms while a timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 20 ms while the timed regions run."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -76,7 +76,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -323,6 +323,71 @@ def bench_mlp_128(drv, dev):
     return res
 
 
+def bench_mlp_f64(drv, dev):
+    """The fp64 variant of the wide MLP on a 16384-row slice of the batch (DMMA gemm + fused epilogue)."""
+    from cortex_b200 import nn
+    from cortex_b200 import tensor as ct
+    stream = dev.create_stream()
+    rows = 16384
+    with ct.with_stream(stream), ct.with_datatype("double"):
+        layers = []
+        for i, w in enumerate(make_weights()):
+            layers.append((ct.to_tensor(w.astype(np.float64)), ct.new_tensor([w.shape[0]]),
+                           "softmax" if i == HIDDEN_LAYERS else "relu"))
+        net = nn.MLP(layers, fused=True)
+        x = ct.to_tensor(make_input(0, rows).astype(np.float64))
+        net.infer(x)
+        ms = time_region(stream, lambda: net.infer(x), 2)
+    return {"rows": rows, "samples_per_s": round(rows / ms * 1000.0, 0),
+            "tflops": round(rows * FLOPS_PER_SAMPLE / ms / 1e9, 2), "ms": round(ms, 2),
+            "note": "full fp64 run of the benchmark: --dtype double"}
+
+
+def bench_column_head(dev, stream, world, rank, dt, dist):
+    """The column-sharded last layer (4096 -> 1000 split by output column over the ranks) on an
+    8192-row replicated activation block: (a) GEMM, NCCL all-gather, re-layout assign!, softmax!;
+    (b) ONE fused GEMM whose epilogue stores its window into every rank's logits over NVLink, a
+    stream-ordered fence, softmax!.  Device time, max over ranks."""
+    import torch
+    from cortex_b200 import tensor as ct
+    from cortex_b200.parallel import (PeerLogits, column_sharded_head, column_sharded_head_fused, shard_bounds,
+                                      stream_fence)
+    B = 8192
+    npdt = np.float32 if dt == "float" else np.float64
+    lo, hi = shard_bounds(CLASSES, world, rank)
+    w = make_weights()[-1].astype(npdt)
+    res = {"rows": B, "columns_per_rank": hi - lo}
+    with ct.with_stream(stream), ct.with_datatype(dt):
+        h = ct.to_tensor(np.maximum(make_input(0, B), 0).astype(npdt))
+        ws, bs = ct.to_tensor(w[lo:hi]), ct.new_tensor([hi - lo])
+        exchange = PeerLogits(dev, B, CLASSES, world, rank, dt)
+        fence = stream_fence(stream)
+        fence()
+
+        def fused():
+            column_sharded_head_fused(h, ws, bs, exchange, fence)
+            fence()       # the logits buffers are reused by the next call
+
+        def nccl():
+            column_sharded_head(h, ws, bs, CLASSES, world, rank)
+
+        for name, fn, iters in (("nccl_allgather_ms", nccl, 5), ("fused_peer_store_ms", fused, 10)):
+            for _ in range(2):
+                fn()
+            stream.sync()
+            dist.barrier()
+            ms = time_region(stream, fn, iters)
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[name] = round(float(t[0]), 4)
+        probs = ct.to_array(exchange.tensor).reshape(B, CLASSES)
+        res["max_abs_rowsum_minus_1"] = float(np.abs(probs.sum(axis=1) - 1.0).max())
+        stream.sync()
+        dist.barrier()
+        exchange.close()
+    return res
+
+
 def run_b200(args, rank, world, local_rank):
     import torch  # plumbing only: rendezvous, barrier, max-over-ranks
     dist = None
@@ -343,10 +408,12 @@ def run_b200(args, rank, world, local_rank):
     stream = dev.create_stream()
     lo, hi = shard_bounds(BATCH, world, rank)
     rows = hi - lo
-    weights = make_weights()
-    x_host = drv.allocate_host_buffer(rows * WIDTH, "float")
+    dt = args.dtype                                    # "float" (the headline) or "double" (the fp64 variant)
+    npdt = np.float32 if dt == "float" else np.float64
+    weights = [w.astype(npdt) for w in make_weights()]
+    x_host = drv.allocate_host_buffer(rows * WIDTH, dt)
     x_host.as_numpy()[:] = make_input(lo, hi).reshape(-1)
-    y_host = drv.allocate_host_buffer(rows * CLASSES, "float")
+    y_host = drv.allocate_host_buffer(rows * CLASSES, dt)
 
     def barrier():
         stream.sync()
@@ -355,13 +422,13 @@ def run_b200(args, rank, world, local_rank):
             dist.barrier()
             torch.cuda.synchronize()
 
-    with ct.with_stream(stream), ct.with_datatype("float"):
+    with ct.with_stream(stream), ct.with_datatype(dt):
         layers = []
         for i, w in enumerate(weights):
             act = "softmax" if i == len(weights) - 1 else "relu"
             layers.append((ct.to_tensor(w), ct.new_tensor([w.shape[0]]), act))
         net = nn.MLP(layers, fused=True)
-        x_dev = dev.allocate_device_buffer(rows * WIDTH, "float")
+        x_dev = dev.allocate_device_buffer(rows * WIDTH, dt)
         stream.copy_host_to_device(x_host, 0, x_dev, 0, rows * WIDTH)
         x = ct.Tensor(dev, dims.dimensions([rows, WIDTH]), x_dev)
 
@@ -371,7 +438,7 @@ def run_b200(args, rank, world, local_rank):
         def step(record=False):
             cur = x
             for idx, (lin, act) in enumerate(net.layers):
-                out = net._buffer(idx, rows, lin.weights.shape()[0], "float")
+                out = net._buffer(idx, rows, lin.weights.shape()[0], dt)
                 if record and idx < HIDDEN_LAYERS:
                     e0 = stream.create_event(timing=True)
                 lin.forward_fused(cur, out, act if act != "softmax" else None)
@@ -396,13 +463,12 @@ def run_b200(args, rank, world, local_rank):
         e1.wait_for_event()
         barrier()
         launches = stream.launch_count() - launches0
-        clocks = sampler.stop() if rank == 0 else None
         ms_step = e1.elapsed_ms_since(e0) / args.steps
         gemm_ms = float(np.mean([b.elapsed_ms_since(a) for a, b in gemm_events]))
 
         # ---- end to end: pinned host in -> H2D -> layers -> D2H, every step --------------------
         chunk = min(8192, rows)
-        pipe = BatchPipeline(dev, net, WIDTH, CLASSES, chunk, "float")
+        pipe = BatchPipeline(dev, net, WIDTH, CLASSES, chunk, dt)
         h2d = d2h = 0
         for _ in range(min(args.warmup, 2)):
             pipe.run(x_host, y_host, rows)
@@ -415,9 +481,10 @@ def run_b200(args, rank, world, local_rank):
         t1.wait_for_event()
         barrier()
         e2e_ms = t1.elapsed_ms_since(t0) / args.steps
-        launches += 0
+        clocks = sampler.stop() if rank == 0 else None      # sampled across both timed regions
         probs = y_host.as_numpy().reshape(rows, CLASSES)
         checksum = float(np.abs(probs.sum(axis=1) - 1.0).max())
+        column_head = bench_column_head(dev, stream, world, rank, dt, dist) if world > 1 else None
 
     # max over ranks
     if dist is not None:
@@ -435,29 +502,38 @@ def run_b200(args, rank, world, local_rank):
     value = BATCH / (ms_step / 1000.0)
     e2e_value = BATCH / (e2e_ms / 1000.0)
     gemm_flops = 2.0 * rows * WIDTH * WIDTH
-    peak_tf32x3 = peaks["bf16_sustained"] / 2.0 / 3.0
+    if dt == "float":
+        peak_tf32x3 = peaks["bf16_sustained"] / 2.0 / 3.0
+        peak_note = ("%s bf16 sustained %.0f TF / 2 (tf32 rate) / 3 (three tf32 MMAs per product); algorithmic work "
+                     "2*M*N*K" % (peaks["source"], peaks["bf16_sustained"]))
+        kernel_name, kernel_path = "gemm_tf32x3_kernel<256>", "gemm_bias_act (tcgen05 3xTF32, bias+ReLU fused) x5 + softmax"
+    else:
+        peak_tf32x3 = 37.0
+        peak_note = "nominal B200 fp64 dense rate 37 TF (no measured fp64 peak exists for this pool); work 2*M*N*K"
+        kernel_name, kernel_path = "gemm_f64_kernel (DMMA)", "gemm_bias_act (DMMA fp64, bias+ReLU fused) x5 + softmax"
     achieved = gemm_flops / gemm_ms / 1e9
     line = {
-        "metric": "wide_mlp_inference_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
+        "metric": "wide_mlp_inference_samples_per_s" + ("" if dt == "float" else "_fp64"), "value": value, "unit": "samples/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "wide_mlp: batch 65536 x 4096 -> 4 x (linear 4096 + ReLU) -> linear 1000 + softmax, fp32, "
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32" if dt == "float" else "f64", "data": "synthetic",
+        "config": {"workload": "wide_mlp: batch 65536 x 4096 -> 4 x (linear 4096 + ReLU) -> linear 1000 + softmax, %s, " % ("fp32" if dt == "float" else "fp64") +
                                "He-normal weights (seeds 502-506), zero biases, batch-sharded, weights replicated",
                    "global_batch": BATCH, "rows_per_gpu": rows, "parallelism": "batch-shard x%d" % world,
                    "l2": "inputs larger than L2 (every layer streams >= %d MiB of activations)" % (rows * WIDTH * 4 >> 20),
-                   "kernel_path": "gemm_bias_act (tcgen05 3xTF32, bias+ReLU fused) x5 + softmax"},
+                   "kernel_path": kernel_path},
         "tflops": value * FLOPS_PER_SAMPLE / 1e12,
         "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                 "ms_per_step": e2e_ms, "chunk_rows": chunk, "max_abs_rowsum_minus_1": checksum},
         "gpu_launches": launches,
-        "roofline": {"bound": "tensor", "kernel": "gemm_tf32x3_kernel<256> (M=%d, N=4096, K=4096)" % rows,
+        "roofline": {"bound": "tensor", "kernel": "%s (M=%d, N=4096, K=4096)" % (kernel_name, rows),
                      "achieved": achieved, "peak": peak_tf32x3, "unit": "TFLOP/s", "frac": achieved / peak_tf32x3,
                      "traffic": None, "ms_per_launch": gemm_ms,
-                     "peak_note": "%s bf16 sustained %.0f TF / 2 (tf32 rate) / 3 (three tf32 MMAs per product); "
-                                  "algorithmic work 2*M*N*K" % (peaks["source"], peaks["bf16_sustained"])},
+                     "peak_note": peak_note},
         "clocks": clocks,
     }
-    if world == 1:
+    if column_head is not None:
+        line["column_sharded_head"] = column_head
+    if world == 1 and dt == "float":
         cores = os.cpu_count() or 1
         rate, secs = cpu_forward_rate(2048, weights)
         line["cpu_baseline"] = {"value": rate, "unit": "samples/s", "cores": cores, "kind": "port",
@@ -468,6 +544,7 @@ def run_b200(args, rank, world, local_rank):
         line["eltwise"] = bench_eltwise(drv, dev, peaks)
         line["conv_64x64x56x56"] = bench_conv(drv, dev, peaks)
         line["mlp_128x784_500_10"] = bench_mlp_128(drv, dev)
+        line["wide_mlp_fp64"] = bench_mlp_f64(drv, dev)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -479,6 +556,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--dtype", default="float", choices=["float", "double"],
+                    help="float = the headline workload; double = its fp64 variant (DMMA gemm)")
     ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128"],
                     help="mlp = the benchmark; gemm4096 / eltwise = the small single-purpose runs used for ncu captures")
     args = ap.parse_args()

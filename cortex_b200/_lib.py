@@ -82,6 +82,12 @@ SIGNATURES = {
     "cb200_convolution_forward_static": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, C.POINTER(ConvDesc)],
     "cb200_unsupported": [C.c_char_p],
     "cb200_gemm_bias_act": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i],
+    "cb200_gemm_bias_act_peers": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i,
+                                  _i, C.POINTER(_vp)],
+    "cb200_peer_enable": [_i, _i],
+    "cb200_ipc_export": [_i, _vp, C.c_char_p],
+    "cb200_ipc_import": [_i, C.c_char_p, C.POINTER(_vp)],
+    "cb200_ipc_close": [_i, _vp],
     "cb200_bias_relu_rowstats": [_vp, _i, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp],
     "cb200_launch_count": [_vp],
     "cb200_stream_status": [_vp, C.POINTER(_i), C.POINTER(_i)],

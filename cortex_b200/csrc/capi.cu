@@ -183,6 +183,48 @@ int cb200_memcpy_d2d(cb200_stream* s, void* dst, const void* src, size_t bytes) 
   return CB200_OK;
 }
 
+// ---- multi-GPU plumbing: peer access inside one process, CUDA IPC across processes ------------
+int cb200_peer_enable(int device, int peer_device) {
+  CB_REQUIRE(device != peer_device, "peer_enable: a device is not its own peer");
+  DeviceGuard g(device);
+  int can = 0;
+  CB_CUDA(cudaDeviceCanAccessPeer(&can, device, peer_device));
+  if (!can) {
+    cb200_set_error("peer_enable: device %d cannot address device %d", device, peer_device);
+    return CB200_ERR_UNSUPPORTED;
+  }
+  cudaError_t err = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (err == cudaErrorPeerAccessAlreadyEnabled) { (void)cudaGetLastError(); return CB200_OK; }
+  CB_CUDA(err);
+  return CB200_OK;
+}
+
+int cb200_ipc_export(int device, void* device_ptr, unsigned char* handle_out) {
+  CB_REQUIRE(device_ptr && handle_out, "ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == CB200_IPC_HANDLE_BYTES, "IPC handle size");
+  DeviceGuard g(device);
+  cudaIpcMemHandle_t h;
+  CB_CUDA(cudaIpcGetMemHandle(&h, device_ptr));
+  memcpy(handle_out, &h, sizeof(h));
+  return CB200_OK;
+}
+
+int cb200_ipc_import(int device, const unsigned char* handle, void** ptr_out) {
+  CB_REQUIRE(handle && ptr_out, "ipc_import: null argument");
+  DeviceGuard g(device);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  CB_CUDA(cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+  return CB200_OK;
+}
+
+int cb200_ipc_close(int device, void* ptr) {
+  if (!ptr) return CB200_OK;
+  DeviceGuard g(device);
+  CB_CUDA(cudaIpcCloseMemHandle(ptr));
+  return CB200_OK;
+}
+
 int cb200_event_record(cb200_stream* s, int timing, cb200_event** out) {
   CB_REQUIRE(s && out, "event_record: null argument");
   DeviceGuard g(s->device);

@@ -165,6 +165,14 @@ static inline void operand_from_dims(Operand& o, const cb200_dims* d) {
   }
 }
 
+// Extra destinations of a GEMM epilogue: the finished C window is also stored at the same row-major
+// position of each buffer (other GPUs' memory, reached by plain stores over NVLink).
+enum { CB_MAX_PEERS = 7 };
+struct PeerList {
+  int n;
+  void* p[CB_MAX_PEERS];
+};
+
 // validation shared by the elementwise entry points
 int cb200_check_dims(const cb200_dims* d, const char* what);
 

@@ -23,7 +23,7 @@ int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans
                              float beta, const float* bias, int act, int store_mode, int hw, int flags);
 int cb200_gemm_f64_launch(cb200_stream* s, double* C, long long ldc, int trans_a, int trans_b, double alpha,
                           const double* A, int M, int K, long long lda, const double* B, int N, long long ldb,
-                          double beta, const double* bias, int act);
+                          double beta, const double* bias, int act, const PeerList* peers);
 int cb200_gemm_simt_f32_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
                                const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
                                float beta);
@@ -139,7 +139,7 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
     // per image, as the reference: out_n[C_out, hw] = W[C_out, K] * cols_n[hw, K]^T + out_alpha * out_n
     rc = cb200_gemm_f64_launch(s, (double*)out + (long long)n * cout * hw, hw, 0, 1, 1.0, (const double*)w, cout,
                                g.kcols, g.kcols, (const double*)cols + (long long)n * hw * g.ld, hw, g.ld, out_alpha,
-                               nullptr, 0);
+                               nullptr, 0, nullptr);
     if (rc) return rc;
   }
   return CB200_OK;
@@ -259,7 +259,7 @@ int cb200_convolution_forward_static(cb200_stream* s, int dtype, void* out, cons
   for (int n = 0; n < g.batch; ++n) {
     rc = cb200_gemm_f64_launch(s, (double*)out + (long long)n * cout * hw, hw, 0, 1, 1.0, (const double*)w, cout,
                                g.kcols, g.kcols, (const double*)cols + (long long)n * hw * g.ld, hw, g.ld, out_alpha,
-                               nullptr, 0);
+                               nullptr, 0, nullptr);
     if (rc) return rc;
   }
   return CB200_OK;

@@ -7,10 +7,14 @@
 int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
                              const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
                              float beta, const float* bias, int act, int store_mode, int hw, int flags);
+int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
+                                   const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
+                                   float beta, const float* bias, int act, int store_mode, int hw, int flags,
+                                   int n_peers, float* const* peers);
 bool cb200_gemm_tf32x3_eligible(const float* A, long long lda, const float* B, long long ldb, int M, int N, int K);
 int cb200_gemm_f64_launch(cb200_stream* s, double* C, long long ldc, int trans_a, int trans_b, double alpha,
                           const double* A, int M, int K, long long lda, const double* B, int N, long long ldb,
-                          double beta, const double* bias, int act);
+                          double beta, const double* bias, int act, const PeerList* peers);
 
 namespace {
 
@@ -28,7 +32,7 @@ template <typename T> __device__ __forceinline__ T act_apply(T v, int act) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_simt(T* C, long long ldc, const T* A, long long sam, long long sak, const T* B, long long sbk, long long sbn,
-          int M, int N, int K, T alpha, T beta, const T* bias, int act) {
+          int M, int N, int K, T alpha, T beta, const T* bias, int act, PeerList peers) {
   __shared__ T As[16][64 + 1];
   __shared__ T Bs[16][64 + 1];
   const int t = threadIdx.x, tx = t % 16, ty = t / 16;
@@ -79,19 +83,23 @@ gemm_simt(T* C, long long ldc, const T* A, long long sam, long long sak, const T
       T o = alpha * acc[i][j];
       if (beta != (T)0) o += beta * (*c);
       if (bias) o += bias[n];
-      *c = act_apply<T>(o, act);
+      o = act_apply<T>(o, act);
+      *c = o;
+      for (int d = 0; d < peers.n; ++d) ((T*)peers.p[d])[(long long)m * ldc + n] = o;
     }
   }
 }
 
 template <typename T>
 int launch_simt(cb200_stream* s, T* C, long long ldc, int ta, int tb, T alpha, const T* A, int M, int K, long long lda,
-                const T* B, int N, long long ldb, T beta, const T* bias, int act) {
+                const T* B, int N, long long ldb, T beta, const T* bias, int act, const PeerList* peer_list = nullptr) {
   DeviceGuard guard(s->device);
+  PeerList peers;
+  if (peer_list) peers = *peer_list; else peers.n = 0;
   dim3 grid((N + 63) / 64, (M + 63) / 64);
   long long sam = ta ? 1 : lda, sak = ta ? lda : 1;
   long long sbk = tb ? 1 : ldb, sbn = tb ? ldb : 1;
-  gemm_simt<T><<<grid, 256, 0, s->stream>>>(C, ldc, A, sam, sak, B, sbk, sbn, M, N, K, alpha, beta, bias, act);
+  gemm_simt<T><<<grid, 256, 0, s->stream>>>(C, ldc, A, sam, sak, B, sbk, sbn, M, N, K, alpha, beta, bias, act, peers);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
@@ -100,13 +108,15 @@ int launch_simt(cb200_stream* s, T* C, long long ldc, int ta, int tb, T alpha, c
 // built and measured: correct, but 142 vs 210 TFLOP/s at 4096^3 -- the lo pass over shared memory
 // slows to 1000-2000 cycles per k-block while the pair's MMAs stream operands -- so single CTAs stay.)
 int tc_f32(cb200_stream* s, float* C, long long ldc, int ta, int tb, float alpha, const float* A, int M, int K,
-           long long lda, const float* B, int N, long long ldb, float beta, const float* bias, int act) {
-  return cb200_gemm_tf32x3_launch(s, C, ldc, ta, tb, alpha, A, M, K, lda, B, N, ldb, beta, bias, act, 0, 1, 0);
+           long long lda, const float* B, int N, long long ldb, float beta, const float* bias, int act,
+           const PeerList* peers) {
+  return cb200_gemm_tf32x3_launch_peers(s, C, ldc, ta, tb, alpha, A, M, K, lda, B, N, ldb, beta, bias, act, 0, 1, 0,
+                                        peers ? peers->n : 0, peers ? (float* const*)peers->p : nullptr);
 }
 
 int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha, const void* A,
               int64_t a_rows, int64_t a_cols, int64_t lda, const void* B, int64_t b_cols, int64_t ldb, double beta,
-              const void* bias, int act) {
+              const void* bias, int act, const PeerList* peers = nullptr) {
   CB_REQUIRE(s && C && A && B, "gemm: null argument");
   CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "gemm! is only defined for float and double tensors");
   CB_REQUIRE(a_rows >= 0 && a_cols >= 0 && b_cols >= 0, "gemm: negative extent");
@@ -128,26 +138,27 @@ int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int
       const int K_CHUNK = 4096;
       if (K <= 2 * K_CHUNK)
         return tc_f32(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb, (float)beta,
-                      (const float*)bias, act);
+                      (const float*)bias, act, peers);
       for (int k0 = 0; k0 < K; k0 += K_CHUNK) {
         const int kc = (K - k0 < K_CHUNK) ? (K - k0) : K_CHUNK;
         const bool last = k0 + kc >= K;
         const float* ak = trans_a ? a + (long long)k0 * lda : a + k0;
         const float* bk = trans_b ? b + k0 : b + (long long)k0 * ldb;
         int rc = tc_f32(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, ak, M, kc, lda, bk, N, ldb,
-                        k0 == 0 ? (float)beta : 1.0f, last ? (const float*)bias : nullptr, last ? act : 0);
+                        k0 == 0 ? (float)beta : 1.0f, last ? (const float*)bias : nullptr, last ? act : 0,
+                        last ? peers : nullptr);
         if (rc) return rc;
       }
       return CB200_OK;
     }
     return launch_simt<float>(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb, (float)beta,
-                              (const float*)bias, act);
+                              (const float*)bias, act, peers);
   }
   if (K >= 1)
     return cb200_gemm_f64_launch(s, (double*)C, ldc, trans_a, trans_b, alpha, (const double*)A, M, K, lda,
-                                 (const double*)B, N, ldb, beta, (const double*)bias, act);
+                                 (const double*)B, N, ldb, beta, (const double*)bias, act, peers);
   return launch_simt<double>(s, (double*)C, ldc, trans_a, trans_b, alpha, (const double*)A, M, K, lda, (const double*)B,
-                             N, ldb, beta, (const double*)bias, act);
+                             N, ldb, beta, (const double*)bias, act, peers);
 }
 
 }  // namespace
@@ -171,6 +182,23 @@ int cb200_gemm_bias_act(cb200_stream* s, int dtype, void* C, int64_t ldc, int tr
                         const void* A, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B, int64_t b_cols,
                         int64_t ldb, double beta, const void* bias, int act) {
   return gemm_impl(s, dtype, C, ldc, trans_a, trans_b, alpha, A, a_rows, a_cols, lda, B, b_cols, ldb, beta, bias, act);
+}
+
+int cb200_gemm_bias_act_peers(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha,
+                              const void* A, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B,
+                              int64_t b_cols, int64_t ldb, double beta, const void* bias, int act, int n_peers,
+                              void* const* peer_C) {
+  CB_REQUIRE(n_peers >= 0 && n_peers <= CB_MAX_PEERS, "gemm_bias_act_peers: n_peers %d outside [0, %d]", n_peers,
+             (int)CB_MAX_PEERS);
+  CB_REQUIRE(n_peers == 0 || peer_C, "gemm_bias_act_peers: null peer list");
+  PeerList peers;
+  peers.n = n_peers;
+  for (int d = 0; d < CB_MAX_PEERS; ++d) {
+    peers.p[d] = d < n_peers ? peer_C[d] : nullptr;
+    CB_REQUIRE(d >= n_peers || peers.p[d], "gemm_bias_act_peers: peer destination %d is null", d);
+  }
+  return gemm_impl(s, dtype, C, ldc, trans_a, trans_b, alpha, A, a_rows, a_cols, lda, B, b_cols, ldb, beta, bias, act,
+                   &peers);
 }
 
 // Test hooks (not part of the public header): force a specific fp32 kernel.

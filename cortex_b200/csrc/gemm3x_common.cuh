@@ -10,6 +10,7 @@ using namespace sm100;
 
 enum { STORE_ROW_MAJOR = 0, STORE_NCHW = 1 };
 enum { FLAG_ONE_TERM = 1 };
+enum { MAX_PEERS = 7 };
 
 struct GemmParams {
   float* C;
@@ -23,6 +24,10 @@ struct GemmParams {
   int hw;              // STORE_NCHW: pixels per image; C[(m / hw) * N * hw + n * hw + m % hw]
   int flags;
   int* status;
+  // Row-major store only: every finished tile is also written to the same (row, column) position of
+  // these buffers, which may live in other GPUs' memory (plain peer stores over NVLink).
+  int n_peers;
+  float* peers[MAX_PEERS];
 };
 
 __device__ __forceinline__ float apply_act(float v, int act) {
@@ -52,7 +57,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
       constexpr int COLS_PER_HALF = BN / 2;
       constexpr int CHUNK = COLS_PER_HALF < 32 ? COLS_PER_HALF : 32;
       static_assert(CHUNK == 32, "BN must be >= 64");
-      const bool vec_ok = p.store_mode == STORE_ROW_MAJOR && (p.ldc % 4) == 0 && (((uintptr_t)p.C) & 15) == 0;
+      bool vec_ok = p.store_mode == STORE_ROW_MAJOR && (p.ldc % 4) == 0 && (((uintptr_t)p.C) & 15) == 0;
+      for (int d = 0; d < p.n_peers; ++d) vec_ok = vec_ok && (((uintptr_t)p.peers[d]) & 15) == 0;
 #pragma unroll 1
       for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
         const int col0 = half * COLS_PER_HALF + cc * 32;
@@ -89,6 +95,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                 }
                 if (p.act) { o.x = apply_act(o.x, p.act); o.y = apply_act(o.y, p.act); o.z = apply_act(o.z, p.act); o.w = apply_act(o.w, p.act); }
                 *reinterpret_cast<float4*>(crow + j) = o;
+                for (int d = 0; d < p.n_peers; ++d)
+                  *reinterpret_cast<float4*>(p.peers[d] + (long long)m * p.ldc + nb + j) = o;
               }
             } else {
 #pragma unroll
@@ -97,7 +105,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                   float o = p.alpha * __uint_as_float(r[j]);
                   if (p.beta != 0.f) o += p.beta * crow[j];
                   if (p.bias) o += p.bias[nb + j];
-                  crow[j] = apply_act(o, p.act);
+                  o = apply_act(o, p.act);
+                  crow[j] = o;
+                  for (int d = 0; d < p.n_peers; ++d) p.peers[d][(long long)m * p.ldc + nb + j] = o;
                 }
               }
             }

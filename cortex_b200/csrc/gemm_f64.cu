@@ -35,7 +35,7 @@ template <bool A_K_CONTIG, bool B_N_CONTIG>
 __global__ void __launch_bounds__(256)
 gemm_f64_kernel(double* C, long long ldc, const double* A, long long sam, long long sak, const double* B,
                 long long sbk, long long sbn, int M, int N, int K, double alpha, double beta, const double* bias,
-                int act) {
+                int act, PeerList peers) {
   __shared__ double As[DBK][DLD];
   __shared__ double Bs[DBK][DLD];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -107,7 +107,9 @@ gemm_f64_kernel(double* C, long long ldc, const double* A, long long sam, long l
         double o = alpha * acc[i][j][e];
         if (beta != 0.0) o += beta * (*c);
         if (bias) o += bias[n];
-        *c = act_f64(o, act);
+        o = act_f64(o, act);
+        *c = o;
+        for (int d = 0; d < peers.n; ++d) ((double*)peers.p[d])[(long long)m * ldc + n] = o;
       }
     }
   }
@@ -117,13 +119,15 @@ gemm_f64_kernel(double* C, long long ldc, const double* A, long long sam, long l
 
 int cb200_gemm_f64_launch(cb200_stream* s, double* C, long long ldc, int trans_a, int trans_b, double alpha,
                           const double* A, int M, int K, long long lda, const double* B, int N, long long ldb,
-                          double beta, const double* bias, int act) {
+                          double beta, const double* bias, int act, const PeerList* peer_list) {
   DeviceGuard guard(s->device);
+  PeerList peers;
+  if (peer_list) peers = *peer_list; else peers.n = 0;
   dim3 grid((N + DBN - 1) / DBN, (M + DBM - 1) / DBM);
   const long long sam = trans_a ? 1 : lda, sak = trans_a ? lda : 1;
   const long long sbk = trans_b ? 1 : ldb, sbn = trans_b ? ldb : 1;
 #define CB_F64(AK, BNC) \
-  gemm_f64_kernel<AK, BNC><<<grid, 256, 0, s->stream>>>(C, ldc, A, sam, sak, B, sbk, sbn, M, N, K, alpha, beta, bias, act)
+  gemm_f64_kernel<AK, BNC><<<grid, 256, 0, s->stream>>>(C, ldc, A, sam, sak, B, sbk, sbn, M, N, K, alpha, beta, bias, act, peers)
   if (!trans_a && !trans_b) CB_F64(true, true);
   else if (!trans_a && trans_b) CB_F64(true, false);
   else if (trans_a && !trans_b) CB_F64(false, true);

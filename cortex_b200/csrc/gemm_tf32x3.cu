@@ -272,11 +272,28 @@ int launch_tile(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmB,
 }  // namespace
 
 // Shared with conv.cu.  A: op(A) is M x K; B: op(B) is K x N.
+int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
+                                   const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
+                                   float beta, const float* bias, int act, int store_mode, int hw, int flags,
+                                   int n_peers, float* const* peers);
+
 int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
                              const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
                              float beta, const float* bias, int act, int store_mode, int hw, int flags) {
+  return cb200_gemm_tf32x3_launch_peers(s, C, ldc, trans_a, trans_b, alpha, A, M, K, lda, B, N, ldb, beta, bias, act,
+                                        store_mode, hw, flags, 0, nullptr);
+}
+
+// The same launch with up to MAX_PEERS extra destinations: every output tile is also stored to
+// peers[d] + (the same row-major position), d < n_peers.
+int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
+                                   const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
+                                   float beta, const float* bias, int act, int store_mode, int hw, int flags,
+                                   int n_peers, float* const* peers) {
   DeviceGuard guard(s->device);
   GemmParams p;
+  p.n_peers = n_peers;
+  for (int d = 0; d < MAX_PEERS; ++d) p.peers[d] = d < n_peers ? peers[d] : nullptr;
   p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta; p.bias = bias; p.act = act;
   p.a_mn_major = trans_a ? 1 : 0;   // op(A)[m][k] = A[k][m]: M is the contiguous axis
   p.b_mn_major = trans_b ? 0 : 1;   // op(B)[k][n] = B[k][n]: N is the contiguous axis

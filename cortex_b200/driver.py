@@ -57,6 +57,14 @@ class Buffer:
         raw = (C.c_char * self.nbytes()).from_address(self.ptr)
         return np.frombuffer(raw, dtype=NUMPY_NAME[self.dtype], count=self.n)
 
+    def ipc_export(self):
+        """64-byte CUDA IPC handle of this device allocation (whole cb200_malloc'ed buffers only)."""
+        if self.host or self._owner is not None:
+            raise TypeError("only whole device allocations can be exported")
+        raw = C.create_string_buffer(64)
+        call("cb200_ipc_export", self.device.index, self.ptr, raw)
+        return raw.raw
+
     def release(self):
         if self._owner is not None or self._released:
             return
@@ -193,6 +201,21 @@ class B200Device:
         p = C.c_void_p()
         call("cb200_malloc", self.index, int(elem_count) * DTYPE_SIZE[elem_type], C.byref(p))
         return Buffer(p.value, elem_type, elem_count, self)
+
+    def enable_peer(self, peer):
+        """Let kernels on this device address `peer`'s memory (one process, several GPUs)."""
+        call("cb200_peer_enable", self.index, peer.index)
+
+    def ipc_import(self, handle, elem_count, elem_type):
+        """Map another process's exported allocation into this device's address space.  The
+        returned buffer is a borrowed view: close it with ipc_close(), never release()."""
+        p = C.c_void_p()
+        call("cb200_ipc_import", self.index, bytes(handle), C.byref(p))
+        buf = Buffer(p.value, elem_type, elem_count, self, owner=self)
+        return buf
+
+    def ipc_close(self, buffer):
+        call("cb200_ipc_close", self.index, buffer.ptr)
 
     def get_device(self):
         return self

@@ -97,6 +97,68 @@ def column_sharded_head(h, w_shard, b_shard, n_total, world_size, rank, group=No
     return ct.softmax(logits2d, logits2d)
 
 
+class PeerLogits:
+    """The full [B, n_total] logits buffer of every rank, mapped into this rank's address space
+    (CUDA IPC, one process per GPU), so that a column-sharded layer's GEMM can store its
+    [B, n_total/g] window straight into all of them: no separate all-gather, the NVLink transfer
+    overlaps the math tile by tile.  `torch.distributed` carries the 64-byte handles only."""
+
+    def __init__(self, device, B, n_total, world_size, rank, datatype="float", group=None):
+        import torch.distributed as dist
+        if n_total % world_size:
+            raise ValueError("column sharding needs n_total divisible by the world size")
+        self.device, self.B, self.n_total, self.world, self.rank = device, B, n_total, world_size, rank
+        self.per, self.datatype, self.group = n_total // world_size, datatype, group
+        self.local = device.allocate_device_buffer(B * n_total, datatype)
+        handles = [None] * world_size
+        dist.all_gather_object(handles, self.local.ipc_export(), group=group)
+        self.remote = {r: device.ipc_import(handles[r], B * n_total, datatype) for r in range(world_size) if r != rank}
+        self.tensor = ct.Tensor(device, dims.dimensions([B, n_total]), self.local)
+
+    def window_ptrs(self):
+        """Address of this rank's column window inside every OTHER rank's logits buffer."""
+        from ._lib import DTYPE_SIZE
+        off = self.rank * self.per * DTYPE_SIZE[self.datatype]
+        return [self.remote[r].ptr + off for r in sorted(self.remote)]
+
+    def close(self):
+        for buf in self.remote.values():
+            self.device.ipc_close(buf)
+        self.remote = {}
+
+
+def column_sharded_head_fused(h, w_shard, b_shard, exchange, fence):
+    """column_sharded_head without the all-gather and the re-layout: ONE fused kernel computes this
+    rank's logits window (bias added in the epilogue) and stores it into every rank's full logits
+    buffer over NVLink; `fence()` must then order all ranks (every rank's kernel finished) before
+    softmax! runs on the local full buffer.  Returns the [B, n_total] probabilities tensor."""
+    stream = ct.check_stream()
+    B, k = h.shape()
+    per, n_total = exchange.per, exchange.n_total
+    window = exchange.local.sub_buffer(exchange.rank * per, B * n_total - exchange.rank * per)
+    stream.gemm_bias_act_peers(window, n_total, False, True, 1.0, h.buffer, B, k, h.dimensions["strides"][0],
+                               w_shard.buffer, per, w_shard.dimensions["strides"][0], 0.0, b_shard.buffer, None,
+                               exchange.window_ptrs())
+    fence()
+    return ct.softmax(exchange.tensor, exchange.tensor)
+
+
+def stream_fence(stream, group=None):
+    """A cross-rank fence enqueued on the backend's own stream: a one-element all-reduce issued
+    with that stream current, so later kernels on it start only after every rank's earlier kernels
+    (and their peer stores) are complete.  No host synchronisation."""
+    import torch
+    import torch.distributed as dist
+    ext = torch.cuda.ExternalStream(stream.native_handle(), device=torch.device("cuda", stream.device.index))
+    token = torch.zeros(1, device=ext.device, dtype=torch.float32)
+
+    def fence():
+        with torch.cuda.stream(ext):
+            dist.all_reduce(token, group=group)
+
+    return fence
+
+
 class ShardedMLP:
     """Batch-sharded inference: this rank's slice of the batch through a replicated network."""
 

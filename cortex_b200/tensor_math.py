@@ -116,6 +116,17 @@ class CTensorMath:
                  b.ptr, int(b_col_count), int(b_colstride), float(beta), bias.ptr if bias is not None else None,
                  ACTIVATIONS[act])
 
+    def gemm_bias_act_peers(self, c, c_colstride, trans_a, trans_b, alpha, a, a_row_count, a_col_count, a_colstride, b,
+                            b_col_count, b_colstride, beta, bias, act, peer_ptrs):
+        """gemm_bias_act whose epilogue also stores the C window at the same position of every
+        address in `peer_ptrs` (other GPUs' memory)."""
+        import ctypes as C
+        arr = (C.c_void_p * max(1, len(peer_ptrs)))(*[int(p) for p in peer_ptrs])
+        self._tm("gemm_bias_act_peers", DTYPE_CODE[c.dtype], c.ptr, int(c_colstride), 1 if trans_a else 0,
+                 1 if trans_b else 0, float(alpha), a.ptr, int(a_row_count), int(a_col_count), int(a_colstride),
+                 b.ptr, int(b_col_count), int(b_colstride), float(beta), bias.ptr if bias is not None else None,
+                 ACTIVATIONS[act], len(peer_ptrs), arr)
+
     def bias_relu_rowstats(self, y, ldy, x, ldx, bias, rows, cols, rowmax, rowsum):
         self._tm("bias_relu_rowstats", DTYPE_CODE[y.dtype], y.ptr, int(ldy), x.ptr, int(ldx), bias.ptr, int(rows),
                  int(cols), rowmax.ptr if rowmax is not None else None, rowsum.ptr if rowsum is not None else None)

@@ -221,6 +221,29 @@ int cb200_gemm_bias_act(cb200_stream* s, int dtype, void* C, int64_t ldc, int tr
                         double alpha, const void* A, int64_t a_rows, int64_t a_cols, int64_t lda,
                         const void* B, int64_t b_cols, int64_t ldb, double beta,
                         const void* bias, int act);
+/* ---- multi-GPU extras (no counterpart: the reference has no multi-device code, README.md:48) ----
+ * The same fused GEMM whose epilogue ALSO stores every finished tile of the C window to the same
+ * row-major position (row*ldc + column from the given base) of up to 7 more buffers, typically the
+ * matching column window of the full output on every other GPU: a column-sharded layer then needs no
+ * separate all-gather, the transfer overlaps the math tile by tile (plain peer stores over NVLink).
+ * peer_C[d] must be addressable from the stream's device (cb200_peer_enable in one process, or a
+ * pointer from cb200_ipc_import across processes), have the pitch ldc, and be 16-byte aligned like C
+ * for the vector store path.  The caller orders the readers: the stores are complete when the
+ * stream reaches the point after this call (event / stream sync, then its own cross-GPU barrier). */
+#define CB200_MAX_PEERS 7
+int cb200_gemm_bias_act_peers(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b,
+                              double alpha, const void* A, int64_t a_rows, int64_t a_cols, int64_t lda,
+                              const void* B, int64_t b_cols, int64_t ldb, double beta,
+                              const void* bias, int act, int n_peers, void* const* peer_C);
+/* One process driving several GPUs: let `device` address `peer_device`'s memory. */
+int cb200_peer_enable(int device, int peer_device);
+/* One process per GPU: export a cb200_malloc'ed buffer as a 64-byte CUDA IPC handle; another
+ * process imports it on its own device (lazy peer access) and closes it when done. */
+#define CB200_IPC_HANDLE_BYTES 64
+int cb200_ipc_export(int device, void* device_ptr, unsigned char* handle_out);
+int cb200_ipc_import(int device, const unsigned char* handle, void** ptr_out);
+int cb200_ipc_close(int device, void* ptr);
+
 /* One pass over X[rows, cols] (pitch ldx): Y = max(X + bias, 0), rowmax[r] = max_j Y[r,j],
  * rowsum[r] = sum_j Y[r,j].  float/double.  Y may alias X; rowmax/rowsum may be NULL. */
 int cb200_bias_relu_rowstats(cb200_stream* s, int dtype, void* Y, int64_t ldy, const void* X,
