@@ -467,7 +467,7 @@ def run_b200(args, rank, world, local_rank):
         gemm_ms = float(np.mean([b.elapsed_ms_since(a) for a, b in gemm_events]))
 
         # ---- end to end: pinned host in -> H2D -> layers -> D2H, every step --------------------
-        chunk = min(8192, rows)
+        chunk = min(8192, max(2048, rows // 4))       # >= 4 chunks per shard so upload / compute / download overlap
         pipe = BatchPipeline(dev, net, WIDTH, CLASSES, chunk, dt)
         h2d = d2h = 0
         for _ in range(min(args.warmup, 2)):
@@ -475,7 +475,8 @@ def run_b200(args, rank, world, local_rank):
         barrier()
         t0 = pipe.compute.create_event(timing=True)
         for _ in range(args.steps):
-            h2d, d2h = pipe.run(x_host, y_host, rows)
+            h2d, d2h = pipe.run(x_host, y_host, rows, wait=False)    # steps stream back to back, drained once
+        pipe.drain()
         pipe.download.sync()
         t1 = pipe.compute.create_event(timing=True)
         t1.wait_for_event()

@@ -31,8 +31,10 @@ class BatchPipeline:
         self._slot_free = [None, None]     # event: compute finished reading in_slot[i]
         self._out_free = [None, None]      # event: download finished reading out_slot[i]
 
-    def run(self, host_in, host_out, rows):
-        """Returns (h2d_bytes, d2h_bytes).  Blocks until every result is in host_out."""
+    def run(self, host_in, host_out, rows, wait=True):
+        """Returns (h2d_bytes, d2h_bytes).  With wait=True blocks until every result is in host_out;
+        with wait=False returns once everything is enqueued (call drain() before reading host_out), so
+        that consecutive batches overlap: the first upload of the next batch runs under this one's tail."""
         es = {"float": 4, "double": 8}[self.datatype]
         h2d = d2h = 0
         n_chunks = (rows + self.chunk_rows - 1) // self.chunk_rows
@@ -63,9 +65,16 @@ class BatchPipeline:
                 self._out_free[slot] = self.download.create_event()
                 last_download = self._out_free[slot]
                 d2h += nr * self.out_width * es
-        if last_download is not None:
-            last_download.wait_for_event()
+        self._last_download = last_download
+        if wait:
+            self.drain()
         return h2d, d2h
+
+    def drain(self):
+        """Block until the results of every run() issued so far are in host memory."""
+        last = getattr(self, "_last_download", None)
+        if last is not None:
+            last.wait_for_event()
 
     def release(self):
         for s in [self.compute, self.download] + self.upload:
