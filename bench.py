@@ -320,7 +320,32 @@ def bench_mlp_128(drv, dev):
                 net.infer(x)
             ms = time_region(stream, lambda: net.infer(x), 200)
             res[label] = {"us_per_forward": round(ms * 1000.0, 1), "samples_per_s": round(128 / ms * 1000.0, 0)}
+        for _ in range(5):
+            net.infer_replayed(x)          # run, capture, replay
+        ms = time_region(stream, lambda: net.infer_replayed(x), 500)
+        res["fused_graph_replay"] = {"us_per_forward": round(ms * 1000.0, 1), "samples_per_s": round(128 / ms * 1000.0, 0)}
     return res
+
+
+def bench_mlp_layer(drv, dev, peaks):
+    """One hidden layer of the wide MLP on an 8192-row shard (the N=8 shard): the fused
+    gemm_bias_act launch the benchmark's roofline is quoted on, small enough for an ncu capture."""
+    from cortex_b200 import nn
+    from cortex_b200 import tensor as ct
+    stream = dev.create_stream()
+    rows = 8192
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        w = ct.to_tensor(make_weights()[0])
+        b = ct.new_tensor([WIDTH])
+        x = ct.to_tensor(make_input(0, rows))
+        out = ct.new_tensor([rows, WIDTH])
+        lin = nn.Linear(w, b)
+        for _ in range(3):
+            lin.forward_fused(x, out, "relu")
+        ms = time_region(stream, lambda: lin.forward_fused(x, out, "relu"), 10)
+    tf = 2.0 * rows * WIDTH * WIDTH / ms / 1e9
+    return {"rows": rows, "ms": round(ms, 4), "tflops": round(tf, 1),
+            "algorithmic_bytes": rows * WIDTH * 4 * 2 + WIDTH * WIDTH * 4 + WIDTH * 4}
 
 
 def bench_mlp_f64(drv, dev):
@@ -559,7 +584,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--dtype", default="float", choices=["float", "double"],
                     help="float = the headline workload; double = its fp64 variant (DMMA gemm)")
-    ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128"],
+    ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128", "mlplayer"],
                     help="mlp = the benchmark; gemm4096 / eltwise = the small single-purpose runs used for ncu captures")
     args = ap.parse_args()
     if args.case != "mlp":
@@ -569,7 +594,7 @@ def main():
         peaks = measured_peaks()
         fns = {"gemm4096": lambda: bench_gemm_4096(drv, dev, peaks), "eltwise": lambda: bench_eltwise(drv, dev, peaks),
                "conv": lambda: bench_conv(drv, dev, peaks), "gemm4096f64": lambda: bench_gemm_f64(drv, dev),
-               "mlp128": lambda: bench_mlp_128(drv, dev)}
+               "mlp128": lambda: bench_mlp_128(drv, dev), "mlplayer": lambda: bench_mlp_layer(drv, dev, peaks)}
         print(json.dumps({args.case: fns[args.case]()}), flush=True)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

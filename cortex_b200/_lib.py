@@ -84,6 +84,10 @@ SIGNATURES = {
     "cb200_gemm_bias_act": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i],
     "cb200_gemm_bias_act_peers": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i,
                                   _i, C.POINTER(_vp)],
+    "cb200_graph_capture_begin": [_vp],
+    "cb200_graph_capture_end": [_vp, C.POINTER(_vp)],
+    "cb200_graph_launch": [_vp, _vp],
+    "cb200_graph_destroy": [_vp],
     "cb200_peer_enable": [_i, _i],
     "cb200_ipc_export": [_i, _vp, C.c_char_p],
     "cb200_ipc_import": [_i, C.c_char_p, C.POINTER(_vp)],

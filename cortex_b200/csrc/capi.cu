@@ -97,6 +97,7 @@ int cb200_stream_create(int device, cb200_stream** out) {
   s->scratch = nullptr;
   s->scratch_bytes = 0;
   s->launches.store(0);
+  s->capture_start = -1;
   cudaError_t e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, device);
   if (e == cudaSuccess) e = cudaMalloc((void**)&s->status_dev, 2 * sizeof(int));
@@ -180,6 +181,57 @@ int cb200_memcpy_d2d(cb200_stream* s, void* dst, const void* src, size_t bytes) 
   CB_REQUIRE(s && (bytes == 0 || (dst && src)), "memcpy_d2d: null argument");
   DeviceGuard g(s->device);
   CB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s->stream));
+  return CB200_OK;
+}
+
+// ---- stream capture: a launch-bound sequence (a small-batch forward pass) replayed as one graph ----
+int cb200_graph_capture_begin(cb200_stream* s) {
+  CB_REQUIRE(s, "graph_capture_begin: null stream");
+  CB_REQUIRE(s->capture_start < 0, "graph_capture_begin: this stream is already capturing");
+  DeviceGuard g(s->device);
+  CB_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+  s->capture_start = s->launches.load();
+  return CB200_OK;
+}
+
+int cb200_graph_capture_end(cb200_stream* s, cb200_graph** out) {
+  CB_REQUIRE(s && out, "graph_capture_end: null argument");
+  CB_REQUIRE(s->capture_start >= 0, "graph_capture_end: this stream is not capturing");
+  DeviceGuard g(s->device);
+  const int64_t kernels = s->launches.load() - s->capture_start;
+  s->capture_start = -1;
+  s->launches.fetch_sub(kernels);     // the captured launches did not run
+  cudaGraph_t graph = nullptr;
+  CB_CUDA(cudaStreamEndCapture(s->stream, &graph));
+  cb200_graph* gr = new (std::nothrow) cb200_graph();
+  if (!gr) { cudaGraphDestroy(graph); cb200_set_error("graph_capture_end: out of host memory"); return CB200_ERR_NOMEM; }
+  gr->device = s->device; gr->graph = graph; gr->exec = nullptr; gr->kernels = kernels;
+  cudaError_t err = cudaGraphInstantiate(&gr->exec, graph, 0);
+  if (err != cudaSuccess) {
+    cudaGraphDestroy(graph);
+    delete gr;
+    return cb200_cuda_fail(err, "cudaGraphInstantiate", __FILE__, __LINE__);
+  }
+  *out = gr;
+  return CB200_OK;
+}
+
+int cb200_graph_launch(cb200_graph* gr, cb200_stream* s) {
+  CB_REQUIRE(gr && s, "graph_launch: null argument");
+  CB_REQUIRE(gr->device == s->device, "graph_launch: graph captured on device %d, stream is on device %d", gr->device,
+             s->device);
+  DeviceGuard g(s->device);
+  CB_CUDA(cudaGraphLaunch(gr->exec, s->stream));
+  s->launches.fetch_add(gr->kernels);
+  return CB200_OK;
+}
+
+int cb200_graph_destroy(cb200_graph* gr) {
+  if (!gr) return CB200_OK;
+  DeviceGuard g(gr->device);
+  if (gr->exec) cudaGraphExecDestroy(gr->exec);
+  if (gr->graph) cudaGraphDestroy(gr->graph);
+  delete gr;
   return CB200_OK;
 }
 

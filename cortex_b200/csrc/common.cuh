@@ -17,6 +17,15 @@ struct cb200_stream {
   void* scratch;       // lazily grown per-stream device workspace
   size_t scratch_bytes;
   std::atomic<int64_t> launches;
+  int64_t capture_start;   // launch counter when the running capture began; -1 when not capturing
+};
+
+// A captured sequence of this library's launches on one stream, replayable with one call.
+struct cb200_graph {
+  int device;
+  cudaGraph_t graph;
+  cudaGraphExec_t exec;
+  int64_t kernels;      // launches recorded while capturing (added to the stream's counter per replay)
 };
 
 struct cb200_event {

@@ -13,6 +13,17 @@
 // split, and run the lo pass over the W tile that TMA delivers (K-major, 64-byte
 // swizzle).  MMA issue, TMEM accumulators (main + cross terms), bounded waits and the
 // NCHW-scatter epilogue are as in gemm_tf32x3.cu.
+//
+// Two gather schemes share the kernel (template flag TAP):
+//  * TAP = false, any geometry: K runs in the reference's order (c, ky, kx); every gathered
+//    element decodes its own (c, ky, kx).
+//  * TAP = true, C_in a multiple of 16: K runs tap-major, k' = (ky*kW + kx)*C_in + c, so a 16-wide
+//    k-block is ONE filter tap and 16 consecutive channels: the bounds test and the input offset
+//    are computed once per k-block and the 8 elements of a thread are loads at a constant stride
+//    (one input plane apart).  The weights are permuted to that order, and split into hi / lo,
+//    by a small kernel into the stream's scratch ([2][C_out][K] floats) before the launch, so the
+//    main kernel has no W pass at all: TMA delivers both W tiles.  Only the order of the fp32
+//    summation over k differs from the reference order.
 #include "common.cuh"
 #include "sm100.cuh"
 #include <mutex>
@@ -57,9 +68,24 @@ __device__ __forceinline__ float conv_lo_part(float x) {
   return ((xb & 0x7f800000u) == 0x7f800000u) ? 0.f : lo;
 }
 
-template <int BN>
+// W[cout][c*khkw + t]  ->  hi[cout][t*cin + c] (raw value), lo[cout][t*cin + c] (x - trunc_tf32(x))
+__global__ void __launch_bounds__(256)
+conv_prep_weights_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int cout, int cin,
+                         int khkw) {
+  const int K = cin * khkw;
+  const int total = cout * K;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int co = i / K, kp = i - co * K;
+    const int t = kp / cin, c = kp - t * cin;
+    const float x = w[(long long)co * K + c * khkw + t];
+    hi[i] = x;
+    lo[i] = conv_lo_part(x);
+  }
+}
+
+template <int BN, bool TAP>
 __global__ void __launch_bounds__(CONV_THREADS, ConvCfg<BN>::CTAS_PER_SM)
-conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
+conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWlo, ConvParams p) {
   typedef ConvCfg<BN> Cfg;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int A_TILE = Cfg::A_TILE, B_TILE = Cfg::B_TILE, RAW = A_TILE + B_TILE;
@@ -97,7 +123,10 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == GATHER_WARPS && lane == 0) tma_prefetch_desc(&tmW);
+  if (warp == GATHER_WARPS && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    if (TAP) tma_prefetch_desc(&tmWlo);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -111,8 +140,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
         const int s = i % STAGES, ph = (i / STAGES) & 1;
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) break;
         const uint32_t full = bar_full + 8 * s;
-        mbar_arrive_expect_tx(full, B_TILE);
+        mbar_arrive_expect_tx(full, TAP ? 2 * B_TILE : B_TILE);
         tma_load_2d(smem_base + s * Cfg::STAGE + A_TILE, &tmW, i * CBK, n0, full);
+        if (TAP) tma_load_2d(smem_base + s * Cfg::STAGE + RAW + A_TILE, &tmWlo, i * CBK, n0, full);
         issued = i + 1;
       }
       if (*abort_flag) {
@@ -129,6 +159,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
       for (int i = 0; i < nkb; ++i) {
         const int s = i % STAGES, ph = (i / STAGES) & 1;
         if (!mbar_wait(bar_conv + 8 * s, ph, abort_flag, p.status, 600 + s)) break;
+        if (TAP && !mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 650 + s)) break;
         tc_fence_after();
         const uint32_t a_hi = smem_base + s * Cfg::STAGE, b_hi = a_hi + A_TILE;
         const uint32_t a_lo = a_hi + RAW, b_lo = b_hi + RAW;
@@ -209,6 +240,46 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
     };
     bool ok = true;
     float vn[8];
+    if (TAP) {
+      // ---- tap-major gather: k-block i = tap (i / cblocks), channels 16*(i % cblocks) + khalf*8 .. +7 ----
+      const int cblocks = p.cin >> 4;
+      // shared-memory offsets of this thread's 8 k-rows (row = khalf*8 + j): 128 B per row, the
+      // 32-byte chunk XOR-ed with (row & 3) = (j & 3)
+      const uint32_t row0 = box_off + (uint32_t)khalf * 1024;
+      const uint32_t sw0 = row0 + ((chunk ^ 0u) << 5), sw1 = row0 + ((chunk ^ 1u) << 5),
+                     sw2 = row0 + ((chunk ^ 2u) << 5), sw3 = row0 + ((chunk ^ 3u) << 5);
+      const long long img_off = (long long)img * p.cin * in_hw + (long long)khalf * 8 * in_hw + pix_off;
+      int tap = 0, cb = 0, ky = 0, kx = 0;
+      auto fetch_tap = [&](float (&v)[8]) {
+        const int iy = iy0 + ky, ix = ix0 + kx;
+        const bool valid = m_ok && iy >= 0 && iy < p.in_h && ix >= 0 && ix < p.in_w;
+        const float* src = p.in + (img_off + (long long)cb * 16 * in_hw + ky * p.in_w + kx);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = valid ? __ldg(src + (long long)j * in_hw) : 0.f;
+        if (++cb == cblocks) { cb = 0; ++tap; if (++kx == p.kw) { kx = 0; ++ky; } }
+      };
+      if (nkb > 0) fetch_tap(vn);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES, ph = (i / STAGES) & 1;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = vn[j];
+        if (i + 1 < nkb) fetch_tap(vn);
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 700 + s)) { ok = false; break; }
+        uint8_t* a_hi = smem + s * Cfg::STAGE;
+        uint8_t* a_lo = a_hi + RAW;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t off = ((j & 3) == 0 ? sw0 : (j & 3) == 1 ? sw1 : (j & 3) == 2 ? sw2 : sw3) + j * 128;
+          *reinterpret_cast<float*>(a_hi + off) = v[j];
+          *reinterpret_cast<float*>(a_lo + off) = conv_lo_part(v[j]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_conv + 8 * s);
+      }
+      (void)tap;
+    } else {
     if (nkb > 0) fetch(0, vn);
     for (int i = 0; i < nkb; ++i) {
       const int s = i % STAGES, ph = (i / STAGES) & 1;
@@ -240,6 +311,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, ConvParams p) {
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_conv + 8 * s);
+    }
     }
     if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 900);
     ok = __all_sync(0xffffffffu, ok);
@@ -305,18 +377,32 @@ EncodeTiledFn conv_encode_fn() {
   return fn;
 }
 
-template <int BN>
-int launch_conv(cb200_stream* s, const CUtensorMap& tmW, const ConvParams& p) {
+template <int BN, bool TAP>
+int launch_conv(cb200_stream* s, const CUtensorMap& tmW, const CUtensorMap& tmWlo, const ConvParams& p) {
   typedef ConvCfg<BN> Cfg;
   static std::once_flag once[64];
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[s->device & 63], [&] {
-    attr_err = cudaFuncSetAttribute(conv_igemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    attr_err = cudaFuncSetAttribute(conv_igemm_kernel<BN, TAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
   });
   if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
   long long tiles = (long long)((p.M + CBM - 1) / CBM) * ((p.cout + BN - 1) / BN);
-  conv_igemm_kernel<BN><<<(unsigned)tiles, CONV_THREADS, Cfg::SMEM, s->stream>>>(tmW, p);
+  conv_igemm_kernel<BN, TAP><<<(unsigned)tiles, CONV_THREADS, Cfg::SMEM, s->stream>>>(tmW, tmWlo, p);
   CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+int encode_weights(CUtensorMap* tm, const float* w, int K, int cout, int BN) {
+  EncodeTiledFn fn = conv_encode_fn();
+  if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
+  cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)cout};
+  cuuint64_t gstride[1] = {(cuuint64_t)K * 4};
+  cuuint32_t box[2] = {(cuuint32_t)CBK, (cuuint32_t)BN};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)w, gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { cb200_set_error("cuTensorMapEncodeTiled failed with %d for the weights", (int)r); return CB200_ERR_CUDA; }
   return CB200_OK;
 }
 
@@ -333,18 +419,35 @@ int cb200_conv_igemm_launch(cb200_stream* s, float* out, const float* in, const 
   p.kh = kh; p.kw = kw; p.pad_x = pad_x; p.pad_y = pad_y; p.stride_x = stride_x; p.stride_y = stride_y;
   p.cout = cout; p.K = cin * kh * kw; p.M = batch * out_h * out_w; p.out_alpha = out_alpha; p.status = s->status_dev;
   const int BN = cout > 128 ? 256 : (cout > 64 ? 128 : 64);
-  EncodeTiledFn fn = conv_encode_fn();
-  if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
-  CUtensorMap tmW;
-  cuuint64_t gdim[2] = {(cuuint64_t)p.K, (cuuint64_t)cout};
-  cuuint64_t gstride[1] = {(cuuint64_t)p.K * 4};
-  cuuint32_t box[2] = {(cuuint32_t)CBK, (cuuint32_t)BN};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)w, gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) { cb200_set_error("cuTensorMapEncodeTiled failed with %d for the weights", (int)r); return CB200_ERR_CUDA; }
-  if (BN == 256) return launch_conv<256>(s, tmW, p);
-  if (BN == 128) return launch_conv<128>(s, tmW, p);
-  return launch_conv<64>(s, tmW, p);
+  CUtensorMap tmW, tmWlo;
+  int rc;
+  const long long in_elems = (long long)batch * cin * in_h * in_w;
+  if ((cin % 16) == 0 && in_elems < 2147483647LL) {
+    // tap-major scheme: permuted hi / lo copies of the weights in the stream's scratch
+    void* scratch = nullptr;
+    const size_t wbytes = (size_t)cout * p.K * sizeof(float);
+    rc = cb200_scratch(s, 2 * wbytes, &scratch);
+    if (rc) return rc;
+    float* w_hi = (float*)scratch;
+    float* w_lo = w_hi + (size_t)cout * p.K;
+    const int total = cout * p.K;
+    int blocks = (total + 255) / 256;
+    if (blocks > s->sm_count * 8) blocks = s->sm_count * 8;
+    conv_prep_weights_kernel<<<blocks, 256, 0, s->stream>>>(w, w_hi, w_lo, cout, cin, kh * kw);
+    CB_LAUNCH_CHECK(s);
+    rc = encode_weights(&tmW, w_hi, p.K, cout, BN);
+    if (rc) return rc;
+    rc = encode_weights(&tmWlo, w_lo, p.K, cout, BN);
+    if (rc) return rc;
+    if (BN == 256) return launch_conv<256, true>(s, tmW, tmWlo, p);
+    if (BN == 128) return launch_conv<128, true>(s, tmW, tmWlo, p);
+    return launch_conv<64, true>(s, tmW, tmWlo, p);
+  }
+  rc = encode_weights(&tmW, w, p.K, cout, BN);
+  if (rc) return rc;
+  tmWlo = tmW;
+  if (BN == 256) return launch_conv<256, false>(s, tmW, tmWlo, p);
+  if (BN == 128) return launch_conv<128, false>(s, tmW, tmWlo, p);
+  return launch_conv<64, false>(s, tmW, tmWlo, p);
 }
+

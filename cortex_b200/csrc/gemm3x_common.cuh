@@ -23,6 +23,7 @@ struct GemmParams {
   int store_mode;
   int hw;              // STORE_NCHW: pixels per image; C[(m / hw) * N * hw + n * hw + m % hw]
   int flags;
+  int group_n;         // column tiles per rasterisation group (>= 1)
   int* status;
   // Row-major store only: every finished tile is also written to the same (row, column) position of
   // these buffers, which may live in other GPUs' memory (plain peer stores over NVLink).

@@ -66,8 +66,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Tile order: column tiles are taken in groups of p.group_n; inside a group the CTAs sweep all row
+  // tiles, so the group's B panel (group_n * BN * K floats) stays in L2 while A streams past it once
+  // per group.
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int grp = blockIdx.x / (tiles_m * p.group_n);
+  const int rem = blockIdx.x - grp * tiles_m * p.group_n;
+  const int in_grp = min(p.group_n, tiles_n - grp * p.group_n);
+  const int tile_m = rem / in_grp, tile_n = grp * p.group_n + rem % in_grp;
   const int m0 = tile_m * BM, n0 = tile_n * BN;
   const int nkb = (p.K + BK - 1) / BK;
 
@@ -298,7 +305,18 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   p.a_mn_major = trans_a ? 1 : 0;   // op(A)[m][k] = A[k][m]: M is the contiguous axis
   p.b_mn_major = trans_b ? 0 : 1;   // op(B)[k][n] = B[k][n]: N is the contiguous axis
   p.store_mode = store_mode; p.hw = hw > 0 ? hw : 1; p.flags = flags; p.status = s->status_dev;
-  const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  // widest tile that still gives every SM a CTA (small problems are latency-bound: more, narrower
+  // tiles finish sooner than two wide ones)
+  int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  const long long tiles_m = (M + BM - 1) / BM;
+  while (BN > 64 && tiles_m * ((N + BN - 1) / BN) < s->sm_count) BN >>= 1;
+  const int tiles_n = (N + BN - 1) / BN;
+  const long long panel_bytes = (long long)BN * K * 4;          // one column tile's share of B
+  p.group_n = tiles_n;
+  if (tiles_n * panel_bytes > (40ll << 20)) {
+    long long g = (32ll << 20) / panel_bytes;
+    p.group_n = (int)(g < 1 ? 1 : (g > tiles_n ? tiles_n : g));
+  }
   constexpr int BK = 16;
   const CUtensorMapSwizzle kswz = CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap tmA, tmB;

@@ -105,6 +105,27 @@ class B200Event:
             pass
 
 
+class B200Graph:
+    """A captured launch sequence (B200Stream.begin_capture / end_capture), replayed with launch()."""
+
+    def __init__(self, handle):
+        self.handle = handle
+
+    def launch(self, stream):
+        call("cb200_graph_launch", self.handle, stream.handle)
+
+    def release(self):
+        if self.handle:
+            call("cb200_graph_destroy", self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
 class B200Stream(CTensorMath):
     """CudaStream of the reference + its TensorMath implementation
     (extend-type CudaStream, src/cortex/compute/cuda/tensor_math.clj:289)."""
@@ -124,6 +145,15 @@ class B200Stream(CTensorMath):
 
     def get_driver(self):
         return self.device.driver
+
+    # --- launch-sequence capture -----------------------------------------------
+    def begin_capture(self):
+        call("cb200_graph_capture_begin", self.handle)
+
+    def end_capture(self):
+        h = C.c_void_p()
+        call("cb200_graph_capture_end", self.handle, C.byref(h))
+        return B200Graph(h.value)
 
     # --- PStream ------------------------------------------------------------------
     def copy_host_to_device(self, host_buffer, host_offset, device_buffer, device_offset, elem_count):

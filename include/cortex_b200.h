@@ -94,6 +94,7 @@ typedef struct cb200_conv_desc {
 
 typedef struct cb200_stream cb200_stream;  /* device + CUDA stream + status word */
 typedef struct cb200_event cb200_event;
+typedef struct cb200_graph cb200_graph;  /* a captured launch sequence */
 
 /* ---- errors -------------------------------------------------------------- */
 /* check-cuda-error: src/cortex/compute/cuda/driver.clj:40-49 */
@@ -221,6 +222,18 @@ int cb200_gemm_bias_act(cb200_stream* s, int dtype, void* C, int64_t ldc, int tr
                         double alpha, const void* A, int64_t a_rows, int64_t a_cols, int64_t lda,
                         const void* B, int64_t b_cols, int64_t ldb, double beta,
                         const void* bias, int act);
+/* ---- launch-sequence capture (no counterpart in the protocol) ----------------
+ * Small batches are launch-bound (the MNIST-shaped 128-row forward is three kernels of a few
+ * microseconds each): everything enqueued on `s` by this library between capture_begin and
+ * capture_end is recorded instead of run, and replayed by ONE cb200_graph_launch.  Rules: run the
+ * sequence once normally first (scratch buffers and kernel attributes are set up on first use and
+ * must not be created while capturing); no sync / event_wait / malloc / free between begin and end;
+ * the graph replays the same buffers, shapes and scalars; destroy it before freeing those buffers. */
+int cb200_graph_capture_begin(cb200_stream* s);
+int cb200_graph_capture_end(cb200_stream* s, cb200_graph** out);
+int cb200_graph_launch(cb200_graph* g, cb200_stream* s);
+int cb200_graph_destroy(cb200_graph* g);
+
 /* ---- multi-GPU extras (no counterpart: the reference has no multi-device code, README.md:48) ----
  * The same fused GEMM whose epilogue ALSO stores every finished tile of the C window to the same
  * row-major position (row*ldc + column from the given base) of up to 7 more buffers, typically the

@@ -96,7 +96,11 @@ def test_mlp_matches_oracle(b200_driver, oracle_driver, datatype, fused):
 @pytest.mark.parametrize("datatype", ["float", "double"])
 def test_conv_matches_oracle(b200_driver, oracle_driver, datatype):
     for args in (dict(batch=2, cin=4, hw=9, cout=5), dict(batch=2, cin=3, hw=8, cout=4, k=2, pad=0, stride=2),
-                 dict(batch=4, cin=64, hw=28, cout=64)):
+                 dict(batch=4, cin=64, hw=28, cout=64),
+                 # channel counts that are multiples of 16 take the tap-major gather
+                 dict(batch=3, cin=16, hw=13, cout=40, k=5, pad=2),
+                 dict(batch=2, cin=32, hw=17, cout=130, k=3, pad=1, stride=2),
+                 dict(batch=1, cin=48, hw=10, cout=100, k=1, pad=0)):
         run, ref = pc.conv_case(datatype, bias_scale=0.1, **args)
         gpu, cpu = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
         assert pc.rel_err(gpu, cpu) <= pc.TOL[datatype]
@@ -151,3 +155,38 @@ def test_batch_pipeline_matches_resident_inference(b200_driver):
     got = host_out.as_numpy().reshape(rows, classes)
     assert np.array_equal(got, resident)
     assert np.abs(got.sum(axis=1) - 1.0).max() < 1e-5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fused", [False, True])
+def test_graph_replay_matches_direct_inference(fused):
+    """The captured launch sequence replays to the same bits as the direct calls, also after the
+    input buffer's contents change."""
+    import numpy as np
+    from cortex_b200 import nn
+    from cortex_b200 import tensor as ct
+    from cortex_b200.driver import driver
+    dev = driver().default_device()
+    stream = dev.create_stream()
+    rng = np.random.default_rng(31)
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        w1 = ct.to_tensor((rng.standard_normal((500, 784)) * 0.05).astype(np.float32))
+        w2 = ct.to_tensor((rng.standard_normal((10, 500)) * 0.06).astype(np.float32))
+        b1 = ct.to_tensor((rng.standard_normal(500) * 0.1).astype(np.float32))
+        b2 = ct.to_tensor((rng.standard_normal(10) * 0.1).astype(np.float32))
+        net = nn.MLP([(w1, b1, "relu"), (w2, b2, "softmax")], fused=fused)
+        x = ct.to_tensor(rng.random((128, 784), dtype=np.float32))
+        launches_per_forward = None
+        for trial in range(4):
+            if trial:
+                ct.assign(x, ct.to_tensor(rng.random((128, 784), dtype=np.float32)))
+            before = stream.launch_count()
+            direct = ct.to_array(net.infer(x)).copy()
+            per = stream.launch_count() - before
+            before = stream.launch_count()
+            replayed = ct.to_array(net.infer_replayed(x)).copy()
+            if trial >= 2:      # trial 0 runs directly, trial 1 captures and replays once
+                assert stream.launch_count() - before == per
+            assert np.array_equal(direct, replayed)
+            launches_per_forward = per
+        assert launches_per_forward >= 3
