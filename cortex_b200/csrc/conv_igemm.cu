@@ -134,16 +134,21 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
   if (warp == GATHER_WARPS) {
     // ---------------------------- TMA producer: W tiles ----------------------------
-    if (lane == 0) {
+    // the whole warp runs the loop (warp-uniform control flow); one elected lane issues
+    {
       int issued = 0;
+      int s = 0;
+      uint32_t ph = 0;
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES, ph = (i / STAGES) & 1;
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) break;
         const uint32_t full = bar_full + 8 * s;
-        mbar_arrive_expect_tx(full, TAP ? 2 * B_TILE : B_TILE);
-        tma_load_2d(smem_base + s * Cfg::STAGE + A_TILE, &tmW, i * CBK, n0, full);
-        if (TAP) tma_load_2d(smem_base + s * Cfg::STAGE + RAW + A_TILE, &tmWlo, i * CBK, n0, full);
+        if (elect_one()) {
+          mbar_arrive_expect_tx(full, TAP ? 2 * B_TILE : B_TILE);
+          tma_load_2d(smem_base + s * Cfg::STAGE + A_TILE, &tmW, i * CBK, n0, full);
+          if (TAP) tma_load_2d(smem_base + s * Cfg::STAGE + RAW + A_TILE, &tmWlo, i * CBK, n0, full);
+        }
         issued = i + 1;
+        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
       if (*abort_flag) {
         for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
@@ -153,34 +158,44 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
   } else if (warp == GATHER_WARPS + 1) {
     // ---------------------------- MMA issuer ---------------------------------------
-    if (lane == 0) {
+    // the whole warp runs the loop; one elected lane issues the MMAs and commits
+    {
       const uint32_t idesc = make_idesc_tf32(CBM, BN, 1 /*A: pixels contiguous*/, 0 /*W: K contiguous*/);
       uint32_t accumulate[2] = {0, 0};
+      // descriptors of stage 0, k-step 0 as (low, high) words; stages and k-steps only move the
+      // start-address field of the low word.
+      // A: 32-pixel boxes 2048 B apart, 4-k-row atoms 512 B apart, 1024 B per k-step
+      // W: 64-byte rows, 8-row groups 512 B apart, 32 B per k-step
+      const uint64_t d_a = make_smem_desc(smem_base, 2048, 512, SWZ_128B_BASE32B);
+      const uint64_t d_b = make_smem_desc(smem_base + A_TILE, 16, 512, SWZ_64B);
+      const uint32_t a_hiw = (uint32_t)(d_a >> 32), b_hiw = (uint32_t)(d_b >> 32);
+      const uint32_t a_low0 = (uint32_t)d_a, b_low0 = (uint32_t)d_b;
+      constexpr uint32_t LO_TILE = RAW >> 4, STAGE_STEP = Cfg::STAGE >> 4;
+      int s = 0;
+      uint32_t ph = 0, stage_off = 0;
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES, ph = (i / STAGES) & 1;
         if (!mbar_wait(bar_conv + 8 * s, ph, abort_flag, p.status, 600 + s)) break;
         if (TAP && !mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 650 + s)) break;
         tc_fence_after();
-        const uint32_t a_hi = smem_base + s * Cfg::STAGE, b_hi = a_hi + A_TILE;
-        const uint32_t a_lo = a_hi + RAW, b_lo = b_hi + RAW;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < CBK / 8; ++kk) {
-          // A: 32-pixel boxes 2048 B apart, 4-k-row atoms 512 B apart, 1024 B per k-step
-          const uint64_t dah = make_smem_desc(a_hi + kk * 1024, 2048, 512, SWZ_128B_BASE32B);
-          const uint64_t dal = make_smem_desc(a_lo + kk * 1024, 2048, 512, SWZ_128B_BASE32B);
-          // W: 64-byte rows, 8-row groups 512 B apart, 32 B per k-step
-          const uint64_t dbh = make_smem_desc(b_hi + kk * 32, 16, 512, SWZ_64B);
-          const uint64_t dbl = make_smem_desc(b_lo + kk * 32, 16, 512, SWZ_64B);
-          const int set = Cfg::ACC_SETS == 2 ? kk : 0;
-          const uint32_t tmem_main = tmem_base + set * 2 * BN, tmem_cross = tmem_main + BN;
-          mma_tf32_ss(tmem_cross, dal, dbh, idesc, accumulate[set]);
-          mma_tf32_ss(tmem_main, dah, dbh, idesc, accumulate[set]);
-          mma_tf32_ss(tmem_cross, dah, dbl, idesc, 1);
-          accumulate[set] = 1;
+          for (int kk = 0; kk < CBK / 8; ++kk) {
+            const uint32_t al = a_low0 + stage_off + kk * (1024 >> 4), bl = b_low0 + stage_off + kk * (32 >> 4);
+            const int set = Cfg::ACC_SETS == 2 ? kk : 0;
+            const uint32_t tmem_main = tmem_base + set * 2 * BN, tmem_cross = tmem_main + BN;
+            const uint32_t acc = (Cfg::ACC_SETS == 1 && kk) ? 1u : accumulate[set];
+            mma_tf32_ss_words(tmem_cross, al + LO_TILE, a_hiw, bl, b_hiw, idesc, acc);
+            mma_tf32_ss_words(tmem_main, al, a_hiw, bl, b_hiw, idesc, acc);
+            mma_tf32_ss_words(tmem_cross, al, a_hiw, bl + LO_TILE, b_hiw, idesc, 1);
+          }
+          mma_commit(bar_empty + 8 * s);
         }
-        mma_commit(bar_empty + 8 * s);
+        accumulate[0] = accumulate[1] = 1;
+        __syncwarp();
+        if (++s == STAGES) { s = 0; ph ^= 1; stage_off = 0; } else { stage_off += STAGE_STEP; }
       }
-      mma_commit(bar_acc);
+      if (elect_one()) mma_commit(bar_acc);
+      __syncwarp();
       if (*abort_flag) {
         for (int it = 0; it < (1 << 16); ++it)
           if (mbar_try_wait(bar_acc, 0)) break;

@@ -57,6 +57,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   typedef TileCfg<BN, BK> Cfg;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int A_TILE = Cfg::A_TILE;
+  // lo pass by one warp per k-block instead of all warps on each: only where warps and stages pair up
+  constexpr bool WARP_PER_KBLOCK = BN <= 64 && STAGES == NUM_CONV_WARPS;
   constexpr int BOX = BK * 128;          // bytes of one 32 x BK MN-major TMA box
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -85,7 +87,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_conv + 8 * s, NUM_CONV_WARPS);
+      mbar_init(bar_conv + 8 * s, WARP_PER_KBLOCK ? 1 : NUM_CONV_WARPS);
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_acc, 1);
@@ -107,28 +109,33 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
   if (warp == NUM_CONV_WARPS) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    // the whole warp runs the loop; one elected lane issues
+    {
       int issued = 0;
+      int s = 0;
+      uint32_t ph = 0;
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES, ph = (i / STAGES) & 1;
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 100 + s)) break;
         const uint32_t full = bar_full + 8 * s;
         const uint32_t a_dst = smem_base + s * Cfg::STAGE, b_dst = a_dst + A_TILE;
         const int k0 = i * BK;
-        mbar_arrive_expect_tx(full, Cfg::RAW);
-        if (!p.a_mn_major) {
-          tma_load_2d(a_dst, &tmA, k0, m0, full);
-        } else {
+        if (elect_one()) {
+          mbar_arrive_expect_tx(full, Cfg::RAW);
+          if (!p.a_mn_major) {
+            tma_load_2d(a_dst, &tmA, k0, m0, full);
+          } else {
 #pragma unroll
-          for (int j = 0; j < BM / 32; ++j) tma_load_2d(a_dst + j * BOX, &tmA, m0 + 32 * j, k0, full);
-        }
-        if (!p.b_mn_major) {
-          tma_load_2d(b_dst, &tmB, k0, n0, full);
-        } else {
+            for (int j = 0; j < BM / 32; ++j) tma_load_2d(a_dst + j * BOX, &tmA, m0 + 32 * j, k0, full);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d(b_dst, &tmB, k0, n0, full);
+          } else {
 #pragma unroll
-          for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * BOX, &tmB, n0 + 32 * j, k0, full);
+            for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * BOX, &tmB, n0 + 32 * j, k0, full);
+          }
         }
         issued = i + 1;
+        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
       if (*abort_flag) {
         // let copies already issued land before this CTA gives its shared memory back
@@ -139,7 +146,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
   } else if (warp == NUM_CONV_WARPS + 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    // the whole warp runs the loop; one elected lane issues the MMAs and commits
+    {
       const uint32_t idesc = make_idesc_tf32(BM, BN, p.a_mn_major, p.b_mn_major);
       // K-major: rows of BK*4 bytes (128- or 64-byte swizzle), 8-row groups 8*BK*4 B apart, 32 B per
       // k-step inside the row.  MN-major: 32-element blocks along M/N one TMA box apart, 4-k-row
@@ -151,31 +159,41 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const uint32_t a_sw = p.a_mn_major ? SWZ_128B_BASE32B : K_SWZ, b_sw = p.b_mn_major ? SWZ_128B_BASE32B : K_SWZ;
       const uint32_t a_kstep = p.a_mn_major ? 1024u : 32u, b_kstep = p.b_mn_major ? 1024u : 32u;
       const uint32_t tmem_main = tmem_base, tmem_cross = tmem_base + BN;
+      // descriptors of stage 0, k-step 0 as (low, high) words; stages and k-steps only move the
+      // start-address field of the low word
+      const uint64_t d_a = make_smem_desc(smem_base, a_lbo, a_sbo, a_sw);
+      const uint64_t d_b = make_smem_desc(smem_base + A_TILE, b_lbo, b_sbo, b_sw);
+      const uint32_t a_hiw = (uint32_t)(d_a >> 32), b_hiw = (uint32_t)(d_b >> 32);
+      const uint32_t a_low0 = (uint32_t)d_a, b_low0 = (uint32_t)d_b;
+      constexpr uint32_t LO_TILE = Cfg::RAW >> 4, STAGE_STEP = Cfg::STAGE >> 4;
+      const uint32_t a_step = a_kstep >> 4, b_step = b_kstep >> 4;
+      const bool one_term = (p.flags & FLAG_ONE_TERM) != 0;
       uint32_t acc_cross = 0;
       uint32_t accumulate = 0;
+      int s = 0;
+      uint32_t ph = 0, stage_off = 0;
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES, ph = (i / STAGES) & 1;
         if (!mbar_wait(bar_conv + 8 * s, ph, abort_flag, p.status, 200 + s)) break;
         tc_fence_after();
-        const uint32_t a_hi = smem_base + s * Cfg::STAGE, b_hi = a_hi + A_TILE;
-        const uint32_t a_lo = a_hi + Cfg::RAW, b_lo = b_hi + Cfg::RAW;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < BK / 8; ++kk) {
-          const uint64_t dah = make_smem_desc(a_hi + kk * a_kstep, a_lbo, a_sbo, a_sw);
-          const uint64_t dbh = make_smem_desc(b_hi + kk * b_kstep, b_lbo, b_sbo, b_sw);
-          if (!(p.flags & FLAG_ONE_TERM)) {
-            const uint64_t dal = make_smem_desc(a_lo + kk * a_kstep, a_lbo, a_sbo, a_sw);
-            const uint64_t dbl = make_smem_desc(b_lo + kk * b_kstep, b_lbo, b_sbo, b_sw);
-            mma_tf32_ss(tmem_cross, dal, dbh, idesc, acc_cross);
-            mma_tf32_ss(tmem_cross, dah, dbl, idesc, 1);
-            acc_cross = 1;
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            const uint32_t al = a_low0 + stage_off + kk * a_step, bl = b_low0 + stage_off + kk * b_step;
+            if (!one_term) {
+              mma_tf32_ss_words(tmem_cross, al + LO_TILE, a_hiw, bl, b_hiw, idesc, kk ? 1u : acc_cross);
+              mma_tf32_ss_words(tmem_cross, al, a_hiw, bl + LO_TILE, b_hiw, idesc, 1);
+            }
+            mma_tf32_ss_words(tmem_main, al, a_hiw, bl, b_hiw, idesc, kk ? 1u : accumulate);
           }
-          mma_tf32_ss(tmem_main, dah, dbh, idesc, accumulate);
-          accumulate = 1;
+          mma_commit(bar_empty + 8 * s);
         }
-        mma_commit(bar_empty + 8 * s);
+        acc_cross = 1;
+        accumulate = 1;
+        __syncwarp();
+        if (++s == STAGES) { s = 0; ph ^= 1; stage_off = 0; } else { stage_off += STAGE_STEP; }
       }
-      mma_commit(bar_acc);
+      if (elect_one()) mma_commit(bar_acc);
+      __syncwarp();
       if (*abort_flag) {
         // every MMA issued must have retired before TMEM is freed
         for (int it = 0; it < (1 << 16); ++it)
@@ -186,6 +204,31 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // ------------------- hi/lo split, then epilogue (warps 0-7) ---------------
     const int tid = threadIdx.x;
     bool ok = true;
+    if (WARP_PER_KBLOCK) {
+      // Narrow tiles belong to small, latency-bound problems, where a k-block's pass (wait, load,
+      // split, store, proxy fence, arrive) is a serial chain of several hundred cycles: each warp
+      // takes whole k-blocks (i = warp, warp + 8, ...), so eight of those chains overlap.  Warp w
+      // always works on stage w (8 warps, 8 stages), in consecutive phases.
+      for (int i = warp; i < nkb; i += NUM_CONV_WARPS) {
+        const int s = warp, ph = (i / STAGES) & 1;
+        if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 300 + s)) { ok = false; break; }
+        uint8_t* hi = smem + s * Cfg::STAGE;
+        uint8_t* lo = hi + Cfg::RAW;
+        if (!(p.flags & FLAG_ONE_TERM)) {
+#pragma unroll 8
+          for (int c = 0; c < Cfg::RAW / 16 / 32; ++c) {
+            const int off = (lane + c * 32) * 16;
+            const float4 v = *reinterpret_cast<const float4*>(hi + off);
+            float4 l;
+            l.x = lo_part(v.x); l.y = lo_part(v.y); l.z = lo_part(v.z); l.w = lo_part(v.w);
+            *reinterpret_cast<float4*>(lo + off) = l;
+          }
+          fence_proxy_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_conv + 8 * s);
+      }
+    } else {
     for (int i = 0; i < nkb; ++i) {
       const int s = i % STAGES, ph = (i / STAGES) & 1;
       if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 300 + s)) { ok = false; break; }
@@ -204,6 +247,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_conv + 8 * s);   // one arrive per warp
+    }
     }
     if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 400);
     ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
