@@ -110,7 +110,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_conv + 8 * s, GATHER_WARPS);
+      // TAP: the W tiles (TMA) complete on the same barrier as the gather warps, so the MMA warp has
+      // one wait per k-block
+      mbar_init(bar_conv + 8 * s, TAP ? GATHER_WARPS + 1 : GATHER_WARPS);
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_acc, 1);
@@ -141,7 +143,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       uint32_t ph = 0;
       for (int i = 0; i < nkb; ++i) {
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) break;
-        const uint32_t full = bar_full + 8 * s;
+        const uint32_t full = (TAP ? bar_conv : bar_full) + 8 * s;
         if (elect_one()) {
           mbar_arrive_expect_tx(full, TAP ? 2 * B_TILE : B_TILE);
           tma_load_2d(smem_base + s * Cfg::STAGE + A_TILE, &tmW, i * CBK, n0, full);
@@ -153,7 +155,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       if (*abort_flag) {
         for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
           for (int it = 0; it < (1 << 16); ++it)
-            if (mbar_try_wait(bar_full + 8 * (i % STAGES), (i / STAGES) & 1)) break;
+            if (mbar_try_wait((TAP ? bar_conv : bar_full) + 8 * (i % STAGES), (i / STAGES) & 1)) break;
       }
     }
   } else if (warp == GATHER_WARPS + 1) {
@@ -175,7 +177,6 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       uint32_t ph = 0, stage_off = 0;
       for (int i = 0; i < nkb; ++i) {
         if (!mbar_wait(bar_conv + 8 * s, ph, abort_flag, p.status, 600 + s)) break;
-        if (TAP && !mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 650 + s)) break;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
