@@ -17,10 +17,11 @@
 // Two gather schemes share the kernel (template flag TAP):
 //  * TAP = false, any geometry: K runs in the reference's order (c, ky, kx); every gathered
 //    element decodes its own (c, ky, kx).
-//  * TAP = true, C_in a multiple of 16: K runs tap-major, k' = (ky*kW + kx)*C_in + c, so a 16-wide
-//    k-block is ONE filter tap and 16 consecutive channels: the bounds test and the input offset
-//    are computed once per k-block and the 8 elements of a thread are loads at a constant stride
-//    (one input plane apart).  The weights are permuted to that order, and split into hi / lo,
+//  * TAP = true, C_in a multiple of 16: K runs as k' = ((c / 16)*kH*kW + ky*kW + kx)*16 + c % 16, so
+//    a 16-wide k-block is ONE filter tap and 16 consecutive channels: the bounds test and the input
+//    offset are computed once per k-block and the 8 elements of a thread are loads at a constant
+//    stride (one input plane apart).  Consecutive k-blocks walk the taps of the same 16 channels,
+//    so they re-read the same few input rows and hit in L1.  The weights are permuted to that order, and split into hi / lo,
 //    by a small kernel into the stream's scratch ([2][C_out][K] floats) before the launch, so the
 //    main kernel has no W pass at all: TMA delivers both W tiles.  Only the order of the fp32
 //    summation over k differs from the reference order.
@@ -68,7 +69,7 @@ __device__ __forceinline__ float conv_lo_part(float x) {
   return ((xb & 0x7f800000u) == 0x7f800000u) ? 0.f : lo;
 }
 
-// W[cout][c*khkw + t]  ->  hi[cout][t*cin + c] (raw value), lo[cout][t*cin + c] (x - trunc_tf32(x))
+// W[cout][c*khkw + t]  ->  hi / lo [cout][((c/16)*khkw + t)*16 + c%16]   (hi = raw value, lo = x - trunc_tf32(x))
 __global__ void __launch_bounds__(256)
 conv_prep_weights_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int cout, int cin,
                          int khkw) {
@@ -76,7 +77,9 @@ conv_prep_weights_kernel(const float* __restrict__ w, float* __restrict__ hi, fl
   const int total = cout * K;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const int co = i / K, kp = i - co * K;
-    const int t = kp / cin, c = kp - t * cin;
+    const int blk = kp >> 4, c16 = kp & 15;
+    const int cb = blk / khkw, t = blk - cb * khkw;
+    const int c = cb * 16 + c16;
     const float x = w[(long long)co * K + c * khkw + t];
     hi[i] = x;
     lo[i] = conv_lo_part(x);
@@ -257,22 +260,21 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     bool ok = true;
     float vn[8];
     if (TAP) {
-      // ---- tap-major gather: k-block i = tap (i / cblocks), channels 16*(i % cblocks) + khalf*8 .. +7 ----
-      const int cblocks = p.cin >> 4;
+      // ---- k-block i = channels 16*(i / taps) + khalf*8 .. +7 at tap (i % taps) ----
       // shared-memory offsets of this thread's 8 k-rows (row = khalf*8 + j): 128 B per row, the
       // 32-byte chunk XOR-ed with (row & 3) = (j & 3)
       const uint32_t row0 = box_off + (uint32_t)khalf * 1024;
       const uint32_t sw0 = row0 + ((chunk ^ 0u) << 5), sw1 = row0 + ((chunk ^ 1u) << 5),
                      sw2 = row0 + ((chunk ^ 2u) << 5), sw3 = row0 + ((chunk ^ 3u) << 5);
       const long long img_off = (long long)img * p.cin * in_hw + (long long)khalf * 8 * in_hw + pix_off;
-      int tap = 0, cb = 0, ky = 0, kx = 0;
+      int cb = 0, ky = 0, kx = 0;
       auto fetch_tap = [&](float (&v)[8]) {
         const int iy = iy0 + ky, ix = ix0 + kx;
         const bool valid = m_ok && iy >= 0 && iy < p.in_h && ix >= 0 && ix < p.in_w;
         const float* src = p.in + (img_off + (long long)cb * 16 * in_hw + ky * p.in_w + kx);
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = valid ? __ldg(src + (long long)j * in_hw) : 0.f;
-        if (++cb == cblocks) { cb = 0; ++tap; if (++kx == p.kw) { kx = 0; ++ky; } }
+        if (++kx == p.kw) { kx = 0; if (++ky == p.kh) { ky = 0; ++cb; } }
       };
       if (nkb > 0) fetch_tap(vn);
       for (int i = 0; i < nkb; ++i) {
@@ -294,7 +296,6 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_conv + 8 * s);
       }
-      (void)tap;
     } else {
     if (nkb > 0) fetch(0, vn);
     for (int i = 0; i < nkb; ++i) {
