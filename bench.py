@@ -538,6 +538,14 @@ def run_b200(args, rank, world, local_rank):
         peak_note = "nominal B200 fp64 dense rate 37 TF (no measured fp64 peak exists for this pool); work 2*M*N*K"
         kernel_name, kernel_path = "gemm_f64_kernel (DMMA)", "gemm_bias_act (DMMA fp64, bias+ReLU fused) x5 + softmax"
     achieved = gemm_flops / gemm_ms / 1e9
+    gemm_bytes = (2 * rows * WIDTH + WIDTH * WIDTH + WIDTH) * (4 if dt == "float" else 8)
+    if dt == "float":
+        # dram__bytes_read + dram__bytes_write of the same kernel on an 8192-row shard (ncu, one launch),
+        # scaled by the number of row tiles
+        traffic = (512.4e6 + 118.1e6) * rows / 8192.0
+        traffic_note = "ncu capture of the 8192-row launch (630.5 MB) x rows/8192; not memory-bound (~8 % of HBM rate)"
+    else:
+        traffic, traffic_note = None, "no capture of the fp64 kernel's DRAM counters"
     line = {
         "metric": "wide_mlp_inference_samples_per_s" + ("" if dt == "float" else "_fp64"), "value": value, "unit": "samples/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -553,7 +561,7 @@ def run_b200(args, rank, world, local_rank):
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": "%s (M=%d, N=4096, K=4096)" % (kernel_name, rows),
                      "achieved": achieved, "peak": peak_tf32x3, "unit": "TFLOP/s", "frac": achieved / peak_tf32x3,
-                     "traffic": None, "ms_per_launch": gemm_ms,
+                     "traffic": traffic, "traffic_note": traffic_note, "algorithmic_bytes": gemm_bytes, "ms_per_launch": gemm_ms,
                      "peak_note": peak_note},
         "clocks": clocks,
     }
