@@ -52,6 +52,24 @@ int cb200_scratch(cb200_stream* s, size_t bytes, void** out) {
   return CB200_OK;
 }
 
+int cb200_tile_flags(cb200_stream* s, size_t count, int** out) {
+  if (count > s->tile_flags_count) {
+    DeviceGuard g(s->device);
+    if (s->tile_flags) {
+      CB_CUDA(cudaStreamSynchronize(s->stream));
+      CB_CUDA(cudaFree(s->tile_flags));
+      s->tile_flags = nullptr;
+      s->tile_flags_count = 0;
+    }
+    size_t want = (count + 4095) & ~(size_t)4095;
+    CB_CUDA(cudaMalloc(&s->tile_flags, want * sizeof(int)));
+    CB_CUDA(cudaMemsetAsync(s->tile_flags, 0, want * sizeof(int), s->stream));
+    s->tile_flags_count = want;
+  }
+  *out = s->tile_flags;
+  return CB200_OK;
+}
+
 extern "C" {
 
 const char* cb200_last_error(void) { return g_err; }
@@ -96,6 +114,8 @@ int cb200_stream_create(int device, cb200_stream** out) {
   s->device = device;
   s->scratch = nullptr;
   s->scratch_bytes = 0;
+  s->tile_flags = nullptr;
+  s->tile_flags_count = 0;
   s->launches.store(0);
   s->capture_start = -1;
   cudaError_t e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
@@ -114,6 +134,7 @@ int cb200_stream_destroy(cb200_stream* s) {
   DeviceGuard g(s->device);
   cudaStreamSynchronize(s->stream);
   if (s->scratch) cudaFree(s->scratch);
+  if (s->tile_flags) cudaFree(s->tile_flags);
   cudaFree(s->status_dev);
   cudaFreeHost(s->status_host);
   cudaStreamDestroy(s->stream);

@@ -16,6 +16,8 @@ struct cb200_stream {
   int* status_host;    // pinned mirror used by cb200_stream_status
   void* scratch;       // lazily grown per-stream device workspace
   size_t scratch_bytes;
+  int* tile_flags;     // zero-initialised device words, one per output tile of a K-split GEMM launch
+  size_t tile_flags_count;
   std::atomic<int64_t> launches;
   int64_t capture_start;   // launch counter when the running capture began; -1 when not capturing
 };
@@ -38,6 +40,8 @@ void cb200_set_error(const char* fmt, ...);
 int cb200_cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 // make `bytes` of per-stream scratch available (grows, never shrinks)
 int cb200_scratch(cb200_stream* s, size_t bytes, void** out);
+// at least `count` zeroed flag words owned by the stream (kernels that use them leave them zero)
+int cb200_tile_flags(cb200_stream* s, size_t count, int** out);
 
 #define CB_CUDA(call)                                                     \
   do {                                                                    \

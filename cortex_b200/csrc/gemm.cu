@@ -109,14 +109,14 @@ int launch_simt(cb200_stream* s, T* C, long long ldc, int ta, int tb, T alpha, c
 // slows to 1000-2000 cycles per k-block while the pair's MMAs stream operands -- so single CTAs stay.)
 int tc_f32(cb200_stream* s, float* C, long long ldc, int ta, int tb, float alpha, const float* A, int M, int K,
            long long lda, const float* B, int N, long long ldb, float beta, const float* bias, int act,
-           const PeerList* peers) {
-  return cb200_gemm_tf32x3_launch_peers(s, C, ldc, ta, tb, alpha, A, M, K, lda, B, N, ldb, beta, bias, act, 0, 1, 0,
+           const PeerList* peers, int flags) {
+  return cb200_gemm_tf32x3_launch_peers(s, C, ldc, ta, tb, alpha, A, M, K, lda, B, N, ldb, beta, bias, act, 0, 1, flags,
                                         peers ? peers->n : 0, peers ? (float* const*)peers->p : nullptr);
 }
 
 int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha, const void* A,
               int64_t a_rows, int64_t a_cols, int64_t lda, const void* B, int64_t b_cols, int64_t ldb, double beta,
-              const void* bias, int act, const PeerList* peers = nullptr) {
+              const void* bias, int act, const PeerList* peers = nullptr, bool layer_stack = false) {
   CB_REQUIRE(s && C && A && B, "gemm: null argument");
   CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "gemm! is only defined for float and double tensors");
   CB_REQUIRE(a_rows >= 0 && a_cols >= 0 && b_cols >= 0, "gemm: negative extent");
@@ -135,18 +135,22 @@ int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int
       // (relative, worst case all-positive data).  Long reductions are therefore cut into K chunks
       // chained through C (beta = 1), each chunk boundary being a round-to-nearest fp32 add in the
       // epilogue; bias and activation join on the last chunk.
+      // layer_stack (the fused layer entry points): each launch also splits its K in two inside the kernel
       const int K_CHUNK = 4096;
-      if (K <= 2 * K_CHUNK)
+      const int tc_flags = layer_stack ? 2 /* FLAG_SPLIT_K */ : 0;
+      if (K <= K_CHUNK)
         return tc_f32(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb, (float)beta,
-                      (const float*)bias, act, peers);
-      for (int k0 = 0; k0 < K; k0 += K_CHUNK) {
-        const int kc = (K - k0 < K_CHUNK) ? (K - k0) : K_CHUNK;
+                      (const float*)bias, act, peers, tc_flags);
+      const int n_chunks = (K + K_CHUNK - 1) / K_CHUNK;
+      const int chunk = ((K + n_chunks - 1) / n_chunks + 15) / 16 * 16;     // even chunks, whole k-blocks
+      for (int k0 = 0; k0 < K; k0 += chunk) {
+        const int kc = (K - k0 < chunk) ? (K - k0) : chunk;
         const bool last = k0 + kc >= K;
         const float* ak = trans_a ? a + (long long)k0 * lda : a + k0;
         const float* bk = trans_b ? b + k0 : b + (long long)k0 * ldb;
         int rc = tc_f32(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, ak, M, kc, lda, bk, N, ldb,
                         k0 == 0 ? (float)beta : 1.0f, last ? (const float*)bias : nullptr, last ? act : 0,
-                        last ? peers : nullptr);
+                        last ? peers : nullptr, tc_flags);
         if (rc) return rc;
       }
       return CB200_OK;
@@ -181,7 +185,8 @@ int cb200_gemm(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, in
 int cb200_gemm_bias_act(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha,
                         const void* A, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B, int64_t b_cols,
                         int64_t ldb, double beta, const void* bias, int act) {
-  return gemm_impl(s, dtype, C, ldc, trans_a, trans_b, alpha, A, a_rows, a_cols, lda, B, b_cols, ldb, beta, bias, act);
+  return gemm_impl(s, dtype, C, ldc, trans_a, trans_b, alpha, A, a_rows, a_cols, lda, B, b_cols, ldb, beta, bias, act,
+                   nullptr, true);
 }
 
 int cb200_gemm_bias_act_peers(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha,
@@ -198,7 +203,7 @@ int cb200_gemm_bias_act_peers(cb200_stream* s, int dtype, void* C, int64_t ldc, 
     CB_REQUIRE(d >= n_peers || peers.p[d], "gemm_bias_act_peers: peer destination %d is null", d);
   }
   return gemm_impl(s, dtype, C, ldc, trans_a, trans_b, alpha, A, a_rows, a_cols, lda, B, b_cols, ldb, beta, bias, act,
-                   &peers);
+                   &peers, true);
 }
 
 // Test hooks (not part of the public header): force a specific fp32 kernel.

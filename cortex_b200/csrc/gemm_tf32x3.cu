@@ -76,14 +76,28 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   // Tile order: column tiles are taken in groups of p.group_n; inside a group the CTAs sweep all row
   // tiles, so the group's B panel (group_n * BN * K floats) stays in L2 while A streams past it once
   // per group.
+  // With a K split the grid holds the tiles twice, in blocks of p.split_block tiles: a block's first K
+  // halves, then its second halves (which add onto what the first ones stored while that is still in L2).
   const int tiles_n = (p.N + BN - 1) / BN;
   const int tiles_m = (p.M + BM - 1) / BM;
-  const int grp = blockIdx.x / (tiles_m * p.group_n);
-  const int rem = blockIdx.x - grp * tiles_m * p.group_n;
+  const int n_tiles = tiles_m * tiles_n;
+  int k_half = 0, tile_id = (int)blockIdx.x;
+  if (p.k_split == 2) {
+    const int blk = (int)blockIdx.x / (2 * p.split_block);
+    const int r = (int)blockIdx.x - blk * 2 * p.split_block;
+    const int in_blk = min(p.split_block, n_tiles - blk * p.split_block);
+    k_half = r >= in_blk ? 1 : 0;
+    tile_id = blk * p.split_block + r - k_half * in_blk;
+  }
+  const int grp = tile_id / (tiles_m * p.group_n);
+  const int rem = tile_id - grp * tiles_m * p.group_n;
   const int in_grp = min(p.group_n, tiles_n - grp * p.group_n);
   const int tile_m = rem / in_grp, tile_n = grp * p.group_n + rem % in_grp;
   const int m0 = tile_m * BM, n0 = tile_n * BN;
-  const int nkb = (p.K + BK - 1) / BK;
+  const int nkb_all = (p.K + BK - 1) / BK;
+  const int kb_first = p.k_split == 2 ? nkb_all / 2 : nkb_all;       // k-blocks of the first half
+  const int kb_begin = k_half ? kb_first : 0;
+  const int nkb = k_half ? nkb_all - kb_first : kb_first;
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_full = smem_u32(bars), bar_conv = smem_u32(bars + STAGES), bar_empty = smem_u32(bars + 2 * STAGES),
@@ -124,7 +138,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 100 + s)) break;
         const uint32_t full = bar_full + 8 * s;
         const uint32_t a_dst = smem_base + s * Cfg::STAGE, b_dst = a_dst + A_TILE;
-        const int k0 = i * BK;
+        const int k0 = (kb_begin + i) * BK;
         if (!PROD_WHOLE || elect_one()) {
           mbar_arrive_expect_tx(full, Cfg::RAW);
           if (!p.a_mn_major) {
@@ -260,13 +274,46 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 400);
     ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
     tc_fence_after();
+    if (ok && k_half) {
+      // the first half of this tile must be in C; by now it has been for a long time (its CTA started
+      // a whole grid-half earlier), the bounded poll is there for correctness only
+      if (lane == 0) {
+        const int* flag = p.tile_flags + tile_id;
+        int seen = 0;
+        const long long t0 = clock64();
+        for (;;) {
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+          if (seen != 0 || *abort_flag) break;
+          if (clock64() - t0 > SM100_WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            if (atomicCAS(p.status, 0, 4 /* CB200_ERR_TIMEOUT */) == 0) p.status[1] = 450;
+            break;
+          }
+          __nanosleep(200);
+        }
+        ok = seen != 0;
+      }
+      ok = __all_sync(0xffffffffu, __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0);
+    }
     if (ok) {
-      epilogue_tile<BN>(p, tmem_base, m0, n0, warp, lane);
+      const bool last = p.k_split != 2 || k_half == 1;
+      epilogue_tile<BN>(p, tmem_base, m0, n0, warp, lane, reinterpret_cast<float*>(smem), k_half ? 1.f : p.beta, last, k_half == 1);
+      if (p.k_split == 2 && k_half == 0) __threadfence();     // this thread's part of C, before the flag below
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (p.k_split == 2 && threadIdx.x == 0 && !*abort_flag) {
+    // first half: publish "C holds the partial tile"; second half: leave the flag zero for the next launch
+    int* flag = p.tile_flags + tile_id;
+    if (k_half == 0) {
+      __threadfence();
+      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(1) : "memory");
+    } else {
+      *flag = 0;
+    }
+  }
   if (warp == NUM_CONV_WARPS + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
@@ -322,7 +369,7 @@ int launch_tile(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmB,
     attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
   });
   if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
-  long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.k_split;
   gemm_tf32x3_kernel<BN, BK><<<(unsigned)tiles, NUM_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmB, p);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
@@ -364,6 +411,18 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   while (BN > 64 && tiles_m * ((N + BN - 1) / BN) < s->sm_count) BN >>= 1;
   const int tiles_n = (N + BN - 1) / BN;
   const long long panel_bytes = (long long)BN * K * 4;          // one column tile's share of B
+  // FLAG_SPLIT_K (the fused layer entry points): reductions of 4096 and more are cut in two K halves per
+  // tile (see GemmParams::k_split).  tcgen05 accumulates with truncation, a result shrinks by about
+  // 7e-9 * K (relative: 2.9e-5 at K = 4096, inside the 1e-4 bound of one gemm!), the same for every
+  // output, so it compounds through a stack of layers (five 4096-wide layers: 1.4e-4 on the softmax
+  // output); two 2048-long halves joined by a round-to-nearest add halve that, at 8-12 % of the speed.
+  p.k_split = ((flags & FLAG_SPLIT_K) && K >= 4096 && store_mode == STORE_ROW_MAJOR) ? 2 : 1;
+  p.tile_flags = nullptr;
+  p.split_block = 2 * s->sm_count;
+  if (p.k_split == 2) {
+    int rcf = cb200_tile_flags(s, (size_t)tiles_m * tiles_n, &p.tile_flags);
+    if (rcf) return rcf;
+  }
   p.group_n = tiles_n;
   if (tiles_n * panel_bytes > (40ll << 20)) {
     long long g = (32ll << 20) / panel_bytes;
