@@ -81,6 +81,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
       static_assert(CHUNK == 32, "BN must be >= 64");
       bool vec_ok = p.store_mode == STORE_ROW_MAJOR && (p.ldc % 4) == 0 && (((uintptr_t)p.C) & 15) == 0;
       for (int d = 0; d < e_peers; ++d) vec_ok = vec_ok && (((uintptr_t)p.peers[d]) & 15) == 0;
+      const bool vec8_ok = vec_ok && e_peers == 0 && (p.ldc % 8) == 0 && (((uintptr_t)p.C) & 31) == 0;
 #pragma unroll 1
       for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
         const int col0 = half * COLS_PER_HALF + cc * 32;
@@ -190,7 +191,30 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
         if (m < p.M && nb < p.N) {
           if (p.store_mode == STORE_ROW_MAJOR) {
             float* crow = p.C + (long long)m * p.ldc + nb;
-            if (vec_ok && nb + 32 <= p.N) {
+            if (vec8_ok && nb + 32 <= p.N) {
+              // 32-byte aligned rows: one 256-bit access per sector
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = p.alpha * __uint_as_float(r[j + e]);
+                if (beta_now != 0.f) {
+                  float c[8];
+                  ld_global_v8(crow + j, c, c_is_partial);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o[e] += beta_now * c[e];
+                }
+                if (e_bias) {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o[e] += e_bias[nb + j + e];
+                }
+                if (e_act) {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o[e] = apply_act(o[e], e_act);
+                }
+                st_global_v8(crow + j, o);
+              }
+            } else if (vec_ok && nb + 32 <= p.N) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
                 float4 o;
