@@ -249,6 +249,12 @@ def bench_eltwise(drv, dev, peaks):
                                                                             stat[(i + 1) % sets].buffer),
                                          2 * rows * cols * 4 + cols * 4 + 2 * rows * 4),
         }
+        # next to the path: ternary select (PReLU-shaped: x >= 0 ? x : 0.25 * x) and gemv! (A [8192, 4096])
+        vec = ct.to_tensor(rng.standard_normal(cols).astype(np.float32))
+        outv = ct.new_tensor([rows])
+        cases["ternary_select_prelu"] = (lambda i: ct.ternary_op(ys[i], 1.0, xs[i], 0.25, xs[i], 1.0, xs[i], "select"),
+                                         2 * rows * cols * 4)
+        cases["gemv_8192x4096"] = (lambda i: ct.gemv(outv, False, 1.0, xs[i], vec, 0.0), rows * cols * 4 + cols * 4 + rows * 4)
         for name, (fn, nbytes) in cases.items():
             for _ in range(3):
                 fn(rot())

@@ -20,6 +20,7 @@ NUMPY_NAME = {"byte": "int8", "short": "int16", "int": "int32", "long": "int64",
 BINARY_OPS = {"+": 0, "-": 1, "*": 2, "/": 3, "min": 4, "max": 5, "bit-and": 6, "bit-xor": 7, "eq": 8,
               ">": 9, ">=": 10, "<": 11, "<=": 12}
 UNARY_OPS = {"floor": 0, "ceil": 1, "round": 2, "-": 3, "tanh": 4, "logistic": 5, "exp": 6, "sqrt": 7, "noop": 8}
+TERNARY_OPS = {"select": 0}
 REDUCE_OPS = {"max": 0, "min": 1, "sum": 2, "mean": 3, "magnitude": 4, "magnitude-squared": 5}
 ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "tanh": 2, "logistic": 3}
 
@@ -80,6 +81,8 @@ SIGNATURES = {
     "cb200_convolution_workspace_size": [C.POINTER(ConvDesc), _i, _i, _i, _i, _i, C.POINTER(_i64)],
     "cb200_convolution_forward": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
     "cb200_convolution_forward_static": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, C.POINTER(ConvDesc)],
+    "cb200_ternary_op": [_vp, _i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
+    "cb200_gemv": [_vp, _i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],
     "cb200_unsupported": [C.c_char_p],
     "cb200_gemm_bias_act": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i],
     "cb200_gemm_bias_act_peers": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i,

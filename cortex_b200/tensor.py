@@ -460,6 +460,44 @@ def binary_op(dest, alpha, x, beta, y, op):
     return dest
 
 
+# ------------------------------ ternary-op! ---------------------------------------
+
+TERNARY_OPERATIONS = ("select",)
+
+
+def ternary_op(dest, alpha, x, beta, y, gamma, z, op):
+    """dest = op(alpha * x, beta * y, gamma * z); x, y, z tensors or numbers (tensor.clj:808-854).
+    select: the reference's backends (and its own tests) give  alpha*x >= 0 ? gamma*z : beta*y."""
+    _require(op in TERNARY_OPERATIONS, "unknown ternary operation", op)
+    args = [(x, alpha, "x"), (y, beta, "y"), (z, gamma, "z")]
+    tensors = [(a, f, nm) for a, f, nm in args if _kind(a) == "tensor"]
+    constants = [(a, f, nm) for a, f, nm in args if _kind(a) != "tensor"]
+    if not tensors:
+        a, b, c = (float(f) * float(v) for v, f, _ in args)
+        return assign(dest, c if a >= 0 else b)          # inline-ternary-op (tensor.clj:782-789)
+    _ensure_datatypes(dest.get_datatype(), *[t for t, _, _ in tensors])
+    _ensure_same_device(dest, *[t for t, _, _ in tensors])
+    for t, _, _ in tensors:
+        _ensure_broadcast_rules(dest, t)
+    n_elems = max(t.ecount() for t, _, _ in tensors)
+    stream = check_stream()
+    # order-ternary-args (tensor.clj:792-805): tensors first, then constants already multiplied
+    arg_order = [nm for _, _, nm in tensors] + [nm for _, _, nm in constants]
+    consts = [float(v) * float(f) for v, f, _ in constants]
+    if len(tensors) == 3:
+        stream.ternary_op(dest.buffer, dest.dimensions, x.buffer, x.dimensions, alpha, y.buffer, y.dimensions, beta,
+                          z.buffer, z.dimensions, gamma, n_elems, op)
+    elif len(tensors) == 2:
+        (a, af, _), (b, bf, _) = tensors
+        stream.ternary_op_constant(dest.buffer, dest.dimensions, a.buffer, a.dimensions, af, b.buffer, b.dimensions, bf,
+                                   consts[0], n_elems, op, arg_order)
+    else:
+        (a, af, _), = tensors
+        stream.ternary_op_constant_constant(dest.buffer, dest.dimensions, a.buffer, a.dimensions, af, consts[0],
+                                            consts[1], n_elems, op, arg_order)
+    return dest
+
+
 # ------------------------------ unary-reduce! ------------------------------------
 
 def unary_reduce(output, alpha, input, op):
@@ -504,6 +542,27 @@ def gemm(C, trans_a, trans_b, alpha, A, B, beta):
     check_stream().gemm(C.buffer, _column_stride(C.dimensions), trans_a, trans_b, alpha, A.buffer, a_rows, a_cols,
                         _column_stride(A.dimensions), B.buffer, b_cols, _column_stride(B.dimensions), beta)
     return C
+
+
+def _ensure_vector_indexable(*tensors):
+    """tensor.clj:954-962."""
+    for t in tensors:
+        _require(dense(t) or _num_columns(t.dimensions) == 1, "Argument is not vector-indexable", t)
+
+
+def _blas_vector_increment(t):
+    """tensor.clj:965-971."""
+    return 1 if dense(t) else (t.dimensions["strides"][-1] or 1)
+
+
+def gemv(c, trans_a, alpha, A, x, beta):
+    """c = alpha * (trans-a? A) * x + beta * c   (tensor.clj:974-989)."""
+    _external_library_check("gemv!", c, A, x)
+    _ensure_vector_indexable(x, c)
+    a_rows, a_cols = tensor_to_2d_shape(A)
+    check_stream().gemv(c.buffer, _blas_vector_increment(c), trans_a, alpha, A.buffer, a_rows, a_cols,
+                        _column_stride(A.dimensions), x.buffer, _blas_vector_increment(x), beta)
+    return c
 
 
 # ------------------------------ softmax! -------------------------------------------

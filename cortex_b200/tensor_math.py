@@ -10,7 +10,7 @@ objects with ``.ptr`` / ``.dtype`` and dimensions are the dicts of
 import ctypes as C
 
 from . import dimensions as dims_mod
-from ._lib import ACTIVATIONS, BINARY_OPS, DTYPE_CODE, REDUCE_OPS, UNARY_OPS, ConvDesc, Dims
+from ._lib import ACTIVATIONS, BINARY_OPS, DTYPE_CODE, REDUCE_OPS, TERNARY_OPS, UNARY_OPS, ConvDesc, Dims
 
 
 def _index_pointer(tensor):
@@ -140,11 +140,37 @@ class CTensorMath:
         from ._lib import call
         call("cb200_unsupported", name.encode())
 
-    def ternary_op(self, *a):
-        self._unsupported("ternary-op!")
+    # --- ternary-op! family: one C entry point, constants travel as (NULL pointer, value * factor) ------
+    def _ternary(self, dest, dest_dims, args, n_elems, op):
+        """args: three (buffer-or-None, dims-or-None, scalar) in x, y, z order."""
+        c_args = []
+        for buf, dms, scalar in args:
+            c_args += [buf.ptr if buf is not None else None, C.byref(wire(dms)) if buf is not None else None,
+                       float(scalar)]
+        self._tm("ternary_op", DTYPE_CODE[dest.dtype], dest.ptr, C.byref(wire(dest_dims)), *c_args, int(n_elems),
+                 TERNARY_OPS[op])
 
-    def gemv(self, *a):
-        self._unsupported("gemv!")
+    def ternary_op(self, dest, dest_dims, x, x_dims, alpha, y, y_dims, beta, z, z_dims, gamma, n_elems, op):
+        self._ternary(dest, dest_dims, [(x, x_dims, alpha), (y, y_dims, beta), (z, z_dims, gamma)], n_elems, op)
+
+    @staticmethod
+    def _expand_arg_order(arg_order, entries):
+        """entries are in arg-order (tensors first, then constants); returns them as x, y, z."""
+        by_name = dict(zip(arg_order, entries))
+        return [by_name["x"], by_name["y"], by_name["z"]]
+
+    def ternary_op_constant(self, dest, dest_dims, a, a_dims, a_alpha, b, b_dims, b_alpha, constant, n_elems, op,
+                            arg_order):
+        self._ternary(dest, dest_dims, self._expand_arg_order(
+            arg_order, [(a, a_dims, a_alpha), (b, b_dims, b_alpha), (None, None, constant)]), n_elems, op)
+
+    def ternary_op_constant_constant(self, dest, dest_dims, a, a_dims, a_alpha, const_1, const_2, n_elems, op, arg_order):
+        self._ternary(dest, dest_dims, self._expand_arg_order(
+            arg_order, [(a, a_dims, a_alpha), (None, None, const_1), (None, None, const_2)]), n_elems, op)
+
+    def gemv(self, c, inc_c, trans_a, alpha, a, a_row_count, a_col_count, a_colstride, x, inc_x, beta):
+        self._tm("gemv", DTYPE_CODE[c.dtype], c.ptr, int(inc_c), 1 if trans_a else 0, float(alpha), a.ptr,
+                 int(a_row_count), int(a_col_count), int(a_colstride), x.ptr, int(inc_x), float(beta))
 
     def batch_normalize_eltwise(self, *a):
         self._unsupported("batch-normalize-eltwise!")

@@ -209,9 +209,28 @@ int cb200_convolution_forward_static(cb200_stream* s, int dtype, void* out, cons
                                      double out_alpha, const void* in, const cb200_dims* in_dims,
                                      const void* w, const cb200_dims* w_dims, const cb200_conv_desc* desc);
 
+/* ---- next to the path: ternary-op! family and gemv! ---------------------------
+ * ternary-op! / ternary-op-constant! / ternary-op-constant-constant!
+ * (src/cortex/tensor/math.clj:71-98; CPU semantics src/cortex/compute/cpu/tensor_math.clj:465-566):
+ *   dest = select(alpha*x, beta*y, gamma*z) = (alpha*x >= 0) ? gamma*z : beta*y
+ * One entry point serves the three protocol methods: an operand that is a constant has a NULL
+ * pointer (and NULL dims) and its scalar holds value * factor, as the reference's
+ * order-ternary-args computes it (src/cortex/tensor.clj:792-805); the binding re-expands arg-order. */
+enum cb200_ternary_op_t { CB200_TERNARY_SELECT = 0 };
+int cb200_ternary_op(cb200_stream* s, int dtype, void* dest, const cb200_dims* dest_dims,
+                     const void* x, const cb200_dims* x_dims, double alpha,
+                     const void* y, const cb200_dims* y_dims, double beta,
+                     const void* z, const cb200_dims* z_dims, double gamma, int64_t n_elems, int op);
+/* gemv! (src/cortex/tensor/math.clj:116-124, cublasSgemv/Dgemv at src/cortex/compute/cuda/tensor_math.clj:155-173):
+ *   c = alpha * op(A) * x + beta * c;  A: a_rows x a_cols row-major with row pitch lda (elements);
+ *   trans_a: op(A) = A^T (c then has a_cols entries, x has a_rows); inc_c / inc_x in elements. */
+int cb200_gemv(cb200_stream* s, int dtype, void* c, int64_t inc_c, int trans_a, double alpha,
+               const void* A, int64_t a_rows, int64_t a_cols, int64_t lda,
+               const void* x, int64_t inc_x, double beta);
+
 /* Protocol methods outside the dense-inference path return CB200_ERR_UNSUPPORTED:
- * ternary-op*, gemv!, batch-normalize-*, activation-gradient!, convolution-backward-*,
- * pooling-*, rand!, lrn-* (src/cortex/tensor/math.clj:71-98, 116-175, 205-250). */
+ * batch-normalize-*, activation-gradient!, convolution-backward-*,
+ * pooling-*, rand!, lrn-* (src/cortex/tensor/math.clj:125-175, 205-250). */
 int cb200_unsupported(const char* method_name);
 
 /* ---- fused extras (no counterpart in the protocol) -------------------------

@@ -42,6 +42,8 @@ _SIGS = {
     "orc_binary_op": [_i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
     "orc_unary_reduce": [_i, _vp, _pd, _d, _vp, _pd, _i],
     "orc_gemm": [_i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d],
+    "orc_gemv": [_i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],
+    "orc_ternary_op": [_i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
     "orc_softmax_eltwise": [_i, _vp, _pd, _vp, _pd],
     "orc_softmax_spatial": [_i, _vp, _pd, _vp, _pd],
     "orc_convolution_forward": [_i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],

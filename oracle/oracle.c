@@ -375,6 +375,57 @@ int orc_gemm(int dtype, void* C, int64_t ldc, int ta, int tb, double alpha, cons
   return 1;
 }
 
+/* ---- gemv (cpu/tensor_math.clj:700-725: BLAS sgemv/dgemv, reference-BLAS loop) ------------------ */
+#define GEMV_BODY(T) { const T* a = (const T*)A; const T* xv = (const T*)x; T* cv = (T*)c; T al = (T)alpha, be = (T)beta; \
+  int64_t out_n = ta ? cols : rows, red_n = ta ? rows : cols; \
+  for (int64_t o = 0; o < out_n; ++o) { T acc = (T)0; \
+    for (int64_t k = 0; k < red_n; ++k) { T av = ta ? a[k * lda + o] : a[o * lda + k]; acc += av * xv[k * incx]; } \
+    T* cp = cv + o * incc; *cp = (be == (T)0) ? al * acc : al * acc + be * (*cp); } return 0; }
+int orc_gemv(int dtype, void* c, int64_t incc, int ta, double alpha, const void* A, int64_t rows, int64_t cols,
+             int64_t lda, const void* x, int64_t incx, double beta) {
+  if (dtype == T_FLOAT) GEMV_BODY(float)
+  if (dtype == T_DOUBLE) GEMV_BODY(double)
+  return 1;
+}
+
+/* ---- ternary select (cpu/tensor_math.clj:465-566) ------------------------------------------------
+ * select-impl picks z when alpha*x >= 0, else y.  Tensor operands are multiplied by their factor (cast to
+ * the element type) in the accumulator type (double / wrapping long).  A NULL pointer marks a constant
+ * whose scalar holds value*factor.  With at least one constant (the -constant / -constant-constant
+ * variants) every argument is cast to the element type before the comparison; with three tensors only
+ * the selected value is cast. */
+#define TERN_ARG(T, ACC, SUF, ptr, dims, simple, fac, cst) \
+  ((ptr) ? (cast_first ? (ACC)ST_##T##_##SUF(MUL_##SUF((ACC)((const T*)(ptr))[ADDR(dims, simple, mx, i)], fac)) \
+                       : MUL_##SUF((ACC)((const T*)(ptr))[ADDR(dims, simple, mx, i)], fac)) \
+         : (cst))
+#define TERN_BODY(T, ACC, SUF) { T* dp = (T*)dest; \
+  ACC xf = SCALAR_##T(alpha), yf = SCALAR_##T(beta), zf = SCALAR_##T(gamma); \
+  ACC xc = (ACC)ST_##T##_d(alpha), yc = (ACC)ST_##T##_d(beta), zc = (ACC)ST_##T##_d(gamma); \
+  _Pragma("omp parallel for") for (int64_t i = 0; i < n; ++i) { \
+    ACC a = TERN_ARG(T, ACC, SUF, x, xd, xs, xf, xc); \
+    ACC r = (a >= (ACC)0) ? TERN_ARG(T, ACC, SUF, z, zd, zs, zf, zc) : TERN_ARG(T, ACC, SUF, y, yd, ys, yf, yc); \
+    dp[ADDR(dd, ds, mx, i)] = ST_##T##_##SUF(r); } return 0; }
+int orc_ternary_op(int dtype, void* dest, const orc_dims* dd, const void* x, const orc_dims* xd, double alpha,
+                   const void* y, const orc_dims* yd, double beta, const void* z, const orc_dims* zd, double gamma,
+                   int64_t n, int op) {
+  if (op != 0) return 1;
+  int32_t mx[5];
+  for (int d = 0; d < 5; ++d) {
+    mx[d] = dd->rev_shape[d];
+    if (x && xd->rev_shape[d] > mx[d]) mx[d] = xd->rev_shape[d];
+    if (y && yd->rev_shape[d] > mx[d]) mx[d] = yd->rev_shape[d];
+    if (z && zd->rev_shape[d] > mx[d]) mx[d] = zd->rev_shape[d];
+  }
+  int ds = is_simple(dd, mx), xs = x ? is_simple(xd, mx) : 1, ys = y ? is_simple(yd, mx) : 1, zs = z ? is_simple(zd, mx) : 1;
+  int cast_first = !(x && y && z);
+  switch (dtype) {
+    case T_BYTE: TERN_BODY(int8_t, int64_t, l) case T_SHORT: TERN_BODY(int16_t, int64_t, l)
+    case T_INT: TERN_BODY(int32_t, int64_t, l) case T_LONG: TERN_BODY(int64_t, int64_t, l)
+    case T_FLOAT: TERN_BODY(float, double, d) case T_DOUBLE: TERN_BODY(double, double, d)
+  }
+  return 1;
+}
+
 /* ---- softmax (cpu/tensor_math.clj:1037-1103) --------------------------------------------------- */
 #define SOFTMAX_BODY(T) { const T* ip = (const T*)in; T* op_ = (T*)out; \
   _Pragma("omp parallel for") for (int64_t r = 0; r < rows; ++r) { \

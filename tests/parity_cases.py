@@ -9,7 +9,8 @@ from cortex_b200 import nn
 from cortex_b200 import tensor as ct
 from cortex_b200.dimensions import ALL
 
-NP = {"float": np.float32, "double": np.float64, "int": np.int32, "long": np.int64}
+NP = {"float": np.float32, "double": np.float64, "int": np.int32, "long": np.int64, "short": np.int16,
+      "byte": np.int8}
 TOL = {"float": 1e-4, "double": 1e-12}
 
 

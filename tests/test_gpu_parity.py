@@ -190,3 +190,64 @@ def test_graph_replay_matches_direct_inference(fused):
             assert np.array_equal(direct, replayed)
             launches_per_forward = per
         assert launches_per_forward >= 3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("datatype", ["float", "double"])
+def test_gemv_matches_oracle(b200_driver, oracle_driver, datatype):
+    """gemv! on configuration-like shapes: both transposes, beta 0 and non-zero, a pitched matrix view and a
+    strided (column) vector."""
+    npdt = np.float32 if datatype == "float" else np.float64
+    rng = np.random.default_rng(71)
+    for rows, cols in ((128, 784), (500, 37), (1000, 4096), (33, 2050)):
+        A = rng.standard_normal((rows, cols + 8)).astype(npdt)
+        xn = rng.standard_normal(cols).astype(npdt)
+        xt = rng.standard_normal((rows, 3)).astype(npdt)          # a column of this is a strided vector
+        c0n = rng.standard_normal(rows).astype(npdt)
+        c0t = rng.standard_normal(cols).astype(npdt)
+
+        def run():
+            a = ct.submatrix(ct.to_tensor(A, datatype), 0, rows, 0, cols)        # row pitch cols + 8
+            cn, ctt = ct.to_tensor(c0n, datatype), ct.to_tensor(c0t, datatype)
+            ct.gemv(cn, False, 1.5, a, ct.to_tensor(xn, datatype), 0.5)
+            ct.gemv(ctt, True, 0.75, a, ct.columns(ct.to_tensor(xt, datatype))[1], 0.0)
+            return ct.to_array(cn), ct.to_array(ctt)
+
+        g, c = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
+        for gv, cv in zip(g, c):
+            assert pc.rel_err(gv, cv) <= pc.TOL[datatype]
+        A64 = A[:, :cols].astype(np.float64)
+        assert pc.rel_err(g[0], 1.5 * A64 @ xn + 0.5 * c0n) <= pc.TOL[datatype]
+        assert pc.rel_err(g[1], 0.75 * A64.T @ xt[:, 1]) <= pc.TOL[datatype]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("datatype", ["float", "double", "int", "long", "short", "byte"])
+def test_ternary_select_matches_oracle(b200_driver, oracle_driver, datatype):
+    """ternary-op! select: three tensors (dense, and with a broadcast row), tensor + constants in every
+    position: bit-exact against the oracle."""
+    npdt = np.dtype(pc.NP[datatype])
+    rng = np.random.default_rng(72)
+    if npdt.kind == "f":
+        X, Y, Z = (rng.standard_normal((257, 1000)).astype(npdt) for _ in range(3))
+    else:
+        hi = min(np.iinfo(npdt).max, 1000)
+        X, Y, Z = (rng.integers(-hi, hi, size=(257, 1000)).astype(npdt) for _ in range(3))
+    row = Y[:1].copy()
+
+    def run():
+        x, y, z, r = (ct.to_tensor(v, datatype) for v in (X, Y, Z, row))
+        outs = []
+        for args in ((1.0, x, 2.0, y, 3.0, z), (1.0, x, 2.0, r, 1.0, z), (-1.0, x, 1.0, 0.0, 1.0, z),
+                     (1.0, x, 1.0, y, 0.25, -3.0), (1.0, x, 2.0, 5.0, 1.0, -1.0)):
+            d = ct.new_tensor([257, 1000], datatype)
+            ct.ternary_op(d, *args, "select")
+            outs.append(ct.to_array(d))
+        return outs
+
+    g, c = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
+    for gv, cv in zip(g, c):
+        assert np.array_equal(gv, cv)
+    ref = np.where(X.astype(np.float64) >= 0, 3.0 * Z.astype(np.float64), 2.0 * Y.astype(np.float64))
+    if npdt.kind == "f":
+        assert pc.rel_err(g[0], ref.astype(npdt)) == 0.0

@@ -256,6 +256,42 @@ def softmax(driver, datatype):
         _eq(([0, 1] + list(ct.to_double_array(answer))) * 5, ct.to_double_array(pred))
 
 
+def gemv(driver, datatype):
+    """verify/tensor.clj:287-306"""
+    with tensor_context(driver, datatype):
+        tens_a = ct.to_tensor(np.arange(12).reshape(4, 3))
+        tens_b = ct.to_tensor([2] * 4)
+        tens_c = ct.to_tensor(list(range(4)))
+        ct.subvector(tens_b, 0, length=3)     # built but unused in the reference test as well
+        ct.gemv(tens_c, False, 1, tens_a, tens_b, 1)
+        _eq([6.0, 25.0, 44.0, 63.0], ct.to_double_array(tens_c))
+        ct.gemv(tens_c, False, 1, tens_a, tens_b, 0)
+        _eq([6, 24, 42, 60], ct.to_double_array(tens_c))
+        tens_c_sub = ct.subvector(tens_c, 0, length=3)
+        tens_a_col = ct.columns(tens_a)[1]          # [1 4 7 10]
+        ct.gemv(tens_c_sub, True, 1, tens_a, tens_a_col, 0)
+        _eq([144.0, 166.0, 188.0], ct.to_double_array(tens_c_sub))
+
+
+def ternary_op_select(driver, datatype):
+    """verify/tensor.clj:623-645"""
+    with tensor_context(driver, datatype):
+        dest = ct.to_tensor([0] * 10)
+        x_arg = ct.to_tensor(list(range(-5, 5)))
+        y_arg = ct.to_tensor(list(range(10)))
+        z_arg = ct.to_tensor([2] * 10)
+        ct.ternary_op(dest, 1, x_arg, 2.0, y_arg, 3.0, z_arg, "select")
+        _eq([0, 2, 4, 6, 8, 6, 6, 6, 6, 6], ct.to_double_array(dest))
+        ct.ternary_op(dest, 1, x_arg, 1.0, -1, 3.0, z_arg, "select")
+        _eq([-1, -1, -1, -1, -1, 6, 6, 6, 6, 6], ct.to_double_array(dest))
+        ct.ternary_op(dest, 1, x_arg, 3.0, z_arg, 1.0, -1, "select")
+        _eq([6, 6, 6, 6, 6, -1, -1, -1, -1, -1], ct.to_double_array(dest))
+        ct.ternary_op(dest, 1, x_arg, 3.0, 2.0, 1.0, -1, "select")
+        _eq([6, 6, 6, 6, 6, -1, -1, -1, -1, -1], ct.to_double_array(dest))
+        ct.ternary_op(dest, 1, x_arg, 1.0, -1, 3.0, 2.0, "select")
+        _eq([-1, -1, -1, -1, -1, 6, 6, 6, 6, 6], ct.to_double_array(dest))
+
+
 def unary_reduce(driver, datatype):
     """verify/tensor.clj:648-665"""
     with tensor_context(driver, datatype):
@@ -418,7 +454,8 @@ def magnitude_and_mag_squared(driver, datatype):
 # how the reference instantiates them (test/clj/cortex/compute/cpu/tensor_test.clj:17-119)
 CASES = [
     (assign_constant, ALL_DTYPES), (assign_marshal, ALL_DTYPES), (unary_op, ALL_DTYPES), (channel_op, ALL_DTYPES),
-    (binary_constant_op, ALL_DTYPES), (binary_op, ALL_DTYPES), (gemm, FLOAT_DTYPES),
+    (binary_constant_op, ALL_DTYPES), (binary_op, ALL_DTYPES), (gemm, FLOAT_DTYPES), (gemv, FLOAT_DTYPES),
+    (ternary_op_select, ALL_DTYPES),
     (activation_forward, FLOAT_DTYPES), (softmax, FLOAT_DTYPES), (unary_reduce, ALL_DTYPES), (transpose, ALL_DTYPES),
     (mask, INT_LONG), (select, ALL_DTYPES), (select_transpose_interaction, ALL_DTYPES),
     (convolution_operator, FLOAT_DTYPES), (indexed_tensor, ALL_DTYPES), (magnitude_and_mag_squared, FLOAT_DTYPES),
