@@ -255,6 +255,12 @@ def bench_eltwise(drv, dev, peaks):
         cases["ternary_select_prelu"] = (lambda i: ct.ternary_op(ys[i], 1.0, xs[i], 0.25, xs[i], 1.0, xs[i], "select"),
                                          2 * rows * cols * 4)
         cases["gemv_8192x4096"] = (lambda i: ct.gemv(outv, False, 1.0, xs[i], vec, 0.0), rows * cols * 4 + cols * 4 + rows * 4)
+        # batch-normalize! (inference, spatial form) on the config-4 activation shape viewed as [128, 64, 4096]
+        bn_stats = [ct.to_tensor(np.abs(rng.standard_normal(64)).astype(np.float32) + 0.5) for _ in range(4)]
+        bn_in = [ct.in_place_reshape(x, [128, 64, 4096]) for x in xs]
+        bn_out = [ct.in_place_reshape(y, [128, 64, 4096]) for y in ys]
+        cases["batch_normalize_spatial"] = (lambda i: ct.batch_normalize(bn_out[i], bn_in[i], *bn_stats, 1e-3),
+                                            2 * rows * cols * 4)
         for name, (fn, nbytes) in cases.items():
             for _ in range(3):
                 fn(rot())

@@ -565,6 +565,42 @@ def gemv(c, trans_a, alpha, A, x, beta):
     return c
 
 
+def batch_normalize(output, input, means, variances, scale, bias, epsilon):
+    """output = (input - mean) / sqrt(variance + epsilon) * scale + bias   (tensor.clj:1047-1145).
+    2 dimensions: elementwise, statistics per column; more: 'spatial', statistics per entry of the
+    second-to-last dimension, everything before it is batch."""
+    stats = [means, variances, scale, bias]
+    input_shape = input.shape()
+    if len(input_shape) == 1:
+        input_shape = [1, input_shape[0]]
+    _external_library_check("batch-normalize", output, input, *stats)
+    _require(float(epsilon) > 1e-5, "Epsilon cannot be smaller than 1e-5 (cudnn limitation", epsilon)
+    _ensure_vector_indexable(*stats)
+    stats = [as_row_vector(t) for t in stats]
+    _require(len(input_shape) > 1, "Input shape needs at least 2 dimensions", input.shape())
+    _require(output.shape() == input.shape(), "Tensor input and output shapes do not match",
+             (input.shape(), output.shape()))
+    _require(len({tuple(t.shape()) for t in stats}) == 1, "means, variances, scale, bias must have same shape",
+             [t.shape() for t in stats])
+    n_stats = stats[0].shape()[0]
+    stream = check_stream()
+    bufs = [t.buffer for t in stats]
+    if len(input_shape) == 2:
+        _require(input_shape[1] == n_stats, "Means, variances, scale, bias must match input element count.",
+                 (input_shape, n_stats))
+        stream.batch_normalize_eltwise(output.buffer, input.buffer, *bufs, epsilon, input_shape[0], input_shape[1])
+    else:
+        batch_count = 1
+        for v in input_shape[:-2]:
+            batch_count *= v
+        channel_count, element_count = input_shape[-2:]
+        _require(channel_count == n_stats, "means, variances, scale bias size must match input channel count",
+                 (input_shape, n_stats))
+        stream.batch_normalize_spatial(output.buffer, input.buffer, *bufs, epsilon, batch_count, channel_count,
+                                       element_count)
+    return output
+
+
 # ------------------------------ softmax! -------------------------------------------
 
 def softmax(output, input):

@@ -172,8 +172,17 @@ class CTensorMath:
         self._tm("gemv", DTYPE_CODE[c.dtype], c.ptr, int(inc_c), 1 if trans_a else 0, float(alpha), a.ptr,
                  int(a_row_count), int(a_col_count), int(a_colstride), x.ptr, int(inc_x), float(beta))
 
-    def batch_normalize_eltwise(self, *a):
-        self._unsupported("batch-normalize-eltwise!")
+    def batch_normalize_eltwise(self, output, input, means, variances, scale, bias, epsilon, batch_count, element_count):
+        self._tm("batch_normalize_eltwise", DTYPE_CODE[output.dtype], output.ptr, input.ptr, means.ptr, variances.ptr,
+                 scale.ptr, bias.ptr, float(epsilon), int(batch_count), int(element_count))
+
+    def batch_normalize_spatial(self, output, input, means, variances, scale, bias, epsilon, batch_count, channel_count,
+                                element_count):
+        self._tm("batch_normalize_spatial", DTYPE_CODE[output.dtype], output.ptr, input.ptr, means.ptr, variances.ptr,
+                 scale.ptr, bias.ptr, float(epsilon), int(batch_count), int(channel_count), int(element_count))
+
+    def batch_normalize_update(self, *a):
+        self._unsupported("batch-normalize-update-*!")
 
     def pooling_forward(self, *a):
         self._unsupported("pooling-forward!")

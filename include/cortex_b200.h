@@ -228,8 +228,20 @@ int cb200_gemv(cb200_stream* s, int dtype, void* c, int64_t inc_c, int trans_a, 
                const void* A, int64_t a_rows, int64_t a_cols, int64_t lda,
                const void* x, int64_t inc_x, double beta);
 
+/* batch-normalize-eltwise! / batch-normalize-spatial! (inference form; src/cortex/tensor/math.clj:125-148,
+ * cudnnBatchNormalizationForwardInference at src/cortex/compute/cuda/tensor_math.clj:662-730):
+ *   output = (input - mean[c]) * sqrt(1 / (variance[c] + epsilon)) * scale[c] + bias[c]
+ * dense buffers; eltwise: input [batch_count, element_count], c = column; spatial: input
+ * [batch_count, channel_count, element_count], c = channel.  Uses channel_count elements of stream scratch. */
+int cb200_batch_normalize_eltwise(cb200_stream* s, int dtype, void* output, const void* input, const void* means,
+                                  const void* variances, const void* scale, const void* bias, double epsilon,
+                                  int64_t batch_count, int64_t element_count);
+int cb200_batch_normalize_spatial(cb200_stream* s, int dtype, void* output, const void* input, const void* means,
+                                  const void* variances, const void* scale, const void* bias, double epsilon,
+                                  int64_t batch_count, int64_t channel_count, int64_t element_count);
+
 /* Protocol methods outside the dense-inference path return CB200_ERR_UNSUPPORTED:
- * batch-normalize-*, activation-gradient!, convolution-backward-*,
+ * batch-normalize-update-*, batch-normalize-gradients-*, activation-gradient!, convolution-backward-*,
  * pooling-*, rand!, lrn-* (src/cortex/tensor/math.clj:125-175, 205-250). */
 int cb200_unsupported(const char* method_name);
 

@@ -42,6 +42,7 @@ _SIGS = {
     "orc_binary_op": [_i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
     "orc_unary_reduce": [_i, _vp, _pd, _d, _vp, _pd, _i],
     "orc_gemm": [_i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d],
+    "orc_batch_normalize": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
     "orc_gemv": [_i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],
     "orc_ternary_op": [_i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
     "orc_softmax_eltwise": [_i, _vp, _pd, _vp, _pd],
@@ -145,6 +146,15 @@ class OracleStream(CTensorMath):
 
     def sync(self):
         pass
+
+    def batch_normalize_eltwise(self, output, input, means, variances, scale, bias, epsilon, batch_count, element_count):
+        _call("batch_normalize", DTYPE_CODE[output.dtype], output.ptr, input.ptr, means.ptr, variances.ptr, scale.ptr,
+              bias.ptr, float(epsilon), int(batch_count), int(element_count), 1)
+
+    def batch_normalize_spatial(self, output, input, means, variances, scale, bias, epsilon, batch_count, channel_count,
+                                element_count):
+        _call("batch_normalize", DTYPE_CODE[output.dtype], output.ptr, input.ptr, means.ptr, variances.ptr, scale.ptr,
+              bias.ptr, float(epsilon), int(batch_count), int(channel_count), int(element_count))
 
     # -- gemm: BLAS semantics (src/cortex/compute/cpu/tensor_math.clj:672-699) ---------------
     @staticmethod

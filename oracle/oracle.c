@@ -388,6 +388,25 @@ int orc_gemv(int dtype, void* c, int64_t incc, int ta, double alpha, const void*
   return 1;
 }
 
+/* ---- batch-normalize, inference form (cpu/tensor_math.clj:731-801) ---------------------------------
+ * inv_std = (T) sqrt(1 / (variance + (T)epsilon)); out = (T)(((x - mean) * inv_std) * scale + bias), every
+ * operation in double.  inner = 1 for the eltwise form (channels = element count). */
+#define BN_BODY(T) { const T* ip = (const T*)in; T* op_ = (T*)out; const T* mp = (const T*)means; const T* vp = (const T*)variances; \
+  const T* sp = (const T*)scale; const T* bp = (const T*)bias; double eps = (double)(T)epsilon; \
+  _Pragma("omp parallel for") for (int64_t c = 0; c < channels; ++c) { \
+    volatile double inv_std = (double)(T)sqrt(1.0 / ((double)vp[c] + eps)); double m = mp[c], g = sp[c], b = bp[c]; \
+    for (int64_t bi = 0; bi < batch; ++bi) for (int64_t e = 0; e < inner; ++e) { \
+      int64_t off = (bi * channels + c) * inner + e; \
+      volatile double x_hat = ((double)ip[off] - m) * inv_std; volatile double sc = x_hat * g; \
+      op_[off] = (T)(sc + b); } } return 0; }
+int orc_batch_normalize(int dtype, void* out, const void* in, const void* means, const void* variances,
+                        const void* scale, const void* bias, double epsilon, int64_t batch, int64_t channels,
+                        int64_t inner) {
+  if (dtype == T_FLOAT) BN_BODY(float)
+  if (dtype == T_DOUBLE) BN_BODY(double)
+  return 1;
+}
+
 /* ---- ternary select (cpu/tensor_math.clj:465-566) ------------------------------------------------
  * select-impl picks z when alpha*x >= 0, else y.  Tensor operands are multiplied by their factor (cast to
  * the element type) in the accumulator type (double / wrapping long).  A NULL pointer marks a constant

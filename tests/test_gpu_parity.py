@@ -251,3 +251,33 @@ def test_ternary_select_matches_oracle(b200_driver, oracle_driver, datatype):
     ref = np.where(X.astype(np.float64) >= 0, 3.0 * Z.astype(np.float64), 2.0 * Y.astype(np.float64))
     if npdt.kind == "f":
         assert pc.rel_err(g[0], ref.astype(npdt)) == 0.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("datatype", ["float", "double"])
+def test_batch_normalize_matches_oracle(b200_driver, oracle_driver, datatype):
+    """batch-normalize! inference form, eltwise and spatial, incl. a zero variance and ragged sizes:
+    bit-exact against the oracle (same double arithmetic, one final rounding)."""
+    npdt = np.float32 if datatype == "float" else np.float64
+    rng = np.random.default_rng(73)
+    for shape in ((128, 500), (33, 7), (64, 64, 56 * 56), (3, 5, 9), (2, 3, 16, 10)):
+        ch = shape[-1] if len(shape) == 2 else shape[-2]
+        X = rng.standard_normal(shape).astype(npdt)
+        mean = rng.standard_normal(ch).astype(npdt)
+        var = np.abs(rng.standard_normal(ch)).astype(npdt)
+        var[0] = 0
+        gamma, beta = rng.standard_normal(ch).astype(npdt), rng.standard_normal(ch).astype(npdt)
+
+        def run():
+            out = ct.new_tensor(list(shape), datatype)
+            ct.batch_normalize(out, ct.to_tensor(X, datatype), ct.to_tensor(mean, datatype), ct.to_tensor(var, datatype),
+                               ct.to_tensor(gamma, datatype), ct.to_tensor(beta, datatype), 1e-3)
+            return ct.to_array(out)
+
+        g, c = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
+        assert np.array_equal(g, c)
+        bshape = (1, ch) if len(shape) == 2 else (1,) * (len(shape) - 2) + (ch, 1)
+        eps = np.float64(npdt(1e-3))
+        ref = (X.astype(np.float64) - mean.reshape(bshape)) / np.sqrt(var.reshape(bshape).astype(np.float64) + eps) * \
+            gamma.reshape(bshape) + beta.reshape(bshape)
+        assert pc.rel_err(g.reshape(shape), ref) <= (1e-5 if datatype == "float" else 1e-12)

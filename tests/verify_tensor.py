@@ -273,6 +273,25 @@ def gemv(driver, datatype):
         _eq([144.0, 166.0, 188.0], ct.to_double_array(tens_c_sub))
 
 
+def batch_normalize(driver, datatype):
+    """verify/tensor.clj:309-347 (inference form; a variance of 0 is included on purpose)"""
+    with tensor_context(driver, datatype):
+        inp = ct.to_tensor(np.arange(12).reshape(4, 3))
+        out = ct.new_tensor([4, 3])
+        means, variances = ct.to_tensor([1] * 3), ct.to_tensor(list(range(3)))
+        scale, bias = ct.to_tensor([3] * 3), ct.to_tensor([4] * 3)
+        ct.batch_normalize(out, inp, means, variances, scale, bias, 1e-2)
+        _eq([-26.0, 4.0, 6.116036847575795, 64.0, 12.955334711889902, 12.46414739030318, 154.0, 21.910669423779805,
+             18.812257933030565, 244.0, 30.86600413566971, 25.16036847575795], ct.to_double_array(out), 1e-4)
+        inp = ct.to_tensor(np.arange(24).reshape(2, 3, 4))
+        out = ct.new_tensor([2, 3, 4])
+        ct.batch_normalize(out, inp, means, variances, scale, bias, 1e-2)
+        _eq([-26.0, 4.0, 34.0, 64.0, 12.955334711889902, 15.94044628251987, 18.925557853149837, 21.910669423779805,
+             18.812257933030565, 20.92829478060636, 23.044331628182157, 25.16036847575795, 334.0, 364.0, 394.0, 424.0,
+             48.77667355944951, 51.76178513007948, 54.74689670070945, 57.73200827133942, 44.204700103940105,
+             46.3207369515159, 48.436773799091696, 50.55281064666749], ct.to_double_array(out), 1e-4)
+
+
 def ternary_op_select(driver, datatype):
     """verify/tensor.clj:623-645"""
     with tensor_context(driver, datatype):
@@ -455,7 +474,7 @@ def magnitude_and_mag_squared(driver, datatype):
 CASES = [
     (assign_constant, ALL_DTYPES), (assign_marshal, ALL_DTYPES), (unary_op, ALL_DTYPES), (channel_op, ALL_DTYPES),
     (binary_constant_op, ALL_DTYPES), (binary_op, ALL_DTYPES), (gemm, FLOAT_DTYPES), (gemv, FLOAT_DTYPES),
-    (ternary_op_select, ALL_DTYPES),
+    (ternary_op_select, ALL_DTYPES), (batch_normalize, FLOAT_DTYPES),
     (activation_forward, FLOAT_DTYPES), (softmax, FLOAT_DTYPES), (unary_reduce, ALL_DTYPES), (transpose, ALL_DTYPES),
     (mask, INT_LONG), (select, ALL_DTYPES), (select_transpose_interaction, ALL_DTYPES),
     (convolution_operator, FLOAT_DTYPES), (indexed_tensor, ALL_DTYPES), (magnitude_and_mag_squared, FLOAT_DTYPES),
