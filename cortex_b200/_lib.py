@@ -34,6 +34,14 @@ class ConvDesc(C.Structure):
                                          "pad_x", "pad_y", "stride_x", "stride_y")]
 
 
+class PoolDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("kernel_width", "kernel_height", "pad_x", "pad_y", "stride_x", "stride_y",
+                                         "pool_op")]
+
+
+POOL_OPS = {"max": 0, "avg": 1, "avg-exc-pad": 2}
+
+
 class B200Error(RuntimeError):
     def __init__(self, code, message):
         super().__init__("cortex_b200 error %d: %s" % (code, message))
@@ -85,6 +93,7 @@ SIGNATURES = {
     "cb200_gemv": [_vp, _i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],
     "cb200_batch_normalize_eltwise": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64],
     "cb200_batch_normalize_spatial": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
+    "cb200_pooling_forward": [_vp, _i, _vp, _pd, _d, _vp, _pd, C.POINTER(PoolDesc)],
     "cb200_unsupported": [C.c_char_p],
     "cb200_gemm_bias_act": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i],
     "cb200_gemm_bias_act_peers": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i,

@@ -668,6 +668,33 @@ def _ensure_conv_io(conv_descriptor, input, output):
              (expected_out, output.shape()))
 
 
+POOL_OPERATIONS = ("max", "avg", "avg-exc-pad")
+
+
+def pooling_descriptor(datatype, channels, kern_width, kern_height, pad_x, pad_y, stride_x, stride_y,
+                       dimension_op="ceil", pool_op="max"):
+    """tensor.clj:1499-1524."""
+    _require(pool_op in POOL_OPERATIONS, "Max pooling layers have three possible pool operations:", pool_op)
+    _require(dimension_op in ("floor", "ceil"), "dimension-op must be :floor or :ceil", dimension_op)
+    desc = {"in-channels": channels, "out-channels": channels, "datatype": datatype, "kernel-width": kern_width,
+            "kernel-height": kern_height, "pad-x": pad_x, "pad-y": pad_y, "stride-x": stride_x, "stride-y": stride_y,
+            "pool-op": pool_op, "dimension-op": dimension_op}
+    _require(all(v is not None for v in desc.values()), "Arguments were nil:", desc)
+    desc["descriptor"] = check_stream().pooling_descriptor(datatype, kern_width, kern_height, pad_x, pad_y, stride_x,
+                                                           stride_y, pool_op, dimension_op)
+    return desc
+
+
+def pooling_forward(output, output_alpha, input, pool_descriptor):
+    """tensor.clj:1527-1538."""
+    _external_library_check("pooling-forward!", output, input)
+    _require(len(input.shape()) == 4 and len(output.shape()) == 4, "Input, output must be 4d tensors")
+    _ensure_conv_io(pool_descriptor, input, output)
+    check_stream().pooling_forward(output.buffer, output.dimensions, output_alpha, input.buffer, input.dimensions,
+                                   pool_descriptor)
+    return output
+
+
 def convolution_forward(output, output_alpha, input, weights, workspace, conv_descriptor, algorithms):
     """tensor.clj:1454-1466."""
     _external_library_check("convolution-forward!", output, input, weights)

@@ -184,8 +184,21 @@ class CTensorMath:
     def batch_normalize_update(self, *a):
         self._unsupported("batch-normalize-update-*!")
 
-    def pooling_forward(self, *a):
-        self._unsupported("pooling-forward!")
+    def pooling_descriptor(self, datatype, kern_width, kern_height, pad_x, pad_y, stride_x, stride_y, pool_op,
+                           dimension_op):
+        """The reference builds a cudnn descriptor here; this backend needs none."""
+        return None
+
+    def pooling_forward(self, output, output_dims, output_alpha, input, input_dims, pool_descriptor):
+        from ._lib import POOL_OPS, PoolDesc
+        d = pool_descriptor
+        desc = PoolDesc(d["kernel-width"], d["kernel-height"], d["pad-x"], d["pad-y"], d["stride-x"], d["stride-y"],
+                        POOL_OPS[d["pool-op"]])
+        self._tm("pooling_forward", DTYPE_CODE[output.dtype], output.ptr, C.byref(wire(output_dims)), float(output_alpha),
+                 input.ptr, C.byref(wire(input_dims)), C.byref(desc))
+
+    def pooling_backward(self, *a):
+        self._unsupported("pooling-backward!")
 
     def rand(self, *a):
         self._unsupported("rand!")

@@ -240,9 +240,20 @@ int cb200_batch_normalize_spatial(cb200_stream* s, int dtype, void* output, cons
                                   const void* variances, const void* scale, const void* bias, double epsilon,
                                   int64_t batch_count, int64_t channel_count, int64_t element_count);
 
+/* pooling-forward! (src/cortex/tensor/math.clj:205-222; cudnnPoolingForward at
+ * src/cortex/compute/cuda/tensor_math.clj:1096-1160).  NCHW dense tensors [batch, channels, h, w]; the output
+ * extent is the output tensor's (the caller applies the descriptor's :floor / :ceil rule).  Padding reads 0 and
+ * takes part in the maximum, as in the reference CPU backend.  output = result + output_alpha * output. */
+enum cb200_pool_op_t { CB200_POOL_MAX = 0, CB200_POOL_AVG = 1, CB200_POOL_AVG_EXC_PAD = 2 };
+typedef struct cb200_pool_desc {
+  int32_t kernel_width, kernel_height, pad_x, pad_y, stride_x, stride_y, pool_op;
+} cb200_pool_desc;
+int cb200_pooling_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, double out_alpha,
+                          const void* in, const cb200_dims* in_dims, const cb200_pool_desc* desc);
+
 /* Protocol methods outside the dense-inference path return CB200_ERR_UNSUPPORTED:
  * batch-normalize-update-*, batch-normalize-gradients-*, activation-gradient!, convolution-backward-*,
- * pooling-*, rand!, lrn-* (src/cortex/tensor/math.clj:125-175, 205-250). */
+ * pooling-backward!, rand!, lrn-* (src/cortex/tensor/math.clj:125-175, 205-250). */
 int cb200_unsupported(const char* method_name);
 
 /* ---- fused extras (no counterpart in the protocol) -------------------------

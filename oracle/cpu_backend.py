@@ -43,6 +43,7 @@ _SIGS = {
     "orc_unary_reduce": [_i, _vp, _pd, _d, _vp, _pd, _i],
     "orc_gemm": [_i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d],
     "orc_batch_normalize": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
+    "orc_pooling_forward": [_i, _vp, _vp] + [_i64] * 11 + [_i],
     "orc_gemv": [_i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],
     "orc_ternary_op": [_i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
     "orc_softmax_eltwise": [_i, _vp, _pd, _vp, _pd],
@@ -155,6 +156,15 @@ class OracleStream(CTensorMath):
                                 element_count):
         _call("batch_normalize", DTYPE_CODE[output.dtype], output.ptr, input.ptr, means.ptr, variances.ptr, scale.ptr,
               bias.ptr, float(epsilon), int(batch_count), int(channel_count), int(element_count))
+
+    def pooling_forward(self, output, output_dims, output_alpha, input, input_dims, pool_descriptor):
+        from cortex_b200._lib import POOL_OPS
+        batch, channels, in_h, in_w = input_dims["shape"]
+        _b, _c, out_h, out_w = output_dims["shape"]
+        d = pool_descriptor
+        _call("pooling_forward", DTYPE_CODE[output.dtype], output.ptr, input.ptr, batch * channels, in_h, in_w, out_h,
+              out_w, d["kernel-width"], d["kernel-height"], d["pad-x"], d["pad-y"], d["stride-x"], d["stride-y"],
+              POOL_OPS[d["pool-op"]])
 
     # -- gemm: BLAS semantics (src/cortex/compute/cpu/tensor_math.clj:672-699) ---------------
     @staticmethod

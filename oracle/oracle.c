@@ -407,6 +407,37 @@ int orc_batch_normalize(int dtype, void* out, const void* in, const void* means,
   return 1;
 }
 
+/* ---- pooling forward (cpu/tensor_math.clj:1153-1261 over the loop nest of nn/impl.clj:8-107) ----------
+ * Per (plane, out-y, out-x), window positions in (k-y, k-x) order; positions outside [-pad, extent + pad)
+ * are skipped, positions in the padding read 0.  max: the first visited position initialises, later ones
+ * replace when greater.  avg: out = (T)(out + x / (kW*kH)), out reset at window position 0.
+ * avg-exc-pad: out = (T)(out + x / n_inside) WITHOUT a reset: the reference accumulates onto whatever the
+ * output holds (its callers pass a zeroed tensor); output-alpha is not used by the CPU backend. */
+#define POOL_BODY(T) { const T* ip = (const T*)in; T* op_ = (T*)out; \
+  _Pragma("omp parallel for") for (int64_t plane = 0; plane < planes; ++plane) { \
+    const T* src = ip + plane * in_h * in_w; T* dst = op_ + plane * out_h * out_w; \
+    for (int64_t oy = 0; oy < out_h; ++oy) for (int64_t ox = 0; ox < out_w; ++ox) { \
+      int64_t rel_x = ox * stride_x - pad_x, rel_y = oy * stride_y - pad_y; \
+      int64_t over_x = rel_x + kw - in_w; if (over_x < 0) over_x = 0; int64_t over_y = rel_y + kh - in_h; if (over_y < 0) over_y = 0; \
+      int64_t under_x = rel_x < 0 ? rel_x : 0, under_y = rel_y < 0 ? rel_y : 0; \
+      int64_t exc_w = kw - over_x + under_x; if (exc_w < 0) exc_w = 0; int64_t exc_h = kh - over_y + under_y; if (exc_h < 0) exc_h = 0; \
+      T* o = dst + oy * out_w + ox; \
+      for (int64_t ky = 0; ky < kh; ++ky) for (int64_t kx = 0; kx < kw; ++kx) { \
+        int64_t ix = rel_x + kx, iy = rel_y + ky; \
+        if (ix < -pad_x || ix >= in_w + pad_x || iy < -pad_y || iy >= in_h + pad_y) continue; \
+        int inside = ix >= 0 && ix < in_w && iy >= 0 && iy < in_h; \
+        T v = inside ? src[iy * in_w + ix] : (T)0; int64_t kidx = ky * kw + kx; \
+        if (op == 0) { if (kidx == 0 || v > *o) *o = v; } \
+        else if (op == 1) { T prev = kidx == 0 ? (T)0 : *o; *o = (T)((double)prev + (double)v / (double)(kw * kh)); } \
+        else { *o = (T)((double)*o + (double)v / (double)(exc_w * exc_h)); } } } } return 0; }
+int orc_pooling_forward(int dtype, void* out, const void* in, int64_t planes, int64_t in_h, int64_t in_w, int64_t out_h,
+                        int64_t out_w, int64_t kw, int64_t kh, int64_t pad_x, int64_t pad_y, int64_t stride_x,
+                        int64_t stride_y, int op) {
+  if (dtype == T_FLOAT) POOL_BODY(float)
+  if (dtype == T_DOUBLE) POOL_BODY(double)
+  return 1;
+}
+
 /* ---- ternary select (cpu/tensor_math.clj:465-566) ------------------------------------------------
  * select-impl picks z when alpha*x >= 0, else y.  Tensor operands are multiplied by their factor (cast to
  * the element type) in the accumulator type (double / wrapping long).  A NULL pointer marks a constant

@@ -281,3 +281,28 @@ def test_batch_normalize_matches_oracle(b200_driver, oracle_driver, datatype):
         ref = (X.astype(np.float64) - mean.reshape(bshape)) / np.sqrt(var.reshape(bshape).astype(np.float64) + eps) * \
             gamma.reshape(bshape) + beta.reshape(bshape)
         assert pc.rel_err(g.reshape(shape), ref) <= (1e-5 if datatype == "float" else 1e-12)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("datatype", ["float", "double"])
+@pytest.mark.parametrize("pool_op", ["max", "avg", "avg-exc-pad"])
+def test_pooling_forward_matches_oracle(b200_driver, oracle_driver, datatype, pool_op):
+    """pooling-forward!: several geometries incl. ceil-mode output sizes, non-square windows and strides;
+    bit-exact against the oracle (same position-by-position arithmetic)."""
+    npdt = np.float32 if datatype == "float" else np.float64
+    rng = np.random.default_rng(74)
+    for (batch, ch, h, w, kw, kh, px, py, sx, sy, dim_op) in (
+            (2, 4, 4, 4, 3, 3, 1, 1, 2, 2, "floor"), (3, 5, 13, 17, 3, 2, 1, 0, 2, 3, "ceil"),
+            (2, 16, 56, 56, 3, 3, 1, 1, 2, 2, "ceil"), (1, 3, 9, 9, 2, 2, 0, 0, 2, 2, "floor"),
+            (2, 2, 7, 7, 7, 7, 0, 0, 1, 1, "floor")):
+        X = rng.standard_normal((batch, ch, h, w)).astype(npdt)
+
+        def run():
+            desc = ct.pooling_descriptor(datatype, ch, kw, kh, px, py, sx, sy, dimension_op=dim_op, pool_op=pool_op)
+            od = ct.get_convolution_output_dimensions(desc, h, w)
+            out = ct.new_tensor([batch, ch, od["output-width"], od["output-height"]], datatype)
+            ct.pooling_forward(out, 0.0, ct.to_tensor(X, datatype), desc)
+            return ct.to_array(out)
+
+        g, c = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
+        assert np.array_equal(g, c)

@@ -292,6 +292,33 @@ def batch_normalize(driver, datatype):
              46.3207369515159, 48.436773799091696, 50.55281064666749], ct.to_double_array(out), 1e-4)
 
 
+def pooling_operator(driver, datatype):
+    """verify/tensor.clj:893-947 (forward half)"""
+    with tensor_context(driver, datatype):
+        channels, dimension, batch = 4, 4, 2
+        n = batch * channels * dimension * dimension
+        data = np.resize(np.arange(-5, 15), n).reshape(batch, channels, dimension, dimension)
+        inp = ct.to_tensor(data)
+        outs = {}
+        for op in ("max", "avg", "avg-exc-pad"):
+            desc = ct.pooling_descriptor(datatype, channels, 3, 3, 1, 1, 2, 2, pool_op=op, dimension_op="floor")
+            od = ct.get_convolution_output_dimensions(desc, dimension, dimension)
+            out = ct.new_tensor([batch, channels, od["output-width"], od["output-height"]])
+            ct.pooling_forward(out, 0.0, inp, desc)
+            outs[op] = ct.to_double_array(out)
+        _eq([0.0, 2.0, 8.0, 10.0, 12.0, 14.0, 4.0, 6.0, 12.0, 14.0, 12.0, 14.0, 8.0, 10.0, 12.0, 14.0, 4.0, 6.0, 12.0,
+             14.0, 0.0, 2.0, 8.0, 10.0, 12.0, 14.0, 4.0, 6.0, 12.0, 14.0, 12.0, 14.0], outs["max"])
+        _eq([-1.1111111111111112, -0.6666666666666666, 2.3333333333333335, 5.0, 1.5555555555555556,
+             3.3333333333333335, -0.3333333333333333, 1.0, 4.222222222222222, 7.333333333333333, 1.4444444444444444,
+             3.6666666666666665, 2.4444444444444446, 4.666666666666667, 3.2222222222222223, 6.333333333333333,
+             0.6666666666666666, 2.0, 5.0, 9.0, -1.1111111111111112, -0.6666666666666666, 2.3333333333333335, 5.0,
+             1.5555555555555556, 3.3333333333333335, -0.3333333333333333, 1.0, 4.222222222222222, 7.333333333333333,
+             1.4444444444444444, 3.6666666666666665], outs["avg"], 1e-4)
+        _eq([-2.5, -1.0, 3.5, 5.0, 3.5, 5.0, -0.5, 1.0, 9.5, 11.0, 2.1666666666666665, 3.6666666666666665, 5.5, 7.0,
+             4.833333333333333, 6.333333333333333, 1.5, 3.0, 7.5, 9.0, -2.5, -1.0, 3.5, 5.0, 3.5, 5.0, -0.5, 1.0, 9.5,
+             11.0, 2.1666666666666665, 3.6666666666666665], outs["avg-exc-pad"], 1e-4)
+
+
 def ternary_op_select(driver, datatype):
     """verify/tensor.clj:623-645"""
     with tensor_context(driver, datatype):
@@ -474,7 +501,7 @@ def magnitude_and_mag_squared(driver, datatype):
 CASES = [
     (assign_constant, ALL_DTYPES), (assign_marshal, ALL_DTYPES), (unary_op, ALL_DTYPES), (channel_op, ALL_DTYPES),
     (binary_constant_op, ALL_DTYPES), (binary_op, ALL_DTYPES), (gemm, FLOAT_DTYPES), (gemv, FLOAT_DTYPES),
-    (ternary_op_select, ALL_DTYPES), (batch_normalize, FLOAT_DTYPES),
+    (ternary_op_select, ALL_DTYPES), (batch_normalize, FLOAT_DTYPES), (pooling_operator, FLOAT_DTYPES),
     (activation_forward, FLOAT_DTYPES), (softmax, FLOAT_DTYPES), (unary_reduce, ALL_DTYPES), (transpose, ALL_DTYPES),
     (mask, INT_LONG), (select, ALL_DTYPES), (select_transpose_interaction, ALL_DTYPES),
     (convolution_operator, FLOAT_DTYPES), (indexed_tensor, ALL_DTYPES), (magnitude_and_mag_squared, FLOAT_DTYPES),
