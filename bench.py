@@ -261,10 +261,10 @@ def bench_eltwise(drv, dev, peaks):
         bn_out = [ct.in_place_reshape(y, [128, 64, 4096]) for y in ys]
         cases["batch_normalize_spatial"] = (lambda i: ct.batch_normalize(bn_out[i], bn_in[i], *bn_stats, 1e-3),
                                             2 * rows * cols * 4)
-        # pooling-forward!: 3x3 max, stride 2, pad 1 on [32, 64, 64, 64]
+        # pooling-forward!: 3x3 max, stride 2, pad 1 on [128, 64, 64, 64]
         pool_desc = ct.pooling_descriptor("float", 64, 3, 3, 1, 1, 2, 2, dimension_op="floor", pool_op="max")
-        pool_in = [ct.in_place_reshape(x, [32, 64, 64, 64]) for x in xs]       # [8192, 4096] = 32 x 64 x 64 x 64
-        pool_out = [ct.new_tensor([32, 64, 32, 32]) for _ in range(sets)]
+        pool_in = [ct.in_place_reshape(x, [128, 64, 64, 64]) for x in xs]      # [8192, 4096] = 128 x 64 x 64 x 64
+        pool_out = [ct.new_tensor([128, 64, 32, 32]) for _ in range(sets)]
         cases["pooling_max_3x3s2"] = (lambda i: ct.pooling_forward(pool_out[i], 0.0, pool_in[i], pool_desc),
                                       rows * cols * 4 + rows * cols)
         for name, (fn, nbytes) in cases.items():

@@ -16,40 +16,120 @@ struct PoolGeom {
   int channels, in_h, in_w, out_h, out_w, kw, kh, pad_x, pad_y, stride_x, stride_y, op;
 };
 
-template <typename T>
+// Window positions are visited in (k-y, k-x) order as in the reference, but the bounds tests are hoisted:
+// only positions inside the image are loaded.  Skipping the padding positions changes nothing for the
+// averages (they add 0 / divisor to the running sum: the identity) and for the maximum they only add the
+// candidate 0, folded in once.
+template <typename T, int OP>
 __global__ void __launch_bounds__(256)
 pooling_forward_kernel(T* out, const T* in, PoolGeom g, long long n_out, double out_alpha) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_out; i += (long long)gridDim.x * blockDim.x) {
-    const int ox = (int)(i % g.out_w);
-    const long long t = i / g.out_w;
-    const int oy = (int)(t % g.out_h);
-    const long long plane = t / g.out_h;                 // batch * channels + channel
+    // 32-bit index arithmetic (the entry point limits the output to 2^31 - 1 elements)
+    const unsigned iu = (unsigned)i;
+    const unsigned tq = iu / (unsigned)g.out_w;
+    const int ox = (int)(iu - tq * (unsigned)g.out_w);
+    const unsigned plane_u = tq / (unsigned)g.out_h;
+    const int oy = (int)(tq - plane_u * (unsigned)g.out_h);
+    const long long plane = plane_u;
     const T* src = in + plane * (long long)g.in_h * g.in_w;
     const int rel_x = ox * g.stride_x - g.pad_x, rel_y = oy * g.stride_y - g.pad_y;
-    const int over_x = max(0, rel_x + g.kw - g.in_w), over_y = max(0, rel_y + g.kh - g.in_h);
-    const int under_x = min(rel_x, 0), under_y = min(rel_y, 0);
-    const int exc_w = max(0, g.kw - over_x + under_x), exc_h = max(0, g.kh - over_y + under_y);
-    const double divisor = g.op == CB200_POOL_AVG ? (double)(g.kw * g.kh) : (double)(exc_w * exc_h);
+    // rows / columns of the window inside the image, and inside the padded extent
+    const int y0 = max(rel_y, 0), y1 = min(rel_y + g.kh, g.in_h);
+    const int x0 = max(rel_x, 0), x1 = min(rel_x + g.kw, g.in_w);
+    const int py1 = min(rel_y + g.kh, g.in_h + g.pad_y), px1 = min(rel_x + g.kw, g.in_w + g.pad_x);
+    const int inside = max(0, y1 - y0) * max(0, x1 - x0);
+    const int visited = max(0, py1 - rel_y) * max(0, px1 - rel_x);     // rel >= -pad always
     T acc = (T)0;
-    bool first = true;
-    for (int ky = 0; ky < g.kh; ++ky) {
-      const int iy = rel_y + ky;
-      if (iy < -g.pad_y || iy >= g.in_h + g.pad_y) continue;
-      for (int kx = 0; kx < g.kw; ++kx) {
-        const int ix = rel_x + kx;
-        if (ix < -g.pad_x || ix >= g.in_w + g.pad_x) continue;
-        const bool inside = iy >= 0 && iy < g.in_h && ix >= 0 && ix < g.in_w;
-        const T v = inside ? src[(long long)iy * g.in_w + ix] : (T)0;
-        if (g.op == CB200_POOL_MAX) {
+    if (OP == CB200_POOL_MAX) {
+      bool first = true;
+      for (int iy = y0; iy < y1; ++iy)
+        for (int ix = x0; ix < x1; ++ix) {
+          const T v = src[(long long)iy * g.in_w + ix];
           if (first || v > acc) acc = v;
-        } else {
-          acc = (T)((double)acc + (double)v / divisor);
+          first = false;
         }
-        first = false;
-      }
+      if (visited > inside && (first || (T)0 > acc)) acc = (T)0;       // padding positions read 0
+    } else {
+      const double divisor = OP == CB200_POOL_AVG ? (double)(g.kw * g.kh) : (double)inside;
+      for (int iy = y0; iy < y1; ++iy)
+        for (int ix = x0; ix < x1; ++ix)
+          acc = (T)((double)acc + (double)src[(long long)iy * g.in_w + ix] / divisor);
+      if (OP == CB200_POOL_AVG_EXC_PAD && inside == 0 && visited > 0) acc = (T)((double)acc + 0.0 / divisor);   // 0/0 as the reference
     }
     out[i] = out_alpha == 0.0 ? acc : (T)((double)acc + out_alpha * (double)out[i]);
   }
+}
+
+// 2x2 and 3x3 windows (the common ones): the window is loaded with independent, predicated loads first
+// (all in flight together) and folded afterwards in the same (k-y, k-x) order.
+template <typename T, int OP, int KH, int KW>
+__global__ void __launch_bounds__(256)
+pooling_forward_small_kernel(T* out, const T* in, PoolGeom g, long long n_out, double out_alpha) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_out; i += (long long)gridDim.x * blockDim.x) {
+    // 32-bit index arithmetic (the entry point limits the output to 2^31 - 1 elements)
+    const unsigned iu = (unsigned)i;
+    const unsigned tq = iu / (unsigned)g.out_w;
+    const int ox = (int)(iu - tq * (unsigned)g.out_w);
+    const unsigned plane_u = tq / (unsigned)g.out_h;
+    const int oy = (int)(tq - plane_u * (unsigned)g.out_h);
+    const long long plane = plane_u;
+    const T* src = in + plane * (long long)g.in_h * g.in_w;
+    const int rel_x = ox * g.stride_x - g.pad_x, rel_y = oy * g.stride_y - g.pad_y;
+    T v[KH * KW];
+    bool ok[KH * KW];
+    // row / column validity once per k-y / k-x, 32-bit offsets inside the plane
+    bool row_ok[KH], col_ok[KW];
+    int n_rows = 0, n_cols = 0;
+#pragma unroll
+    for (int ky = 0; ky < KH; ++ky) { row_ok[ky] = (unsigned)(rel_y + ky) < (unsigned)g.in_h; n_rows += row_ok[ky] ? 1 : 0; }
+#pragma unroll
+    for (int kx = 0; kx < KW; ++kx) { col_ok[kx] = (unsigned)(rel_x + kx) < (unsigned)g.in_w; n_cols += col_ok[kx] ? 1 : 0; }
+    const int inside = n_rows * n_cols;
+    const int base = rel_y * g.in_w + rel_x;
+#pragma unroll
+    for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+      for (int kx = 0; kx < KW; ++kx) {
+        const bool in_img = row_ok[ky] && col_ok[kx];
+        ok[ky * KW + kx] = in_img;
+        v[ky * KW + kx] = in_img ? src[base + ky * g.in_w + kx] : (T)0;
+      }
+    const int py1 = min(rel_y + KH, g.in_h + g.pad_y), px1 = min(rel_x + KW, g.in_w + g.pad_x);
+    const int visited = max(0, py1 - rel_y) * max(0, px1 - rel_x);
+    T acc = (T)0;
+    if (OP == CB200_POOL_MAX) {
+      bool first = true;
+#pragma unroll
+      for (int k = 0; k < KH * KW; ++k)
+        if (ok[k]) { if (first || v[k] > acc) acc = v[k]; first = false; }
+      if (visited > inside && (first || (T)0 > acc)) acc = (T)0;
+    } else {
+      const double divisor = OP == CB200_POOL_AVG ? (double)(KW * KH) : (double)inside;
+#pragma unroll
+      for (int k = 0; k < KH * KW; ++k)
+        if (ok[k]) acc = (T)((double)acc + (double)v[k] / divisor);
+      if (OP == CB200_POOL_AVG_EXC_PAD && inside == 0 && visited > 0) acc = (T)((double)acc + 0.0 / divisor);
+    }
+    out[i] = out_alpha == 0.0 ? acc : (T)((double)acc + out_alpha * (double)out[i]);
+  }
+}
+
+template <typename T, int OP>
+void pooling_launch_op(cb200_stream* s, T* out, const T* in, const PoolGeom& g, long long n_out, double out_alpha,
+                       unsigned blocks) {
+  if (g.kh == 3 && g.kw == 3)
+    pooling_forward_small_kernel<T, OP, 3, 3><<<blocks, 256, 0, s->stream>>>(out, in, g, n_out, out_alpha);
+  else if (g.kh == 2 && g.kw == 2)
+    pooling_forward_small_kernel<T, OP, 2, 2><<<blocks, 256, 0, s->stream>>>(out, in, g, n_out, out_alpha);
+  else
+    pooling_forward_kernel<T, OP><<<blocks, 256, 0, s->stream>>>(out, in, g, n_out, out_alpha);
+}
+
+template <typename T>
+void pooling_launch(cb200_stream* s, T* out, const T* in, const PoolGeom& g, long long n_out, double out_alpha, unsigned blocks) {
+  if (g.op == CB200_POOL_MAX) pooling_launch_op<T, CB200_POOL_MAX>(s, out, in, g, n_out, out_alpha, blocks);
+  else if (g.op == CB200_POOL_AVG) pooling_launch_op<T, CB200_POOL_AVG>(s, out, in, g, n_out, out_alpha, blocks);
+  else pooling_launch_op<T, CB200_POOL_AVG_EXC_PAD>(s, out, in, g, n_out, out_alpha, blocks);
 }
 
 }  // namespace
@@ -85,14 +165,13 @@ extern "C" int cb200_pooling_forward(cb200_stream* s, int dtype, void* out, cons
   g.stride_x = desc->stride_x; g.stride_y = desc->stride_y; g.op = desc->pool_op;
   const long long n_out = (long long)out_dims->rev_shape[3] * out_dims->rev_shape[2] * g.out_h * g.out_w;
   if (n_out == 0) return CB200_OK;
+  CB_REQUIRE(n_out <= 2147483647LL, "pooling_forward: output has more than 2^31 - 1 elements");
   DeviceGuard guard(s->device);
   long long blocks = (n_out + 255) / 256;
   const long long cap = (long long)s->sm_count * 32;
   if (blocks > cap) blocks = cap;
-  if (dtype == CB200_FLOAT)
-    pooling_forward_kernel<float><<<(unsigned)blocks, 256, 0, s->stream>>>((float*)out, (const float*)in, g, n_out, out_alpha);
-  else
-    pooling_forward_kernel<double><<<(unsigned)blocks, 256, 0, s->stream>>>((double*)out, (const double*)in, g, n_out, out_alpha);
+  if (dtype == CB200_FLOAT) pooling_launch<float>(s, (float*)out, (const float*)in, g, n_out, out_alpha, (unsigned)blocks);
+  else pooling_launch<double>(s, (double*)out, (const double*)in, g, n_out, out_alpha, (unsigned)blocks);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }

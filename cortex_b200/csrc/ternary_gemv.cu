@@ -58,9 +58,21 @@ ternary_select_flat_kernel(T* dest, const T* x, double xf, const T* y, double yf
     if (z) zv = reinterpret_cast<const V*>(z)[i];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
-      double a = x ? (double)xv.v[e] * xf : xf, b = y ? (double)yv.v[e] * yf : yf, c = z ? (double)zv.v[e] * zf : zf;
-      if (cast_first) { a = (double)(T)a; b = (double)(T)b; c = (double)(T)c; }
-      o.v[e] = (T)((a >= 0.0) ? c : b);
+      if (sizeof(T) == 4) {
+        // fp32: the product of two floats is exact in double, so (float)((double)v * f) is the fp32 product:
+        // no conversions needed.  Without cast_first the reference compares the unrounded product with 0,
+        // which only differs from the rounded one when it underflows: decide that case by the signs.
+        const float xfl = (float)xf, yfl = (float)yf, zfl = (float)zf;
+        const float a = x ? (float)xv.v[e] * xfl : xfl;
+        bool nonneg = a >= 0.f;
+        if (!cast_first && x && a == 0.f) nonneg = (float)xv.v[e] == 0.f || xfl == 0.f || (((float)xv.v[e] > 0.f) == (xfl > 0.f));
+        const float b = y ? (float)yv.v[e] * yfl : yfl, c = z ? (float)zv.v[e] * zfl : zfl;
+        o.v[e] = (T)(nonneg ? c : b);
+      } else {
+        double a = x ? (double)xv.v[e] * xf : xf, b = y ? (double)yv.v[e] * yf : yf, c = z ? (double)zv.v[e] * zf : zf;
+        if (cast_first) { a = (double)(T)a; b = (double)(T)b; c = (double)(T)c; }
+        o.v[e] = (T)((a >= 0.0) ? c : b);
+      }
     }
     reinterpret_cast<V*>(dest)[i] = o;
   }
@@ -91,12 +103,25 @@ gemv_n_kernel(T* c, long long incc, T alpha, const T* A, int rows, int cols, lon
     if (vec) {
       struct alignas(16) V { T v[VEC]; };
       const int nv = cols / VEC;
-      for (int j = lane; j < nv; j += 32) {
+      T acc1 = (T)0, acc2 = (T)0, acc3 = (T)0;
+      int j = lane;
+      for (; j + 96 < nv; j += 128) {            // four 16-byte loads of the row in flight per lane
+        const V a0 = reinterpret_cast<const V*>(row)[j], a1 = reinterpret_cast<const V*>(row)[j + 32];
+        const V a2 = reinterpret_cast<const V*>(row)[j + 64], a3 = reinterpret_cast<const V*>(row)[j + 96];
+        const V b0 = reinterpret_cast<const V*>(x)[j], b1 = reinterpret_cast<const V*>(x)[j + 32];
+        const V b2 = reinterpret_cast<const V*>(x)[j + 64], b3 = reinterpret_cast<const V*>(x)[j + 96];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          acc += a0.v[e] * b0.v[e]; acc1 += a1.v[e] * b1.v[e]; acc2 += a2.v[e] * b2.v[e]; acc3 += a3.v[e] * b3.v[e];
+        }
+      }
+      for (; j < nv; j += 32) {
         const V a = reinterpret_cast<const V*>(row)[j];
         const V b = reinterpret_cast<const V*>(x)[j];
 #pragma unroll
         for (int e = 0; e < VEC; ++e) acc += a.v[e] * b.v[e];
       }
+      acc = (acc + acc1) + (acc2 + acc3);
     } else {
       for (int j = lane; j < cols; j += 32) acc += row[j] * x[(long long)j * incx];
     }
