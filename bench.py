@@ -345,6 +345,42 @@ def bench_mlp_128(drv, dev):
     return res
 
 
+def bench_mnist_convnet(drv, dev):
+    """The reference's MNIST-NETWORK shape (conv 5x5 -> max-pool -> batch-norm -> ReLU -> conv 5x5 -> max-pool ->
+    batch-norm -> linear 500 + ReLU -> linear 10 -> softmax), batch 128, inference."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import parity_cases as pc
+    from cortex_b200 import tensor as ct
+    stream = dev.create_stream()
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        # the case builder returns a closure that rebuilds the network; time a prebuilt one instead
+        from cortex_b200 import nn
+        rng = np.random.default_rng(601)
+        t = lambda a: ct.to_tensor(np.asarray(a, np.float32))
+        he = lambda shape, fan: rng.standard_normal(shape) * np.sqrt(2.0 / fan)
+        bn = lambda n: [t(rng.standard_normal(n) * 0.1), t(np.abs(rng.standard_normal(n)) + 0.5),
+                        t(1 + 0.1 * rng.standard_normal(n)), t(rng.standard_normal(n) * 0.1)]
+        net = nn.ConvNet([
+            ("conv", nn.Convolution(t(he((20, 25), 25)), t(np.zeros(20)), (5, 5), (0, 0), (1, 1), 1, 20, "float")),
+            ("pool", nn.Pooling(20, (2, 2), (0, 0), (2, 2), "float")), ("bn", nn.BatchNormalization(*bn(20))), ("relu",),
+            ("conv", nn.Convolution(t(he((50, 500), 500)), t(np.zeros(50)), (5, 5), (0, 0), (1, 1), 20, 50, "float")),
+            ("pool", nn.Pooling(50, (2, 2), (0, 0), (2, 2), "float")), ("flatten",), ("bn", nn.BatchNormalization(*bn(800))),
+            ("linear", nn.Linear(t(he((500, 800), 800)), t(np.zeros(500))), "relu"),
+            ("linear", nn.Linear(t(he((10, 500), 500)), t(np.zeros(10))), None), ("softmax",)])
+        x = t(rng.random((128, 1, 28, 28)))
+        for _ in range(3):
+            net.infer(x)
+        l0 = stream.launch_count()
+        ms = time_region(stream, lambda: net.infer(x), 50)
+        launches = (stream.launch_count() - l0) // 50
+        for _ in range(3):
+            net.infer_replayed(x)
+        ms_g = time_region(stream, lambda: net.infer_replayed(x), 200)
+    return {"us_per_forward": round(ms * 1000.0, 1), "samples_per_s": round(128 / ms * 1000.0, 0),
+            "launches_per_forward": launches, "graph_replay_us_per_forward": round(ms_g * 1000.0, 1),
+            "graph_replay_samples_per_s": round(128 / ms_g * 1000.0, 0)}
+
+
 def bench_mlp_layer(drv, dev, peaks):
     """One hidden layer of the wide MLP on an 8192-row shard (the N=8 shard): the fused
     gemm_bias_act launch the benchmark's roofline is quoted on, small enough for an ncu capture."""
@@ -597,6 +633,7 @@ def run_b200(args, rank, world, local_rank):
         line["conv_64x64x56x56"] = bench_conv(drv, dev, peaks)
         line["mlp_128x784_500_10"] = bench_mlp_128(drv, dev)
         line["wide_mlp_fp64"] = bench_mlp_f64(drv, dev)
+        line["mnist_convnet_128"] = bench_mnist_convnet(drv, dev)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -610,7 +647,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--dtype", default="float", choices=["float", "double"],
                     help="float = the headline workload; double = its fp64 variant (DMMA gemm)")
-    ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128", "mlplayer"],
+    ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128", "mlplayer", "mnistcnn"],
                     help="mlp = the benchmark; gemm4096 / eltwise = the small single-purpose runs used for ncu captures")
     args = ap.parse_args()
     if args.case != "mlp":
@@ -620,7 +657,7 @@ def main():
         peaks = measured_peaks()
         fns = {"gemm4096": lambda: bench_gemm_4096(drv, dev, peaks), "eltwise": lambda: bench_eltwise(drv, dev, peaks),
                "conv": lambda: bench_conv(drv, dev, peaks), "gemm4096f64": lambda: bench_gemm_f64(drv, dev),
-               "mlp128": lambda: bench_mlp_128(drv, dev), "mlplayer": lambda: bench_mlp_layer(drv, dev, peaks)}
+               "mlp128": lambda: bench_mlp_128(drv, dev), "mlplayer": lambda: bench_mlp_layer(drv, dev, peaks), "mnistcnn": lambda: bench_mnist_convnet(drv, dev)}
         print(json.dumps({args.case: fns[args.case]()}), flush=True)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

@@ -110,11 +110,11 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
   const long long rows = (long long)g.batch * hw;
   CB_REQUIRE(rows <= 2147483647LL, "convolution_forward: more than 2^31-1 output pixels");
   if (rows == 0 || cout == 0) return CB200_OK;
-  if (dtype == CB200_FLOAT && (((uintptr_t)w) & 15) == 0 && (g.kcols % 4) == 0)
+  if (dtype == CB200_FLOAT)
     return cb200_conv_igemm_launch(s, (float*)out, (const float*)in, (const float*)w, g.batch, g.cin, g.in_h, g.in_w,
                                    cout, g.out_h, g.out_w, g.kh, g.kw, g.pad_x, g.pad_y, g.stride_x, g.stride_y,
                                    (float)out_alpha);
-  const size_t es = dtype == CB200_FLOAT ? 4 : 8;
+  const size_t es = 8;
   const long long total = rows * g.ld;
   void* cols = nullptr;
   int rc = cb200_scratch(s, (size_t)total * es, &cols);
@@ -122,17 +122,7 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
   DeviceGuard guard(s->device);
   long long blocks = (total + 255) / 256, cap = (long long)s->sm_count * 32;
   if (blocks > cap) blocks = cap;
-  if (dtype == CB200_FLOAT) {
-    im2col_kernel<float><<<(unsigned)blocks, 256, 0, s->stream>>>((float*)cols, (const float*)in, g, total);
-    CB_LAUNCH_CHECK(s);
-    for (int n = 0; n < g.batch; ++n) {
-      rc = cb200_gemm_simt_f32_launch(s, (float*)out + (long long)n * cout * hw, hw, 0, 1, 1.0f, (const float*)w, cout,
-                                      g.kcols, g.kcols, (const float*)cols + (long long)n * hw * g.ld, hw, g.ld,
-                                      (float)out_alpha);
-      if (rc) return rc;
-    }
-    return CB200_OK;
-  }
+  // fp64: im2col into the stream's scratch, then one DMMA GEMM per image as the reference does
   im2col_kernel<double><<<(unsigned)blocks, 256, 0, s->stream>>>((double*)cols, (const double*)in, g, total);
   CB_LAUNCH_CHECK(s);
   for (int n = 0; n < g.batch; ++n) {

@@ -409,6 +409,15 @@ int launch_conv(cb200_stream* s, const CUtensorMap& tmW, const CUtensorMap& tmWl
   return CB200_OK;
 }
 
+// W[cout][K] -> padded[cout][K4], zero-filled (the generic gather zero-fills k >= K on the A side as well)
+__global__ void conv_pad_weights_kernel(const float* __restrict__ w, float* __restrict__ padded, int cout, int K, int K4) {
+  const int total = cout * K4;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int co = i / K4, k = i - co * K4;
+    padded[i] = k < K ? w[(long long)co * K + k] : 0.f;
+  }
+}
+
 int encode_weights(CUtensorMap* tm, const float* w, int K, int cout, int BN) {
   EncodeTiledFn fn = conv_encode_fn();
   if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
@@ -425,8 +434,8 @@ int encode_weights(CUtensorMap* tm, const float* w, int K, int cout, int BN) {
 
 }  // namespace
 
-// Dense NCHW fp32 input/output, weights [cout][cin*kh*kw] with a 16-byte aligned base and
-// cin*kh*kw a multiple of 4 (checked by the caller).
+// Dense NCHW fp32 input/output, weights [cout][cin*kh*kw] (rows that TMA cannot address -- length not a
+// multiple of 4, or an unaligned base -- are copied, zero-padded, into the stream's scratch first).
 int cb200_conv_igemm_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                             int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
                             int stride_x, int stride_y, float out_alpha) {
@@ -460,7 +469,22 @@ int cb200_conv_igemm_launch(cb200_stream* s, float* out, const float* in, const 
     if (BN == 128) return launch_conv<128, true>(s, tmW, tmWlo, p);
     return launch_conv<64, true>(s, tmW, tmWlo, p);
   }
-  rc = encode_weights(&tmW, w, p.K, cout, BN);
+  const float* w_use = w;
+  int k_pitch = p.K;
+  if ((p.K % 4) != 0 || (((uintptr_t)w) & 15) != 0) {
+    // TMA wants 16-byte aligned rows: copy the weights into the stream's scratch with the row length rounded up to 4
+    k_pitch = (p.K + 3) & ~3;
+    void* scratch = nullptr;
+    rc = cb200_scratch(s, (size_t)cout * k_pitch * sizeof(float), &scratch);
+    if (rc) return rc;
+    const int total = cout * k_pitch;
+    int blocks = (total + 255) / 256;
+    if (blocks > s->sm_count * 8) blocks = s->sm_count * 8;
+    conv_pad_weights_kernel<<<blocks, 256, 0, s->stream>>>(w, (float*)scratch, cout, p.K, k_pitch);
+    CB_LAUNCH_CHECK(s);
+    w_use = (const float*)scratch;
+  }
+  rc = encode_weights(&tmW, w_use, k_pitch, cout, BN);
   if (rc) return rc;
   tmWlo = tmW;
   if (BN == 256) return launch_conv<256, false>(s, tmW, tmWlo, p);

@@ -6,6 +6,9 @@ Mirrors the reference's compute layers:
   relu / Activation activations/relu, ActivationLayer   compute/nn/activations.clj:15-16, layers.clj:91-116
   Softmax           SoftmaxLayer                  compute/nn/layers.clj:141-168
   Convolution       ConvolutionLayer              compute/nn/layers.clj:306-360
+  Pooling           PoolingLayer                  compute/nn/layers.clj:391-409
+  BatchNormalization  (inference branch)          compute/nn/layers.clj:228-285
+  ConvNet           a layer list run in order, the shape of verify/nn/train.clj:24-41 (MNIST-NETWORK)
 
 ``fused=True`` replaces the reference's three calls per dense layer
 (assign! bias, gemm! NT beta=1, binary-op! max 0) with the backend's single
@@ -93,7 +96,118 @@ class Convolution:
         return output
 
 
-class MLP:
+class _Replayable:
+    """Launch-sequence capture for networks whose forward pass is launch-bound (small batches)."""
+
+    def infer_replayed(self, x):
+        """infer() for launch-bound batch sizes: the first call for a given input buffer runs the
+        layers normally, the second records them into a graph, later calls replay it with one host
+        call.  The result tensor is the same network-owned buffer every time; x's CONTENTS may
+        change between calls, its buffer and shape may not."""
+        stream = ct.check_stream()
+        key = (x.buffer.ptr, tuple(x.shape()), x.get_datatype(), id(stream))
+        entry = self._graphs.get(key)
+        if entry is None:
+            out = self.infer(x)
+            self._graphs[key] = [None, out]
+            return out
+        if entry[0] is None:
+            stream.begin_capture()
+            try:
+                self.infer(x)
+            finally:
+                entry[0] = stream.end_capture()
+        entry[0].launch(stream)
+        return entry[1]
+
+
+class Pooling:
+    """PoolingLayer.forward: pooling-forward! output 0.0 input pool-desc."""
+
+    def __init__(self, channels, kernel, pad, stride, datatype, pool_op="max", dimension_op="ceil"):
+        self.desc = ct.pooling_descriptor(datatype, channels, kernel[0], kernel[1], pad[0], pad[1], stride[0], stride[1],
+                                          dimension_op=dimension_op, pool_op=pool_op)
+
+    def output_shape(self, input_shape):
+        batch, ch, h, w = input_shape
+        od = ct.get_convolution_output_dimensions(self.desc, h, w)
+        return [batch, ch, od["output-width"], od["output-height"]]
+
+    def forward(self, input, output):
+        return ct.pooling_forward(output, 0.0, input, self.desc)
+
+
+class BatchNormalization:
+    """Inference branch of the BatchNormalization layer: batch-normalize! with the running statistics.
+    A 4-d input [batch, channels, h, w] is normalised per channel (spatial mode) through the view
+    [batch, channels, h*w]; a 2-d input per column."""
+
+    def __init__(self, means, variances, scale, bias, epsilon=1e-4):
+        self.means, self.variances, self.scale, self.bias, self.epsilon = means, variances, scale, bias, epsilon
+
+    def forward(self, input, output):
+        shp = input.shape()
+        if len(shp) == 4:
+            view = [shp[0], shp[1], shp[2] * shp[3]]
+            ct.batch_normalize(ct.in_place_reshape(output, view), ct.in_place_reshape(input, view), self.means,
+                               self.variances, self.scale, self.bias, self.epsilon)
+        else:
+            ct.batch_normalize(output, input, self.means, self.variances, self.scale, self.bias, self.epsilon)
+        return output
+
+
+class ConvNet(_Replayable):
+    """Runs a list of layer specs in order (inference; dropout layers are the identity and are left out):
+      ("conv", Convolution)  ("pool", Pooling)  ("bn", BatchNormalization)  ("relu",)  ("flatten",)
+      ("linear", Linear, act-or-None)  ("softmax",)
+    Activation buffers are allocated on first use per (layer, batch) and reused."""
+
+    def __init__(self, layers, fused=True):
+        self.layers, self.fused, self._buffers, self._graphs = layers, fused, {}, {}
+
+    def _buffer(self, idx, shape, datatype):
+        key = (idx, tuple(shape), datatype)
+        if key not in self._buffers:
+            self._buffers[key] = ct.new_tensor(list(shape), datatype=datatype, init_value=None)
+        return self._buffers[key]
+
+    def infer(self, x):
+        dt = x.get_datatype()
+        cur = x
+        for idx, spec in enumerate(self.layers):
+            kind = spec[0]
+            if kind == "conv":
+                conv = spec[1]
+                batch, _c, h, w = cur.shape()
+                od = ct.get_convolution_output_dimensions(conv.desc, h, w)
+                out = self._buffer(idx, [batch, conv.desc["out-channels"], od["output-width"], od["output-height"]], dt)
+                cur = conv.forward(cur, out)
+            elif kind == "pool":
+                out = self._buffer(idx, spec[1].output_shape(cur.shape()), dt)
+                cur = spec[1].forward(cur, out)
+            elif kind == "bn":
+                cur = spec[1].forward(cur, self._buffer(idx, cur.shape(), dt))
+            elif kind == "relu":
+                cur = relu(cur, cur)
+            elif kind == "flatten":
+                cur = ct.as_batch_matrix(cur)
+            elif kind == "linear":
+                lin, act = spec[1], spec[2]
+                out = self._buffer(idx, [cur.shape()[0], lin.weights.shape()[0]], dt)
+                if self.fused:
+                    cur = lin.forward_fused(cur, out, act)
+                else:
+                    cur = lin.forward(cur, out)
+                    if act is not None:
+                        _ACTIVATIONS[act](cur, cur)
+            elif kind == "softmax":
+                cur = ct.softmax(cur, cur)
+            else:
+                raise ValueError("unknown layer kind %r" % (kind,))
+        return cur
+
+
+class MLP(_Replayable):
     """A stack of dense layers: [(weights[out,in], bias[out], act)], act in
     {None, "relu", "tanh", "logistic", "softmax"}.  Activation buffers are
     allocated once per batch size and reused (the reference pools them in
@@ -131,24 +245,3 @@ class MLP:
                     _ACTIVATIONS[act](out, out)   # in place: binary-accum-constant! on the backend
             cur = out
         return cur
-
-    def infer_replayed(self, x):
-        """infer() for launch-bound batch sizes: the first call for a given input buffer runs the
-        layers normally, the second records them into a graph, later calls replay it with one host
-        call.  The result tensor is the same network-owned buffer every time; x's CONTENTS may
-        change between calls, its buffer and shape may not."""
-        stream = ct.check_stream()
-        key = (x.buffer.ptr, tuple(x.shape()), x.get_datatype(), id(stream))
-        entry = self._graphs.get(key)
-        if entry is None:
-            out = self.infer(x)
-            self._graphs[key] = [None, out]
-            return out
-        if entry[0] is None:
-            stream.begin_capture()
-            try:
-                self.infer(x)
-            finally:
-                entry[0] = stream.end_capture()
-        entry[0].launch(stream)
-        return entry[1]

@@ -174,3 +174,43 @@ def conv_case(datatype, batch, cin, hw, cout, k=3, pad=1, stride=1, seed=401, bi
         return np.maximum(out, 0.0).reshape(batch, cout, out_hw, out_hw)
 
     return run, reference
+
+
+def mnist_convnet_case(datatype, batch=32, seed=601):
+    """The reference's MNIST-NETWORK (src/cortex/verify/nn/train.clj:24-41) as an inference pass on seeded data:
+    conv 5x5 (1->20) -> max-pool 2 -> batch-norm (spatial) -> ReLU -> conv 5x5 (20->50) -> max-pool 2 ->
+    batch-norm -> linear 500 + ReLU -> linear 10 -> softmax   (dropout is the identity at inference)."""
+    dt = NP[datatype]
+    rng = np.random.default_rng(seed)
+    X = rng.random((batch, 1, 28, 28)).astype(dt)
+
+    def he(shape, fan_in):
+        return (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(dt)
+
+    W1, b1 = he((20, 25), 25), (rng.standard_normal(20) * 0.1).astype(dt)
+    W2, b2 = he((50, 500), 500), (rng.standard_normal(50) * 0.1).astype(dt)
+    W3, b3 = he((500, 800), 800), (rng.standard_normal(500) * 0.1).astype(dt)
+    W4, b4 = he((10, 500), 500), (rng.standard_normal(10) * 0.1).astype(dt)
+    bn1 = [(rng.standard_normal(20) * 0.1).astype(dt), (np.abs(rng.standard_normal(20)) + 0.5).astype(dt),
+           (1 + 0.1 * rng.standard_normal(20)).astype(dt), (rng.standard_normal(20) * 0.1).astype(dt)]
+    bn2 = [(rng.standard_normal(800) * 0.1).astype(dt), (np.abs(rng.standard_normal(800)) + 0.5).astype(dt),
+           (1 + 0.1 * rng.standard_normal(800)).astype(dt), (rng.standard_normal(800) * 0.1).astype(dt)]
+
+    def run(fused=True):
+        t = lambda a: ct.to_tensor(a, datatype)
+        net = nn.ConvNet([
+            ("conv", nn.Convolution(t(W1), t(b1), (5, 5), (0, 0), (1, 1), 1, 20, datatype)),
+            ("pool", nn.Pooling(20, (2, 2), (0, 0), (2, 2), datatype)),
+            ("bn", nn.BatchNormalization(*[t(a) for a in bn1])),
+            ("relu",),
+            ("conv", nn.Convolution(t(W2), t(b2), (5, 5), (0, 0), (1, 1), 20, 50, datatype)),
+            ("pool", nn.Pooling(50, (2, 2), (0, 0), (2, 2), datatype)),
+            ("flatten",),
+            ("bn", nn.BatchNormalization(*[t(a) for a in bn2])),
+            ("linear", nn.Linear(t(W3), t(b3)), "relu"),
+            ("linear", nn.Linear(t(W4), t(b4)), None),
+            ("softmax",),
+        ], fused=fused)
+        return ct.to_array(net.infer(t(X)))
+
+    return run

@@ -306,3 +306,14 @@ def test_pooling_forward_matches_oracle(b200_driver, oracle_driver, datatype, po
 
         g, c = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
         assert np.array_equal(g, c)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("datatype", ["float", "double"])
+def test_mnist_convnet_matches_oracle(b200_driver, oracle_driver, datatype):
+    """The reference's MNIST network shape end to end (conv, max-pool, batch-norm, ReLU, linear, softmax)."""
+    run = pc.mnist_convnet_case(datatype)
+    gpu = _on(b200_driver, datatype, run)
+    cpu = _on(oracle_driver, datatype, lambda: run(fused=False))
+    assert pc.rel_err(gpu.reshape(32, 10), cpu.reshape(32, 10)) <= pc.TOL[datatype]
+    assert np.abs(gpu.reshape(32, 10).astype(np.float64).sum(axis=1) - 1.0).max() <= (1e-5 if datatype == "float" else 1e-12)
