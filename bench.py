@@ -265,7 +265,8 @@ def bench_eltwise(drv, dev, peaks):
         pool_desc = ct.pooling_descriptor("float", 64, 3, 3, 1, 1, 2, 2, dimension_op="floor", pool_op="max")
         pool_in = [ct.in_place_reshape(x, [128, 64, 64, 64]) for x in xs]      # [8192, 4096] = 128 x 64 x 64 x 64
         pool_out = [ct.new_tensor([128, 64, 32, 32]) for _ in range(sets)]
-        cases["pooling_max_3x3s2"] = (lambda i: ct.pooling_forward(pool_out[i], 0.0, pool_in[i], pool_desc),
+        cases["pooling_max_3x3s2"] = (lambda i: stream.pooling_forward(pool_out[i].buffer, pool_out[i].dimensions, 0.0,
+                                                                       pool_in[i].buffer, pool_in[i].dimensions, pool_desc),
                                       rows * cols * 4 + rows * cols)
         for name, (fn, nbytes) in cases.items():
             for _ in range(3):
