@@ -14,6 +14,7 @@
 //   row), partial sums combined with atomics into a zero-initialised accumulator... kept simple here:
 //   a slice per block row-group and a second pass is avoided by letting one block own its columns.
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace {
 
@@ -105,6 +106,32 @@ gemv_n_kernel(T* c, long long incc, T alpha, const T* A, int rows, int cols, lon
       const int nv = cols / VEC;
       T acc1 = (T)0, acc2 = (T)0, acc3 = (T)0;
       int j = lane;
+      if (sizeof(T) == 4 && (cols % 8) == 0 && (lda % 8) == 0 && ((uintptr_t)A % 32) == 0 && ((uintptr_t)x % 32) == 0) {
+        // fp32, 32-byte aligned rows: 256-bit loads, four per lane in flight
+        const int n8 = cols / 8;
+        const float* rowf = reinterpret_cast<const float*>(row);
+        const float* xf = reinterpret_cast<const float*>(x);
+        int q = lane;
+        for (; q + 96 < n8; q += 128) {
+          float a0[8], a1[8], a2[8], a3[8], b0[8], b1[8], b2[8], b3[8];
+          sm100::ld_global_v8(rowf + 8 * q, a0, false); sm100::ld_global_v8(rowf + 8 * (q + 32), a1, false);
+          sm100::ld_global_v8(rowf + 8 * (q + 64), a2, false); sm100::ld_global_v8(rowf + 8 * (q + 96), a3, false);
+          sm100::ld_global_v8(xf + 8 * q, b0, false); sm100::ld_global_v8(xf + 8 * (q + 32), b1, false);
+          sm100::ld_global_v8(xf + 8 * (q + 64), b2, false); sm100::ld_global_v8(xf + 8 * (q + 96), b3, false);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            acc += (T)(a0[e] * b0[e]); acc1 += (T)(a1[e] * b1[e]); acc2 += (T)(a2[e] * b2[e]); acc3 += (T)(a3[e] * b3[e]);
+          }
+        }
+        for (; q < n8; q += 32) {
+          float a0[8], b0[8];
+          sm100::ld_global_v8(rowf + 8 * q, a0, false);
+          sm100::ld_global_v8(xf + 8 * q, b0, false);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc += (T)(a0[e] * b0[e]);
+        }
+        j = nv;      // everything consumed
+      }
       for (; j + 96 < nv; j += 128) {            // four 16-byte loads of the row in flight per lane
         const V a0 = reinterpret_cast<const V*>(row)[j], a1 = reinterpret_cast<const V*>(row)[j + 32];
         const V a2 = reinterpret_cast<const V*>(row)[j + 64], a3 = reinterpret_cast<const V*>(row)[j + 96];
