@@ -398,8 +398,14 @@ def bench_mlp_layer(drv, dev, peaks):
         for _ in range(3):
             lin.forward_fused(x, out, "relu")
         ms = time_region(stream, lambda: lin.forward_fused(x, out, "relu"), 10)
+        x_lo, out_lo = ct.new_tensor([rows, WIDTH]), ct.new_tensor([rows, WIDTH])
+        stream.split_lo(x_lo.buffer, x.buffer, rows * WIDTH)
+        for _ in range(3):
+            lin.forward_presplit(x, x_lo, out, out_lo, "relu")
+        ms_p = time_region(stream, lambda: lin.forward_presplit(x, x_lo, out, out_lo, "relu"), 10)
     tf = 2.0 * rows * WIDTH * WIDTH / ms / 1e9
-    return {"rows": rows, "ms": round(ms, 4), "tflops": round(tf, 1),
+    return {"rows": rows, "ms": round(ms, 4), "tflops": round(tf, 1), "presplit_ms": round(ms_p, 4),
+            "presplit_tflops": round(2.0 * rows * WIDTH * WIDTH / ms_p / 1e9, 1),
             "algorithmic_bytes": rows * WIDTH * 4 * 2 + WIDTH * WIDTH * 4 + WIDTH * 4}
 
 

@@ -27,6 +27,8 @@ struct GemmParams {
   // K split: with k_split == 2 the grid holds every output tile twice; CTA (tile, 0) reduces the first
   // half of K and stores alpha * acc + beta * C, CTA (tile, 1) the second half and stores
   // act(alpha * acc + C + bias) once tile_flags[tile] says the first part is in C.
+  int drain_every;     // pre-split kernel only: k-blocks between drains of the main accumulator (0 = never)
+  float* C_lo;         // pre-split kernel only: where lo_part(C) goes (same layout as C), or null
   int k_split;
   int split_block;     // tiles per block of (first halves, second halves) in the grid order
   int* tile_flags;
@@ -53,6 +55,26 @@ __device__ __forceinline__ float lo_part(float x) {
   return ((xb & 0x7f800000u) == 0x7f800000u) ? 0.f : lo;
 }
 
+// tcgen05 accumulates in fp32 with truncation, so a long reduction shrinks toward zero (about 7e-9 * K
+// relative, the same for every output, so it compounds through a stack of layers).  A kernel whose epilogue
+// warps are idle during the main loop can move the main accumulator into per-thread partial sums every few
+// thousand k values (round-to-nearest adds) and restart it from zero: thread (warp, lane) keeps the BN/2
+// values of its own row and column half -- exactly the elements it stores in the epilogue -- in thread-local
+// memory (touched once per drain and once in the epilogue).
+template <int BN>
+__device__ __noinline__ void drain_main(uint32_t tmem_base, int warp, float* part, bool first) {
+  const int q = warp & 3, half = warp >> 2;
+#pragma unroll 1
+  for (int cc = 0; cc < BN / 2 / 32; ++cc) {
+    uint32_t r[32];
+    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * (BN / 2) + cc * 32), r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      part[cc * 32 + j] = first ? __uint_as_float(r[j]) : part[cc * 32 + j] + __uint_as_float(r[j]);
+  }
+}
+
 // Epilogue of one 128 x BN accumulator tile held in this CTA's TMEM (main accumulator at column 0,
 // cross-term accumulator at column BN).  Called by warps 0-7 (all lanes): warp w reads TMEM lanes
 // 32*(w%4).., warps 0-3 take the left half of the columns, warps 4-7 the right half.
@@ -68,9 +90,15 @@ __device__ __forceinline__ float4 ld_c4(const float* p, bool partial) {
 // `last_pass`: bias, activation and peer stores join only on the pass that completes the tile.
 // `staging`: shared memory that is free by now (the pipeline stages), 32 x 36 floats per warp: slabs are
 // transposed through it so that global loads / stores cover whole 128-byte row segments.
-template <int BN>
+// WITH_LO: also store lo_part(result) at the same position of p.C_lo (last pass only): the next layer's
+// pre-split operand.
+// `part` (may be null): BN/2 partial sums per thread drained from the main accumulator earlier (drain_main),
+// added to the accumulators before alpha / beta.
+template <int BN, bool WITH_LO = false>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem_base, int m0, int n0, int warp,
-                                              int lane, float* staging, float beta_now, bool last_pass, bool c_is_partial) {
+                                              int lane, float* staging, float beta_now, bool last_pass, bool c_is_partial,
+                                              const float* part = nullptr) {
+      float* c_lo = (WITH_LO && last_pass) ? p.C_lo : nullptr;
       const float* e_bias = last_pass ? p.bias : nullptr;
       const int e_act = last_pass ? p.act : 0;
       const int e_peers = last_pass ? p.n_peers : 0;
@@ -95,6 +123,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(rc[j]));
         } else {
           tmem_ld_wait();
+        }
+        if (part) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + part[cc * 32 + j]);
         }
         const int nb = n0 + col0;
         if (e_peers > 0 && vec_ok && staging != nullptr && nb + 32 <= p.N) {
@@ -213,6 +245,12 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                   for (int e = 0; e < 8; ++e) o[e] = apply_act(o[e], e_act);
                 }
                 st_global_v8(crow + j, o);
+                if (WITH_LO && c_lo) {
+                  float l[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) l[e] = lo_part(o[e]);
+                  st_global_v8(c_lo + (long long)m * p.ldc + nb + j, l);
+                }
               }
             } else if (vec_ok && nb + 32 <= p.N) {
 #pragma unroll
@@ -232,6 +270,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                 }
                 if (e_act) { o.x = apply_act(o.x, e_act); o.y = apply_act(o.y, e_act); o.z = apply_act(o.z, e_act); o.w = apply_act(o.w, e_act); }
                 *reinterpret_cast<float4*>(crow + j) = o;
+                if (WITH_LO && c_lo)
+                  *reinterpret_cast<float4*>(c_lo + (long long)m * p.ldc + nb + j) =
+                      make_float4(lo_part(o.x), lo_part(o.y), lo_part(o.z), lo_part(o.w));
                 for (int d = 0; d < e_peers; ++d)
                   *reinterpret_cast<float4*>(p.peers[d] + (long long)m * p.ldc + nb + j) = o;
               }
@@ -244,6 +285,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                   if (e_bias) o += e_bias[nb + j];
                   o = apply_act(o, e_act);
                   crow[j] = o;
+                  if (WITH_LO && c_lo) c_lo[(long long)m * p.ldc + nb + j] = lo_part(o);
                   for (int d = 0; d < e_peers; ++d) p.peers[d][(long long)m * p.ldc + nb + j] = o;
                 }
               }

@@ -1,0 +1,339 @@
+// fp32 GEMM for layer stacks whose operands arrive ALREADY split:  C = act(alpha * A * B^T + beta * C + bias)
+// with A = A_hi + A_lo and B = B_hi + B_lo given as separate matrices (hi = the fp32 value itself, of which
+// the tensor core reads the top 19 bits; lo = x - trunc_tf32(x)), and C written as C (+ optionally C_lo, the
+// next layer's pre-split operand).  Same 3xTF32 arithmetic, same tiles, same epilogue as gemm_tf32x3.cu, but
+// nothing passes over shared memory between TMA and the MMAs: in the general kernel that pass (read every
+// operand byte, write the lo tile) shares the shared-memory bandwidth with the tensor core's operand fetch
+// and holds the tensor pipe to ~2/3 busy; here the weights' lo matrix is computed once per model and the
+// activations' lo matrix by the epilogue of the layer that produced them.
+//
+// K-major operands only (A [M, K] and B [N, K] row-major: the :linear forward), 256-wide tiles.
+// Warp roles: warps 0-7 epilogue; warp 8 TMA producer for A_hi / A_lo; warp 9 TMEM + MMA issue; warp 10 TMA
+// producer for B_hi / B_lo.  Per stage: empty -> 4 TMA tiles -> full -> 6 x tcgen05.mma -> commit -> empty.
+#include "gemm3x_common.cuh"
+#include <mutex>
+
+using namespace sm100;
+using namespace gemm3x;
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 16;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = (EPI_WARPS + 3) * 32;
+constexpr int A_TILE = BM * BK * 4, B_TILE = BN * BK * 4, RAW = A_TILE + B_TILE, STAGE = 2 * RAW;
+constexpr int STAGES = 196608 / STAGE;      // 4
+constexpr int TMEM_COLS = 2 * BN;
+constexpr int SMEM = STAGES * STAGE + 1024 + 256;
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_presplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlo,
+                     const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmBlo, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE);
+  // bars[0..S) full (two producers), [S..2S) empty, [2S] accumulators ready, [2S+1] main accumulator may be
+  // drained, [2S+2] main accumulator drained
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 3);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // tile order and K halves as in gemm_tf32x3_kernel
+  const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + BM - 1) / BM, n_tiles = tiles_m * tiles_n;
+  int k_half = 0, tile_id = (int)blockIdx.x;
+  if (p.k_split == 2) {
+    const int blk = (int)blockIdx.x / (2 * p.split_block);
+    const int r = (int)blockIdx.x - blk * 2 * p.split_block;
+    const int in_blk = min(p.split_block, n_tiles - blk * p.split_block);
+    k_half = r >= in_blk ? 1 : 0;
+    tile_id = blk * p.split_block + r - k_half * in_blk;
+  }
+  const int grp = tile_id / (tiles_m * p.group_n);
+  const int rem = tile_id - grp * tiles_m * p.group_n;
+  const int in_grp = min(p.group_n, tiles_n - grp * p.group_n);
+  const int m0 = (rem / in_grp) * BM, n0 = (grp * p.group_n + rem % in_grp) * BN;
+  const int nkb_all = (p.K + BK - 1) / BK;
+  const int kb_first = p.k_split == 2 ? nkb_all / 2 : nkb_all;
+  const int kb_begin = k_half ? kb_first : 0;
+  const int nkb = k_half ? nkb_all - kb_first : kb_first;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES), bar_acc = smem_u32(bars + 2 * STAGES),
+                 bar_mid = bar_acc + 8, bar_drained = bar_acc + 16;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 2);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    mbar_init(bar_mid, 1);
+    mbar_init(bar_drained, EPI_WARPS);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == EPI_WARPS + 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (lane == 0 && warp == EPI_WARPS) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmAlo); }
+  if (lane == 0 && warp == EPI_WARPS + 2) { tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmBlo); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == EPI_WARPS || warp == EPI_WARPS + 2) {
+    // ---------------- TMA producers: warp 8 loads the A tiles, warp 10 the B tiles ----------------
+    if (lane == 0) {
+      const bool is_a = warp == EPI_WARPS;
+      const CUtensorMap* hi_map = is_a ? &tmA : &tmB;
+      const CUtensorMap* lo_map = is_a ? &tmAlo : &tmBlo;
+      const uint32_t tile_off = is_a ? 0u : (uint32_t)A_TILE;
+      const uint32_t bytes = is_a ? 2u * A_TILE : 2u * B_TILE;
+      const int row0 = is_a ? m0 : n0;
+      int issued = 0, s = 0;
+      uint32_t ph = 0;
+      for (int i = 0; i < nkb; ++i) {
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 100 + s)) break;
+        const uint32_t full = bar_full + 8 * s;
+        const uint32_t dst = smem_base + s * STAGE + tile_off;
+        const int k0 = (kb_begin + i) * BK;
+        mbar_arrive_expect_tx(full, bytes);
+        tma_load_2d(dst, hi_map, k0, row0, full);
+        tma_load_2d(dst + RAW, lo_map, k0, row0, full);
+        issued = i + 1;
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
+      if (*abort_flag) {
+        for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+          for (int spin = 0; spin < (1 << 16); ++spin)
+            if (mbar_try_wait(bar_full + 8 * (i % STAGES), (i / STAGES) & 1)) break;
+      }
+    }
+  } else if (warp == EPI_WARPS + 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_tf32(BM, BN, 0, 0);
+      const uint64_t d_a = make_smem_desc(smem_base, 16, 8 * BK * 4, SWZ_64B);
+      const uint64_t d_b = make_smem_desc(smem_base + A_TILE, 16, 8 * BK * 4, SWZ_64B);
+      const uint32_t a_hiw = (uint32_t)(d_a >> 32), b_hiw = (uint32_t)(d_b >> 32);
+      const uint32_t a_low0 = (uint32_t)d_a, b_low0 = (uint32_t)d_b;
+      constexpr uint32_t LO_TILE = RAW >> 4, STAGE_STEP = STAGE >> 4;
+      const uint32_t tmem_main = tmem_base, tmem_cross = tmem_base + BN;
+      uint32_t acc_cross = 0, accumulate = 0;
+      int s = 0;
+      uint32_t ph = 0, stage_off = 0;
+      // every p.drain_every k-blocks the (otherwise idle) epilogue warps move the main accumulator into
+      // partial sums and it restarts from zero; the small cross-term accumulator keeps running
+      int to_drain = p.drain_every > 0 ? p.drain_every : 0x7fffffff;
+      uint32_t dph = 0;
+      for (int i = 0; i < nkb; ++i) {
+        if (to_drain == 0) {
+          mma_commit(bar_mid);
+          if (!mbar_wait(bar_drained, dph, abort_flag, p.status, 250)) break;
+          dph ^= 1;
+          tc_fence_after();
+          accumulate = 0;
+          to_drain = p.drain_every;
+        }
+        --to_drain;
+        if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 200 + s)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BK / 8; ++kk) {
+          const uint32_t al = a_low0 + stage_off + kk * 2, bl = b_low0 + stage_off + kk * 2;    // 32 B per k-step
+          mma_tf32_ss_words(tmem_cross, al + LO_TILE, a_hiw, bl, b_hiw, idesc, kk ? 1u : acc_cross);
+          mma_tf32_ss_words(tmem_cross, al, a_hiw, bl + LO_TILE, b_hiw, idesc, 1);
+          mma_tf32_ss_words(tmem_main, al, a_hiw, bl, b_hiw, idesc, kk ? 1u : accumulate);
+        }
+        mma_commit(bar_empty + 8 * s);
+        acc_cross = 1;
+        accumulate = 1;
+        if (++s == STAGES) { s = 0; ph ^= 1; stage_off = 0; } else { stage_off += STAGE_STEP; }
+      }
+      mma_commit(bar_acc);
+      if (*abort_flag) {
+        for (int spin = 0; spin < (1 << 16); ++spin)
+          if (mbar_try_wait(bar_acc, 0)) break;
+      }
+    }
+  } else {
+    // ---------------- epilogue warps ----------------
+    float part[BN / 2];
+    int drains = 0;
+    bool ok = true;
+    if (p.drain_every > 0) {
+      uint32_t mph = 0;
+      for (int b = p.drain_every; ok && b < nkb; b += p.drain_every) {
+        ok = mbar_wait(bar_mid, mph, abort_flag, p.status, 350);
+        mph ^= 1;
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        if (ok) drain_main<BN>(tmem_base, warp, part, drains == 0);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_drained);
+        ++drains;
+      }
+    }
+    if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 400);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    if (ok && k_half) {
+      if (lane == 0) {
+        const int* flag = p.tile_flags + tile_id;
+        int seen = 0;
+        const long long t0 = clock64();
+        for (;;) {
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+          if (seen != 0 || *abort_flag) break;
+          if (clock64() - t0 > SM100_WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            if (atomicCAS(p.status, 0, 4 /* CB200_ERR_TIMEOUT */) == 0) p.status[1] = 450;
+            break;
+          }
+          __nanosleep(200);
+        }
+        ok = seen != 0;
+      }
+      ok = __all_sync(0xffffffffu, __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0);
+    }
+    if (ok) {
+      const bool last = p.k_split != 2 || k_half == 1;
+      epilogue_tile<BN, true>(p, tmem_base, m0, n0, warp, lane, nullptr, k_half ? 1.f : p.beta, last, k_half == 1,
+                              drains > 0 ? part : nullptr);
+      if (p.k_split == 2 && k_half == 0) __threadfence();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (p.k_split == 2 && threadIdx.x == 0 && !*abort_flag) {
+    int* flag = p.tile_flags + tile_id;
+    if (k_half == 0) {
+      __threadfence();
+      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(1) : "memory");
+    } else {
+      *flag = 0;
+    }
+  }
+  if (warp == EPI_WARPS + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn presplit_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)f;
+  });
+  return fn;
+}
+
+int kmajor_tmap(CUtensorMap* tm, const float* base, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = presplit_encode_fn();
+  if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { cb200_set_error("cuTensorMapEncodeTiled failed with %d", (int)r); return CB200_ERR_CUDA; }
+  return CB200_OK;
+}
+
+// lo = x - trunc_tf32(x), elementwise over a dense span
+__global__ void __launch_bounds__(256) split_lo_kernel(float* lo, const float* x, long long n) {
+  const long long n4 = n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    reinterpret_cast<float4*>(lo)[i] = make_float4(lo_part(v.x), lo_part(v.y), lo_part(v.z), lo_part(v.w));
+  }
+  for (long long i = n4 * 4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    lo[i] = lo_part(x[i]);
+}
+
+}  // namespace
+
+extern "C" {
+
+int cb200_split_lo(cb200_stream* s, void* lo, const void* x, int64_t n_elems) {
+  CB_REQUIRE(s && lo && x && n_elems >= 0, "split_lo: bad argument");
+  CB_REQUIRE((((uintptr_t)lo | (uintptr_t)x) & 15) == 0, "split_lo: buffers must be 16-byte aligned");
+  if (n_elems == 0) return CB200_OK;
+  DeviceGuard guard(s->device);
+  long long blocks = (n_elems / 4 + 255) / 256 + 1;
+  const long long cap = (long long)s->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  split_lo_kernel<<<(unsigned)blocks, 256, 0, s->stream>>>((float*)lo, (const float*)x, n_elems);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t ldc, double alpha, const void* A_hi,
+                                 const void* A_lo, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B_hi,
+                                 const void* B_lo, int64_t b_rows, int64_t ldb, double beta, const void* bias, int act) {
+  CB_REQUIRE(s && C && A_hi && A_lo && B_hi && B_lo, "gemm_bias_act_presplit: null argument");
+  CB_REQUIRE(a_rows >= 1 && a_cols >= 1 && b_rows >= 1 && a_rows <= 2147483647LL && a_cols <= 2147483647LL &&
+                 b_rows <= 2147483647LL, "gemm_bias_act_presplit: bad extents");
+  CB_REQUIRE(ldc >= b_rows && lda >= a_cols && ldb >= a_cols, "gemm_bias_act_presplit: pitch smaller than the row");
+  CB_REQUIRE((((uintptr_t)A_hi | (uintptr_t)A_lo | (uintptr_t)B_hi | (uintptr_t)B_lo) & 15) == 0 && (lda % 4) == 0 &&
+                 (ldb % 4) == 0, "gemm_bias_act_presplit: operands must be 16-byte aligned with pitches that are multiples of 4");
+  CB_REQUIRE(act >= CB200_ACT_NONE && act <= CB200_ACT_LOGISTIC, "gemm_bias_act_presplit: unknown activation %d", act);
+  const int M = (int)a_rows, K = (int)a_cols, N = (int)b_rows;
+  DeviceGuard guard(s->device);
+  GemmParams p;
+  p.n_peers = 0;
+  for (int d = 0; d < MAX_PEERS; ++d) p.peers[d] = nullptr;
+  p.C = (float*)C; p.C_lo = (float*)C_lo; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
+  p.alpha = (float)alpha; p.beta = (float)beta; p.bias = (const float*)bias; p.act = act;
+  p.a_mn_major = 0; p.b_mn_major = 0; p.store_mode = STORE_ROW_MAJOR; p.hw = 1; p.flags = 0; p.status = s->status_dev;
+  const long long tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  // reductions of 4096 and more: the main accumulator is folded into partial sums every 2048 k values
+  // (the general kernel has to use two K halves per tile for this; here the epilogue warps are free)
+  p.k_split = 1;
+  p.drain_every = K >= 4096 ? 2048 / BK : 0;
+  p.split_block = 2 * s->sm_count;
+  p.tile_flags = nullptr;
+  if (p.k_split == 2) {
+    int rcf = cb200_tile_flags(s, (size_t)tiles_m * tiles_n, &p.tile_flags);
+    if (rcf) return rcf;
+  }
+  const long long panel_bytes = (long long)BN * K * 8;      // hi + lo share of one column tile
+  p.group_n = tiles_n;
+  if (tiles_n * panel_bytes > (40ll << 20)) {
+    long long g = (32ll << 20) / panel_bytes;
+    p.group_n = (int)(g < 1 ? 1 : (g > tiles_n ? tiles_n : g));
+  }
+  CUtensorMap tmA, tmAlo, tmB, tmBlo;
+  int rc;
+  if ((rc = kmajor_tmap(&tmA, (const float*)A_hi, M, K, lda, BM))) return rc;
+  if ((rc = kmajor_tmap(&tmAlo, (const float*)A_lo, M, K, lda, BM))) return rc;
+  if ((rc = kmajor_tmap(&tmB, (const float*)B_hi, N, K, ldb, BN))) return rc;
+  if ((rc = kmajor_tmap(&tmBlo, (const float*)B_lo, N, K, ldb, BN))) return rc;
+  static std::once_flag once[64];
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[s->device & 63], [&] {
+    attr_err = cudaFuncSetAttribute(gemm_presplit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  });
+  if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
+  const long long grid = tiles_m * tiles_n * p.k_split;
+  gemm_presplit_kernel<<<(unsigned)grid, THREADS, SMEM, s->stream>>>(tmA, tmAlo, tmB, tmBlo, p);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+}  // extern "C"

@@ -417,6 +417,8 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   // output, so it compounds through a stack of layers (five 4096-wide layers: 1.4e-4 on the softmax
   // output); two 2048-long halves joined by a round-to-nearest add halve that, at 8-12 % of the speed.
   p.k_split = ((flags & FLAG_SPLIT_K) && K >= 4096 && store_mode == STORE_ROW_MAJOR) ? 2 : 1;
+  p.C_lo = nullptr;
+  p.drain_every = 0;
   p.tile_flags = nullptr;
   p.split_block = 2 * s->sm_count;
   if (p.k_split == 2) {

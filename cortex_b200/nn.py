@@ -50,6 +50,26 @@ class Linear:
     def forward(self, input, output):
         return biased_multiply(input, self.weights, self.bias, output)
 
+    def prepare_presplit(self):
+        """Compute the weights' lo matrix (x - trunc_tf32(x)) once; needed by forward_presplit."""
+        if getattr(self, "weights_lo", None) is None:
+            self.weights_lo = ct.new_tensor(self.weights.shape(), datatype="float", init_value=None)
+            ct.check_stream().split_lo(self.weights_lo.buffer, self.weights.buffer, self.weights.ecount())
+        return self.weights_lo
+
+    def forward_presplit(self, input, input_lo, output, output_lo, act=None):
+        """One kernel: output = act(input . W^T + bias) from operands that are already split into hi / lo,
+        and (if output_lo is given) the output's lo matrix for the next layer."""
+        input, output = ct.as_batch_matrix(input), ct.as_batch_matrix(output)
+        m, k = input.shape()
+        n = self.weights.shape()[0]
+        w_lo = self.prepare_presplit()
+        ct.check_stream().gemm_bias_act_presplit(
+            output.buffer, output_lo.buffer if output_lo is not None else None, output.dimensions["strides"][0], 1.0,
+            input.buffer, input_lo.buffer, m, k, input.dimensions["strides"][0], self.weights.buffer, w_lo.buffer, n,
+            self.weights.dimensions["strides"][0], 0.0, self.bias.buffer, act)
+        return output
+
     def forward_fused(self, input, output, act=None):
         """One kernel: output = act(input . W^T + bias)."""
         input, output = ct.as_batch_matrix(input), ct.as_batch_matrix(output)
@@ -60,6 +80,13 @@ class Linear:
                              input.dimensions["strides"][0], self.weights.buffer, n,
                              self.weights.dimensions["strides"][0], 0.0, self.bias.buffer, act)
         return output
+
+
+def _presplit_ok(linear, input):
+    """The pre-split kernel wants fp32, dense row-major operands with 16-byte aligned rows and a wide output."""
+    k = linear.weights.shape()[1]
+    return (input.get_datatype() == "float" and k % 4 == 0 and linear.weights.shape()[0] > 128 and
+            hasattr(ct.check_stream(), "gemm_bias_act_presplit") and not getattr(ct.check_stream(), "is_oracle", False))
 
 
 class Activation:
@@ -213,9 +240,12 @@ class MLP(_Replayable):
     allocated once per batch size and reused (the reference pools them in
     nn/compute_binding.clj:208-259)."""
 
-    def __init__(self, layers, fused=False):
+    def __init__(self, layers, fused=False, presplit=False):
+        """presplit (implies fused; fp32 on the B200 backend only): layers whose operands qualify run the
+        pre-split GEMM: weights are split into hi / lo once, every layer writes its output already split."""
         self.layers = [(Linear(w, b), act) for (w, b, act) in layers]
-        self.fused = fused
+        self.fused = fused or presplit
+        self.presplit = presplit
         self._buffers = {}
         self._graphs = {}
 
@@ -229,9 +259,22 @@ class MLP(_Replayable):
         batch = x.shape()[0]
         dt = x.get_datatype()
         cur = x
+        cur_lo = None          # lo matrix of `cur`, when the previous layer produced it
         for idx, (lin, act) in enumerate(self.layers):
             width = lin.weights.shape()[0]
             out = self._buffer(idx, batch, width, dt)
+            if self.presplit and _presplit_ok(lin, cur):
+                if cur_lo is None:
+                    cur_lo = self._buffer(("lo-in", idx), batch, cur.shape()[1], dt)
+                    ct.check_stream().split_lo(cur_lo.buffer, cur.buffer, cur.ecount())
+                nxt = self.layers[idx + 1][0] if idx + 1 < len(self.layers) else None
+                out_lo = self._buffer(("lo", idx), batch, width, dt) if nxt is not None and self.presplit else None
+                lin.forward_presplit(cur, cur_lo, out, out_lo, act if act != "softmax" else None)
+                if act == "softmax":
+                    ct.softmax(out, out)
+                cur, cur_lo = out, out_lo
+                continue
+            cur_lo = None
             if self.fused and act in (None, "relu", "tanh", "logistic"):
                 lin.forward_fused(cur, out, act)
             elif self.fused and act == "softmax":

@@ -127,6 +127,16 @@ class CTensorMath:
                  b.ptr, int(b_col_count), int(b_colstride), float(beta), bias.ptr if bias is not None else None,
                  ACTIVATIONS[act], len(peer_ptrs), arr)
 
+    def split_lo(self, lo, x, n_elems):
+        """lo = x - trunc_tf32(x) over a dense span (fp32)."""
+        self._tm("split_lo", lo.ptr, x.ptr, int(n_elems))
+
+    def gemm_bias_act_presplit(self, c, c_lo, ldc, alpha, a_hi, a_lo, a_rows, a_cols, lda, b_hi, b_lo, b_rows, ldb, beta,
+                               bias, act):
+        self._tm("gemm_bias_act_presplit", c.ptr, c_lo.ptr if c_lo is not None else None, int(ldc), float(alpha),
+                 a_hi.ptr, a_lo.ptr, int(a_rows), int(a_cols), int(lda), b_hi.ptr, b_lo.ptr, int(b_rows), int(ldb),
+                 float(beta), bias.ptr if bias is not None else None, ACTIVATIONS[act])
+
     def bias_relu_rowstats(self, y, ldy, x, ldx, bias, rows, cols, rowmax, rowsum):
         self._tm("bias_relu_rowstats", DTYPE_CODE[y.dtype], y.ptr, int(ldy), x.ptr, int(ldx), bias.ptr, int(rows),
                  int(cols), rowmax.ptr if rowmax is not None else None, rowsum.ptr if rowsum is not None else None)

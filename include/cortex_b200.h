@@ -299,6 +299,20 @@ int cb200_ipc_export(int device, void* device_ptr, unsigned char* handle_out);
 int cb200_ipc_import(int device, const unsigned char* handle, void** ptr_out);
 int cb200_ipc_close(int device, void* ptr);
 
+/* ---- pre-split layer GEMM (no counterpart in the protocol) ----------------------
+ * The 3xTF32 GEMM splits every fp32 operand into hi (the value itself) and lo = x - trunc_tf32(x).  In a
+ * stack of layers the weights' lo matrix can be computed once and an activation's lo matrix by the layer
+ * that produces it; this entry point takes both operands already split and can write its result split:
+ *   C = act(alpha * A * B^T + beta * C + bias),  C_lo = C - trunc_tf32(C)   (C_lo may be NULL)
+ * A_hi / A_lo: [a_rows, a_cols] row-major, pitch lda; B_hi / B_lo: [b_rows, a_cols] row-major, pitch ldb
+ * (the :linear layout: weights [out, in]); C / C_lo: [a_rows, b_rows], pitch ldc.  fp32 only; operands
+ * 16-byte aligned, pitches multiples of 4.  cb200_split_lo computes lo for a dense span (inputs, weights). */
+int cb200_split_lo(cb200_stream* s, void* lo, const void* x, int64_t n_elems);
+int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t ldc, double alpha,
+                                 const void* A_hi, const void* A_lo, int64_t a_rows, int64_t a_cols, int64_t lda,
+                                 const void* B_hi, const void* B_lo, int64_t b_rows, int64_t ldb, double beta,
+                                 const void* bias, int act);
+
 /* One pass over X[rows, cols] (pitch ldx): Y = max(X + bias, 0), rowmax[r] = max_j Y[r,j],
  * rowsum[r] = sum_j Y[r,j].  float/double.  Y may alias X; rowmax/rowsum may be NULL. */
 int cb200_bias_relu_rowstats(cb200_stream* s, int dtype, void* Y, int64_t ldy, const void* X,

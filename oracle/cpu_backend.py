@@ -101,6 +101,8 @@ class OracleEvent:
 class OracleStream(CTensorMath):
     """The oracle's CPUStream: every call runs synchronously on the caller's thread."""
 
+    is_oracle = True
+
     # GEMMs above this many multiply-adds go to OpenBLAS instead of the C loop nest
     BLAS_THRESHOLD = 1 << 18
 

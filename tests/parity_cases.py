@@ -114,7 +114,7 @@ def gather_case(datatype, src_rows, n_idx, cols, seed=303):
     return run, lambda: M[idx]
 
 
-def mlp_case(datatype, batch, widths, seed=101, fused=False, bias_scale=0.0):
+def mlp_case(datatype, batch, widths, seed=101, fused=False, bias_scale=0.0, presplit=False):
     """Configs 1 and 5: dense layers with ReLU, softmax head.  widths = [in, h1, ..., out]."""
     dt = NP[datatype]
     X = np.random.default_rng(seed).random((batch, widths[0])).astype(dt)
@@ -130,7 +130,7 @@ def mlp_case(datatype, batch, widths, seed=101, fused=False, bias_scale=0.0):
         for i, (w, b) in enumerate(zip(Ws, bs)):
             act = "softmax" if i == len(Ws) - 1 else "relu"
             layers.append((ct.to_tensor(w, datatype), ct.to_tensor(b, datatype), act))
-        net = nn.MLP(layers, fused=fused)
+        net = nn.MLP(layers, fused=fused, presplit=presplit)
         return ct.to_array(net.infer(ct.to_tensor(X, datatype)))
 
     def reference():

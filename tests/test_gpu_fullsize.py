@@ -134,8 +134,8 @@ def test_convolution_config_full_size_sampled(b200_driver):
     assert np.abs(g - ref).max() / max(np.abs(ref).max(), rms) <= 1e-4
 
 
-@pytest.mark.parametrize("datatype,rows", [("float", 8192), ("double", 2048)])
-def test_wide_mlp_full_width_sampled_rows(b200_driver, datatype, rows):
+@pytest.mark.parametrize("datatype,rows,presplit", [("float", 8192, False), ("float", 8192, True), ("double", 2048, False)])
+def test_wide_mlp_full_width_sampled_rows(b200_driver, datatype, rows, presplit):
     """Config 5 at full width (4096 -> 4 x 4096 + ReLU -> 1000 + softmax) on a slice of the batch:
     every row sums to 1; sampled rows against a float64 forward."""
     dt = NP[datatype]
@@ -146,7 +146,7 @@ def test_wide_mlp_full_width_sampled_rows(b200_driver, datatype, rows):
     with ct.with_stream(stream), ct.with_datatype(datatype):
         layers = [(ct.to_tensor(w), ct.new_tensor([w.shape[0]]), "softmax" if i == 4 else "relu")
                   for i, w in enumerate(Ws)]
-        net = nn.MLP(layers, fused=True)
+        net = nn.MLP(layers, fused=True, presplit=presplit)
         probs = ct.to_array(net.infer(ct.to_tensor(X))).reshape(rows, 1000)
     assert np.abs(probs.astype(np.float64).sum(axis=1) - 1.0).max() <= (1e-5 if datatype == "float" else 1e-13)
     pick = rng.integers(0, rows, size=48)

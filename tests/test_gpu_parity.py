@@ -319,3 +319,50 @@ def test_mnist_convnet_matches_oracle(b200_driver, oracle_driver, datatype):
     cpu = _on(oracle_driver, datatype, lambda: run(fused=False))
     assert pc.rel_err(gpu.reshape(32, 10), cpu.reshape(32, 10)) <= pc.TOL[datatype]
     assert np.abs(gpu.reshape(32, 10).astype(np.float64).sum(axis=1) - 1.0).max() <= (1e-5 if datatype == "float" else 1e-12)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(300, 384, 256), (130, 1000, 500), (128, 256, 16), (513, 260, 4112), (1024, 4096, 4096)])
+@pytest.mark.parametrize("act", [None, "relu"])
+def test_presplit_layer_gemm(b200_driver, M, N, K, act):
+    """The pre-split layer GEMM (operands given as hi / lo matrices, result written as hi / lo) against the
+    general fused kernel (same arithmetic: equal up to summation order) and against float64."""
+    rng = np.random.default_rng(M * 7 + N)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    stream = b200_driver.default_device().create_stream()
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        a, w, b = ct.to_tensor(A), ct.to_tensor(W), ct.to_tensor(bias)
+        a_lo, w_lo = ct.new_tensor([M, K]), ct.new_tensor([N, K])
+        stream.split_lo(a_lo.buffer, a.buffer, M * K)
+        stream.split_lo(w_lo.buffer, w.buffer, N * K)
+        lo_host = ct.to_array(a_lo).reshape(M, K)
+        hi_trunc = (A.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32)
+        assert np.array_equal(lo_host, A - hi_trunc)                      # lo = x - trunc_tf32(x), exact
+        c, c_lo, ref = ct.new_tensor([M, N]), ct.new_tensor([M, N]), ct.new_tensor([M, N])
+        for _ in range(2):
+            stream.gemm_bias_act_presplit(c.buffer, c_lo.buffer, N, 1.0, a.buffer, a_lo.buffer, M, K, K, w.buffer,
+                                          w_lo.buffer, N, K, 0.0, b.buffer, act)
+        stream.gemm_bias_act(ref.buffer, N, False, True, 1.0, a.buffer, M, K, K, w.buffer, N, K, 0.0, b.buffer, act)
+        got, got_lo, want = (ct.to_array(t).reshape(M, N) for t in (c, c_lo, ref))
+    exact = A.astype(np.float64) @ W.astype(np.float64).T + bias
+    if act == "relu":
+        exact = np.maximum(exact, 0.0)
+    assert pc.rel_err(got, exact) <= 1e-4
+    assert pc.rel_err(got, want) <= 2e-5
+    got_trunc = (got.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32)
+    assert np.array_equal(got_lo, got - got_trunc)
+
+
+@pytest.mark.gpu
+def test_presplit_mlp_matches_oracle(b200_driver, oracle_driver):
+    """A 4-layer MLP through the pre-split layer GEMMs (weights split once, every layer writes its output
+    split) against the oracle's unfused call sequence."""
+    widths = [784, 1024, 1024, 1024, 1000]
+    run_gpu, ref = pc.mlp_case("float", 300, widths, seed=77, bias_scale=0.1, presplit=True)
+    run_cpu, _ = pc.mlp_case("float", 300, widths, seed=77, bias_scale=0.1, fused=False)
+    gpu = _on(b200_driver, "float", run_gpu).reshape(300, 1000)
+    cpu = _on(oracle_driver, "float", run_cpu).reshape(300, 1000)
+    assert pc.rel_err(gpu, cpu) <= pc.TOL["float"]
+    assert pc.rel_err(gpu, ref()) <= pc.TOL["float"]
