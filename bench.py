@@ -603,8 +603,8 @@ def run_b200(args, rank, world, local_rank):
         peak_tf32x3 = peaks["bf16_sustained"] / 2.0 / 3.0
         peak_note = ("%s bf16 sustained %.0f TF / 2 (tf32 rate) / 3 (three tf32 MMAs per product); algorithmic work "
                      "2*M*N*K" % (peaks["source"], peaks["bf16_sustained"]))
-        kernel_name = "gemm_presplit_kernel"
-        kernel_path = "split_lo + gemm_bias_act_presplit (tcgen05 3xTF32 on pre-split operands, bias+ReLU fused) x5 + softmax"
+        kernel_name = "gemm_presplit_pair_kernel"
+        kernel_path = "split_lo + gemm_bias_act_presplit (tcgen05 cta_group::2 3xTF32 on pre-split operands, CTA pairs, bias+ReLU fused) x5 + softmax"
     else:
         peak_tf32x3 = 37.0
         peak_note = "nominal B200 fp64 dense rate 37 TF (no measured fp64 peak exists for this pool); work 2*M*N*K"

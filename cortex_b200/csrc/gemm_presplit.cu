@@ -10,6 +10,12 @@
 // K-major operands only (A [M, K] and B [N, K] row-major: the :linear forward), 256-wide tiles.
 // Warp roles: warps 0-7 epilogue; warp 8 TMA producer for A_hi / A_lo; warp 9 TMEM + MMA issue; warp 10 TMA
 // producer for B_hi / B_lo.  Per stage: empty -> 4 TMA tiles -> full -> 6 x tcgen05.mma -> commit -> empty.
+//
+// Large problems run the same scheme on CTA PAIRS (gemm_presplit_pair_kernel): the two CTAs of a 2-CTA
+// cluster compute one 256 x 256 tile with tcgen05.mma.cta_group::2, each staging its own 128 rows of A and
+// only HALF of the B tile, so a CTA moves 2/3 of the shared-memory bytes per MMA cycle and its 32 KB stages
+// fit 6 deep.  (The single-CTA kernel above reads 72 KB of operands and receives 48 KB from TMA per 768
+// tensor-pipe cycles: more than the 128 B/cycle a shared memory delivers.)
 #include "gemm3x_common.cuh"
 #include <mutex>
 
@@ -223,6 +229,270 @@ gemm_presplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant.  Per CTA: warps 0-7 epilogue of the CTA's own 128 rows; warp 8 TMA producer for
+// its A_hi / A_lo rows; warp 10 TMA producer for its half of B_hi / B_lo.  Every TMA load of either
+// CTA writes the issuing CTA's own shared memory and completes its bytes on the LEADER's full
+// barrier (the .cta_group::2 form of the load, which lets the barrier live in the peer CTA); the
+// leader's producers arm that barrier with the byte count of both CTAs.  Warp 9 owns TMEM and, in the
+// leader CTA (cluster rank 0), issues the pair's MMAs and commits to the empty barriers of both
+// CTAs.  (A first version had each CTA wait for its own tiles and then arrive on the leader's
+// barrier with a cluster-scope release: that arrive took ~1000 cycles and halved the MMA rate.)
+// Every load is a plain unicast tile load.  Every wait is bounded; both CTAs always reach the closing
+// cluster barrier.
+constexpr int PNH = BN / 2;                              // columns of B staged per CTA
+constexpr int P_B_TILE = PNH * BK * 4;                   // 8 KiB
+constexpr int P_RAW = A_TILE + P_B_TILE;                 // 16 KiB: A | B-half
+constexpr int P_STAGE = 2 * P_RAW;                       // 32 KiB: A_hi | B_hi | A_lo | B_lo
+constexpr int P_STAGES = 196608 / P_STAGE;               // 6
+constexpr int P_THREADS = (EPI_WARPS + 3) * 32;
+constexpr int P_SMEM = P_STAGES * P_STAGE + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on a barrier that may live in the peer CTA (address in the shared::cluster window)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// bounded wait on a local barrier whose arrivals may come from the peer CTA
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  int site) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > SM100_WAIT_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        if (atomicCAS(status, 0, 4 /* CB200_ERR_TIMEOUT */) == 0) status[1] = site;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_tf32_pair_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                    uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// tile load into this CTA's shared memory whose byte count completes on a barrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int c0, int c1, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"((uint64_t)tmap), "r"(c0), "r"(c1), "r"(cluster_bar)
+      : "memory");
+}
+// arrives (once) on the given barrier -- local or the peer's -- when the pair's MMAs issued so far have retired
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlo,
+                          const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmBlo,
+                          GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + P_STAGES * P_STAGE);
+  // bars[0..S) full (the leader's copy is used: its two producers arrive, both CTAs' loads complete bytes),
+  // [S..2S) unused, [2S..3S) empty, [3S] accumulators ready, [3S+1] main accumulator may be drained,
+  // [3S+2] drained (the leader's copy is used)
+  uint32_t* tmem_slot = (uint32_t*)(bars + 3 * P_STAGES + 3);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  // pair tiles: 256 rows x 256 columns, swept like the single-CTA tiles (column groups, rows inside)
+  const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tile_id = (int)blockIdx.x >> 1;
+  const int grp = tile_id / (tiles_m * p.group_n);
+  const int rem = tile_id - grp * tiles_m * p.group_n;
+  const int in_grp = min(p.group_n, tiles_n - grp * p.group_n);
+  const int m0 = (rem / in_grp) * (2 * BM) + (int)rank * BM;       // this CTA's rows of C
+  const int n0 = (grp * p.group_n + rem % in_grp) * BN;            // the pair's columns of C
+  const int nb0 = n0 + (int)rank * PNH;                            // this CTA's slice of B
+  const int nkb = (p.K + BK - 1) / BK;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_full = smem_u32(bars),
+                 bar_empty = smem_u32(bars + 2 * P_STAGES), bar_acc = smem_u32(bars + 3 * P_STAGES),
+                 bar_mid = bar_acc + 8, bar_drained = bar_acc + 16;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 2);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    mbar_init(bar_mid, 1);
+    mbar_init(bar_drained, 2 * EPI_WARPS);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == EPI_WARPS + 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  if (lane == 0 && warp == EPI_WARPS) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmAlo); }
+  if (lane == 0 && warp == EPI_WARPS + 2) { tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmBlo); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();     // the peer's barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == EPI_WARPS || warp == EPI_WARPS + 2) {
+    // ---------------- TMA producers (each CTA, its own tiles) ----------------
+    if (lane == 0) {
+      const bool is_a = warp == EPI_WARPS;
+      const CUtensorMap* hi_map = is_a ? &tmA : &tmB;
+      const CUtensorMap* lo_map = is_a ? &tmAlo : &tmBlo;
+      const uint32_t tile_off = is_a ? 0u : (uint32_t)A_TILE;
+      const uint32_t bytes = 2u * (is_a ? 2u * A_TILE : 2u * P_B_TILE);      // this CTA's tiles and the peer's
+      const int row0 = is_a ? m0 : nb0;
+      const uint32_t leader_full = mapa(bar_full, 0);
+      int issued = 0, s = 0;
+      uint32_t ph = 0;
+      for (int i = 0; i < nkb; ++i) {
+        if (!mbar_wait_cluster(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) break;
+        const uint32_t dst = smem_base + s * P_STAGE + tile_off;
+        const int k0 = i * BK;
+        if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, bytes);
+        tma_load_2d_pair(dst, hi_map, k0, row0, leader_full + 8 * s);
+        tma_load_2d_pair(dst + P_RAW, lo_map, k0, row0, leader_full + 8 * s);
+        issued = i + 1;
+        if (++s == P_STAGES) { s = 0; ph ^= 1; }
+      }
+      if (leader && *abort_flag) {
+        for (int i = issued > P_STAGES ? issued - P_STAGES : 0; i < issued; ++i)
+          for (int spin = 0; spin < (1 << 16); ++spin)
+            if (mbar_try_wait(bar_full + 8 * (i % P_STAGES), (i / P_STAGES) & 1)) break;
+      }
+    }
+  } else if (warp == EPI_WARPS + 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      const uint32_t idesc = make_idesc_tf32(2 * BM, BN, 0, 0);
+      const uint64_t d_a = make_smem_desc(smem_base, 16, 8 * BK * 4, SWZ_64B);
+      const uint64_t d_b = make_smem_desc(smem_base + A_TILE, 16, 8 * BK * 4, SWZ_64B);
+      const uint32_t a_hiw = (uint32_t)(d_a >> 32), b_hiw = (uint32_t)(d_b >> 32);
+      const uint32_t a_low0 = (uint32_t)d_a, b_low0 = (uint32_t)d_b;
+      constexpr uint32_t LO_TILE = P_RAW >> 4, STAGE_STEP = P_STAGE >> 4;
+      const uint32_t tmem_main = tmem_base, tmem_cross = tmem_base + BN;
+      const uint32_t peer_empty = mapa(bar_empty, 1), peer_acc = mapa(bar_acc, 1), peer_mid = mapa(bar_mid, 1);
+      uint32_t acc_cross = 0, accumulate = 0;
+      int s = 0;
+      uint32_t ph = 0, stage_off = 0;
+      int to_drain = p.drain_every > 0 ? p.drain_every : 0x7fffffff;
+      uint32_t dph = 0;
+      for (int i = 0; i < nkb; ++i) {
+        if (to_drain == 0) {
+          mma_commit_pair(bar_mid);
+          mma_commit_pair(peer_mid);
+          if (!mbar_wait_cluster(bar_drained, dph, abort_flag, p.status, 750)) break;
+          dph ^= 1;
+          tc_fence_after();
+          accumulate = 0;
+          to_drain = p.drain_every;
+        }
+        --to_drain;
+        if (!mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, 700 + s)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BK / 8; ++kk) {
+          const uint32_t al = a_low0 + stage_off + kk * 2, bl = b_low0 + stage_off + kk * 2;    // 32 B per k-step
+          mma_tf32_pair_words(tmem_cross, al + LO_TILE, a_hiw, bl, b_hiw, idesc, kk ? 1u : acc_cross);
+          mma_tf32_pair_words(tmem_cross, al, a_hiw, bl + LO_TILE, b_hiw, idesc, 1);
+          mma_tf32_pair_words(tmem_main, al, a_hiw, bl, b_hiw, idesc, kk ? 1u : accumulate);
+        }
+        mma_commit_pair(bar_empty + 8 * s);      // stage free in the leader ...
+        mma_commit_pair(peer_empty + 8 * s);     // ... and in the peer
+        acc_cross = 1;
+        accumulate = 1;
+        if (++s == P_STAGES) { s = 0; ph ^= 1; stage_off = 0; } else { stage_off += STAGE_STEP; }
+      }
+      mma_commit_pair(bar_acc);
+      mma_commit_pair(peer_acc);
+      if (*abort_flag) {
+        for (int spin = 0; spin < (1 << 16); ++spin)
+          if (mbar_try_wait(bar_acc, 0)) break;
+      }
+    }
+  } else {
+    // ---------------- epilogue warps: this CTA's 128 rows ----------------
+    float part[BN / 2];
+    int drains = 0;
+    bool ok = true;
+    if (p.drain_every > 0) {
+      const uint32_t leader_drained = mapa(bar_drained, 0);
+      uint32_t mph = 0;
+      for (int b = p.drain_every; ok && b < nkb; b += p.drain_every) {
+        ok = mbar_wait_cluster(bar_mid, mph, abort_flag, p.status, 850);
+        mph ^= 1;
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        if (ok) drain_main<BN>(tmem_base, warp, part, drains == 0);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_drained);
+        ++drains;
+      }
+    }
+    if (ok) ok = mbar_wait_cluster(bar_acc, 0, abort_flag, p.status, 900);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    if (ok) epilogue_tile<BN, true>(p, tmem_base, m0, n0, warp, lane, nullptr, p.beta, true, false,
+                                    drains > 0 ? part : nullptr);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();     // neither CTA leaves (or frees TMEM) while the pair's MMAs may still touch it
+  if (warp == EPI_WARPS + 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -253,6 +523,8 @@ int kmajor_tmap(CUtensorMap* tm, const float* base, long long rows, long long co
   if (r != CUDA_SUCCESS) { cb200_set_error("cuTensorMapEncodeTiled failed with %d", (int)r); return CB200_ERR_CUDA; }
   return CB200_OK;
 }
+
+int g_force_variant = 0;     // test hook, see cb200_gemm_presplit_force_variant
 
 // lo = x - trunc_tf32(x), elementwise over a dense span
 __global__ void __launch_bounds__(256) split_lo_kernel(float* lo, const float* x, long long n) {
@@ -318,22 +590,48 @@ int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t l
     long long g = (32ll << 20) / panel_bytes;
     p.group_n = (int)(g < 1 ? 1 : (g > tiles_n ? tiles_n : g));
   }
+  // CTA pairs (256 x 256 tiles) once the single-CTA tiles would fill every SM; smaller problems keep the
+  // 128-row tiles, which spread over more SMs
+  const bool pair = g_force_variant == 2 || (g_force_variant == 0 && tiles_m * tiles_n >= s->sm_count && M > BM);
   CUtensorMap tmA, tmAlo, tmB, tmBlo;
   int rc;
   if ((rc = kmajor_tmap(&tmA, (const float*)A_hi, M, K, lda, BM))) return rc;
   if ((rc = kmajor_tmap(&tmAlo, (const float*)A_lo, M, K, lda, BM))) return rc;
-  if ((rc = kmajor_tmap(&tmB, (const float*)B_hi, N, K, ldb, BN))) return rc;
-  if ((rc = kmajor_tmap(&tmBlo, (const float*)B_lo, N, K, ldb, BN))) return rc;
+  if ((rc = kmajor_tmap(&tmB, (const float*)B_hi, N, K, ldb, pair ? PNH : BN))) return rc;
+  if ((rc = kmajor_tmap(&tmBlo, (const float*)B_lo, N, K, ldb, pair ? PNH : BN))) return rc;
   static std::once_flag once[64];
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[s->device & 63], [&] {
     attr_err = cudaFuncSetAttribute(gemm_presplit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(gemm_presplit_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
   });
   if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
-  const long long grid = tiles_m * tiles_n * p.k_split;
-  gemm_presplit_kernel<<<(unsigned)grid, THREADS, SMEM, s->stream>>>(tmA, tmAlo, tmB, tmBlo, p);
+  if (pair) {
+    const long long pairs = ((M + 2 * BM - 1) / (2 * BM)) * (long long)tiles_n;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(P_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = P_SMEM;
+    cfg.stream = s->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_presplit_pair_kernel, tmA, tmAlo, tmB, tmBlo, p);
+    if (e != cudaSuccess) return cb200_cuda_fail(e, "cudaLaunchKernelEx(gemm_presplit_pair_kernel)", __FILE__, __LINE__);
+  } else {
+    const long long grid = tiles_m * tiles_n * p.k_split;
+    gemm_presplit_kernel<<<(unsigned)grid, THREADS, SMEM, s->stream>>>(tmA, tmAlo, tmB, tmBlo, p);
+  }
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
+
+// Test hook: 0 = choose by problem size (default), 1 = always the single-CTA kernel, 2 = always CTA pairs.
+int cb200_gemm_presplit_force_variant(int variant) { g_force_variant = variant; return CB200_OK; }
 
 }  // extern "C"

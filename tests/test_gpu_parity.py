@@ -2,6 +2,8 @@
 through the C ABI.  Tolerances are the ones the backend is specified to:
 bit-exact for integer / copy work, max rel err <= 1e-4 (fp32) and <= 1e-12
 (fp64), error measured as abs(gpu - ref) / max(abs(ref), rms(ref))."""
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -321,12 +323,27 @@ def test_mnist_convnet_matches_oracle(b200_driver, oracle_driver, datatype):
     assert np.abs(gpu.reshape(32, 10).astype(np.float64).sum(axis=1) - 1.0).max() <= (1e-5 if datatype == "float" else 1e-12)
 
 
+@pytest.fixture
+def presplit_variant():
+    """Forces the pre-split GEMM onto its single-CTA (1) or CTA-pair (2) kernel; back to automatic after."""
+    from cortex_b200 import _lib
+    hook = _lib.load().cb200_gemm_presplit_force_variant
+    hook.argtypes, hook.restype = [ctypes.c_int], ctypes.c_int
+    yield hook
+    hook(0)
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("M,N,K", [(300, 384, 256), (130, 1000, 500), (128, 256, 16), (513, 260, 4112), (1024, 4096, 4096)])
+@pytest.mark.parametrize("M,N,K", [(300, 384, 256), (130, 1000, 500), (128, 256, 16), (513, 260, 4112), (1024, 4096, 4096),
+                                   (1300, 520, 48)])
 @pytest.mark.parametrize("act", [None, "relu"])
-def test_presplit_layer_gemm(b200_driver, M, N, K, act):
+@pytest.mark.parametrize("variant", [1, 2])
+def test_presplit_layer_gemm(b200_driver, presplit_variant, M, N, K, act, variant):
     """The pre-split layer GEMM (operands given as hi / lo matrices, result written as hi / lo) against the
-    general fused kernel (same arithmetic: equal up to summation order) and against float64."""
+    general fused kernel (same arithmetic: equal up to summation order) and against float64, on both of its
+    kernels: 128-row tiles per CTA, and 256-row tiles on CTA pairs (ragged last pair: M = 130, 300, 513, 1300
+    leave the second CTA of the last pair partly or wholly outside the matrix)."""
+    presplit_variant(variant)
     rng = np.random.default_rng(M * 7 + N)
     A = rng.standard_normal((M, K)).astype(np.float32)
     W = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
