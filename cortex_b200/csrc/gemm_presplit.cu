@@ -586,8 +586,10 @@ int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t l
   }
   const long long panel_bytes = (long long)BN * K * 8;      // hi + lo share of one column tile
   p.group_n = tiles_n;
-  if (tiles_n * panel_bytes > (40ll << 20)) {
-    long long g = (32ll << 20) / panel_bytes;
+  // column tiles are swept in groups whose hi + lo panels of B take <= 64 MB (measured best of 16 .. 128 MB
+  // at 8192 x 4096 x 4096: the group's panel stays in L2 while all row tiles pass, and A is re-read once per group)
+  if (tiles_n * panel_bytes > (72ll << 20)) {
+    long long g = (64ll << 20) / panel_bytes;
     p.group_n = (int)(g < 1 ? 1 : (g > tiles_n ? tiles_n : g));
   }
   // CTA pairs (256 x 256 tiles) once the single-CTA tiles would fill every SM; smaller problems keep the
