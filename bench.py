@@ -610,7 +610,9 @@ def run_b200(args, rank, world, local_rank):
         peak_note = "nominal B200 fp64 dense rate 37 TF (no measured fp64 peak exists for this pool); work 2*M*N*K"
         kernel_name, kernel_path = "gemm_f64_kernel (DMMA)", "gemm_bias_act (DMMA fp64, bias+ReLU fused) x5 + softmax"
     achieved = gemm_flops / gemm_ms / 1e9
-    gemm_bytes = (2 * rows * WIDTH + WIDTH * WIDTH + WIDTH) * (4 if dt == "float" else 8)
+    # fp32: the pre-split kernel reads hi + lo of both operands and writes C + C_lo
+    gemm_bytes = ((4 * rows * WIDTH + 2 * WIDTH * WIDTH + WIDTH) * 4 if dt == "float"
+                  else (2 * rows * WIDTH + WIDTH * WIDTH + WIDTH) * 8)
     if dt == "float":
         # dram__bytes_read + dram__bytes_write of the same kernel on an 8192-row shard (ncu, one launch),
         # scaled by the number of row tiles

@@ -326,6 +326,91 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
+// One accumulator read-out by an epilogue thread: its 128 columns of the main accumulator (and, on the last
+// read-out of a tile, of the cross-term accumulator) are added into acc[], which lives in registers (every
+// index below is a compile-time constant).
+__device__ __forceinline__ void read_out(uint32_t tmem_base, int q, int half, float (&acc)[BN / 2], bool first,
+                                         bool with_cross) {
+  const uint32_t lane_col = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * (BN / 2));
+#pragma unroll
+  for (int cc = 0; cc < BN / 2 / 32; ++cc) {
+    uint32_t r[32];
+    tmem_ld_32x32(lane_col + cc * 32, r);
+    tmem_ld_wait();
+    if (first) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = __uint_as_float(r[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[cc * 32 + j] += __uint_as_float(r[j]);
+    }
+    if (with_cross) {
+      tmem_ld_32x32(lane_col + BN + cc * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[cc * 32 + j] += __uint_as_float(r[j]);
+    }
+  }
+}
+
+// C = act(alpha * acc + beta * C + bias) (+ C_lo) for one thread's row m and its 128 columns from n_first on,
+// out of registers: runs while the tensor cores are already busy with the pair's next tile.
+__device__ __forceinline__ void store_row(const GemmParams& p, int m, int n_first, const float (&acc)[BN / 2]) {
+  if (m >= p.M) return;
+  float* crow = p.C + (long long)m * p.ldc;
+  float* lrow = p.C_lo ? p.C_lo + (long long)m * p.ldc : nullptr;
+  const bool vec8 = (p.ldc % 8) == 0 && ((((uintptr_t)p.C) | ((uintptr_t)p.C_lo)) & 31) == 0;
+#pragma unroll
+  for (int cc = 0; cc < BN / 2 / 32; ++cc) {
+    const int nb = n_first + cc * 32;
+    if (nb >= p.N) continue;
+    if (vec8 && nb + 32 <= p.N) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = p.alpha * acc[cc * 32 + j + e];
+        if (p.beta != 0.f) {
+          float c[8];
+          ld_global_v8(crow + nb + j, c, false);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += p.beta * c[e];
+        }
+        if (p.bias) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += p.bias[nb + j + e];
+        }
+        if (p.act) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = apply_act(o[e], p.act);
+        }
+        st_global_v8(crow + nb + j, o);
+        if (lrow) {
+          float l[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) l[e] = lo_part(o[e]);
+          st_global_v8(lrow + nb + j, l);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (nb + j < p.N) {
+          float o = p.alpha * acc[cc * 32 + j];
+          if (p.beta != 0.f) o += p.beta * crow[nb + j];
+          if (p.bias) o += p.bias[nb + j];
+          o = apply_act(o, p.act);
+          crow[nb + j] = o;
+          if (lrow) lrow[nb + j] = lo_part(o);
+        }
+      }
+    }
+  }
+}
+
+// Persistent: cluster c of the grid computes pair tiles c, c + #clusters, ...  The producers run ahead into
+// the next tile while the epilogue warps still hold the previous one; the tensor cores wait only for the
+// accumulators to be READ OUT of TMEM into registers (bar_drained), not for the stores.
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlo,
                           const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmBlo,
@@ -334,35 +419,34 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + P_STAGES * P_STAGE);
   // bars[0..S) full (the leader's copy is used: its two producers arrive, both CTAs' loads complete bytes),
-  // [S..2S) unused, [2S..3S) empty, [3S] accumulators ready, [3S+1] main accumulator may be drained,
-  // [3S+2] drained (the leader's copy is used)
-  uint32_t* tmem_slot = (uint32_t*)(bars + 3 * P_STAGES + 3);
+  // [S..2S) empty, [2S] accumulators may be read out (each CTA's own copy), [2S+1] accumulators have been read
+  // out (the leader's copy is used: one arrival per epilogue warp of both CTAs)
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * P_STAGES + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
 
-  // pair tiles: 256 rows x 256 columns, swept like the single-CTA tiles (column groups, rows inside)
-  const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
-  const int tile_id = (int)blockIdx.x >> 1;
-  const int grp = tile_id / (tiles_m * p.group_n);
-  const int rem = tile_id - grp * tiles_m * p.group_n;
-  const int in_grp = min(p.group_n, tiles_n - grp * p.group_n);
-  const int m0 = (rem / in_grp) * (2 * BM) + (int)rank * BM;       // this CTA's rows of C
-  const int n0 = (grp * p.group_n + rem % in_grp) * BN;            // the pair's columns of C
-  const int nb0 = n0 + (int)rank * PNH;                            // this CTA's slice of B
+  // pair tiles: 256 rows x 256 columns, numbered like the single-CTA tiles (column groups, rows inside)
+  const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + 2 * BM - 1) / (2 * BM), n_tiles = tiles_m * tiles_n;
+  const int n_clusters = (int)gridDim.x >> 1, cluster_id = (int)blockIdx.x >> 1;
   const int nkb = (p.K + BK - 1) / BK;
+  auto tile_origin = [&](int tile_id, int& m0, int& n0) {
+    const int grp = tile_id / (tiles_m * p.group_n);
+    const int rem = tile_id - grp * tiles_m * p.group_n;
+    const int in_grp = min(p.group_n, tiles_n - grp * p.group_n);
+    m0 = (rem / in_grp) * (2 * BM) + (int)rank * BM;       // this CTA's rows of C
+    n0 = (grp * p.group_n + rem % in_grp) * BN;            // the pair's columns of C
+  };
 
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_full = smem_u32(bars),
-                 bar_empty = smem_u32(bars + 2 * P_STAGES), bar_acc = smem_u32(bars + 3 * P_STAGES),
-                 bar_mid = bar_acc + 8, bar_drained = bar_acc + 16;
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + P_STAGES),
+                 bar_mid = smem_u32(bars + 2 * P_STAGES), bar_drained = bar_mid + 8;
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 2);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_acc, 1);
     mbar_init(bar_mid, 1);
     mbar_init(bar_drained, 2 * EPI_WARPS);
     *abort_flag = 0;
@@ -388,24 +472,31 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       const CUtensorMap* lo_map = is_a ? &tmAlo : &tmBlo;
       const uint32_t tile_off = is_a ? 0u : (uint32_t)A_TILE;
       const uint32_t bytes = 2u * (is_a ? 2u * A_TILE : 2u * P_B_TILE);      // this CTA's tiles and the peer's
-      const int row0 = is_a ? m0 : nb0;
       const uint32_t leader_full = mapa(bar_full, 0);
-      int issued = 0, s = 0;
+      long long issued = 0;
+      int s = 0;
       uint32_t ph = 0;
-      for (int i = 0; i < nkb; ++i) {
-        if (!mbar_wait_cluster(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) break;
-        const uint32_t dst = smem_base + s * P_STAGE + tile_off;
-        const int k0 = i * BK;
-        if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, bytes);
-        tma_load_2d_pair(dst, hi_map, k0, row0, leader_full + 8 * s);
-        tma_load_2d_pair(dst + P_RAW, lo_map, k0, row0, leader_full + 8 * s);
-        issued = i + 1;
-        if (++s == P_STAGES) { s = 0; ph ^= 1; }
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < n_tiles; tile += n_clusters) {
+        int m0, n0;
+        tile_origin(tile, m0, n0);
+        const int row0 = is_a ? m0 : n0 + (int)rank * PNH;
+        for (int i = 0; i < nkb; ++i) {
+          if (!mbar_wait_cluster(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) { ok = false; break; }
+          const uint32_t dst = smem_base + s * P_STAGE + tile_off;
+          const int k0 = i * BK;
+          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, bytes);
+          tma_load_2d_pair(dst, hi_map, k0, row0, leader_full + 8 * s);
+          tma_load_2d_pair(dst + P_RAW, lo_map, k0, row0, leader_full + 8 * s);
+          ++issued;
+          if (++s == P_STAGES) { s = 0; ph ^= 1; }
+        }
       }
       if (leader && *abort_flag) {
-        for (int i = issued > P_STAGES ? issued - P_STAGES : 0; i < issued; ++i)
+        // loads in flight complete on the leader's full barriers: give them (bounded) time before leaving
+        for (long long i = issued > P_STAGES ? issued - P_STAGES : 0; i < issued; ++i)
           for (int spin = 0; spin < (1 << 16); ++spin)
-            if (mbar_try_wait(bar_full + 8 * (i % P_STAGES), (i / P_STAGES) & 1)) break;
+            if (mbar_try_wait(bar_full + 8 * (int)(i % P_STAGES), (uint32_t)((i / P_STAGES) & 1))) break;
       }
     }
   } else if (warp == EPI_WARPS + 1) {
@@ -418,70 +509,80 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       const uint32_t a_low0 = (uint32_t)d_a, b_low0 = (uint32_t)d_b;
       constexpr uint32_t LO_TILE = P_RAW >> 4, STAGE_STEP = P_STAGE >> 4;
       const uint32_t tmem_main = tmem_base, tmem_cross = tmem_base + BN;
-      const uint32_t peer_empty = mapa(bar_empty, 1), peer_acc = mapa(bar_acc, 1), peer_mid = mapa(bar_mid, 1);
-      uint32_t acc_cross = 0, accumulate = 0;
+      const uint32_t peer_empty = mapa(bar_empty, 1), peer_mid = mapa(bar_mid, 1);
       int s = 0;
-      uint32_t ph = 0, stage_off = 0;
-      int to_drain = p.drain_every > 0 ? p.drain_every : 0x7fffffff;
-      uint32_t dph = 0;
-      for (int i = 0; i < nkb; ++i) {
-        if (to_drain == 0) {
-          mma_commit_pair(bar_mid);
-          mma_commit_pair(peer_mid);
-          if (!mbar_wait_cluster(bar_drained, dph, abort_flag, p.status, 750)) break;
-          dph ^= 1;
+      uint32_t ph = 0, stage_off = 0, dph = 0;
+      bool ok = true, pending_read_out = false;
+      for (int tile = cluster_id; ok && tile < n_tiles; tile += n_clusters) {
+        uint32_t acc_cross = 0, accumulate = 0;
+        // every p.drain_every k-blocks the epilogue warps add the main accumulator into their registers and
+        // it restarts from zero (tcgen05 accumulates with truncation: shorter runs, smaller bias)
+        int to_drain = p.drain_every > 0 ? p.drain_every : 0x7fffffff;
+        for (int i = 0; i < nkb; ++i) {
+          if (to_drain == 0) {
+            mma_commit_pair(bar_mid);
+            mma_commit_pair(peer_mid);
+            pending_read_out = true;
+            accumulate = 0;
+            to_drain = p.drain_every;
+          }
+          --to_drain;
+          if (!mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, 700 + s)) { ok = false; break; }
+          if (pending_read_out) {
+            // the previous read-out (mid-tile, or the previous tile's last) must be over before these MMAs
+            // overwrite the accumulators
+            if (!mbar_wait_cluster(bar_drained, dph, abort_flag, p.status, 750)) { ok = false; break; }
+            dph ^= 1;
+            pending_read_out = false;
+          }
           tc_fence_after();
-          accumulate = 0;
-          to_drain = p.drain_every;
-        }
-        --to_drain;
-        if (!mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, 700 + s)) break;
-        tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < BK / 8; ++kk) {
-          const uint32_t al = a_low0 + stage_off + kk * 2, bl = b_low0 + stage_off + kk * 2;    // 32 B per k-step
-          mma_tf32_pair_words(tmem_cross, al + LO_TILE, a_hiw, bl, b_hiw, idesc, kk ? 1u : acc_cross);
-          mma_tf32_pair_words(tmem_cross, al, a_hiw, bl + LO_TILE, b_hiw, idesc, 1);
-          mma_tf32_pair_words(tmem_main, al, a_hiw, bl, b_hiw, idesc, kk ? 1u : accumulate);
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            const uint32_t al = a_low0 + stage_off + kk * 2, bl = b_low0 + stage_off + kk * 2;    // 32 B per k-step
+            mma_tf32_pair_words(tmem_cross, al + LO_TILE, a_hiw, bl, b_hiw, idesc, kk ? 1u : acc_cross);
+            mma_tf32_pair_words(tmem_cross, al, a_hiw, bl + LO_TILE, b_hiw, idesc, 1);
+            mma_tf32_pair_words(tmem_main, al, a_hiw, bl, b_hiw, idesc, kk ? 1u : accumulate);
+          }
+          mma_commit_pair(bar_empty + 8 * s);      // stage free in the leader ...
+          mma_commit_pair(peer_empty + 8 * s);     // ... and in the peer
+          acc_cross = 1;
+          accumulate = 1;
+          if (++s == P_STAGES) { s = 0; ph ^= 1; stage_off = 0; } else { stage_off += STAGE_STEP; }
         }
-        mma_commit_pair(bar_empty + 8 * s);      // stage free in the leader ...
-        mma_commit_pair(peer_empty + 8 * s);     // ... and in the peer
-        acc_cross = 1;
-        accumulate = 1;
-        if (++s == P_STAGES) { s = 0; ph ^= 1; stage_off = 0; } else { stage_off += STAGE_STEP; }
+        if (!ok) break;
+        mma_commit_pair(bar_mid);                  // tile finished: last read-out
+        mma_commit_pair(peer_mid);
+        pending_read_out = true;
       }
-      mma_commit_pair(bar_acc);
-      mma_commit_pair(peer_acc);
       if (*abort_flag) {
         for (int spin = 0; spin < (1 << 16); ++spin)
-          if (mbar_try_wait(bar_acc, 0)) break;
+          if (mbar_try_wait(bar_mid, 0) || mbar_try_wait(bar_mid, 1)) break;
       }
     }
   } else {
     // ---------------- epilogue warps: this CTA's 128 rows ----------------
-    float part[BN / 2];
-    int drains = 0;
+    const int q = warp & 3, half = warp >> 2;
+    const uint32_t leader_drained = mapa(bar_drained, 0);
+    float acc[BN / 2];
+    uint32_t mph = 0;
     bool ok = true;
-    if (p.drain_every > 0) {
-      const uint32_t leader_drained = mapa(bar_drained, 0);
-      uint32_t mph = 0;
-      for (int b = p.drain_every; ok && b < nkb; b += p.drain_every) {
+    for (int tile = cluster_id; ok && tile < n_tiles; tile += n_clusters) {
+      int m0, n0;
+      tile_origin(tile, m0, n0);
+      const int n_mid = p.drain_every > 0 ? (nkb - 1) / p.drain_every : 0;
+      for (int ev = 0; ev <= n_mid; ++ev) {
         ok = mbar_wait_cluster(bar_mid, mph, abort_flag, p.status, 850);
         mph ^= 1;
         ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         tc_fence_after();
-        if (ok) drain_main<BN>(tmem_base, warp, part, drains == 0);
+        read_out(tmem_base, q, half, acc, ev == 0, ev == n_mid);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(leader_drained);
-        ++drains;
       }
+      if (ok) store_row(p, m0 + q * 32 + lane, n0 + half * (BN / 2), acc);
     }
-    if (ok) ok = mbar_wait_cluster(bar_acc, 0, abort_flag, p.status, 900);
-    ok = __all_sync(0xffffffffu, ok);
-    tc_fence_after();
-    if (ok) epilogue_tile<BN, true>(p, tmem_base, m0, n0, warp, lane, nullptr, p.beta, true, false,
-                                    drains > 0 ? part : nullptr);
   }
 
   tc_fence_before();
@@ -611,8 +712,9 @@ int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t l
   if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
   if (pair) {
     const long long pairs = ((M + 2 * BM - 1) / (2 * BM)) * (long long)tiles_n;
+    const long long clusters = pairs < s->sm_count / 2 ? pairs : s->sm_count / 2;     // persistent: one pair per two SMs
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
     cfg.blockDim = dim3(P_THREADS, 1, 1);
     cfg.dynamicSmemBytes = P_SMEM;
     cfg.stream = s->stream;
