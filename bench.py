@@ -616,8 +616,9 @@ def run_b200(args, rank, world, local_rank):
     if dt == "float":
         # dram__bytes_read + dram__bytes_write of the same kernel on an 8192-row shard (ncu, one launch),
         # scaled by the number of row tiles
-        traffic = (538.3e6 + 223.1e6) * rows / 8192.0
-        traffic_note = "ncu capture of the 8192-row launch (761 MB) x rows/8192; not memory-bound (~8 % of HBM rate)"
+        traffic = (1221.3e6 + 243.7e6) * rows / 8192.0
+        traffic_note = ("ncu capture of the 8192-row launch of gemm_presplit_pair_kernel (1.22 GB read + 0.24 GB "
+                        "written) x rows/8192; not memory-bound (~18 % of HBM rate)")
     else:
         traffic, traffic_note = None, "no capture of the fp64 kernel's DRAM counters"
     line = {
