@@ -16,6 +16,11 @@ int cb200_gemm_f64_launch(cb200_stream* s, double* C, long long ldc, int trans_a
                           const double* A, int M, int K, long long lda, const double* B, int N, long long ldb,
                           double beta, const double* bias, int act, const PeerList* peers);
 
+bool cb200_gemm_presplit_auto_ok(cb200_stream* s, int M, int N, int K, int trans_a, int trans_b);
+int cb200_gemm_presplit_auto_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
+                                    const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
+                                    float beta, const float* bias, int act);
+
 namespace {
 
 template <typename T> __device__ __forceinline__ T act_apply(T v, int act) {
@@ -131,6 +136,12 @@ int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int
     const float* a = (const float*)A;
     const float* b = (const float*)B;
     if (cb200_gemm_tf32x3_eligible(a, lda, b, ldb, M, N, K)) {
+      // problems that fill the GPU with 256 x 256 tiles: split (and, for MN-major operands, transpose) the
+      // operands into the stream's workspace once, then the CTA-pair kernel, whose main loop has no
+      // shared-memory pass; its in-kernel accumulator read-outs replace the K chunking below
+      if ((!peers || peers->n == 0) && cb200_gemm_presplit_auto_ok(s, M, N, K, trans_a, trans_b))
+        return cb200_gemm_presplit_auto_launch(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb,
+                                               (float)beta, (const float*)bias, act);
       // tcgen05 accumulates with truncation, so the result drifts toward zero by about 7e-9 * K
       // (relative, worst case all-positive data).  Long reductions are therefore cut into K chunks
       // chained through C (beta = 1), each chunk boundary being a round-to-nearest fp32 add in the

@@ -638,40 +638,60 @@ __global__ void __launch_bounds__(256) split_lo_kernel(float* lo, const float* x
     lo[i] = lo_part(x[i]);
 }
 
-}  // namespace
-
-extern "C" {
-
-int cb200_split_lo(cb200_stream* s, void* lo, const void* x, int64_t n_elems) {
-  CB_REQUIRE(s && lo && x && n_elems >= 0, "split_lo: bad argument");
-  CB_REQUIRE((((uintptr_t)lo | (uintptr_t)x) & 15) == 0, "split_lo: buffers must be 16-byte aligned");
-  if (n_elems == 0) return CB200_OK;
-  DeviceGuard guard(s->device);
-  long long blocks = (n_elems / 4 + 255) / 256 + 1;
-  const long long cap = (long long)s->sm_count * 16;
-  if (blocks > cap) blocks = cap;
-  split_lo_kernel<<<(unsigned)blocks, 256, 0, s->stream>>>((float*)lo, (const float*)x, n_elems);
-  CB_LAUNCH_CHECK(s);
-  return CB200_OK;
+// lo[r, c] = x[r, c] - trunc_tf32(x[r, c]) for a pitched [rows, cols] view (pitches multiples of 4, 16-byte bases)
+__global__ void __launch_bounds__(256) split_lo_rows_kernel(float* lo, long long ldl, const float* x, long long ldx,
+                                                            int rows, int cols) {
+  const int groups = (cols + 3) / 4;
+  const long long total = (long long)rows * groups;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / groups), c = (int)(i - (long long)r * groups) * 4;
+    const float* src = x + (long long)r * ldx + c;
+    float* dst = lo + (long long)r * ldl + c;
+    if (c + 4 <= cols) {
+      const float4 v = *reinterpret_cast<const float4*>(src);
+      *reinterpret_cast<float4*>(dst) = make_float4(lo_part(v.x), lo_part(v.y), lo_part(v.z), lo_part(v.w));
+    } else {
+      for (int e = 0; c + e < cols; ++e) dst[e] = lo_part(src[e]);
+    }
+  }
 }
 
-int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t ldc, double alpha, const void* A_hi,
-                                 const void* A_lo, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B_hi,
-                                 const void* B_lo, int64_t b_rows, int64_t ldb, double beta, const void* bias, int act) {
-  CB_REQUIRE(s && C && A_hi && A_lo && B_hi && B_lo, "gemm_bias_act_presplit: null argument");
-  CB_REQUIRE(a_rows >= 1 && a_cols >= 1 && b_rows >= 1 && a_rows <= 2147483647LL && a_cols <= 2147483647LL &&
-                 b_rows <= 2147483647LL, "gemm_bias_act_presplit: bad extents");
-  CB_REQUIRE(ldc >= b_rows && lda >= a_cols && ldb >= a_cols, "gemm_bias_act_presplit: pitch smaller than the row");
-  CB_REQUIRE((((uintptr_t)A_hi | (uintptr_t)A_lo | (uintptr_t)B_hi | (uintptr_t)B_lo) & 15) == 0 && (lda % 4) == 0 &&
-                 (ldb % 4) == 0, "gemm_bias_act_presplit: operands must be 16-byte aligned with pitches that are multiples of 4");
-  CB_REQUIRE(act >= CB200_ACT_NONE && act <= CB200_ACT_LOGISTIC, "gemm_bias_act_presplit: unknown activation %d", act);
-  const int M = (int)a_rows, K = (int)a_cols, N = (int)b_rows;
+// x stored [K, R] (pitch ldx)  ->  hi[R, K] = x^T and lo[R, K] = x^T - trunc_tf32(x^T) (pitch ldo): makes an
+// MN-major gemm! operand K-major and splits it in the same pass
+__global__ void __launch_bounds__(256) split_transpose_kernel(float* hi, float* lo, long long ldo, const float* x,
+                                                              long long ldx, int K, int R) {
+  __shared__ float t[32][33];
+  const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int k = k0 + threadIdx.y + 8 * j, r = r0 + threadIdx.x;
+    if (k < K && r < R) t[threadIdx.y + 8 * j][threadIdx.x] = x[(long long)k * ldx + r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int r = r0 + threadIdx.y + 8 * j, k = k0 + threadIdx.x;
+    if (r < R && k < K) {
+      const float v = t[threadIdx.x][threadIdx.y + 8 * j];
+      hi[(long long)r * ldo + k] = v;
+      lo[(long long)r * ldo + k] = lo_part(v);
+    }
+  }
+}
+
+int g_gemm_auto_mode = 0;    // test hook, see cb200_gemm_auto_presplit_mode
+
+// The launch itself: operands as (hi, lo) pairs with their own pitches.
+int launch_presplit(cb200_stream* s, float* C, float* C_lo, long long ldc, float alpha, const float* A_hi,
+                    long long lda_hi, const float* A_lo, long long lda_lo, int M, int K, const float* B_hi,
+                    long long ldb_hi, const float* B_lo, long long ldb_lo, int N, float beta, const float* bias, int act,
+                    int variant) {
   DeviceGuard guard(s->device);
   GemmParams p;
   p.n_peers = 0;
   for (int d = 0; d < MAX_PEERS; ++d) p.peers[d] = nullptr;
-  p.C = (float*)C; p.C_lo = (float*)C_lo; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
-  p.alpha = (float)alpha; p.beta = (float)beta; p.bias = (const float*)bias; p.act = act;
+  p.C = C; p.C_lo = C_lo; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
+  p.alpha = alpha; p.beta = beta; p.bias = bias; p.act = act;
   p.a_mn_major = 0; p.b_mn_major = 0; p.store_mode = STORE_ROW_MAJOR; p.hw = 1; p.flags = 0; p.status = s->status_dev;
   const long long tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
@@ -681,10 +701,6 @@ int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t l
   p.drain_every = K >= 4096 ? 2048 / BK : 0;
   p.split_block = 2 * s->sm_count;
   p.tile_flags = nullptr;
-  if (p.k_split == 2) {
-    int rcf = cb200_tile_flags(s, (size_t)tiles_m * tiles_n, &p.tile_flags);
-    if (rcf) return rcf;
-  }
   const long long panel_bytes = (long long)BN * K * 8;      // hi + lo share of one column tile
   p.group_n = tiles_n;
   // column tiles are swept in groups whose hi + lo panels of B take <= 64 MB (measured best of 16 .. 128 MB
@@ -695,13 +711,13 @@ int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t l
   }
   // CTA pairs (256 x 256 tiles) once the single-CTA tiles would fill every SM; smaller problems keep the
   // 128-row tiles, which spread over more SMs
-  const bool pair = g_force_variant == 2 || (g_force_variant == 0 && tiles_m * tiles_n >= s->sm_count && M > BM);
+  const bool pair = variant == 2 || (variant == 0 && tiles_m * tiles_n >= s->sm_count && M > BM);
   CUtensorMap tmA, tmAlo, tmB, tmBlo;
   int rc;
-  if ((rc = kmajor_tmap(&tmA, (const float*)A_hi, M, K, lda, BM))) return rc;
-  if ((rc = kmajor_tmap(&tmAlo, (const float*)A_lo, M, K, lda, BM))) return rc;
-  if ((rc = kmajor_tmap(&tmB, (const float*)B_hi, N, K, ldb, pair ? PNH : BN))) return rc;
-  if ((rc = kmajor_tmap(&tmBlo, (const float*)B_lo, N, K, ldb, pair ? PNH : BN))) return rc;
+  if ((rc = kmajor_tmap(&tmA, A_hi, M, K, lda_hi, BM))) return rc;
+  if ((rc = kmajor_tmap(&tmAlo, A_lo, M, K, lda_lo, BM))) return rc;
+  if ((rc = kmajor_tmap(&tmB, B_hi, N, K, ldb_hi, pair ? PNH : BN))) return rc;
+  if ((rc = kmajor_tmap(&tmBlo, B_lo, N, K, ldb_lo, pair ? PNH : BN))) return rc;
   static std::once_flag once[64];
   cudaError_t attr_err = cudaSuccess;
   std::call_once(once[s->device & 63], [&] {
@@ -733,6 +749,93 @@ int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t l
   }
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
+}
+
+}  // namespace
+
+// gemm! / gemm_bias_act through the pre-split pair kernel: worth it when the problem fills the GPU with
+// 256 x 256 pair tiles and the split copies fit a bounded per-stream workspace.
+bool cb200_gemm_presplit_auto_ok(cb200_stream* s, int M, int N, int K, int trans_a, int trans_b) {
+  if (g_gemm_auto_mode == 1) return false;
+  const long long kp = (K + 3) / 4 * 4;
+  const long long floats = (long long)M * kp * (trans_a ? 2 : 1) + (long long)N * kp * (trans_b ? 1 : 2);
+  if (floats * 4 > (2ll << 30)) return false;
+  if (g_gemm_auto_mode == 2) return true;
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return M > BM && tiles >= s->sm_count && K >= 256;
+}
+
+// C = act(alpha * op(A) * op(B) + beta * C + bias) for TMA-addressable fp32 operands in any of the four
+// layouts: a K-major operand (A not transposed, B transposed) is used in place and only its lo matrix is
+// written to the stream's workspace; an MN-major one is transposed into the workspace as hi and lo.
+int cb200_gemm_presplit_auto_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
+                                    const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
+                                    float beta, const float* bias, int act) {
+  DeviceGuard guard(s->device);
+  const long long kp = (K + 3) / 4 * 4;
+  const size_t a_lo_f = (size_t)M * kp, a_hi_f = trans_a ? (size_t)M * kp : 0;
+  const size_t b_lo_f = (size_t)N * kp, b_hi_f = trans_b ? 0 : (size_t)N * kp;
+  void* ws = nullptr;
+  int rc = cb200_scratch(s, (a_lo_f + a_hi_f + b_lo_f + b_hi_f) * sizeof(float), &ws);
+  if (rc) return rc;
+  float* a_lo = (float*)ws;
+  float* a_hi = a_lo + a_lo_f;
+  float* b_lo = a_hi + a_hi_f;
+  float* b_hi = b_lo + b_lo_f;
+  const long long cap = (long long)s->sm_count * 16;
+  auto split_rows = [&](float* lo, const float* x, long long ldx, int rows) {
+    long long blocks = ((long long)rows * (kp / 4) + 255) / 256;
+    if (blocks > cap) blocks = cap;
+    split_lo_rows_kernel<<<(unsigned)blocks, 256, 0, s->stream>>>(lo, kp, x, ldx, rows, K);
+  };
+  auto split_t = [&](float* hi, float* lo, const float* x, long long ldx, int R) {
+    dim3 grid((unsigned)((R + 31) / 32), (unsigned)((K + 31) / 32), 1);
+    split_transpose_kernel<<<grid, dim3(32, 8, 1), 0, s->stream>>>(hi, lo, kp, x, ldx, K, R);
+  };
+  const float* a_hi_p = A;
+  long long a_hi_ld = lda;
+  if (trans_a) { split_t(a_hi, a_lo, A, lda, M); a_hi_p = a_hi; a_hi_ld = kp; } else { split_rows(a_lo, A, lda, M); }
+  CB_LAUNCH_CHECK(s);
+  const float* b_hi_p = B;
+  long long b_hi_ld = ldb;
+  if (!trans_b) { split_t(b_hi, b_lo, B, ldb, N); b_hi_p = b_hi; b_hi_ld = kp; } else { split_rows(b_lo, B, ldb, N); }
+  CB_LAUNCH_CHECK(s);
+  return launch_presplit(s, C, nullptr, ldc, alpha, a_hi_p, a_hi_ld, a_lo, kp, M, K, b_hi_p, b_hi_ld, b_lo, kp, N, beta,
+                         bias, act, g_gemm_auto_mode == 2 ? 2 : 0);
+}
+
+extern "C" {
+
+// Test hook: 0 = gemm! takes the pre-split path by problem size (default), 1 = never, 2 = whenever TMA can
+// address the operands (on CTA pairs).
+int cb200_gemm_auto_presplit_mode(int mode) { g_gemm_auto_mode = mode; return CB200_OK; }
+
+int cb200_split_lo(cb200_stream* s, void* lo, const void* x, int64_t n_elems) {
+  CB_REQUIRE(s && lo && x && n_elems >= 0, "split_lo: bad argument");
+  CB_REQUIRE((((uintptr_t)lo | (uintptr_t)x) & 15) == 0, "split_lo: buffers must be 16-byte aligned");
+  if (n_elems == 0) return CB200_OK;
+  DeviceGuard guard(s->device);
+  long long blocks = (n_elems / 4 + 255) / 256 + 1;
+  const long long cap = (long long)s->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  split_lo_kernel<<<(unsigned)blocks, 256, 0, s->stream>>>((float*)lo, (const float*)x, n_elems);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t ldc, double alpha, const void* A_hi,
+                                 const void* A_lo, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B_hi,
+                                 const void* B_lo, int64_t b_rows, int64_t ldb, double beta, const void* bias, int act) {
+  CB_REQUIRE(s && C && A_hi && A_lo && B_hi && B_lo, "gemm_bias_act_presplit: null argument");
+  CB_REQUIRE(a_rows >= 1 && a_cols >= 1 && b_rows >= 1 && a_rows <= 2147483647LL && a_cols <= 2147483647LL &&
+                 b_rows <= 2147483647LL, "gemm_bias_act_presplit: bad extents");
+  CB_REQUIRE(ldc >= b_rows && lda >= a_cols && ldb >= a_cols, "gemm_bias_act_presplit: pitch smaller than the row");
+  CB_REQUIRE((((uintptr_t)A_hi | (uintptr_t)A_lo | (uintptr_t)B_hi | (uintptr_t)B_lo) & 15) == 0 && (lda % 4) == 0 &&
+                 (ldb % 4) == 0, "gemm_bias_act_presplit: operands must be 16-byte aligned with pitches that are multiples of 4");
+  CB_REQUIRE(act >= CB200_ACT_NONE && act <= CB200_ACT_LOGISTIC, "gemm_bias_act_presplit: unknown activation %d", act);
+  return launch_presplit(s, (float*)C, (float*)C_lo, ldc, (float)alpha, (const float*)A_hi, lda, (const float*)A_lo, lda,
+                         (int)a_rows, (int)a_cols, (const float*)B_hi, ldb, (const float*)B_lo, ldb, (int)b_rows,
+                         (float)beta, (const float*)bias, act, g_force_variant);
 }
 
 // Test hook: 0 = choose by problem size (default), 1 = always the single-CTA kernel, 2 = always CTA pairs.

@@ -48,6 +48,34 @@ def test_gemm_matches_oracle(b200_driver, oracle_driver, datatype, ta, tb, shape
         assert pc.rel_err(gpu, ref64()) <= pc.TOL[datatype], (alpha, beta)
 
 
+@pytest.fixture
+def gemm_auto_presplit():
+    """gemm! routing hook: 2 = take the split-into-workspace + CTA-pair kernel path whenever TMA can address
+    the operands, 1 = never; back to the size-based choice afterwards."""
+    from cortex_b200 import _lib
+    hook = _lib.load().cb200_gemm_auto_presplit_mode
+    hook.argtypes, hook.restype = [ctypes.c_int], ctypes.c_int
+    yield hook
+    hook(0)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)],
+                         ids=["NN", "NT", "TN", "TT"])
+@pytest.mark.parametrize("shape", GEMM_SHAPES + [(700, 520, 4200, 8, 4)], ids=lambda s: "x".join(map(str, s)))
+def test_gemm_through_presplit_pair_path(b200_driver, oracle_driver, gemm_auto_presplit, ta, tb, shape):
+    """gemm! forced onto the path large problems take: operands split (MN-major ones also transposed) into
+    the stream's workspace, then the CTA-pair kernel.  Same cases and bounds as test_gemm_matches_oracle,
+    whole backing buffer compared (the frame around a pitched window stays untouched)."""
+    gemm_auto_presplit(2)
+    m, n, k, pad, off = shape
+    for alpha, beta in ((1.5, 0.5), (1.0, 0.0), (1.0, 1.0)):
+        run, ref64 = pc.gemm_case("float", m, n, k, ta, tb, alpha, beta, pad, off)
+        gpu = _on(b200_driver, "float", run)
+        cpu = _on(oracle_driver, "float", run)
+        assert pc.rel_err(gpu, cpu) <= pc.TOL["float"], (alpha, beta)
+        assert pc.rel_err(gpu, ref64()) <= pc.TOL["float"], (alpha, beta)
+
+
 def test_gemm_beta_zero_ignores_nan_in_c(b200_driver):
     """BLAS semantics: with beta = 0, C is overwritten without being read."""
     rng = np.random.default_rng(5)
