@@ -255,6 +255,11 @@ def bench_eltwise(drv, dev, peaks):
         cases["ternary_select_prelu"] = (lambda i: ct.ternary_op(ys[i], 1.0, xs[i], 0.25, xs[i], 1.0, xs[i], "select"),
                                          2 * rows * cols * 4)
         cases["gemv_8192x4096"] = (lambda i: ct.gemv(outv, False, 1.0, xs[i], vec, 0.0), rows * cols * 4 + cols * 4 + rows * 4)
+        # backward ring: activation-gradient! (reads output and output-gradient, writes input-gradient)
+        grads = [ct.to_tensor(rng.standard_normal((rows, cols), dtype=np.float32)) for _ in range(sets)]
+        for op_name in ("relu", "tanh"):
+            cases["activation_gradient_" + op_name] = (
+                lambda i, op_name=op_name: ct.activation_gradient(ys[i], grads[i], xs[i], op_name), 3 * rows * cols * 4)
         # batch-normalize! (inference, spatial form) on the config-4 activation shape viewed as [128, 64, 4096]
         bn_stats = [ct.to_tensor(np.abs(rng.standard_normal(64)).astype(np.float32) + 0.5) for _ in range(4)]
         bn_in = [ct.in_place_reshape(x, [128, 64, 4096]) for x in xs]

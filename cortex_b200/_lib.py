@@ -106,6 +106,7 @@ SIGNATURES = {
     "cb200_ipc_export": [_i, _vp, C.c_char_p],
     "cb200_ipc_import": [_i, C.c_char_p, C.POINTER(_vp)],
     "cb200_ipc_close": [_i, _vp],
+    "cb200_activation_gradient": [_vp, _i, _vp, _pd, _vp, _pd, _vp, _pd, _i, _i64],
     "cb200_split_lo": [_vp, _vp, _vp, _i64],
     "cb200_gemm_bias_act_presplit": [_vp, _vp, _vp, _i64, _d, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _d, _vp, _i],
     "cb200_bias_relu_rowstats": [_vp, _i, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp],

@@ -9,6 +9,9 @@ Mirrors the reference's compute layers:
   Pooling           PoolingLayer                  compute/nn/layers.clj:391-409
   BatchNormalization  (inference branch)          compute/nn/layers.clj:228-285
   ConvNet           a layer list run in order, the shape of verify/nn/train.clj:24-41 (MNIST-NETWORK)
+Backward passes of the dense layers (the next ring around the inference path):
+  biased_multiply_backward   nn-backend/biased-multiply-backward!   compute/nn/backend.clj:115-139
+  Linear.backward / Activation.backward / Softmax.backward          compute/nn/layers.clj:78-88, 104-116, 164-168
 
 ``fused=True`` replaces the reference's three calls per dense layer
 (assign! bias, gemm! NT beta=1, binary-op! max 0) with the backend's single
@@ -25,6 +28,19 @@ def biased_multiply(input, weights, bias, output):
     ct.assign(output, bias)
     ct.gemm(output, False, True, 1.0, input, weights, 1.0)
     return output
+
+
+def biased_multiply_backward(input, weights, bias, output, input_gradient, weight_gradient, bias_gradient,
+                             output_gradient):
+    """bias-gradient += sum over the batch of output-gradient (binary-op! with a destination smaller than the
+    operation: compare-and-swap accumulation); input-gradient = output-gradient . weights (gemm! NN, beta 0);
+    weight-gradient += output-gradient^T . input (gemm! TN, beta 1).  Any of the three gradients may be None."""
+    if bias_gradient is not None:
+        ct.binary_op(bias_gradient, 1.0, output_gradient, 1.0, bias_gradient, "+")
+    if input_gradient is not None:
+        ct.gemm(ct.as_batch_matrix(input_gradient), False, False, 1.0, ct.as_batch_matrix(output_gradient), weights, 0.0)
+    if weight_gradient is not None:
+        ct.gemm(weight_gradient, True, False, 1.0, ct.as_batch_matrix(output_gradient), ct.as_batch_matrix(input), 1.0)
 
 
 def relu(input, output):
@@ -49,6 +65,11 @@ class Linear:
 
     def forward(self, input, output):
         return biased_multiply(input, self.weights, self.bias, output)
+
+    def backward(self, input, output, input_gradient, output_gradient, weight_gradient, bias_gradient):
+        """Gradients ACCUMULATE into weight_gradient / bias_gradient, as in the reference (the optimiser clears them)."""
+        return biased_multiply_backward(input, self.weights, self.bias, output, input_gradient, weight_gradient,
+                                        bias_gradient, output_gradient)
 
     def prepare_presplit(self):
         """Compute the weights' lo matrix (x - trunc_tf32(x)) once; needed by forward_presplit."""
@@ -96,10 +117,17 @@ class Activation:
     def forward(self, input, output):
         return _ACTIVATIONS[self.act_type](input, output)
 
+    def backward(self, output, input_gradient, output_gradient):
+        return ct.activation_gradient(input_gradient, output_gradient, output, self.act_type)
+
 
 class Softmax:
     def forward(self, input, output):
         return ct.softmax(output, input)
+
+    def backward(self, input_gradient, output_gradient):
+        """The reference pairs softmax with the cross-entropy loss: the layer passes the gradient through."""
+        return ct.assign(input_gradient, output_gradient)
 
 
 class Convolution:

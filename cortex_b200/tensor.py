@@ -462,6 +462,24 @@ def binary_op(dest, alpha, x, beta, y, op):
 
 # ------------------------------ ternary-op! ---------------------------------------
 
+def activation_gradient(input_gradient, output_gradient, output, op):
+    """input-gradient from the output of an activation (tensor.clj:1256-1283):
+    logistic: out * (1 - out) * out-grad;  tanh: (1 - out * out) * out-grad;  relu: (out > 0) ? out-grad : 0."""
+    _ensure_datatypes(input_gradient.get_datatype(), output, output_gradient)
+    _ensure_same_device(input_gradient, output, output_gradient)
+    _require(input_gradient.get_datatype() in ("float", "double"),
+             "activation-gradient! is only defined for float and double tensors", input_gradient.get_datatype())
+    _require(op in ("logistic", "tanh", "relu"), "Only :logistic :tanh and :relu are supported", op)
+    out_ecount = output.ecount()
+    _require(out_ecount == input_gradient.ecount() and out_ecount == output_gradient.ecount(),
+             "All element ecounts must match",
+             {"out-ecount": out_ecount, "in-grad-ecount": input_gradient.ecount(),
+              "out-grad-ecount": output_gradient.ecount()})
+    check_stream().activation_gradient(input_gradient.buffer, input_gradient.dimensions, output_gradient.buffer,
+                                       output_gradient.dimensions, output.buffer, output.dimensions, op, out_ecount)
+    return input_gradient
+
+
 TERNARY_OPERATIONS = ("select",)
 
 

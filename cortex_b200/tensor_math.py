@@ -150,6 +150,13 @@ class CTensorMath:
         from ._lib import call
         call("cb200_unsupported", name.encode())
 
+    def activation_gradient(self, input_gradient, input_grad_dims, output_gradient, output_grad_dims, output,
+                            output_dims, op, element_count):
+        """tm/activation-gradient! (tensor/math.clj; CPU cpu/tensor_math.clj:1638-1650)."""
+        self._tm("activation_gradient", DTYPE_CODE[input_gradient.dtype], input_gradient.ptr,
+                 C.byref(wire(input_grad_dims)), output_gradient.ptr, C.byref(wire(output_grad_dims)), output.ptr,
+                 C.byref(wire(output_dims)), ACTIVATIONS[op], int(element_count))
+
     # --- ternary-op! family: one C entry point, constants travel as (NULL pointer, value * factor) ------
     def _ternary(self, dest, dest_dims, args, n_elems, op):
         """args: three (buffer-or-None, dims-or-None, scalar) in x, y, z order."""

@@ -221,6 +221,14 @@ int cb200_ternary_op(cb200_stream* s, int dtype, void* dest, const cb200_dims* d
                      const void* x, const cb200_dims* x_dims, double alpha,
                      const void* y, const cb200_dims* y_dims, double beta,
                      const void* z, const cb200_dims* z_dims, double gamma, int64_t n_elems, int op);
+/* activation-gradient! (src/cortex/tensor.clj:1256-1283 -> tm/activation-gradient!; CPU semantics
+ * src/cortex/compute/cpu/tensor_math.clj:1318-1363; CUDA reference cudnnActivationBackward):
+ *   logistic: in_grad = out * (1 - out) * out_grad;  tanh: (1 - out*out) * out_grad;  relu: (out > 0) * out_grad.
+ * float / double; float views are computed in double and rounded once (bit-identical to the CPU backend).
+ * act: CB200_ACT_RELU / CB200_ACT_TANH / CB200_ACT_LOGISTIC.  in_grad may alias out_grad or out. */
+int cb200_activation_gradient(cb200_stream* s, int dtype, void* in_grad, const cb200_dims* in_grad_dims,
+                              const void* out_grad, const cb200_dims* out_grad_dims,
+                              const void* out, const cb200_dims* out_dims, int act, int64_t n_elems);
 /* gemv! (src/cortex/tensor/math.clj:116-124, cublasSgemv/Dgemv at src/cortex/compute/cuda/tensor_math.clj:155-173):
  *   c = alpha * op(A) * x + beta * c;  A: a_rows x a_cols row-major with row pitch lda (elements);
  *   trans_a: op(A) = A^T (c then has a_cols entries, x has a_rows); inc_c / inc_x in elements. */

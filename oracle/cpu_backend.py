@@ -46,6 +46,7 @@ _SIGS = {
     "orc_pooling_forward": [_i, _vp, _vp] + [_i64] * 11 + [_i],
     "orc_gemv": [_i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],
     "orc_ternary_op": [_i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
+    "orc_activation_gradient": [_i, _vp, _pd, _vp, _pd, _vp, _pd, _i, _i64],
     "orc_softmax_eltwise": [_i, _vp, _pd, _vp, _pd],
     "orc_softmax_spatial": [_i, _vp, _pd, _vp, _pd],
     "orc_convolution_forward": [_i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],

@@ -476,6 +476,30 @@ int orc_ternary_op(int dtype, void* dest, const orc_dims* dd, const void* x, con
   return 1;
 }
 
+/* ---- activation gradient (cpu/tensor_math.clj:1318-1363, act-backward-impl) -------------------------
+ * logistic: out * (1 - out) * out_grad;  tanh: (1 - out*out) * out_grad;  relu: (out > 0 ? 1 : 0) * out_grad.
+ * Clojure arithmetic on float views runs in double, (* a b c) folds left to right, one final cast. */
+#define ACTGRAD_BODY(T) { T* ig = (T*)in_grad; const T* og = (const T*)out_grad; const T* o = (const T*)out; \
+  _Pragma("omp parallel for") for (int64_t i = 0; i < n; ++i) { \
+    double ov = (double)o[ADDR(od, os, mx, i)], gv = (double)og[ADDR(ogd, ogs, mx, i)], r; \
+    if (act == 3) r = (ov * (1.0 - ov)) * gv; else if (act == 2) r = (1.0 - ov * ov) * gv; \
+    else r = (ov > 0.0 ? 1.0 : 0.0) * gv; \
+    ig[ADDR(igd, igs, mx, i)] = (T)r; } return 0; }
+int orc_activation_gradient(int dtype, void* in_grad, const orc_dims* igd, const void* out_grad, const orc_dims* ogd,
+                            const void* out, const orc_dims* od, int act, int64_t n) {
+  if (act < 1 || act > 3) return 1;
+  int32_t mx[5];
+  for (int d = 0; d < 5; ++d) {
+    mx[d] = igd->rev_shape[d];
+    if (ogd->rev_shape[d] > mx[d]) mx[d] = ogd->rev_shape[d];
+    if (od->rev_shape[d] > mx[d]) mx[d] = od->rev_shape[d];
+  }
+  int igs = is_simple(igd, mx), ogs = is_simple(ogd, mx), os = is_simple(od, mx);
+  if (dtype == T_FLOAT) ACTGRAD_BODY(float)
+  if (dtype == T_DOUBLE) ACTGRAD_BODY(double)
+  return 1;
+}
+
 /* ---- softmax (cpu/tensor_math.clj:1037-1103) --------------------------------------------------- */
 #define SOFTMAX_BODY(T) { const T* ip = (const T*)in; T* op_ = (T*)out; \
   _Pragma("omp parallel for") for (int64_t r = 0; r < rows; ++r) { \

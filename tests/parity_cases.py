@@ -145,6 +145,109 @@ def mlp_case(datatype, batch, widths, seed=101, fused=False, bias_scale=0.0, pre
     return run, reference
 
 
+def mlp_backward_case(datatype, batch, widths, seed=131, act="relu"):
+    """One training step's forward + backward through dense layers with an activation between them and a
+    softmax head: d(loss)/d(logits) = probs - onehot (softmax + cross-entropy), then the reference's backward
+    calls per layer (assign! for softmax, activation-gradient!, biased-multiply-backward!).
+    Returns the concatenation [input-gradient, weight and bias gradients of every layer]."""
+    dt = NP[datatype]
+    rng = np.random.default_rng(seed)
+    X = rng.random((batch, widths[0])).astype(dt)
+    labels = rng.integers(0, widths[-1], size=batch)
+    Ws = [(rng.standard_normal((widths[i + 1], widths[i])) * np.sqrt(2.0 / widths[i])).astype(dt)
+          for i in range(len(widths) - 1)]
+    bs = [(rng.standard_normal(widths[i + 1]) * 0.1).astype(dt) for i in range(len(widths) - 1)]
+    onehot = np.zeros((batch, widths[-1]), dt)
+    onehot[np.arange(batch), labels] = 1
+
+    def run():
+        n = len(Ws)
+        lins = [nn.Linear(ct.to_tensor(w, datatype), ct.to_tensor(b, datatype)) for w, b in zip(Ws, bs)]
+        acts = [nn.Activation(act) for _ in range(n - 1)]
+        x = ct.to_tensor(X, datatype)
+        pre, post, cur = [], [], x
+        for i, lin in enumerate(lins):
+            z = ct.new_tensor([batch, widths[i + 1]], datatype)
+            lin.forward(cur, z)
+            pre.append(z)
+            if i < n - 1:
+                a = ct.new_tensor([batch, widths[i + 1]], datatype)
+                acts[i].forward(z, a)
+            else:
+                a = ct.new_tensor([batch, widths[i + 1]], datatype)
+                nn.Softmax().forward(z, a)
+            post.append(a)
+            cur = a
+        # loss gradient with respect to the softmax layer's output buffer, as the reference's softmax-loss gives it
+        grad = ct.new_tensor([batch, widths[-1]], datatype)
+        ct.binary_op(grad, 1.0, post[-1], 1.0, ct.to_tensor(onehot, datatype), "-")
+        outs = []
+        g_in = ct.new_tensor([batch, widths[-1]], datatype)
+        nn.Softmax().backward(g_in, grad)
+        grad = g_in
+        for i in range(n - 1, -1, -1):
+            inp = x if i == 0 else post[i - 1]
+            w_grad = ct.new_tensor([widths[i + 1], widths[i]], datatype)
+            b_grad = ct.new_tensor([widths[i + 1]], datatype)
+            in_grad = ct.new_tensor([batch, widths[i]], datatype)
+            lins[i].backward(inp, pre[i], in_grad, grad, w_grad, b_grad)
+            outs = [ct.to_array(w_grad).ravel(), ct.to_array(b_grad).ravel()] + outs
+            grad = in_grad
+            if i > 0:
+                g2 = ct.new_tensor([batch, widths[i]], datatype)
+                acts[i - 1].backward(post[i - 1], g2, grad)
+                grad = g2
+        return np.concatenate([ct.to_array(grad).ravel()] + outs)
+
+    def reference():
+        h = X.astype(np.float64)
+        hs, zs = [h], []
+        for i, (w, b) in enumerate(zip(Ws, bs)):
+            z = h @ w.astype(np.float64).T + b.astype(np.float64)
+            zs.append(z)
+            if i < len(Ws) - 1:
+                h = {"relu": lambda v: np.maximum(v, 0.0), "tanh": np.tanh,
+                     "logistic": lambda v: 1.0 / (1.0 + np.exp(-v))}[act](z)
+                hs.append(h)
+        e = np.exp(z - z.max(axis=1, keepdims=True))
+        g = e / e.sum(axis=1, keepdims=True) - onehot
+        outs = []
+        for i in range(len(Ws) - 1, -1, -1):
+            outs = [(g.T @ hs[i]).ravel(), g.sum(axis=0)] + outs
+            g = g @ Ws[i].astype(np.float64)
+            if i > 0:
+                a = hs[i]
+                g = g * {"relu": (a > 0).astype(np.float64), "tanh": 1.0 - a * a, "logistic": a * (1.0 - a)}[act]
+        return np.concatenate([g.ravel()] + outs)
+
+    return run, reference
+
+
+def activation_gradient_case(datatype, rows, cols, op, seed=141, pitched=False):
+    """activation-gradient! on dense [rows, cols] operands, or on windows of wider buffers (index-system path)."""
+    dt = NP[datatype]
+    rng = np.random.default_rng(seed + rows)
+    pad = 5 if pitched else 0
+    OUT = rng.standard_normal((rows, cols + pad)).astype(dt)
+    if op == "logistic":
+        OUT = (1.0 / (1.0 + np.exp(-OUT))).astype(dt)
+    elif op == "tanh":
+        OUT = np.tanh(OUT).astype(dt)
+    GRAD = rng.standard_normal((rows, cols + pad)).astype(dt)
+
+    def run():
+        out, grad = ct.to_tensor(OUT, datatype), ct.to_tensor(GRAD, datatype)
+        dest = ct.new_tensor([rows, cols + pad], datatype)
+        if pitched:
+            out, grad, d = (ct.submatrix(t, 0, rows, 2, cols) for t in (out, grad, dest))
+            ct.activation_gradient(d, grad, out, op)
+        else:
+            ct.activation_gradient(dest, grad, out, op)
+        return ct.to_array(dest)
+
+    return run
+
+
 def conv_case(datatype, batch, cin, hw, cout, k=3, pad=1, stride=1, seed=401, bias_scale=0.0):
     """Config 4: NCHW conv + bias + ReLU."""
     dt = NP[datatype]

@@ -124,6 +124,28 @@ def test_mlp_matches_oracle(b200_driver, oracle_driver, datatype, fused):
 
 
 @pytest.mark.parametrize("datatype", ["float", "double"])
+@pytest.mark.parametrize("op", ["relu", "tanh", "logistic"])
+def test_activation_gradient_bit_exact(b200_driver, oracle_driver, datatype, op):
+    """activation-gradient!: float views computed in double and rounded once on both sides -> identical bits;
+    dense operands (16-byte path) and windows of wider buffers (index-system path, frame untouched)."""
+    for rows, cols, pitched in ((257, 1000, False), (512, 4096, False), (33, 10, False), (130, 75, True), (64, 1024, True)):
+        run = pc.activation_gradient_case(datatype, rows, cols, op, pitched=pitched)
+        assert np.array_equal(_on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)), (rows, cols, pitched)
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
+@pytest.mark.parametrize("act", ["relu", "tanh"])
+def test_mlp_backward_matches_oracle(b200_driver, oracle_driver, datatype, act):
+    """Forward + backward of config 1's network (128 x 784 -> 500 -> 10) and of a 3-layer 256-wide one: input
+    gradient and every weight / bias gradient against the oracle's identical call sequence and float64 numpy."""
+    for batch, widths in ((128, [784, 500, 10]), (64, [256, 256, 256, 100])):
+        run, ref = pc.mlp_backward_case(datatype, batch, widths, act=act)
+        gpu, cpu = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
+        assert pc.rel_err(gpu, cpu) <= pc.TOL[datatype]
+        assert pc.rel_err(gpu, ref()) <= pc.TOL[datatype]
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
 def test_conv_matches_oracle(b200_driver, oracle_driver, datatype):
     for args in (dict(batch=2, cin=4, hw=9, cout=5), dict(batch=2, cin=3, hw=8, cout=4, k=2, pad=0, stride=2),
                  dict(batch=4, cin=64, hw=28, cout=64),

@@ -338,6 +338,56 @@ def ternary_op_select(driver, datatype):
         _eq([-1, -1, -1, -1, -1, 6, 6, 6, 6, 6], ct.to_double_array(dest))
 
 
+def activation_gradient(driver, datatype):
+    """verify/tensor.clj:557-574"""
+    with tensor_context(driver, datatype):
+        output = ct.to_tensor(list(range(12)))
+        output_gradient = ct.to_tensor(list(range(-4, 8)))
+        input_gradient = ct.new_tensor([12])
+        ct.activation_gradient(input_gradient, output_gradient, output, "logistic")
+        _eq([-0.0, -0.0, 4.0, 6.0, -0.0, -20.0, -60.0, -126.0, -224.0, -360.0, -540.0, -770.0],
+            ct.to_double_array(input_gradient))
+        ct.activation_gradient(input_gradient, output_gradient, output, "tanh")
+        _eq([-4.0, -0.0, 6.0, 8.0, -0.0, -24.0, -70.0, -144.0, -252.0, -400.0, -594.0, -840.0],
+            ct.to_double_array(input_gradient))
+        ct.activation_gradient(input_gradient, output_gradient, output, "relu")
+        _eq([0.0, -3.0, -2.0, -1.0, 0.0, 1.0, 2.0, 3.0, 4.0, 5.0, 6.0, 7.0], ct.to_double_array(input_gradient))
+
+
+def linear_layer_backward(driver, datatype):
+    """verify/nn/layers.clj:193-235 (linear, linear-batch): forward, then biased-multiply-backward! into
+    zeroed gradient buffers."""
+    from cortex_b200 import nn
+    with tensor_context(driver, datatype):
+        for batch in (1, 10):
+            lin = nn.Linear(ct.to_tensor([[1, 2], [3, 4]]), ct.to_tensor([0, 10]))
+            x = ct.to_tensor([[1, 2]] * batch)
+            out_grad = ct.to_tensor([[1, 2]] * batch)
+            out, in_grad = ct.new_tensor([batch, 2]), ct.new_tensor([batch, 2])
+            w_grad, b_grad = ct.new_tensor([2, 2]), ct.new_tensor([2])
+            lin.forward(x, out)
+            lin.backward(x, out, in_grad, out_grad, w_grad, b_grad)
+            _eq([5, 21] * batch, ct.to_double_array(out))
+            _eq([v * batch for v in (1, 2, 2, 4)], ct.to_double_array(w_grad))
+            _eq([v * batch for v in (1, 2)], ct.to_double_array(b_grad))
+            _eq([7, 10] * batch, ct.to_double_array(in_grad))
+
+
+def relu_layer_backward(driver, datatype):
+    """verify/nn/layers.clj:155-191 (relu-activation, relu-activation-batch)"""
+    from cortex_b200 import nn
+    with tensor_context(driver, datatype):
+        for batch, items in ((1, 10), (5, 10000)):
+            act = nn.Activation("relu")
+            x = ct.to_tensor(np.tile([-1, 1], batch * items // 2).reshape(batch, items))
+            out_grad = ct.to_tensor(np.ones((batch, items)))
+            out, in_grad = ct.new_tensor([batch, items]), ct.new_tensor([batch, items])
+            act.forward(x, out)
+            act.backward(out, in_grad, out_grad)
+            assert float(np.sum(ct.to_double_array(out))) == batch * items / 2
+            assert float(np.sum(ct.to_double_array(in_grad))) == batch * items / 2
+
+
 def unary_reduce(driver, datatype):
     """verify/tensor.clj:648-665"""
     with tensor_context(driver, datatype):
@@ -502,6 +552,7 @@ CASES = [
     (assign_constant, ALL_DTYPES), (assign_marshal, ALL_DTYPES), (unary_op, ALL_DTYPES), (channel_op, ALL_DTYPES),
     (binary_constant_op, ALL_DTYPES), (binary_op, ALL_DTYPES), (gemm, FLOAT_DTYPES), (gemv, FLOAT_DTYPES),
     (ternary_op_select, ALL_DTYPES), (batch_normalize, FLOAT_DTYPES), (pooling_operator, FLOAT_DTYPES),
+    (activation_gradient, FLOAT_DTYPES), (linear_layer_backward, FLOAT_DTYPES), (relu_layer_backward, FLOAT_DTYPES),
     (activation_forward, FLOAT_DTYPES), (softmax, FLOAT_DTYPES), (unary_reduce, ALL_DTYPES), (transpose, ALL_DTYPES),
     (mask, INT_LONG), (select, ALL_DTYPES), (select_transpose_interaction, ALL_DTYPES),
     (convolution_operator, FLOAT_DTYPES), (indexed_tensor, ALL_DTYPES), (magnitude_and_mag_squared, FLOAT_DTYPES),
