@@ -88,6 +88,8 @@ SIGNATURES = {
     "cb200_softmax_spatial": [_vp, _i, _vp, _pd, _vp, _pd],
     "cb200_convolution_workspace_size": [C.POINTER(ConvDesc), _i, _i, _i, _i, _i, C.POINTER(_i64)],
     "cb200_convolution_forward": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
+    "cb200_convolution_backward_weights": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
+    "cb200_convolution_backward_data": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
     "cb200_convolution_forward_static": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, C.POINTER(ConvDesc)],
     "cb200_ternary_op": [_vp, _i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
     "cb200_gemv": [_vp, _i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],

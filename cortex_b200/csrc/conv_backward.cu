@@ -1,0 +1,208 @@
+// convolution-backward-weights! and convolution-backward-data!
+// (src/cortex/tensor.clj:1469-1493 -> tm/convolution-backward-weights! / -data!; CPU semantics
+// src/cortex/compute/cpu/tensor_math.clj:1716-1800 and the roll / unroll kernels of src/cortex/nn/impl.clj).
+//
+//   weights:  W_grad[C_out, K] = alpha * W_grad + sum over images n of  OG_n[C_out, hw] . cols_n[hw, K]
+//             with cols_n the unrolled (im2col) input of image n, K = C_in*kH*kW
+//   data:     colsgrad_n[hw, K] = OG_n^T[hw, C_out] . W[C_out, K], rolled back (col2im) into
+//             I_grad[n, C_in, H, W] = alpha * I_grad + sum of the colsgrad entries that came from that pixel
+//
+// The reference CPU backend reuses the unrolled input its forward pass left in the caller's workspace; here the
+// unrolled matrix is rebuilt in the stream's own workspace (the forward pass keeps none: it gathers straight
+// into the tensor-core tiles).  GEMMs go through the same dispatch as gemm! (tcgen05 3xTF32 / DMMA / SIMT),
+// one per image, chained through beta = 1 for the weight gradient.  col2im is a gather: one thread per input
+// pixel sums the (at most kH*kW) unrolled entries that read it, so there are no atomics and the sum order is
+// fixed.  The CPU backend ignores input-gradient-alpha (it always clears the gradient); this backend applies it,
+// as the reference's CUDA backend does -- the two agree for alpha = 0, which is what the layers pass.
+#include "common.cuh"
+
+int cb200_gemm_no_workspace(cb200_stream* s, int dtype, void* C, long long ldc, int trans_a, int trans_b, double alpha,
+                            const void* A, long long a_rows, long long a_cols, long long lda, const void* B,
+                            long long b_cols, long long ldb, double beta);
+
+namespace {
+
+struct BwdGeom {
+  int batch, cin, in_h, in_w, out_h, out_w, kh, kw, pad_x, pad_y, stride_x, stride_y;
+  int kcols;   // cin*kh*kw
+  int ld;      // row pitch of the unrolled matrix (kcols rounded up to 4)
+};
+
+// cols[(n*hw + p) * ld + c*kh*kw + ky*kw + kx] = in[n, c, oy*sy - py + ky, ox*sx - px + kx] (0 in the padding)
+template <typename T>
+__global__ void __launch_bounds__(256) unroll_kernel(T* cols, const T* in, BwdGeom g, long long total) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const unsigned row = (unsigned)(i / (unsigned)g.ld);
+    const int col = (int)(i - (long long)row * g.ld);
+    T v = (T)0;
+    if (col < g.kcols) {
+      const int kx = col % g.kw, ky = (col / g.kw) % g.kh, c = col / (g.kw * g.kh);
+      const unsigned hw = (unsigned)(g.out_h * g.out_w);
+      const int n = (int)(row / hw), p = (int)(row % hw);
+      const int oy = p / g.out_w, ox = p % g.out_w;
+      const int iy = oy * g.stride_y - g.pad_y + ky, ix = ox * g.stride_x - g.pad_x + kx;
+      if (iy >= 0 && iy < g.in_h && ix >= 0 && ix < g.in_w)
+        v = in[(((long long)n * g.cin + c) * g.in_h + iy) * g.in_w + ix];
+    }
+    cols[i] = v;
+  }
+}
+
+// in_grad[n, c, iy, ix] = alpha * in_grad + sum over taps (ky, kx) with (iy + py - ky) % sy == 0 etc. of
+// colsgrad[(n*hw + oy*out_w + ox) * ld + c*kh*kw + ky*kw + kx]
+template <typename T>
+__global__ void __launch_bounds__(256) roll_kernel(T* in_grad, const T* colsgrad, BwdGeom g, T alpha, long long total) {
+  typedef typename acc_of<T>::type A;
+  const int hw = g.out_h * g.out_w;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int ix = (int)(i % g.in_w);
+    long long r = i / g.in_w;
+    const int iy = (int)(r % g.in_h);
+    r /= g.in_h;
+    const int c = (int)(r % g.cin), n = (int)(r / g.cin);
+    A acc = (A)0;
+    for (int ky = 0; ky < g.kh; ++ky) {
+      const int ty = iy + g.pad_y - ky;
+      if (ty < 0 || ty % g.stride_y) continue;
+      const int oy = ty / g.stride_y;
+      if (oy >= g.out_h) continue;
+      for (int kx = 0; kx < g.kw; ++kx) {
+        const int tx = ix + g.pad_x - kx;
+        if (tx < 0 || tx % g.stride_x) continue;
+        const int ox = tx / g.stride_x;
+        if (ox >= g.out_w) continue;
+        acc += (A)colsgrad[((long long)n * hw + oy * g.out_w + ox) * g.ld + (c * g.kh + ky) * g.kw + kx];
+      }
+    }
+    in_grad[i] = alpha == (T)0 ? (T)acc : (T)((A)alpha * (A)in_grad[i] + acc);
+  }
+}
+
+bool dense4(const cb200_dims* d) {
+  long long e = 1;
+  for (int i = 0; i < 4; ++i) {
+    if (d->index[i]) return false;
+    if (d->rev_shape[i] > 1 && d->rev_strides[i] != e) return false;
+    e *= d->rev_shape[i];
+  }
+  return d->rev_shape[4] == 1;
+}
+
+// shared validation: fills the geometry from the input-side and output-side NCHW descriptors
+int make_geom(BwdGeom& g, int& cout, const cb200_dims* in_dims, const cb200_dims* og_dims, const cb200_dims* w_dims,
+              const cb200_conv_desc* desc, const char* who) {
+  CB_REQUIRE(dense4(in_dims) && dense4(og_dims), "%s: Convolution arguments must be dense 4-d tensors", who);
+  g.batch = in_dims->rev_shape[3]; g.cin = in_dims->rev_shape[2]; g.in_h = in_dims->rev_shape[1]; g.in_w = in_dims->rev_shape[0];
+  g.out_h = og_dims->rev_shape[1]; g.out_w = og_dims->rev_shape[0];
+  cout = og_dims->rev_shape[2];
+  g.kh = desc->kernel_height; g.kw = desc->kernel_width;
+  g.pad_x = desc->pad_x; g.pad_y = desc->pad_y; g.stride_x = desc->stride_x; g.stride_y = desc->stride_y;
+  CB_REQUIRE(g.cin == desc->in_channels && cout == desc->out_channels && og_dims->rev_shape[3] == g.batch,
+             "%s: tensor shapes do not match the descriptor", who);
+  CB_REQUIRE(g.kh >= 1 && g.kw >= 1 && g.stride_x >= 1 && g.stride_y >= 1 && g.pad_x >= 0 && g.pad_y >= 0,
+             "%s: bad descriptor", who);
+  CB_REQUIRE(g.out_w == (g.in_w + 2 * g.pad_x - g.kw) / g.stride_x + 1 &&
+             g.out_h == (g.in_h + 2 * g.pad_y - g.kh) / g.stride_y + 1,
+             "%s: output extent does not match floor((in + 2*pad - k)/stride) + 1", who);
+  g.kcols = g.cin * g.kh * g.kw;
+  g.ld = (g.kcols + 3) & ~3;
+  long long wec = 1;
+  for (int i = 0; i < 5; ++i) wec *= w_dims->rev_shape[i];
+  CB_REQUIRE(wec == (long long)cout * g.kcols, "%s: weight element count does not equal out-channels * kernel * in-channels", who);
+  CB_REQUIRE((long long)g.batch * g.out_h * g.out_w <= 2147483647LL, "%s: more than 2^31-1 output pixels", who);
+  return CB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cb200_convolution_backward_weights(cb200_stream* s, int dtype, void* w_grad, const cb200_dims* w_grad_dims,
+                                       double w_grad_alpha, const void* out_grad, const cb200_dims* out_grad_dims,
+                                       const void* in, const cb200_dims* in_dims, void* workspace,
+                                       int64_t workspace_ecount, const cb200_conv_desc* desc) {
+  (void)workspace; (void)workspace_ecount;
+  CB_REQUIRE(s && w_grad && w_grad_dims && out_grad && out_grad_dims && in && in_dims && desc,
+             "convolution_backward_weights: null argument");
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE,
+             "convolution-backward-weights! is only defined for float and double tensors");
+  BwdGeom g;
+  int cout = 0;
+  int rc = make_geom(g, cout, in_dims, out_grad_dims, w_grad_dims, desc, "convolution_backward_weights");
+  if (rc) return rc;
+  const int hw = g.out_h * g.out_w;
+  const long long rows = (long long)g.batch * hw;
+  if (cout == 0 || g.kcols == 0) return CB200_OK;
+  const size_t es = dtype == CB200_FLOAT ? 4 : 8;
+  if (rows == 0) {
+    // nothing to add: W_grad = alpha * W_grad is the caller's binary-op!; with no images leave it untouched
+    return CB200_OK;
+  }
+  const long long total = rows * g.ld;
+  void* cols = nullptr;
+  if ((rc = cb200_scratch(s, (size_t)total * es, &cols))) return rc;
+  DeviceGuard guard(s->device);
+  long long blocks = (total + 255) / 256, cap = (long long)s->sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  if (dtype == CB200_FLOAT)
+    unroll_kernel<float><<<(unsigned)blocks, 256, 0, s->stream>>>((float*)cols, (const float*)in, g, total);
+  else
+    unroll_kernel<double><<<(unsigned)blocks, 256, 0, s->stream>>>((double*)cols, (const double*)in, g, total);
+  CB_LAUNCH_CHECK(s);
+  for (int n = 0; n < g.batch; ++n) {
+    const char* og_n = (const char*)out_grad + (size_t)n * cout * hw * es;
+    const char* cols_n = (const char*)cols + (size_t)n * hw * g.ld * es;
+    rc = cb200_gemm_no_workspace(s, dtype, w_grad, g.kcols, 0, 0, 1.0, og_n, cout, hw, hw, cols_n, g.kcols, g.ld,
+                                 n == 0 ? w_grad_alpha : 1.0);
+    if (rc) return rc;
+  }
+  return CB200_OK;
+}
+
+int cb200_convolution_backward_data(cb200_stream* s, int dtype, void* in_grad, const cb200_dims* in_grad_dims,
+                                    double in_grad_alpha, const void* out_grad, const cb200_dims* out_grad_dims,
+                                    const void* w, const cb200_dims* w_dims, void* workspace, int64_t workspace_ecount,
+                                    const cb200_conv_desc* desc) {
+  (void)workspace; (void)workspace_ecount;
+  CB_REQUIRE(s && in_grad && in_grad_dims && out_grad && out_grad_dims && w && w_dims && desc,
+             "convolution_backward_data: null argument");
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE,
+             "convolution-backward-data! is only defined for float and double tensors");
+  BwdGeom g;
+  int cout = 0;
+  int rc = make_geom(g, cout, in_grad_dims, out_grad_dims, w_dims, desc, "convolution_backward_data");
+  if (rc) return rc;
+  const int hw = g.out_h * g.out_w;
+  const long long rows = (long long)g.batch * hw;
+  const long long in_total = (long long)g.batch * g.cin * g.in_h * g.in_w;
+  if (in_total == 0) return CB200_OK;
+  const size_t es = dtype == CB200_FLOAT ? 4 : 8;
+  DeviceGuard guard(s->device);
+  void* colsgrad = nullptr;
+  if (rows > 0 && cout > 0) {
+    if ((rc = cb200_scratch(s, (size_t)rows * g.ld * es, &colsgrad))) return rc;
+    for (int n = 0; n < g.batch; ++n) {
+      const char* og_n = (const char*)out_grad + (size_t)n * cout * hw * es;
+      char* cg_n = (char*)colsgrad + (size_t)n * hw * g.ld * es;
+      // colsgrad_n[hw, K] = OG_n^T . W : op(A) = OG_n^T is hw x cout, stored [cout, hw]
+      rc = cb200_gemm_no_workspace(s, dtype, cg_n, g.ld, 1, 0, 1.0, og_n, hw, cout, hw, w, g.kcols, g.kcols, 0.0);
+      if (rc) return rc;
+    }
+  } else {
+    // no output pixels: the sum is empty; a one-element dummy keeps the kernel's pointer valid
+    if ((rc = cb200_scratch(s, 16, &colsgrad))) return rc;
+    g.out_h = 0; g.out_w = 0;
+  }
+  long long blocks = (in_total + 255) / 256, cap = (long long)s->sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  if (dtype == CB200_FLOAT)
+    roll_kernel<float><<<(unsigned)blocks, 256, 0, s->stream>>>((float*)in_grad, (const float*)colsgrad, g,
+                                                                (float)in_grad_alpha, in_total);
+  else
+    roll_kernel<double><<<(unsigned)blocks, 256, 0, s->stream>>>((double*)in_grad, (const double*)colsgrad, g,
+                                                                 in_grad_alpha, in_total);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+}  // extern "C"

@@ -121,7 +121,8 @@ int tc_f32(cb200_stream* s, float* C, long long ldc, int ta, int tb, float alpha
 
 int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int trans_b, double alpha, const void* A,
               int64_t a_rows, int64_t a_cols, int64_t lda, const void* B, int64_t b_cols, int64_t ldb, double beta,
-              const void* bias, int act, const PeerList* peers = nullptr, bool layer_stack = false) {
+              const void* bias, int act, const PeerList* peers = nullptr, bool layer_stack = false,
+              bool allow_workspace = true) {
   CB_REQUIRE(s && C && A && B, "gemm: null argument");
   CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "gemm! is only defined for float and double tensors");
   CB_REQUIRE(a_rows >= 0 && a_cols >= 0 && b_cols >= 0, "gemm: negative extent");
@@ -139,7 +140,7 @@ int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int
       // problems that fill the GPU with 256 x 256 tiles: split (and, for MN-major operands, transpose) the
       // operands into the stream's workspace once, then the CTA-pair kernel, whose main loop has no
       // shared-memory pass; its in-kernel accumulator read-outs replace the K chunking below
-      if ((!peers || peers->n == 0) && cb200_gemm_presplit_auto_ok(s, M, N, K, trans_a, trans_b))
+      if (allow_workspace && (!peers || peers->n == 0) && cb200_gemm_presplit_auto_ok(s, M, N, K, trans_a, trans_b))
         return cb200_gemm_presplit_auto_launch(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb,
                                                (float)beta, (const float*)bias, act);
       // tcgen05 accumulates with truncation, so the result drifts toward zero by about 7e-9 * K
@@ -177,6 +178,15 @@ int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int
 }
 
 }  // namespace
+
+// gemm! for callers that keep their own data in the stream's workspace (the convolution backward passes):
+// same dispatch, but never the path that splits the operands into that workspace
+int cb200_gemm_no_workspace(cb200_stream* s, int dtype, void* C, long long ldc, int trans_a, int trans_b, double alpha,
+                            const void* A, long long a_rows, long long a_cols, long long lda, const void* B,
+                            long long b_cols, long long ldb, double beta) {
+  return gemm_impl(s, dtype, C, ldc, trans_a, trans_b, alpha, A, a_rows, a_cols, lda, B, b_cols, ldb, beta, nullptr,
+                   CB200_ACT_NONE, nullptr, false, false);
+}
 
 // used by conv.cu when the weight pitch is not addressable by TMA
 int cb200_gemm_simt_f32_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,

@@ -12,6 +12,7 @@ Mirrors the reference's compute layers:
 Backward passes of the dense layers (the next ring around the inference path):
   biased_multiply_backward   nn-backend/biased-multiply-backward!   compute/nn/backend.clj:115-139
   Linear.backward / Activation.backward / Softmax.backward          compute/nn/layers.clj:78-88, 104-116, 164-168
+  Convolution.backward                                              compute/nn/layers.clj:320-340
 
 ``fused=True`` replaces the reference's three calls per dense layer
 (assign! bias, gemm! NT beta=1, binary-op! max 0) with the backend's single
@@ -149,6 +150,18 @@ class Convolution:
         ct.convolution_forward(output, 0.0, input, self.weights, self.workspace, self.desc, self.algorithms)
         ct.binary_op(output, 1.0, output, 1.0, bias, "+")
         return output
+
+    def backward(self, input, input_gradient, output_gradient, weight_gradient, bias_gradient):
+        """ConvolutionLayer.backward (compute/nn/layers.clj:320-340): the bias gradient accumulates over batch and
+        pixels (destination [C_out 1 1] smaller than the operation), weight and input gradients are overwritten."""
+        bias_gradient = ct.in_place_reshape(bias_gradient, [self.desc["out-channels"], 1, 1])
+        ct.binary_op(bias_gradient, 1.0, output_gradient, 1.0, bias_gradient, "+")
+        ct.convolution_backward_weights(weight_gradient, 0.0, output_gradient, input, self.workspace, self.desc,
+                                        self.algorithms)
+        if input_gradient is not None:
+            ct.convolution_backward_data(input_gradient, 0.0, output_gradient, self.weights, self.workspace, self.desc,
+                                         self.algorithms)
+        return input_gradient
 
 
 class _Replayable:

@@ -723,3 +723,28 @@ def convolution_forward(output, output_alpha, input, weights, workspace, conv_de
                                        workspace.buffer if workspace is not None else None,
                                        workspace.ecount() if workspace is not None else 0, conv_descriptor, algorithms)
     return output
+
+
+def convolution_backward_weights(weight_gradient, weight_gradient_alpha, output_gradient, input, workspace,
+                                 conv_descriptor, algorithms):
+    """tensor.clj:1469-1479."""
+    _external_library_check("convolution-backward-weights!", weight_gradient, output_gradient, input)
+    check_stream().convolution_backward_weights(
+        weight_gradient.buffer, weight_gradient.dimensions, weight_gradient_alpha, output_gradient.buffer,
+        output_gradient.dimensions, input.buffer, input.dimensions,
+        workspace.buffer if workspace is not None else None, workspace.ecount() if workspace is not None else 0,
+        conv_descriptor, algorithms)
+    return weight_gradient
+
+
+def convolution_backward_data(input_gradient, input_gradient_alpha, output_gradient, weights, workspace,
+                              conv_descriptor, algorithms):
+    """tensor.clj:1482-1493."""
+    _external_library_check("convolution-backward-data!", input_gradient, output_gradient, weights)
+    _ensure_conv_io(conv_descriptor, input_gradient, output_gradient)
+    check_stream().convolution_backward_data(
+        input_gradient.buffer, input_gradient.dimensions, input_gradient_alpha, output_gradient.buffer,
+        output_gradient.dimensions, weights.buffer, weights.dimensions,
+        workspace.buffer if workspace is not None else None, workspace.ecount() if workspace is not None else 0,
+        conv_descriptor, algorithms)
+    return input_gradient

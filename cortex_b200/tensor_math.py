@@ -108,6 +108,24 @@ class CTensorMath:
                  workspace.ptr if workspace is not None else None, int(workspace_ecount),
                  C.byref(conv_desc_struct(conv_descriptor)))
 
+    def convolution_backward_weights(self, weight_gradient, weight_gradient_dims, weight_gradient_alpha,
+                                     output_gradient, output_gradient_dims, input, input_dims, workspace,
+                                     workspace_ecount, conv_descriptor, algorithms):
+        self._tm("convolution_backward_weights", DTYPE_CODE[weight_gradient.dtype], weight_gradient.ptr,
+                 C.byref(wire(weight_gradient_dims)), float(weight_gradient_alpha), output_gradient.ptr,
+                 C.byref(wire(output_gradient_dims)), input.ptr, C.byref(wire(input_dims)),
+                 workspace.ptr if workspace is not None else None, int(workspace_ecount),
+                 C.byref(conv_desc_struct(conv_descriptor)))
+
+    def convolution_backward_data(self, input_gradient, input_gradient_dims, input_gradient_alpha, output_gradient,
+                                  output_gradient_dims, weights, weight_dims, workspace, workspace_ecount,
+                                  conv_descriptor, algorithms):
+        self._tm("convolution_backward_data", DTYPE_CODE[input_gradient.dtype], input_gradient.ptr,
+                 C.byref(wire(input_gradient_dims)), float(input_gradient_alpha), output_gradient.ptr,
+                 C.byref(wire(output_gradient_dims)), weights.ptr, C.byref(wire(weight_dims)),
+                 workspace.ptr if workspace is not None else None, int(workspace_ecount),
+                 C.byref(conv_desc_struct(conv_descriptor)))
+
     # --- fused extras (no protocol counterpart) ----------------------------------
     def gemm_bias_act(self, c, c_colstride, trans_a, trans_b, alpha, a, a_row_count, a_col_count, a_colstride, b,
                       b_col_count, b_colstride, beta, bias, act):

@@ -197,6 +197,21 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
                               void* workspace, int64_t workspace_ecount,
                               const cb200_conv_desc* desc);
 
+/* convolution-backward-weights! / convolution-backward-data! (src/cortex/tensor.clj:1469-1493;
+ * src/cortex/tensor/math.clj; CPU semantics src/cortex/compute/cpu/tensor_math.clj:1716-1800):
+ *   w_grad[C_out, C_in*kH*kW] = w_grad_alpha * w_grad + sum_n out_grad_n[C_out, hw] . unrolled(in_n)[hw, K]
+ *   in_grad[N, C_in, H, W]    = in_grad_alpha * in_grad + roll(out_grad_n^T . w)
+ * (the CPU backend treats in_grad_alpha as 0 whatever is passed; the layers pass 0).  All tensors dense NCHW /
+ * [C_out, K]; float / double; the caller's workspace is not used (the unrolled matrix lives in the stream's own). */
+int cb200_convolution_backward_weights(cb200_stream* s, int dtype, void* w_grad, const cb200_dims* w_grad_dims,
+                                       double w_grad_alpha, const void* out_grad, const cb200_dims* out_grad_dims,
+                                       const void* in, const cb200_dims* in_dims,
+                                       void* workspace, int64_t workspace_ecount, const cb200_conv_desc* desc);
+int cb200_convolution_backward_data(cb200_stream* s, int dtype, void* in_grad, const cb200_dims* in_grad_dims,
+                                    double in_grad_alpha, const void* out_grad, const cb200_dims* out_grad_dims,
+                                    const void* w, const cb200_dims* w_dims,
+                                    void* workspace, int64_t workspace_ecount, const cb200_conv_desc* desc);
+
 /* convolution-forward! without any allocation.  No counterpart in the reference: cortex's backends
  * take a caller-provided workspace tensor instead.  For hosts that cannot call cudaMalloc on this
  * path (all device memory owned by their own pool, or no tolerance for the device-wide

@@ -50,6 +50,8 @@ _SIGS = {
     "orc_softmax_eltwise": [_i, _vp, _pd, _vp, _pd],
     "orc_softmax_spatial": [_i, _vp, _pd, _vp, _pd],
     "orc_convolution_forward": [_i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
+    "orc_convolution_backward_weights": [_i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
+    "orc_convolution_backward_data": [_i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
     "orc_bias_relu_rowstats": [_i, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp],
 }
 
@@ -62,8 +64,11 @@ def build():
 def load():
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            build()
+        try:
+            build()          # make: rebuilds only when oracle.c is newer than the library
+        except Exception:
+            if not os.path.exists(LIB_PATH):
+                raise
         lib = C.CDLL(LIB_PATH)
         for name, argtypes in _SIGS.items():
             fn = getattr(lib, name)

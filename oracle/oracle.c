@@ -576,6 +576,67 @@ int orc_convolution_forward(int dtype, void* out, const orc_dims* od, double out
   return rc;
 }
 
+/* ---- convolution backward (cpu/tensor_math.clj:1716-1800) ---------------------------------------
+ * weights: per image, in batch order, gemm!(W_grad, false, false, 1.0, OG_n[C_out, hw], cols_n[hw, K],
+ *          n == 0 ? alpha : 1.0) with cols_n the unrolled input (the CPU backend finds it in the workspace the
+ *          forward pass filled; it is rebuilt here).
+ * data:    input-gradient := 0 (the CPU backend overrides its alpha with 0.0, :1763), then per image
+ *          colsgrad = OG_n^T . W and convolution->planar-output! (:1134-1152): every valid unrolled entry is
+ *          added onto the input pixel it was read from, in the unroll loop order of nn/impl.clj. */
+#define CONV_BW_W_BODY(T) { T* wg = (T*)w_grad; const T* og = (const T*)out_grad + (size_t)n * cout * hw; const T* cl = (const T*)cols; \
+  T be = (T)(n == 0 ? alpha : 1.0); \
+  for (int64_t co = 0; co < cout; ++co) for (int64_t k = 0; k < kcols; ++k) { T acc = (T)0; \
+    for (int64_t p_ = 0; p_ < hw; ++p_) acc += og[co * hw + p_] * cl[p_ * kcols + k]; \
+    wg[co * kcols + k] = (be == (T)0) ? acc : acc + be * wg[co * kcols + k]; } }
+int orc_convolution_backward_weights(int dtype, void* w_grad, const orc_dims* wgd, double alpha, const void* out_grad,
+                                     const orc_dims* ogd, const void* in, const orc_dims* id, void* workspace,
+                                     int64_t workspace_ecount, const orc_conv_desc* d) {
+  (void)wgd; (void)workspace; (void)workspace_ecount;
+  int batch = id->rev_shape[3], cin = id->rev_shape[2], in_h = id->rev_shape[1], in_w = id->rev_shape[0];
+  int cout = ogd->rev_shape[2], out_h = ogd->rev_shape[1], out_w = ogd->rev_shape[0];
+  int kh = d->kernel_height, kw = d->kernel_width;
+  int64_t kcols = (int64_t)cin * kh * kw, hw = (int64_t)out_h * out_w;
+  size_t es = dtype == T_FLOAT ? 4 : 8;
+  if (dtype != T_FLOAT && dtype != T_DOUBLE) return 1;
+  void* cols = malloc((size_t)(hw * kcols > 0 ? hw * kcols : 1) * es);
+  for (int n = 0; n < batch; ++n) {
+    const char* in_img = (const char*)in + (size_t)n * cin * in_h * in_w * es;
+    if (dtype == T_FLOAT) { IM2COL_BODY(float) CONV_BW_W_BODY(float) } else { IM2COL_BODY(double) CONV_BW_W_BODY(double) }
+  }
+  free(cols);
+  return 0;
+}
+
+#define CONV_BW_D_BODY(T) { T* ig = (T*)in_grad + (size_t)n * cin * in_h * in_w; const T* og = (const T*)out_grad + (size_t)n * cout * hw; \
+  const T* W = (const T*)w; T* cg = (T*)colsgrad; \
+  for (int64_t p_ = 0; p_ < hw; ++p_) for (int64_t k = 0; k < kcols; ++k) { T acc = (T)0; \
+    for (int64_t co = 0; co < cout; ++co) acc += og[co * hw + p_] * W[co * kcols + k]; cg[p_ * kcols + k] = acc; } \
+  for (int c = 0; c < cin; ++c) for (int oy = 0; oy < out_h; ++oy) for (int ox = 0; ox < out_w; ++ox) { \
+    int rel_y = oy * d->stride_y - d->pad_y, rel_x = ox * d->stride_x - d->pad_x; \
+    for (int ky = 0; ky < kh; ++ky) for (int kx = 0; kx < kw; ++kx) { int iy = rel_y + ky, ix = rel_x + kx; \
+      if (ix >= 0 && ix < in_w && iy >= 0 && iy < in_h) { \
+        T* dst = ig + ((int64_t)c * in_h + iy) * in_w + ix; \
+        *dst = (T)((double)cg[(int64_t)(oy * out_w + ox) * kcols + c * kh * kw + ky * kw + kx] + (double)*dst); } } } }
+int orc_convolution_backward_data(int dtype, void* in_grad, const orc_dims* igd, double alpha, const void* out_grad,
+                                  const orc_dims* ogd, const void* w, const orc_dims* wd, void* workspace,
+                                  int64_t workspace_ecount, const orc_conv_desc* d) {
+  (void)wd; (void)workspace; (void)workspace_ecount; (void)alpha;   /* the CPU backend forces alpha = 0 */
+  int batch = igd->rev_shape[3], cin = igd->rev_shape[2], in_h = igd->rev_shape[1], in_w = igd->rev_shape[0];
+  int cout = ogd->rev_shape[2], out_h = ogd->rev_shape[1], out_w = ogd->rev_shape[0];
+  int kh = d->kernel_height, kw = d->kernel_width;
+  int64_t kcols = (int64_t)cin * kh * kw, hw = (int64_t)out_h * out_w;
+  size_t es = dtype == T_FLOAT ? 4 : 8;
+  if (dtype != T_FLOAT && dtype != T_DOUBLE) return 1;
+  memset(in_grad, 0, (size_t)batch * cin * in_h * in_w * es);
+#pragma omp parallel for
+  for (int n = 0; n < batch; ++n) {
+    void* colsgrad = malloc((size_t)(hw * kcols > 0 ? hw * kcols : 1) * es);
+    if (dtype == T_FLOAT) CONV_BW_D_BODY(float) else CONV_BW_D_BODY(double)
+    free(colsgrad);
+  }
+  return 0;
+}
+
 /* ---- fused extras, as the unfused reference sequence ------------------------------------------------ */
 int orc_bias_relu_rowstats(int dtype, void* Y, int64_t ldy, const void* X, int64_t ldx, const void* bias, int64_t rows,
                            int64_t cols, void* rowmax, void* rowsum) {

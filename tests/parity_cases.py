@@ -248,6 +248,48 @@ def activation_gradient_case(datatype, rows, cols, op, seed=141, pitched=False):
     return run
 
 
+def conv_backward_case(datatype, batch, cin, hw, cout, k=3, pad=1, stride=1, seed=451):
+    """ConvolutionLayer forward + backward: returns [input-gradient, weight-gradient, bias-gradient]."""
+    dt = NP[datatype]
+    rng = np.random.default_rng(seed)
+    X = rng.standard_normal((batch, cin, hw, hw)).astype(dt)
+    W = (rng.standard_normal((cout, cin * k * k)) * np.sqrt(2.0 / (cin * k * k))).astype(dt)
+    b = (rng.standard_normal(cout) * 0.1).astype(dt)
+    out_hw = (hw + 2 * pad - k) // stride + 1
+    OG = rng.standard_normal((batch, cout, out_hw, out_hw)).astype(dt)
+
+    def run():
+        layer = nn.Convolution(ct.to_tensor(W, datatype), ct.to_tensor(b, datatype), (k, k), (pad, pad),
+                               (stride, stride), cin, cout, datatype)
+        x = ct.to_tensor(X, datatype)
+        out = ct.new_tensor([batch, cout, out_hw, out_hw], datatype)
+        layer.forward(x, out)
+        in_grad = ct.new_tensor([batch, cin, hw, hw], datatype)
+        w_grad, b_grad = ct.new_tensor([cout, cin * k * k], datatype), ct.new_tensor([cout], datatype)
+        ct.assign(in_grad, 3)       # must be overwritten (alpha = 0)
+        ct.assign(w_grad, 3)
+        layer.backward(x, in_grad, ct.to_tensor(OG, datatype), w_grad, b_grad)
+        return np.concatenate([ct.to_array(t).ravel() for t in (in_grad, w_grad, b_grad)])
+
+    def reference():
+        Xp = np.zeros((batch, cin, hw + 2 * pad, hw + 2 * pad), np.float64)
+        Xp[:, :, pad:pad + hw, pad:pad + hw] = X
+        W4 = W.astype(np.float64).reshape(cout, cin, k, k)
+        og = OG.astype(np.float64)
+        gw = np.zeros_like(W4)
+        gx = np.zeros_like(Xp)
+        for ky in range(k):
+            for kx in range(k):
+                patch = Xp[:, :, ky:ky + stride * out_hw:stride, kx:kx + stride * out_hw:stride]   # [B, cin, oh, ow]
+                gw[:, :, ky, kx] = np.einsum("bohw,bchw->oc", og, patch)
+                gx[:, :, ky:ky + stride * out_hw:stride, kx:kx + stride * out_hw:stride] += np.einsum(
+                    "bohw,oc->bchw", og, W4[:, :, ky, kx])
+        gx = gx[:, :, pad:pad + hw, pad:pad + hw]
+        return np.concatenate([gx.ravel(), gw.ravel(), og.sum(axis=(0, 2, 3))])
+
+    return run, reference
+
+
 def conv_case(datatype, batch, cin, hw, cout, k=3, pad=1, stride=1, seed=401, bias_scale=0.0):
     """Config 4: NCHW conv + bias + ReLU."""
     dt = NP[datatype]

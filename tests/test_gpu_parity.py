@@ -146,6 +146,19 @@ def test_mlp_backward_matches_oracle(b200_driver, oracle_driver, datatype, act):
 
 
 @pytest.mark.parametrize("datatype", ["float", "double"])
+def test_conv_backward_matches_oracle(b200_driver, oracle_driver, datatype):
+    """ConvolutionLayer backward (bias gradient by compare-and-swap accumulation, weight gradient, input gradient)
+    against the oracle's restatement of the CPU backend and a float64 numpy convolution transpose."""
+    for args in (dict(batch=2, cin=4, hw=9, cout=5), dict(batch=2, cin=3, hw=8, cout=4, k=2, pad=0, stride=2),
+                 dict(batch=3, cin=16, hw=13, cout=40, k=5, pad=2), dict(batch=2, cin=32, hw=17, cout=36, k=3, pad=1, stride=2),
+                 dict(batch=4, cin=64, hw=28, cout=64)):
+        run, ref = pc.conv_backward_case(datatype, **args)
+        gpu, cpu = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
+        assert pc.rel_err(gpu, cpu) <= pc.TOL[datatype], args
+        assert pc.rel_err(gpu, ref()) <= pc.TOL[datatype], args
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
 def test_conv_matches_oracle(b200_driver, oracle_driver, datatype):
     for args in (dict(batch=2, cin=4, hw=9, cout=5), dict(batch=2, cin=3, hw=8, cout=4, k=2, pad=0, stride=2),
                  dict(batch=4, cin=64, hw=28, cout=64),

@@ -489,8 +489,27 @@ CONV_EXPECTED = [25062.0, 25692.0, 27582.0, 28212.0, 62646.0, 64572.0, 70350.0, 
                  318804.0, 512646.0, 515868.0, 525534.0, 528756.0]
 
 
+CONV_WEIGHT_GRADIENT = [798, 810, 822, 846, 858, 870, 894, 906, 918, 990, 1002, 1014, 1038, 1050, 1062, 1086,
+        1098, 1110, 1182, 1194, 1206, 1230, 1242, 1254, 1278, 1290, 1302, 1374, 1386, 1398, 1422, 1434, 1446, 1470,
+        1482, 1494, 798, 810, 822, 846, 858, 870, 894, 906, 918, 990, 1002, 1014, 1038, 1050, 1062, 1086, 1098,
+        1110, 1182, 1194, 1206, 1230, 1242, 1254, 1278, 1290, 1302, 1374, 1386, 1398, 1422, 1434, 1446, 1470, 1482,
+        1494, 798, 810, 822, 846, 858, 870, 894, 906, 918, 990, 1002, 1014, 1038, 1050, 1062, 1086, 1098, 1110,
+        1182, 1194, 1206, 1230, 1242, 1254, 1278, 1290, 1302, 1374, 1386, 1398, 1422, 1434, 1446, 1470, 1482, 1494]
+
+CONV_INPUT_GRADIENT = [108, 219, 225, 114, 225, 456, 468, 237, 243, 492, 504, 255, 126, 255, 261, 132, 135,
+        273, 279, 141, 279, 564, 576, 291, 297, 600, 612, 309, 153, 309, 315, 159, 162, 327, 333, 168, 333, 672,
+        684, 345, 351, 708, 720, 363, 180, 363, 369, 186, 189, 381, 387, 195, 387, 780, 792, 399, 405, 816, 828,
+        417, 207, 417, 423, 213, 108, 219, 225, 114, 225, 456, 468, 237, 243, 492, 504, 255, 126, 255, 261, 132,
+        135, 273, 279, 141, 279, 564, 576, 291, 297, 600, 612, 309, 153, 309, 315, 159, 162, 327, 333, 168, 333,
+        672, 684, 345, 351, 708, 720, 363, 180, 363, 369, 186, 189, 381, 387, 195, 387, 780, 792, 399, 405, 816,
+        828, 417, 207, 417, 423, 213, 108, 219, 225, 114, 225, 456, 468, 237, 243, 492, 504, 255, 126, 255, 261,
+        132, 135, 273, 279, 141, 279, 564, 576, 291, 297, 600, 612, 309, 153, 309, 315, 159, 162, 327, 333, 168,
+        333, 672, 684, 345, 351, 708, 720, 363, 180, 363, 369, 186, 189, 381, 387, 195, 387, 780, 792, 399, 405,
+        816, 828, 417, 207, 417, 423, 213]
+
+
 def convolution_operator(driver, datatype):
-    """verify/tensor.clj:808-849 (forward part)"""
+    """verify/tensor.clj:808-890 (forward, backward-weights, backward-data)"""
     with tensor_context(driver, datatype):
         batch, cin, cout, dim = 3, 4, 3, 4
         inp = ct.to_tensor(np.arange(dim * dim * batch * cin).reshape(batch, cin, dim, dim))
@@ -504,6 +523,15 @@ def convolution_operator(driver, datatype):
         ct.convolution_forward(out, 0.0, inp, weights, workspace, desc, algorithms)
         tol = 0.0 if datatype == "double" else 0.5   # exact in fp64; fp32 results reach 5e5 (ulp 0.03)
         _eq(CONV_EXPECTED, ct.to_double_array(out), tol)
+        out_grad = ct.in_place_reshape(ct.to_tensor([1] * (batch * cout * od["output-height"] * od["output-width"])),
+                                       [batch, cout, od["output-height"], od["output-width"]])
+        weight_gradient, input_gradient = ct.new_tensor(weights.shape()), ct.new_tensor(inp.shape())
+        ct.assign(weight_gradient, 1)   # pre-existing contents must not leak through alpha = 0
+        ct.assign(input_gradient, 1)
+        ct.convolution_backward_weights(weight_gradient, 0.0, out_grad, inp, workspace, desc, algorithms)
+        _eq(CONV_WEIGHT_GRADIENT, ct.to_double_array(weight_gradient))
+        ct.convolution_backward_data(input_gradient, 0.0, out_grad, weights, workspace, desc, algorithms)
+        _eq(CONV_INPUT_GRADIENT, ct.to_double_array(input_gradient))
 
 
 def indexed_tensor(driver, datatype):
