@@ -21,8 +21,9 @@ namespace {
 template <typename T> __device__ __forceinline__ T act_grad(T out, T grad, int op) {
   const double o = (double)out, g = (double)grad;
   switch (op) {
-    case CB200_ACT_LOGISTIC: return (T)((o * (1.0 - o)) * g);
-    case CB200_ACT_TANH: return (T)((1.0 - o * o) * g);
+    // explicit round-to-nearest operations: no fused multiply-add (the JVM rounds after every operation)
+    case CB200_ACT_LOGISTIC: return (T)__dmul_rn(__dmul_rn(o, __dsub_rn(1.0, o)), g);
+    case CB200_ACT_TANH: return (T)__dmul_rn(__dsub_rn(1.0, __dmul_rn(o, o)), g);
     default: return (out > (T)0 ? (T)1 : (T)0) * grad;      // relu; exact in the element type
   }
 }
