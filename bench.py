@@ -310,6 +310,59 @@ def bench_conv(drv, dev, peaks):
             "note": "ms = conv + bias + ReLU (3 protocol calls); work = 2*64*64*3136*576"}
 
 
+def bench_backward(drv, dev, peaks):
+    """The backward ring at the benchmark's layer shapes (fp32, CUDA events): one hidden layer of the wide MLP
+    on an 8192-row shard (bias gradient by compare-and-swap accumulation, input gradient = gemm! NN, weight
+    gradient = gemm! TN, ReLU gradient) and the config-4 convolution layer's backward."""
+    from cortex_b200 import nn
+    from cortex_b200 import tensor as ct
+    stream = dev.create_stream()
+    rows = 8192
+    rng = np.random.default_rng(701)
+    res = {}
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        lin = nn.Linear(ct.to_tensor(make_weights()[0]), ct.new_tensor([WIDTH]))
+        x = ct.to_tensor(make_input(0, rows))
+        out = ct.new_tensor([rows, WIDTH])
+        lin.forward_fused(x, out, "relu")
+        og = ct.to_tensor(rng.standard_normal((rows, WIDTH), dtype=np.float32))
+        g_act, g_in = ct.new_tensor([rows, WIDTH]), ct.new_tensor([rows, WIDTH])
+        g_w, g_b = ct.new_tensor([WIDTH, WIDTH]), ct.new_tensor([WIDTH])
+        act = nn.Activation("relu")
+
+        def layer_bwd():
+            act.backward(out, g_act, og)
+            lin.backward(x, out, g_in, g_act, g_w, g_b)
+
+        for _ in range(2):
+            layer_bwd()
+        ms = time_region(stream, layer_bwd, 5)
+        ms_bias = time_region(stream, lambda: ct.binary_op(g_b, 1.0, g_act, 1.0, g_b, "+"), 5)
+        ms_in = time_region(stream, lambda: ct.gemm(g_in, False, False, 1.0, g_act, lin.weights, 0.0), 5)
+        ms_w = time_region(stream, lambda: ct.gemm(g_w, True, False, 1.0, g_act, x, 1.0), 5)
+        flops = 2.0 * rows * WIDTH * WIDTH
+        res["mlp_layer_8192x4096x4096"] = {
+            "ms": round(ms, 4), "input_gradient_ms": round(ms_in, 4), "input_gradient_tflops": round(flops / ms_in / 1e9, 1),
+            "weight_gradient_ms": round(ms_w, 4), "weight_gradient_tflops": round(flops / ms_w / 1e9, 1),
+            "bias_gradient_ms": round(ms_bias, 4)}
+        cx = ct.to_tensor(rng.standard_normal((64, 64, 56, 56), dtype=np.float32))
+        cw = ct.to_tensor((rng.standard_normal((64, 576), dtype=np.float32) * np.float32(np.sqrt(2.0 / 576))))
+        cout = ct.new_tensor([64, 64, 56, 56])
+        conv = nn.Convolution(cw, ct.new_tensor([64]), (3, 3), (1, 1), (1, 1), 64, 64, "float")
+        conv.forward(cx, cout)
+        cog = ct.to_tensor(rng.standard_normal((64, 64, 56, 56), dtype=np.float32))
+        c_gin, c_gw, c_gb = ct.new_tensor([64, 64, 56, 56]), ct.new_tensor([64, 576]), ct.new_tensor([64])
+        for _ in range(2):
+            conv.backward(cx, c_gin, cog, c_gw, c_gb)
+        ms_c = time_region(stream, lambda: conv.backward(cx, c_gin, cog, c_gw, c_gb), 3)
+        ms_cw = time_region(stream, lambda: ct.convolution_backward_weights(c_gw, 0.0, cog, cx, None, conv.desc, None), 3)
+        ms_cd = time_region(stream, lambda: ct.convolution_backward_data(c_gin, 0.0, cog, cw, None, conv.desc, None), 3)
+        res["conv_64x64x56x56"] = {"ms": round(ms_c, 3), "backward_weights_ms": round(ms_cw, 3),
+                                   "backward_data_ms": round(ms_cd, 3),
+                                   "note": "unroll + 64 per-image GEMMs each; work 2 x 1.48e10 flop"}
+    return res
+
+
 def bench_gemm_f64(drv, dev):
     """Config 2, fp64: 4096^3 DMMA gemm!, alpha 1.5 beta 0.5."""
     from cortex_b200 import tensor as ct
@@ -673,7 +726,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--dtype", default="float", choices=["float", "double"],
                     help="float = the headline workload; double = its fp64 variant (DMMA gemm)")
-    ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128", "mlplayer", "mnistcnn"],
+    ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128", "mlplayer", "mnistcnn", "backward"],
                     help="mlp = the benchmark; gemm4096 / eltwise = the small single-purpose runs used for ncu captures")
     args = ap.parse_args()
     if args.case != "mlp":
@@ -683,7 +736,8 @@ def main():
         peaks = measured_peaks()
         fns = {"gemm4096": lambda: bench_gemm_4096(drv, dev, peaks), "eltwise": lambda: bench_eltwise(drv, dev, peaks),
                "conv": lambda: bench_conv(drv, dev, peaks), "gemm4096f64": lambda: bench_gemm_f64(drv, dev),
-               "mlp128": lambda: bench_mlp_128(drv, dev), "mlplayer": lambda: bench_mlp_layer(drv, dev, peaks), "mnistcnn": lambda: bench_mnist_convnet(drv, dev)}
+               "mlp128": lambda: bench_mlp_128(drv, dev), "mlplayer": lambda: bench_mlp_layer(drv, dev, peaks), "mnistcnn": lambda: bench_mnist_convnet(drv, dev),
+               "backward": lambda: bench_backward(drv, dev, peaks)}
         print(json.dumps({args.case: fns[args.case]()}), flush=True)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

@@ -503,6 +503,137 @@ ew_accum_cas(T* dest, const T* y, Operand od, Operand oy, Geometry g, long long 
   }
 }
 
+// Broadcast-sum accumulation  dest[c] += ya * sum over n, e of y[n, c, e]  (dest [C] dense, y [N, C, E] dense):
+// what the bias gradients are (binary-op! with a destination smaller than the operation, y_alpha * y + dest).
+// The compare-and-swap kernel above serialises every element that maps to one destination address (N * E of
+// them); here each block sums a slab privately and issues ONE atomic add per destination it touches.  The sum
+// order is as unspecified as with compare-and-swap; partial sums are kept in double.
+template <typename T>
+__global__ void __launch_bounds__(128)
+bcast_sum_cols_kernel(T* dest, const T* y, int N, int C, double ya, int rows_per_slab, int vec) {
+  // E == 1: columns are contiguous; a thread owns `vec` adjacent columns and walks the rows of its slab
+  const long long col = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * vec;
+  if (col >= C) return;
+  const int r0 = blockIdx.y * rows_per_slab, r1 = min(N, r0 + rows_per_slab);
+  double acc[4] = {0.0, 0.0, 0.0, 0.0};
+  if (vec == 4) {
+    struct alignas(16) V { T v[4]; };
+    T p0[4] = {T(), T(), T(), T()}, p1[4] = {T(), T(), T(), T()};
+    int r = r0;
+    for (; r + 1 < r1; r += 2) {          // two rows in flight, accumulated in the element type over a short run
+      const V a = *reinterpret_cast<const V*>(y + (long long)r * C + col);
+      const V b = *reinterpret_cast<const V*>(y + (long long)(r + 1) * C + col);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { p0[e] += a.v[e]; p1[e] += b.v[e]; }
+      if (((r - r0) & 62) == 62) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc[e] += (double)p0[e] + (double)p1[e]; p0[e] = T(); p1[e] = T(); }
+      }
+    }
+    if (r < r1) {
+      const V a = *reinterpret_cast<const V*>(y + (long long)r * C + col);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) p0[e] += a.v[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] += (double)p0[e] + (double)p1[e];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) atomicAdd(dest + col + e, (T)(acc[e] * ya));
+  } else {
+    for (int r = r0; r < r1; ++r) acc[0] += (double)y[(long long)r * C + col];
+    atomicAdd(dest + col, (T)(acc[0] * ya));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+bcast_sum_runs_kernel(T* dest, const T* y, int N, int C, long long E, double ya, int n_per_chunk, int vec) {
+  // E > 1: for a fixed (n, c) the E elements are contiguous; block = (c, chunk of n)
+  const int c = blockIdx.x;
+  const int n0 = blockIdx.y * n_per_chunk, n1 = min(N, n0 + n_per_chunk);
+  double acc = 0.0;
+  for (int n = n0; n < n1; ++n) {
+    const T* base = y + ((long long)n * C + c) * E;
+    if (vec == 4) {
+      struct alignas(16) V { T v[4]; };
+      T p = T();
+      for (long long e = threadIdx.x; e < E / 4; e += blockDim.x) {
+        const V a = reinterpret_cast<const V*>(base)[e];
+        p += (a.v[0] + a.v[1]) + (a.v[2] + a.v[3]);
+      }
+      acc += (double)p;
+    } else {
+      for (long long e = threadIdx.x; e < E; e += blockDim.x) acc += (double)base[e];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __shared__ double part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += part[w];
+    atomicAdd(dest + c, (T)(t * ya));
+  }
+}
+
+// Recognises dest [C] (+ unit dims) accumulated over a dense y [N, C, E]; returns false if the shapes are not of
+// that form (the caller then uses compare-and-swap).
+template <typename T>
+bool try_bcast_sum(cb200_stream* s, T* dest, const cb200_dims* dd, const T* y, const cb200_dims* yd, long long n,
+                   double ya, int* rc_out) {
+  long long expect_y = 1, expect_d = 1, E = 1, Cn = 1, N = 1;
+  int phase = 0;      // 0: inner dims absent from dest, 1: dims shared with dest, 2: outer dims absent from dest
+  for (int d = 0; d < 5; ++d) {
+    const long long ys = yd->rev_shape[d], ds = dd->rev_shape[d];
+    if (yd->index[d] || dd->index[d]) return false;
+    if (ys > 1 && yd->rev_strides[d] != expect_y) return false;
+    if (ds > 1 && dd->rev_strides[d] != expect_d) return false;
+    expect_y *= ys;
+    expect_d *= ds;
+    if (ys == 1 && ds == 1) continue;
+    if (ds == ys) {                      // shared dimension
+      if (phase == 2) return false;
+      phase = 1;
+      Cn *= ys;
+    } else if (ds == 1) {                // summed dimension
+      if (phase == 0) E *= ys; else { phase = 2; N *= ys; }
+    } else {
+      return false;
+    }
+  }
+  if (phase == 0 || N * E == 1 || N * Cn * E != n) return false;
+  if (N > 2147483647LL || Cn > 2147483647LL) return false;
+  DeviceGuard guard(s->device);
+  const int target_blocks = s->sm_count * 8;
+  if (E == 1) {
+    const int vec = (Cn % 4 == 0 && (((uintptr_t)y) & 15) == 0) ? 4 : 1;
+    const long long col_threads = Cn / vec;
+    const unsigned gx = (unsigned)((col_threads + 127) / 128);
+    long long slabs = (target_blocks + gx - 1) / gx;
+    if (slabs > N) slabs = N;
+    if (slabs > 65535) slabs = 65535;
+    if (slabs < 1) slabs = 1;
+    const int rows_per_slab = (int)((N + slabs - 1) / slabs);
+    dim3 grid(gx, (unsigned)((N + rows_per_slab - 1) / rows_per_slab), 1);
+    bcast_sum_cols_kernel<T><<<grid, 128, 0, s->stream>>>(dest, y, (int)N, (int)Cn, ya, rows_per_slab, vec);
+  } else {
+    const int vec = (E % 4 == 0 && (((uintptr_t)y) & 15) == 0) ? 4 : 1;
+    long long chunks = (target_blocks + Cn - 1) / Cn;
+    if (chunks > N) chunks = N;
+    if (chunks > 65535) chunks = 65535;
+    if (chunks < 1) chunks = 1;
+    const int n_per_chunk = (int)((N + chunks - 1) / chunks);
+    dim3 grid((unsigned)Cn, (unsigned)((N + n_per_chunk - 1) / n_per_chunk), 1);
+    bcast_sum_runs_kernel<T><<<grid, 256, 0, s->stream>>>(dest, y, (int)N, (int)Cn, E, ya, n_per_chunk, vec);
+  }
+  *rc_out = CB200_OK;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) *rc_out = cb200_cuda_fail(e, "bcast_sum launch", __FILE__, __LINE__);
+  return true;
+}
+
 // ------------------------------ host-side planning --------------------------
 
 struct Plan {
@@ -886,6 +1017,19 @@ int cb200_binary_accum(cb200_stream* s, int dtype, void* dest, const cb200_dims*
   if (rc) return rc;
   bool indexed_dest = false;
   for (int d = 0; d < 5; ++d) if (dest_dims->index[d]) indexed_dest = true;
+  if (requires_cas && !indexed_dest && op == CB200_ADD && (dtype == CB200_FLOAT || dtype == CB200_DOUBLE) &&
+      dest != y) {
+    // bias-gradient shape: dest + y_alpha * y summed over the dimensions dest does not have
+    int rc2 = CB200_OK;
+    const bool unit = dtype == CB200_FLOAT ? (float)dest_alpha == 1.0f : dest_alpha == 1.0;
+    if (unit) {
+      bool done = dtype == CB200_FLOAT
+                      ? try_bcast_sum<float>(s, (float*)dest, dest_dims, (const float*)y, y_dims, n_elems,
+                                             (double)(float)y_alpha, &rc2)
+                      : try_bcast_sum<double>(s, (double*)dest, dest_dims, (const double*)y, y_dims, n_elems, y_alpha, &rc2);
+      if (done) { if (rc2 == CB200_OK) { CB_LAUNCH_CHECK(s); } return rc2; }
+    }
+  }
   if (requires_cas || indexed_dest) {
     switch (dtype) {
 #define CB_CAS_CASE(DT, T)                                                                        \
