@@ -9,8 +9,9 @@
 //
 // The reference CPU backend reuses the unrolled input its forward pass left in the caller's workspace; here the
 // unrolled matrix is rebuilt in the stream's own workspace (the forward pass keeps none: it gathers straight
-// into the tensor-core tiles).  GEMMs go through the same dispatch as gemm! (tcgen05 3xTF32 / DMMA / SIMT),
-// one per image, chained through beta = 1 for the weight gradient.  col2im is a gather: one thread per input
+// into the tensor-core tiles).  The data gradient's GEMMs go through the same dispatch as gemm! (tcgen05 3xTF32 /
+// DMMA / SIMT), one per image; the weight gradient is a split reduction of its own (conv_wgrad_kernel): its
+// output is C_out x K small while the reduction runs over every pixel of the batch.  col2im is a gather: one thread per input
 // pixel sums the (at most kH*kW) unrolled entries that read it, so there are no atomics and the sum order is
 // fixed.  The CPU backend ignores input-gradient-alpha (it always clears the gradient); this backend applies it,
 // as the reference's CUDA backend does -- the two agree for alpha = 0, which is what the layers pass.
@@ -76,6 +77,89 @@ __global__ void __launch_bounds__(256) roll_kernel(T* in_grad, const T* colsgrad
     }
     in_grad[i] = alpha == (T)0 ? (T)acc : (T)((A)alpha * (A)in_grad[i] + acc);
   }
+}
+
+// W_grad[C_out, K] += sum over the block's images of OG_n[C_out, hw] . cols_n[hw, K].  The output is tiny
+// (C_out x K) and the reduction runs over batch * hw pixels, so the parallelism has to come from splitting that
+// reduction: block = (64 x 64 output tile, group of images); 4 x 4 outputs per thread from 16-deep shared-memory
+// tiles (fp32 / fp64 FMA: the reduction length per block is one or a few images, far too short per tile for the
+// tensor-core kernel's pipeline to pay); one atomic add per output and block at the end.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_wgrad_kernel(T* wg, const T* og, const T* cols, int cout, int kcols, int ld, int hw, int batch, int imgs_per_block,
+                  int vec_a) {
+  constexpr int TM = 64, TN = 64, TK = 16;
+  __shared__ T As[TK][TM + 4];
+  __shared__ T Bs[TK][TN];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int n0 = blockIdx.x * TN, m0 = blockIdx.y * TM;
+  const int img0 = blockIdx.z * imgs_per_block, img1 = min(batch, img0 + imgs_per_block);
+  T acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = T();
+  const int a_row = tid >> 2, a_kq = (tid & 3) * 4;      // A tile: 64 rows x 16 k, 4 consecutive k per thread
+  const int b_k = tid >> 4, b_nq = (tid & 15) * 4;       // B tile: 16 k x 64 n, 4 consecutive n per thread
+  for (int img = img0; img < img1; ++img) {
+    const T* A = og + (long long)img * cout * hw;
+    const T* B = cols + (long long)img * hw * ld;
+    for (int k0 = 0; k0 < hw; k0 += TK) {
+      T av[4] = {T(), T(), T(), T()}, bv[4] = {T(), T(), T(), T()};
+      if (m0 + a_row < cout) {
+        const T* src = A + (long long)(m0 + a_row) * hw + k0 + a_kq;
+        if (vec_a && k0 + a_kq + 4 <= hw) {
+          struct alignas(sizeof(T) * 4) V { T v[4]; };
+          const V v = *reinterpret_cast<const V*>(src);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) av[e] = v.v[e];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) if (k0 + a_kq + e < hw) av[e] = src[e];
+        }
+      }
+      if (k0 + b_k < hw && n0 + b_nq < ld) {
+        // ld is a multiple of 4 and the workspace is 16-byte aligned; columns kcols .. ld-1 hold zeros
+        struct alignas(sizeof(T) * 4) V { T v[4]; };
+        const V v = *reinterpret_cast<const V*>(B + (long long)(k0 + b_k) * ld + n0 + b_nq);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) bv[e] = v.v[e];
+      }
+      __syncthreads();          // the previous tile has been consumed
+#pragma unroll
+      for (int e = 0; e < 4; ++e) As[a_kq + e][a_row] = av[e];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) Bs[b_k][b_nq + e] = bv[e];
+      __syncthreads();
+#pragma unroll
+      for (int kk = 0; kk < TK; ++kk) {
+        T a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= cout) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < kcols) atomicAdd(wg + (long long)m * kcols + n, acc[i][j]);
+    }
+  }
+}
+
+template <typename T> __global__ void scale_kernel(T* p, T alpha, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    p[i] = alpha * p[i];
 }
 
 bool dense4(const cb200_dims* d) {
@@ -149,13 +233,32 @@ int cb200_convolution_backward_weights(cb200_stream* s, int dtype, void* w_grad,
   else
     unroll_kernel<double><<<(unsigned)blocks, 256, 0, s->stream>>>((double*)cols, (const double*)in, g, total);
   CB_LAUNCH_CHECK(s);
-  for (int n = 0; n < g.batch; ++n) {
-    const char* og_n = (const char*)out_grad + (size_t)n * cout * hw * es;
-    const char* cols_n = (const char*)cols + (size_t)n * hw * g.ld * es;
-    rc = cb200_gemm_no_workspace(s, dtype, w_grad, g.kcols, 0, 0, 1.0, og_n, cout, hw, hw, cols_n, g.kcols, g.ld,
-                                 n == 0 ? w_grad_alpha : 1.0);
-    if (rc) return rc;
+  // W_grad = alpha * W_grad first (alpha = 0: cleared without being read), then the split reduction adds onto it
+  const long long wn = (long long)cout * g.kcols;
+  if (w_grad_alpha == 0.0) {
+    CB_CUDA(cudaMemsetAsync(w_grad, 0, (size_t)wn * es, s->stream));
+  } else if (w_grad_alpha != 1.0) {
+    const unsigned sb = (unsigned)((wn + 255) / 256 > cap ? cap : (wn + 255) / 256);
+    if (dtype == CB200_FLOAT) scale_kernel<float><<<sb, 256, 0, s->stream>>>((float*)w_grad, (float)w_grad_alpha, wn);
+    else scale_kernel<double><<<sb, 256, 0, s->stream>>>((double*)w_grad, w_grad_alpha, wn);
+    CB_LAUNCH_CHECK(s);
   }
+  const int tiles = ((g.kcols + 63) / 64) * ((cout + 63) / 64);
+  // enough image groups for ~4 blocks per SM, at most one group per image
+  int groups = (4 * s->sm_count + tiles - 1) / tiles;
+  if (groups > g.batch) groups = g.batch;
+  if (groups > 65535) groups = 65535;
+  if (groups < 1) groups = 1;
+  const int per = (g.batch + groups - 1) / groups;
+  dim3 grid((unsigned)((g.kcols + 63) / 64), (unsigned)((cout + 63) / 64), (unsigned)((g.batch + per - 1) / per));
+  const int vec_a = (hw % 4 == 0) && ((((uintptr_t)out_grad) & (4 * es - 1)) == 0);
+  if (dtype == CB200_FLOAT)
+    conv_wgrad_kernel<float><<<grid, 256, 0, s->stream>>>((float*)w_grad, (const float*)out_grad, (const float*)cols, cout,
+                                                          g.kcols, g.ld, hw, g.batch, per, vec_a);
+  else
+    conv_wgrad_kernel<double><<<grid, 256, 0, s->stream>>>((double*)w_grad, (const double*)out_grad, (const double*)cols,
+                                                           cout, g.kcols, g.ld, hw, g.batch, per, vec_a);
+  CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
 
