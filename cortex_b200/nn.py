@@ -13,6 +13,7 @@ Backward passes of the dense layers (the next ring around the inference path):
   biased_multiply_backward   nn-backend/biased-multiply-backward!   compute/nn/backend.clj:115-139
   Linear.backward / Activation.backward / Softmax.backward          compute/nn/layers.clj:78-88, 104-116, 164-168
   Convolution.backward                                              compute/nn/layers.clj:320-340
+  softmax_loss_gradient      calculate-cross-entropy-gradient       src/cortex/loss/softmax.clj:13-20
 
 ``fused=True`` replaces the reference's three calls per dense layer
 (assign! bias, gemm! NT beta=1, binary-op! max 0) with the backend's single
@@ -42,6 +43,12 @@ def biased_multiply_backward(input, weights, bias, output, input_gradient, weigh
         ct.gemm(ct.as_batch_matrix(input_gradient), False, False, 1.0, ct.as_batch_matrix(output_gradient), weights, 0.0)
     if weight_gradient is not None:
         ct.gemm(weight_gradient, True, False, 1.0, ct.as_batch_matrix(output_gradient), ct.as_batch_matrix(input), 1.0)
+
+
+def softmax_loss_gradient(output, target, gradient):
+    """d(cross-entropy)/d(softmax input) = output - target, written into the output's gradient buffer
+    (calculate-cross-entropy-gradient, src/cortex/loss/softmax.clj:13-20)."""
+    return ct.binary_op(gradient, 1.0, output, 1.0, target, "-")
 
 
 def relu(input, output):

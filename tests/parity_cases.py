@@ -180,7 +180,7 @@ def mlp_backward_case(datatype, batch, widths, seed=131, act="relu"):
             cur = a
         # loss gradient with respect to the softmax layer's output buffer, as the reference's softmax-loss gives it
         grad = ct.new_tensor([batch, widths[-1]], datatype)
-        ct.binary_op(grad, 1.0, post[-1], 1.0, ct.to_tensor(onehot, datatype), "-")
+        nn.softmax_loss_gradient(post[-1], ct.to_tensor(onehot, datatype), grad)
         outs = []
         g_in = ct.new_tensor([batch, widths[-1]], datatype)
         nn.Softmax().backward(g_in, grad)
