@@ -9,8 +9,8 @@
 //
 // The reference CPU backend reuses the unrolled input its forward pass left in the caller's workspace; here the
 // unrolled matrix is rebuilt in the stream's own workspace (the forward pass keeps none: it gathers straight
-// into the tensor-core tiles).  The data gradient's GEMMs go through the same dispatch as gemm! (tcgen05 3xTF32 /
-// DMMA / SIMT), one per image; the weight gradient is a split reduction of its own (conv_wgrad_kernel): its
+// into the tensor-core tiles).  The data gradient is ONE product over all images (the output gradient is first
+// transposed to pixel rows) through the same dispatch as gemm! (tcgen05 3xTF32 / DMMA / SIMT); the weight gradient is a split reduction of its own (conv_wgrad_kernel): its
 // output is C_out x K small while the reduction runs over every pixel of the batch.  col2im is a gather: one thread per input
 // pixel sums the (at most kH*kW) unrolled entries that read it, so there are no atomics and the sum order is
 // fixed.  The CPU backend ignores input-gradient-alpha (it always clears the gradient); this backend applies it,
@@ -157,6 +157,25 @@ conv_wgrad_kernel(T* wg, const T* og, const T* cols, int cout, int kcols, int ld
   }
 }
 
+// out[(n*hw + p) * ldo + c] = in[(n*C + c) * hw + p]: NCHW gradient -> one [batch*hw, C] matrix (pitch ldo)
+template <typename T>
+__global__ void __launch_bounds__(256) nchw_to_pixel_rows_kernel(T* out, const T* in, int C, int hw, int ldo) {
+  __shared__ T t[32][33];
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32, n = blockIdx.z;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = c0 + ty + 8 * j, p_ = p0 + tx;
+    if (c < C && p_ < hw) t[ty + 8 * j][tx] = in[((long long)n * C + c) * hw + p_];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int p_ = p0 + ty + 8 * j, c = c0 + tx;
+    if (p_ < hw && c < ldo) out[((long long)n * hw + p_) * ldo + c] = c < C ? t[tx][ty + 8 * j] : T();
+  }
+}
+
 template <typename T> __global__ void scale_kernel(T* p, T alpha, long long n) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     p[i] = alpha * p[i];
@@ -283,14 +302,21 @@ int cb200_convolution_backward_data(cb200_stream* s, int dtype, void* in_grad, c
   DeviceGuard guard(s->device);
   void* colsgrad = nullptr;
   if (rows > 0 && cout > 0) {
-    if ((rc = cb200_scratch(s, (size_t)rows * g.ld * es, &colsgrad))) return rc;
-    for (int n = 0; n < g.batch; ++n) {
-      const char* og_n = (const char*)out_grad + (size_t)n * cout * hw * es;
-      char* cg_n = (char*)colsgrad + (size_t)n * hw * g.ld * es;
-      // colsgrad_n[hw, K] = OG_n^T . W : op(A) = OG_n^T is hw x cout, stored [cout, hw]
-      rc = cb200_gemm_no_workspace(s, dtype, cg_n, g.ld, 1, 0, 1.0, og_n, hw, cout, hw, w, g.kcols, g.kcols, 0.0);
-      if (rc) return rc;
-    }
+    // all images in ONE product: the gradient is first laid out as pixel rows, OGt[batch*hw, C_out] (a 32 x 32
+    // tile transpose per image), then colsgrad[batch*hw, K] = OGt . W
+    const int ldt = (cout + 3) & ~3;
+    const size_t cg_bytes = (size_t)rows * g.ld * es;
+    if ((rc = cb200_scratch(s, cg_bytes + (size_t)rows * ldt * es, &colsgrad))) return rc;
+    void* ogt = (char*)colsgrad + cg_bytes;
+    CB_REQUIRE(g.batch <= 65535 && (ldt + 31) / 32 <= 65535, "convolution_backward_data: batch or channel count too large");
+    dim3 tgrid((unsigned)((hw + 31) / 32), (unsigned)((ldt + 31) / 32), (unsigned)g.batch);
+    if (dtype == CB200_FLOAT)
+      nchw_to_pixel_rows_kernel<float><<<tgrid, 256, 0, s->stream>>>((float*)ogt, (const float*)out_grad, cout, hw, ldt);
+    else
+      nchw_to_pixel_rows_kernel<double><<<tgrid, 256, 0, s->stream>>>((double*)ogt, (const double*)out_grad, cout, hw, ldt);
+    CB_LAUNCH_CHECK(s);
+    rc = cb200_gemm_no_workspace(s, dtype, colsgrad, g.ld, 0, 0, 1.0, ogt, rows, cout, ldt, w, g.kcols, g.kcols, 0.0);
+    if (rc) return rc;
   } else {
     // no output pixels: the sum is empty; a one-element dummy keeps the kernel's pointer valid
     if ((rc = cb200_scratch(s, 16, &colsgrad))) return rc;
