@@ -29,23 +29,28 @@ struct BwdGeom {
   int ld;      // row pitch of the unrolled matrix (kcols rounded up to 4)
 };
 
-// cols[(n*hw + p) * ld + c*kh*kw + ky*kw + kx] = in[n, c, oy*sy - py + ky, ox*sx - px + kx] (0 in the padding)
+// cols[(n*hw + p) * ld + c*kh*kw + ky*kw + kx] = in[n, c, oy*sy - py + ky, ox*sx - px + kx] (0 in the padding).
+// One block walks whole rows of the unrolled matrix (one output pixel each): the pixel's coordinates are worked
+// out once per row, a thread then needs two small divisions per element, and a warp writes 128 contiguous bytes.
 template <typename T>
-__global__ void __launch_bounds__(256) unroll_kernel(T* cols, const T* in, BwdGeom g, long long total) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const unsigned row = (unsigned)(i / (unsigned)g.ld);
-    const int col = (int)(i - (long long)row * g.ld);
-    T v = (T)0;
-    if (col < g.kcols) {
-      const int kx = col % g.kw, ky = (col / g.kw) % g.kh, c = col / (g.kw * g.kh);
-      const unsigned hw = (unsigned)(g.out_h * g.out_w);
-      const int n = (int)(row / hw), p = (int)(row % hw);
-      const int oy = p / g.out_w, ox = p % g.out_w;
-      const int iy = oy * g.stride_y - g.pad_y + ky, ix = ox * g.stride_x - g.pad_x + kx;
-      if (iy >= 0 && iy < g.in_h && ix >= 0 && ix < g.in_w)
-        v = in[(((long long)n * g.cin + c) * g.in_h + iy) * g.in_w + ix];
+__global__ void __launch_bounds__(256) unroll_kernel(T* cols, const T* in, BwdGeom g, long long rows) {
+  const int hw = g.out_h * g.out_w, taps = g.kh * g.kw;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int n = (int)(row / hw), p = (int)(row - (long long)n * hw);
+    const int oy = p / g.out_w, ox = p - oy * g.out_w;
+    const int y0 = oy * g.stride_y - g.pad_y, x0 = ox * g.stride_x - g.pad_x;
+    const T* img = in + (long long)n * g.cin * g.in_h * g.in_w;
+    T* dst = cols + row * g.ld;
+    for (int col = threadIdx.x; col < g.ld; col += blockDim.x) {
+      T v = (T)0;
+      if (col < g.kcols) {
+        const int c = col / taps, t = col - c * taps;
+        const int ky = t / g.kw, kx = t - ky * g.kw;
+        const int iy = y0 + ky, ix = x0 + kx;
+        if (iy >= 0 && iy < g.in_h && ix >= 0 && ix < g.in_w) v = img[((long long)c * g.in_h + iy) * g.in_w + ix];
+      }
+      dst[col] = v;
     }
-    cols[i] = v;
   }
 }
 
@@ -245,12 +250,12 @@ int cb200_convolution_backward_weights(cb200_stream* s, int dtype, void* w_grad,
   void* cols = nullptr;
   if ((rc = cb200_scratch(s, (size_t)total * es, &cols))) return rc;
   DeviceGuard guard(s->device);
-  long long blocks = (total + 255) / 256, cap = (long long)s->sm_count * 32;
-  if (blocks > cap) blocks = cap;
+  const long long cap = (long long)s->sm_count * 32;
+  const long long blocks = rows < cap ? rows : cap;
   if (dtype == CB200_FLOAT)
-    unroll_kernel<float><<<(unsigned)blocks, 256, 0, s->stream>>>((float*)cols, (const float*)in, g, total);
+    unroll_kernel<float><<<(unsigned)blocks, 256, 0, s->stream>>>((float*)cols, (const float*)in, g, rows);
   else
-    unroll_kernel<double><<<(unsigned)blocks, 256, 0, s->stream>>>((double*)cols, (const double*)in, g, total);
+    unroll_kernel<double><<<(unsigned)blocks, 256, 0, s->stream>>>((double*)cols, (const double*)in, g, rows);
   CB_LAUNCH_CHECK(s);
   // W_grad = alpha * W_grad first (alpha = 0: cleared without being read), then the split reduction adds onto it
   const long long wn = (long long)cout * g.kcols;
