@@ -22,6 +22,21 @@ import sys
 import threading
 import time
 
+
+def _host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
+
+
+if "--impl" in sys.argv and "reference" in sys.argv:
+    # The CPU arm uses every host core it may run on.  torch.distributed.run exports OMP_NUM_THREADS=1 to
+    # its workers; OpenBLAS and the OpenMP runtime read these variables when they are loaded, so they are
+    # set here, before numpy is imported.
+    for _var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS"):
+        os.environ[_var] = str(_host_cores())
+
 import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -31,6 +46,27 @@ if ROOT not in sys.path:
 BATCH, WIDTH, CLASSES, HIDDEN_LAYERS = 65536, 4096, 1000, 4
 SEED_X, SEED_W = 501, 502
 FLOPS_PER_SAMPLE = 2.0 * (HIDDEN_LAYERS * WIDTH * WIDTH + WIDTH * CLASSES)
+CPU_SAMPLE_ROWS = 8192        # rows of the batch the CPU arm runs per step (one 8-GPU shard)
+
+
+def workload_config(world, dt="float"):
+    """The `config` object: the same for the B200 arm and for the CPU reference arm."""
+    prec = "fp32" if dt == "float" else "fp64"
+    return {"workload": "wide_mlp: batch 65536 x 4096 -> 4 x (linear 4096 + ReLU) -> linear 1000 + softmax, %s, "
+                        "He-normal weights (seeds 502-506), zero biases, batch-sharded, weights replicated" % prec,
+            "global_batch": BATCH, "parallelism": "batch-shard x%d" % world,
+            "l2": "inputs larger than L2 (every layer streams >= %d MiB of activations per GPU)"
+                  % ((BATCH // max(world, 1)) * WIDTH * 4 >> 20)}
+
+
+def threads_in_use():
+    """Thread counts the loaded BLAS / OpenMP runtimes report (what the CPU arm really ran on)."""
+    try:
+        import threadpoolctl
+        info = threadpoolctl.threadpool_info()
+        return {"%s:%s" % (i.get("user_api"), i.get("internal_api")): i.get("num_threads") for i in info}
+    except Exception as exc:      # reporting only
+        return {"error": repr(exc)}
 
 
 def measured_peaks():
@@ -40,6 +76,111 @@ def measured_peaks():
         return {"hbm_gbs": p["hbm_gbs"], "bf16_burst": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"],
                 "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def measure_library_peaks(device_index, sustained_s=4.0):
+    """MEASUREMENT ONLY -- never on the product path.  The library matmul (torch.matmul -> cuBLAS) timed the way
+    MEASURED_PEAKS.json was (best of 10 = burst; back to back for `sustained_s` seconds = sustained, CUDA
+    events on torch's stream): fp32 with TF32 tensor cores (the 3xTF32 roofline is this / 3), fp32 without
+    (the CUDA-core SGEMM the reference's cuBLAS 8 would run), and fp64.  8192^3, 2*N^3 flop."""
+    import torch
+    dev = torch.device("cuda", device_index)
+    n = 8192
+    flop = 2.0 * n ** 3
+
+    def set_tf32(on):
+        try:
+            torch.backends.cuda.matmul.fp32_precision = "tf32" if on else "ieee"
+        except Exception:
+            torch.backends.cuda.matmul.allow_tf32 = bool(on)
+
+    def run(dtype, tf32, sustained):
+        set_tf32(tf32)
+        with torch.cuda.device(dev):
+            a = torch.randn(n, n, device=dev, dtype=dtype)
+            b = torch.randn(n, n, device=dev, dtype=dtype)
+            c = torch.empty_like(a)
+            for _ in range(3):
+                torch.matmul(a, b, out=c)
+            torch.cuda.synchronize(dev)
+            best = None
+            for _ in range(10):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                torch.matmul(a, b, out=c)
+                e1.record()
+                e1.synchronize()
+                ms = e0.elapsed_time(e1)
+                best = ms if best is None else min(best, ms)
+            out = {"burst_tflops": round(flop / best / 1e9, 1)}
+            if sustained:
+                per = max(1, int(0.25 * 1000.0 / best))       # launches per quarter second
+                total_ms, count = 0.0, 0
+                while total_ms < sustained * 1000.0:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(per):
+                        torch.matmul(a, b, out=c)
+                    e1.record()
+                    e1.synchronize()
+                    total_ms += e0.elapsed_time(e1)
+                    count += per
+                out["sustained_tflops"] = round(flop * count / total_ms / 1e9, 1)
+            del a, b, c
+        return out
+
+    res = {"how": "torch.matmul 8192^3 (cuBLAS), best of 10 and back to back for %.0f s, CUDA events; "
+                  "measurement only" % sustained_s}
+    try:
+        res["fp32_tf32"] = run(torch.float32, True, sustained_s)
+        res["fp32_no_tf32"] = run(torch.float32, False, 0)
+        res["fp64"] = run(torch.float64, False, sustained_s)
+    except Exception as exc:
+        res["error"] = repr(exc)
+    finally:
+        set_tf32(False)
+        torch.cuda.empty_cache()
+    return res
+
+
+def rooflines(peaks, lib):
+    """Denominators: 3xTF32 = measured library TF32 rate / 3 (three MMAs per product); fp64 = measured library
+    dgemm rate.  Falls back to the bf16-derived proxy / the nominal fp64 figure when the measurement is missing."""
+    out = {"source": {}}
+    tf = (lib or {}).get("fp32_tf32")
+    if tf and "sustained_tflops" in tf:
+        out["tf32x3_burst"], out["tf32x3_sustained"] = tf["burst_tflops"] / 3.0, tf["sustained_tflops"] / 3.0
+        out["source"]["tf32x3"] = "measured in this run: library fp32 matmul with TF32 on, / 3"
+    else:
+        out["tf32x3_burst"], out["tf32x3_sustained"] = peaks["bf16_burst"] / 6.0, peaks["bf16_sustained"] / 6.0
+        out["source"]["tf32x3"] = "%s bf16 / 2 (tf32 rate) / 3 (proxy: no TF32 measurement in this run)" % peaks["source"]
+    f64 = (lib or {}).get("fp64")
+    if f64 and "sustained_tflops" in f64:
+        out["fp64_burst"], out["fp64_sustained"] = f64["burst_tflops"], f64["sustained_tflops"]
+        out["source"]["fp64"] = "measured in this run: library fp64 matmul"
+    else:
+        out["fp64_burst"] = out["fp64_sustained"] = 37.0
+        out["source"]["fp64"] = "nominal B200 fp64 dense rate (no measurement in this run)"
+    return out
+
+
+def fp64_forward(x, weights):
+    """float64 numpy forward of the benchmark network on a few rows: the arbiter of the parity figures."""
+    h = x.astype(np.float64)
+    for i, w in enumerate(weights):
+        h = h @ w.astype(np.float64).T
+        if i + 1 < len(weights):
+            h = np.maximum(h, 0.0)
+    e = np.exp(h - h.max(axis=1, keepdims=True))
+    return e / e.sum(axis=1, keepdims=True)
+
+
+def rel_err(got, ref):
+    """max abs(got - ref) / max(abs(ref), rms(ref)) -- the measure the parity tests use."""
+    ref = np.asarray(ref, np.float64)
+    got = np.asarray(got, np.float64).reshape(ref.shape)
+    rms = float(np.sqrt(np.mean(ref ** 2))) or 1.0
+    return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), rms)))
 
 
 def make_weights():
@@ -118,9 +259,9 @@ class ClockSampler:
 # reference arm: the CPU oracle (restatement of the reference's CPU backend) on host cores
 # --------------------------------------------------------------------------------------
 
-def cpu_forward_rate(sample_rows, weights, repeats=1):
-    """samples/s of the oracle MLP forward (bias assign!, gemm! NT beta=1, ReLU binary-op!, softmax!)
-    on `sample_rows` rows of the workload."""
+def cpu_arm(sample_rows, weights):
+    """The oracle MLP forward (bias assign!, gemm! NT beta=1, ReLU binary-op!, softmax!: the reference's call
+    sequence) on `sample_rows` rows of the workload.  Returns step() -> (samples/s, seconds) for one pass."""
     from cortex_b200 import nn
     from cortex_b200 import tensor as ct
     from oracle.cpu_backend import OracleDriver
@@ -135,33 +276,44 @@ def cpu_forward_rate(sample_rows, weights, repeats=1):
         net = nn.MLP(layers, fused=False)
         xt = ct.to_tensor(x)
         net.infer(xt)   # touch buffers once
-        t0 = time.perf_counter()
-        for _ in range(repeats):
+
+    def step():
+        with ct.with_stream(stream), ct.with_datatype("float"):
+            t0 = time.perf_counter()
             net.infer(xt)
-        dt = (time.perf_counter() - t0) / repeats
-    return sample_rows / dt, dt
+            dt = time.perf_counter() - t0
+        return sample_rows / dt, dt
+
+    return step
+
+
+def cpu_baseline_object(value, secs, sample):
+    pools = threads_in_use()
+    counts = [v for v in pools.values() if isinstance(v, int)]
+    return {"value": value, "unit": "samples/s", "cores": max(counts) if counts else 1, "kind": "port",
+            "host_cores_available": _host_cores(), "thread_pools": pools, "sample_rows": sample,
+            "sample": "%d rows of the 65536-row batch per step (%.2f s per step), samples/s = rows / time; oracle "
+                      "elementwise / softmax in C with OpenMP, gemm! through OpenBLAS sgemm; the reference itself is "
+                      "Clojure on the JVM and cannot run here" % (sample, secs)}
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    weights = make_weights()
-    sample = 2048
-    cores = os.cpu_count() or 1
+    sample = CPU_SAMPLE_ROWS
+    step = cpu_arm(sample, make_weights())
     for _ in range(args.warmup):
-        cpu_forward_rate(sample, weights)
+        step()
     t0 = time.perf_counter()
-    rates = [cpu_forward_rate(sample, weights)[0] for _ in range(args.steps)]
+    rates = [step()[0] for _ in range(args.steps)]
     total = time.perf_counter() - t0
     value = float(np.mean(rates))
     line = {
         "impl": "reference", "metric": "wide_mlp_inference_samples_per_s", "value": value, "unit": "samples/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * sample / value,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "wide_mlp 65536x4096 -> 4x(4096+ReLU) -> 1000+softmax, fp32 (CPU: %d-row sample per step)" % sample},
-        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": "port",
-                         "sample": "%d rows of the 65536-row batch per step; oracle elementwise/softmax in C (OpenMP), "
-                                   "gemm! through OpenBLAS sgemm; the reference itself is Clojure/JVM and cannot run here" % sample},
+        "config": workload_config(world),
+        "cpu_baseline": cpu_baseline_object(value, sample / value, sample),
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": total,
     }
@@ -187,25 +339,35 @@ def time_region(stream, fn, iters, prime=None):
     return e1.elapsed_ms_since(e0) / iters
 
 
-def bench_gemm_4096(drv, dev, peaks):
-    """Config 2 in brief: C = 1.5*A*B^T + 0.5*C, 4096^3 fp32, all four transposes."""
+def bench_gemm_4096(drv, dev, roofs):
+    """Config 2 in brief: C = 1.5*op(A)*op(B) + 0.5*C, 4096^3 fp32, all four transposes, on dense operands
+    and on [4096, 4096] windows at (64, 64) of [4224, 4224] backing buffers (row pitch 4224)."""
     from cortex_b200 import tensor as ct
     stream = dev.create_stream()
     rng = np.random.default_rng(201)
-    out = {}
+    out, pitched = {}, {}
+    combos = (("NT", False, True), ("NN", False, False), ("TN", True, False), ("TT", True, True))
     with ct.with_stream(stream), ct.with_datatype("float"):
         A = ct.to_tensor(rng.standard_normal((4096, 4096), dtype=np.float32))
         B = ct.to_tensor(rng.standard_normal((4096, 4096), dtype=np.float32))
         Cm = ct.to_tensor(rng.standard_normal((4096, 4096), dtype=np.float32))
-        for name, ta, tb in (("NT", False, True), ("NN", False, False), ("TN", True, False), ("TT", True, True)):
+        for name, ta, tb in combos:
             for _ in range(3):
                 ct.gemm(Cm, ta, tb, 1.5, A, B, 0.5)
             ms = time_region(stream, lambda: ct.gemm(Cm, ta, tb, 1.5, A, B, 0.5), 10)
             out[name] = round(2.0 * 4096 ** 3 / ms / 1e9, 1)
-    peak = peaks["bf16_burst"] / 2.0 / 3.0
-    best = max(out.values())
-    return {"tflops": out, "roofline_peak_tflops": round(peak, 1), "frac_of_%s" % peaks["source"]: round(out["NT"] / peak, 3),
-            "note": "peak = bf16 burst / 2 (tf32) / 3 (3xTF32); work counted as 2*M*N*K", "best": best}
+        big = [ct.to_tensor(rng.standard_normal((4224, 4224), dtype=np.float32)) for _ in range(3)]
+        Av, Bv, Cv = (ct.submatrix(t, 64, 4096, 64, 4096) for t in big)
+        for name, ta, tb in combos:
+            for _ in range(3):
+                ct.gemm(Cv, ta, tb, 1.5, Av, Bv, 0.5)
+            ms = time_region(stream, lambda: ct.gemm(Cv, ta, tb, 1.5, Av, Bv, 0.5), 10)
+            pitched[name] = round(2.0 * 4096 ** 3 / ms / 1e9, 1)
+    peak = roofs["tf32x3_burst"]
+    return {"tflops": out, "tflops_pitch_4224_views": pitched, "roofline_peak_tflops": round(peak, 1),
+            "frac": {k: round(v / peak, 3) for k, v in out.items()},
+            "note": "peak (burst, kernel timed alone): %s; work counted as 2*M*N*K" % roofs["source"]["tf32x3"],
+            "best": max(out.values())}
 
 
 def bench_eltwise(drv, dev, peaks):
@@ -282,7 +444,7 @@ def bench_eltwise(drv, dev, peaks):
     return res
 
 
-def bench_conv(drv, dev, peaks):
+def bench_conv(drv, dev, roofs):
     """Config 4 in brief: NCHW conv 64x64x56x56, 3x3 s1 p1, 64 output channels, + bias + ReLU, fp32."""
     from cortex_b200 import nn
     from cortex_b200 import tensor as ct
@@ -305,14 +467,18 @@ def bench_conv(drv, dev, peaks):
         conv_only = lambda: ct.convolution_forward(out, 0.0, x, w, layer.workspace, layer.desc, layer.algorithms)
         ms_conv = time_region(stream, conv_only, 10)
     flops = 2.0 * 64 * 64 * 3136 * 576
+    hbm_bytes = 2 * 64 * 64 * 56 * 56 * 4 + 64 * 576 * 4
     return {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "images_per_s": round(64 / ms * 1000.0, 0),
             "conv_kernel_ms": round(ms_conv, 4), "conv_kernel_tflops": round(flops / ms_conv / 1e9, 1),
-            "note": "ms = conv + bias + ReLU (3 protocol calls); work = 2*64*64*3136*576"}
+            "conv_kernel_frac_of_tf32x3_burst": round(flops / ms_conv / 1e9 / roofs["tf32x3_burst"], 3),
+            "conv_kernel_gbs_compulsory": round(hbm_bytes / ms_conv / 1e6, 0),
+            "note": "ms = conv + bias + ReLU (3 protocol calls); work = 2*64*64*3136*576; compulsory bytes = input + "
+                    "output + weights once"}
 
 
 def bench_backward(drv, dev, peaks):
     """The backward ring at the benchmark's layer shapes (fp32, CUDA events): one hidden layer of the wide MLP
-    on an 8192-row shard (bias gradient by compare-and-swap accumulation, input gradient = gemm! NN, weight
+    on an 8192-row shard (bias gradient = a slab sum over the batch, input gradient = gemm! NN, weight
     gradient = gemm! TN, ReLU gradient) and the config-4 convolution layer's backward."""
     from cortex_b200 import nn
     from cortex_b200 import tensor as ct
@@ -363,7 +529,7 @@ def bench_backward(drv, dev, peaks):
     return res
 
 
-def bench_gemm_f64(drv, dev):
+def bench_gemm_f64(drv, dev, roofs=None):
     """Config 2, fp64: 4096^3 DMMA gemm!, alpha 1.5 beta 0.5."""
     from cortex_b200 import tensor as ct
     stream = dev.create_stream()
@@ -377,7 +543,12 @@ def bench_gemm_f64(drv, dev):
             ct.gemm(Cm, ta, tb, 1.5, A, B, 0.5)
             ms = time_region(stream, lambda: ct.gemm(Cm, ta, tb, 1.5, A, B, 0.5), 3)
             out[name] = round(2.0 * 4096 ** 3 / ms / 1e9, 2)
-    return {"tflops": out}
+    res = {"tflops": out}
+    if roofs:
+        res["roofline_peak_tflops"] = round(roofs["fp64_burst"], 2)
+        res["frac"] = {k: round(v / roofs["fp64_burst"], 3) for k, v in out.items()}
+        res["note"] = "peak (burst): %s" % roofs["source"]["fp64"]
+    return res
 
 
 def bench_mlp_128(drv, dev):
@@ -407,13 +578,10 @@ def bench_mlp_128(drv, dev):
 def bench_mnist_convnet(drv, dev):
     """The reference's MNIST-NETWORK shape (conv 5x5 -> max-pool -> batch-norm -> ReLU -> conv 5x5 -> max-pool ->
     batch-norm -> linear 500 + ReLU -> linear 10 -> softmax), batch 128, inference."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import parity_cases as pc
+    from cortex_b200 import nn
     from cortex_b200 import tensor as ct
     stream = dev.create_stream()
     with ct.with_stream(stream), ct.with_datatype("float"):
-        # the case builder returns a closure that rebuilds the network; time a prebuilt one instead
-        from cortex_b200 import nn
         rng = np.random.default_rng(601)
         t = lambda a: ct.to_tensor(np.asarray(a, np.float32))
         he = lambda shape, fan: rng.standard_normal(shape) * np.sqrt(2.0 / fan)
@@ -489,9 +657,11 @@ def bench_mlp_f64(drv, dev):
 
 def bench_column_head(dev, stream, world, rank, dt, dist):
     """The column-sharded last layer (4096 -> 1000 split by output column over the ranks) on an
-    8192-row replicated activation block: (a) GEMM, NCCL all-gather, re-layout assign!, softmax!;
-    (b) ONE fused GEMM whose epilogue stores its window into every rank's logits over NVLink, a
-    stream-ordered fence, softmax!.  Device time, max over ranks."""
+    8192-row replicated activation block: (a) GEMM, NCCL all-gather enqueued on the backend's stream,
+    re-layout assign!, softmax!; (b) ONE fused GEMM whose epilogue stores its window into every rank's
+    logits over NVLink, a stream-ordered fence, softmax!.  Device time, max over ranks.  Outside the
+    timed regions both results are compared with a float64 softmax(h . W^T) on sampled rows, over all
+    1000 columns (every rank's window), max over ranks."""
     import torch
     from cortex_b200 import tensor as ct
     from cortex_b200.parallel import (PeerLogits, column_sharded_head, column_sharded_head_fused, shard_bounds,
@@ -500,23 +670,26 @@ def bench_column_head(dev, stream, world, rank, dt, dist):
     npdt = np.float32 if dt == "float" else np.float64
     lo, hi = shard_bounds(CLASSES, world, rank)
     w = make_weights()[-1].astype(npdt)
+    h_host = np.maximum(make_input(0, B), 0).astype(npdt)
     res = {"rows": B, "columns_per_rank": hi - lo}
     with ct.with_stream(stream), ct.with_datatype(dt):
-        h = ct.to_tensor(np.maximum(make_input(0, B), 0).astype(npdt))
+        h = ct.to_tensor(h_host)
         ws, bs = ct.to_tensor(w[lo:hi]), ct.new_tensor([hi - lo])
         exchange = PeerLogits(dev, B, CLASSES, world, rank, dt)
         fence = stream_fence(stream)
         fence()
+        nccl_ws = {}
+        out = {}
 
         def fused():
-            column_sharded_head_fused(h, ws, bs, exchange, fence)
+            out["fused"] = column_sharded_head_fused(h, ws, bs, exchange, fence)
             fence()       # the logits buffers are reused by the next call
 
         def nccl():
-            column_sharded_head(h, ws, bs, CLASSES, world, rank)
+            out["nccl"] = column_sharded_head(h, ws, bs, CLASSES, world, rank, workspace=nccl_ws)
 
-        for name, fn, iters in (("nccl_allgather_ms", nccl, 5), ("fused_peer_store_ms", fused, 10)):
-            for _ in range(2):
+        for name, fn, iters in (("nccl_allgather_ms", nccl, 10), ("fused_peer_store_ms", fused, 10)):
+            for _ in range(3):
                 fn()
             stream.sync()
             dist.barrier()
@@ -524,16 +697,43 @@ def bench_column_head(dev, stream, world, rank, dt, dist):
             t = torch.tensor([ms], device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             res[name] = round(float(t[0]), 4)
-        probs = ct.to_array(exchange.tensor).reshape(B, CLASSES)
-        res["max_abs_rowsum_minus_1"] = float(np.abs(probs.sum(axis=1) - 1.0).max())
+        # parity, outside the timed regions: 48 sampled rows x all columns against float64
+        rows_s = np.random.default_rng(77).choice(B, size=48, replace=False)
+        z = h_host[rows_s].astype(np.float64) @ w.astype(np.float64).T
+        e = np.exp(z - z.max(axis=1, keepdims=True))
+        want = e / e.sum(axis=1, keepdims=True)
+        errs = []
+        for name in ("nccl", "fused"):
+            got = ct.to_array(out[name]).reshape(B, CLASSES)
+            errs.append(rel_err(got[rows_s], want))
+            if name == "fused":
+                res["max_abs_rowsum_minus_1"] = float(np.abs(got.sum(axis=1) - 1.0).max())
+        t = torch.tensor(errs, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res["parity"] = {"nccl_allgather_rel_err_vs_fp64": float(t[0]), "fused_peer_store_rel_err_vs_fp64": float(t[1]),
+                         "sample": "48 rows x all 1000 columns (every rank's window), max over ranks; "
+                                   "abs(got-ref)/max(abs(ref), rms(ref))"}
         stream.sync()
         dist.barrier()
         exchange.close()
     return res
 
 
+def with_clocks(local_rank, fn):
+    """Runs fn() with nvidia-smi clock sampling around it; the clocks object is attached to fn's dict."""
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    try:
+        res = fn()
+    finally:
+        clocks = sampler.stop()
+    if isinstance(res, dict):
+        res["clocks"] = clocks
+    return res
+
+
 def run_b200(args, rank, world, local_rank):
-    import torch  # plumbing only: rendezvous, barrier, max-over-ranks
+    import torch  # plumbing only: rendezvous, barrier, max-over-ranks (and the measurement-only library peaks)
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -555,9 +755,10 @@ def run_b200(args, rank, world, local_rank):
     dt = args.dtype                                    # "float" (the headline) or "double" (the fp64 variant)
     npdt = np.float32 if dt == "float" else np.float64
     weights = [w.astype(npdt) for w in make_weights()]
-    x_host = drv.allocate_host_buffer(rows * WIDTH, dt)
+    # page-locked staging buffers on the NUMA node of this GPU's PCIe slot
+    x_host = drv.allocate_host_buffer(rows * WIDTH, dt, near=dev)
     x_host.as_numpy()[:] = make_input(lo, hi).reshape(-1)
-    y_host = drv.allocate_host_buffer(rows * CLASSES, dt)
+    y_host = drv.allocate_host_buffer(rows * CLASSES, dt, near=dev)
 
     def barrier():
         stream.sync()
@@ -565,6 +766,11 @@ def run_b200(args, rank, world, local_rank):
             torch.cuda.synchronize()
             dist.barrier()
             torch.cuda.synchronize()
+
+    lib_peaks = None
+    if rank == 0 and not args.no_peaks:
+        lib_peaks = measure_library_peaks(local_rank)
+    roofs = rooflines(peaks, lib_peaks)
 
     with ct.with_stream(stream), ct.with_datatype(dt):
         layers = []
@@ -604,7 +810,7 @@ def run_b200(args, rank, world, local_rank):
             return cur
 
         for _ in range(args.warmup):
-            step()
+            resident_out = step()
         barrier()
         sampler = ClockSampler(local_rank)
         if rank == 0:
@@ -616,17 +822,26 @@ def run_b200(args, rank, world, local_rank):
         e1 = stream.create_event(timing=True)
         e1.wait_for_event()
         barrier()
+        clocks = sampler.stop() if rank == 0 else None
         launches = stream.launch_count() - launches0
         ms_step = e1.elapsed_ms_since(e0) / args.steps
         gemm_ms = float(np.mean([b.elapsed_ms_since(a) for a, b in gemm_events]))
+        # rows of the resident result kept for the parity object below
+        parity_rows = np.random.default_rng(1000 + rank).choice(rows, size=16, replace=False)
+        resident_sample = ct.to_array(resident_out).reshape(rows, CLASSES)[parity_rows].copy()
 
         # ---- end to end: pinned host in -> H2D -> layers -> D2H, every step --------------------
-        chunk = min(8192, max(2048, rows // 4))       # >= 4 chunks per shard so upload / compute / download overlap
-        pipe = BatchPipeline(dev, net, WIDTH, CLASSES, chunk, dt)
+        # chunks of 4096-8192 rows (>= 256 pair tiles each, two waves of the 74 clusters or more), three
+        # rotating input slots so that two uploads can be in flight under one chunk's compute
+        chunk = min(8192, max(4096, rows // 2))
+        pipe = BatchPipeline(dev, net, WIDTH, CLASSES, chunk, dt, slots=3)
         h2d = d2h = 0
-        for _ in range(min(args.warmup, 2)):
+        for _ in range(min(args.warmup, 3)):
             pipe.run(x_host, y_host, rows)
         barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
         t0 = pipe.compute.create_event(timing=True)
         for _ in range(args.steps):
             h2d, d2h = pipe.run(x_host, y_host, rows, wait=False)    # steps stream back to back, drained once
@@ -636,19 +851,37 @@ def run_b200(args, rank, world, local_rank):
         t1.wait_for_event()
         barrier()
         e2e_ms = t1.elapsed_ms_since(t0) / args.steps
-        clocks = sampler.stop() if rank == 0 else None      # sampled across both timed regions
+        e2e_clocks = sampler.stop() if rank == 0 else None
+        # two more steps with timing events around every copy and every chunk's forward pass (not timed above)
+        for _ in range(2):
+            pipe.run(x_host, y_host, rows, wait=False, profile=True)
+        pipe.drain()
+        pipe.download.sync()
+        pstats = pipe.stats()
+        barrier()
         probs = y_host.as_numpy().reshape(rows, CLASSES)
         checksum = float(np.abs(probs.sum(axis=1) - 1.0).max())
+        # parity of what came back through the pipeline: sampled rows of this rank's shard against float64
+        want = fp64_forward(x_host.as_numpy().reshape(rows, WIDTH)[parity_rows], weights)
+        parity_err = rel_err(probs[parity_rows], want)
+        same_bits = bool(np.array_equal(probs[parity_rows], resident_sample))
         column_head = bench_column_head(dev, stream, world, rank, dt, dist) if world > 1 else None
 
     # max over ranks
+    rank_stats = [pstats.get("h2d", {}).get("gbs") or 0.0, pstats.get("d2h", {}).get("gbs") or 0.0,
+                  pstats.get("compute", {}).get("ms_per_chunk") or 0.0, pstats.get("compute", {}).get("ms") or 0.0]
     if dist is not None:
-        t = torch.tensor([ms_step, e2e_ms], device="cuda", dtype=torch.float64)
+        t = torch.tensor([ms_step, e2e_ms, parity_err, 0.0 if same_bits else 1.0], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step, e2e_ms = float(t[0]), float(t[1])
+        ms_step, e2e_ms, parity_err, same_bits = float(t[0]), float(t[1]), float(t[2]), float(t[3]) == 0.0
         lt = torch.tensor([launches], device="cuda", dtype=torch.int64)
         dist.all_reduce(lt, op=dist.ReduceOp.SUM)
         launches = int(lt[0])
+        gathered = [torch.zeros(4, device="cuda", dtype=torch.float64) for _ in range(world)]
+        dist.all_gather(gathered, torch.tensor(rank_stats, device="cuda", dtype=torch.float64))
+        all_stats = [[float(v) for v in g] for g in gathered]
+    else:
+        all_stats = [rank_stats]
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -657,15 +890,17 @@ def run_b200(args, rank, world, local_rank):
     value = BATCH / (ms_step / 1000.0)
     e2e_value = BATCH / (e2e_ms / 1000.0)
     gemm_flops = 2.0 * rows * WIDTH * WIDTH
+    timed_s = ms_step * args.steps / 1000.0
+    regime = "sustained" if timed_s >= 1.0 else "burst"
     if dt == "float":
-        peak_tf32x3 = peaks["bf16_sustained"] / 2.0 / 3.0
-        peak_note = ("%s bf16 sustained %.0f TF / 2 (tf32 rate) / 3 (three tf32 MMAs per product); algorithmic work "
-                     "2*M*N*K" % (peaks["source"], peaks["bf16_sustained"]))
+        peak = roofs["tf32x3_" + regime]
+        peak_note = ("3xTF32 roofline = TF32 rate / 3 (three tf32 MMAs per fp32 product; work counted as 2*M*N*K); %s; "
+                     "%s figure because the timed region lasted %.2f s" % (roofs["source"]["tf32x3"], regime, timed_s))
         kernel_name = "gemm_presplit_pair_kernel"
         kernel_path = "split_lo + gemm_bias_act_presplit (tcgen05 cta_group::2 3xTF32 on pre-split operands, CTA pairs, bias+ReLU fused) x5 + softmax"
     else:
-        peak_tf32x3 = 37.0
-        peak_note = "nominal B200 fp64 dense rate 37 TF (no measured fp64 peak exists for this pool); work 2*M*N*K"
+        peak = roofs["fp64_" + regime]
+        peak_note = "fp64 roofline: %s; %s figure (timed region %.2f s); work 2*M*N*K" % (roofs["source"]["fp64"], regime, timed_s)
         kernel_name, kernel_path = "gemm_f64_kernel (DMMA)", "gemm_bias_act (DMMA fp64, bias+ReLU fused) x5 + softmax"
     achieved = gemm_flops / gemm_ms / 1e9
     # fp32: the pre-split kernel reads hi + lo of both operands and writes C + C_lo
@@ -679,40 +914,48 @@ def run_b200(args, rank, world, local_rank):
                         "written) x rows/8192; not memory-bound (~18 % of HBM rate)")
     else:
         traffic, traffic_note = None, "no capture of the fp64 kernel's DRAM counters"
+    config = workload_config(world, dt)
     line = {
         "metric": "wide_mlp_inference_samples_per_s" + ("" if dt == "float" else "_fp64"), "value": value, "unit": "samples/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32" if dt == "float" else "f64", "data": "synthetic",
-        "config": {"workload": "wide_mlp: batch 65536 x 4096 -> 4 x (linear 4096 + ReLU) -> linear 1000 + softmax, %s, " % ("fp32" if dt == "float" else "fp64") +
-                               "He-normal weights (seeds 502-506), zero biases, batch-sharded, weights replicated",
-                   "global_batch": BATCH, "rows_per_gpu": rows, "parallelism": "batch-shard x%d" % world,
-                   "l2": "inputs larger than L2 (every layer streams >= %d MiB of activations)" % (rows * WIDTH * 4 >> 20),
-                   "kernel_path": kernel_path},
+        "config": config, "rows_per_gpu": rows, "kernel_path": kernel_path,
         "tflops": value * FLOPS_PER_SAMPLE / 1e12,
         "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
-                "ms_per_step": e2e_ms, "chunk_rows": chunk, "max_abs_rowsum_minus_1": checksum},
+                "ms_per_step": e2e_ms, "chunk_rows": chunk, "input_slots": pipe.slots,
+                "host_buffer_numa_node": getattr(x_host, "numa_node", -1),
+                "max_abs_rowsum_minus_1": checksum, "clocks": e2e_clocks,
+                "per_rank": [{"h2d_gbs": round(s_[0], 2), "d2h_gbs": round(s_[1], 2), "forward_ms_per_chunk": round(s_[2], 3),
+                              "compute_busy_frac": round(s_[3] / 2.0 / e2e_ms, 3) if e2e_ms > 0 else None} for s_ in all_stats],
+                "per_rank_note": "two extra profiled steps after the timed region: achieved copy rates (copy time "
+                                 "includes waiting for the link), device time of one chunk's forward pass, and that "
+                                 "time x chunks / the timed ms_per_step"},
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": "%s (M=%d, N=4096, K=4096)" % (kernel_name, rows),
-                     "achieved": achieved, "peak": peak_tf32x3, "unit": "TFLOP/s", "frac": achieved / peak_tf32x3,
+                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "traffic": traffic, "traffic_note": traffic_note, "algorithmic_bytes": gemm_bytes, "ms_per_launch": gemm_ms,
-                     "peak_note": peak_note},
+                     "peak_note": peak_note, "frac_of_burst": achieved / (roofs["tf32x3_burst"] if dt == "float" else roofs["fp64_burst"])},
+        "parity": {"batch_sharded_rel_err_vs_fp64": parity_err, "tolerance": 1e-4 if dt == "float" else 1e-12,
+                   "e2e_rows_bit_equal_to_resident": same_bits,
+                   "sample": "16 random rows of every rank's shard, as returned through the host pipeline, against a "
+                             "float64 numpy forward; abs(got-ref)/max(abs(ref), rms(ref)), max over ranks"},
         "clocks": clocks,
+        "library_peaks": lib_peaks,
     }
     if column_head is not None:
         line["column_sharded_head"] = column_head
     if world == 1 and dt == "float":
-        cores = os.cpu_count() or 1
-        rate, secs = cpu_forward_rate(2048, weights)
-        line["cpu_baseline"] = {"value": rate, "unit": "samples/s", "cores": cores, "kind": "port",
-                                "sample": "2048 rows of the batch, one forward (%.1f s): oracle C/OpenMP elementwise + "
-                                          "OpenBLAS sgemm" % secs}
-        line["gemm_4096"] = bench_gemm_4096(drv, dev, peaks)
-        line["gemm_4096_f64"] = bench_gemm_f64(drv, dev)
-        line["eltwise"] = bench_eltwise(drv, dev, peaks)
-        line["conv_64x64x56x56"] = bench_conv(drv, dev, peaks)
-        line["mlp_128x784_500_10"] = bench_mlp_128(drv, dev)
-        line["wide_mlp_fp64"] = bench_mlp_f64(drv, dev)
-        line["mnist_convnet_128"] = bench_mnist_convnet(drv, dev)
+        step_cpu = cpu_arm(CPU_SAMPLE_ROWS, weights)
+        rate, secs = step_cpu()
+        line["cpu_baseline"] = cpu_baseline_object(rate, secs, CPU_SAMPLE_ROWS)
+        extra = lambda fn: with_clocks(local_rank, fn)
+        line["gemm_4096"] = extra(lambda: bench_gemm_4096(drv, dev, roofs))
+        line["gemm_4096_f64"] = extra(lambda: bench_gemm_f64(drv, dev, roofs))
+        line["eltwise"] = extra(lambda: bench_eltwise(drv, dev, peaks))
+        line["conv_64x64x56x56"] = extra(lambda: bench_conv(drv, dev, roofs))
+        line["mlp_128x784_500_10"] = extra(lambda: bench_mlp_128(drv, dev))
+        line["wide_mlp_fp64"] = extra(lambda: bench_mlp_f64(drv, dev))
+        line["mnist_convnet_128"] = extra(lambda: bench_mnist_convnet(drv, dev))
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -726,6 +969,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--dtype", default="float", choices=["float", "double"],
                     help="float = the headline workload; double = its fp64 variant (DMMA gemm)")
+    ap.add_argument("--no-peaks", action="store_true",
+                    help="skip the measurement-only library matmul peaks (rooflines then use the bf16-derived proxy)")
     ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128", "mlplayer", "mnistcnn", "backward"],
                     help="mlp = the benchmark; gemm4096 / eltwise = the small single-purpose runs used for ncu captures")
     args = ap.parse_args()
@@ -734,8 +979,9 @@ def main():
         drv = driver()
         dev = drv.default_device()
         peaks = measured_peaks()
-        fns = {"gemm4096": lambda: bench_gemm_4096(drv, dev, peaks), "eltwise": lambda: bench_eltwise(drv, dev, peaks),
-               "conv": lambda: bench_conv(drv, dev, peaks), "gemm4096f64": lambda: bench_gemm_f64(drv, dev),
+        roofs = rooflines(peaks, None)
+        fns = {"gemm4096": lambda: bench_gemm_4096(drv, dev, roofs), "eltwise": lambda: bench_eltwise(drv, dev, peaks),
+               "conv": lambda: bench_conv(drv, dev, roofs), "gemm4096f64": lambda: bench_gemm_f64(drv, dev, roofs),
                "mlp128": lambda: bench_mlp_128(drv, dev), "mlplayer": lambda: bench_mlp_layer(drv, dev, peaks), "mnistcnn": lambda: bench_mnist_convnet(drv, dev),
                "backward": lambda: bench_backward(drv, dev, peaks)}
         print(json.dumps({args.case: fns[args.case]()}), flush=True)

@@ -23,6 +23,8 @@ UNARY_OPS = {"floor": 0, "ceil": 1, "round": 2, "-": 3, "tanh": 4, "logistic": 5
 TERNARY_OPS = {"select": 0}
 REDUCE_OPS = {"max": 0, "min": 1, "sum": 2, "mean": 3, "magnitude": 4, "magnitude-squared": 5}
 ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "tanh": 2, "logistic": 3}
+STREAM_OPTIONS = {"gemm-auto-presplit": 0, "presplit-variant": 1, "f64-simple-kernel": 2, "wait-limit-cycles": 3,
+                  "inject-fault": 4}
 
 
 class Dims(C.Structure):
@@ -64,6 +66,8 @@ SIGNATURES = {
     "cb200_free": [_i, _vp],
     "cb200_host_alloc": [_sz, C.POINTER(_vp)],
     "cb200_host_free": [_vp],
+    "cb200_host_alloc_near": [_i, _sz, C.POINTER(_vp), C.POINTER(_i)],
+    "cb200_device_numa_node": [_i, C.POINTER(_i)],
     "cb200_memcpy_h2d": [_vp, _vp, _vp, _sz],
     "cb200_memcpy_d2h": [_vp, _vp, _vp, _sz],
     "cb200_memcpy_d2d": [_vp, _vp, _vp, _sz],
@@ -112,6 +116,9 @@ SIGNATURES = {
     "cb200_split_lo": [_vp, _vp, _vp, _i64],
     "cb200_gemm_bias_act_presplit": [_vp, _vp, _vp, _i64, _d, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _d, _vp, _i],
     "cb200_bias_relu_rowstats": [_vp, _i, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp],
+    "cb200_stream_set_option": [_vp, _i, _i64],
+    "cb200_stream_workspace_info": [_vp, C.POINTER(_sz), C.POINTER(_i), C.POINTER(_i)],
+    "cb200_gemm_f32_variant": [_vp, _i, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d],
     "cb200_launch_count": [_vp],
     "cb200_stream_status": [_vp, C.POINTER(_i), C.POINTER(_i)],
     "cb200_last_error": [],
@@ -136,11 +143,6 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = _RESTYPE.get(name, _i)
-    # test hook, not in the public header
-    if hasattr(lib, "cb200_gemm_f32_variant"):
-        lib.cb200_gemm_f32_variant.argtypes = [_vp, _i, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64,
-                                               _i64, _d]
-        lib.cb200_gemm_f32_variant.restype = _i
     _lib = lib
     return lib
 

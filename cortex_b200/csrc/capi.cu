@@ -2,8 +2,15 @@
 // the reference's CudaDriver / CudaDevice / CudaStream records
 // (src/cortex/compute/cuda/driver.clj:725-733, 849-1045).
 #include "common.cuh"
+#include <ctype.h>
+#include <errno.h>
 #include <stdarg.h>
 #include <string.h>
+#include <sys/mman.h>
+#include <sys/syscall.h>
+#include <unistd.h>
+#include <map>
+#include <mutex>
 #include <new>
 
 static thread_local char g_err[1024] = "";
@@ -35,15 +42,34 @@ int cb200_check_dims(const cb200_dims* d, const char* what) {
   return CB200_OK;
 }
 
+// A per-stream block (workspace or tile flags) has to grow.  Kernels already enqueued, and graphs
+// captured on the stream, still hold the old address: while capturing nothing may be allocated at
+// all; with live graphs the old block is retired (freed with the stream); otherwise it is freed
+// once the stream has drained.
+static int release_for_growth(cb200_stream* s, void* old_block, const char* what) {
+  if (s->capture_start >= 0) {
+    cb200_set_error("%s has to grow while the stream is capturing: run the sequence once before capturing it", what);
+    return CB200_ERR_INVALID;
+  }
+  if (!old_block) return CB200_OK;
+  if (s->live_graphs && s->live_graphs->load() > 0) {
+    s->retired.push_back(old_block);
+    return CB200_OK;
+  }
+  CB_CUDA(cudaStreamSynchronize(s->stream));
+  CB_CUDA(cudaFree(old_block));
+  for (void* r : s->retired) cudaFree(r);      // no graph is left that could replay them
+  s->retired.clear();
+  return CB200_OK;
+}
+
 int cb200_scratch(cb200_stream* s, size_t bytes, void** out) {
   if (bytes > s->scratch_bytes) {
     DeviceGuard g(s->device);
-    if (s->scratch) {
-      CB_CUDA(cudaStreamSynchronize(s->stream));
-      CB_CUDA(cudaFree(s->scratch));
-      s->scratch = nullptr;
-      s->scratch_bytes = 0;
-    }
+    int rc = release_for_growth(s, s->scratch, "the stream's workspace");
+    if (rc) return rc;
+    s->scratch = nullptr;
+    s->scratch_bytes = 0;
     size_t want = (bytes + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
     CB_CUDA(cudaMalloc(&s->scratch, want));
     s->scratch_bytes = want;
@@ -55,12 +81,10 @@ int cb200_scratch(cb200_stream* s, size_t bytes, void** out) {
 int cb200_tile_flags(cb200_stream* s, size_t count, int** out) {
   if (count > s->tile_flags_count) {
     DeviceGuard g(s->device);
-    if (s->tile_flags) {
-      CB_CUDA(cudaStreamSynchronize(s->stream));
-      CB_CUDA(cudaFree(s->tile_flags));
-      s->tile_flags = nullptr;
-      s->tile_flags_count = 0;
-    }
+    int rc = release_for_growth(s, s->tile_flags, "the stream's tile-flag block");
+    if (rc) return rc;
+    s->tile_flags = nullptr;
+    s->tile_flags_count = 0;
     size_t want = (count + 4095) & ~(size_t)4095;
     CB_CUDA(cudaMalloc(&s->tile_flags, want * sizeof(int)));
     CB_CUDA(cudaMemsetAsync(s->tile_flags, 0, want * sizeof(int), s->stream));
@@ -118,11 +142,13 @@ int cb200_stream_create(int device, cb200_stream** out) {
   s->tile_flags_count = 0;
   s->launches.store(0);
   s->capture_start = -1;
+  s->live_graphs = std::make_shared<std::atomic<int>>(0);
+  s->opt_gemm_auto_presplit = s->opt_presplit_variant = s->opt_f64_simple = 0;
   cudaError_t e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, device);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&s->status_dev, 2 * sizeof(int));
-  if (e == cudaSuccess) e = cudaMemset(s->status_dev, 0, 2 * sizeof(int));
-  if (e == cudaSuccess) e = cudaMallocHost((void**)&s->status_host, 2 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc((void**)&s->status_dev, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(s->status_dev, 0, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&s->status_host, 4 * sizeof(int));
   if (e != cudaSuccess) { delete s; return cb200_cuda_fail(e, "stream_create", __FILE__, __LINE__); }
   s->status_host[0] = s->status_host[1] = 0;
   *out = s;
@@ -135,6 +161,7 @@ int cb200_stream_destroy(cb200_stream* s) {
   cudaStreamSynchronize(s->stream);
   if (s->scratch) cudaFree(s->scratch);
   if (s->tile_flags) cudaFree(s->tile_flags);
+  for (void* r : s->retired) cudaFree(r);
   cudaFree(s->status_dev);
   cudaFreeHost(s->status_host);
   cudaStreamDestroy(s->stream);
@@ -145,6 +172,46 @@ int cb200_stream_destroy(cb200_stream* s) {
 void* cb200_stream_native(cb200_stream* s) { return s ? (void*)s->stream : nullptr; }
 int cb200_stream_device(cb200_stream* s) { return s ? s->device : -1; }
 int64_t cb200_launch_count(cb200_stream* s) { return s ? s->launches.load() : 0; }
+
+int cb200_stream_set_option(cb200_stream* s, int option, int64_t value) {
+  CB_REQUIRE(s, "stream_set_option: null stream");
+  switch (option) {
+    case CB200_OPT_GEMM_AUTO_PRESPLIT:
+      CB_REQUIRE(value >= 0 && value <= 2, "stream_set_option: gemm routing %lld outside [0, 2]", (long long)value);
+      s->opt_gemm_auto_presplit = (int)value;
+      return CB200_OK;
+    case CB200_OPT_PRESPLIT_VARIANT:
+      CB_REQUIRE(value >= 0 && value <= 2, "stream_set_option: pre-split kernel %lld outside [0, 2]", (long long)value);
+      s->opt_presplit_variant = (int)value;
+      return CB200_OK;
+    case CB200_OPT_F64_SIMPLE_KERNEL:
+      s->opt_f64_simple = value != 0;
+      return CB200_OK;
+    case CB200_OPT_WAIT_LIMIT_CYCLES:
+    case CB200_OPT_INJECT_FAULT: {
+      CB_REQUIRE(value >= 0 && value < ((int64_t)1 << 40), "stream_set_option: value out of range");
+      CB_REQUIRE(s->capture_start < 0, "stream_set_option: not while capturing");
+      DeviceGuard g(s->device);
+      // stream-ordered: launches already enqueued keep the old setting
+      const int word = option == CB200_OPT_WAIT_LIMIT_CYCLES ? (int)((value + 1023) >> 10) : (int)value;
+      s->status_host[2] = word;      // staging only; the device copy is what kernels read
+      CB_CUDA(cudaMemcpyAsync(s->status_dev + (option == CB200_OPT_WAIT_LIMIT_CYCLES ? 2 : 3), &s->status_host[2],
+                              sizeof(int), cudaMemcpyHostToDevice, s->stream));
+      CB_CUDA(cudaStreamSynchronize(s->stream));
+      return CB200_OK;
+    }
+  }
+  cb200_set_error("stream_set_option: unknown option %d", option);
+  return CB200_ERR_INVALID;
+}
+
+int cb200_stream_workspace_info(cb200_stream* s, size_t* workspace_bytes, int* retired_blocks, int* live_graphs) {
+  CB_REQUIRE(s, "stream_workspace_info: null stream");
+  if (workspace_bytes) *workspace_bytes = s->scratch_bytes;
+  if (retired_blocks) *retired_blocks = (int)s->retired.size();
+  if (live_graphs) *live_graphs = s->live_graphs ? s->live_graphs->load() : 0;
+  return CB200_OK;
+}
 
 int cb200_stream_status(cb200_stream* s, int* code, int* detail) {
   CB_REQUIRE(s, "stream_status: null stream");
@@ -178,8 +245,75 @@ int cb200_host_alloc(size_t bytes, void** out) {
   return CB200_OK;
 }
 
+// NUMA node of the GPU's PCIe slot, from sysfs; -1 when the platform does not say
+static int device_numa_node(int device) {
+  char bus[32] = "";
+  if (cudaDeviceGetPCIBusId(bus, (int)sizeof(bus), device) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+  for (char* c = bus; *c; ++c) *c = (char)tolower(*c);
+  char path[128];
+  snprintf(path, sizeof(path), "/sys/bus/pci/devices/%s/numa_node", bus);
+  FILE* f = fopen(path, "r");
+  if (!f) return -1;
+  int node = -1;
+  if (fscanf(f, "%d", &node) != 1) node = -1;
+  fclose(f);
+  return node;
+}
+
+namespace {
+std::mutex g_near_mutex;
+std::map<void*, size_t> g_near_blocks;     // mmap'ed + registered blocks of cb200_host_alloc_near
+}
+
+int cb200_device_numa_node(int device, int* node) {
+  CB_REQUIRE(node, "device_numa_node: null out pointer");
+  *node = device_numa_node(device);
+  return CB200_OK;
+}
+
+int cb200_host_alloc_near(int device, size_t bytes, void** out, int* node_out) {
+  CB_REQUIRE(out, "host_alloc_near: null out pointer");
+  const int node = device_numa_node(device);
+  if (node_out) *node_out = -1;
+  if (node < 0 || node >= 1024) return cb200_host_alloc(bytes, out);
+  const size_t page = (size_t)sysconf(_SC_PAGESIZE);
+  const size_t len = ((bytes ? bytes : 1) + page - 1) / page * page;
+  void* p = mmap(nullptr, len, PROT_READ | PROT_WRITE, MAP_PRIVATE | MAP_ANONYMOUS, -1, 0);
+  if (p == MAP_FAILED) return cb200_host_alloc(bytes, out);
+  // MPOL_PREFERRED (1): pages come from `node` while it has room; set before the first touch
+  unsigned long mask[16] = {0};
+  mask[node / (8 * sizeof(unsigned long))] |= 1ul << (node % (8 * sizeof(unsigned long)));
+  const long bound = syscall(SYS_mbind, p, len, 1 /* MPOL_PREFERRED */, mask, (unsigned long)(8 * sizeof(mask)), 0u);
+  memset(p, 0, len);     // first touch: the pages exist, on the chosen node, before they are pinned
+  DeviceGuard g(device);
+  cudaError_t e = cudaHostRegister(p, len, cudaHostRegisterPortable);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    munmap(p, len);
+    return cb200_host_alloc(bytes, out);
+  }
+  {
+    std::lock_guard<std::mutex> lock(g_near_mutex);
+    g_near_blocks[p] = len;
+  }
+  if (node_out && bound == 0) *node_out = node;
+  *out = p;
+  return CB200_OK;
+}
+
 int cb200_host_free(void* ptr) {
   if (!ptr) return CB200_OK;
+  size_t len = 0;
+  {
+    std::lock_guard<std::mutex> lock(g_near_mutex);
+    auto it = g_near_blocks.find(ptr);
+    if (it != g_near_blocks.end()) { len = it->second; g_near_blocks.erase(it); }
+  }
+  if (len) {
+    CB_CUDA(cudaHostUnregister(ptr));
+    munmap(ptr, len);
+    return CB200_OK;
+  }
   CB_CUDA(cudaFreeHost(ptr));
   return CB200_OK;
 }
@@ -233,6 +367,8 @@ int cb200_graph_capture_end(cb200_stream* s, cb200_graph** out) {
     delete gr;
     return cb200_cuda_fail(err, "cudaGraphInstantiate", __FILE__, __LINE__);
   }
+  gr->live = s->live_graphs;        // from now on the stream's blocks are retired, not freed, when they grow
+  gr->live->fetch_add(1);
   *out = gr;
   return CB200_OK;
 }
@@ -252,6 +388,7 @@ int cb200_graph_destroy(cb200_graph* gr) {
   DeviceGuard g(gr->device);
   if (gr->exec) cudaGraphExecDestroy(gr->exec);
   if (gr->graph) cudaGraphDestroy(gr->graph);
+  if (gr->live) gr->live->fetch_sub(1);
   delete gr;
   return CB200_OK;
 }

@@ -6,13 +6,15 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <atomic>
+#include <memory>
+#include <vector>
 #include "../../include/cortex_b200.h"
 
 struct cb200_stream {
   int device;
   cudaStream_t stream;
   int sm_count;
-  int* status_dev;     // device status word pair {code, detail}; 0 = clean
+  int* status_dev;     // device words {code, detail, wait limit in cycles >> 10 (0 = default), injected fault bits}
   int* status_host;    // pinned mirror used by cb200_stream_status
   void* scratch;       // lazily grown per-stream device workspace
   size_t scratch_bytes;
@@ -20,6 +22,13 @@ struct cb200_stream {
   size_t tile_flags_count;
   std::atomic<int64_t> launches;
   int64_t capture_start;   // launch counter when the running capture began; -1 when not capturing
+  // Graphs captured on this stream hold the workspace / flag pointers of their launches as kernel
+  // arguments.  While any is alive a block that has to grow is retired (kept until the stream is
+  // destroyed) instead of freed.  The counter is shared with the graphs, which may outlive the stream.
+  std::shared_ptr<std::atomic<int>> live_graphs;
+  std::vector<void*> retired;
+  // per-stream routing options (cb200_stream_set_option); 0 = automatic
+  int opt_gemm_auto_presplit, opt_presplit_variant, opt_f64_simple;
 };
 
 // A captured sequence of this library's launches on one stream, replayable with one call.
@@ -28,6 +37,7 @@ struct cb200_graph {
   cudaGraph_t graph;
   cudaGraphExec_t exec;
   int64_t kernels;      // launches recorded while capturing (added to the stream's counter per replay)
+  std::shared_ptr<std::atomic<int>> live;   // the capturing stream's live-graph counter
 };
 
 struct cb200_event {

@@ -9,9 +9,9 @@
 // whole batch is ONE GEMM with the output pixels as the M dimension and an
 // epilogue that scatters [pixel, channel] tiles straight into NCHW.
 //   fp32: conv_igemm.cu gathers the unrolled rows directly into the tensor-core
-//         operand tiles; nothing is materialised and no scratch memory is used.
-//         (Weights whose row length is not a multiple of 4, or an unaligned
-//         weight pointer, take the explicit path below with the SIMT GEMM.)
+//         operand tiles; the unrolled matrix is never materialised.  The only
+//         scratch memory it takes from the stream is for re-ordered / zero-padded
+//         hi and lo copies of the WEIGHTS (2 * C_out * K floats).
 //   fp64: explicit im2col into the stream's scratch buffer, then one DMMA GEMM
 //         per image as the reference does.
 // The caller's workspace tensor is not used by either.
@@ -138,8 +138,8 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
 // ---------------------------------------------------------------------------------------------
 // convolution-forward! for callers that must not allocate.
 //
-// cb200_convolution_forward unrolls the input into a per-stream scratch buffer that it grows with
-// cudaMalloc on demand.  Some hosts of this library cannot tolerate that: a serving loop that has
+// cb200_convolution_forward takes scratch memory from a per-stream buffer that it grows with
+// cudaMalloc on demand (fp64: the unrolled input; fp32: split copies of the weights).  Some hosts of this library cannot tolerate that: a serving loop that has
 // handed all device memory to its own pool, a process that forbids the implicit device-wide
 // synchronisation of cudaMalloc / cudaFree on its latency path, or code that runs between two
 // points where allocation is simply not allowed.  This variant keeps the unrolled matrix in a
@@ -219,6 +219,7 @@ int cb200_convolution_forward_static(cb200_stream* s, int dtype, void* out, cons
   if (rows == 0 || cout == 0) return CB200_OK;
   const size_t es = dtype == CB200_FLOAT ? 4 : 8;
   const long long total = rows * g.ld;
+  if (total == 0) return CB200_OK;
   CB_REQUIRE((unsigned long long)total * es <= CB200_STATIC_CONV_SCRATCH_BYTES,
              "convolution_forward_static: the unrolled input needs %lld bytes but the static scratch array holds %llu; "
              "use cb200_convolution_forward (which allocates) for this size",

@@ -269,12 +269,7 @@ gemm_f64_kernel(double* C, long long ldc, const double* A, long long sam, long l
   }
 }
 
-bool g_force_simple = false;     // test hook: route aligned operands to the register-staged kernel too
-
 }  // namespace
-
-// test hook (not in the public header): 1 = always use the register-staged m8n8k4 kernel
-extern "C" int cb200_gemm_f64_force_simple(int on) { g_force_simple = on != 0; return CB200_OK; }
 
 int cb200_gemm_f64_launch(cb200_stream* s, double* C, long long ldc, int trans_a, int trans_b, double alpha,
                           const double* A, int M, int K, long long lda, const double* B, int N, long long ldb,
@@ -284,7 +279,7 @@ int cb200_gemm_f64_launch(cb200_stream* s, double* C, long long ldc, int trans_a
   if (peer_list) peers = *peer_list; else peers.n = 0;
   dim3 grid((N + DBN - 1) / DBN, (M + DBM - 1) / DBM);
   const bool aligned = (((uintptr_t)A | (uintptr_t)B) & 15) == 0 && (lda % 2) == 0 && (ldb % 2) == 0;
-  if (aligned && !g_force_simple) {
+  if (aligned && !s->opt_f64_simple) {
     static std::once_flag once[64];
     cudaError_t attr_err = cudaSuccess;
     std::call_once(once[s->device & 63], [&] {

@@ -99,15 +99,18 @@ gemm_presplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int row0 = is_a ? m0 : n0;
       int issued = 0, s = 0;
       uint32_t ph = 0;
+      const bool withhold = (p.status[3] & 1) != 0;     // host-injected fault: arm nothing, load nothing
       for (int i = 0; i < nkb; ++i) {
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 100 + s)) break;
         const uint32_t full = bar_full + 8 * s;
         const uint32_t dst = smem_base + s * STAGE + tile_off;
         const int k0 = (kb_begin + i) * BK;
-        mbar_arrive_expect_tx(full, bytes);
-        tma_load_2d(dst, hi_map, k0, row0, full);
-        tma_load_2d(dst + RAW, lo_map, k0, row0, full);
-        issued = i + 1;
+        if (!withhold) {
+          mbar_arrive_expect_tx(full, bytes);
+          tma_load_2d(dst, hi_map, k0, row0, full);
+          tma_load_2d(dst + RAW, lo_map, k0, row0, full);
+          issued = i + 1;
+        }
         if (++s == STAGES) { s = 0; ph ^= 1; }
       }
       if (*abort_flag) {
@@ -193,7 +196,7 @@ gemm_presplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         for (;;) {
           asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
           if (seen != 0 || *abort_flag) break;
-          if (clock64() - t0 > SM100_WAIT_LIMIT_CYCLES) {
+          if (clock64() - t0 > wait_limit(p.status)) {
             *abort_flag = 1;
             if (atomicCAS(p.status, 0, 4 /* CB200_ERR_TIMEOUT */) == 0) p.status[1] = 450;
             break;
@@ -286,7 +289,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     if (mbar_try_wait_cluster(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > SM100_WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > wait_limit(status)) {
         *abort_flag = 1;
         if (atomicCAS(status, 0, 4 /* CB200_ERR_TIMEOUT */) == 0) status[1] = site;
         return false;
@@ -421,7 +424,8 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   // bars[0..S) full (the leader's copy is used: its two producers arrive, both CTAs' loads complete bytes),
   // [S..2S) empty, [2S] accumulators may be read out (each CTA's own copy), [2S+1] accumulators have been read
   // out (the leader's copy is used: one arrival per epilogue warp of both CTAs)
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * P_STAGES + 2);
+  // [2S+2] used only when unwinding after a timeout: "every MMA issued so far has retired"
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * P_STAGES + 3);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -441,7 +445,7 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + P_STAGES),
-                 bar_mid = smem_u32(bars + 2 * P_STAGES), bar_drained = bar_mid + 8;
+                 bar_mid = smem_u32(bars + 2 * P_STAGES), bar_drained = bar_mid + 8, bar_retired = bar_mid + 16;
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 2);
@@ -449,6 +453,7 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     }
     mbar_init(bar_mid, 1);
     mbar_init(bar_drained, 2 * EPI_WARPS);
+    mbar_init(bar_retired, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -477,6 +482,7 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      const bool withhold = (p.status[3] & 1) != 0;     // host-injected fault: arm nothing, load nothing
       for (int tile = cluster_id; ok && tile < n_tiles; tile += n_clusters) {
         int m0, n0;
         tile_origin(tile, m0, n0);
@@ -485,10 +491,12 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
           if (!mbar_wait_cluster(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) { ok = false; break; }
           const uint32_t dst = smem_base + s * P_STAGE + tile_off;
           const int k0 = i * BK;
-          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, bytes);
-          tma_load_2d_pair(dst, hi_map, k0, row0, leader_full + 8 * s);
-          tma_load_2d_pair(dst + P_RAW, lo_map, k0, row0, leader_full + 8 * s);
-          ++issued;
+          if (!withhold) {
+            if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, bytes);
+            tma_load_2d_pair(dst, hi_map, k0, row0, leader_full + 8 * s);
+            tma_load_2d_pair(dst + P_RAW, lo_map, k0, row0, leader_full + 8 * s);
+            ++issued;
+          }
           if (++s == P_STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -555,8 +563,11 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         pending_read_out = true;
       }
       if (*abort_flag) {
-        for (int spin = 0; spin < (1 << 16); ++spin)
-          if (mbar_try_wait(bar_mid, 0) || mbar_try_wait(bar_mid, 1)) break;
+        // TMEM is freed after the closing cluster barrier: every MMA of the pair issued above must have
+        // retired by then.  A commit on a barrier nothing else uses says exactly that (bounded poll).
+        mma_commit_pair(bar_retired);
+        for (int spin = 0; spin < (1 << 20); ++spin)
+          if (mbar_try_wait(bar_retired, 0)) break;
       }
     }
   } else {
@@ -625,8 +636,6 @@ int kmajor_tmap(CUtensorMap* tm, const float* base, long long rows, long long co
   return CB200_OK;
 }
 
-int g_force_variant = 0;     // test hook, see cb200_gemm_presplit_force_variant
-
 // lo = x - trunc_tf32(x), elementwise over a dense span
 __global__ void __launch_bounds__(256) split_lo_kernel(float* lo, const float* x, long long n) {
   const long long n4 = n / 4;
@@ -678,8 +687,6 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(float* hi, float* 
     }
   }
 }
-
-int g_gemm_auto_mode = 0;    // test hook, see cb200_gemm_auto_presplit_mode
 
 // The launch itself: operands as (hi, lo) pairs with their own pitches.
 int launch_presplit(cb200_stream* s, float* C, float* C_lo, long long ldc, float alpha, const float* A_hi,
@@ -756,11 +763,11 @@ int launch_presplit(cb200_stream* s, float* C, float* C_lo, long long ldc, float
 // gemm! / gemm_bias_act through the pre-split pair kernel: worth it when the problem fills the GPU with
 // 256 x 256 pair tiles and the split copies fit a bounded per-stream workspace.
 bool cb200_gemm_presplit_auto_ok(cb200_stream* s, int M, int N, int K, int trans_a, int trans_b) {
-  if (g_gemm_auto_mode == 1) return false;
+  if (s->opt_gemm_auto_presplit == 1) return false;
   const long long kp = (K + 3) / 4 * 4;
   const long long floats = (long long)M * kp * (trans_a ? 2 : 1) + (long long)N * kp * (trans_b ? 1 : 2);
   if (floats * 4 > (2ll << 30)) return false;
-  if (g_gemm_auto_mode == 2) return true;
+  if (s->opt_gemm_auto_presplit == 2) return true;
   const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return M > BM && tiles >= s->sm_count && K >= 256;
 }
@@ -801,14 +808,10 @@ int cb200_gemm_presplit_auto_launch(cb200_stream* s, float* C, long long ldc, in
   if (!trans_b) { split_t(b_hi, b_lo, B, ldb, N); b_hi_p = b_hi; b_hi_ld = kp; } else { split_rows(b_lo, B, ldb, N); }
   CB_LAUNCH_CHECK(s);
   return launch_presplit(s, C, nullptr, ldc, alpha, a_hi_p, a_hi_ld, a_lo, kp, M, K, b_hi_p, b_hi_ld, b_lo, kp, N, beta,
-                         bias, act, g_gemm_auto_mode == 2 ? 2 : 0);
+                         bias, act, s->opt_gemm_auto_presplit == 2 ? 2 : 0);
 }
 
 extern "C" {
-
-// Test hook: 0 = gemm! takes the pre-split path by problem size (default), 1 = never, 2 = whenever TMA can
-// address the operands (on CTA pairs).
-int cb200_gemm_auto_presplit_mode(int mode) { g_gemm_auto_mode = mode; return CB200_OK; }
 
 int cb200_split_lo(cb200_stream* s, void* lo, const void* x, int64_t n_elems) {
   CB_REQUIRE(s && lo && x && n_elems >= 0, "split_lo: bad argument");
@@ -835,10 +838,7 @@ int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t l
   CB_REQUIRE(act >= CB200_ACT_NONE && act <= CB200_ACT_LOGISTIC, "gemm_bias_act_presplit: unknown activation %d", act);
   return launch_presplit(s, (float*)C, (float*)C_lo, ldc, (float)alpha, (const float*)A_hi, lda, (const float*)A_lo, lda,
                          (int)a_rows, (int)a_cols, (const float*)B_hi, ldb, (const float*)B_lo, ldb, (int)b_rows,
-                         (float)beta, (const float*)bias, act, g_force_variant);
+                         (float)beta, (const float*)bias, act, s->opt_presplit_variant);
 }
-
-// Test hook: 0 = choose by problem size (default), 1 = always the single-CTA kernel, 2 = always CTA pairs.
-int cb200_gemm_presplit_force_variant(int variant) { g_force_variant = variant; return CB200_OK; }
 
 }  // extern "C"

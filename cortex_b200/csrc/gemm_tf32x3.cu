@@ -134,11 +134,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       int issued = 0;
       int s = 0;
       uint32_t ph = 0;
+      const bool withhold = (p.status[3] & 1) != 0;     // host-injected fault: arm nothing, load nothing
       for (int i = 0; i < nkb; ++i) {
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 100 + s)) break;
         const uint32_t full = bar_full + 8 * s;
         const uint32_t a_dst = smem_base + s * Cfg::STAGE, b_dst = a_dst + A_TILE;
         const int k0 = (kb_begin + i) * BK;
+        if (withhold) {
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+          continue;
+        }
         if (!PROD_WHOLE || elect_one()) {
           mbar_arrive_expect_tx(full, Cfg::RAW);
           if (!p.a_mn_major) {
@@ -284,7 +289,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (;;) {
           asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
           if (seen != 0 || *abort_flag) break;
-          if (clock64() - t0 > SM100_WAIT_LIMIT_CYCLES) {
+          if (clock64() - t0 > wait_limit(p.status)) {
             *abort_flag = 1;
             if (atomicCAS(p.status, 0, 4 /* CB200_ERR_TIMEOUT */) == 0) p.status[1] = 450;
             break;

@@ -73,6 +73,12 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // false when the wait ran out; status[0] / status[1] (global) get the code and
 // the site of the first failure.
 #define SM100_WAIT_LIMIT_CYCLES (4000000000LL)   /* ~2 s at 2 GHz */
+// status[2], when non-zero, replaces the limit (in units of 1024 cycles): a per-stream setting the host
+// writes before the launch.  Read only on the slow path of a wait (every 64th failed poll).
+__device__ __forceinline__ long long wait_limit(const int* status) {
+  const int k = status[2];
+  return k > 0 ? ((long long)k << 10) : SM100_WAIT_LIMIT_CYCLES;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int site) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -81,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > SM100_WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > wait_limit(status)) {
         *abort_flag = 1;
         if (atomicCAS(status, 0, 4 /* CB200_ERR_TIMEOUT */) == 0) status[1] = site;
         return false;

@@ -195,6 +195,15 @@ class B200Stream(CTensorMath):
     def native_handle(self):
         return _lib.load().cb200_stream_native(self.handle)
 
+    def set_option(self, name, value):
+        """A per-stream routing / diagnostic option (cb200_stream_set_option): see _lib.STREAM_OPTIONS."""
+        call("cb200_stream_set_option", self.handle, _lib.STREAM_OPTIONS[name], int(value))
+
+    def workspace_info(self):
+        b, r, g = C.c_size_t(), C.c_int(), C.c_int()
+        call("cb200_stream_workspace_info", self.handle, C.byref(b), C.byref(r), C.byref(g))
+        return {"bytes": b.value, "retired-blocks": r.value, "live-graphs": g.value}
+
     def launch_count(self):
         return int(_lib.load().cb200_launch_count(self.handle))
 
@@ -274,12 +283,20 @@ class B200Driver:
             raise _lib.B200Error(3, "no CUDA device is visible")
         return devs[0]
 
-    def allocate_host_buffer(self, elem_count, elem_type, usage_type="one-time"):
+    def allocate_host_buffer(self, elem_count, elem_type, usage_type="one-time", near=None):
+        """Page-locked host memory.  `near` (a device) places it on the NUMA node of that GPU's PCIe slot;
+        the buffer's `numa_node` attribute then says which (-1: unknown / not bound)."""
         if usage_type not in ("one-time", "reusable"):
             raise ValueError("Usage type is not in expected set")
         p = C.c_void_p()
-        call("cb200_host_alloc", int(elem_count) * DTYPE_SIZE[elem_type], C.byref(p))
-        return Buffer(p.value, elem_type, elem_count, None, host=True)
+        node = C.c_int(-1)
+        if near is not None:
+            call("cb200_host_alloc_near", near.index, int(elem_count) * DTYPE_SIZE[elem_type], C.byref(p), C.byref(node))
+        else:
+            call("cb200_host_alloc", int(elem_count) * DTYPE_SIZE[elem_type], C.byref(p))
+        buf = Buffer(p.value, elem_type, elem_count, None, host=True)
+        buf.numa_node = node.value
+        return buf
 
 
 _driver = None

@@ -35,7 +35,7 @@ def biased_multiply(input, weights, bias, output):
 def biased_multiply_backward(input, weights, bias, output, input_gradient, weight_gradient, bias_gradient,
                              output_gradient):
     """bias-gradient += sum over the batch of output-gradient (binary-op! with a destination smaller than the
-    operation: compare-and-swap accumulation); input-gradient = output-gradient . weights (gemm! NN, beta 0);
+    operation: the reference accumulates with compare-and-swap, this backend with a slab sum); input-gradient = output-gradient . weights (gemm! NN, beta 0);
     weight-gradient += output-gradient^T . input (gemm! TN, beta 1).  Any of the three gradients may be None."""
     if bias_gradient is not None:
         ct.binary_op(bias_gradient, 1.0, output_gradient, 1.0, bias_gradient, "+")

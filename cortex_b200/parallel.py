@@ -54,30 +54,49 @@ def _as_torch(buffer, shape):
     return torch.as_tensor(holder, device="cuda:%d" % buffer.device.index)
 
 
+_external_streams = {}
+
+
+def _external(stream):
+    """The backend stream as a torch stream (cached per stream handle), so that a torch.distributed
+    collective can be enqueued ON it: ordered after the kernels already there, before the ones that
+    follow, with no host synchronisation on either side."""
+    import torch
+    key = (stream.device.index, stream.native_handle())
+    ext = _external_streams.get(key)
+    if ext is None:
+        ext = torch.cuda.ExternalStream(key[1], device=torch.device("cuda", key[0]))
+        _external_streams[key] = ext
+    return ext
+
+
 def all_gather_buffers(local, gathered, world_size, group=None):
-    """gathered[r] = rank r's `local` (both backend tensors, dense).  One collective."""
+    """gathered[r] = rank r's `local` (both backend tensors, dense).  One collective, enqueued on the
+    backend's own stream (NCCL), or run on the host after a stream sync (gloo, CPU tests)."""
     import torch.distributed as dist
     stream = ct.check_stream()
     n = local.ecount()
     src = _as_torch(local.buffer, [n])
     dst = _as_torch(gathered.buffer, [world_size * n])
-    stream.sync()                      # the producer kernels run on the backend's own stream
     if dst.is_cuda:
         import torch
-        dist.all_gather_into_tensor(dst, src, group=group)
-        torch.cuda.synchronize(dst.device)
+        with torch.cuda.stream(_external(stream)):
+            dist.all_gather_into_tensor(dst, src, group=group)
     else:
+        stream.sync()                  # host collective: the producers must have finished
         parts = [dst[r * n:(r + 1) * n] for r in range(world_size)]
         dist.all_gather(parts, src, group=group)
     return gathered
 
 
-def column_sharded_head(h, w_shard, b_shard, n_total, world_size, rank, group=None):
+def column_sharded_head(h, w_shard, b_shard, n_total, world_size, rank, group=None, workspace=None):
     """softmax(h . W^T + b) where W[n_total, k] is split by output column across ranks.
 
     h        [B, k]            this rank's (replicated or gathered) activations
     w_shard  [n_total/g, k]    this rank's rows of W
     b_shard  [n_total/g]
+    workspace  a dict the caller keeps between calls: the three intermediate tensors are then allocated
+               once per shape instead of per call (allocation synchronises the device)
     returns  [B, n_total]      dense probabilities, identical on every rank
     """
     if n_total % world_size:
@@ -85,13 +104,19 @@ def column_sharded_head(h, w_shard, b_shard, n_total, world_size, rank, group=No
     B = h.shape()[0]
     per = n_total // world_size
     dt = h.get_datatype()
-    local = ct.new_tensor([B, per], datatype=dt, init_value=None)
+    bufs = workspace if workspace is not None else {}
+    key = (B, per, world_size, dt)
+    if bufs.get("key") != key:
+        bufs.clear()
+        bufs["key"] = key
+        bufs["local"] = ct.new_tensor([B, per], datatype=dt, init_value=None)
+        bufs["gathered"] = ct.new_tensor([world_size, B, per], datatype=dt, init_value=None)
+        bufs["logits"] = ct.new_tensor([B, world_size, per], datatype=dt, init_value=None)
+    local, gathered, logits = bufs["local"], bufs["gathered"], bufs["logits"]
     ct.assign(local, b_shard)
     ct.gemm(local, False, True, 1.0, h, w_shard, 1.0)
-    gathered = ct.new_tensor([world_size, B, per], datatype=dt, init_value=None)
     all_gather_buffers(local, gathered, world_size, group)
     view = ct.Tensor(gathered.device, {"shape": [B, world_size, per], "strides": [per, B * per, 1]}, gathered.buffer)
-    logits = ct.new_tensor([B, world_size, per], datatype=dt, init_value=None)
     ct.assign(logits, view)                                   # strided gather through the index system
     logits2d = ct.in_place_reshape(logits, [B, n_total])
     return ct.softmax(logits2d, logits2d)
@@ -131,7 +156,12 @@ def column_sharded_head_fused(h, w_shard, b_shard, exchange, fence):
     """column_sharded_head without the all-gather and the re-layout: ONE fused kernel computes this
     rank's logits window (bias added in the epilogue) and stores it into every rank's full logits
     buffer over NVLink; `fence()` must then order all ranks (every rank's kernel finished) before
-    softmax! runs on the local full buffer.  Returns the [B, n_total] probabilities tensor."""
+    softmax! runs on the local full buffer.  Returns the [B, n_total] probabilities tensor.
+
+    softmax! runs IN PLACE on the buffer the peers store into.  Before this function is called again
+    with the same `exchange`, the caller must issue one more `fence()` after it has consumed the
+    probabilities: otherwise a faster rank's next GEMM overwrites this rank's logits while its softmax
+    (or its reader) is still on them."""
     stream = ct.check_stream()
     B, k = h.shape()
     per, n_total = exchange.per, exchange.n_total
@@ -149,7 +179,7 @@ def stream_fence(stream, group=None):
     (and their peer stores) are complete.  No host synchronisation."""
     import torch
     import torch.distributed as dist
-    ext = torch.cuda.ExternalStream(stream.native_handle(), device=torch.device("cuda", stream.device.index))
+    ext = _external(stream)
     token = torch.zeros(1, device=ext.device, dtype=torch.float32)
 
     def fence():
@@ -157,16 +187,3 @@ def stream_fence(stream, group=None):
             dist.all_reduce(token, group=group)
 
     return fence
-
-
-class ShardedMLP:
-    """Batch-sharded inference: this rank's slice of the batch through a replicated network."""
-
-    def __init__(self, net, world_size, rank):
-        self.net, self.world_size, self.rank = net, world_size, rank
-
-    def local_rows(self, global_batch):
-        return shard_bounds(global_batch, self.world_size, self.rank)
-
-    def infer_local(self, x_local):
-        return self.net.infer(x_local)

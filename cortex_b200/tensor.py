@@ -9,6 +9,7 @@ stream object is bound with :func:`with_stream` (the B200 stream in production).
 """
 import contextlib
 import math
+import threading
 
 import numpy as np
 
@@ -16,8 +17,14 @@ from . import dimensions as dims
 from .dimensions import ALL, DimensionError  # noqa: F401  (re-exported)
 from ._lib import NUMPY_NAME
 
-_stream = None
-_datatype = "double"          # ct/*datatype* defaults to :double (tensor.clj:106)
+class _Bindings(threading.local):
+    """ct/*stream* and ct/*datatype* are Clojure dynamic vars: bindings are per thread, which is what lets
+    N host threads drive N streams of one device at once (src/cortex/verify/nn/train.clj:211-236)."""
+    stream = None
+    datatype = "double"       # ct/*datatype* defaults to :double (tensor.clj:106)
+
+
+_bound = _Bindings()
 
 UNARY_OPERATIONS = ["floor", "ceil", "round", "-", "tanh", "logistic", "exp", "sqrt", "noop"]
 BINARY_OPERATIONS = ["+", "-", "*", "/", "max", "min", "bit-and", "bit-xor", "eq", ">", ">=", "<", "<="]
@@ -36,27 +43,25 @@ def _require(cond, msg, data=None):
 @contextlib.contextmanager
 def with_stream(stream):
     """ct/with-stream (tensor.clj:91-100)."""
-    global _stream
-    prev, _stream = _stream, stream
+    prev, _bound.stream = _bound.stream, stream
     try:
         yield stream
     finally:
-        _stream = prev
+        _bound.stream = prev
 
 
 @contextlib.contextmanager
 def with_datatype(datatype):
-    global _datatype
-    prev, _datatype = _datatype, datatype
+    prev, _bound.datatype = _bound.datatype, datatype
     try:
         yield
     finally:
-        _datatype = prev
+        _bound.datatype = prev
 
 
 def check_stream():
-    _require(_stream is not None, "Stream is nil. Use with_stream to bind a stream.")
-    return _stream
+    _require(_bound.stream is not None, "Stream is nil. Use with_stream to bind a stream.")
+    return _bound.stream
 
 
 def dtype_cast(value, datatype):
@@ -217,7 +222,7 @@ def _index_value(tensor, i):
 
 def to_tensor(data, datatype=None):
     """->tensor (tensor.clj:415-435): upload nested sequence / array data."""
-    datatype = datatype or _datatype
+    datatype = datatype or _bound.datatype
     stream = check_stream()
     arr = np.ascontiguousarray(np.asarray(data), dtype=NUMPY_NAME[datatype])
     n = int(arr.size)
@@ -234,7 +239,7 @@ def to_tensor(data, datatype=None):
 
 def new_tensor(shp, datatype=None, init_value=0):
     """new-tensor (tensor.clj:438-450)."""
-    datatype = datatype or _datatype
+    datatype = datatype or _bound.datatype
     shp = [int(s) for s in shp]
     stream = check_stream()
     device = stream.get_device()

@@ -17,8 +17,9 @@
  *     destination before use (drv/dtype-cast, src/cortex/compute/cuda/tensor_math.clj:293).
  *   - Nothing here aborts the process or traps on the device.
  *   - The stream handle carries its device; there is no process-global
- *     "current device / current stream" state, so N host threads x N streams
- *     are safe (src/cortex/verify/nn/train.clj:211-236 is the usage model).
+ *     "current device / current stream" state and no process-global option:
+ *     N host threads x N streams are safe (src/cortex/verify/nn/train.clj:211-236
+ *     is the usage model).  One stream is driven by one thread at a time.
  */
 #ifndef CORTEX_B200_H
 #define CORTEX_B200_H
@@ -119,6 +120,14 @@ int cb200_free(int device, void* ptr);
 /* allocate-host-buffer-impl (page-locked: src/cortex/compute/cuda/driver.clj:522-542) */
 int cb200_host_alloc(size_t bytes, void** out);
 int cb200_host_free(void* ptr);
+/* The same page-locked buffer placed on the NUMA node the GPU's PCIe slot hangs off (pages bound and
+ * touched before they are pinned), so that uploads to that GPU do not cross the socket interconnect:
+ * with one process per GPU, eight uploads otherwise compete for one node's memory channels.  *node
+ * gets the node used, or -1 when the platform does not report one (then this is cb200_host_alloc).
+ * Staging buffers of the reference: allocate-host-buffer-impl, src/cortex/compute/cuda/driver.clj:522-542;
+ * the upload path they feed: src/cortex/nn/execute.clj:387-434.  Free with cb200_host_free. */
+int cb200_host_alloc_near(int device, size_t bytes, void** out, int* node);
+int cb200_device_numa_node(int device, int* node);
 
 /* ---- PStream / PEvent (src/cortex/compute/driver.clj:180-203) ------------ */
 /* copy-host->device / copy-device->host / copy-device->device (sizes in bytes) */
@@ -274,9 +283,8 @@ typedef struct cb200_pool_desc {
 int cb200_pooling_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, double out_alpha,
                           const void* in, const cb200_dims* in_dims, const cb200_pool_desc* desc);
 
-/* Protocol methods outside the dense-inference path return CB200_ERR_UNSUPPORTED:
- * batch-normalize-update-*, batch-normalize-gradients-*, activation-gradient!, convolution-backward-*,
- * pooling-backward!, rand!, lrn-* (src/cortex/tensor/math.clj:125-175, 205-250). */
+/* Protocol methods this backend does not implement return CB200_ERR_UNSUPPORTED through this call:
+ * lrn-forward! / lrn-backward! (src/cortex/tensor/math.clj:239-250). */
 int cb200_unsupported(const char* method_name);
 
 /* ---- fused extras (no counterpart in the protocol) -------------------------
@@ -292,8 +300,12 @@ int cb200_gemm_bias_act(cb200_stream* s, int dtype, void* C, int64_t ldc, int tr
  * microseconds each): everything enqueued on `s` by this library between capture_begin and
  * capture_end is recorded instead of run, and replayed by ONE cb200_graph_launch.  Rules: run the
  * sequence once normally first (scratch buffers and kernel attributes are set up on first use and
- * must not be created while capturing); no sync / event_wait / malloc / free between begin and end;
- * the graph replays the same buffers, shapes and scalars; destroy it before freeing those buffers. */
+ * must not be created while capturing: a call that would have to grow them returns CB200_ERR_INVALID);
+ * no sync / event_wait / malloc / free between begin and end; the graph replays the same buffers, shapes
+ * and scalars; destroy it before freeing those buffers and before destroying the stream it was captured
+ * on.  The graph also replays the stream's internal workspace addresses: while a graph captured on a
+ * stream is alive, a workspace that has to grow is replaced without freeing the old block (it is released
+ * with the stream), so earlier graphs stay valid. */
 int cb200_graph_capture_begin(cb200_stream* s);
 int cb200_graph_capture_end(cb200_stream* s, cb200_graph** out);
 int cb200_graph_launch(cb200_graph* g, cb200_stream* s);
@@ -341,6 +353,30 @@ int cb200_gemm_bias_act_presplit(cb200_stream* s, void* C, void* C_lo, int64_t l
 int cb200_bias_relu_rowstats(cb200_stream* s, int dtype, void* Y, int64_t ldy, const void* X,
                              int64_t ldx, const void* bias, int64_t rows, int64_t cols,
                              void* rowmax, void* rowsum);
+
+/* ---- diagnostics (no counterpart in the protocol) -----------------------------------
+ * Per-stream options; nothing here is process-global.  They exist so that every kernel behind one entry
+ * point can be parity-tested at sizes the automatic choice would route elsewhere, and so that the
+ * bounded device-side waits can be made to run out without faulting the GPU. */
+enum cb200_stream_option {
+  CB200_OPT_GEMM_AUTO_PRESPLIT = 0, /* gemm!: 0 = split-into-workspace + CTA-pair kernel by problem size,
+                                       1 = never, 2 = whenever TMA can address the operands */
+  CB200_OPT_PRESPLIT_VARIANT = 1,   /* gemm_bias_act_presplit: 0 = by size, 1 = single-CTA tiles, 2 = CTA pairs */
+  CB200_OPT_F64_SIMPLE_KERNEL = 2,  /* fp64 gemm!: 1 = always the register-staged kernel */
+  CB200_OPT_WAIT_LIMIT_CYCLES = 3,  /* limit of every bounded device-side wait, in SM cycles (0 = default, ~2 s) */
+  CB200_OPT_INJECT_FAULT = 4        /* bit 0: the TMA producers of the fp32 tensor-core GEMM issue no loads, so
+                                       the consumers' waits run out -> CB200_ERR_TIMEOUT from cb200_stream_sync.
+                                       The failure is made on the host side of the barrier protocol; the kernel
+                                       unwinds through its normal abort path (no trap, no bad address). */
+};
+int cb200_stream_set_option(cb200_stream* s, int option, int64_t value);
+/* bytes of the stream's workspace, blocks retired because a live graph may still replay them, live graphs */
+int cb200_stream_workspace_info(cb200_stream* s, size_t* workspace_bytes, int* retired_blocks, int* live_graphs);
+/* One fp32 gemm! on a named kernel: which = 0 the SIMT kernel, 1 the tcgen05 kernel with `flags`
+ * (1 = single tf32 term: no hi/lo split, which exposes how the tensor core reads an fp32 word). */
+int cb200_gemm_f32_variant(cb200_stream* s, int which, int flags, void* C, int64_t ldc, int trans_a, int trans_b,
+                           double alpha, const void* A, int64_t a_rows, int64_t a_cols, int64_t lda, const void* B,
+                           int64_t b_cols, int64_t ldb, double beta);
 
 /* number of kernels this library has launched on the stream since creation */
 int64_t cb200_launch_count(cb200_stream* s);

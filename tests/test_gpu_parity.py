@@ -13,8 +13,10 @@ from cortex_b200 import tensor as ct
 pytestmark = pytest.mark.gpu
 
 
-def _on(driver, datatype, fn):
+def _on(driver, datatype, fn, options=None):
     stream = driver.default_device().create_stream()
+    for name, value in (options or {}).items():
+        stream.set_option(name, value)
     with ct.with_stream(stream), ct.with_datatype(datatype):
         out = fn()
     stream.sync()
@@ -48,29 +50,18 @@ def test_gemm_matches_oracle(b200_driver, oracle_driver, datatype, ta, tb, shape
         assert pc.rel_err(gpu, ref64()) <= pc.TOL[datatype], (alpha, beta)
 
 
-@pytest.fixture
-def gemm_auto_presplit():
-    """gemm! routing hook: 2 = take the split-into-workspace + CTA-pair kernel path whenever TMA can address
-    the operands, 1 = never; back to the size-based choice afterwards."""
-    from cortex_b200 import _lib
-    hook = _lib.load().cb200_gemm_auto_presplit_mode
-    hook.argtypes, hook.restype = [ctypes.c_int], ctypes.c_int
-    yield hook
-    hook(0)
-
-
 @pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)],
                          ids=["NN", "NT", "TN", "TT"])
 @pytest.mark.parametrize("shape", GEMM_SHAPES + [(700, 520, 4200, 8, 4)], ids=lambda s: "x".join(map(str, s)))
-def test_gemm_through_presplit_pair_path(b200_driver, oracle_driver, gemm_auto_presplit, ta, tb, shape):
+def test_gemm_through_presplit_pair_path(b200_driver, oracle_driver, ta, tb, shape):
     """gemm! forced onto the path large problems take: operands split (MN-major ones also transposed) into
     the stream's workspace, then the CTA-pair kernel.  Same cases and bounds as test_gemm_matches_oracle,
-    whole backing buffer compared (the frame around a pitched window stays untouched)."""
-    gemm_auto_presplit(2)
+    whole backing buffer compared (the frame around a pitched window stays untouched).  The routing is a
+    per-stream option: 2 = take that path whenever TMA can address the operands."""
     m, n, k, pad, off = shape
     for alpha, beta in ((1.5, 0.5), (1.0, 0.0), (1.0, 1.0)):
         run, ref64 = pc.gemm_case("float", m, n, k, ta, tb, alpha, beta, pad, off)
-        gpu = _on(b200_driver, "float", run)
+        gpu = _on(b200_driver, "float", run, {"gemm-auto-presplit": 2})
         cpu = _on(oracle_driver, "float", run)
         assert pc.rel_err(gpu, cpu) <= pc.TOL["float"], (alpha, beta)
         assert pc.rel_err(gpu, ref64()) <= pc.TOL["float"], (alpha, beta)
@@ -147,7 +138,7 @@ def test_mlp_backward_matches_oracle(b200_driver, oracle_driver, datatype, act):
 
 @pytest.mark.parametrize("datatype", ["float", "double"])
 def test_conv_backward_matches_oracle(b200_driver, oracle_driver, datatype):
-    """ConvolutionLayer backward (bias gradient by compare-and-swap accumulation, weight gradient, input gradient)
+    """ConvolutionLayer backward (bias gradient = a slab sum over batch and pixels, weight gradient, input gradient)
     against the oracle's restatement of the CPU backend and a float64 numpy convolution transpose."""
     for args in (dict(batch=2, cin=4, hw=9, cout=5), dict(batch=2, cin=3, hw=8, cout=4, k=2, pad=0, stride=2),
                  dict(batch=3, cin=16, hw=13, cout=40, k=5, pad=2), dict(batch=2, cin=32, hw=17, cout=36, k=3, pad=1, stride=2),
@@ -386,32 +377,22 @@ def test_mnist_convnet_matches_oracle(b200_driver, oracle_driver, datatype):
     assert np.abs(gpu.reshape(32, 10).astype(np.float64).sum(axis=1) - 1.0).max() <= (1e-5 if datatype == "float" else 1e-12)
 
 
-@pytest.fixture
-def presplit_variant():
-    """Forces the pre-split GEMM onto its single-CTA (1) or CTA-pair (2) kernel; back to automatic after."""
-    from cortex_b200 import _lib
-    hook = _lib.load().cb200_gemm_presplit_force_variant
-    hook.argtypes, hook.restype = [ctypes.c_int], ctypes.c_int
-    yield hook
-    hook(0)
-
-
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(300, 384, 256), (130, 1000, 500), (128, 256, 16), (513, 260, 4112), (1024, 4096, 4096),
                                    (1300, 520, 48)])
 @pytest.mark.parametrize("act", [None, "relu"])
 @pytest.mark.parametrize("variant", [1, 2])
-def test_presplit_layer_gemm(b200_driver, presplit_variant, M, N, K, act, variant):
+def test_presplit_layer_gemm(b200_driver, M, N, K, act, variant):
     """The pre-split layer GEMM (operands given as hi / lo matrices, result written as hi / lo) against the
     general fused kernel (same arithmetic: equal up to summation order) and against float64, on both of its
     kernels: 128-row tiles per CTA, and 256-row tiles on CTA pairs (ragged last pair: M = 130, 300, 513, 1300
     leave the second CTA of the last pair partly or wholly outside the matrix)."""
-    presplit_variant(variant)
     rng = np.random.default_rng(M * 7 + N)
     A = rng.standard_normal((M, K)).astype(np.float32)
     W = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
     bias = rng.standard_normal(N).astype(np.float32)
     stream = b200_driver.default_device().create_stream()
+    stream.set_option("presplit-variant", variant)      # 1 = single-CTA tiles, 2 = CTA pairs
     with ct.with_stream(stream), ct.with_datatype("float"):
         a, w, b = ct.to_tensor(A), ct.to_tensor(W), ct.to_tensor(bias)
         a_lo, w_lo = ct.new_tensor([M, K]), ct.new_tensor([N, K])

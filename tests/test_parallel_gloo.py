@@ -53,9 +53,8 @@ def _worker(rank, world, port, out_dir):
     with ct.with_stream(stream), ct.with_datatype("float"):
         # 1. batch sharding: this rank's rows through the replicated network
         net = nn.MLP([(ct.to_tensor(W1), ct.to_tensor(b1), "relu"), (ct.to_tensor(W2), ct.to_tensor(b2), "softmax")])
-        sharded = parallel.ShardedMLP(net, world, rank)
-        lo, hi = sharded.local_rows(X.shape[0])
-        local = ct.to_array(sharded.infer_local(ct.to_tensor(X[lo:hi]))).reshape(hi - lo, 20)
+        lo, hi = parallel.shard_bounds(X.shape[0], world, rank)
+        local = ct.to_array(net.infer(ct.to_tensor(X[lo:hi]))).reshape(hi - lo, 20)
         # 2. column-sharded head on replicated activations
         h = ct.new_tensor([X.shape[0], 32])
         nn.Linear(ct.to_tensor(W1), ct.to_tensor(b1)).forward(ct.to_tensor(X), h)
