@@ -435,6 +435,22 @@ def bench_eltwise(drv, dev, peaks):
         cases["pooling_max_3x3s2"] = (lambda i: stream.pooling_forward(pool_out[i].buffer, pool_out[i].dimensions, 0.0,
                                                                        pool_in[i].buffer, pool_in[i].dimensions, pool_desc),
                                       rows * cols * 4 + rows * cols)
+        # optimiser steps over a flat 64 Mi-parameter buffer (two buffer sets of 4 x 256 MiB: far beyond L2) and rand!
+        n_par = 64 << 20
+        from cortex_b200 import optimize
+        opt_sets = [[ct.new_tensor([n_par]) for _ in range(4)] for _ in range(2)]       # gradient, parameters, 2 x state
+        for st_ in opt_sets:
+            ct.rand(st_[0], ct.gaussian_distribution())
+            ct.rand(st_[2], ct.flat_distribution(minimum=0.0, maximum=0.01))
+            ct.rand(st_[3], ct.flat_distribution(minimum=0.0, maximum=0.01))
+        adam, adadelta = optimize.Adam().batch_update(), optimize.Adadelta()
+        cases["adam_step_64Mi"] = (lambda i: adam.compute_parameters(
+            {"m": opt_sets[i % 2][2], "v": opt_sets[i % 2][3]}, 1.0, 0, opt_sets[i % 2][0], opt_sets[i % 2][1]), 7 * n_par * 4)
+        cases["adadelta_step_64Mi"] = (lambda i: adadelta.compute_parameters(
+            {"grad-accum": opt_sets[i % 2][2], "dx-accum": opt_sets[i % 2][3]}, 1.0, 0, opt_sets[i % 2][0],
+            opt_sets[i % 2][1]), 7 * n_par * 4)
+        cases["rand_gaussian_64Mi"] = (lambda i: ct.rand(opt_sets[i % 2][0], ct.gaussian_distribution()), n_par * 4)
+        cases["rand_flat_64Mi"] = (lambda i: ct.rand(opt_sets[i % 2][0], ct.flat_distribution()), n_par * 4)
         for name, (fn, nbytes) in cases.items():
             for _ in range(3):
                 fn(rot())

@@ -23,6 +23,7 @@ UNARY_OPS = {"floor": 0, "ceil": 1, "round": 2, "-": 3, "tanh": 4, "logistic": 5
 TERNARY_OPS = {"select": 0}
 REDUCE_OPS = {"max": 0, "min": 1, "sum": 2, "mean": 3, "magnitude": 4, "magnitude-squared": 5}
 ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "tanh": 2, "logistic": 3}
+DISTRIBUTIONS = {"flat": 0, "gaussian": 1}
 STREAM_OPTIONS = {"gemm-auto-presplit": 0, "presplit-variant": 1, "f64-simple-kernel": 2, "wait-limit-cycles": 3,
                   "inject-fault": 4}
 
@@ -100,6 +101,9 @@ SIGNATURES = {
     "cb200_batch_normalize_eltwise": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64],
     "cb200_batch_normalize_spatial": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
     "cb200_pooling_forward": [_vp, _i, _vp, _pd, _d, _vp, _pd, C.POINTER(PoolDesc)],
+    "cb200_adam_step": [_vp, _i, _d, _d, _d, _d, _d, _d, _d, _vp, _vp, _vp, _vp, _i64],
+    "cb200_adadelta_step": [_vp, _i, _d, _d, _vp, _vp, _d, _vp, _vp, _i64],
+    "cb200_rand": [_vp, _vp, _pd, _i, _d, _d, C.c_uint64, C.c_uint64],
     "cb200_unsupported": [C.c_char_p],
     "cb200_gemm_bias_act": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i],
     "cb200_gemm_bias_act_peers": [_vp, _i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d, _vp, _i,

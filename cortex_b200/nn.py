@@ -130,12 +130,29 @@ class Activation:
 
 
 class Softmax:
+    """SoftmaxLayer (compute/nn/layers.clj:141-168).  `output_channels` > 1: the buffer is read as
+    [ecount / channels, channels] rows (softmax over runs of `channels` values); `output_channels` == 1 with
+    an image-shaped input (`input_dimension` = (channels, height, width), channels != 1): spatial softmax over
+    the channel axis of [batch, channels, height*width]; otherwise one softmax per batch row."""
+
+    def __init__(self, output_channels=1, input_dimension=None):
+        self.output_channels, self.input_dimension = int(output_channels), input_dimension
+
+    def _tensor(self, t):
+        """softmax-tensor (layers.clj:141-152)."""
+        if self.output_channels > 1:
+            return ct.in_place_reshape(t, [t.ecount() // self.output_channels, self.output_channels])
+        if self.input_dimension is not None and self.input_dimension[0] != 1:
+            channels, height, width = self.input_dimension
+            return ct.in_place_reshape(t, [t.shape()[0], channels, height * width])
+        return ct.as_batch_matrix(t)
+
     def forward(self, input, output):
-        return ct.softmax(output, input)
+        return ct.softmax(self._tensor(output), self._tensor(input))
 
     def backward(self, input_gradient, output_gradient):
         """The reference pairs softmax with the cross-entropy loss: the layer passes the gradient through."""
-        return ct.assign(input_gradient, output_gradient)
+        return ct.assign(self._tensor(input_gradient), self._tensor(output_gradient))
 
 
 class Convolution:

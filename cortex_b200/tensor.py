@@ -626,6 +626,44 @@ def batch_normalize(output, input, means, variances, scale, bias, epsilon):
 
 # ------------------------------ softmax! -------------------------------------------
 
+def gaussian_distribution(mean=0, variance=1):
+    """ct/gaussian-distribution (tensor.clj:990-998)."""
+    return {"type": "gaussian", "mean": float(mean), "variance": float(variance)}
+
+
+def flat_distribution(minimum=0, maximum=1):
+    """ct/flat-distribution (tensor.clj:1001-1014): [minimum, maximum)."""
+    _require(float(minimum) < float(maximum), "Minimum must be less than maximum",
+             {"minimum": minimum, "maximum": maximum})
+    return {"type": "flat", "minimum": float(minimum), "maximum": float(maximum)}
+
+
+_rand_state = {"seed": 0x5EEDC0DE, "sequence": 0}
+_rand_lock = threading.Lock()
+
+
+def seed_rand(seed):
+    """Restart the generator behind rand!: the same seed replays the same sequence of rand! results.
+    (The reference draws from SecureRandom / cuRAND's default generator and cannot be replayed.)"""
+    with _rand_lock:
+        _rand_state["seed"], _rand_state["sequence"] = int(seed), 0
+
+
+def rand(dest, distribution):
+    """ct/rand! (tensor.clj:1028-1044): float tensors only, dense, access-increasing."""
+    _require(dest.get_datatype() == "float", "Can only generate rands into floating point buffers",
+             {"expected-datatype": "float", "received-datatype": dest.get_datatype()})
+    _require(dims.dense(dest.dimensions) and dims.access_increasing(dest.dimensions),
+             "Rand generation must have simple dense buffers")
+    _require(distribution.get("type") in ("gaussian", "flat"), "Invalid distibution type",
+             {"valid-types": ["flat", "gaussian"], "type": distribution.get("type")})
+    with _rand_lock:
+        seed, sequence = _rand_state["seed"], _rand_state["sequence"]
+        _rand_state["sequence"] += 1
+    check_stream().rand(dest.buffer, dest.dimensions, distribution, seed, sequence)
+    return dest
+
+
 def softmax(output, input):
     """tensor.clj:1286-1312."""
     _external_library_check("softmax!", output, input)

@@ -235,5 +235,22 @@ class CTensorMath:
     def pooling_backward(self, *a):
         self._unsupported("pooling-backward!")
 
-    def rand(self, *a):
-        self._unsupported("rand!")
+    def rand(self, dest, dest_dims, distribution, seed=0, sequence=0):
+        """tm/rand! (tensor/math.clj:237) + the (seed, sequence) pair of the counter-based generator."""
+        from ._lib import DISTRIBUTIONS
+        kind = distribution["type"]
+        p0, p1 = ((distribution["minimum"], distribution["maximum"]) if kind == "flat"
+                  else (distribution["mean"], distribution["variance"]))
+        self._tm("rand", dest.ptr, C.byref(wire(dest_dims)), DISTRIBUTIONS[kind], float(p0), float(p1),
+                 int(seed) & 0xFFFFFFFFFFFFFFFF, int(sequence) & 0xFFFFFFFFFFFFFFFF)
+
+    # --- optimiser steps (cortex.optimize.adam / adadelta): buffers are flat, already offset by the caller ---
+    def adam_step(self, alpha, beta1, beta2, epsilon, pow_beta1_t, pow_beta2_t, gradient_alpha, gradient, parameters,
+                  m, v, n_elems):
+        self._tm("adam_step", DTYPE_CODE[parameters.dtype], float(alpha), float(beta1), float(beta2), float(epsilon),
+                 float(pow_beta1_t), float(pow_beta2_t), float(gradient_alpha), gradient.ptr, parameters.ptr, m.ptr,
+                 v.ptr, int(n_elems))
+
+    def adadelta_step(self, decay, epsilon, grad_accum, dx_accum, gradient_beta, gradient, parameters, n_elems):
+        self._tm("adadelta_step", DTYPE_CODE[parameters.dtype], float(decay), float(epsilon), grad_accum.ptr,
+                 dx_accum.ptr, float(gradient_beta), gradient.ptr, parameters.ptr, int(n_elems))

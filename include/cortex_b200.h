@@ -283,6 +283,31 @@ typedef struct cb200_pool_desc {
 int cb200_pooling_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, double out_alpha,
                           const void* in, const cb200_dims* in_dims, const cb200_pool_desc* desc);
 
+/* ---- optimiser steps and rand! (the ring of the training path that touches the flat parameter buffer) ----
+ * adam_step: resources/adam.cu:1-36 (the kernel this replaces), src/cortex/optimize/adam.clj:68-102 (CPU
+ * arithmetic, which this follows bit for bit) and :123-142 (call site: scalars cast to the buffer type; m and v
+ * arrive already offset by the parameter offset).  One pass:
+ *   g = gradient_alpha*grad;  m = beta1*m + (1-beta1)*g;  v = beta2*v + (1-beta2)*g*g;
+ *   param -= alpha * (m / ((1 - pow_beta1_t) * (sqrt(v / (1 - pow_beta2_t)) + epsilon)))        float / double */
+int cb200_adam_step(cb200_stream* s, int dtype, double alpha, double beta1, double beta2, double epsilon,
+                    double pow_beta1_t, double pow_beta2_t, double gradient_alpha, const void* gradients,
+                    void* parameters, void* m, void* v, int64_t n_elems);
+/* adadelta_step: resources/adadelta.cu:1-68 (argument order kept), CPU arithmetic
+ * java/cortex/compute/optimize/AdadeltaOptimizer.java; call site src/cortex/optimize/adadelta.clj:27-75.
+ *   g = gradient_beta*grad;  ga = g*g*decay + ga*(1-decay);  dx = -sqrt(dxa + eps) * g / sqrt(ga + eps);
+ *   dxa = dx*dx*decay + dxa*(1-decay);  param += dx                                           float / double */
+int cb200_adadelta_step(cb200_stream* s, int dtype, double decay, double epsilon, void* grad_accum, void* dx_accum,
+                        double gradient_beta, const void* gradient, void* parameters, int64_t n_elems);
+/* rand! (src/cortex/tensor/math.clj:237; distributions src/cortex/tensor.clj:990-1012): float, dense dest.
+ *   CB200_RAND_FLAT:     p0 = minimum, p1 = maximum,  dest in [minimum, maximum)
+ *   CB200_RAND_GAUSSIAN: p0 = mean,    p1 = variance
+ * The protocol carries no seed (the reference draws from SecureRandom / cuRAND's global generator); here the
+ * generator is counter-based, so the caller supplies (seed, sequence): the same pair reproduces the same
+ * values, a different sequence number gives an independent stream. */
+enum cb200_distribution { CB200_RAND_FLAT = 0, CB200_RAND_GAUSSIAN = 1 };
+int cb200_rand(cb200_stream* s, void* dest, const cb200_dims* dest_dims, int distribution, double p0, double p1,
+               uint64_t seed, uint64_t sequence);
+
 /* Protocol methods this backend does not implement return CB200_ERR_UNSUPPORTED through this call:
  * lrn-forward! / lrn-backward! (src/cortex/tensor/math.clj:239-250). */
 int cb200_unsupported(const char* method_name);

@@ -53,6 +53,10 @@ _SIGS = {
     "orc_convolution_backward_weights": [_i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
     "orc_convolution_backward_data": [_i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
     "orc_bias_relu_rowstats": [_i, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp, _vp],
+    "orc_adam_step": [_i, _d, _d, _d, _d, _d, _d, _d, _vp, _vp, _vp, _vp, _i64],
+    "orc_adadelta_step": [_i, _d, _d, _vp, _vp, _d, _vp, _vp, _i64],
+    "orc_rand": [_vp, _pd, _i, _d, _d, C.c_uint64, C.c_uint64],
+    "orc_philox4x32_10": [_vp, _vp, _vp],
 }
 
 

@@ -649,3 +649,132 @@ int orc_bias_relu_rowstats(int dtype, void* Y, int64_t ldy, const void* X, int64
   if (dtype == T_DOUBLE) BRS(double)
   return 1;
 }
+
+/* ---- optimiser steps and rand! ---------------------------------------------------
+ * adam: src/cortex/optimize/adam.clj:68-102 (cpu-adam-step-impl!): scalars cast to the buffer type, then
+ *   every operation in double, one rounding per operation, results rounded once on store.
+ * adadelta: java/cortex/compute/optimize/AdadeltaOptimizer.java (step_f / step_d): step_f forms
+ *   gradient_alpha * gradient as a FLOAT product and adds (float)dx to the parameter as a float add.
+ * rand!: src/cortex/compute/cpu/tensor_math.clj:1867-1890 draws from java.security.SecureRandom, which cannot
+ *   be reproduced; the reference pins only the distribution's mean and variance
+ *   (src/cortex/verify/tensor.clj:1036-1066).  The generator restated here is the counter-based Philox-4x32-10
+ *   (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11) that the B200 backend
+ *   uses, with the reference's own shaping of the draws (min + u * range, sqrt(variance) * z + mean in double). */
+int orc_adam_step(int dtype, double alpha, double beta1, double beta2, double epsilon, double pow_beta1_t,
+                  double pow_beta2_t, double gradient_alpha, const void* gradients, void* parameters, void* m, void* v,
+                  int64_t n) {
+  if (dtype != T_FLOAT && dtype != T_DOUBLE) return 1;
+#define CASTS(x) (dtype == T_FLOAT ? (double)(float)(x) : (double)(x))
+  const double a = CASTS(alpha), b1 = CASTS(beta1), b2 = CASTS(beta2), eps = CASTS(epsilon), p1 = CASTS(pow_beta1_t),
+               p2 = CASTS(pow_beta2_t), ga = CASTS(gradient_alpha);
+  const double omb1 = 1.0 - b1, omb2 = 1.0 - b2;
+#pragma omp parallel for
+  for (int64_t i = 0; i < n; ++i) {
+    const double g0 = dtype == T_FLOAT ? (double)((const float*)gradients)[i] : ((const double*)gradients)[i];
+    const double pv = dtype == T_FLOAT ? (double)((float*)parameters)[i] : ((double*)parameters)[i];
+    const double mv = dtype == T_FLOAT ? (double)((float*)m)[i] : ((double*)m)[i];
+    const double vv = dtype == T_FLOAT ? (double)((float*)v)[i] : ((double*)v)[i];
+    const volatile double g = ga * g0;
+    const volatile double t1 = b1 * mv, t2 = omb1 * g;
+    const volatile double lm = t1 + t2;
+    const volatile double t3 = b2 * vv, t4 = omb2 * g;
+    const volatile double t5 = t4 * g;
+    const volatile double lv = t3 + t5;
+    const volatile double q = lv / (1.0 - p2);
+    const volatile double sq = sqrt(q) + eps;
+    const volatile double den = (1.0 - p1) * sq;
+    const volatile double r = lm / den;
+    const volatile double dx = a * r;
+    const double np_ = pv - dx;
+    if (dtype == T_FLOAT) { ((float*)m)[i] = (float)lm; ((float*)v)[i] = (float)lv; ((float*)parameters)[i] = (float)np_; }
+    else { ((double*)m)[i] = lm; ((double*)v)[i] = lv; ((double*)parameters)[i] = np_; }
+  }
+  return 0;
+}
+
+int orc_adadelta_step(int dtype, double decay, double epsilon, void* grad_accum, void* dx_accum, double gradient_beta,
+                      const void* gradient, void* parameters, int64_t n) {
+  if (dtype != T_FLOAT && dtype != T_DOUBLE) return 1;
+  const double dec = CASTS(decay), eps = CASTS(epsilon);
+#pragma omp parallel for
+  for (int64_t i = 0; i < n; ++i) {
+    double g, ga_in, dxa_in;
+    if (dtype == T_FLOAT) {
+      const volatile float gf = (float)gradient_beta * ((const float*)gradient)[i];   /* float product */
+      g = (double)gf; ga_in = (double)((float*)grad_accum)[i]; dxa_in = (double)((float*)dx_accum)[i];
+    } else {
+      const volatile double gd = gradient_beta * ((const double*)gradient)[i];
+      g = gd; ga_in = ((double*)grad_accum)[i]; dxa_in = ((double*)dx_accum)[i];
+    }
+    const volatile double gg = g * g;
+    const volatile double u1 = gg * dec, u2 = ga_in * (1.0 - dec);
+    const volatile double ga = u1 + u2;
+    const volatile double rms_g = sqrt(ga + eps), rms_dx = sqrt(dxa_in + eps);
+    const volatile double w1 = -1.0 * rms_dx;
+    const volatile double w2 = w1 * g;
+    const volatile double dx = w2 / rms_g;
+    const volatile double dd = dx * dx;
+    const volatile double u3 = dd * dec, u4 = dxa_in * (1.0 - dec);
+    const volatile double dxa = u3 + u4;
+    if (dtype == T_FLOAT) {
+      ((float*)grad_accum)[i] = (float)ga; ((float*)dx_accum)[i] = (float)dxa;
+      const volatile float np_ = ((float*)parameters)[i] + (float)dx;                  /* float add */
+      ((float*)parameters)[i] = np_;
+    } else {
+      ((double*)grad_accum)[i] = ga; ((double*)dx_accum)[i] = dxa; ((double*)parameters)[i] += dx;
+    }
+  }
+  return 0;
+}
+#undef CASTS
+
+static void philox4x32_10(uint64_t index, uint64_t sequence, uint64_t seed, uint32_t out[4]) {
+  uint32_t c[4] = {(uint32_t)index, (uint32_t)(index >> 32), (uint32_t)sequence, (uint32_t)(sequence >> 32)};
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c[0], p1 = (uint64_t)0xCD9E8D57u * c[2];
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0, n1 = (uint32_t)p1, n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1,
+                   n3 = (uint32_t)p0;
+    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  for (int j = 0; j < 4; ++j) out[j] = c[j];
+}
+
+/* raw block function, exported so that the tests can check it against the published known-answer vectors */
+int orc_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]) {
+  philox4x32_10((uint64_t)ctr[0] | ((uint64_t)ctr[1] << 32), (uint64_t)ctr[2] | ((uint64_t)ctr[3] << 32),
+                (uint64_t)key[0] | ((uint64_t)key[1] << 32), out);
+  return 0;
+}
+
+enum { RAND_FLAT = 0, RAND_GAUSSIAN = 1 };
+int orc_rand(void* dest, const orc_dims* dd, int distribution, double p0, double p1, uint64_t seed, uint64_t sequence) {
+  int64_t n = 1;
+  for (int d = 0; d < 5; ++d) n *= dd->rev_shape[d];
+  float* out = (float*)dest;
+  double a, b;
+  if (distribution == RAND_FLAT) { const float mn = (float)p0, mx = (float)p1; a = mn; b = (double)mx - (double)mn; }
+  else if (distribution == RAND_GAUSSIAN) { a = (double)(float)p0; b = sqrt((double)(float)p1); }
+  else return 1;
+  const int64_t groups = (n + 3) / 4;
+  for (int64_t i = 0; i < groups; ++i) {
+    uint32_t r[4];
+    float o[4];
+    philox4x32_10((uint64_t)i, sequence, seed, r);
+    if (distribution == RAND_FLAT) {
+      for (int j = 0; j < 4; ++j) o[j] = (float)(a + (double)((float)(r[j] >> 8) * 5.9604644775390625e-8f) * b);
+    } else {
+      for (int j = 0; j < 4; j += 2) {
+        const float u1 = 1.0f - (float)(r[j] >> 8) * 5.9604644775390625e-8f;
+        const float u2 = (float)(r[j + 1] >> 8) * 5.9604644775390625e-8f;
+        const float rad = sqrtf(-2.0f * logf(u1));
+        const float ang = 6.283185307179586f * u2;
+        o[j] = (float)(b * (double)(rad * cosf(ang)) + a);
+        o[j + 1] = (float)(b * (double)(rad * sinf(ang)) + a);
+      }
+    }
+    for (int j = 0; j < 4 && 4 * i + j < n; ++j) out[4 * i + j] = o[j];
+  }
+  return 0;
+}

@@ -57,3 +57,25 @@ def test_conv(oracle_driver, datatype):
     assert pc.rel_err(_run(oracle_driver, datatype, run), ref()) <= pc.TOL[datatype]
     run, ref = pc.conv_case(datatype, 2, 3, 8, 4, k=2, pad=0, stride=2, bias_scale=0.1)
     assert pc.rel_err(_run(oracle_driver, datatype, run), ref()) <= pc.TOL[datatype]
+
+
+def test_philox_known_answers():
+    """The generator behind rand! against the known-answer vectors published with the algorithm
+    (Random123's Philox-4x32-10: zero counter and key, all-ones, and the digits-of-pi vector)."""
+    import ctypes
+
+    import numpy as np
+
+    from oracle import cpu_backend
+    lib = cpu_backend.load()
+    vectors = [
+        ([0, 0, 0, 0], [0, 0], [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]),
+        ([0xffffffff] * 4, [0xffffffff] * 2, [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]),
+        ([0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344], [0xa4093822, 0x299f31d0],
+         [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]),
+    ]
+    for ctr, key, want in vectors:
+        c, k, out = np.asarray(ctr, np.uint32), np.asarray(key, np.uint32), np.zeros(4, np.uint32)
+        lib.orc_philox4x32_10(c.ctypes.data_as(ctypes.c_void_p), k.ctypes.data_as(ctypes.c_void_p),
+                              out.ctypes.data_as(ctypes.c_void_p))
+        assert [int(v) for v in out] == want

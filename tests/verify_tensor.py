@@ -388,6 +388,144 @@ def relu_layer_backward(driver, datatype):
             assert float(np.sum(ct.to_double_array(in_grad))) == batch * items / 2
 
 
+def softmax_layer(driver, datatype):
+    """verify/nn/layers.clj:399-499: softmax, softmax-batch, softmax-image (spatial: one softmax per pixel over
+    4 channels), softmax-batch-channels (:output-channels 4), forward and backward through the layer."""
+    from cortex_b200 import nn
+    row = [0.015127670383492609, 0.041121271510366035, 0.11177920510975863, 0.30384738204945333,
+           0.015127670383492609, 0.041121271510366035, 0.11177920510975863, 0.30384738204945333,
+           0.015127670383492609, 0.041121271510366035]
+    chan = [0.03205860328008499, 0.08714431874203257, 0.23688281808991013, 0.6439142598879724]
+    tol = 1e-6 / 10 if datatype == "double" else 1e-6       # about-there?: summed abs difference < 1e-6
+    with tensor_context(driver, datatype):
+        for batch in (1, 10):                                 # softmax, softmax-batch
+            layer = nn.Softmax()
+            x = ct.to_tensor([([1, 2, 3, 4] * 3)[:10]] * batch)
+            out, in_grad = ct.new_tensor([batch, 10]), ct.new_tensor([batch, 10])
+            out_grad = ct.to_tensor(np.ones((batch, 10)))
+            layer.forward(x, out)
+            layer.backward(in_grad, out_grad)
+            _eq(row * batch, ct.to_double_array(out), tol)
+            _eq([1.0] * (10 * batch), ct.to_double_array(in_grad))
+        # softmax-image: input 5x5 image, 4 channels, channel c filled with c + 1
+        img = 5
+        layer = nn.Softmax(output_channels=1, input_dimension=(4, img, img))
+        data = [[float(c)] * (img * img) for c in range(1, 5)]
+        x = ct.to_tensor([np.asarray(data).reshape(-1)])
+        out, in_grad = ct.new_tensor([1, 4 * img * img]), ct.new_tensor([1, 4 * img * img])
+        out_grad = ct.to_tensor([np.asarray(data).reshape(-1)])
+        layer.forward(x, out)
+        layer.backward(in_grad, out_grad)
+        _eq([v for c in chan for v in [c] * (img * img)], ct.to_double_array(out), 1e-4)
+        _eq(np.asarray(data).reshape(-1), ct.to_double_array(in_grad), 1e-6)
+        # softmax-batch-channels: 10 pixels of [1 2 3 4], :output-channels 4
+        batch, pixels = 10, 10
+        layer = nn.Softmax(output_channels=4)
+        x = ct.to_tensor([[1, 2, 3, 4] * pixels] * batch)
+        out, in_grad = ct.new_tensor([batch, 4 * pixels]), ct.new_tensor([batch, 4 * pixels])
+        out_grad = ct.to_tensor(np.ones((batch, 4 * pixels)))
+        layer.forward(x, out)
+        layer.backward(in_grad, out_grad)
+        assert float(np.abs(np.asarray(chan * (pixels * batch)) - ct.to_double_array(out).reshape(-1)).sum()) < 1e-4
+        _eq([1.0] * (4 * pixels * batch), ct.to_double_array(in_grad))
+
+
+def basic_conv_layer(driver, datatype):
+    """verify/nn/layers.clj:502-556: 2x2 kernels (kernel k filled with k, bias 1) over a 3x3 and a 3-wide x
+    4-high single-channel input, batch 10: output, weight / bias gradients and input gradient."""
+    from cortex_b200 import nn
+    cases = [
+        # (in_w, in_h, out_grad per image, output, weight grad per kernel, bias grad, input grad)
+        (3, 3, [13.0, 17.0, 25.0, 29.0, 25.0, 33.0, 49.0, 57.0, 37.0, 49.0, 73.0, 85.0, 49.0, 65.0, 97.0, 113.0],
+         [120.0, 160.0, 240.0, 280.0], 4, [1, 2, 1, 2, 4, 2, 1, 2, 1]),
+        (3, 4, [13.0, 17.0, 25.0, 29.0, 37.0, 41.0, 25.0, 33.0, 49.0, 57.0, 73.0, 81.0, 37.0, 49.0, 73.0, 85.0, 109.0,
+                121.0, 49.0, 65.0, 97.0, 113.0, 145.0, 161.0],
+         [270.0, 330.0, 450.0, 510.0], 6, [1, 2, 1, 2, 4, 2, 2, 4, 2, 1, 2, 1]),
+    ]
+    batch, kernels, k = 10, 4, 2
+    with tensor_context(driver, datatype):
+        for in_w, in_h, output, w_grad_k, bias_per_image, in_grad_unit in cases:
+            out_w, out_h = in_w - k + 1, in_h - k + 1
+            weights = ct.to_tensor([[float(i)] * (k * k) for i in range(1, kernels + 1)])
+            bias = ct.to_tensor([1.0] * kernels)
+            layer = nn.Convolution(weights, bias, (k, k), (0, 0), (1, 1), 1, kernels, datatype)
+            x = ct.to_tensor(np.tile(np.arange(1, in_w * in_h + 1), batch).reshape(batch, 1, in_h, in_w))
+            out = ct.new_tensor([batch, kernels, out_h, out_w])
+            out_grad = ct.to_tensor(np.ones((batch, kernels, out_h, out_w)))
+            in_grad = ct.new_tensor([batch, 1, in_h, in_w])
+            w_grad, b_grad = ct.new_tensor([kernels, k * k]), ct.new_tensor([kernels])
+            layer.forward(x, out)
+            layer.backward(x, in_grad, out_grad, w_grad, b_grad)
+            _eq(output * batch, ct.to_double_array(out))
+            _eq(w_grad_k * kernels, ct.to_double_array(w_grad))
+            _eq([float(bias_per_image * batch)] * kernels, ct.to_double_array(b_grad))
+            _eq([10.0 * v for v in in_grad_unit] * batch, ct.to_double_array(in_grad))
+
+
+ADAM_ANSWERS = [
+    [0.999000000005, 1.9990000000025, 2.9990000000016668, 3.99900000000125],
+    [0.9980000262138343, 1.9980000130723587, 2.998000008707231, 3.998000006527546],
+    [0.9970000960651408, 1.9970000478972731, 2.9970000319014805, 3.9970000239148513],
+    [0.9960002269257634, 1.9960001131228113, 2.9960000753397424, 3.9960000564765217],
+    [0.995000436052392, 1.9950002173334274, 2.995000144735273, 3.995000108493863],
+    [0.9940007405541528, 1.9940003690339771, 2.994000245746984, 3.9940001842069432],
+    [0.9930011573564278, 1.9930005766318695, 2.9930003839675967, 3.993000287805732],
+    [0.9920017031661642, 1.9920008484199827, 2.992000564912314, 3.992000423421624],
+    [0.9910023944389119, 1.991001192560463, 2.9910007940080785, 3.9910005951194076],
+    [0.9900032473478027, 1.9900016170695067, 2.9900010765834972, 3.990000806889731],
+    [0.9890042777546556, 1.9890021298032192, 2.9890014178594777, 3.9890010626421075],
+    [0.9880055011833645, 1.9880027384446224, 2.9880018229406398, 3.988001366198499],
+    [0.9870069327956914, 1.987003450491873, 2.98700229680753, 3.9870017212875037],
+    [0.9860085873695607, 1.986004273247733, 2.9860028443096756, 3.9860021315391725],
+    [0.9850104792799151, 1.9850052138103236, 2.9850034701594894, 3.9850026004804673],
+    [0.9840126224821667, 1.984006279065173, 2.984004178927043, 3.984003131531364],
+    [0.9830150304982433, 1.9830074756785594, 2.9830049750356973, 3.9830037280016044],
+    [0.9820177164052082, 1.9820088100921336, 2.982005862758586, 3.9820043930880837],
+    [0.9810206928263993, 1.9810102885187928, 2.981006846215933, 3.9810051298728633],
+]
+
+
+def adam_optimizer(driver, datatype):
+    """compute/verify/optimize.clj:11-61 (test-adam): 19 steps on parameters [1 2 3 4] with gradient
+    2 * parameters; a second buffer at offset 4 of m / v stepped with gradient-alpha 0 must not move.
+    about-there? = summed abs difference < 1e-6; a float buffer cannot hold the literals closer than its
+    own spacing (2.4e-7 at 4.0), so floats are compared at 2e-6."""
+    from cortex_b200 import optimize
+    tol = 1e-6 if datatype == "double" else 2e-6
+    with tensor_context(driver, datatype):
+        parameters_1, parameters_2 = ct.to_tensor([1, 2, 3, 4]), ct.to_tensor([1, 2, 3, 4])
+        state = {"m": ct.new_tensor([8]), "v": ct.new_tensor([8])}
+        optimizer = optimize.Adam()
+        for item in ADAM_ANSWERS:
+            gradient_1 = ct.to_tensor(2.0 * ct.to_double_array(parameters_1))
+            gradient_2 = ct.to_tensor(2.0 * ct.to_double_array(parameters_2))
+            optimizer = optimizer.batch_update()
+            optimizer.compute_parameters(state, 1.0, 0, gradient_1, parameters_1)
+            optimizer.compute_parameters(state, 0.0, 4, gradient_2, parameters_2)
+            assert float(np.abs(ct.to_double_array(parameters_1) - np.asarray(item)).sum()) < tol
+            assert float(np.abs(ct.to_double_array(parameters_2) - np.asarray([1.0, 2.0, 3.0, 4.0])).sum()) < 1e-6
+
+
+def rand_operator(driver, datatype):
+    """verify/tensor.clj:1036-1066: mean and variance of 10,000 draws within 1 of the request, for means /
+    variances 1..10 (gaussian) and centres 1..10 with half-width 2 (flat)."""
+    with tensor_context(driver, datatype):
+        test_vec = []
+        for idx in range(1, 11):
+            tens = ct.rand(ct.new_tensor([10000]), ct.gaussian_distribution(mean=idx, variance=idx))
+            values = ct.to_double_array(tens)
+            test_vec += [float(np.mean(values)), float(np.var(values, ddof=1))]
+        expected = [v for idx in range(1, 11) for v in (idx, idx)]
+        assert np.all(np.abs(np.asarray(test_vec) - np.asarray(expected)) <= 1.0), test_vec
+        test_vec = []
+        for idx in range(1, 11):
+            tens = ct.rand(ct.new_tensor([10000]), ct.flat_distribution(minimum=idx - 2, maximum=idx + 2))
+            values = ct.to_double_array(tens)
+            assert values.min() >= idx - 2 and values.max() <= idx + 2
+            test_vec.append(float(np.mean(values)))
+        assert np.all(np.abs(np.asarray(test_vec) - np.arange(1, 11)) <= 1.0), test_vec
+
+
 def unary_reduce(driver, datatype):
     """verify/tensor.clj:648-665"""
     with tensor_context(driver, datatype):
@@ -584,6 +722,8 @@ CASES = [
     (activation_forward, FLOAT_DTYPES), (softmax, FLOAT_DTYPES), (unary_reduce, ALL_DTYPES), (transpose, ALL_DTYPES),
     (mask, INT_LONG), (select, ALL_DTYPES), (select_transpose_interaction, ALL_DTYPES),
     (convolution_operator, FLOAT_DTYPES), (indexed_tensor, ALL_DTYPES), (magnitude_and_mag_squared, FLOAT_DTYPES),
+    (softmax_layer, FLOAT_DTYPES), (basic_conv_layer, FLOAT_DTYPES), (adam_optimizer, FLOAT_DTYPES),
+    (rand_operator, ["float"]),
 ]
 
 
