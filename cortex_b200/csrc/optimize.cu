@@ -7,11 +7,14 @@
 //
 // Each step is ONE pass over the buffers (adam: gradient, parameters, m, v read; parameters, m, v written =
 // 28 bytes per fp32 parameter), HBM-bound, 16-byte accesses, two vectors per array in flight per thread, grid
-// sized to the SM count.  Arithmetic follows the reference CPU backend: float buffers are computed in
-// double with the scalars rounded to float first, one operation at a time (explicit round-to-nearest
-// intrinsics, no contraction into fused multiply-adds, as the JVM), and rounded once on store -- so the
-// result is bit-identical to the CPU backend for float and for double.  (SGD with momentum needs no kernel:
-// the reference issues it as four tensor calls, src/cortex/optimize/sgd.clj:16-40, and so does the host.)
+// sized to the SM count.  Arithmetic: double buffers follow the reference CPU backend operation for operation
+// (explicit round-to-nearest intrinsics, no contraction into fused multiply-adds, as the JVM) and are
+// bit-identical to it.  Float buffers are computed in single precision with IEEE-rounded divide and square
+// root, as the reference's own CUDA kernels do (the CPU backend evaluates them in double and rounds on
+// store: the two differ by a few units in the last place, far inside the 1e-4 bound; evaluating float
+// buffers in double costs ~70 fp64 instructions per parameter, which makes the pass ALU-bound -- measured
+// 0.76 / 0.38 of the HBM copy rate for adam / adadelta -- instead of memory-bound).  (SGD with momentum
+// needs no kernel: the reference issues it as four tensor calls, src/cortex/optimize/sgd.clj:16-40.)
 //
 // rand! has no reproducible counterpart in the reference (SecureRandom on the CPU, cuRAND's default
 // generator on CUDA; its test is statistical, src/cortex/verify/tensor.clj:1036-1066).  Here it is a
@@ -26,18 +29,36 @@ namespace {
 // CPU formula (adam.clj:83-95): g = ga * grad; m' = b1*m + (1-b1)*g; v' = b2*v + (1-b2)*g*g;
 //   dx = alpha * (m' / ((1 - p1) * (sqrt(v' / (1 - p2)) + eps)));  param -= dx
 // m' and v' enter dx unrounded (they are locals; the stores round copies of them).
-struct AdamScalars { double alpha, beta1, beta2, eps, p1, p2, ga, omb1, omb2, omp1, omp2; };
+struct AdamScalars {
+  double alpha, beta1, beta2, eps, p1, p2, ga, omb1, omb2, omp1, omp2;
+  float f_alpha, f_beta1, f_beta2, f_eps, f_ga, f_omb1, f_omb2, f_omp1, f_omp2;
+};
 
 template <typename T>
-__device__ __forceinline__ void adam_one(const AdamScalars& c, T grad, T& param, T& m, T& v) {
-  const double g = __dmul_rn(c.ga, (double)grad);
-  const double lm = __dadd_rn(__dmul_rn(c.beta1, (double)m), __dmul_rn(c.omb1, g));
-  const double lv = __dadd_rn(__dmul_rn(c.beta2, (double)v), __dmul_rn(__dmul_rn(c.omb2, g), g));
+__device__ __forceinline__ void adam_one(const AdamScalars& c, T grad, T& param, T& m, T& v);
+
+template <>
+__device__ __forceinline__ void adam_one<double>(const AdamScalars& c, double grad, double& param, double& m, double& v) {
+  const double g = __dmul_rn(c.ga, grad);
+  const double lm = __dadd_rn(__dmul_rn(c.beta1, m), __dmul_rn(c.omb1, g));
+  const double lv = __dadd_rn(__dmul_rn(c.beta2, v), __dmul_rn(__dmul_rn(c.omb2, g), g));
   const double denom = __dmul_rn(c.omp1, __dadd_rn(__dsqrt_rn(__ddiv_rn(lv, c.omp2)), c.eps));
   const double dx = __dmul_rn(c.alpha, __ddiv_rn(lm, denom));
-  m = (T)lm;
-  v = (T)lv;
-  param = (T)__dsub_rn((double)param, dx);
+  m = lm;
+  v = lv;
+  param = __dsub_rn(param, dx);
+}
+
+template <>
+__device__ __forceinline__ void adam_one<float>(const AdamScalars& c, float grad, float& param, float& m, float& v) {
+  const float g = c.f_ga * grad;
+  const float lm = fmaf(c.f_beta1, m, c.f_omb1 * g);
+  const float lv = fmaf(c.f_beta2, v, (c.f_omb2 * g) * g);
+  const float denom = c.f_omp1 * (__fsqrt_rn(__fdiv_rn(lv, c.f_omp2)) + c.f_eps);
+  const float dx = c.f_alpha * __fdiv_rn(lm, denom);
+  m = lm;
+  v = lv;
+  param = param - dx;
 }
 
 template <typename T, int VEC>
@@ -88,7 +109,7 @@ adam_scalar_kernel(AdamScalars c, const T* grad, T* param, T* m, T* v, long long
 // CPU (AdadeltaOptimizer.java): g = ga * grad (a FLOAT product in step_f, double in step_d);
 //   ga' = g*g*decay + ga_acc*(1 - decay);  dx = (-1 * sqrt(dx_acc + eps) * g) / sqrt(ga' + eps);
 //   dxa' = dx*dx*decay + dx_acc*(1 - decay);  param += (T)dx  (a float add in step_f)
-struct AdadeltaScalars { double decay, eps, ga, omd; float ga_f; };
+struct AdadeltaScalars { double decay, eps, ga, omd; float ga_f, f_decay, f_eps, f_omd; };
 
 template <typename T>
 __device__ __forceinline__ void adadelta_one(const AdadeltaScalars& c, T grad, T& param, T& gacc, T& dxacc);
@@ -110,15 +131,15 @@ __device__ __forceinline__ void adadelta_one<double>(const AdadeltaScalars& c, d
 template <>
 __device__ __forceinline__ void adadelta_one<float>(const AdadeltaScalars& c, float grad, float& param, float& gacc,
                                                     float& dxacc) {
-  const double g = (double)__fmul_rn(c.ga_f, grad);
-  const double ga = __dadd_rn(__dmul_rn(__dmul_rn(g, g), c.decay), __dmul_rn((double)gacc, c.omd));
-  const double rms_g = __dsqrt_rn(__dadd_rn(ga, c.eps));
-  const double rms_dx = __dsqrt_rn(__dadd_rn((double)dxacc, c.eps));
-  const double dx = __ddiv_rn(__dmul_rn(__dmul_rn(-1.0, rms_dx), g), rms_g);
-  const double dxa = __dadd_rn(__dmul_rn(__dmul_rn(dx, dx), c.decay), __dmul_rn((double)dxacc, c.omd));
-  gacc = (float)ga;
-  dxacc = (float)dxa;
-  param = __fadd_rn(param, (float)dx);
+  const float g = c.ga_f * grad;
+  const float ga = fmaf(g * g, c.f_decay, gacc * c.f_omd);
+  const float rms_g = __fsqrt_rn(ga + c.f_eps);
+  const float rms_dx = __fsqrt_rn(dxacc + c.f_eps);
+  const float dx = __fdiv_rn(-rms_dx * g, rms_g);
+  const float dxa = fmaf(dx * dx, c.f_decay, dxacc * c.f_omd);
+  gacc = ga;
+  dxacc = dxa;
+  param = param + dx;
 }
 
 template <typename T, int VEC>
@@ -188,10 +209,12 @@ __host__ __device__ inline void philox4x32_10(uint64_t index, uint64_t sequence,
 // 24 random bits -> [0, 1): includes 0, excludes 1, every value exactly representable
 __device__ __forceinline__ float u01(uint32_t x) { return (float)(x >> 8) * 5.9604644775390625e-8f; }
 
-// flat:      dest = (float)(min + u * (max - min))      evaluated in double like the CPU backend
-// gaussian:  dest = (float)(sqrt(variance) * z + mean), z from Box-Muller on two uniforms in (0, 1]
+// flat:      dest = min + u * (max - min): one fused multiply-add.  u has 24 bits and the range 24, so
+//            the product is exact and the result is the correctly rounded sum -- what the CPU backend's
+//            double evaluation followed by the float store gives too, short of a double-rounding tie
+// gaussian:  dest = sqrt(variance) * z + mean, z from Box-Muller on two uniforms, the first in (0, 1]
 __global__ void __launch_bounds__(256)
-rand_kernel(float* dest, long long n, int gaussian, double a, double b, uint64_t seed, uint64_t sequence) {
+rand_kernel(float* dest, long long n, int gaussian, float a, float b, uint64_t seed, uint64_t sequence) {
   const long long groups = (n + 3) / 4;
   const bool vec_ok = (((uintptr_t)dest) & 15) == 0;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += (long long)gridDim.x * blockDim.x) {
@@ -200,7 +223,7 @@ rand_kernel(float* dest, long long n, int gaussian, double a, double b, uint64_t
     float o[4];
     if (!gaussian) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) o[j] = (float)__dadd_rn(a, __dmul_rn((double)u01(r[j]), b));
+      for (int j = 0; j < 4; ++j) o[j] = fmaf(u01(r[j]), b, a);
     } else {
 #pragma unroll
       for (int j = 0; j < 4; j += 2) {
@@ -208,8 +231,8 @@ rand_kernel(float* dest, long long n, int gaussian, double a, double b, uint64_t
         const float rad = sqrtf(-2.0f * logf(u1));
         float sn, cs;
         sincospif(2.0f * u01(r[j + 1]), &sn, &cs);
-        o[j] = (float)__dadd_rn(__dmul_rn(b, (double)(rad * cs)), a);
-        o[j + 1] = (float)__dadd_rn(__dmul_rn(b, (double)(rad * sn)), a);
+        o[j] = fmaf(b, rad * cs, a);
+        o[j + 1] = fmaf(b, rad * sn, a);
       }
     }
     if (vec_ok && 4 * i + 4 <= n) {
@@ -249,6 +272,9 @@ int cb200_adam_step(cb200_stream* s, int dtype, double alpha, double beta1, doub
   c.alpha = cast(alpha); c.beta1 = cast(beta1); c.beta2 = cast(beta2); c.eps = cast(epsilon);
   c.p1 = cast(pow_beta1_t); c.p2 = cast(pow_beta2_t); c.ga = cast(gradient_alpha);
   c.omb1 = 1.0 - c.beta1; c.omb2 = 1.0 - c.beta2; c.omp1 = 1.0 - c.p1; c.omp2 = 1.0 - c.p2;
+  c.f_alpha = (float)c.alpha; c.f_beta1 = (float)c.beta1; c.f_beta2 = (float)c.beta2; c.f_eps = (float)c.eps;
+  c.f_ga = (float)c.ga; c.f_omb1 = (float)c.omb1; c.f_omb2 = (float)c.omb2; c.f_omp1 = (float)c.omp1;
+  c.f_omp2 = (float)c.omp2;
   DeviceGuard guard(s->device);
   if (dtype == CB200_FLOAT) {
     if (aligned16<float>(gradients, parameters, m, v))
@@ -279,6 +305,7 @@ int cb200_adadelta_step(cb200_stream* s, int dtype, double decay, double epsilon
   auto cast = [&](double x) { return dtype == CB200_FLOAT ? (double)(float)x : x; };
   c.decay = cast(decay); c.eps = cast(epsilon); c.ga = cast(gradient_beta); c.ga_f = (float)gradient_beta;
   c.omd = 1.0 - c.decay;
+  c.f_decay = (float)c.decay; c.f_eps = (float)c.eps; c.f_omd = (float)c.omd;
   DeviceGuard guard(s->device);
   if (dtype == CB200_FLOAT) {
     if (aligned16<float>(gradient, parameters, grad_accum, dx_accum))
@@ -327,7 +354,7 @@ int cb200_rand(cb200_stream* s, void* dest, const cb200_dims* dest_dims, int dis
   }
   DeviceGuard guard(s->device);
   rand_kernel<<<grid_for(s, (n + 3) / 4 * 2), 256, 0, s->stream>>>((float*)dest, n, distribution == CB200_RAND_GAUSSIAN,
-                                                                  a, b, seed, sequence);
+                                                                  (float)a, (float)b, seed, sequence);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }

@@ -320,7 +320,31 @@ class MLP(_Replayable):
             self._buffers[key] = ct.new_tensor([batch, width], datatype=datatype, init_value=None)
         return self._buffers[key]
 
-    def infer(self, x):
+    def infer(self, x, row_block=None, trace=None):
+        """Forward pass.  `row_block`: run the stack depth-first over blocks of that many rows (every layer of
+        block 0, then block 1, ...): the activations between layers are then block-sized buffers that are reused
+        for every block, so they stay (partly) in L2 from one layer to the next instead of streaming through
+        HBM; the result is the same, bit for bit (rows are independent).  `trace(idx, when)` is called around
+        every layer's GEMM launch with when = "begin" / "end" (measurement hooks)."""
+        batch = x.shape()[0]
+        if not row_block or batch <= row_block:
+            return self._infer_rows(x, trace)
+        dt = x.get_datatype()
+        in_width = x.shape()[1]
+        out_width = self.layers[-1][0].weights.shape()[0]
+        full = self._buffer(("row-blocked-out",), batch, out_width, dt)
+        stream = ct.check_stream()
+        xm = ct.as_batch_matrix(x)
+        ct._require(ct.dense(xm), "row-blocked inference wants a dense input")
+        from . import dimensions as dims
+        for r0 in range(0, batch, row_block):
+            nr = min(row_block, batch - r0)
+            xb = ct.Tensor(x.device, dims.dimensions([nr, in_width]), xm.buffer.sub_buffer(r0 * in_width, nr * in_width))
+            yb = self._infer_rows(xb, trace)
+            stream.copy_device_to_device(yb.buffer, 0, full.buffer, r0 * out_width, nr * out_width)
+        return full
+
+    def _infer_rows(self, x, trace=None):
         batch = x.shape()[0]
         dt = x.get_datatype()
         cur = x
@@ -334,19 +358,31 @@ class MLP(_Replayable):
                     ct.check_stream().split_lo(cur_lo.buffer, cur.buffer, cur.ecount())
                 nxt = self.layers[idx + 1][0] if idx + 1 < len(self.layers) else None
                 out_lo = self._buffer(("lo", idx), batch, width, dt) if nxt is not None and self.presplit else None
+                if trace:
+                    trace(idx, "begin")
                 lin.forward_presplit(cur, cur_lo, out, out_lo, act if act != "softmax" else None)
+                if trace:
+                    trace(idx, "end")
                 if act == "softmax":
                     ct.softmax(out, out)
                 cur, cur_lo = out, out_lo
                 continue
             cur_lo = None
+            if trace:
+                trace(idx, "begin")
             if self.fused and act in (None, "relu", "tanh", "logistic"):
                 lin.forward_fused(cur, out, act)
+                if trace:
+                    trace(idx, "end")
             elif self.fused and act == "softmax":
                 lin.forward_fused(cur, out, None)
+                if trace:
+                    trace(idx, "end")
                 ct.softmax(out, out)
             else:
                 lin.forward(cur, out)
+                if trace:
+                    trace(idx, "end")
                 if act == "softmax":
                     ct.softmax(out, out)
                 elif act is not None:

@@ -285,8 +285,9 @@ int cb200_pooling_forward(cb200_stream* s, int dtype, void* out, const cb200_dim
 
 /* ---- optimiser steps and rand! (the ring of the training path that touches the flat parameter buffer) ----
  * adam_step: resources/adam.cu:1-36 (the kernel this replaces), src/cortex/optimize/adam.clj:68-102 (CPU
- * arithmetic, which this follows bit for bit) and :123-142 (call site: scalars cast to the buffer type; m and v
- * arrive already offset by the parameter offset).  One pass:
+ * arithmetic: double buffers follow it bit for bit, float buffers are evaluated in single precision like the
+ * reference's CUDA kernel) and :123-142 (call site: scalars cast to the buffer type; m and v arrive already
+ * offset by the parameter offset).  One pass:
  *   g = gradient_alpha*grad;  m = beta1*m + (1-beta1)*g;  v = beta2*v + (1-beta2)*g*g;
  *   param -= alpha * (m / ((1 - pow_beta1_t) * (sqrt(v / (1 - pow_beta2_t)) + epsilon)))        float / double */
 int cb200_adam_step(cb200_stream* s, int dtype, double alpha, double beta1, double beta2, double epsilon,

