@@ -3,10 +3,16 @@
 // src/cortex/compute/cuda/tensor_math.clj:662-730; arithmetic after the CPU backend,
 // src/cortex/compute/cpu/tensor_math.clj:731-801):
 //   inv_std[c] = (T) sqrt(1 / (variance[c] + (T)epsilon))           computed in double, rounded to T
-//   out = ((x - mean[c]) * inv_std[c]) * scale[c] + bias[c]         in double, every step rounded (no fma),
-//                                                                   one final rounding to T
+//   out = ((x - mean[c]) * inv_std[c]) * scale[c] + bias[c]
+// double tensors: every step in double, rounded (no fma), as the CPU backend: bit-identical to it.
+// float tensors: the CPU backend widens every operand to double and rounds once at the end; here the three
+// operations run in single precision (subtract, multiply, fused multiply-add: three roundings instead of
+// one, |error| <= ~2 ulp, bound 1e-4): two f32<->f64 conversions per element go through a quarter-rate pipe
+// and held the pass at 0.7 of the HBM copy rate.
 // eltwise: input [batch, elements], c = column.  spatial: input [batch, channels, elements], c = channel.
 // One pass over the data with 16-byte accesses; inv_std comes from a tiny pre-pass into the stream's scratch.
+// Spatial inputs with long channel slabs are walked slab by slab (the channel's four parameters are read once
+// per slab, no division per element); everything else takes the flat kernel with 32-bit index arithmetic.
 #include "common.cuh"
 
 namespace {
@@ -17,10 +23,43 @@ __global__ void bn_inv_std_kernel(T* inv_std, const T* variances, double eps_t, 
   if (c < channels) inv_std[c] = (T)sqrt(1.0 / ((double)variances[c] + eps_t));
 }
 
-template <typename T>
-__device__ __forceinline__ T bn_one(T x, double mean, double inv_std, double scale, double bias) {
-  const double x_hat = __dmul_rn(__dsub_rn((double)x, mean), inv_std);
-  return (T)__dadd_rn(__dmul_rn(x_hat, scale), bias);
+__device__ __forceinline__ double bn_one(double x, double mean, double inv_std, double scale, double bias) {
+  const double x_hat = __dmul_rn(__dsub_rn(x, mean), inv_std);
+  return __dadd_rn(__dmul_rn(x_hat, scale), bias);
+}
+__device__ __forceinline__ float bn_one(float x, float mean, float inv_std, float scale, float bias) {
+  return __fmaf_rn(__fmul_rn(__fsub_rn(x, mean), inv_std), scale, bias);
+}
+
+// spatial, long slabs: block b walks slabs b, b + grid, ...; slab = (image, channel), `inner` contiguous elements
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+bn_slab_kernel(T* out, const T* in, const T* means, const T* inv_std, const T* scale, const T* bias, long long slabs,
+               int inner, int channels) {
+  struct alignas(sizeof(T) * VEC) V { T v[VEC]; };
+  const int nvec = inner / VEC;
+  for (long long slab = blockIdx.x; slab < slabs; slab += gridDim.x) {
+    const int c = (int)(slab % channels);
+    const T m = means[c], sd = inv_std[c], g = scale[c], b = bias[c];
+    const V* src = reinterpret_cast<const V*>(in + slab * inner);
+    V* dst = reinterpret_cast<V*>(out + slab * inner);
+    int j = threadIdx.x;
+    for (; j + 3 * 256 < nvec; j += 4 * 256) {
+      V x0 = src[j], x1 = src[j + 256], x2 = src[j + 512], x3 = src[j + 768];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        x0.v[e] = bn_one(x0.v[e], m, sd, g, b); x1.v[e] = bn_one(x1.v[e], m, sd, g, b);
+        x2.v[e] = bn_one(x2.v[e], m, sd, g, b); x3.v[e] = bn_one(x3.v[e], m, sd, g, b);
+      }
+      dst[j] = x0; dst[j + 256] = x1; dst[j + 512] = x2; dst[j + 768] = x3;
+    }
+    for (; j < nvec; j += 256) {
+      V x0 = src[j];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) x0.v[e] = bn_one(x0.v[e], m, sd, g, b);
+      dst[j] = x0;
+    }
+  }
 }
 
 // channel of flat element i: (i / inner) % channels   (eltwise: inner = 1, channels = elements)
@@ -29,30 +68,39 @@ __global__ void __launch_bounds__(256)
 bn_apply_kernel(T* out, const T* in, const T* means, const T* inv_std, const T* scale, const T* bias, long long n,
                 int inner, int channels) {
   struct alignas(sizeof(T) * VEC) V { T v[VEC]; };
-  const long long nvec = n / VEC;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+  // n < 2^32 (checked by the caller): element indexes and their divisions stay 32-bit
+  const unsigned nvec = (unsigned)(n / VEC);
+  const unsigned uinner = (unsigned)inner, uch = (unsigned)channels;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += gridDim.x * blockDim.x) {
     const V x = reinterpret_cast<const V*>(in)[i];
     V o;
-    const long long e0 = i * VEC;
+    const unsigned e0 = i * VEC;
     if (inner % VEC == 0) {
       // the whole vector lies in one channel
-      const int c = (int)((e0 / inner) % channels);
-      const double m = means[c], s = inv_std[c], g = scale[c], b = bias[c];
+      const unsigned c = (e0 / uinner) % uch;
+      const T m = means[c], s = inv_std[c], g = scale[c], b = bias[c];
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) o.v[e] = bn_one<T>(x.v[e], m, s, g, b);
+      for (int e = 0; e < VEC; ++e) o.v[e] = bn_one(x.v[e], m, s, g, b);
+    } else if (inner == 1) {
+      unsigned c = e0 % uch;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        o.v[e] = bn_one(x.v[e], means[c], inv_std[c], scale[c], bias[c]);
+        if (++c == uch) c = 0;
+      }
     } else {
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        const int c = (int)(((e0 + e) / inner) % channels);
-        o.v[e] = bn_one<T>(x.v[e], means[c], inv_std[c], scale[c], bias[c]);
+        const unsigned c = ((e0 + e) / uinner) % uch;
+        o.v[e] = bn_one(x.v[e], means[c], inv_std[c], scale[c], bias[c]);
       }
     }
     reinterpret_cast<V*>(out)[i] = o;
   }
   // tail
-  for (long long i = nvec * VEC + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)((i / inner) % channels);
-    out[i] = bn_one<T>(in[i], means[c], inv_std[c], scale[c], bias[c]);
+  for (unsigned i = nvec * VEC + blockIdx.x * blockDim.x + threadIdx.x; i < (unsigned)n; i += gridDim.x * blockDim.x) {
+    const unsigned c = (i / uinner) % uch;
+    out[i] = bn_one(in[i], means[c], inv_std[c], scale[c], bias[c]);
   }
 }
 
@@ -72,7 +120,11 @@ int bn_launch(cb200_stream* s, T* out, const T* in, const T* means, const T* var
   long long blocks = (n / VEC + 255) / 256 + 1;
   const long long cap = (long long)s->sm_count * 16;
   if (blocks > cap) blocks = cap;
-  if (aligned)
+  if (aligned && inner >= 256 * VEC && (inner % VEC) == 0) {
+    const long long slabs = batch * channels;
+    long long sb = slabs < cap ? slabs : cap;
+    bn_slab_kernel<T, VEC><<<(unsigned)sb, 256, 0, s->stream>>>(out, in, means, inv_std, scale, bias, slabs, inner, channels);
+  } else if (aligned)
     bn_apply_kernel<T, VEC><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, means, inv_std, scale, bias, n, inner, channels);
   else
     bn_apply_kernel<T, 1><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, means, inv_std, scale, bias, n, inner, channels);
@@ -86,7 +138,7 @@ int bn_entry(cb200_stream* s, int dtype, void* out, const void* in, const void* 
   CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "batch-normalization is only defined for float and double tensors");
   CB_REQUIRE(batch >= 0 && channels >= 1 && inner >= 1 && channels <= 2147483647LL && inner <= 2147483647LL,
              "batch_normalize: bad extents");
-  CB_REQUIRE(batch * channels * inner <= 2147483647LL * 4, "batch_normalize: too many elements");
+  CB_REQUIRE(batch * channels * inner < 4294967296LL, "batch_normalize: more than 2^32 - 1 elements");
   if (batch == 0) return CB200_OK;
   if (dtype == CB200_FLOAT)
     return bn_launch<float>(s, (float*)out, (const float*)in, (const float*)means, (const float*)variances,

@@ -1,0 +1,458 @@
+// fp32 convolution-forward! (stride 1) as an implicit GEMM whose A operand -- the rows of the im2col
+// matrix of the reference CPU backend (src/cortex/compute/cpu/tensor_math.clj:1118-1131, loop nest of
+// src/cortex/nn/impl.clj:8-90) -- is fetched by TMA: no thread touches an input element.
+//
+//   M = batch*outH*outW output pixels, N = C_out, K = C_in*kH*kW
+//   out[pixel, co] = sum_k im2col[pixel, k] * W[co, k]   (+ out_alpha * out)
+//
+// K runs channel-block-major / tap-inner: k' = ((c / 16)*kH*kW + ky*kW + kx)*16 + c % 16, so one 16-wide
+// k-block is ONE filter tap (ky, kx) of 16 consecutive channels.  For such a k-block the A tile of a
+// rectangular patch of output pixels is a rectangular patch of the input, shifted by (kx - pad, ky - pad):
+// one tiled TMA load, whose out-of-bounds zero fill supplies the padding.  Two things stand between the
+// NCHW input and that load, and one pre-pass removes both:
+//   * a TMA copy must start on a 16-byte boundary of the innermost dimension, and in NCHW the innermost
+//     dimension is x, where the tap shift kx - pad lands on arbitrary elements;
+//   * the tensor core wants either 32 pixels contiguous per k value (MN-major) or the k values of a pixel
+//     contiguous (K-major); a shifted NCHW patch is neither.
+// `nchw_to_nhwc_split_kernel` writes the input once as NHWC, already split for the 3xTF32 product into
+// hi = x and lo = x - trunc_tf32(x) (one HBM-bound pass: input read once, two copies written).  In NHWC the
+// innermost dimension is the channel (always a multiple of 16 here), x and y are free coordinates, and a box
+// {16 channels, bx, by} lands in shared memory as bx*by pixel rows of 64 bytes: exactly the K-major,
+// 64-byte-swizzled operand tile of the GEMM kernels.  A 128-row CTA tile is 1, 2 or 4 such boxes (picked per
+// geometry so that the boxes tile the output with the least overhang: 56x56 is covered exactly by 8x8 boxes).
+// The weights are permuted to the same k order and split into hi / lo by `conv_prep_weights` (scratch), so
+// every operand tile -- A_hi, A_lo, W_hi, W_lo -- arrives by TMA and the main loop contains no generic-proxy
+// pass, no proxy fence and no thread-issued load.  Warp roles: 8 = A_hi boxes, 10 = A_lo boxes, 11 = W tiles,
+// 9 = TMEM owner + MMA issuer, 0-7 = epilogue (TMEM -> registers -> NCHW stores).  Only the order of the fp32
+// summation over k differs from the reference.  Every wait is bounded (sm100.cuh).
+#include "common.cuh"
+#include "sm100.cuh"
+#include <mutex>
+
+using namespace sm100;
+
+namespace {
+
+constexpr int TBM = 128;            // pixel rows per CTA tile
+constexpr int TBK = 16;             // k values per stage
+constexpr int T_EPI_WARPS = 8;
+constexpr int T_THREADS = (T_EPI_WARPS + 4) * 32;
+
+struct TmaConvParams {
+  float* out;
+  float out_alpha;
+  int batch, cout, out_h, out_w, kh, kw, pad_x, pad_y;
+  int bx, by, nbox;         // one box = bx x by output pixels; nbox * bx * by = 128
+  int tiles_x, tiles_y;     // boxes per image along x / y
+  int n_boxes;              // batch * tiles_x * tiles_y
+  int nkb;                  // (C_in / 16) * kH * kW
+  int* status;
+};
+
+template <int BN> struct TmaConvCfg {
+  static constexpr int A_TILE = TBM * TBK * 4;          // 8 KiB
+  static constexpr int B_TILE = BN * TBK * 4;
+  static constexpr int RAW = A_TILE + B_TILE;
+  static constexpr int STAGE = 2 * RAW;                 // A_hi | W_hi | A_lo | W_lo
+  static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
+  static constexpr int BUDGET = 196608 / CTAS_PER_SM;
+  static constexpr int STAGES = (BUDGET / STAGE) > 8 ? 8 : (BUDGET / STAGE);
+  // narrow tiles: one (main, cross) accumulator pair per k-step of a k-block
+  static constexpr int ACC_SETS = BN <= 64 ? 2 : 1;
+  static constexpr int TMEM_COLS = 2 * BN * ACC_SETS;
+  static constexpr int SMEM = STAGES * STAGE + 1024 + 256;
+};
+
+__device__ __forceinline__ float tconv_lo_part(float x) {
+  const uint32_t xb = __float_as_uint(x);
+  const float lo = x - __uint_as_float(xb & 0xffffe000u);
+  return ((xb & 0x7f800000u) == 0x7f800000u) ? 0.f : lo;
+}
+
+// 4-d tiled load {c, x, y, n} into this CTA's shared memory; c * 4 bytes must be a multiple of 16, the other
+// coordinates are free and may lie outside the tensor (the box is zero-filled there)
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"((uint64_t)tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+
+// in [N][C][HW]  ->  hi / lo [N][HW][C]   (hi = x, lo = x - trunc_tf32(x)); 32 x 32 tiles through shared memory
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_split_kernel(const float* __restrict__ in, float* __restrict__ hi, float* __restrict__ lo, int C, int HW) {
+  __shared__ float t[32][33];
+  const long long img = (long long)blockIdx.z * C * HW;
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = c0 + threadIdx.y + 8 * j, p = p0 + threadIdx.x;
+    if (c < C && p < HW) t[threadIdx.y + 8 * j][threadIdx.x] = in[img + (long long)c * HW + p];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int p = p0 + threadIdx.y + 8 * j, c = c0 + threadIdx.x;
+    if (p < HW && c < C) {
+      const float v = t[threadIdx.x][threadIdx.y + 8 * j];
+      hi[img + (long long)p * C + c] = v;
+      lo[img + (long long)p * C + c] = tconv_lo_part(v);
+    }
+  }
+}
+
+// W[cout][c*khkw + t]  ->  hi / lo [cout][((c/16)*khkw + t)*16 + c%16]
+__global__ void __launch_bounds__(256)
+tconv_prep_weights_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int cout, int cin,
+                          int khkw) {
+  const int K = cin * khkw;
+  const int total = cout * K;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int co = i / K, kp = i - co * K;
+    const int blk = kp >> 4, c16 = kp & 15;
+    const int cb = blk / khkw, t = blk - cb * khkw;
+    const float x = w[(long long)co * K + (cb * 16 + c16) * khkw + t];
+    hi[i] = x;
+    lo[i] = tconv_lo_part(x);
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(T_THREADS, TmaConvCfg<BN>::CTAS_PER_SM)
+conv_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlo,
+                const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWlo, TmaConvParams p) {
+  typedef TmaConvCfg<BN> Cfg;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int A_TILE = Cfg::A_TILE, B_TILE = Cfg::B_TILE, RAW = Cfg::RAW;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::STAGE);
+  // bars[0..S) full (three producers), [S..2S) empty, [2S] accumulators ready
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (p.cout + BN - 1) / BN;
+  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
+  const int n0 = tile_n * BN;
+  const int box0 = tile_m * p.nbox;                                   // first box of this tile
+  const int boxes_here = min(p.nbox, p.n_boxes - box0);
+  const int per_img = p.tiles_x * p.tiles_y;
+  const int box_rows = p.bx * p.by;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES), bar_acc = smem_u32(bars + 2 * STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 3);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == T_EPI_WARPS + 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (lane == 0) {
+    if (warp == T_EPI_WARPS) tma_prefetch_desc(&tmA);
+    if (warp == T_EPI_WARPS + 2) tma_prefetch_desc(&tmAlo);
+    if (warp == T_EPI_WARPS + 3) { tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmWlo); }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == T_EPI_WARPS || warp == T_EPI_WARPS + 2) {
+    // ---------------- A producers: warp 8 the hi boxes, warp 10 the lo boxes ----------------
+    // the whole warp runs the loop (warp-uniform control flow); one elected lane issues
+    const bool is_hi = warp == T_EPI_WARPS;
+    const CUtensorMap* map = is_hi ? &tmA : &tmAlo;
+    const uint32_t tile_off = is_hi ? 0u : (uint32_t)RAW;
+    const uint32_t box_bytes = (uint32_t)box_rows * TBK * 4;
+    // coordinates of this tile's boxes (image, first input column / row at tap (0, 0))
+    int bn[4], bx0[4], by0[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int id = box0 + b;
+      const int img = id / per_img, rem = id - img * per_img;
+      bn[b] = img;
+      by0[b] = (rem / p.tiles_x) * p.by - p.pad_y;
+      bx0[b] = (rem % p.tiles_x) * p.bx - p.pad_x;
+    }
+    int issued = 0, s = 0, cb = 0, ky = 0, kx = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < p.nkb; ++i) {
+      if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1000 + s)) break;
+      const uint32_t full = bar_full + 8 * s;
+      const uint32_t dst = smem_base + s * Cfg::STAGE + tile_off;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(full, box_bytes * boxes_here);
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (b < boxes_here) tma_load_4d(dst + b * box_bytes, map, cb * 16, bx0[b] + kx, by0[b] + ky, bn[b], full);
+      }
+      __syncwarp();
+      issued = i + 1;
+      if (++kx == p.kw) { kx = 0; if (++ky == p.kh) { ky = 0; ++cb; } }
+      if (++s == STAGES) { s = 0; ph ^= 1; }
+    }
+    if (*abort_flag) {
+      // let copies already issued land before this CTA gives its shared memory back
+      for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+        for (int it = 0; it < (1 << 16); ++it)
+          if (mbar_try_wait(bar_full + 8 * (i % STAGES), (i / STAGES) & 1)) break;
+    }
+  } else if (warp == T_EPI_WARPS + 3) {
+    // ---------------- W producer: hi and lo tiles of this CTA's output channels ----------------
+    int issued = 0, s = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < p.nkb; ++i) {
+      if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1100 + s)) break;
+      const uint32_t full = bar_full + 8 * s;
+      const uint32_t dst = smem_base + s * Cfg::STAGE + A_TILE;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(full, 2 * B_TILE);
+        tma_load_2d(dst, &tmW, i * TBK, n0, full);
+        tma_load_2d(dst + RAW, &tmWlo, i * TBK, n0, full);
+      }
+      __syncwarp();
+      issued = i + 1;
+      if (++s == STAGES) { s = 0; ph ^= 1; }
+    }
+    if (*abort_flag) {
+      for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+        for (int it = 0; it < (1 << 16); ++it)
+          if (mbar_try_wait(bar_full + 8 * (i % STAGES), (i / STAGES) & 1)) break;
+    }
+  } else if (warp == T_EPI_WARPS + 1) {
+    // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+    const uint32_t idesc = make_idesc_tf32(TBM, BN, 0, 0);
+    // both operands K-major: 64-byte rows (16 k values), 8-row groups 512 B apart, 32 B per k-step
+    const uint64_t d_a = make_smem_desc(smem_base, 16, 8 * TBK * 4, SWZ_64B);
+    const uint64_t d_b = make_smem_desc(smem_base + A_TILE, 16, 8 * TBK * 4, SWZ_64B);
+    const uint32_t a_hiw = (uint32_t)(d_a >> 32), b_hiw = (uint32_t)(d_b >> 32);
+    const uint32_t a_low0 = (uint32_t)d_a, b_low0 = (uint32_t)d_b;
+    constexpr uint32_t LO_TILE = RAW >> 4, STAGE_STEP = Cfg::STAGE >> 4;
+    uint32_t accumulate[2] = {0, 0};
+    int s = 0;
+    uint32_t ph = 0, stage_off = 0;
+    for (int i = 0; i < p.nkb; ++i) {
+      if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 1200 + s)) break;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < TBK / 8; ++kk) {
+          const uint32_t al = a_low0 + stage_off + kk * 2, bl = b_low0 + stage_off + kk * 2;
+          const int set = Cfg::ACC_SETS == 2 ? kk : 0;
+          const uint32_t tmem_main = tmem_base + set * 2 * BN, tmem_cross = tmem_main + BN;
+          const uint32_t acc = (Cfg::ACC_SETS == 1 && kk) ? 1u : accumulate[set];
+          mma_tf32_ss_words(tmem_cross, al + LO_TILE, a_hiw, bl, b_hiw, idesc, acc);
+          mma_tf32_ss_words(tmem_main, al, a_hiw, bl, b_hiw, idesc, acc);
+          mma_tf32_ss_words(tmem_cross, al, a_hiw, bl + LO_TILE, b_hiw, idesc, 1);
+        }
+        mma_commit(bar_empty + 8 * s);
+      }
+      accumulate[0] = accumulate[1] = 1;
+      __syncwarp();
+      if (++s == STAGES) { s = 0; ph ^= 1; stage_off = 0; } else { stage_off += STAGE_STEP; }
+    }
+    if (elect_one()) mma_commit(bar_acc);
+    __syncwarp();
+    if (*abort_flag) {
+      for (int it = 0; it < (1 << 16); ++it)
+        if (mbar_try_wait(bar_acc, 0)) break;
+    }
+  } else {
+    // ---------------- epilogue (warps 0-7): this tile's accumulators -> NCHW ----------------
+    bool ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 1300);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    if (ok) {
+      const int q = warp & 3, half = warp >> 2;
+      const int row = q * 32 + lane;                      // tile row = TMEM lane
+      const int b = row / box_rows, within = row - b * box_rows;
+      const int id = box0 + b;
+      const int img = id / per_img, rem = id - img * per_img;
+      const int oy = (rem / p.tiles_x) * p.by + within / p.bx;
+      const int ox = (rem % p.tiles_x) * p.bx + within % p.bx;
+      const bool row_ok = b < boxes_here && oy < p.out_h && ox < p.out_w;
+      const long long hw = (long long)p.out_h * p.out_w;
+      float* obase = p.out + (long long)img * p.cout * hw + (long long)oy * p.out_w + ox;
+      constexpr int COLS_PER_HALF = BN / 2;
+#pragma unroll 1
+      for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
+        const int col0 = half * COLS_PER_HALF + cc * 32;
+        uint32_t r[32], t[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
+        tmem_ld_wait();
+#pragma unroll 1
+        for (int a = 1; a < 2 * Cfg::ACC_SETS; ++a) {
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + col0), t);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(t[j]));
+        }
+        const int nb = n0 + col0;
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (nb + j < p.cout) {
+              float* cp = obase + (long long)(nb + j) * hw;     // lanes of a box row = adjacent pixels
+              float o = __uint_as_float(r[j]);
+              if (p.out_alpha != 0.f) o += p.out_alpha * (*cp);
+              *cp = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == T_EPI_WARPS + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn tconv_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)f;
+  });
+  return fn;
+}
+
+// NHWC activations [N][H][W][C] as the 4-d tensor {C, W, H, N}; box {16, bx, by, 1}
+int encode_nhwc(CUtensorMap* tm, const float* base, int C, int W, int H, int N, int bx, int by) {
+  EncodeTiledFn fn = tconv_encode_fn();
+  if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
+  cuuint64_t gdim[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+  cuuint64_t gstride[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
+  cuuint32_t box[4] = {(cuuint32_t)TBK, (cuuint32_t)bx, (cuuint32_t)by, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)base, gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    cb200_set_error("cuTensorMapEncodeTiled failed with %d for the NHWC input (C %d W %d H %d N %d box %dx%d)", (int)r, C,
+                    W, H, N, bx, by);
+    return CB200_ERR_CUDA;
+  }
+  return CB200_OK;
+}
+
+int encode_w(CUtensorMap* tm, const float* w, int K, int cout, int BN) {
+  EncodeTiledFn fn = tconv_encode_fn();
+  if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
+  cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)cout};
+  cuuint64_t gstride[1] = {(cuuint64_t)K * 4};
+  cuuint32_t box[2] = {(cuuint32_t)TBK, (cuuint32_t)BN};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)w, gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { cb200_set_error("cuTensorMapEncodeTiled failed with %d for the weights", (int)r); return CB200_ERR_CUDA; }
+  return CB200_OK;
+}
+
+template <int BN>
+int launch_tconv(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmAlo, const CUtensorMap& tmW,
+                 const CUtensorMap& tmWlo, const TmaConvParams& p) {
+  typedef TmaConvCfg<BN> Cfg;
+  static std::once_flag once[64];
+  cudaError_t attr_err = cudaSuccess;
+  std::call_once(once[s->device & 63], [&] {
+    attr_err = cudaFuncSetAttribute(conv_tma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  });
+  if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
+  const long long tiles_m = (p.n_boxes + p.nbox - 1) / p.nbox;
+  const long long tiles = tiles_m * ((p.cout + BN - 1) / BN);
+  conv_tma_kernel<BN><<<(unsigned)tiles, T_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmAlo, tmW, tmWlo, p);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+}  // namespace
+
+// Which box tiles the output with the least overhang: bx * by in {128, 64, 32}, both powers of two.
+// Returns the padded / real pixel ratio (>= 1), or 0 when no geometry qualifies.
+double cb200_conv_tma_plan(int out_w, int out_h, int* bx_out, int* by_out, int* nbox_out) {
+  double best = 0.0;
+  // candidates in order of preference (fewer boxes per tile, then wider rows for the stores): only a strictly
+  // smaller overhang replaces an earlier one
+  for (int rows = 128; rows >= 32; rows /= 2) {
+    for (int bx = rows; bx >= 1; bx /= 2) {
+      const int by = rows / bx;
+      if (bx > 256 || by > 256) continue;
+      const long long padded = (long long)((out_w + bx - 1) / bx) * bx * ((out_h + by - 1) / by) * by;
+      const double ratio = (double)padded / ((double)out_w * out_h);
+      if (best == 0.0 || ratio < best - 1e-9) {
+        best = ratio; *bx_out = bx; *by_out = by; *nbox_out = 128 / rows;
+      }
+    }
+  }
+  return best;
+}
+
+// Eligible: stride 1, C_in a multiple of 16, the output tiles with <= 35 % overhang.
+bool cb200_conv_tma_eligible(int cin, int out_w, int out_h, int stride_x, int stride_y, long long in_elems) {
+  if (stride_x != 1 || stride_y != 1 || (cin % 16) != 0 || in_elems >= 2147483647LL) return false;
+  int bx, by, nbox;
+  const double ratio = cb200_conv_tma_plan(out_w, out_h, &bx, &by, &nbox);
+  return ratio > 0.0 && ratio <= 1.35;
+}
+
+int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
+                          int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
+                          float out_alpha) {
+  DeviceGuard guard(s->device);
+  TmaConvParams p;
+  p.out = out; p.out_alpha = out_alpha; p.batch = batch; p.cout = cout; p.out_h = out_h; p.out_w = out_w;
+  p.kh = kh; p.kw = kw; p.pad_x = pad_x; p.pad_y = pad_y; p.status = s->status_dev;
+  cb200_conv_tma_plan(out_w, out_h, &p.bx, &p.by, &p.nbox);
+  p.tiles_x = (out_w + p.bx - 1) / p.bx;
+  p.tiles_y = (out_h + p.by - 1) / p.by;
+  p.n_boxes = batch * p.tiles_x * p.tiles_y;
+  p.nkb = (cin / 16) * kh * kw;
+  const int K = cin * kh * kw;
+  const size_t in_elems = (size_t)batch * cin * in_h * in_w, w_elems = (size_t)cout * K;
+  void* scratch = nullptr;
+  int rc = cb200_scratch(s, (2 * in_elems + 2 * w_elems) * sizeof(float), &scratch);
+  if (rc) return rc;
+  float* a_hi = (float*)scratch;
+  float* a_lo = a_hi + in_elems;
+  float* w_hi = a_lo + in_elems;
+  float* w_lo = w_hi + w_elems;
+  const int hw = in_h * in_w;
+  dim3 tgrid((unsigned)((hw + 31) / 32), (unsigned)((cin + 31) / 32), (unsigned)batch);
+  nchw_to_nhwc_split_kernel<<<tgrid, dim3(32, 8, 1), 0, s->stream>>>(in, a_hi, a_lo, cin, hw);
+  CB_LAUNCH_CHECK(s);
+  int blocks = (int)((w_elems + 255) / 256);
+  if (blocks > s->sm_count * 8) blocks = s->sm_count * 8;
+  tconv_prep_weights_kernel<<<blocks, 256, 0, s->stream>>>(w, w_hi, w_lo, cout, cin, kh * kw);
+  CB_LAUNCH_CHECK(s);
+  const int BN = cout > 128 ? 256 : (cout > 64 ? 128 : 64);
+  CUtensorMap tmA, tmAlo, tmW, tmWlo;
+  if ((rc = encode_nhwc(&tmA, a_hi, cin, in_w, in_h, batch, p.bx, p.by))) return rc;
+  if ((rc = encode_nhwc(&tmAlo, a_lo, cin, in_w, in_h, batch, p.bx, p.by))) return rc;
+  if ((rc = encode_w(&tmW, w_hi, K, cout, BN))) return rc;
+  if ((rc = encode_w(&tmWlo, w_lo, K, cout, BN))) return rc;
+  if (BN == 256) return launch_tconv<256>(s, tmA, tmAlo, tmW, tmWlo, p);
+  if (BN == 128) return launch_tconv<128>(s, tmA, tmAlo, tmW, tmWlo, p);
+  return launch_tconv<64>(s, tmA, tmAlo, tmW, tmWlo, p);
+}
