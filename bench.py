@@ -446,8 +446,13 @@ def bench_eltwise(drv, dev, peaks):
         adam, adadelta = optimize.Adam().batch_update(), optimize.Adadelta()
         cases["adam_step_64Mi"] = (lambda i: adam.compute_parameters(
             {"m": opt_sets[i % 2][2], "v": opt_sets[i % 2][3]}, 1.0, 0, opt_sets[i % 2][0], opt_sets[i % 2][1]), 7 * n_par * 4)
+        # adadelta's accumulators are running averages of squares: non-negative (adam's m above is not)
+        acc_sets = [[ct.new_tensor([n_par]) for _ in range(2)] for _ in range(2)]
+        for st_ in acc_sets:
+            for t_ in st_:
+                ct.rand(t_, ct.flat_distribution(minimum=0.0, maximum=0.01))
         cases["adadelta_step_64Mi"] = (lambda i: adadelta.compute_parameters(
-            {"grad-accum": opt_sets[i % 2][2], "dx-accum": opt_sets[i % 2][3]}, 1.0, 0, opt_sets[i % 2][0],
+            {"grad-accum": acc_sets[i % 2][0], "dx-accum": acc_sets[i % 2][1]}, 1.0, 0, opt_sets[i % 2][0],
             opt_sets[i % 2][1]), 7 * n_par * 4)
         cases["rand_gaussian_64Mi"] = (lambda i: ct.rand(opt_sets[i % 2][0], ct.gaussian_distribution()), n_par * 4)
         cases["rand_flat_64Mi"] = (lambda i: ct.rand(opt_sets[i % 2][0], ct.flat_distribution()), n_par * 4)

@@ -23,7 +23,12 @@
 // The weights are permuted to the same k order and split into hi / lo by `conv_prep_weights` (scratch), so
 // every operand tile -- A_hi, A_lo, W_hi, W_lo -- arrives by TMA and the main loop contains no generic-proxy
 // pass, no proxy fence and no thread-issued load.  Warp roles: 8 = A_hi boxes, 10 = A_lo boxes, 11 = W tiles,
-// 9 = TMEM owner + MMA issuer, 0-7 = epilogue (TMEM -> registers -> NCHW stores).  Only the order of the fp32
+// 9 = TMEM owner + MMA issuer, 0-7 = epilogue (TMEM -> registers -> NCHW stores).  W_lo is staged right behind
+// W_hi, so hi x [hi | lo] is ONE instruction of width 2*C_out-tile (main product and the hi x lo cross term side by
+// side in TMEM) and lo x hi a second one onto the cross columns: two MMAs per k-step instead of three.
+// Persistent CTAs (two per SM for 64-channel tiles, one otherwise), two accumulator buffers in TMEM each.  What bounds it at C_out = 64: shared-memory
+// bandwidth (per 16-wide k-block the tensor core reads 28 KB of operands and TMA writes 24 KB: ~52 KB per
+// ~440 cycles against 128 B/clk), not the tensor pipe (224 cycles) and not HBM.  Only the order of the fp32
 // summation over k differs from the reference.  Every wait is bounded (sm100.cuh).
 #include "common.cuh"
 #include "sm100.cuh"
@@ -53,13 +58,16 @@ template <int BN> struct TmaConvCfg {
   static constexpr int A_TILE = TBM * TBK * 4;          // 8 KiB
   static constexpr int B_TILE = BN * TBK * 4;
   static constexpr int RAW = A_TILE + B_TILE;
-  static constexpr int STAGE = 2 * RAW;                 // A_hi | W_hi | A_lo | W_lo
+  static constexpr int STAGE = 2 * RAW;                 // A_hi | W_hi | W_lo | A_lo
+  static constexpr int A_LO_OFF = A_TILE + 2 * B_TILE;  // W_lo sits right behind W_hi: together one 2*BN-row operand
+  // 64-channel tiles: TWO persistent CTAs per SM.  One issuing thread sustains one of these narrow MMAs per
+  // ~135 cycles (measured: a k-block of four took ~540 cycles per CTA whether one or two CTAs shared the SM),
+  // the tensor pipe needs only 48-64 cycles for each, so two issuers are needed to keep it busy.
   static constexpr int CTAS_PER_SM = BN <= 64 ? 2 : 1;
   static constexpr int BUDGET = 196608 / CTAS_PER_SM;
   static constexpr int STAGES = (BUDGET / STAGE) > 8 ? 8 : (BUDGET / STAGE);
-  // narrow tiles: one (main, cross) accumulator pair per k-step of a k-block
-  static constexpr int ACC_SETS = BN <= 64 ? 2 : 1;
-  static constexpr int TMEM_COLS = 2 * BN * ACC_SETS;
+  // two accumulator buffers (main | cross each) so that a tile's read-out overlaps the next tile's MMAs
+  static constexpr int TMEM_COLS = 4 * BN;
   static constexpr int SMEM = STAGES * STAGE + 1024 + 256;
 };
 
@@ -117,38 +125,47 @@ tconv_prep_weights_kernel(const float* __restrict__ w, float* __restrict__ hi, f
   }
 }
 
+// Persistent: CTA c computes tiles c, c + grid, ...  The three producers run ahead across tile boundaries; the
+// MMA warp alternates between two accumulator buffers in TMEM; the eight epilogue warps read a finished buffer
+// out into registers, hand it back (bar_acc_empty) and only then store to NCHW -- so the tensor cores never wait
+// for a tile's stores, its launch or its set-up.  (Measured before: one CTA per tile, two per SM: 45 us of the
+// 130 us kernel were per-tile launch / set-up / epilogue, only partly hidden behind the other CTA.)
 template <int BN>
 __global__ void __launch_bounds__(T_THREADS, TmaConvCfg<BN>::CTAS_PER_SM)
 conv_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlo,
                 const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWlo, TmaConvParams p) {
   typedef TmaConvCfg<BN> Cfg;
   constexpr int STAGES = Cfg::STAGES;
-  constexpr int A_TILE = Cfg::A_TILE, B_TILE = Cfg::B_TILE, RAW = Cfg::RAW;
+  constexpr int A_TILE = Cfg::A_TILE, B_TILE = Cfg::B_TILE;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::STAGE);
-  // bars[0..S) full (three producers), [S..2S) empty, [2S] accumulators ready
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  // bars[0..S) full (three producers), [S..2S) empty, [2S..2S+2) accumulator buffer ready, [2S+2..2S+4)
+  // accumulator buffer read out, [2S+4] used only when unwinding: every MMA issued has retired
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 5);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (p.cout + BN - 1) / BN;
-  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
-  const int n0 = tile_n * BN;
-  const int box0 = tile_m * p.nbox;                                   // first box of this tile
-  const int boxes_here = min(p.nbox, p.n_boxes - box0);
+  const int tiles_m = (p.n_boxes + p.nbox - 1) / p.nbox;
+  const int n_tiles = tiles_m * tiles_n;
   const int per_img = p.tiles_x * p.tiles_y;
   const int box_rows = p.bx * p.by;
 
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES), bar_acc = smem_u32(bars + 2 * STAGES);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES), bar_acc_full = smem_u32(bars + 2 * STAGES),
+                 bar_acc_empty = bar_acc_full + 16, bar_retired = bar_acc_full + 32;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 3);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    mbar_init(bar_acc, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, T_EPI_WARPS);
+    }
+    mbar_init(bar_retired, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -171,141 +188,174 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // the whole warp runs the loop (warp-uniform control flow); one elected lane issues
     const bool is_hi = warp == T_EPI_WARPS;
     const CUtensorMap* map = is_hi ? &tmA : &tmAlo;
-    const uint32_t tile_off = is_hi ? 0u : (uint32_t)RAW;
+    const uint32_t tile_off = is_hi ? 0u : (uint32_t)Cfg::A_LO_OFF;
     const uint32_t box_bytes = (uint32_t)box_rows * TBK * 4;
-    // coordinates of this tile's boxes (image, first input column / row at tap (0, 0))
-    int bn[4], bx0[4], by0[4];
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      const int id = box0 + b;
-      const int img = id / per_img, rem = id - img * per_img;
-      bn[b] = img;
-      by0[b] = (rem / p.tiles_x) * p.by - p.pad_y;
-      bx0[b] = (rem % p.tiles_x) * p.bx - p.pad_x;
-    }
-    int issued = 0, s = 0, cb = 0, ky = 0, kx = 0;
+    long long issued = 0;
+    int s = 0;
     uint32_t ph = 0;
-    for (int i = 0; i < p.nkb; ++i) {
-      if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1000 + s)) break;
-      const uint32_t full = bar_full + 8 * s;
-      const uint32_t dst = smem_base + s * Cfg::STAGE + tile_off;
-      if (elect_one()) {
-        mbar_arrive_expect_tx(full, box_bytes * boxes_here);
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+      const int box0 = (tile / tiles_n) * p.nbox;
+      const int boxes_here = min(p.nbox, p.n_boxes - box0);
+      // coordinates of this tile's boxes (image, first input column / row at tap (0, 0))
+      int bn[4], bx0[4], by0[4];
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-          if (b < boxes_here) tma_load_4d(dst + b * box_bytes, map, cb * 16, bx0[b] + kx, by0[b] + ky, bn[b], full);
+      for (int b = 0; b < 4; ++b) {
+        const int id = box0 + b;
+        const int img = id / per_img, rem = id - img * per_img;
+        bn[b] = img;
+        by0[b] = (rem / p.tiles_x) * p.by - p.pad_y;
+        bx0[b] = (rem % p.tiles_x) * p.bx - p.pad_x;
       }
-      __syncwarp();
-      issued = i + 1;
-      if (++kx == p.kw) { kx = 0; if (++ky == p.kh) { ky = 0; ++cb; } }
-      if (++s == STAGES) { s = 0; ph ^= 1; }
+      int cb = 0, ky = 0, kx = 0;
+      for (int i = 0; i < p.nkb; ++i) {
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1000 + s)) { ok = false; break; }
+        const uint32_t full = bar_full + 8 * s;
+        const uint32_t dst = smem_base + s * Cfg::STAGE + tile_off;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(full, box_bytes * boxes_here);
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+            if (b < boxes_here) tma_load_4d(dst + b * box_bytes, map, cb * 16, bx0[b] + kx, by0[b] + ky, bn[b], full);
+        }
+        __syncwarp();
+        ++issued;
+        if (++kx == p.kw) { kx = 0; if (++ky == p.kh) { ky = 0; ++cb; } }
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      }
     }
     if (*abort_flag) {
       // let copies already issued land before this CTA gives its shared memory back
-      for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+      for (long long i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
         for (int it = 0; it < (1 << 16); ++it)
-          if (mbar_try_wait(bar_full + 8 * (i % STAGES), (i / STAGES) & 1)) break;
+          if (mbar_try_wait(bar_full + 8 * (int)(i % STAGES), (uint32_t)((i / STAGES) & 1))) break;
     }
   } else if (warp == T_EPI_WARPS + 3) {
-    // ---------------- W producer: hi and lo tiles of this CTA's output channels ----------------
-    int issued = 0, s = 0;
+    // ---------------- W producer: hi and lo tiles of the tile's output channels ----------------
+    long long issued = 0;
+    int s = 0;
     uint32_t ph = 0;
-    for (int i = 0; i < p.nkb; ++i) {
-      if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1100 + s)) break;
-      const uint32_t full = bar_full + 8 * s;
-      const uint32_t dst = smem_base + s * Cfg::STAGE + A_TILE;
-      if (elect_one()) {
-        mbar_arrive_expect_tx(full, 2 * B_TILE);
-        tma_load_2d(dst, &tmW, i * TBK, n0, full);
-        tma_load_2d(dst + RAW, &tmWlo, i * TBK, n0, full);
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+      const int n0 = (tile % tiles_n) * BN;
+      for (int i = 0; i < p.nkb; ++i) {
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1100 + s)) { ok = false; break; }
+        const uint32_t full = bar_full + 8 * s;
+        const uint32_t dst = smem_base + s * Cfg::STAGE + A_TILE;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(full, 2 * B_TILE);
+          tma_load_2d(dst, &tmW, i * TBK, n0, full);
+          tma_load_2d(dst + B_TILE, &tmWlo, i * TBK, n0, full);
+        }
+        __syncwarp();
+        ++issued;
+        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
-      __syncwarp();
-      issued = i + 1;
-      if (++s == STAGES) { s = 0; ph ^= 1; }
     }
     if (*abort_flag) {
-      for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
+      for (long long i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
         for (int it = 0; it < (1 << 16); ++it)
-          if (mbar_try_wait(bar_full + 8 * (i % STAGES), (i / STAGES) & 1)) break;
+          if (mbar_try_wait(bar_full + 8 * (int)(i % STAGES), (uint32_t)((i / STAGES) & 1))) break;
     }
   } else if (warp == T_EPI_WARPS + 1) {
     // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
     const uint32_t idesc = make_idesc_tf32(TBM, BN, 0, 0);
+    const uint32_t idesc_wide = make_idesc_tf32(TBM, 2 * BN, 0, 0);
     // both operands K-major: 64-byte rows (16 k values), 8-row groups 512 B apart, 32 B per k-step
     const uint64_t d_a = make_smem_desc(smem_base, 16, 8 * TBK * 4, SWZ_64B);
     const uint64_t d_b = make_smem_desc(smem_base + A_TILE, 16, 8 * TBK * 4, SWZ_64B);
     const uint32_t a_hiw = (uint32_t)(d_a >> 32), b_hiw = (uint32_t)(d_b >> 32);
     const uint32_t a_low0 = (uint32_t)d_a, b_low0 = (uint32_t)d_b;
-    constexpr uint32_t LO_TILE = RAW >> 4, STAGE_STEP = Cfg::STAGE >> 4;
-    uint32_t accumulate[2] = {0, 0};
+    constexpr uint32_t A_LO = Cfg::A_LO_OFF >> 4, STAGE_STEP = Cfg::STAGE >> 4;
     int s = 0;
     uint32_t ph = 0, stage_off = 0;
-    for (int i = 0; i < p.nkb; ++i) {
-      if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 1200 + s)) break;
+    bool ok = true;
+    int local = 0;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      // the buffer's previous tile (two tiles ago) must have been read out of TMEM
+      if (!mbar_wait(bar_acc_empty + 8 * buf, ((local >> 1) & 1) ^ 1, abort_flag, p.status, 1250)) { ok = false; break; }
       tc_fence_after();
-      if (elect_one()) {
+      const uint32_t tmem_main = tmem_base + buf * 2 * BN, tmem_cross = tmem_main + BN;
+      uint32_t accumulate = 0;
+      for (int i = 0; i < p.nkb; ++i) {
+        if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 1200 + s)) { ok = false; break; }
+        tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < TBK / 8; ++kk) {
-          const uint32_t al = a_low0 + stage_off + kk * 2, bl = b_low0 + stage_off + kk * 2;
-          const int set = Cfg::ACC_SETS == 2 ? kk : 0;
-          const uint32_t tmem_main = tmem_base + set * 2 * BN, tmem_cross = tmem_main + BN;
-          const uint32_t acc = (Cfg::ACC_SETS == 1 && kk) ? 1u : accumulate[set];
-          mma_tf32_ss_words(tmem_cross, al + LO_TILE, a_hiw, bl, b_hiw, idesc, acc);
-          mma_tf32_ss_words(tmem_main, al, a_hiw, bl, b_hiw, idesc, acc);
-          mma_tf32_ss_words(tmem_cross, al, a_hiw, bl + LO_TILE, b_hiw, idesc, 1);
+          for (int kk = 0; kk < TBK / 8; ++kk) {
+            const uint32_t al = a_low0 + stage_off + kk * 2, bl = b_low0 + stage_off + kk * 2;
+            // A_hi x [W_hi ; W_lo]: columns [0, BN) of the result are the main product, [BN, 2BN) the hi x lo
+            // cross term; A_lo x W_hi then adds the other cross term onto columns [BN, 2BN)
+            mma_tf32_ss_words(tmem_main, al, a_hiw, bl, b_hiw, idesc_wide, kk ? 1u : accumulate);
+            mma_tf32_ss_words(tmem_cross, al + A_LO, a_hiw, bl, b_hiw, idesc, 1);
+          }
+          mma_commit(bar_empty + 8 * s);
         }
-        mma_commit(bar_empty + 8 * s);
+        accumulate = 1;
+        __syncwarp();
+        if (++s == STAGES) { s = 0; ph ^= 1; stage_off = 0; } else { stage_off += STAGE_STEP; }
       }
-      accumulate[0] = accumulate[1] = 1;
+      if (!ok) break;
+      if (elect_one()) mma_commit(bar_acc_full + 8 * buf);
       __syncwarp();
-      if (++s == STAGES) { s = 0; ph ^= 1; stage_off = 0; } else { stage_off += STAGE_STEP; }
     }
-    if (elect_one()) mma_commit(bar_acc);
-    __syncwarp();
     if (*abort_flag) {
-      for (int it = 0; it < (1 << 16); ++it)
-        if (mbar_try_wait(bar_acc, 0)) break;
+      // TMEM is freed below: every MMA issued must have retired by then
+      if (elect_one()) mma_commit(bar_retired);
+      __syncwarp();
+      for (int it = 0; it < (1 << 20); ++it)
+        if (mbar_try_wait(bar_retired, 0)) break;
     }
   } else {
-    // ---------------- epilogue (warps 0-7): this tile's accumulators -> NCHW ----------------
-    bool ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 1300);
-    ok = __all_sync(0xffffffffu, ok);
-    tc_fence_after();
-    if (ok) {
-      const int q = warp & 3, half = warp >> 2;
-      const int row = q * 32 + lane;                      // tile row = TMEM lane
-      const int b = row / box_rows, within = row - b * box_rows;
+    // ---------------- epilogue (warps 0-7): accumulators -> registers -> NCHW ----------------
+    const int q = warp & 3, half = warp >> 2;
+    const int row = q * 32 + lane;                      // tile row = TMEM lane
+    const int b = row / box_rows, within = row - b * box_rows;
+    const int ly = within / p.bx, lx = within % p.bx;
+    const long long hw = (long long)p.out_h * p.out_w;
+    constexpr int COLS_PER_HALF = BN / 2;
+    bool ok = true;
+    int local = 0;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      ok = mbar_wait(bar_acc_full + 8 * buf, (local >> 1) & 1, abort_flag, p.status, 1300);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tbase = tmem_base + (uint32_t)(buf * 2 * BN) + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * COLS_PER_HALF);
+      float acc[COLS_PER_HALF];
+#pragma unroll
+      for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(tbase + cc * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = __uint_as_float(r[j]);
+        tmem_ld_32x32(tbase + BN + cc * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[cc * 32 + j] += __uint_as_float(r[j]);
+      }
+      // the buffer may be overwritten by the tile after next
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+      const int box0 = (tile / tiles_n) * p.nbox, n0 = (tile % tiles_n) * BN;
       const int id = box0 + b;
       const int img = id / per_img, rem = id - img * per_img;
-      const int oy = (rem / p.tiles_x) * p.by + within / p.bx;
-      const int ox = (rem % p.tiles_x) * p.bx + within % p.bx;
-      const bool row_ok = b < boxes_here && oy < p.out_h && ox < p.out_w;
-      const long long hw = (long long)p.out_h * p.out_w;
-      float* obase = p.out + (long long)img * p.cout * hw + (long long)oy * p.out_w + ox;
-      constexpr int COLS_PER_HALF = BN / 2;
-#pragma unroll 1
-      for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
-        const int col0 = half * COLS_PER_HALF + cc * 32;
-        uint32_t r[32], t[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
-        tmem_ld_wait();
-#pragma unroll 1
-        for (int a = 1; a < 2 * Cfg::ACC_SETS; ++a) {
-          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + col0), t);
-          tmem_ld_wait();
+      const int oy = (rem / p.tiles_x) * p.by + ly;
+      const int ox = (rem % p.tiles_x) * p.bx + lx;
+      if (id < p.n_boxes && b < p.nbox && oy < p.out_h && ox < p.out_w) {
+        float* obase = p.out + (long long)img * p.cout * hw + (long long)oy * p.out_w + ox;
+        const int nb = n0 + half * COLS_PER_HALF;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(t[j]));
-        }
-        const int nb = n0 + col0;
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (nb + j < p.cout) {
-              float* cp = obase + (long long)(nb + j) * hw;     // lanes of a box row = adjacent pixels
-              float o = __uint_as_float(r[j]);
-              if (p.out_alpha != 0.f) o += p.out_alpha * (*cp);
-              *cp = o;
-            }
+        for (int j = 0; j < COLS_PER_HALF; ++j) {
+          if (nb + j < p.cout) {
+            float* cp = obase + (long long)(nb + j) * hw;       // lanes of a box row = adjacent pixels
+            float o = acc[j];
+            if (p.out_alpha != 0.f) o += p.out_alpha * (*cp);
+            *cp = o;
           }
         }
       }
@@ -382,7 +432,9 @@ int launch_tconv(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmA
   if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
   const long long tiles_m = (p.n_boxes + p.nbox - 1) / p.nbox;
   const long long tiles = tiles_m * ((p.cout + BN - 1) / BN);
-  conv_tma_kernel<BN><<<(unsigned)tiles, T_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmAlo, tmW, tmWlo, p);
+  const long long slots = (long long)s->sm_count * Cfg::CTAS_PER_SM;     // persistent: every resident CTA slot
+  const long long grid = tiles < slots ? tiles : slots;
+  conv_tma_kernel<BN><<<(unsigned)grid, T_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmAlo, tmW, tmWlo, p);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
@@ -429,6 +481,7 @@ int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const fl
   p.tiles_y = (out_h + p.by - 1) / p.by;
   p.n_boxes = batch * p.tiles_x * p.tiles_y;
   p.nkb = (cin / 16) * kh * kw;
+
   const int K = cin * kh * kw;
   const size_t in_elems = (size_t)batch * cin * in_h * in_w, w_elems = (size_t)cout * K;
   void* scratch = nullptr;
@@ -446,13 +499,12 @@ int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const fl
   if (blocks > s->sm_count * 8) blocks = s->sm_count * 8;
   tconv_prep_weights_kernel<<<blocks, 256, 0, s->stream>>>(w, w_hi, w_lo, cout, cin, kh * kw);
   CB_LAUNCH_CHECK(s);
-  const int BN = cout > 128 ? 256 : (cout > 64 ? 128 : 64);
+  const int BN = cout > 64 ? 128 : 64;       // wider layers take several 128-channel tiles
   CUtensorMap tmA, tmAlo, tmW, tmWlo;
   if ((rc = encode_nhwc(&tmA, a_hi, cin, in_w, in_h, batch, p.bx, p.by))) return rc;
   if ((rc = encode_nhwc(&tmAlo, a_lo, cin, in_w, in_h, batch, p.bx, p.by))) return rc;
   if ((rc = encode_w(&tmW, w_hi, K, cout, BN))) return rc;
   if ((rc = encode_w(&tmWlo, w_lo, K, cout, BN))) return rc;
-  if (BN == 256) return launch_tconv<256>(s, tmA, tmAlo, tmW, tmWlo, p);
   if (BN == 128) return launch_tconv<128>(s, tmA, tmAlo, tmW, tmWlo, p);
   return launch_tconv<64>(s, tmA, tmAlo, tmW, tmWlo, p);
 }

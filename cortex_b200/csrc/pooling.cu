@@ -186,77 +186,108 @@ pooling_forward_quad_kernel(T* out, const T* in, PoolGeom g, long long n_groups,
 // kernel moves from issue-bound to HBM-bound.  PX = pad_x (0 or 1).  Same fold order as above.
 template <int OP, int KH, int KW, int SX, int PX>
 __global__ void __launch_bounds__(256)
-pooling_forward_vec_kernel(float* out, const float* in, PoolGeom g, long long n_groups, int groups_per_row, double out_alpha) {
+pooling_forward_vec_kernel(float* out, const float* in, PoolGeom g, int planes, int groups_per_row, double out_alpha) {
   constexpr int NX = 4, W_IN = (NX - 1) * SX + KW, SEG = NX * SX;
   const bool out_vec = (g.out_w % 4) == 0 && ((((uintptr_t)out) & 15) == 0);
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_groups; i += (long long)gridDim.x * blockDim.x) {
-    const unsigned iu = (unsigned)i;
-    const unsigned tq = iu / (unsigned)groups_per_row;
-    const int ox0 = (int)(iu - tq * (unsigned)groups_per_row) * NX;
-    const unsigned plane_u = tq / (unsigned)g.out_h;
-    const int oy = (int)(tq - plane_u * (unsigned)g.out_h);
+  const unsigned per_plane = (unsigned)(g.out_h * groups_per_row);
+  const unsigned blocks_per_plane = (per_plane + 255) / 256;
+  // block -> (plane, chunk of the plane's (row, group) pairs): one division per thread
+  for (unsigned b = blockIdx.x; b < (unsigned)planes * blocks_per_plane; b += gridDim.x) {
+    const unsigned plane_u = b / blocks_per_plane;
+    const unsigned within = (b - plane_u * blocks_per_plane) * 256 + threadIdx.x;
+    if (within >= per_plane) continue;
+    const int oy = (int)(within / (unsigned)groups_per_row);
+    const int ox0 = (int)(within - (unsigned)oy * (unsigned)groups_per_row) * NX;
     const float* src = in + (long long)plane_u * g.in_h * g.in_w;
     const int rel_x = ox0 * SX - PX, rel_y = oy * g.stride_y - g.pad_y;
     const int seg_x = ox0 * SX;                         // first column of the aligned segment (multiple of 4)
-    bool row_ok[KH], col_ok[W_IN];
-    int n_rows = 0;
-#pragma unroll
-    for (int ky = 0; ky < KH; ++ky) { row_ok[ky] = (unsigned)(rel_y + ky) < (unsigned)g.in_h; n_rows += row_ok[ky] ? 1 : 0; }
-#pragma unroll
-    for (int c = 0; c < W_IN; ++c) col_ok[c] = (unsigned)(rel_x + c) < (unsigned)g.in_w;
-    float v[KH][W_IN];
-#pragma unroll
-    for (int ky = 0; ky < KH; ++ky) {
-      const float* row = src + (rel_y + ky) * g.in_w;
-      float seg[SEG];
-#pragma unroll
-      for (int q = 0; q < SEG / 4; ++q) {
-        if (row_ok[ky] && seg_x + 4 * q + 3 < g.in_w) {
-          const float4 t = *reinterpret_cast<const float4*>(row + seg_x + 4 * q);
-          seg[4 * q] = t.x; seg[4 * q + 1] = t.y; seg[4 * q + 2] = t.z; seg[4 * q + 3] = t.w;
-        } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            seg[4 * q + e] = (row_ok[ky] && seg_x + 4 * q + e < g.in_w) ? row[seg_x + 4 * q + e] : 0.f;
-        }
-      }
-#pragma unroll
-      for (int c = 0; c < W_IN; ++c) {
-        if (c >= PX && c < PX + SEG) v[ky][c] = seg[c - PX];
-        else v[ky][c] = (row_ok[ky] && col_ok[c]) ? row[rel_x + c] : 0.f;
-      }
-    }
-    const int py1 = min(rel_y + KH, g.in_h + g.pad_y);
-    const int rows_visited = max(0, py1 - rel_y);
     float* dst = out + ((long long)plane_u * g.out_h + oy) * g.out_w + ox0;
     float res[NX];
+    if (OP == CB200_POOL_MAX && rel_y >= 0 && rel_y + KH <= g.in_h && rel_x >= 0 && rel_x + W_IN <= g.in_w &&
+        seg_x + SEG <= g.in_w) {
+      // every window of this thread lies inside the image: no tests, the fold is compare + select
+      float v[KH][W_IN];
 #pragma unroll
-    for (int o = 0; o < NX; ++o) {
-      int n_cols = 0;
+      for (int ky = 0; ky < KH; ++ky) {
+        const float* row = src + (rel_y + ky) * g.in_w;
+        float seg[SEG];
 #pragma unroll
-      for (int kx = 0; kx < KW; ++kx) n_cols += col_ok[o * SX + kx] ? 1 : 0;
-      const int inside = n_rows * n_cols;
-      const int rx = rel_x + o * SX;
-      const int visited = rows_visited * max(0, min(rx + KW, g.in_w + g.pad_x) - rx);
-      float acc = 0.f;
-      if (OP == CB200_POOL_MAX) {
-        bool first = true;
+        for (int q = 0; q < SEG / 4; ++q) {
+          const float4 t = *reinterpret_cast<const float4*>(row + seg_x + 4 * q);
+          seg[4 * q] = t.x; seg[4 * q + 1] = t.y; seg[4 * q + 2] = t.z; seg[4 * q + 3] = t.w;
+        }
 #pragma unroll
-        for (int ky = 0; ky < KH; ++ky)
-#pragma unroll
-          for (int kx = 0; kx < KW; ++kx)
-            if (row_ok[ky] && col_ok[o * SX + kx]) { const float x = v[ky][o * SX + kx]; if (first || x > acc) acc = x; first = false; }
-        if (visited > inside && (first || 0.f > acc)) acc = 0.f;
-      } else {
-        const double divisor = OP == CB200_POOL_AVG ? (double)(KW * KH) : (double)inside;
-#pragma unroll
-        for (int ky = 0; ky < KH; ++ky)
-#pragma unroll
-          for (int kx = 0; kx < KW; ++kx)
-            if (row_ok[ky] && col_ok[o * SX + kx]) acc = (float)((double)acc + (double)v[ky][o * SX + kx] / divisor);
-        if (OP == CB200_POOL_AVG_EXC_PAD && inside == 0 && visited > 0) acc = (float)((double)acc + 0.0 / divisor);
+        for (int c = 0; c < W_IN; ++c) v[ky][c] = (c >= PX && c < PX + SEG) ? seg[c - PX] : row[rel_x + c];
       }
-      res[o] = acc;
+#pragma unroll
+      for (int o = 0; o < NX; ++o) {
+        float acc = v[0][o * SX];
+#pragma unroll
+        for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+          for (int kx = 0; kx < KW; ++kx)
+            if (ky + kx > 0) { const float x = v[ky][o * SX + kx]; acc = x > acc ? x : acc; }
+        res[o] = acc;
+      }
+    } else {
+      bool row_ok[KH], col_ok[W_IN];
+      int n_rows = 0;
+#pragma unroll
+      for (int ky = 0; ky < KH; ++ky) { row_ok[ky] = (unsigned)(rel_y + ky) < (unsigned)g.in_h; n_rows += row_ok[ky] ? 1 : 0; }
+#pragma unroll
+      for (int c = 0; c < W_IN; ++c) col_ok[c] = (unsigned)(rel_x + c) < (unsigned)g.in_w;
+      float v[KH][W_IN];
+#pragma unroll
+      for (int ky = 0; ky < KH; ++ky) {
+        const float* row = src + (rel_y + ky) * g.in_w;
+        float seg[SEG];
+#pragma unroll
+        for (int q = 0; q < SEG / 4; ++q) {
+          if (row_ok[ky] && seg_x + 4 * q + 3 < g.in_w) {
+            const float4 t = *reinterpret_cast<const float4*>(row + seg_x + 4 * q);
+            seg[4 * q] = t.x; seg[4 * q + 1] = t.y; seg[4 * q + 2] = t.z; seg[4 * q + 3] = t.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              seg[4 * q + e] = (row_ok[ky] && seg_x + 4 * q + e < g.in_w) ? row[seg_x + 4 * q + e] : 0.f;
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < W_IN; ++c) {
+          if (c >= PX && c < PX + SEG) v[ky][c] = seg[c - PX];
+          else v[ky][c] = (row_ok[ky] && col_ok[c]) ? row[rel_x + c] : 0.f;
+        }
+      }
+      const int py1 = min(rel_y + KH, g.in_h + g.pad_y);
+      const int rows_visited = max(0, py1 - rel_y);
+#pragma unroll
+      for (int o = 0; o < NX; ++o) {
+        int n_cols = 0;
+#pragma unroll
+        for (int kx = 0; kx < KW; ++kx) n_cols += col_ok[o * SX + kx] ? 1 : 0;
+        const int inside = n_rows * n_cols;
+        const int rx = rel_x + o * SX;
+        const int visited = rows_visited * max(0, min(rx + KW, g.in_w + g.pad_x) - rx);
+        float acc = 0.f;
+        if (OP == CB200_POOL_MAX) {
+          bool first = true;
+#pragma unroll
+          for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+            for (int kx = 0; kx < KW; ++kx)
+              if (row_ok[ky] && col_ok[o * SX + kx]) { const float x = v[ky][o * SX + kx]; if (first || x > acc) acc = x; first = false; }
+          if (visited > inside && (first || 0.f > acc)) acc = 0.f;
+        } else {
+          const double divisor = OP == CB200_POOL_AVG ? (double)(KW * KH) : (double)inside;
+#pragma unroll
+          for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+            for (int kx = 0; kx < KW; ++kx)
+              if (row_ok[ky] && col_ok[o * SX + kx]) acc = (float)((double)acc + (double)v[ky][o * SX + kx] / divisor);
+          if (OP == CB200_POOL_AVG_EXC_PAD && inside == 0 && visited > 0) acc = (float)((double)acc + 0.0 / divisor);
+        }
+        res[o] = acc;
+      }
     }
     if (out_vec && out_alpha == 0.0) {
       *reinterpret_cast<float4*>(dst) = make_float4(res[0], res[1], res[2], res[3]);
@@ -275,11 +306,13 @@ template <int OP, int KH, int KW>
 bool pooling_launch_vec_f(cb200_stream* s, float* out, const float* in, const PoolGeom& g, long long n_out, double out_alpha) {
   if ((g.stride_x != 1 && g.stride_x != 2) || g.pad_x > 1 || (g.in_w % 4) != 0 || ((((uintptr_t)in) & 15) != 0)) return false;
   const int groups_per_row = (g.out_w + 3) / 4;
-  const long long n_groups = (n_out / g.out_w) * groups_per_row;
-  long long blocks = (n_groups + 255) / 256;
+  const long long planes = n_out / ((long long)g.out_w * g.out_h);
+  const long long per_plane = (long long)g.out_h * groups_per_row;
+  if (planes > 2147483647LL / ((per_plane + 255) / 256)) return false;
+  long long blocks = planes * ((per_plane + 255) / 256);
   const long long cap = (long long)s->sm_count * 16;
   if (blocks > cap) blocks = cap;
-#define CB_POOL_VEC(SX, PX) pooling_forward_vec_kernel<OP, KH, KW, SX, PX><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g, n_groups, groups_per_row, out_alpha)
+#define CB_POOL_VEC(SX, PX) pooling_forward_vec_kernel<OP, KH, KW, SX, PX><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g, (int)planes, groups_per_row, out_alpha)
   if (g.stride_x == 2 && g.pad_x == 0) CB_POOL_VEC(2, 0);
   else if (g.stride_x == 2) CB_POOL_VEC(2, 1);
   else if (g.pad_x == 0) CB_POOL_VEC(1, 0);

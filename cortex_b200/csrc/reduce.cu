@@ -117,18 +117,24 @@ reduce_rows(T* out, const T* in, Operand oo, Operand oi, Geometry go, Geometry g
 template <typename T, int VEC>
 struct alignas(sizeof(T) * VEC) RVec { T v[VEC]; };
 
+// FAST keeps a plain fmaxf / fminf (which drop NaNs) plus a running sum whose only job is to turn NaN when
+// the row holds one: a NaN sum sends the row through an exact second pass (clojure's max / min propagate
+// NaN), so the common case costs two instructions per element.  Everything else keeps FOUR independent
+// accumulators per thread (element k of a vector goes to accumulator k & 3): the dependent chain of fp64
+// adds per load batch is a quarter as long.
 template <typename T, typename A, bool FAST>
-__device__ __forceinline__ void red_vec_accum(int op, A& acc, float& facc, const RVec<T, 16 / sizeof(T)>& v, A alpha,
-                                              bool unit) {
+__device__ __forceinline__ void red_vec_accum(int op, A (&acc)[4], float& facc, float& fsum,
+                                              const RVec<T, 16 / sizeof(T)>& v, A alpha, bool unit) {
   constexpr int VEC = 16 / sizeof(T);
 #pragma unroll
   for (int k = 0; k < VEC; ++k) {
     if (FAST) {
-      float f = (float)v.v[k];
-      facc = op == CB200_RMAX ? clj_max(facc, f) : ((facc != facc) ? facc : ((f != f) ? f : (facc < f ? facc : f)));
+      const float f = (float)v.v[k];
+      facc = op == CB200_RMAX ? fmaxf(facc, f) : fminf(facc, f);
+      fsum += f;
     } else {
       A e = unit ? (A)v.v[k] : (A)(alpha * (A)v.v[k]);
-      acc = red_combine(op, acc, red_elem(op, e));
+      acc[k & 3] = red_combine(op, acc[k & 3], red_elem(op, e));
     }
   }
 }
@@ -141,6 +147,7 @@ reduce_rows_vec(T* out, const T* in, Operand oo, Operand oi, Geometry go, Geomet
   constexpr int VEC = 16 / sizeof(T);
   constexpr int U = 8;
   __shared__ A smem[8];
+  __shared__ float fsmem[8];
   const int rows_per_block = NWARPS == 1 ? 8 : 1;
   const int tid = NWARPS == 1 ? (threadIdx.x & 31) : threadIdx.x;
   const int nthreads = NWARPS == 1 ? 32 : 256;
@@ -148,26 +155,57 @@ reduce_rows_vec(T* out, const T* in, Operand oo, Operand oi, Geometry go, Geomet
   const bool unit = alpha == (A)1;
   for (long long r0 = (long long)blockIdx.x * rows_per_block; r0 < n_rows; r0 += (long long)gridDim.x * rows_per_block) {
     long long r = NWARPS == 1 ? r0 + (threadIdx.x >> 5) : r0;
-    A acc = red_identity<A>(op);
-    float facc = op == CB200_RMAX ? -INFINITY : INFINITY;
+    A acc[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k] = red_identity<A>(op);
+    float facc = op == CB200_RMAX ? -INFINITY : INFINITY, fsum = 0.f;
+    const RVec<T, VEC>* row = nullptr;
     if (r < n_rows) {
-      const RVec<T, VEC>* row = reinterpret_cast<const RVec<T, VEC>*>(in + operand_offset(oi, gi, r * len));
+      row = reinterpret_cast<const RVec<T, VEC>*>(in + operand_offset(oi, gi, r * len));
       int j = tid;
       for (; j + (U - 1) * nthreads < nvec; j += U * nthreads) {
         RVec<T, VEC> v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) v[u] = row[j + u * nthreads];
 #pragma unroll
-        for (int u = 0; u < U; ++u) red_vec_accum<T, A, FAST>(op, acc, facc, v[u], alpha, unit);
+        for (int u = 0; u < U; ++u) red_vec_accum<T, A, FAST>(op, acc, facc, fsum, v[u], alpha, unit);
       }
       for (; j < nvec; j += nthreads) {
         RVec<T, VEC> v0 = row[j];
-        red_vec_accum<T, A, FAST>(op, acc, facc, v0, alpha, unit);
+        red_vec_accum<T, A, FAST>(op, acc, facc, fsum, v0, alpha, unit);
       }
     }
-    if (FAST) acc = (A)facc;
-    acc = block_combine<A, NWARPS>(op, acc, smem);
-    if (tid == 0 && r < n_rows) out[operand_offset(oo, go, r)] = red_finish<T>(op, acc, len);
+    A total;
+    if (FAST) {
+      // did any thread of the row see a NaN (or +inf and -inf together)?  then redo the row exactly
+      float bad = fsum;
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) bad += __shfl_xor_sync(0xffffffffu, bad, d);
+      if (NWARPS > 1) {
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) fsmem[threadIdx.x >> 5] = bad;
+        __syncthreads();
+        bad = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) bad += fsmem[w];
+      }
+      if (bad != bad && r < n_rows) {
+        facc = op == CB200_RMAX ? -INFINITY : INFINITY;
+        for (int j = tid; j < nvec; j += nthreads) {
+          const RVec<T, VEC> v0 = row[j];
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) {
+            const float f = (float)v0.v[k];
+            facc = op == CB200_RMAX ? clj_max(facc, f) : ((facc != facc) ? facc : ((f != f) ? f : (facc < f ? facc : f)));
+          }
+        }
+      }
+      total = (A)facc;
+    } else {
+      total = red_combine(op, red_combine(op, acc[0], acc[1]), red_combine(op, acc[2], acc[3]));
+    }
+    total = block_combine<A, NWARPS>(op, total, smem);
+    if (tid == 0 && r < n_rows) out[operand_offset(oo, go, r)] = red_finish<T>(op, total, len);
   }
 }
 

@@ -390,8 +390,10 @@ enum cb200_stream_option {
   CB200_OPT_PRESPLIT_VARIANT = 1,   /* gemm_bias_act_presplit: 0 = by size, 1 = single-CTA tiles, 2 = CTA pairs */
   CB200_OPT_F64_SIMPLE_KERNEL = 2,  /* fp64 gemm!: 1 = always the register-staged kernel */
   CB200_OPT_WAIT_LIMIT_CYCLES = 3,  /* limit of every bounded device-side wait, in SM cycles (0 = default, ~2 s) */
-  CB200_OPT_CONV_ROUTE = 5,         /* fp32 convolution-forward!: 0 = by geometry (TMA-fed kernel for stride-1 layers
-                                       with a multiple of 16 input channels), 1 = always the thread-gathered kernel */
+  CB200_OPT_CONV_ROUTE = 5,         /* fp32 convolution-forward!: 0 = by geometry (TMA-fed kernels for stride-1 layers
+                                       with a multiple of 16 input channels), 1 = always the thread-gathered kernel,
+                                       2 = the TMA kernel that loads one tile per filter tap, never the one that
+                                       keeps the input patch in shared memory */
   CB200_OPT_INJECT_FAULT = 4        /* bit 0: the TMA producers of the fp32 tensor-core GEMM issue no loads, so
                                        the consumers' waits run out -> CB200_ERR_TIMEOUT from cb200_stream_sync.
                                        The failure is made on the host side of the barrier protocol; the kernel

@@ -172,18 +172,26 @@ def test_conv_matches_oracle(b200_driver, oracle_driver, datatype):
     dict(batch=2, cin=16, hw=18, cout=16, k=3, pad=0),           # no padding
     dict(batch=1, cin=16, hw=14, cout=16, k=3, pad=2),           # padding wider than the filter's reach
     dict(batch=3, cin=16, hw=13, cout=40, k=5, pad=2),           # 16 x 2 boxes, four per tile, overhang in x and y
+    dict(batch=2, cin=32, hw=32, cout=100, k=3, pad=1),          # 8 x 16 patch tiles exactly, two channel blocks
+    dict(batch=1, cin=16, hw=40, cout=64, k=7, pad=3),           # 7 x 7 filter: 14 x 22 patch
+    dict(batch=2, cin=48, hw=24, cout=20, k=2, pad=0),           # even filter, output 23 x 23 (overhang)
 ], ids=lambda a: "x".join(str(v) for v in a.values()))
-def test_conv_tma_fed_kernel(b200_driver, oracle_driver, args):
-    """Stride-1 fp32 convolutions with a multiple of 16 input channels run the kernel whose im2col tiles arrive
-    by TMA from an NHWC hi / lo copy of the input.  Against the oracle, float64, and the thread-gathered kernel
-    (per-stream option conv-route = 1), which sums in the same k order."""
+def test_conv_tma_fed_kernels(b200_driver, oracle_driver, args):
+    """Stride-1 fp32 convolutions with a multiple of 16 input channels run kernels whose operand tiles all arrive
+    by TMA: by geometry (route 0) the one that keeps the input patch in shared memory across the filter taps, or
+    the one that loads a shifted tile per tap (route 2: forced here so that both run on every geometry they
+    accept).  Against the oracle, float64, and the thread-gathered kernel (route 1), which sums in the same
+    k order."""
     run, ref = pc.conv_case("float", bias_scale=0.1, **args)
-    tma = _on(b200_driver, "float", run)
+    by_geometry = _on(b200_driver, "float", run)
+    per_tap = _on(b200_driver, "float", run, {"conv-route": 2})
     gathered = _on(b200_driver, "float", run, {"conv-route": 1})
     cpu = _on(oracle_driver, "float", run)
-    assert pc.rel_err(tma, cpu) <= pc.TOL["float"]
-    assert pc.rel_err(tma, ref()) <= pc.TOL["float"]
-    assert pc.rel_err(tma, gathered) <= 2e-5
+    want = ref()
+    for got in (by_geometry, per_tap):
+        assert pc.rel_err(got, cpu) <= pc.TOL["float"]
+        assert pc.rel_err(got, want) <= pc.TOL["float"]
+        assert pc.rel_err(got, gathered) <= 2e-5
 
 
 def test_fused_bias_relu_rowstats(b200_driver, oracle_driver):
