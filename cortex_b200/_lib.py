@@ -101,6 +101,11 @@ SIGNATURES = {
     "cb200_batch_normalize_eltwise": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64],
     "cb200_batch_normalize_spatial": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
     "cb200_pooling_forward": [_vp, _i, _vp, _pd, _d, _vp, _pd, C.POINTER(PoolDesc)],
+    "cb200_pooling_backward": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _pd, C.POINTER(PoolDesc)],
+    "cb200_batch_normalize_update_and_apply_eltwise": [_vp, _i] + [_vp] * 6 + [_d, _vp, _vp, _d, _i64, _i64],
+    "cb200_batch_normalize_update_and_apply_spatial": [_vp, _i] + [_vp] * 6 + [_d, _vp, _vp, _d, _i64, _i64, _i64],
+    "cb200_batch_normalize_gradients_eltwise": [_vp, _i] + [_vp] * 10 + [_d, _i64, _i64],
+    "cb200_batch_normalize_gradients_spatial": [_vp, _i] + [_vp] * 10 + [_d, _i64, _i64, _i64],
     "cb200_adam_step": [_vp, _i, _d, _d, _d, _d, _d, _d, _d, _vp, _vp, _vp, _vp, _i64],
     "cb200_adadelta_step": [_vp, _i, _d, _d, _vp, _vp, _d, _vp, _vp, _i64],
     "cb200_rand": [_vp, _vp, _pd, _i, _d, _d, C.c_uint64, C.c_uint64],

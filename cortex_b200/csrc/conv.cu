@@ -41,6 +41,31 @@ int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const fl
                           int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
                           float out_alpha);
 
+// fp32 forward convolution on dense NCHW tensors, routed by geometry.  Stride-1 layers with a multiple of 16 input
+// channels: every operand tile by TMA -- the input patch kept in shared memory across the filter taps
+// (conv_halo.cu) where the 8 x 16 tiles fit the output, one shifted tile per tap otherwise (conv_tma.cu); the rest:
+// im2col rows gathered by threads (conv_igemm.cu).  opt_conv_route: 0 = by geometry, 1 = always gather, 2 = never
+// the patch kernel.  Also the engine of convolution-backward-data! (conv_backward.cu).
+bool cb200_conv_forward_f32_uses_tma(const cb200_stream* s, int batch, int cin, int in_h, int in_w, int cout, int out_h,
+                                     int out_w, int kh, int kw, int stride_x, int stride_y) {
+  const long long in_elems = (long long)batch * cin * in_h * in_w;
+  if (s->opt_conv_route == 0 && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
+    return true;
+  return s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, out_w, out_h, stride_x, stride_y, in_elems);
+}
+
+int cb200_conv_forward_f32(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
+                           int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y, int stride_x,
+                           int stride_y, float out_alpha) {
+  const long long in_elems = (long long)batch * cin * in_h * in_w;
+  if (s->opt_conv_route == 0 && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
+    return cb200_conv_halo_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha);
+  if (s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, out_w, out_h, stride_x, stride_y, in_elems))
+    return cb200_conv_tma_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha);
+  return cb200_conv_igemm_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, stride_x,
+                                 stride_y, out_alpha);
+}
+
 namespace {
 
 struct ConvGeom {
@@ -120,23 +145,9 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
   const long long rows = (long long)g.batch * hw;
   CB_REQUIRE(rows <= 2147483647LL, "convolution_forward: more than 2^31-1 output pixels");
   if (rows == 0 || cout == 0) return CB200_OK;
-  if (dtype == CB200_FLOAT) {
-    // stride-1 layers with a multiple of 16 input channels: every operand tile by TMA -- the input patch kept in
-    // shared memory across the filter taps (conv_halo.cu) where the 8 x 16 tiles fit the output, one shifted
-    // tile per tap otherwise (conv_tma.cu); the rest: im2col rows gathered by threads (conv_igemm.cu).
-    // opt_conv_route: 0 = by geometry, 1 = always gather, 2 = never the patch kernel
-    const long long in_elems = (long long)g.batch * g.cin * g.in_h * g.in_w;
-    if (s->opt_conv_route == 0 &&
-        cb200_conv_halo_eligible(g.cin, cout, g.out_w, g.out_h, g.kh, g.kw, g.stride_x, g.stride_y, in_elems))
-      return cb200_conv_halo_launch(s, (float*)out, (const float*)in, (const float*)w, g.batch, g.cin, g.in_h, g.in_w,
-                                    cout, g.out_h, g.out_w, g.kh, g.kw, g.pad_x, g.pad_y, (float)out_alpha);
-    if (s->opt_conv_route != 1 && cb200_conv_tma_eligible(g.cin, g.out_w, g.out_h, g.stride_x, g.stride_y, in_elems))
-      return cb200_conv_tma_launch(s, (float*)out, (const float*)in, (const float*)w, g.batch, g.cin, g.in_h, g.in_w,
-                                   cout, g.out_h, g.out_w, g.kh, g.kw, g.pad_x, g.pad_y, (float)out_alpha);
-    return cb200_conv_igemm_launch(s, (float*)out, (const float*)in, (const float*)w, g.batch, g.cin, g.in_h, g.in_w,
-                                   cout, g.out_h, g.out_w, g.kh, g.kw, g.pad_x, g.pad_y, g.stride_x, g.stride_y,
-                                   (float)out_alpha);
-  }
+  if (dtype == CB200_FLOAT)
+    return cb200_conv_forward_f32(s, (float*)out, (const float*)in, (const float*)w, g.batch, g.cin, g.in_h, g.in_w, cout,
+                                  g.out_h, g.out_w, g.kh, g.kw, g.pad_x, g.pad_y, g.stride_x, g.stride_y, (float)out_alpha);
   const size_t es = 8;
   const long long total = rows * g.ld;
   void* cols = nullptr;

@@ -21,6 +21,12 @@ int cb200_gemm_no_workspace(cb200_stream* s, int dtype, void* C, long long ldc, 
                             const void* A, long long a_rows, long long a_cols, long long lda, const void* B,
                             long long b_cols, long long ldb, double beta);
 
+bool cb200_conv_forward_f32_uses_tma(const cb200_stream* s, int batch, int cin, int in_h, int in_w, int cout, int out_h,
+                                     int out_w, int kh, int kw, int stride_x, int stride_y);
+int cb200_conv_forward_f32(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
+                           int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y, int stride_x,
+                           int stride_y, float out_alpha);
+
 namespace {
 
 struct BwdGeom {
@@ -286,6 +292,18 @@ int cb200_convolution_backward_weights(cb200_stream* s, int dtype, void* w_grad,
   return CB200_OK;
 }
 
+// W[C_out][c*khkw + t]  ->  Wt[c][co*khkw + (khkw - 1 - t)]: the filter of the forward convolution that computes the
+// data gradient (input and output channels swapped, taps mirrored)
+__global__ void __launch_bounds__(256)
+flip_weights_kernel(float* __restrict__ wt, const float* __restrict__ w, int cout, int cin, int khkw) {
+  const int total = cout * cin * khkw;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int c = i / (cout * khkw), r = i - c * (cout * khkw);
+    const int co = r / khkw, t = r - co * khkw;
+    wt[i] = w[((long long)co * cin + c) * khkw + (khkw - 1 - t)];
+  }
+}
+
 int cb200_convolution_backward_data(cb200_stream* s, int dtype, void* in_grad, const cb200_dims* in_grad_dims,
                                     double in_grad_alpha, const void* out_grad, const cb200_dims* out_grad_dims,
                                     const void* w, const cb200_dims* w_dims, void* workspace, int64_t workspace_ecount,
@@ -305,6 +323,28 @@ int cb200_convolution_backward_data(cb200_stream* s, int dtype, void* in_grad, c
   if (in_total == 0) return CB200_OK;
   const size_t es = dtype == CB200_FLOAT ? 4 : 8;
   DeviceGuard guard(s->device);
+  // Stride 1: the data gradient IS a forward convolution of the output gradient with the mirrored, channel-swapped
+  // filter and padding k - 1 - pad:  in_grad[n, c, y, x] = sum over (co, ky, kx) of
+  // out_grad[n, co, y + pad - ky, x + pad - kx] * W[co, c, ky, kx].  When that convolution qualifies for the TMA-fed
+  // tensor-core kernels it runs there: no unrolled gradient matrix (K x pixels floats) is written or read back.
+  if (dtype == CB200_FLOAT && rows > 0 && cout > 0 && g.stride_x == 1 && g.stride_y == 1 && g.pad_x <= g.kw - 1 &&
+      g.pad_y <= g.kh - 1 &&
+      cb200_conv_forward_f32_uses_tma(s, g.batch, cout, g.out_h, g.out_w, g.cin, g.in_h, g.in_w, g.kh, g.kw, 1, 1)) {
+    // the forward launch takes (2 * its input + 2 * its weights) floats from the head of the stream's workspace:
+    // the mirrored filter goes behind that
+    const size_t og_elems = (size_t)rows * cout, w_elems = (size_t)cout * g.kcols;
+    const size_t head = (2 * og_elems + 2 * w_elems) * sizeof(float);
+    void* ws = nullptr;
+    if ((rc = cb200_scratch(s, head + w_elems * sizeof(float), &ws))) return rc;
+    float* wt = (float*)((char*)ws + head);
+    int fb = (int)((w_elems + 255) / 256);
+    if (fb > s->sm_count * 8) fb = s->sm_count * 8;
+    flip_weights_kernel<<<fb, 256, 0, s->stream>>>(wt, (const float*)w, cout, g.cin, g.kh * g.kw);
+    CB_LAUNCH_CHECK(s);
+    return cb200_conv_forward_f32(s, (float*)in_grad, (const float*)out_grad, wt, g.batch, cout, g.out_h, g.out_w, g.cin,
+                                  g.in_h, g.in_w, g.kh, g.kw, g.kw - 1 - g.pad_x, g.kh - 1 - g.pad_y, 1, 1,
+                                  (float)in_grad_alpha);
+  }
   void* colsgrad = nullptr;
   if (rows > 0 && cout > 0) {
     // all images in ONE product: the gradient is first laid out as pixel rows, OGt[batch*hw, C_out] (a 32 x 32

@@ -332,11 +332,14 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
 // One accumulator read-out by an epilogue thread: its 128 columns of the main accumulator (and, on the last
 // read-out of a tile, of the cross-term accumulator) are added into acc[], which lives in registers (every
 // index below is a compile-time constant).
-__device__ __forceinline__ void read_out(uint32_t tmem_base, int q, int half, float (&acc)[BN / 2], bool first,
+// `col0` / `ncc`: the thread's first accumulator column and its number of 32-column chunks (4 for a 256-wide tile,
+// 2 for the 128-wide half tiles of the last round).
+__device__ __forceinline__ void read_out(uint32_t tmem_base, int q, int col0, int ncc, float (&acc)[BN / 2], bool first,
                                          bool with_cross) {
-  const uint32_t lane_col = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * (BN / 2));
+  const uint32_t lane_col = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0;
 #pragma unroll
   for (int cc = 0; cc < BN / 2 / 32; ++cc) {
+    if (cc >= ncc) break;
     uint32_t r[32];
     tmem_ld_32x32(lane_col + cc * 32, r);
     tmem_ld_wait();
@@ -358,13 +361,14 @@ __device__ __forceinline__ void read_out(uint32_t tmem_base, int q, int half, fl
 
 // C = act(alpha * acc + beta * C + bias) (+ C_lo) for one thread's row m and its 128 columns from n_first on,
 // out of registers: runs while the tensor cores are already busy with the pair's next tile.
-__device__ __forceinline__ void store_row(const GemmParams& p, int m, int n_first, const float (&acc)[BN / 2]) {
+__device__ __forceinline__ void store_row(const GemmParams& p, int m, int n_first, int ncc, const float (&acc)[BN / 2]) {
   if (m >= p.M) return;
   float* crow = p.C + (long long)m * p.ldc;
   float* lrow = p.C_lo ? p.C_lo + (long long)m * p.ldc : nullptr;
   const bool vec8 = (p.ldc % 8) == 0 && ((((uintptr_t)p.C) | ((uintptr_t)p.C_lo)) & 31) == 0;
 #pragma unroll
   for (int cc = 0; cc < BN / 2 / 32; ++cc) {
+    if (cc >= ncc) break;
     const int nb = n_first + cc * 32;
     if (nb >= p.N) continue;
     if (vec8 && nb + 32 <= p.N) {
@@ -435,12 +439,24 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + 2 * BM - 1) / (2 * BM), n_tiles = tiles_m * tiles_n;
   const int n_clusters = (int)gridDim.x >> 1, cluster_id = (int)blockIdx.x >> 1;
   const int nkb = (p.K + BK - 1) / BK;
-  auto tile_origin = [&](int tile_id, int& m0, int& n0) {
+  // Work units: tiles below p.split_from are whole 256 x 256 tiles; the tiles of the last, partial round (when
+  // they are at most half as many as the clusters) are cut into two 256 x 128 halves each, so that the round
+  // takes half a tile's time on twice as many clusters instead of a whole one on few (4096^3 on 74 clusters:
+  // 3.5 rounds instead of 4).  `width` = 256 or 128, n0 = first column of the unit.
+  const int n_units = p.split_from + 2 * (n_tiles - p.split_from);
+  auto tile_origin = [&](int unit, int& m0, int& n0, int& width) {
+    int tile_id = unit, nh = 0;
+    width = BN;
+    if (unit >= p.split_from) {
+      tile_id = p.split_from + ((unit - p.split_from) >> 1);
+      nh = (unit - p.split_from) & 1;
+      width = BN / 2;
+    }
     const int grp = tile_id / (tiles_m * p.group_n);
     const int rem = tile_id - grp * tiles_m * p.group_n;
     const int in_grp = min(p.group_n, tiles_n - grp * p.group_n);
     m0 = (rem / in_grp) * (2 * BM) + (int)rank * BM;       // this CTA's rows of C
-    n0 = (grp * p.group_n + rem % in_grp) * BN;            // the pair's columns of C
+    n0 = (grp * p.group_n + rem % in_grp) * BN + nh * (BN / 2);      // the pair's columns of C
   };
 
   const uint32_t smem_base = smem_u32(smem);
@@ -483,10 +499,12 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       uint32_t ph = 0;
       bool ok = true;
       const bool withhold = (p.status[3] & 1) != 0;     // host-injected fault: arm nothing, load nothing
-      for (int tile = cluster_id; ok && tile < n_tiles; tile += n_clusters) {
-        int m0, n0;
-        tile_origin(tile, m0, n0);
-        const int row0 = is_a ? m0 : n0 + (int)rank * PNH;
+      for (int tile = cluster_id; ok && tile < n_units; tile += n_clusters) {
+        int m0, n0, width;
+        tile_origin(tile, m0, n0, width);
+        // each CTA stages half of the unit's B rows (the box is always PNH rows: a half tile's box carries 64
+        // rows it does not use)
+        const int row0 = is_a ? m0 : n0 + (int)rank * (width / 2);
         for (int i = 0; i < nkb; ++i) {
           if (!mbar_wait_cluster(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) { ok = false; break; }
           const uint32_t dst = smem_base + s * P_STAGE + tile_off;
@@ -510,7 +528,7 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   } else if (warp == EPI_WARPS + 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (leader && lane == 0) {
-      const uint32_t idesc = make_idesc_tf32(2 * BM, BN, 0, 0);
+      const uint32_t idesc_full = make_idesc_tf32(2 * BM, BN, 0, 0), idesc_half = make_idesc_tf32(2 * BM, BN / 2, 0, 0);
       const uint64_t d_a = make_smem_desc(smem_base, 16, 8 * BK * 4, SWZ_64B);
       const uint64_t d_b = make_smem_desc(smem_base + A_TILE, 16, 8 * BK * 4, SWZ_64B);
       const uint32_t a_hiw = (uint32_t)(d_a >> 32), b_hiw = (uint32_t)(d_b >> 32);
@@ -521,7 +539,8 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       int s = 0;
       uint32_t ph = 0, stage_off = 0, dph = 0;
       bool ok = true, pending_read_out = false;
-      for (int tile = cluster_id; ok && tile < n_tiles; tile += n_clusters) {
+      for (int tile = cluster_id; ok && tile < n_units; tile += n_clusters) {
+        const uint32_t idesc = tile >= p.split_from ? idesc_half : idesc_full;
         uint32_t acc_cross = 0, accumulate = 0;
         // every p.drain_every k-blocks the epilogue warps add the main accumulator into their registers and
         // it restarts from zero (tcgen05 accumulates with truncation: shorter runs, smaller bias)
@@ -577,9 +596,10 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     float acc[BN / 2];
     uint32_t mph = 0;
     bool ok = true;
-    for (int tile = cluster_id; ok && tile < n_tiles; tile += n_clusters) {
-      int m0, n0;
-      tile_origin(tile, m0, n0);
+    for (int tile = cluster_id; ok && tile < n_units; tile += n_clusters) {
+      int m0, n0, width;
+      tile_origin(tile, m0, n0, width);
+      const int col0 = half * (width / 2), ncc = width / 2 / 32;     // this thread's accumulator columns
       const int n_mid = p.drain_every > 0 ? (nkb - 1) / p.drain_every : 0;
       for (int ev = 0; ev <= n_mid; ++ev) {
         ok = mbar_wait_cluster(bar_mid, mph, abort_flag, p.status, 850);
@@ -587,12 +607,12 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        read_out(tmem_base, q, half, acc, ev == 0, ev == n_mid);
+        read_out(tmem_base, q, col0, ncc, acc, ev == 0, ev == n_mid);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(leader_drained);
       }
-      if (ok) store_row(p, m0 + q * 32 + lane, n0 + half * (BN / 2), acc);
+      if (ok) store_row(p, m0 + q * 32 + lane, n0 + col0, ncc, acc);
     }
   }
 
@@ -736,6 +756,9 @@ int launch_presplit(cb200_stream* s, float* C, float* C_lo, long long ldc, float
   if (pair) {
     const long long pairs = ((M + 2 * BM - 1) / (2 * BM)) * (long long)tiles_n;
     const long long clusters = pairs < s->sm_count / 2 ? pairs : s->sm_count / 2;     // persistent: one pair per two SMs
+    // a last round with at most half as many tiles as clusters runs as 256 x 128 half tiles
+    const long long tail = pairs % clusters;
+    p.split_from = (int)((tail > 0 && 2 * tail <= clusters && pairs > clusters) ? pairs - tail : pairs);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
     cfg.blockDim = dim3(P_THREADS, 1, 1);

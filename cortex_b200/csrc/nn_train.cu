@@ -1,0 +1,383 @@
+// The layer-gradient methods of the tensor-math protocol that the training path of a convolutional
+// network calls next to the convolution gradients:
+//   pooling-backward!                          src/cortex/tensor/math.clj:223-236
+//   batch-normalize-update-and-apply-*!        src/cortex/tensor/math.clj:137-158
+//   batch-normalize-gradients-*!               src/cortex/tensor/math.clj:159-174
+// Arithmetic after the reference CPU backend (src/cortex/compute/cpu/tensor_math.clj:820-1032 and
+// :1175-1284): every expression is evaluated in double and rounded to the element type where the
+// reference stores or casts.
+//
+// Pooling backward is written in gather form: one thread per INPUT element walks the output positions whose
+// window covers it, in (out-y, out-x) order, which is the order in which the reference's scatter loop
+// (src/cortex/nn/impl.clj:8-107) reaches that element; so the running sum sees the same partial sums and
+// the result is bit-identical, with no atomics.
+//
+// The batch-normalisation statistics are sums over (batch x element) per channel.  Elementwise form: one
+// thread per column, rows visited in order (coalesced across threads, and the same summation order as the
+// reference).  Spatial form: one CTA per channel, double-precision tree reduction (the summation order
+// differs from the reference's sequential loop: results agree to rounding of the double sums).
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------------
+// pooling backward
+// ------------------------------------------------------------------------------------------------------
+struct PoolBwdGeom {
+  int in_h, in_w, out_h, out_w, kw, kh, pad_x, pad_y, stride_x, stride_y;
+};
+
+__device__ __forceinline__ int floor_div(int a, int b) {   // b > 0
+  int q = a / b;
+  return (a % b != 0 && a < 0) ? q - 1 : q;
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(256)
+pooling_backward_kernel(T* in_grad, const T* in, const T* out, const T* out_grad, PoolBwdGeom g, long long n_in,
+                        double in_grad_alpha) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_in; i += (long long)gridDim.x * blockDim.x) {
+    const unsigned iu = (unsigned)i;
+    const unsigned tq = iu / (unsigned)g.in_w;
+    const int ix = (int)(iu - tq * (unsigned)g.in_w);
+    const unsigned plane = tq / (unsigned)g.in_h;
+    const int iy = (int)(tq - plane * (unsigned)g.in_h);
+    const long long out_base = (long long)plane * g.out_h * g.out_w;
+    // output rows / columns whose window [o*stride - pad, o*stride - pad + k) holds iy / ix
+    const int oy0 = max(0, floor_div(iy + g.pad_y - g.kh + g.stride_y, g.stride_y));   // ceil((iy+pad-kh+1)/stride)
+    const int oy1 = min(g.out_h - 1, (iy + g.pad_y) / g.stride_y);
+    const int ox0 = max(0, floor_div(ix + g.pad_x - g.kw + g.stride_x, g.stride_x));
+    const int ox1 = min(g.out_w - 1, (ix + g.pad_x) / g.stride_x);
+    T acc = in_grad_alpha == 0.0 ? (T)0 : (T)(in_grad_alpha * (double)in_grad[i]);
+    const T x = OP == CB200_POOL_MAX ? in[i] : (T)0;
+    for (int oy = oy0; oy <= oy1; ++oy) {
+      int exc_h = 0;
+      if (OP == CB200_POOL_AVG_EXC_PAD) {
+        const int rel_y = oy * g.stride_y - g.pad_y;
+        exc_h = min(rel_y + g.kh, g.in_h) - max(rel_y, 0);
+      }
+      for (int ox = ox0; ox <= ox1; ++ox) {
+        const long long o = out_base + (long long)oy * g.out_w + ox;
+        if (OP == CB200_POOL_MAX) {
+          if (x == out[o]) acc = (T)((double)acc + (double)out_grad[o]);
+        } else if (OP == CB200_POOL_AVG) {
+          acc = (T)((double)acc + (double)out_grad[o] / (double)(g.kw * g.kh));
+        } else {
+          const int rel_x = ox * g.stride_x - g.pad_x;
+          const int exc_w = min(rel_x + g.kw, g.in_w) - max(rel_x, 0);
+          acc = (T)((double)acc + (double)out_grad[o] / (double)(exc_w * exc_h));
+        }
+      }
+    }
+    in_grad[i] = acc;
+  }
+}
+
+template <typename T>
+void pooling_backward_launch(cb200_stream* s, int op, T* in_grad, const T* in, const T* out, const T* out_grad,
+                             const PoolBwdGeom& g, long long n_in, double alpha) {
+  long long blocks = (n_in + 255) / 256;
+  const long long cap = (long long)s->sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  const unsigned b = (unsigned)blocks;
+  if (op == CB200_POOL_MAX)
+    pooling_backward_kernel<T, CB200_POOL_MAX><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_in, alpha);
+  else if (op == CB200_POOL_AVG)
+    pooling_backward_kernel<T, CB200_POOL_AVG><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_in, alpha);
+  else
+    pooling_backward_kernel<T, CB200_POOL_AVG_EXC_PAD><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_in, alpha);
+}
+
+// ------------------------------------------------------------------------------------------------------
+// batch normalisation: statistics update and gradients
+// ------------------------------------------------------------------------------------------------------
+// (parallel index, running index) -> element offset; the reference's BNEltwiseOffsetter / BNSpatialOffsetter
+// (src/cortex/compute/cpu/tensor_math.clj:716-756)
+struct BnShape {
+  long long batch;      // rows before the channel dimension
+  int channels;         // parallel count
+  int inner;            // elements per (row, channel): 1 in the elementwise form
+  __device__ __forceinline__ long long count() const { return batch * inner; }
+  __device__ __forceinline__ long long offset(int c, long long idx) const {
+    const long long b = idx / inner;
+    const int e = (int)(idx - b * inner);
+    return (b * channels + c) * (long long)inner + e;
+  }
+};
+
+constexpr int BN_TEAM = 512;
+
+// Sum of one value per thread over the team that owns a parallel index: the thread itself (TEAM == 1) or
+// the whole CTA (every thread receives the total).
+template <int TEAM>
+__device__ __forceinline__ double team_sum(double v, double* sh) {
+  if (TEAM == 1) return v;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();                      // sh may still be read by the previous call
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  double t = 0.0;
+#pragma unroll
+  for (int w = 0; w < TEAM / 32; ++w) t += sh[w];   // the same order in every thread
+  return t;
+}
+
+template <typename T, int TEAM>
+__global__ void __launch_bounds__(TEAM == 1 ? 128 : TEAM)
+bn_update_kernel(const T* __restrict__ in, T* batch_means, T* batch_variances, T* running_means, T* running_variances,
+                 double average_factor, BnShape sh) {
+  __shared__ double red[32];
+  const int c = TEAM == 1 ? (int)(blockIdx.x * blockDim.x + threadIdx.x) : (int)blockIdx.x;
+  if (TEAM == 1 && c >= sh.channels) return;
+  const long long count = sh.count();
+  const int t0 = TEAM == 1 ? 0 : (int)threadIdx.x;
+  const double factor = (double)(T)average_factor;
+  const double lerp = (double)(T)1.0 - factor;
+  const double n = count > 1 ? (double)count : 1.0;
+  const double n_running = n - 1.0 > 1.0 ? n - 1.0 : 1.0;
+  double sum = 0.0;
+  for (long long idx = t0; idx < count; idx += TEAM) sum += (double)in[sh.offset(c, idx)];
+  sum = team_sum<TEAM>(sum, red);
+  const T new_mean = (T)(sum / n);
+  double var = 0.0;
+  for (long long idx = t0; idx < count; idx += TEAM) {
+    const double d = (double)new_mean - (double)in[sh.offset(c, idx)];
+    var = __dadd_rn(var, __dmul_rn(d, d));
+  }
+  var = team_sum<TEAM>(var, red);
+  if (TEAM == 1 || threadIdx.x == 0) {
+    const double mean_old = (double)running_means[c], var_old = (double)running_variances[c];
+    batch_means[c] = new_mean;
+    batch_variances[c] = (T)(var / n);
+    running_means[c] = (T)(__dmul_rn(mean_old, lerp) + __dmul_rn((double)new_mean, factor));
+    running_variances[c] = (T)(__dmul_rn(var_old, lerp) + __dmul_rn((double)(T)(var / n_running), factor));
+  }
+}
+
+template <typename T, int TEAM>
+__global__ void __launch_bounds__(TEAM == 1 ? 128 : TEAM)
+bn_gradients_kernel(T* in_grad, T* scale_grad, T* bias_grad, const T* out_grad, const T* in,
+                    const T* __restrict__ batch_means, const T* __restrict__ batch_variances,
+                    const T* __restrict__ scale, double epsilon, BnShape sh) {
+  __shared__ double red[32];
+  const int c = TEAM == 1 ? (int)(blockIdx.x * blockDim.x + threadIdx.x) : (int)blockIdx.x;
+  if (TEAM == 1 && c >= sh.channels) return;
+  const long long count = sh.count();
+  const int t0 = TEAM == 1 ? 0 : (int)threadIdx.x;
+  const double g = (double)scale[c];
+  const double variance = (double)(T)epsilon + (double)batch_variances[c];
+  const double inv_std = 1.0 / sqrt(variance);
+  const double mean = (double)batch_means[c];
+  const double d_var = (double)(T)(-0.5 * pow(variance, -1.5));
+  // pass 1: bias gradient, scale gradient, and the three sums of the input gradient
+  double s_og = 0.0, s_og_xhat = 0.0, s_dvar = 0.0, s_dmean = 0.0, s_centered = 0.0;
+  for (long long idx = t0; idx < count; idx += TEAM) {
+    const long long o = sh.offset(c, idx);
+    const double og = (double)out_grad[o];
+    const double centered = (double)in[o] - mean;
+    const double dxhat = (double)(T)__dmul_rn(g, og);          // the reference stores it in the input gradient
+    s_og += og;
+    s_og_xhat += __dmul_rn(og, __dmul_rn(centered, inv_std));
+    s_dvar += __dmul_rn(__dmul_rn(dxhat, centered), d_var);
+    s_dmean += __dmul_rn(-dxhat, inv_std);
+    s_centered += __dmul_rn(-2.0, centered);
+  }
+  s_og = team_sum<TEAM>(s_og, red);
+  s_og_xhat = team_sum<TEAM>(s_og_xhat, red);
+  s_dvar = team_sum<TEAM>(s_dvar, red);
+  s_dmean = team_sum<TEAM>(s_dmean, red);
+  s_centered = team_sum<TEAM>(s_centered, red);
+  if (TEAM == 1 || threadIdx.x == 0) {
+    bias_grad[c] = (T)s_og;
+    scale_grad[c] = (T)s_og_xhat;
+  }
+  const double d_var_d_out = (double)(T)s_dvar;
+  const double d_mean_d_out = (double)(T)(s_dmean + __dmul_rn(d_var_d_out, s_centered / (double)count));
+  const double one_over_count = 1.0 / (double)count;
+  // pass 2: the input gradient
+  const double part3 = __dmul_rn(d_mean_d_out, one_over_count);
+  for (long long idx = t0; idx < count; idx += TEAM) {
+    const long long o = sh.offset(c, idx);
+    const double dxhat = (double)(T)__dmul_rn(g, (double)out_grad[o]);
+    const double centered = (double)in[o] - mean;
+    const double part1 = __dmul_rn(dxhat, inv_std);
+    const double part2 = __dmul_rn(__dmul_rn(__dmul_rn(d_var_d_out, 2.0), centered), one_over_count);
+    in_grad[o] = (T)__dadd_rn(__dadd_rn(part1, part2), part3);
+  }
+}
+
+int bn_train_check(cb200_stream* s, int dtype, int64_t batch, int64_t channels, int64_t inner, const char* what) {
+  CB_REQUIRE(s, "%s: null stream", what);
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "batch-normalization is only defined for float and double tensors");
+  CB_REQUIRE(batch >= 0 && channels >= 1 && inner >= 1 && channels <= 2147483647LL && inner <= 2147483647LL,
+             "%s: bad extents", what);
+  CB_REQUIRE(batch * channels * inner < 4294967296LL, "%s: more than 2^32 - 1 elements", what);
+  return CB200_OK;
+}
+
+template <typename T>
+int bn_update_launch(cb200_stream* s, const void* in, void* bm, void* bv, void* rm, void* rv, double factor,
+                     int64_t batch, int64_t channels, int64_t inner) {
+  DeviceGuard guard(s->device);
+  BnShape sh{batch, (int)channels, (int)inner};
+  if (inner == 1)
+    bn_update_kernel<T, 1><<<(unsigned)((channels + 127) / 128), 128, 0, s->stream>>>(
+        (const T*)in, (T*)bm, (T*)bv, (T*)rm, (T*)rv, factor, sh);
+  else
+    bn_update_kernel<T, BN_TEAM><<<(unsigned)channels, BN_TEAM, 0, s->stream>>>(
+        (const T*)in, (T*)bm, (T*)bv, (T*)rm, (T*)rv, factor, sh);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+int bn_update_entry(cb200_stream* s, int dtype, void* output, const void* input, void* batch_means, void* batch_variances,
+                    void* running_means, void* running_variances, double average_factor, const void* scale,
+                    const void* bias, double epsilon, int64_t batch, int64_t channels, int64_t inner) {
+  int rc = bn_train_check(s, dtype, batch, channels, inner, "batch_normalize_update_and_apply");
+  if (rc) return rc;
+  CB_REQUIRE(output && input && batch_means && batch_variances && running_means && running_variances && scale && bias,
+             "batch_normalize_update_and_apply: null argument");
+  if (batch == 0) return CB200_OK;
+  rc = dtype == CB200_FLOAT
+           ? bn_update_launch<float>(s, input, batch_means, batch_variances, running_means, running_variances,
+                                     average_factor, batch, channels, inner)
+           : bn_update_launch<double>(s, input, batch_means, batch_variances, running_means, running_variances,
+                                      average_factor, batch, channels, inner);
+  if (rc) return rc;
+  // the apply half is the inference kernel fed with this batch's statistics (cpu/tensor_math.clj:1574-1608)
+  return inner == 1 ? cb200_batch_normalize_eltwise(s, dtype, output, input, batch_means, batch_variances, scale, bias,
+                                                    epsilon, batch, channels)
+                    : cb200_batch_normalize_spatial(s, dtype, output, input, batch_means, batch_variances, scale, bias,
+                                                    epsilon, batch, channels, inner);
+}
+
+template <typename T>
+int bn_gradients_launch(cb200_stream* s, void* ig, void* sg, void* bg, const void* og, const void* in, const void* bm,
+                        const void* bv, const void* scale, double epsilon, int64_t batch, int64_t channels, int64_t inner) {
+  DeviceGuard guard(s->device);
+  BnShape sh{batch, (int)channels, (int)inner};
+  if (inner == 1)
+    bn_gradients_kernel<T, 1><<<(unsigned)((channels + 127) / 128), 128, 0, s->stream>>>(
+        (T*)ig, (T*)sg, (T*)bg, (const T*)og, (const T*)in, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, sh);
+  else
+    bn_gradients_kernel<T, BN_TEAM><<<(unsigned)channels, BN_TEAM, 0, s->stream>>>(
+        (T*)ig, (T*)sg, (T*)bg, (const T*)og, (const T*)in, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, sh);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+int bn_gradients_entry(cb200_stream* s, int dtype, void* input_gradient, void* scale_gradient, void* bias_gradient,
+                       const void* output_gradient, const void* input, const void* batch_means,
+                       const void* batch_variances, const void* scale, double epsilon, int64_t batch, int64_t channels,
+                       int64_t inner) {
+  int rc = bn_train_check(s, dtype, batch, channels, inner, "batch_normalize_gradients");
+  if (rc) return rc;
+  CB_REQUIRE(input_gradient && scale_gradient && bias_gradient && output_gradient && input && batch_means &&
+                 batch_variances && scale, "batch_normalize_gradients: null argument");
+  if (batch == 0) return CB200_OK;
+  return dtype == CB200_FLOAT
+             ? bn_gradients_launch<float>(s, input_gradient, scale_gradient, bias_gradient, output_gradient, input,
+                                          batch_means, batch_variances, scale, epsilon, batch, channels, inner)
+             : bn_gradients_launch<double>(s, input_gradient, scale_gradient, bias_gradient, output_gradient, input,
+                                           batch_means, batch_variances, scale, epsilon, batch, channels, inner);
+}
+
+int dense_nchw(const cb200_dims* d, const char* what) {
+  CB_REQUIRE(d->rev_shape[4] == 1, "%s: tensors must be 4-d [batch, channels, height, width]", what);
+  long long expect = 1;
+  for (int k = 0; k < 4; ++k) {
+    CB_REQUIRE(!d->index[k], "%s: index arrays are not supported", what);
+    CB_REQUIRE(d->rev_shape[k] == 1 || d->rev_strides[k] == expect, "%s: tensors must be dense", what);
+    expect *= d->rev_shape[k];
+  }
+  return CB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cb200_pooling_backward(cb200_stream* s, int dtype, void* in_grad, const cb200_dims* in_grad_dims, double in_grad_alpha,
+                           const void* in, const cb200_dims* in_dims, const void* out, const cb200_dims* out_dims,
+                           const void* out_grad, const cb200_dims* out_grad_dims, const cb200_pool_desc* desc) {
+  CB_REQUIRE(s && in_grad && in_grad_dims && in && in_dims && out && out_dims && out_grad && out_grad_dims && desc,
+             "pooling_backward: null argument");
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "pooling-backward! is only defined for float and double tensors");
+  CB_REQUIRE(desc->pool_op >= CB200_POOL_MAX && desc->pool_op <= CB200_POOL_AVG_EXC_PAD, "pooling_backward: unknown pool op %d",
+             desc->pool_op);
+  CB_REQUIRE(desc->kernel_width >= 1 && desc->kernel_height >= 1 && desc->stride_x >= 1 && desc->stride_y >= 1 &&
+                 desc->pad_x >= 0 && desc->pad_y >= 0, "pooling_backward: bad descriptor");
+  for (const cb200_dims* d : {in_grad_dims, in_dims, out_dims, out_grad_dims}) {
+    int rc = cb200_check_dims(d, "pooling_backward");
+    if (rc) return rc;
+    rc = dense_nchw(d, "pooling_backward");
+    if (rc) return rc;
+  }
+  for (int k = 0; k < 4; ++k) {
+    CB_REQUIRE(in_grad_dims->rev_shape[k] == in_dims->rev_shape[k], "pooling_backward: input and input-gradient shapes differ");
+    CB_REQUIRE(out_grad_dims->rev_shape[k] == out_dims->rev_shape[k], "pooling_backward: output and output-gradient shapes differ");
+  }
+  CB_REQUIRE(out_dims->rev_shape[3] == in_dims->rev_shape[3] && out_dims->rev_shape[2] == in_dims->rev_shape[2],
+             "pooling_backward: batch / channel counts of input and output differ");
+  PoolBwdGeom g;
+  g.in_h = in_dims->rev_shape[1]; g.in_w = in_dims->rev_shape[0];
+  g.out_h = out_dims->rev_shape[1]; g.out_w = out_dims->rev_shape[0];
+  g.kw = desc->kernel_width; g.kh = desc->kernel_height; g.pad_x = desc->pad_x; g.pad_y = desc->pad_y;
+  g.stride_x = desc->stride_x; g.stride_y = desc->stride_y;
+  const long long planes = (long long)in_dims->rev_shape[3] * in_dims->rev_shape[2];
+  const long long n_in = planes * g.in_h * g.in_w;
+  const long long n_out = planes * g.out_h * g.out_w;
+  if (n_in == 0) return CB200_OK;
+  CB_REQUIRE(n_in <= 2147483647LL && n_out <= 2147483647LL, "pooling_backward: a tensor has more than 2^31 - 1 elements");
+  DeviceGuard guard(s->device);
+  if (dtype == CB200_FLOAT)
+    pooling_backward_launch<float>(s, desc->pool_op, (float*)in_grad, (const float*)in, (const float*)out,
+                                   (const float*)out_grad, g, n_in, in_grad_alpha);
+  else
+    pooling_backward_launch<double>(s, desc->pool_op, (double*)in_grad, (const double*)in, (const double*)out,
+                                    (const double*)out_grad, g, n_in, in_grad_alpha);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+int cb200_batch_normalize_update_and_apply_eltwise(cb200_stream* s, int dtype, void* output, const void* input,
+                                                   void* batch_means, void* batch_variances, void* running_means,
+                                                   void* running_variances, double average_factor, const void* scale,
+                                                   const void* bias, double epsilon, int64_t batch_count,
+                                                   int64_t element_count) {
+  return bn_update_entry(s, dtype, output, input, batch_means, batch_variances, running_means, running_variances,
+                         average_factor, scale, bias, epsilon, batch_count, element_count, 1);
+}
+
+int cb200_batch_normalize_update_and_apply_spatial(cb200_stream* s, int dtype, void* output, const void* input,
+                                                   void* batch_means, void* batch_variances, void* running_means,
+                                                   void* running_variances, double average_factor, const void* scale,
+                                                   const void* bias, double epsilon, int64_t batch_count,
+                                                   int64_t channel_count, int64_t element_count) {
+  return bn_update_entry(s, dtype, output, input, batch_means, batch_variances, running_means, running_variances,
+                         average_factor, scale, bias, epsilon, batch_count, channel_count, element_count);
+}
+
+int cb200_batch_normalize_gradients_eltwise(cb200_stream* s, int dtype, void* input_gradient, void* scale_gradient,
+                                            void* bias_gradient, const void* output_gradient, const void* output,
+                                            const void* input, const void* batch_means, const void* batch_variances,
+                                            const void* scale, const void* bias, double epsilon, int64_t batch_count,
+                                            int64_t element_count) {
+  (void)output; (void)bias;      // carried by the protocol, not read by the arithmetic
+  return bn_gradients_entry(s, dtype, input_gradient, scale_gradient, bias_gradient, output_gradient, input, batch_means,
+                            batch_variances, scale, epsilon, batch_count, element_count, 1);
+}
+
+int cb200_batch_normalize_gradients_spatial(cb200_stream* s, int dtype, void* input_gradient, void* scale_gradient,
+                                            void* bias_gradient, const void* output_gradient, const void* output,
+                                            const void* input, const void* batch_means, const void* batch_variances,
+                                            const void* scale, const void* bias, double epsilon, int64_t batch_count,
+                                            int64_t channel_count, int64_t element_count) {
+  (void)output; (void)bias;
+  return bn_gradients_entry(s, dtype, input_gradient, scale_gradient, bias_gradient, output_gradient, input, batch_means,
+                            batch_variances, scale, epsilon, batch_count, channel_count, element_count);
+}
+
+}  // extern "C"

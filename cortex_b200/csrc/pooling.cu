@@ -309,9 +309,10 @@ bool pooling_launch_vec_f(cb200_stream* s, float* out, const float* in, const Po
   const long long planes = n_out / ((long long)g.out_w * g.out_h);
   const long long per_plane = (long long)g.out_h * groups_per_row;
   if (planes > 2147483647LL / ((per_plane + 255) / 256)) return false;
+  // one block per 256 (row, group) pairs of a plane, no cap: with a capped grid every block walks 3-4 planes and
+  // the ones with 4 set the kernel's duration
   long long blocks = planes * ((per_plane + 255) / 256);
-  const long long cap = (long long)s->sm_count * 16;
-  if (blocks > cap) blocks = cap;
+  if (blocks > 1048576) blocks = 1048576;
 #define CB_POOL_VEC(SX, PX) pooling_forward_vec_kernel<OP, KH, KW, SX, PX><<<(unsigned)blocks, 256, 0, s->stream>>>(out, in, g, (int)planes, groups_per_row, out_alpha)
   if (g.stride_x == 2 && g.pad_x == 0) CB_POOL_VEC(2, 0);
   else if (g.stride_x == 2) CB_POOL_VEC(2, 1);

@@ -588,40 +588,88 @@ def gemv(c, trans_a, alpha, A, x, beta):
     return c
 
 
-def batch_normalize(output, input, means, variances, scale, bias, epsilon):
-    """output = (input - mean) / sqrt(variance + epsilon) * scale + bias   (tensor.clj:1047-1145).
-    2 dimensions: elementwise, statistics per column; more: 'spatial', statistics per entry of the
-    second-to-last dimension, everything before it is batch."""
-    stats = [means, variances, scale, bias]
+def _batch_normalize_setup(io_args, stat_args, epsilon):
+    """The shared precondition checks of the batch-normalize calls (tensor.clj:1047-1102): returns
+    (kind, stat tensors as row vectors, input shape with a leading 1 for vectors)."""
+    input = io_args[0]
     input_shape = input.shape()
     if len(input_shape) == 1:
         input_shape = [1, input_shape[0]]
-    _external_library_check("batch-normalize", output, input, *stats)
+    _external_library_check("batch-normalize", *io_args, *stat_args)
     _require(float(epsilon) > 1e-5, "Epsilon cannot be smaller than 1e-5 (cudnn limitation", epsilon)
-    _ensure_vector_indexable(*stats)
-    stats = [as_row_vector(t) for t in stats]
+    _require(input.get_datatype() in ("float", "double"),
+             "batch-normalization is only defined for float and double tensors", input.get_datatype())
+    _ensure_vector_indexable(*stat_args)
+    stats = [as_row_vector(t) for t in stat_args]
     _require(len(input_shape) > 1, "Input shape needs at least 2 dimensions", input.shape())
-    _require(output.shape() == input.shape(), "Tensor input and output shapes do not match",
-             (input.shape(), output.shape()))
+    _require(len({tuple(t.shape()) for t in io_args}) == 1, "Tensor input and output shapes do not match",
+             [t.shape() for t in io_args])
     _require(len({tuple(t.shape()) for t in stats}) == 1, "means, variances, scale, bias must have same shape",
              [t.shape() for t in stats])
     n_stats = stats[0].shape()[0]
-    stream = check_stream()
-    bufs = [t.buffer for t in stats]
     if len(input_shape) == 2:
         _require(input_shape[1] == n_stats, "Means, variances, scale, bias must match input element count.",
                  (input_shape, n_stats))
+        return "eltwise", stats, input_shape
+    _require(input_shape[-2] == n_stats, "means, variances, scale bias size must match input channel count",
+             (input_shape, n_stats))
+    return "spatial", stats, input_shape
+
+
+def _spatial_extents(input_shape):
+    batch_count = 1
+    for v in input_shape[:-2]:
+        batch_count *= v
+    return batch_count, input_shape[-2], input_shape[-1]
+
+
+def batch_normalize(output, input, means, variances, scale, bias, epsilon):
+    """output = (input - mean) / sqrt(variance + epsilon) * scale + bias   (tensor.clj:1105-1145).
+    2 dimensions: elementwise, statistics per column; more: 'spatial', statistics per entry of the
+    second-to-last dimension, everything before it is batch."""
+    kind, stats, input_shape = _batch_normalize_setup([output, input], [means, variances, scale, bias], epsilon)
+    stream = check_stream()
+    bufs = [t.buffer for t in stats]
+    if kind == "eltwise":
         stream.batch_normalize_eltwise(output.buffer, input.buffer, *bufs, epsilon, input_shape[0], input_shape[1])
     else:
-        batch_count = 1
-        for v in input_shape[:-2]:
-            batch_count *= v
-        channel_count, element_count = input_shape[-2:]
-        _require(channel_count == n_stats, "means, variances, scale bias size must match input channel count",
-                 (input_shape, n_stats))
-        stream.batch_normalize_spatial(output.buffer, input.buffer, *bufs, epsilon, batch_count, channel_count,
-                                       element_count)
+        stream.batch_normalize_spatial(output.buffer, input.buffer, *bufs, epsilon, *_spatial_extents(input_shape))
     return output
+
+
+def batch_normalize_update_and_apply(output, input, batch_means, batch_variances, running_means, running_variances,
+                                     ave_factor, scale, bias, epsilon):
+    """Per-batch statistics, running statistics (running * (1 - ave-factor) + batch * ave-factor) and the
+    normalised output in one call (tensor.clj:1147-1199).  Returns
+    [output, batch_means, batch_variances, running_means, running_variances]."""
+    kind, stats, input_shape = _batch_normalize_setup(
+        [output, input], [batch_means, batch_variances, running_means, running_variances, scale, bias], epsilon)
+    bm, bv, rm, rv, sc, bi = [t.buffer for t in stats]
+    stream = check_stream()
+    if kind == "eltwise":
+        stream.batch_normalize_update_and_apply_eltwise(output.buffer, input.buffer, bm, bv, rm, rv, ave_factor, sc, bi,
+                                                        epsilon, input_shape[0], input_shape[1])
+    else:
+        stream.batch_normalize_update_and_apply_spatial(output.buffer, input.buffer, bm, bv, rm, rv, ave_factor, sc, bi,
+                                                        epsilon, *_spatial_extents(input_shape))
+    return [output, batch_means, batch_variances, running_means, running_variances]
+
+
+def batch_normalize_gradients(input_gradient, scale_gradient, bias_gradient, output_gradient, output, input,
+                              batch_means, batch_variances, scale, bias, epsilon):
+    """Gradients of the training form; batch_means / batch_variances must be what update-and-apply wrote
+    (tensor.clj:1202-1250).  Returns [input_gradient, scale_gradient, bias_gradient]."""
+    kind, stats, input_shape = _batch_normalize_setup(
+        [output, input, output_gradient, input_gradient],
+        [batch_means, batch_variances, scale, bias, scale_gradient, bias_gradient], epsilon)
+    bm, bv, sc, bi, sg, bg = [t.buffer for t in stats]
+    stream = check_stream()
+    args = (input_gradient.buffer, sg, bg, output_gradient.buffer, output.buffer, input.buffer, bm, bv, sc, bi, epsilon)
+    if kind == "eltwise":
+        stream.batch_normalize_gradients_eltwise(*args, input_shape[0], input_shape[1])
+    else:
+        stream.batch_normalize_gradients_spatial(*args, *_spatial_extents(input_shape))
+    return [input_gradient, scale_gradient, bias_gradient]
 
 
 # ------------------------------ softmax! -------------------------------------------
@@ -754,6 +802,19 @@ def pooling_forward(output, output_alpha, input, pool_descriptor):
     check_stream().pooling_forward(output.buffer, output.dimensions, output_alpha, input.buffer, input.dimensions,
                                    pool_descriptor)
     return output
+
+
+def pooling_backward(input_gradient, input_grad_alpha, input, output, output_gradient, pool_descriptor):
+    """tensor.clj:1541-1551."""
+    _external_library_check("pooling-backward!", input_gradient, input, output, output_gradient)
+    for t in (input_gradient, input, output, output_gradient):
+        _require(len(t.shape()) == 4, "Input, output must be 4d tensors")
+    _ensure_conv_io(pool_descriptor, input_gradient, output)
+    _ensure_conv_io(pool_descriptor, input, output_gradient)
+    check_stream().pooling_backward(input_gradient.buffer, input_gradient.dimensions, input_grad_alpha, input.buffer,
+                                    input.dimensions, output.buffer, output.dimensions, output_gradient.buffer,
+                                    output_gradient.dimensions, pool_descriptor)
+    return input_gradient
 
 
 def convolution_forward(output, output_alpha, input, weights, workspace, conv_descriptor, algorithms):

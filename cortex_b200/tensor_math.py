@@ -216,8 +216,37 @@ class CTensorMath:
         self._tm("batch_normalize_spatial", DTYPE_CODE[output.dtype], output.ptr, input.ptr, means.ptr, variances.ptr,
                  scale.ptr, bias.ptr, float(epsilon), int(batch_count), int(channel_count), int(element_count))
 
-    def batch_normalize_update(self, *a):
-        self._unsupported("batch-normalize-update-*!")
+    def batch_normalize_update_and_apply_eltwise(self, output, input, batch_means, batch_variances, running_means,
+                                                 running_variances, average_factor, scale, bias, epsilon, batch_count,
+                                                 element_count):
+        """tm/batch-normalize-update-and-apply-eltwise! (tensor/math.clj:137-148)."""
+        self._tm("batch_normalize_update_and_apply_eltwise", DTYPE_CODE[output.dtype], output.ptr, input.ptr,
+                 batch_means.ptr, batch_variances.ptr, running_means.ptr, running_variances.ptr, float(average_factor),
+                 scale.ptr, bias.ptr, float(epsilon), int(batch_count), int(element_count))
+
+    def batch_normalize_update_and_apply_spatial(self, output, input, batch_means, batch_variances, running_means,
+                                                 running_variances, average_factor, scale, bias, epsilon, batch_count,
+                                                 channel_count, element_count):
+        """tm/batch-normalize-update-and-apply-spatial! (tensor/math.clj:149-158)."""
+        self._tm("batch_normalize_update_and_apply_spatial", DTYPE_CODE[output.dtype], output.ptr, input.ptr,
+                 batch_means.ptr, batch_variances.ptr, running_means.ptr, running_variances.ptr, float(average_factor),
+                 scale.ptr, bias.ptr, float(epsilon), int(batch_count), int(channel_count), int(element_count))
+
+    def batch_normalize_gradients_eltwise(self, input_gradient, scale_gradient, bias_gradient, output_gradient, output,
+                                          input, batch_means, batch_variances, scale, bias, epsilon, batch_count,
+                                          element_count):
+        """tm/batch-normalize-gradients-eltwise! (tensor/math.clj:159-166)."""
+        self._tm("batch_normalize_gradients_eltwise", DTYPE_CODE[output.dtype], input_gradient.ptr, scale_gradient.ptr,
+                 bias_gradient.ptr, output_gradient.ptr, output.ptr, input.ptr, batch_means.ptr, batch_variances.ptr,
+                 scale.ptr, bias.ptr, float(epsilon), int(batch_count), int(element_count))
+
+    def batch_normalize_gradients_spatial(self, input_gradient, scale_gradient, bias_gradient, output_gradient, output,
+                                          input, batch_means, batch_variances, scale, bias, epsilon, batch_count,
+                                          channel_count, element_count):
+        """tm/batch-normalize-gradients-spatial! (tensor/math.clj:167-174)."""
+        self._tm("batch_normalize_gradients_spatial", DTYPE_CODE[output.dtype], input_gradient.ptr, scale_gradient.ptr,
+                 bias_gradient.ptr, output_gradient.ptr, output.ptr, input.ptr, batch_means.ptr, batch_variances.ptr,
+                 scale.ptr, bias.ptr, float(epsilon), int(batch_count), int(channel_count), int(element_count))
 
     def pooling_descriptor(self, datatype, kern_width, kern_height, pad_x, pad_y, stride_x, stride_y, pool_op,
                            dimension_op):
@@ -232,8 +261,16 @@ class CTensorMath:
         self._tm("pooling_forward", DTYPE_CODE[output.dtype], output.ptr, C.byref(wire(output_dims)), float(output_alpha),
                  input.ptr, C.byref(wire(input_dims)), C.byref(desc))
 
-    def pooling_backward(self, *a):
-        self._unsupported("pooling-backward!")
+    def pooling_backward(self, input_grad, input_grad_dims, input_grad_alpha, input, input_dims, output, output_dims,
+                         output_grad, output_grad_dims, pool_descriptor):
+        """tm/pooling-backward! (tensor/math.clj:223-236)."""
+        from ._lib import POOL_OPS, PoolDesc
+        d = pool_descriptor
+        desc = PoolDesc(d["kernel-width"], d["kernel-height"], d["pad-x"], d["pad-y"], d["stride-x"], d["stride-y"],
+                        POOL_OPS[d["pool-op"]])
+        self._tm("pooling_backward", DTYPE_CODE[output.dtype], input_grad.ptr, C.byref(wire(input_grad_dims)),
+                 float(input_grad_alpha), input.ptr, C.byref(wire(input_dims)), output.ptr, C.byref(wire(output_dims)),
+                 output_grad.ptr, C.byref(wire(output_grad_dims)), C.byref(desc))
 
     def rand(self, dest, dest_dims, distribution, seed=0, sequence=0):
         """tm/rand! (tensor/math.clj:237) + the (seed, sequence) pair of the counter-based generator."""

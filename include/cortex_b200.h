@@ -283,6 +283,60 @@ typedef struct cb200_pool_desc {
 int cb200_pooling_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, double out_alpha,
                           const void* in, const cb200_dims* in_dims, const cb200_pool_desc* desc);
 
+/* pooling-backward! (src/cortex/tensor/math.clj:223-236; cudnnPoolingBackward at
+ * src/cortex/compute/cuda/tensor_math.clj:1201-1235; arithmetic after the CPU backend,
+ * src/cortex/compute/cpu/tensor_math.clj:1175-1284).  NCHW dense tensors; `in` / `out` are the tensors of the
+ * forward call, `out_grad` has the shape of `out`, `in_grad` the shape of `in`.
+ *   max:         every input position equal to its window's output receives that window's output gradient;
+ *   avg:         output gradient / (kernel_width * kernel_height) to every position of the window inside the image;
+ *   avg-exc-pad: the same with the number of window positions inside the image as divisor.
+ *   in_grad = in_grad_alpha * in_grad + sum of contributions, summed in the reference's visiting order with every
+ *   partial sum rounded to the element type (bit-identical to the CPU backend, which always accumulates onto the
+ *   buffer it is given: in_grad_alpha = 1 on that buffer, or 0 on a zeroed one, reproduces it). */
+int cb200_pooling_backward(cb200_stream* s, int dtype, void* in_grad, const cb200_dims* in_grad_dims, double in_grad_alpha,
+                           const void* in, const cb200_dims* in_dims, const void* out, const cb200_dims* out_dims,
+                           const void* out_grad, const cb200_dims* out_grad_dims, const cb200_pool_desc* desc);
+
+/* batch-normalize-update-and-apply-eltwise! / -spatial! (src/cortex/tensor/math.clj:137-158;
+ * cudnnBatchNormalizationForwardTraining at src/cortex/compute/cuda/tensor_math.clj:727-775; arithmetic after
+ * src/cortex/compute/cpu/tensor_math.clj:820-900).  Per channel c over N = batch_count (* element_count) values:
+ *   batch_means[c]       = sum(x) / N                      batch_variances[c] = sum((mean - x)^2) / N
+ *   running_means[c]     = running_means[c] * (1 - f) + batch_means[c] * f
+ *   running_variances[c] = running_variances[c] * (1 - f) + (sum((mean - x)^2) / max(1, N - 1)) * f
+ * then output = batch-normalize of input with the batch statistics (the inference call above).  batch_variances
+ * holds plain variances (the reference's CUDA backend stores cudnn's 1/sqrt form there; the CPU backend, followed
+ * here, stores the variance).  Sums are carried in double. */
+int cb200_batch_normalize_update_and_apply_eltwise(cb200_stream* s, int dtype, void* output, const void* input,
+                                                   void* batch_means, void* batch_variances, void* running_means,
+                                                   void* running_variances, double average_factor, const void* scale,
+                                                   const void* bias, double epsilon, int64_t batch_count,
+                                                   int64_t element_count);
+int cb200_batch_normalize_update_and_apply_spatial(cb200_stream* s, int dtype, void* output, const void* input,
+                                                   void* batch_means, void* batch_variances, void* running_means,
+                                                   void* running_variances, double average_factor, const void* scale,
+                                                   const void* bias, double epsilon, int64_t batch_count,
+                                                   int64_t channel_count, int64_t element_count);
+
+/* batch-normalize-gradients-eltwise! / -spatial! (src/cortex/tensor/math.clj:159-174;
+ * cudnnBatchNormalizationBackward at src/cortex/compute/cuda/tensor_math.clj:790-850; arithmetic after
+ * src/cortex/compute/cpu/tensor_math.clj:903-1032).  batch_means / batch_variances are what update-and-apply
+ * wrote.  With inv_std = 1 / sqrt(variance + epsilon), d = scale * output_gradient, xc = input - mean:
+ *   bias_gradient[c]  = sum(output_gradient)          scale_gradient[c] = sum(output_gradient * xc * inv_std)
+ *   d_var  = sum(d * xc * (-0.5 * (variance + epsilon)^(-3/2)))
+ *   d_mean = sum(-d * inv_std) + d_var * sum(-2 * xc) / N
+ *   input_gradient = d * inv_std + d_var * 2 * xc / N + d_mean / N
+ * `output` and `bias` are part of the protocol signature and are not read. */
+int cb200_batch_normalize_gradients_eltwise(cb200_stream* s, int dtype, void* input_gradient, void* scale_gradient,
+                                            void* bias_gradient, const void* output_gradient, const void* output,
+                                            const void* input, const void* batch_means, const void* batch_variances,
+                                            const void* scale, const void* bias, double epsilon, int64_t batch_count,
+                                            int64_t element_count);
+int cb200_batch_normalize_gradients_spatial(cb200_stream* s, int dtype, void* input_gradient, void* scale_gradient,
+                                            void* bias_gradient, const void* output_gradient, const void* output,
+                                            const void* input, const void* batch_means, const void* batch_variances,
+                                            const void* scale, const void* bias, double epsilon, int64_t batch_count,
+                                            int64_t channel_count, int64_t element_count);
+
 /* ---- optimiser steps and rand! (the ring of the training path that touches the flat parameter buffer) ----
  * adam_step: resources/adam.cu:1-36 (the kernel this replaces), src/cortex/optimize/adam.clj:68-102 (CPU
  * arithmetic: double buffers follow it bit for bit, float buffers are evaluated in single precision like the

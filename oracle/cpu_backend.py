@@ -44,6 +44,9 @@ _SIGS = {
     "orc_gemm": [_i, _vp, _i64, _i, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _i64, _d],
     "orc_batch_normalize": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
     "orc_pooling_forward": [_i, _vp, _vp] + [_i64] * 11 + [_i],
+    "orc_pooling_backward": [_i, _vp, _vp, _vp, _vp] + [_i64] * 11 + [_i],
+    "orc_batch_normalize_update": [_i, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
+    "orc_batch_normalize_gradients": [_i] + [_vp] * 8 + [_d, _i64, _i64, _i64],
     "orc_gemv": [_i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],
     "orc_ternary_op": [_i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
     "orc_activation_gradient": [_i, _vp, _pd, _vp, _pd, _vp, _pd, _i, _i64],
@@ -177,6 +180,48 @@ class OracleStream(CTensorMath):
         _call("pooling_forward", DTYPE_CODE[output.dtype], output.ptr, input.ptr, batch * channels, in_h, in_w, out_h,
               out_w, d["kernel-width"], d["kernel-height"], d["pad-x"], d["pad-y"], d["stride-x"], d["stride-y"],
               POOL_OPS[d["pool-op"]])
+
+    def pooling_backward(self, input_grad, input_grad_dims, input_grad_alpha, input, input_dims, output, output_dims,
+                         output_grad, output_grad_dims, pool_descriptor):
+        """cpu/tensor_math.clj:1829-1866: input-grad-alpha is not read; the loops add onto input-grad."""
+        from cortex_b200._lib import POOL_OPS
+        batch, channels, in_h, in_w = input_dims["shape"]
+        _b, _c, out_h, out_w = output_dims["shape"]
+        d = pool_descriptor
+        _call("pooling_backward", DTYPE_CODE[output.dtype], input_grad.ptr, input.ptr, output.ptr, output_grad.ptr,
+              batch * channels, in_h, in_w, out_h, out_w, d["kernel-width"], d["kernel-height"], d["pad-x"], d["pad-y"],
+              d["stride-x"], d["stride-y"], POOL_OPS[d["pool-op"]])
+
+    # -- batch-normalize training half (cpu/tensor_math.clj:1574-1640) ------------------------
+    def batch_normalize_update_and_apply_eltwise(self, output, input, batch_means, batch_variances, running_means,
+                                                 running_variances, average_factor, scale, bias, epsilon, batch_count,
+                                                 element_count):
+        self.batch_normalize_update_and_apply_spatial(output, input, batch_means, batch_variances, running_means,
+                                                      running_variances, average_factor, scale, bias, epsilon,
+                                                      batch_count, element_count, 1)
+
+    def batch_normalize_update_and_apply_spatial(self, output, input, batch_means, batch_variances, running_means,
+                                                 running_variances, average_factor, scale, bias, epsilon, batch_count,
+                                                 channel_count, element_count):
+        _call("batch_normalize_update", DTYPE_CODE[output.dtype], input.ptr, batch_means.ptr, batch_variances.ptr,
+              running_means.ptr, running_variances.ptr, float(average_factor), int(batch_count), int(channel_count),
+              int(element_count))
+        _call("batch_normalize", DTYPE_CODE[output.dtype], output.ptr, input.ptr, batch_means.ptr, batch_variances.ptr,
+              scale.ptr, bias.ptr, float(epsilon), int(batch_count), int(channel_count), int(element_count))
+
+    def batch_normalize_gradients_eltwise(self, input_gradient, scale_gradient, bias_gradient, output_gradient, output,
+                                          input, batch_means, batch_variances, scale, bias, epsilon, batch_count,
+                                          element_count):
+        self.batch_normalize_gradients_spatial(input_gradient, scale_gradient, bias_gradient, output_gradient, output,
+                                               input, batch_means, batch_variances, scale, bias, epsilon, batch_count,
+                                               element_count, 1)
+
+    def batch_normalize_gradients_spatial(self, input_gradient, scale_gradient, bias_gradient, output_gradient, output,
+                                          input, batch_means, batch_variances, scale, bias, epsilon, batch_count,
+                                          channel_count, element_count):
+        _call("batch_normalize_gradients", DTYPE_CODE[output.dtype], input_gradient.ptr, scale_gradient.ptr,
+              bias_gradient.ptr, output_gradient.ptr, input.ptr, batch_means.ptr, batch_variances.ptr, scale.ptr,
+              float(epsilon), int(batch_count), int(channel_count), int(element_count))
 
     # -- gemm: BLAS semantics (src/cortex/compute/cpu/tensor_math.clj:672-699) ---------------
     @staticmethod

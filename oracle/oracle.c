@@ -438,6 +438,100 @@ int orc_pooling_forward(int dtype, void* out, const void* in, int64_t planes, in
   return 1;
 }
 
+/* ---- pooling backward (cpu/tensor_math.clj:1175-1284, same loop nest) ------------------------------------
+ * Scatter form, as the reference: for each (plane, out-y, out-x) and window position inside the image,
+ * max: if in == out then in_grad = (T)(in_grad + out_grad); avg: in_grad = (T)(in_grad + out_grad / (kW*kH));
+ * avg-exc-pad: the same with the number of window positions inside the image.  Always accumulates onto the
+ * buffer it is given (the CPU backend never reads input-grad-alpha). */
+#define POOLB_BODY(T) { const T* ip = (const T*)in; const T* op_ = (const T*)out; const T* ogp = (const T*)out_grad; T* igp = (T*)in_grad; \
+  _Pragma("omp parallel for") for (int64_t plane = 0; plane < planes; ++plane) { \
+    const T* src = ip + plane * in_h * in_w; T* ig = igp + plane * in_h * in_w; \
+    const T* o = op_ + plane * out_h * out_w; const T* og = ogp + plane * out_h * out_w; \
+    for (int64_t oy = 0; oy < out_h; ++oy) for (int64_t ox = 0; ox < out_w; ++ox) { \
+      int64_t rel_x = ox * stride_x - pad_x, rel_y = oy * stride_y - pad_y; \
+      int64_t over_x = rel_x + kw - in_w; if (over_x < 0) over_x = 0; int64_t over_y = rel_y + kh - in_h; if (over_y < 0) over_y = 0; \
+      int64_t under_x = rel_x < 0 ? rel_x : 0, under_y = rel_y < 0 ? rel_y : 0; \
+      int64_t exc_w = kw - over_x + under_x; if (exc_w < 0) exc_w = 0; int64_t exc_h = kh - over_y + under_y; if (exc_h < 0) exc_h = 0; \
+      int64_t oaddr = oy * out_w + ox; \
+      for (int64_t ky = 0; ky < kh; ++ky) for (int64_t kx = 0; kx < kw; ++kx) { \
+        int64_t ix = rel_x + kx, iy = rel_y + ky; \
+        if (!(ix >= 0 && ix < in_w && iy >= 0 && iy < in_h)) continue; \
+        T* g = ig + iy * in_w + ix; \
+        if (op == 0) { if (src[iy * in_w + ix] == o[oaddr]) *g = (T)((double)*g + (double)og[oaddr]); } \
+        else if (op == 1) *g = (T)((double)*g + (double)og[oaddr] / (double)(kw * kh)); \
+        else *g = (T)((double)*g + (double)og[oaddr] / (double)(exc_w * exc_h)); } } } return 0; }
+int orc_pooling_backward(int dtype, void* in_grad, const void* in, const void* out, const void* out_grad, int64_t planes,
+                         int64_t in_h, int64_t in_w, int64_t out_h, int64_t out_w, int64_t kw, int64_t kh, int64_t pad_x,
+                         int64_t pad_y, int64_t stride_x, int64_t stride_y, int op) {
+  if (dtype == T_FLOAT) POOLB_BODY(float)
+  if (dtype == T_DOUBLE) POOLB_BODY(double)
+  return 1;
+}
+
+/* ---- batch-normalize statistics update (cpu/tensor_math.clj:820-900) -----------------------------------
+ * Per channel, sequential double sums over idx = 0 .. batch*inner - 1 (offset as in BN_BODY):
+ *   new_mean = (T)(sum(x) / max(1, N));  var = sum((new_mean - x)^2)
+ *   batch_means = new_mean; batch_variances = (T)(var / max(1, N))
+ *   running_means = (T)(running_means * (1 - f) + new_mean * f), f = (T)average_factor, 1 - f in double
+ *   running_variances = (T)(running_variances * (1 - f) + (T)(var / max(1, N - 1)) * f) */
+#define BNU_BODY(T) { const T* ip = (const T*)in; T* bm = (T*)batch_means; T* bv = (T*)batch_variances; \
+  T* rm = (T*)running_means; T* rv = (T*)running_variances; \
+  double f = (double)(T)average_factor, lerp = (double)(T)1.0 - f; int64_t count = batch * inner; \
+  double n = count > 1 ? (double)count : 1.0, nr = n - 1.0 > 1.0 ? n - 1.0 : 1.0; \
+  _Pragma("omp parallel for") for (int64_t c = 0; c < channels; ++c) { \
+    double sum = 0.0; \
+    for (int64_t idx = 0; idx < count; ++idx) sum += (double)ip[((idx / inner) * channels + c) * inner + idx % inner]; \
+    T new_mean = (T)(sum / n); double var = 0.0; \
+    for (int64_t idx = 0; idx < count; ++idx) { \
+      double d = (double)new_mean - (double)ip[((idx / inner) * channels + c) * inner + idx % inner]; var += d * d; } \
+    double mean_old = rm[c], var_old = rv[c]; \
+    bm[c] = new_mean; bv[c] = (T)(var / n); \
+    rm[c] = (T)(mean_old * lerp + (double)new_mean * f); \
+    rv[c] = (T)(var_old * lerp + (double)(T)(var / nr) * f); } return 0; }
+int orc_batch_normalize_update(int dtype, const void* in, void* batch_means, void* batch_variances, void* running_means,
+                               void* running_variances, double average_factor, int64_t batch, int64_t channels,
+                               int64_t inner) {
+  if (dtype == T_FLOAT) BNU_BODY(float)
+  if (dtype == T_DOUBLE) BNU_BODY(double)
+  return 1;
+}
+
+/* ---- batch-normalize gradients (cpu/tensor_math.clj:903-1032) --------------------------------------------
+ * Per channel, with variance = (T)epsilon + batch_variance, inv_std = 1 / sqrt(variance),
+ * d_var = (T)(-0.5 * pow(variance, -1.5)) and sequential double sums:
+ *   bias_grad = (T)sum(og); scale_grad = (T)sum(og * ((x - mean) * inv_std))
+ *   in_grad <- (T)(scale * og)                                   (d x_hat / d out, kept in the input gradient)
+ *   d_var_d_out = (T)sum((in_grad * (x - mean)) * d_var)
+ *   d_mean_d_out = (T)(sum(-in_grad * inv_std) + d_var_d_out * (sum(-2 * (x - mean)) / N))
+ *   in_grad <- (T)((in_grad * inv_std + ((d_var_d_out * 2) * (x - mean)) * (1 / N)) + d_mean_d_out * (1 / N)) */
+#define BNG_OFF(idx) (((idx) / inner) * channels + c) * inner + (idx) % inner
+#define BNG_BODY(T) { T* ig = (T*)in_grad; T* sg = (T*)scale_grad; T* bg = (T*)bias_grad; const T* og = (const T*)out_grad; \
+  const T* ip = (const T*)in; const T* bm = (const T*)batch_means; const T* bv = (const T*)batch_variances; \
+  const T* sp = (const T*)scale; double eps = (double)(T)epsilon; int64_t count = batch * inner; \
+  _Pragma("omp parallel for") for (int64_t c = 0; c < channels; ++c) { \
+    double g = sp[c], variance = eps + (double)bv[c], inv_std = 1.0 / sqrt(variance), mean = bm[c]; \
+    double d_var = (double)(T)(-0.5 * pow(variance, (double)(T)(-3.0 / 2.0))); \
+    double s = 0.0; for (int64_t i = 0; i < count; ++i) s += (double)og[BNG_OFF(i)]; bg[c] = (T)s; \
+    s = 0.0; for (int64_t i = 0; i < count; ++i) { int64_t o = BNG_OFF(i); s += (double)og[o] * (((double)ip[o] - mean) * inv_std); } sg[c] = (T)s; \
+    for (int64_t i = 0; i < count; ++i) { int64_t o = BNG_OFF(i); ig[o] = (T)(g * (double)og[o]); } \
+    s = 0.0; for (int64_t i = 0; i < count; ++i) { int64_t o = BNG_OFF(i); s += ((double)ig[o] * ((double)ip[o] - mean)) * d_var; } \
+    double d_var_d_out = (double)(T)s; \
+    double s1 = 0.0; for (int64_t i = 0; i < count; ++i) { int64_t o = BNG_OFF(i); s1 += (-(double)ig[o]) * inv_std; } \
+    double s2 = 0.0; for (int64_t i = 0; i < count; ++i) { int64_t o = BNG_OFF(i); s2 += -2.0 * ((double)ip[o] - mean); } \
+    double d_mean_d_out = (double)(T)(s1 + d_var_d_out * (s2 / (double)count)); \
+    double one_over = 1.0 / (double)count; \
+    for (int64_t i = 0; i < count; ++i) { int64_t o = BNG_OFF(i); \
+      double p1 = (double)ig[o] * inv_std, p2 = ((d_var_d_out * 2.0) * ((double)ip[o] - mean)) * one_over, p3 = d_mean_d_out * one_over; \
+      ig[o] = (T)((p1 + p2) + p3); } } return 0; }
+int orc_batch_normalize_gradients(int dtype, void* in_grad, void* scale_grad, void* bias_grad, const void* out_grad,
+                                  const void* in, const void* batch_means, const void* batch_variances, const void* scale,
+                                  double epsilon, int64_t batch, int64_t channels, int64_t inner) {
+  if (batch * inner == 0) return 0;
+  if (dtype == T_FLOAT) BNG_BODY(float)
+  if (dtype == T_DOUBLE) BNG_BODY(double)
+  return 1;
+}
+
 /* ---- ternary select (cpu/tensor_math.clj:465-566) ------------------------------------------------
  * select-impl picks z when alpha*x >= 0, else y.  Tensor operands are multiplied by their factor (cast to
  * the element type) in the accumulator type (double / wrapping long).  A NULL pointer marks a constant

@@ -142,7 +142,11 @@ def test_conv_backward_matches_oracle(b200_driver, oracle_driver, datatype):
     against the oracle's restatement of the CPU backend and a float64 numpy convolution transpose."""
     for args in (dict(batch=2, cin=4, hw=9, cout=5), dict(batch=2, cin=3, hw=8, cout=4, k=2, pad=0, stride=2),
                  dict(batch=3, cin=16, hw=13, cout=40, k=5, pad=2), dict(batch=2, cin=32, hw=17, cout=36, k=3, pad=1, stride=2),
-                 dict(batch=4, cin=64, hw=28, cout=64)):
+                 dict(batch=4, cin=64, hw=28, cout=64),
+                 # stride 1 and a multiple of 16 output channels: the fp32 data gradient runs as a forward
+                 # convolution of the output gradient (mirrored filter, padding k - 1 - pad) on the TMA-fed kernels
+                 dict(batch=2, cin=24, hw=16, cout=32, k=3, pad=1), dict(batch=3, cin=8, hw=20, cout=16, k=5, pad=2),
+                 dict(batch=2, cin=16, hw=12, cout=16, k=3, pad=0), dict(batch=2, cin=40, hw=32, cout=48, k=1, pad=0)):
         run, ref = pc.conv_backward_case(datatype, **args)
         gpu, cpu = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
         assert pc.rel_err(gpu, cpu) <= pc.TOL[datatype], args
@@ -418,7 +422,9 @@ def test_mnist_convnet_matches_oracle(b200_driver, oracle_driver, datatype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(300, 384, 256), (130, 1000, 500), (128, 256, 16), (513, 260, 4112), (1024, 4096, 4096),
-                                   (1300, 520, 48)])
+                                   (1300, 520, 48),
+                                   # 84 / 91 pair tiles on 74 clusters: the last round runs as 256 x 128 half tiles
+                                   (3072, 1792, 64), (3300, 1700, 48)])
 @pytest.mark.parametrize("act", [None, "relu"])
 @pytest.mark.parametrize("variant", [1, 2])
 def test_presplit_layer_gemm(b200_driver, M, N, K, act, variant):

@@ -292,20 +292,104 @@ def batch_normalize(driver, datatype):
              46.3207369515159, 48.436773799091696, 50.55281064666749], ct.to_double_array(out), 1e-4)
 
 
+_BN_TRAIN_ELTWISE_OUT = [-0.023134696804511745, -0.023134696804511745, -0.023134696804511745, 2.6589551010651626,
+                         2.6589551010651626, 2.6589551010651626, 5.341044898934837, 5.341044898934837,
+                         5.341044898934837, 8.023134696804512, 8.023134696804512, 8.023134696804512]
+_BN_TRAIN_SPATIAL_OUT = [0.3139510961275713, 0.8054242833105618, 1.2968974704935523, 1.7883706576765428,
+                         0.3139510961275713, 0.8054242833105618, 1.2968974704935523, 1.7883706576765428,
+                         0.3139510961275713, 0.8054242833105618, 1.2968974704935523, 1.7883706576765428,
+                         6.211629342323457, 6.703102529506448, 7.194575716689438, 7.686048903872429,
+                         6.211629342323457, 6.703102529506448, 7.194575716689438, 7.686048903872429,
+                         6.211629342323457, 6.703102529506448, 7.194575716689438, 7.686048903872429]
+
+
+def _bn_train_stats():
+    return {"means": ct.to_tensor([1] * 3), "variances": ct.to_tensor(list(range(3))),       # a variance of 0 included
+            "running-means": ct.to_tensor([2] * 3), "running-variances": ct.to_tensor([4] * 3),
+            "scale": ct.to_tensor([3] * 3), "bias": ct.to_tensor([4] * 3)}
+
+
+def batch_normalize_update_and_apply(driver, datatype):
+    """verify/tensor.clj:349-428"""
+    with tensor_context(driver, datatype):
+        for shape, exp_out, exp_means, exp_rm, exp_rv in (
+                ([4, 3], _BN_TRAIN_ELTWISE_OUT, [4.5, 5.5, 6.5], [4.0, 4.8, 5.6000000000000005], [12.8] * 3),
+                ([2, 3, 4], _BN_TRAIN_SPATIAL_OUT, [7.5, 11.5, 15.5], [6.4, 9.6, 12.8], [34.857142857142854] * 3)):
+            inp = ct.to_tensor(np.arange(int(np.prod(shape))).reshape(shape))
+            out = ct.new_tensor(shape)
+            st = _bn_train_stats()
+            ct.batch_normalize_update_and_apply(out, inp, st["means"], st["variances"], st["running-means"],
+                                                st["running-variances"], 0.8, st["scale"], st["bias"], 1e-2)
+            _eq(exp_out, ct.to_double_array(out), 1e-4)
+            _eq(exp_means, ct.to_double_array(st["means"]), 1e-4)
+            _eq(exp_rm, ct.to_double_array(st["running-means"]), 1e-4)
+            _eq(exp_rv, ct.to_double_array(st["running-variances"]), 1e-4)
+
+
+def batch_normalize_gradients(driver, datatype):
+    """verify/tensor.clj:431-530"""
+    with tensor_context(driver, datatype):
+        cases = (
+            ([4, 3], _BN_TRAIN_ELTWISE_OUT,
+             [-0.003572943780465465, -0.003572943780465465, -0.003572943780465465, -0.001190981260155155,
+              -0.001190981260154711, -0.001190981260154489, 0.001190981260154933, 0.001190981260155155,
+              0.0011909812601555991, 0.0035729437804663533, 0.0035729437804663533, 0.0035729437804663533], 1e-4,
+             [13.410448989348373] * 3, [18, 22, 26]),
+            ([2, 3, 4], _BN_TRAIN_SPATIAL_OUT,
+             [-9.892777519776665E-4, -8.57374051714065E-4, -7.254703514504634E-4, -5.935666511868618E-4,
+              -9.89277751978103E-4, -8.57374051714065E-4, -7.254703514500268E-4, -5.935666511868618E-4,
+              -9.89277751978103E-4, -8.57374051714065E-4, -7.254703514500268E-4, -5.935666511868618E-4,
+              5.935666511868618E-4, 7.254703514504634E-4, 8.57374051714065E-4, 9.892777519776665E-4,
+              5.935666511868618E-4, 7.254703514500268E-4, 8.57374051714065E-4, 9.89277751978103E-4,
+              5.935666511868618E-4, 7.254703514500268E-4, 8.57374051714065E-4, 9.89277751978103E-4], 1e-6,
+             [48.81966992684372] * 3, [60.0, 92.0, 124.0]))
+        for shape, exp_out, exp_in_grad, grad_tol, exp_scale_grad, exp_bias_grad in cases:
+            n = int(np.prod(shape))
+            inp = ct.to_tensor(np.arange(n).reshape(shape))
+            out = ct.new_tensor(shape)
+            in_grad = ct.new_tensor(shape)
+            out_grad = ct.to_tensor(np.arange(n).reshape(shape))
+            st = _bn_train_stats()
+            scale_grad, bias_grad = ct.new_tensor([3]), ct.new_tensor([3])
+            ct.batch_normalize_update_and_apply(out, inp, st["means"], st["variances"], st["running-means"],
+                                                st["running-variances"], 0.8, st["scale"], st["bias"], 1e-2)
+            ct.batch_normalize_gradients(in_grad, scale_grad, bias_grad, out_grad, out, inp, st["means"],
+                                         st["variances"], st["scale"], st["bias"], 1e-2)
+            _eq(exp_out, ct.to_double_array(out), 1e-4)
+            _eq(exp_in_grad, ct.to_double_array(in_grad), grad_tol)
+            _eq(exp_scale_grad, ct.to_double_array(scale_grad), 1e-4)
+            _eq(exp_bias_grad, ct.to_double_array(bias_grad), 1e-4)
+
+
+_POOL_MAX_BACKWARD = [
+    0.0, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 1.0, 0.0, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 1.0, 0.0, 1.0, 0.0, 1.0, 0.0, 0.0,
+    0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 1.0, 0.0, 0.0, 0.0, 0.0, 0.0, 2.0, 0.0, 2.0, 0.0, 0.0, 0.0, 0.0,
+    0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 1.0, 0.0, 1.0, 0.0, 1.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0,
+    0.0, 0.0, 0.0, 1.0, 0.0, 1.0, 0.0, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 1.0, 0.0, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 1.0,
+    0.0, 0.0, 0.0, 0.0, 0.0, 1.0, 0.0, 1.0, 0.0, 1.0, 0.0, 1.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 1.0,
+    0.0, 1.0, 0.0, 0.0, 0.0, 0.0, 0.0, 2.0, 0.0, 2.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0]
+
+
 def pooling_operator(driver, datatype):
-    """verify/tensor.clj:893-947 (forward half)"""
+    """verify/tensor.clj:893-1033: the three pool operations forward, then backward with an output gradient of
+    ones into zeroed input gradients."""
     with tensor_context(driver, datatype):
         channels, dimension, batch = 4, 4, 2
         n = batch * channels * dimension * dimension
         data = np.resize(np.arange(-5, 15), n).reshape(batch, channels, dimension, dimension)
         inp = ct.to_tensor(data)
-        outs = {}
+        outs, grads = {}, {}
         for op in ("max", "avg", "avg-exc-pad"):
             desc = ct.pooling_descriptor(datatype, channels, 3, 3, 1, 1, 2, 2, pool_op=op, dimension_op="floor")
             od = ct.get_convolution_output_dimensions(desc, dimension, dimension)
-            out = ct.new_tensor([batch, channels, od["output-width"], od["output-height"]])
+            out_shape = [batch, channels, od["output-width"], od["output-height"]]
+            out = ct.new_tensor(out_shape)
             ct.pooling_forward(out, 0.0, inp, desc)
             outs[op] = ct.to_double_array(out)
+            out_grad = ct.to_tensor(np.ones(out_shape))
+            in_grad = ct.new_tensor([batch, channels, dimension, dimension])
+            ct.pooling_backward(in_grad, 0.0, inp, out, out_grad, desc)
+            grads[op] = ct.to_double_array(in_grad)
         _eq([0.0, 2.0, 8.0, 10.0, 12.0, 14.0, 4.0, 6.0, 12.0, 14.0, 12.0, 14.0, 8.0, 10.0, 12.0, 14.0, 4.0, 6.0, 12.0,
              14.0, 0.0, 2.0, 8.0, 10.0, 12.0, 14.0, 4.0, 6.0, 12.0, 14.0, 12.0, 14.0], outs["max"])
         _eq([-1.1111111111111112, -0.6666666666666666, 2.3333333333333335, 5.0, 1.5555555555555556,
@@ -317,6 +401,16 @@ def pooling_operator(driver, datatype):
         _eq([-2.5, -1.0, 3.5, 5.0, 3.5, 5.0, -0.5, 1.0, 9.5, 11.0, 2.1666666666666665, 3.6666666666666665, 5.5, 7.0,
              4.833333333333333, 6.333333333333333, 1.5, 3.0, 7.5, 9.0, -2.5, -1.0, 3.5, 5.0, 3.5, 5.0, -0.5, 1.0, 9.5,
              11.0, 2.1666666666666665, 3.6666666666666665], outs["avg-exc-pad"], 1e-4)
+        _eq(_POOL_MAX_BACKWARD, grads["max"], 1e-4)
+        # the averaged forms give every plane the same pattern (the reference spells the 128 values out)
+        ninth = 0.1111111111111111
+        avg_plane = [ninth, 2 * ninth, ninth, ninth, 2 * ninth, 4 * ninth, 2 * ninth, 2 * ninth,
+                     ninth, 2 * ninth, ninth, ninth, ninth, 2 * ninth, ninth, ninth]
+        _eq(avg_plane * (batch * channels), grads["avg"], 1e-4)
+        exc_plane = [0.25, 0.41666666666666663, 0.16666666666666666, 0.16666666666666666, 0.41666666666666663,
+                     0.6944444444444444, 0.2777777777777778, 0.2777777777777778, 0.16666666666666666,
+                     0.2777777777777778, ninth, ninth, 0.16666666666666666, 0.2777777777777778, ninth, ninth]
+        _eq(exc_plane * (batch * channels), grads["avg-exc-pad"], 1e-4)
 
 
 def ternary_op_select(driver, datatype):
@@ -718,6 +812,7 @@ CASES = [
     (assign_constant, ALL_DTYPES), (assign_marshal, ALL_DTYPES), (unary_op, ALL_DTYPES), (channel_op, ALL_DTYPES),
     (binary_constant_op, ALL_DTYPES), (binary_op, ALL_DTYPES), (gemm, FLOAT_DTYPES), (gemv, FLOAT_DTYPES),
     (ternary_op_select, ALL_DTYPES), (batch_normalize, FLOAT_DTYPES), (pooling_operator, FLOAT_DTYPES),
+    (batch_normalize_update_and_apply, FLOAT_DTYPES), (batch_normalize_gradients, FLOAT_DTYPES),
     (activation_gradient, FLOAT_DTYPES), (linear_layer_backward, FLOAT_DTYPES), (relu_layer_backward, FLOAT_DTYPES),
     (activation_forward, FLOAT_DTYPES), (softmax, FLOAT_DTYPES), (unary_reduce, ALL_DTYPES), (transpose, ALL_DTYPES),
     (mask, INT_LONG), (select, ALL_DTYPES), (select_transpose_interaction, ALL_DTYPES),
