@@ -45,6 +45,10 @@ class PoolDesc(C.Structure):
 POOL_OPS = {"max": 0, "avg": 1, "avg-exc-pad": 2}
 
 
+class LrnDesc(C.Structure):
+    _fields_ = [("n", C.c_int32), ("k", C.c_double), ("alpha", C.c_double), ("beta", C.c_double)]
+
+
 class B200Error(RuntimeError):
     def __init__(self, code, message):
         super().__init__("cortex_b200 error %d: %s" % (code, message))
@@ -102,6 +106,8 @@ SIGNATURES = {
     "cb200_batch_normalize_spatial": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
     "cb200_pooling_forward": [_vp, _i, _vp, _pd, _d, _vp, _pd, C.POINTER(PoolDesc)],
     "cb200_pooling_backward": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _pd, C.POINTER(PoolDesc)],
+    "cb200_lrn_forward": [_vp, _i, _vp, _pd, _vp, _pd, C.POINTER(LrnDesc)],
+    "cb200_lrn_backward": [_vp, _i, _vp, _pd, _vp, _pd, _vp, _pd, _vp, _pd, C.POINTER(LrnDesc)],
     "cb200_batch_normalize_update_and_apply_eltwise": [_vp, _i] + [_vp] * 6 + [_d, _vp, _vp, _d, _i64, _i64],
     "cb200_batch_normalize_update_and_apply_spatial": [_vp, _i] + [_vp] * 6 + [_d, _vp, _vp, _d, _i64, _i64, _i64],
     "cb200_batch_normalize_gradients_eltwise": [_vp, _i] + [_vp] * 10 + [_d, _i64, _i64],

@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(LIBDIR, "obj")
 LIB = os.path.join(LIBDIR, "libcortex_b200.so")
-SOURCES = ["capi.cu", "elementwise.cu", "reduce.cu", "gemm.cu", "gemm_tf32x3.cu", "gemm_f64.cu", "conv.cu", "conv_igemm.cu", "conv_tma.cu", "conv_halo.cu", "ternary_gemv.cu", "batch_norm.cu", "pooling.cu", "gemm_presplit.cu", "backward.cu", "conv_backward.cu", "optimize.cu", "nn_train.cu"]
+SOURCES = ["capi.cu", "elementwise.cu", "reduce.cu", "gemm.cu", "gemm_tf32x3.cu", "gemm_f64.cu", "conv.cu", "conv_igemm.cu", "conv_tma.cu", "conv_halo.cu", "ternary_gemv.cu", "batch_norm.cu", "pooling.cu", "gemm_presplit.cu", "backward.cu", "conv_backward.cu", "optimize.cu", "nn_train.cu", "lrn.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--expt-relaxed-constexpr",

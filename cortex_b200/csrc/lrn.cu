@@ -1,0 +1,156 @@
+// lrn-forward! / lrn-backward! (local response normalisation across channels):
+// src/cortex/tensor/math.clj:240-252; cudnnLRNCrossChannelForward / Backward with CUDNN_LRN_CROSS_CHANNEL_DIM1
+// in the reference CUDA backend (src/cortex/compute/cuda/tensor_math.clj:1277-1335; its CPU backend has no
+// implementation).  With the window W(c) = [c - floor((n-1)/2), c + n - 1 - floor((n-1)/2)] clipped to the
+// channel range and s(c) = k + (alpha / n) * sum_{j in W(c)} x_j^2:
+//   forward:   y_c  = x_c * s(c)^-beta
+//   backward:  dx_c = dy_c * s(c)^-beta - (2 * alpha * beta / n) * x_c * sum_{j in W(c)} dy_j * y_j / s(j)
+// (the backward sum runs over the same window as the forward one, as the library the reference calls does;
+// the reference's literals for n = 2 pin this).  Dense [.., channels, height, width] tensors of rank 3 to 5;
+// evaluated in double, rounded to the element type on store.
+#include "common.cuh"
+
+namespace {
+
+struct LrnGeom {
+  long long batch;
+  int channels;
+  long long plane;       // height * width
+  int look_behind, look_ahead;
+  double k, alpha_over_n, beta;
+};
+
+template <typename T>
+__device__ __forceinline__ double lrn_scale(const T* x, const LrnGeom& g, long long b, int c, long long p) {
+  const int c0 = max(0, c - g.look_behind), c1 = min(g.channels - 1, c + g.look_ahead);
+  double sum = 0.0;
+  for (int j = c0; j <= c1; ++j) {
+    const double v = (double)x[(b * g.channels + j) * g.plane + p];
+    sum += v * v;
+  }
+  return g.k + g.alpha_over_n * sum;
+}
+
+// WRITE_SCALE: store s(c) (backward pre-pass) instead of y
+template <typename T, bool WRITE_SCALE>
+__global__ void __launch_bounds__(256)
+lrn_forward_kernel(T* out, double* scale_out, const T* in, LrnGeom g, long long n_elems) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += (long long)gridDim.x * blockDim.x) {
+    const long long p = i % g.plane;
+    const long long bc = i / g.plane;
+    const int c = (int)(bc % g.channels);
+    const long long b = bc / g.channels;
+    const double s = lrn_scale(in, g, b, c, p);
+    if (WRITE_SCALE) scale_out[i] = s;
+    else out[i] = (T)((double)in[i] * pow(s, -g.beta));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+lrn_backward_kernel(T* in_grad, const T* out, const T* in, const T* out_grad, const double* scale, LrnGeom g,
+                    long long n_elems) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += (long long)gridDim.x * blockDim.x) {
+    const long long p = i % g.plane;
+    const long long bc = i / g.plane;
+    const int c = (int)(bc % g.channels);
+    const long long b = bc / g.channels;
+    const int c0 = max(0, c - g.look_behind), c1 = min(g.channels - 1, c + g.look_ahead);
+    double sum = 0.0;
+    for (int j = c0; j <= c1; ++j) {
+      const long long o = (b * g.channels + j) * g.plane + p;
+      sum += (double)out_grad[o] * (double)out[o] / scale[o];
+    }
+    const double direct = (double)out_grad[i] * pow(scale[i], -g.beta);
+    in_grad[i] = (T)(direct - 2.0 * g.alpha_over_n * g.beta * (double)in[i] * sum);
+  }
+}
+
+int lrn_geom(const cb200_dims* const* all, int count, const cb200_lrn_desc* desc, LrnGeom* g, long long* n_elems,
+             const char* what) {
+  CB_REQUIRE(desc->n >= 1, "%s: window width n must be at least 1", what);
+  for (int t = 0; t < count; ++t) {
+    const cb200_dims* d = all[t];
+    int rc = cb200_check_dims(d, what);
+    if (rc) return rc;
+    long long expect = 1;
+    for (int k = 0; k < 5; ++k) {
+      CB_REQUIRE(!d->index[k], "%s: index arrays are not supported", what);
+      CB_REQUIRE(d->rev_shape[k] == 1 || d->rev_strides[k] == expect, "%s: tensors must be dense", what);
+      CB_REQUIRE(d->rev_shape[k] == all[0]->rev_shape[k], "Input and output shapes must match");
+      expect *= d->rev_shape[k];
+    }
+  }
+  const cb200_dims* d = all[0];
+  g->plane = (long long)d->rev_shape[0] * d->rev_shape[1];
+  g->channels = d->rev_shape[2];
+  g->batch = (long long)d->rev_shape[3] * d->rev_shape[4];
+  g->look_behind = (desc->n - 1) / 2;
+  g->look_ahead = desc->n - g->look_behind - 1;
+  g->k = desc->k; g->alpha_over_n = desc->alpha / (double)desc->n; g->beta = desc->beta;
+  *n_elems = g->plane * g->channels * g->batch;
+  return CB200_OK;
+}
+
+unsigned lrn_blocks(cb200_stream* s, long long n) {
+  long long blocks = (n + 255) / 256;
+  const long long cap = (long long)s->sm_count * 32;
+  return (unsigned)(blocks < cap ? blocks : cap);
+}
+
+}  // namespace
+
+extern "C" {
+
+int cb200_lrn_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, const void* in,
+                      const cb200_dims* in_dims, const cb200_lrn_desc* desc) {
+  CB_REQUIRE(s && out && out_dims && in && in_dims && desc, "lrn_forward: null argument");
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "lrn-forward is only defined for float and double tensors");
+  const cb200_dims* all[2] = {in_dims, out_dims};
+  LrnGeom g;
+  long long n = 0;
+  int rc = lrn_geom(all, 2, desc, &g, &n, "lrn_forward");
+  if (rc) return rc;
+  if (n == 0) return CB200_OK;
+  DeviceGuard guard(s->device);
+  if (dtype == CB200_FLOAT)
+    lrn_forward_kernel<float, false><<<lrn_blocks(s, n), 256, 0, s->stream>>>((float*)out, nullptr, (const float*)in, g, n);
+  else
+    lrn_forward_kernel<double, false><<<lrn_blocks(s, n), 256, 0, s->stream>>>((double*)out, nullptr, (const double*)in, g, n);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+int cb200_lrn_backward(cb200_stream* s, int dtype, void* in_grad, const cb200_dims* in_grad_dims, const void* out,
+                       const cb200_dims* out_dims, const void* in, const cb200_dims* in_dims, const void* out_grad,
+                       const cb200_dims* out_grad_dims, const cb200_lrn_desc* desc) {
+  CB_REQUIRE(s && in_grad && in_grad_dims && out && out_dims && in && in_dims && out_grad && out_grad_dims && desc,
+             "lrn_backward: null argument");
+  CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "lrn-backward is only defined for float and double tensors");
+  const cb200_dims* all[4] = {in_dims, out_dims, in_grad_dims, out_grad_dims};
+  LrnGeom g;
+  long long n = 0;
+  int rc = lrn_geom(all, 4, desc, &g, &n, "lrn_backward");
+  if (rc) return rc;
+  if (n == 0) return CB200_OK;
+  DeviceGuard guard(s->device);
+  void* scratch = nullptr;
+  rc = cb200_scratch(s, (size_t)n * sizeof(double), &scratch);
+  if (rc) return rc;
+  double* scale = (double*)scratch;
+  if (dtype == CB200_FLOAT) {
+    lrn_forward_kernel<float, true><<<lrn_blocks(s, n), 256, 0, s->stream>>>(nullptr, scale, (const float*)in, g, n);
+    CB_LAUNCH_CHECK(s);
+    lrn_backward_kernel<float><<<lrn_blocks(s, n), 256, 0, s->stream>>>((float*)in_grad, (const float*)out, (const float*)in,
+                                                                         (const float*)out_grad, scale, g, n);
+  } else {
+    lrn_forward_kernel<double, true><<<lrn_blocks(s, n), 256, 0, s->stream>>>(nullptr, scale, (const double*)in, g, n);
+    CB_LAUNCH_CHECK(s);
+    lrn_backward_kernel<double><<<lrn_blocks(s, n), 256, 0, s->stream>>>((double*)in_grad, (const double*)out, (const double*)in,
+                                                                          (const double*)out_grad, scale, g, n);
+  }
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
+}  // extern "C"

@@ -817,6 +817,36 @@ def pooling_backward(input_gradient, input_grad_alpha, input, output, output_gra
     return input_gradient
 
 
+def lrn_descriptor(n=5, k=2, alpha=1e-4, beta=0.75):
+    """Local response normalisation across channels (tensor.clj:1553-1560)."""
+    return check_stream().lrn_descriptor(n, k, alpha, beta)
+
+
+def _lrn_checks(name, output, *others):
+    shapes = [t.shape() for t in (output,) + others]
+    _require(all(sh == shapes[0] for sh in shapes), "Input and output shapes must match", shapes)
+    _require(len(shapes[0]) >= 3, "tensor must be of at least rank 3", shapes[0])
+    _ensure_datatypes(output.get_datatype(), *others)
+    _require(output.get_datatype() in ("float", "double"), name + " is only defined for float and double tensors",
+             output.get_datatype())
+
+
+def lrn_forward(output, input, lrn_descriptor):
+    """a[i] = a[i] / (k + alpha/n * sum of a[j]^2 over the window around i)^beta   (tensor.clj:1563-1585)."""
+    _lrn_checks("lrn-forward", output, input)
+    check_stream().lrn_forward(output.buffer, output.dimensions, input.buffer, input.dimensions, lrn_descriptor)
+    return output
+
+
+def lrn_backward(input_gradient, output, input, output_gradient, lrn_descriptor):
+    """tensor.clj:1588-1617."""
+    _lrn_checks("lrn-backward", output, input, input_gradient, output_gradient)
+    check_stream().lrn_backward(input_gradient.buffer, input_gradient.dimensions, output.buffer, output.dimensions,
+                                input.buffer, input.dimensions, output_gradient.buffer, output_gradient.dimensions,
+                                lrn_descriptor)
+    return input_gradient
+
+
 def convolution_forward(output, output_alpha, input, weights, workspace, conv_descriptor, algorithms):
     """tensor.clj:1454-1466."""
     _external_library_check("convolution-forward!", output, input, weights)

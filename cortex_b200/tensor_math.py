@@ -272,6 +272,29 @@ class CTensorMath:
                  float(input_grad_alpha), input.ptr, C.byref(wire(input_dims)), output.ptr, C.byref(wire(output_dims)),
                  output_grad.ptr, C.byref(wire(output_grad_dims)), C.byref(desc))
 
+    def lrn_descriptor(self, n, k, alpha, beta):
+        """tm/lrn-descriptor (tensor/math.clj:240): the reference builds a cudnn descriptor; here a plain record."""
+        return {"n": int(n), "k": float(k), "alpha": float(alpha), "beta": float(beta)}
+
+    @staticmethod
+    def _lrn_desc(d):
+        from ._lib import LrnDesc
+        return LrnDesc(d["n"], d["k"], d["alpha"], d["beta"])
+
+    def lrn_forward(self, output, output_dims, input, input_dims, lrn_descriptor):
+        """tm/lrn-forward! (tensor/math.clj:242-245)."""
+        desc = self._lrn_desc(lrn_descriptor)
+        self._tm("lrn_forward", DTYPE_CODE[output.dtype], output.ptr, C.byref(wire(output_dims)), input.ptr,
+                 C.byref(wire(input_dims)), C.byref(desc))
+
+    def lrn_backward(self, input_gradient, input_grad_dims, output, output_dims, input, input_dims, output_gradient,
+                     output_grad_dims, lrn_descriptor):
+        """tm/lrn-backward! (tensor/math.clj:247-252)."""
+        desc = self._lrn_desc(lrn_descriptor)
+        self._tm("lrn_backward", DTYPE_CODE[output.dtype], input_gradient.ptr, C.byref(wire(input_grad_dims)),
+                 output.ptr, C.byref(wire(output_dims)), input.ptr, C.byref(wire(input_dims)), output_gradient.ptr,
+                 C.byref(wire(output_grad_dims)), C.byref(desc))
+
     def rand(self, dest, dest_dims, distribution, seed=0, sequence=0):
         """tm/rand! (tensor/math.clj:237) + the (seed, sequence) pair of the counter-based generator."""
         from ._lib import DISTRIBUTIONS

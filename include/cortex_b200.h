@@ -363,8 +363,21 @@ enum cb200_distribution { CB200_RAND_FLAT = 0, CB200_RAND_GAUSSIAN = 1 };
 int cb200_rand(cb200_stream* s, void* dest, const cb200_dims* dest_dims, int distribution, double p0, double p1,
                uint64_t seed, uint64_t sequence);
 
-/* Protocol methods this backend does not implement return CB200_ERR_UNSUPPORTED through this call:
- * lrn-forward! / lrn-backward! (src/cortex/tensor/math.clj:239-250). */
+/* lrn-forward! / lrn-backward! (src/cortex/tensor/math.clj:240-252; cudnnLRNCrossChannelForward / Backward at
+ * src/cortex/compute/cuda/tensor_math.clj:1277-1335; descriptor defaults src/cortex/tensor.clj:1553-1560).
+ * Dense tensors [.., channels, height, width] of rank 3 to 5, all of one shape.  With
+ * W(c) = [c - (n-1)/2, c + n - 1 - (n-1)/2] (integer division, clipped) and s(c) = k + (alpha/n) * sum_{W(c)} x^2:
+ *   forward:  y = x * s^-beta;   backward:  dx = dy * s^-beta - (2*alpha*beta/n) * x * sum_{j in W(c)} dy_j*y_j/s(j).
+ * The backward call uses 8 bytes of stream scratch per element. */
+typedef struct cb200_lrn_desc { int32_t n; double k, alpha, beta; } cb200_lrn_desc;
+int cb200_lrn_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, const void* in,
+                      const cb200_dims* in_dims, const cb200_lrn_desc* desc);
+int cb200_lrn_backward(cb200_stream* s, int dtype, void* in_grad, const cb200_dims* in_grad_dims, const void* out,
+                       const cb200_dims* out_dims, const void* in, const cb200_dims* in_dims, const void* out_grad,
+                       const cb200_dims* out_grad_dims, const cb200_lrn_desc* desc);
+
+/* Every method of the protocol (src/cortex/tensor/math.clj) has an entry point above.  This call reports a method
+ * name as CB200_ERR_UNSUPPORTED; bindings use it for calls outside the protocol. */
 int cb200_unsupported(const char* method_name);
 
 /* ---- fused extras (no counterpart in the protocol) -------------------------

@@ -45,6 +45,7 @@ _SIGS = {
     "orc_batch_normalize": [_i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
     "orc_pooling_forward": [_i, _vp, _vp] + [_i64] * 11 + [_i],
     "orc_pooling_backward": [_i, _vp, _vp, _vp, _vp] + [_i64] * 11 + [_i],
+    "orc_lrn": [_i, _i, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _d, _d, _d],
     "orc_batch_normalize_update": [_i, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64, _i64],
     "orc_batch_normalize_gradients": [_i] + [_vp] * 8 + [_d, _i64, _i64, _i64],
     "orc_gemv": [_i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],
@@ -191,6 +192,27 @@ class OracleStream(CTensorMath):
         _call("pooling_backward", DTYPE_CODE[output.dtype], input_grad.ptr, input.ptr, output.ptr, output_grad.ptr,
               batch * channels, in_h, in_w, out_h, out_w, d["kernel-width"], d["kernel-height"], d["pad-x"], d["pad-y"],
               d["stride-x"], d["stride-y"], POOL_OPS[d["pool-op"]])
+
+    # -- lrn: not in the reference's CPU backend; restated from the operation its CUDA backend calls ----
+    def lrn_descriptor(self, n, k, alpha, beta):
+        return {"n": int(n), "k": float(k), "alpha": float(alpha), "beta": float(beta)}
+
+    @staticmethod
+    def _lrn_extents(dims):
+        shape = list(dims["shape"])
+        batch = 1
+        for v in shape[:-3]:
+            batch *= v
+        return batch, shape[-3], shape[-2] * shape[-1]
+
+    def lrn_forward(self, output, output_dims, input, input_dims, d):
+        _call("lrn", DTYPE_CODE[output.dtype], 0, output.ptr, None, None, input.ptr, None, *self._lrn_extents(input_dims),
+              d["n"], d["k"], d["alpha"], d["beta"])
+
+    def lrn_backward(self, input_gradient, input_grad_dims, output, output_dims, input, input_dims, output_gradient,
+                     output_grad_dims, d):
+        _call("lrn", DTYPE_CODE[output.dtype], 1, None, input_gradient.ptr, output.ptr, input.ptr, output_gradient.ptr,
+              *self._lrn_extents(input_dims), d["n"], d["k"], d["alpha"], d["beta"])
 
     # -- batch-normalize training half (cpu/tensor_math.clj:1574-1640) ------------------------
     def batch_normalize_update_and_apply_eltwise(self, output, input, batch_means, batch_variances, running_means,

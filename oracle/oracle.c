@@ -532,6 +532,31 @@ int orc_batch_normalize_gradients(int dtype, void* in_grad, void* scale_grad, vo
   return 1;
 }
 
+/* ---- local response normalisation across channels ---------------------------------------------------
+ * The reference has no CPU implementation (its CUDA backend calls cudnnLRNCrossChannelForward / Backward,
+ * cuda/tensor_math.clj:1277-1335); this restates the published definition of that operation and is pinned by
+ * the reference's literals for n = 1, 2, 3 (verify/tensor.clj:1068-1136):
+ *   W(c) = [c - (n-1)/2, c + n - 1 - (n-1)/2] clipped; s(c) = k + (alpha/n) * sum_{W(c)} x^2
+ *   y = x * s^-beta;  dx = dy * s^-beta - (2*alpha*beta/n) * x * sum_{j in W(c)} dy_j * y_j / s(j) */
+#define LRN_SCALE(T, xp, b, c, p, res) { int64_t c0 = (c) - lb < 0 ? 0 : (c) - lb, c1 = (c) + la > channels - 1 ? channels - 1 : (c) + la; \
+  double sum_ = 0.0; for (int64_t j = c0; j <= c1; ++j) { double v = (double)(xp)[((b) * channels + j) * plane + (p)]; sum_ += v * v; } \
+  res = k + (alpha / (double)n) * sum_; }
+#define LRN_BODY(T) { const T* xp = (const T*)in; const T* yp = (const T*)out_c; const T* dyp = (const T*)out_grad; \
+  _Pragma("omp parallel for") for (int64_t b = 0; b < batch; ++b) for (int64_t c = 0; c < channels; ++c) for (int64_t p = 0; p < plane; ++p) { \
+    int64_t i = (b * channels + c) * plane + p; double s; LRN_SCALE(T, xp, b, c, p, s) \
+    if (!backward) { ((T*)out)[i] = (T)((double)xp[i] * pow(s, -beta)); continue; } \
+    int64_t c0 = c - lb < 0 ? 0 : c - lb, c1 = c + la > channels - 1 ? channels - 1 : c + la; double acc = 0.0; \
+    for (int64_t j = c0; j <= c1; ++j) { int64_t o = (b * channels + j) * plane + p; double sj; LRN_SCALE(T, xp, b, j, p, sj) \
+      acc += (double)dyp[o] * (double)yp[o] / sj; } \
+    ((T*)in_grad)[i] = (T)((double)dyp[i] * pow(s, -beta) - 2.0 * (alpha / (double)n) * beta * (double)xp[i] * acc); } return 0; }
+int orc_lrn(int dtype, int backward, void* out, void* in_grad, const void* out_c, const void* in, const void* out_grad,
+            int64_t batch, int64_t channels, int64_t plane, int64_t n, double k, double alpha, double beta) {
+  int64_t lb = (n - 1) / 2, la = n - lb - 1;
+  if (dtype == T_FLOAT) LRN_BODY(float)
+  if (dtype == T_DOUBLE) LRN_BODY(double)
+  return 1;
+}
+
 /* ---- ternary select (cpu/tensor_math.clj:465-566) ------------------------------------------------
  * select-impl picks z when alpha*x >= 0, else y.  Tensor operands are multiplied by their factor (cast to
  * the element type) in the accumulator type (double / wrapping long).  A NULL pointer marks a constant

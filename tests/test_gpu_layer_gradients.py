@@ -149,3 +149,27 @@ def test_batch_normalize_update_normalises(b200_driver, datatype):
     o = np.asarray(out, np.float64).reshape(shape)
     assert np.abs(o.mean(axis=(0, 2))).max() <= 10 * tol
     assert np.abs(o.var(axis=(0, 2)) - 1.0).max() <= 1e-3
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
+@pytest.mark.parametrize("shape,n", [([2, 3, 2, 2], 1), ([2, 3, 2, 2], 2), ([2, 7, 5, 3], 5), ([3, 16, 9, 9], 4),
+                                     ([5, 6, 7], 3), ([2, 2, 4, 3, 3], 9), ([1, 96, 27, 27], 5)],
+                         ids=lambda v: "x".join(map(str, v)) if isinstance(v, list) else "n%d" % v)
+def test_lrn_matches_oracle(b200_driver, oracle_driver, datatype, shape, n):
+    """lrn-forward! / lrn-backward!: both sides evaluate in double and round once; compared at the backend's
+    bounds (the power function differs in the last bits between the two maths libraries)."""
+    rng = np.random.default_rng(3 + n)
+    X = rng.standard_normal(shape).astype(NP[datatype])
+    DY = rng.standard_normal(shape).astype(NP[datatype])
+
+    def run():
+        inp, dy = ct.to_tensor(X, datatype), ct.to_tensor(DY, datatype)
+        out, dx = ct.new_tensor(shape, datatype), ct.new_tensor(shape, datatype)
+        desc = ct.lrn_descriptor(n=n, k=2, alpha=0.3, beta=0.75)
+        ct.lrn_forward(out, inp, desc)
+        ct.lrn_backward(dx, out, inp, dy, desc)
+        return ct.to_array(out), ct.to_array(dx)
+
+    (g_out, g_dx), (c_out, c_dx) = _run(b200_driver, datatype, run), _run(oracle_driver, datatype, run)
+    assert _rel(g_out, c_out) <= TOL[datatype]
+    assert _rel(g_dx, c_dx) <= TOL[datatype]

@@ -413,6 +413,44 @@ def pooling_operator(driver, datatype):
         _eq(exc_plane * (batch * channels), grads["avg-exc-pad"], 1e-4)
 
 
+def _lrn_forward_backward(num_input_channels, lrn_n):
+    """verify/tensor.clj:1068-1085"""
+    batch_size, input_dim = 2, 2
+    n_input = num_input_channels * input_dim * input_dim
+    shape = [batch_size, num_input_channels, input_dim, input_dim]
+    inp = ct.in_place_reshape(ct.to_tensor(list(range(n_input)) * batch_size), shape)
+    out_grad = ct.in_place_reshape(ct.to_tensor([1.0] * (batch_size * n_input)), shape)
+    out, in_grad = ct.new_tensor(shape), ct.new_tensor(shape)
+    desc = ct.lrn_descriptor(n=lrn_n, k=1, alpha=1, beta=1)
+    ct.lrn_forward(out, inp, desc)
+    ct.lrn_backward(in_grad, out, inp, out_grad, desc)
+    return ct.to_double_array(out), ct.to_double_array(in_grad), ct.to_double_array(inp)
+
+
+def lrn_operator(driver, datatype):
+    """verify/tensor.clj:1088-1136 (the reference runs it on its CUDA backend only)"""
+    with tensor_context(driver, datatype):
+        out, in_grad, data = _lrn_forward_backward(3, 1)
+        _eq([v / (1 + v * v) for v in data], out, 1e-4)
+        _eq([1.0, 0.0, -0.12000000000000002, -0.07999999999999999, -0.0519031141868512, -0.03550295857988165,
+             -0.02556610664718773, -0.019200000000000002, -0.0149112426035503, -0.01189767995240928,
+             -0.009704930889128518, -0.008062348830959416] * 2, in_grad, 1e-4)
+        out, in_grad, _ = _lrn_forward_backward(3, 2)
+        _eq([0.0, 0.07142857142857142, 0.09523809523809523, 0.1, 0.0975609756097561, 0.09259259259259259,
+             0.08695652173913043, 0.08139534883720931, 0.24242424242424243, 0.21686746987951808, 0.19607843137254902,
+             0.17886178861788618] * 2, out, 1e-4)
+        _eq([0.1111111111111111, 0.06461185297164132, 0.03602827394347783, 0.020493960699477193,
+             -0.014512656716972328, -0.016183480513356906, -0.016136733799491102, -0.015355548198598244,
+             -0.02846648301193755, -0.022935113949774988, -0.0188389081122645, -0.015731376825963386] * 2, in_grad, 1e-4)
+        out, in_grad, _ = _lrn_forward_backward(3, 3)
+        _eq([0.0, 0.10344827586206898, 0.13953488372093023, 0.14754098360655737, 0.14457831325301207,
+             0.13636363636363638, 0.1258741258741259, 0.11538461538461539, 0.28915662650602414, 0.24770642201834867,
+             0.21582733812949642, 0.19075144508670522] * 2, out, 1e-4)
+        _eq([0.15789473684210528, 0.09383457316653729, 0.05326649810721716, 0.030864211553852466,
+             -0.005661199012919144, -0.04352114602312829, -0.04715638623434852, -0.04169062137988738,
+             -0.047466976339091305, -0.03569676147971518, -0.027076332292621106, -0.020863959610017586] * 2, in_grad, 1e-4)
+
+
 def ternary_op_select(driver, datatype):
     """verify/tensor.clj:623-645"""
     with tensor_context(driver, datatype):
@@ -813,6 +851,7 @@ CASES = [
     (binary_constant_op, ALL_DTYPES), (binary_op, ALL_DTYPES), (gemm, FLOAT_DTYPES), (gemv, FLOAT_DTYPES),
     (ternary_op_select, ALL_DTYPES), (batch_normalize, FLOAT_DTYPES), (pooling_operator, FLOAT_DTYPES),
     (batch_normalize_update_and_apply, FLOAT_DTYPES), (batch_normalize_gradients, FLOAT_DTYPES),
+    (lrn_operator, FLOAT_DTYPES),
     (activation_gradient, FLOAT_DTYPES), (linear_layer_backward, FLOAT_DTYPES), (relu_layer_backward, FLOAT_DTYPES),
     (activation_forward, FLOAT_DTYPES), (softmax, FLOAT_DTYPES), (unary_reduce, ALL_DTYPES), (transpose, ALL_DTYPES),
     (mask, INT_LONG), (select, ALL_DTYPES), (select_transpose_interaction, ALL_DTYPES),
