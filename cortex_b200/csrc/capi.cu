@@ -94,6 +94,21 @@ int cb200_tile_flags(cb200_stream* s, size_t count, int** out) {
   return CB200_OK;
 }
 
+int cb200_partials(cb200_stream* s, size_t bytes, void** out) {
+  if (bytes > s->partials_bytes) {
+    DeviceGuard g(s->device);
+    int rc = release_for_growth(s, s->partials, "the stream's partial-sum block");
+    if (rc) return rc;
+    s->partials = nullptr;
+    s->partials_bytes = 0;
+    size_t want = (bytes + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
+    CB_CUDA(cudaMalloc(&s->partials, want));
+    s->partials_bytes = want;
+  }
+  *out = s->partials;
+  return CB200_OK;
+}
+
 extern "C" {
 
 const char* cb200_last_error(void) { return g_err; }
@@ -140,6 +155,8 @@ int cb200_stream_create(int device, cb200_stream** out) {
   s->scratch_bytes = 0;
   s->tile_flags = nullptr;
   s->tile_flags_count = 0;
+  s->partials = nullptr;
+  s->partials_bytes = 0;
   s->launches.store(0);
   s->capture_start = -1;
   s->live_graphs = std::make_shared<std::atomic<int>>(0);
@@ -161,6 +178,7 @@ int cb200_stream_destroy(cb200_stream* s) {
   cudaStreamSynchronize(s->stream);
   if (s->scratch) cudaFree(s->scratch);
   if (s->tile_flags) cudaFree(s->tile_flags);
+  if (s->partials) cudaFree(s->partials);
   for (void* r : s->retired) cudaFree(r);
   cudaFree(s->status_dev);
   cudaFreeHost(s->status_host);
@@ -211,7 +229,7 @@ int cb200_stream_set_option(cb200_stream* s, int option, int64_t value) {
 
 int cb200_stream_workspace_info(cb200_stream* s, size_t* workspace_bytes, int* retired_blocks, int* live_graphs) {
   CB_REQUIRE(s, "stream_workspace_info: null stream");
-  if (workspace_bytes) *workspace_bytes = s->scratch_bytes;
+  if (workspace_bytes) *workspace_bytes = s->scratch_bytes + s->partials_bytes;
   if (retired_blocks) *retired_blocks = (int)s->retired.size();
   if (live_graphs) *live_graphs = s->live_graphs ? s->live_graphs->load() : 0;
   return CB200_OK;
@@ -225,6 +243,9 @@ int cb200_stream_status(cb200_stream* s, int* code, int* detail) {
   CB_CUDA(cudaStreamSynchronize(s->stream));
   if (code) *code = s->status_host[0];
   if (detail) *detail = s->status_host[1];
+  // a launch that gave up may have left tile flags set: later launches expect them zero
+  if (s->status_host[0] != 0 && s->tile_flags)
+    CB_CUDA(cudaMemsetAsync(s->tile_flags, 0, s->tile_flags_count * sizeof(int), s->stream));
   return CB200_OK;
 }
 

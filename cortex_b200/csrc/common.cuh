@@ -20,6 +20,8 @@ struct cb200_stream {
   size_t scratch_bytes;
   int* tile_flags;     // zero-initialised device words, one per output tile of a K-split GEMM launch
   size_t tile_flags_count;
+  void* partials;      // lazily grown block for partial accumulators of K-split tail tiles (pair GEMM kernel)
+  size_t partials_bytes;
   std::atomic<int64_t> launches;
   int64_t capture_start;   // launch counter when the running capture began; -1 when not capturing
   // Graphs captured on this stream hold the workspace / flag pointers of their launches as kernel
@@ -52,6 +54,9 @@ int cb200_cuda_fail(cudaError_t e, const char* what, const char* file, int line)
 int cb200_scratch(cb200_stream* s, size_t bytes, void** out);
 // at least `count` zeroed flag words owned by the stream (kernels that use them leave them zero)
 int cb200_tile_flags(cb200_stream* s, size_t count, int** out);
+// at least `bytes` of a second workspace block that is independent of cb200_scratch (which callers may already
+// hold operands in); contents undefined
+int cb200_partials(cb200_stream* s, size_t bytes, void** out);
 
 #define CB_CUDA(call)                                                     \
   do {                                                                    \

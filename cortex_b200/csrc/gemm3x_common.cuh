@@ -30,7 +30,8 @@ struct GemmParams {
   int drain_every;     // pre-split kernel only: k-blocks between drains of the main accumulator (0 = never)
   float* C_lo;         // pre-split kernel only: where lo_part(C) goes (same layout as C), or null
   int k_split;
-  int split_from;      // pair kernel only: tiles from this index on are computed as two 256 x 128 halves
+  int split_from;      // pair kernel only: tiles from this index on are computed as two K halves by two clusters
+  float* partials;     // pair kernel only: [tail tile][K half][rank][128][BN] partial accumulators
   int split_block;     // tiles per block of (first halves, second halves) in the grid order
   int* tile_flags;
   int* status;

@@ -332,8 +332,7 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
 // One accumulator read-out by an epilogue thread: its 128 columns of the main accumulator (and, on the last
 // read-out of a tile, of the cross-term accumulator) are added into acc[], which lives in registers (every
 // index below is a compile-time constant).
-// `col0` / `ncc`: the thread's first accumulator column and its number of 32-column chunks (4 for a 256-wide tile,
-// 2 for the 128-wide half tiles of the last round).
+// `col0` / `ncc`: the thread's first accumulator column and its number of 32-column chunks.
 __device__ __forceinline__ void read_out(uint32_t tmem_base, int q, int col0, int ncc, float (&acc)[BN / 2], bool first,
                                          bool with_cross) {
   const uint32_t lane_col = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0;
@@ -439,24 +438,25 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + 2 * BM - 1) / (2 * BM), n_tiles = tiles_m * tiles_n;
   const int n_clusters = (int)gridDim.x >> 1, cluster_id = (int)blockIdx.x >> 1;
   const int nkb = (p.K + BK - 1) / BK;
-  // Work units: tiles below p.split_from are whole 256 x 256 tiles; the tiles of the last, partial round (when
-  // they are at most half as many as the clusters) are cut into two 256 x 128 halves each, so that the round
-  // takes half a tile's time on twice as many clusters instead of a whole one on few (4096^3 on 74 clusters:
-  // 3.5 rounds instead of 4).  `width` = 256 or 128, n0 = first column of the unit.
+  // Work units: tiles below p.split_from are reduced over the whole of K by one cluster; the tiles of the last,
+  // partial round (when they are at most half as many as the clusters) are cut into two K halves each, taken by
+  // two clusters, so that the round takes half a tile's time (4096^3 on 74 clusters: 3.5 rounds instead of 4).
+  // The epilogue warp that finishes second adds the other half's partial sums (parked in p.partials) to its
+  // own and stores the tile; nobody waits for anybody.
   const int n_units = p.split_from + 2 * (n_tiles - p.split_from);
-  auto tile_origin = [&](int unit, int& m0, int& n0, int& width) {
-    int tile_id = unit, nh = 0;
-    width = BN;
+  auto tile_origin = [&](int unit, int& m0, int& n0, int& kb0, int& kb1) {
+    int tile_id = unit;
+    kb0 = 0;
+    kb1 = nkb;
     if (unit >= p.split_from) {
       tile_id = p.split_from + ((unit - p.split_from) >> 1);
-      nh = (unit - p.split_from) & 1;
-      width = BN / 2;
+      if ((unit - p.split_from) & 1) kb0 = nkb >> 1; else kb1 = nkb >> 1;
     }
     const int grp = tile_id / (tiles_m * p.group_n);
     const int rem = tile_id - grp * tiles_m * p.group_n;
     const int in_grp = min(p.group_n, tiles_n - grp * p.group_n);
     m0 = (rem / in_grp) * (2 * BM) + (int)rank * BM;       // this CTA's rows of C
-    n0 = (grp * p.group_n + rem % in_grp) * BN + nh * (BN / 2);      // the pair's columns of C
+    n0 = (grp * p.group_n + rem % in_grp) * BN;            // the pair's columns of C
   };
 
   const uint32_t smem_base = smem_u32(smem);
@@ -500,12 +500,10 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       bool ok = true;
       const bool withhold = (p.status[3] & 1) != 0;     // host-injected fault: arm nothing, load nothing
       for (int tile = cluster_id; ok && tile < n_units; tile += n_clusters) {
-        int m0, n0, width;
-        tile_origin(tile, m0, n0, width);
-        // each CTA stages half of the unit's B rows (the box is always PNH rows: a half tile's box carries 64
-        // rows it does not use)
-        const int row0 = is_a ? m0 : n0 + (int)rank * (width / 2);
-        for (int i = 0; i < nkb; ++i) {
+        int m0, n0, kb0, kb1;
+        tile_origin(tile, m0, n0, kb0, kb1);
+        const int row0 = is_a ? m0 : n0 + (int)rank * PNH;      // each CTA stages half of the tile's B rows
+        for (int i = kb0; i < kb1; ++i) {
           if (!mbar_wait_cluster(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 500 + s)) { ok = false; break; }
           const uint32_t dst = smem_base + s * P_STAGE + tile_off;
           const int k0 = i * BK;
@@ -528,7 +526,7 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
   } else if (warp == EPI_WARPS + 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (leader && lane == 0) {
-      const uint32_t idesc_full = make_idesc_tf32(2 * BM, BN, 0, 0), idesc_half = make_idesc_tf32(2 * BM, BN / 2, 0, 0);
+      const uint32_t idesc = make_idesc_tf32(2 * BM, BN, 0, 0);
       const uint64_t d_a = make_smem_desc(smem_base, 16, 8 * BK * 4, SWZ_64B);
       const uint64_t d_b = make_smem_desc(smem_base + A_TILE, 16, 8 * BK * 4, SWZ_64B);
       const uint32_t a_hiw = (uint32_t)(d_a >> 32), b_hiw = (uint32_t)(d_b >> 32);
@@ -540,12 +538,13 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
       uint32_t ph = 0, stage_off = 0, dph = 0;
       bool ok = true, pending_read_out = false;
       for (int tile = cluster_id; ok && tile < n_units; tile += n_clusters) {
-        const uint32_t idesc = tile >= p.split_from ? idesc_half : idesc_full;
+        int m0_, n0_, kb0, kb1;
+        tile_origin(tile, m0_, n0_, kb0, kb1);
         uint32_t acc_cross = 0, accumulate = 0;
         // every p.drain_every k-blocks the epilogue warps add the main accumulator into their registers and
         // it restarts from zero (tcgen05 accumulates with truncation: shorter runs, smaller bias)
         int to_drain = p.drain_every > 0 ? p.drain_every : 0x7fffffff;
-        for (int i = 0; i < nkb; ++i) {
+        for (int i = kb0; i < kb1; ++i) {
           if (to_drain == 0) {
             mma_commit_pair(bar_mid);
             mma_commit_pair(peer_mid);
@@ -597,10 +596,11 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     uint32_t mph = 0;
     bool ok = true;
     for (int tile = cluster_id; ok && tile < n_units; tile += n_clusters) {
-      int m0, n0, width;
-      tile_origin(tile, m0, n0, width);
-      const int col0 = half * (width / 2), ncc = width / 2 / 32;     // this thread's accumulator columns
-      const int n_mid = p.drain_every > 0 ? (nkb - 1) / p.drain_every : 0;
+      int m0, n0, kb0, kb1;
+      tile_origin(tile, m0, n0, kb0, kb1);
+      constexpr int ncc = BN / 2 / 32;
+      const int col0 = half * (BN / 2);                              // this thread's accumulator columns
+      const int n_mid = p.drain_every > 0 ? (kb1 - kb0 - 1) / p.drain_every : 0;
       for (int ev = 0; ev <= n_mid; ++ev) {
         ok = mbar_wait_cluster(bar_mid, mph, abort_flag, p.status, 850);
         mph ^= 1;
@@ -612,7 +612,34 @@ gemm_presplit_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(leader_drained);
       }
-      if (ok) store_row(p, m0 + q * 32 + lane, n0 + col0, ncc, acc);
+      if (!ok) break;
+      if (tile >= p.split_from) {
+        // half of K: park this warp's 32 x 128 partial sums, then see whether the other half is already there
+        const int tail = (tile - p.split_from) >> 1, kh = (tile - p.split_from) & 1;
+        const long long slot_floats = (long long)BM * BN;            // one CTA's share of one K half
+        float* mine = p.partials + ((long long)(tail * 2 + kh) * 2 + rank) * slot_floats +
+                      (long long)(q * 32 + lane) * BN + col0;
+        const float* other = p.partials + ((long long)(tail * 2 + (kh ^ 1)) * 2 + rank) * slot_floats +
+                             (long long)(q * 32 + lane) * BN + col0;
+#pragma unroll
+        for (int j = 0; j < BN / 2; j += 4)
+          __stcg(reinterpret_cast<float4*>(mine + j), make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]));
+        __threadfence();
+        __syncwarp();
+        int* flag = p.tile_flags + (tail * 2 + (int)rank) * EPI_WARPS + warp;
+        int before = 0;
+        if (lane == 0) before = atomicAdd(flag, 1);
+        before = __shfl_sync(0xffffffffu, before, 0);
+        if (before == 0) continue;                                   // first to finish: the other half stores the tile
+        __threadfence();
+#pragma unroll
+        for (int j = 0; j < BN / 2; j += 4) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(other + j));
+          acc[j] += v.x; acc[j + 1] += v.y; acc[j + 2] += v.z; acc[j + 3] += v.w;
+        }
+        if (lane == 0) *flag = 0;                                    // left zero for the next launch
+      }
+      store_row(p, m0 + q * 32 + lane, n0 + col0, ncc, acc);
     }
   }
 
@@ -756,9 +783,19 @@ int launch_presplit(cb200_stream* s, float* C, float* C_lo, long long ldc, float
   if (pair) {
     const long long pairs = ((M + 2 * BM - 1) / (2 * BM)) * (long long)tiles_n;
     const long long clusters = pairs < s->sm_count / 2 ? pairs : s->sm_count / 2;     // persistent: one pair per two SMs
-    // a last round with at most half as many tiles as clusters runs as 256 x 128 half tiles
+    // a last round with at most half as many tiles as clusters: each of its tiles is shared by two clusters,
+    // one per K half
     const long long tail = pairs % clusters;
-    p.split_from = (int)((tail > 0 && 2 * tail <= clusters && pairs > clusters) ? pairs - tail : pairs);
+    const int nkb = (K + BK - 1) / BK;
+    p.split_from = (int)pairs;
+    p.partials = nullptr;
+    if (tail > 0 && 2 * tail <= clusters && pairs > clusters && nkb >= 16) {
+      void* partials = nullptr;
+      if ((rc = cb200_partials(s, (size_t)tail * 2 * 2 * BM * BN * sizeof(float), &partials))) return rc;
+      if ((rc = cb200_tile_flags(s, (size_t)tail * 2 * EPI_WARPS, &p.tile_flags))) return rc;
+      p.partials = (float*)partials;
+      p.split_from = (int)(pairs - tail);
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
     cfg.blockDim = dim3(P_THREADS, 1, 1);

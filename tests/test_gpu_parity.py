@@ -67,6 +67,18 @@ def test_gemm_through_presplit_pair_path(b200_driver, oracle_driver, ta, tb, sha
         assert pc.rel_err(gpu, ref64()) <= pc.TOL["float"], (alpha, beta)
 
 
+@pytest.mark.parametrize("ta,tb", [(False, True), (True, False)], ids=["NT", "TN"])
+def test_gemm_pair_path_shared_tail_tiles(b200_driver, ta, tb):
+    """84 pair tiles on 74 clusters: the 10 tiles of the last round are each reduced by two clusters (one per
+    K half) and combined by whichever finishes second; with beta != 0 and twice in a row (the flags that
+    order the two halves must be left clear)."""
+    m, n, k = 3072, 1792, 320
+    run, ref64 = pc.gemm_case("float", m, n, k, ta, tb, 1.5, 0.5, 0, 0)
+    for _ in range(2):
+        gpu = _on(b200_driver, "float", run, {"gemm-auto-presplit": 2})
+        assert pc.rel_err(gpu, ref64()) <= pc.TOL["float"]
+
+
 def test_gemm_beta_zero_ignores_nan_in_c(b200_driver):
     """BLAS semantics: with beta = 0, C is overwritten without being read."""
     rng = np.random.default_rng(5)
@@ -423,8 +435,9 @@ def test_mnist_convnet_matches_oracle(b200_driver, oracle_driver, datatype):
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(300, 384, 256), (130, 1000, 500), (128, 256, 16), (513, 260, 4112), (1024, 4096, 4096),
                                    (1300, 520, 48),
-                                   # 84 / 91 pair tiles on 74 clusters: the last round runs as 256 x 128 half tiles
-                                   (3072, 1792, 64), (3300, 1700, 48)])
+                                   # 84 / 91 / 80 pair tiles on 74 clusters: each tile of the last round is reduced
+                                   # by two clusters, one per K half (the third also drains mid-tile in both halves)
+                                   (3072, 1792, 320), (3300, 1700, 272), (2560, 2048, 4160)])
 @pytest.mark.parametrize("act", [None, "relu"])
 @pytest.mark.parametrize("variant", [1, 2])
 def test_presplit_layer_gemm(b200_driver, M, N, K, act, variant):
