@@ -756,6 +756,12 @@ def with_clocks(local_rank, fn):
 def run_b200(args, rank, world, local_rank):
     import torch  # plumbing only: rendezvous, barrier, max-over-ranks (and the measurement-only library peaks)
     dist = None
+    # Ranks are spread evenly over the GPUs this process can see (stride = visible / world): on an 8-GPU board
+    # consecutive GPUs share a PCIe switch / host bridge, and the host-fed path is bound by those links (measured:
+    # four ranks on GPUs 0-3 upload at 26 GB/s each, two at 54 GB/s each).  With exactly `world` GPUs visible this
+    # is the identity.
+    visible = torch.cuda.device_count()
+    local_rank = local_rank * max(1, visible // world) if 1 < world <= visible else local_rank
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
@@ -883,16 +889,18 @@ def run_b200(args, rank, world, local_rank):
         # parity of what came back through the pipeline: sampled rows of this rank's shard against float64
         want = fp64_forward(x_host.as_numpy().reshape(rows, WIDTH)[parity_rows], weights)
         parity_err = rel_err(probs[parity_rows], want)
-        same_bits = bool(np.array_equal(probs[parity_rows], resident_sample))
+        # host-fed chunks and the resident shard differ in row count, so the GEMM may share the K range of some
+        # tiles differently (same products, another summation order): compared at rounding level, not bit for bit
+        e2e_vs_resident = rel_err(probs[parity_rows], resident_sample.astype(np.float64))
         column_head = bench_column_head(dev, stream, world, rank, dt, dist) if world > 1 else None
 
     # max over ranks
     rank_stats = [pstats.get("h2d", {}).get("gbs") or 0.0, pstats.get("d2h", {}).get("gbs") or 0.0,
                   pstats.get("compute", {}).get("ms_per_chunk") or 0.0, pstats.get("compute", {}).get("ms") or 0.0]
     if dist is not None:
-        t = torch.tensor([ms_step, e2e_ms, parity_err, 0.0 if same_bits else 1.0], device="cuda", dtype=torch.float64)
+        t = torch.tensor([ms_step, e2e_ms, parity_err, e2e_vs_resident], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step, e2e_ms, parity_err, same_bits = float(t[0]), float(t[1]), float(t[2]), float(t[3]) == 0.0
+        ms_step, e2e_ms, parity_err, e2e_vs_resident = float(t[0]), float(t[1]), float(t[2]), float(t[3])
         lt = torch.tensor([launches], device="cuda", dtype=torch.int64)
         dist.all_reduce(lt, op=dist.ReduceOp.SUM)
         launches = int(lt[0])
@@ -940,6 +948,7 @@ def run_b200(args, rank, world, local_rank):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32" if dt == "float" else "f64", "data": "synthetic",
         "config": config, "rows_per_gpu": rows, "row_block": row_block, "kernel_path": kernel_path,
+        "gpu_indices": [r * max(1, visible // world) if 1 < world <= visible else r for r in range(world)],
         "tflops": value * FLOPS_PER_SAMPLE / 1e12,
         "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                 "ms_per_step": e2e_ms, "chunk_rows": chunk, "input_slots": pipe.slots,
@@ -956,7 +965,7 @@ def run_b200(args, rank, world, local_rank):
                      "traffic": traffic, "traffic_note": traffic_note, "algorithmic_bytes": gemm_bytes, "ms_per_launch": gemm_ms,
                      "peak_note": peak_note, "frac_of_burst": achieved / (roofs["tf32x3_burst"] if dt == "float" else roofs["fp64_burst"])},
         "parity": {"batch_sharded_rel_err_vs_fp64": parity_err, "tolerance": 1e-4 if dt == "float" else 1e-12,
-                   "e2e_rows_bit_equal_to_resident": same_bits,
+                   "e2e_rows_vs_resident_rel_err": e2e_vs_resident,
                    "sample": "16 random rows of every rank's shard, as returned through the host pipeline, against a "
                              "float64 numpy forward; abs(got-ref)/max(abs(ref), rms(ref)), max over ranks"},
         "clocks": clocks,

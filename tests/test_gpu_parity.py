@@ -485,3 +485,42 @@ def test_presplit_mlp_matches_oracle(b200_driver, oracle_driver):
     cpu = _on(oracle_driver, "float", run_cpu).reshape(300, 1000)
     assert pc.rel_err(gpu, cpu) <= pc.TOL["float"]
     assert pc.rel_err(gpu, ref()) <= pc.TOL["float"]
+
+
+@pytest.mark.parametrize("ta,tb", [(False, True), (True, False)], ids=["NT", "TN"])
+def test_tensor_core_reads_fp32_words_truncated(b200_driver, ta, tb):
+    """The fact the hi / lo split rests on: fed an fp32 word as tf32, the tensor core drops the low 13 mantissa
+    bits (truncation, not rounding).  One-term run (no split) of the tcgen05 kernel against float64 products of
+    (a) truncated and (b) round-to-nearest-tf32 inputs: it must agree with (a) to accumulation error and be far
+    from (b); and hi + lo must rebuild every input exactly, so the three-term product loses nothing."""
+    from cortex_b200._lib import call
+    m, n, k = 256, 256, 512
+    rng = np.random.default_rng(11)
+    a_shape, b_shape = ((k, m) if ta else (m, k)), ((n, k) if tb else (k, n))
+    A = rng.standard_normal(a_shape).astype(np.float32)
+    B = rng.standard_normal(b_shape).astype(np.float32)
+    stream = b200_driver.default_device().create_stream()
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        a, b, c = ct.to_tensor(A), ct.to_tensor(B), ct.new_tensor([m, n])
+        # extents are those of op(A) (m x k) and op(B) (.. x n); pitches those of the stored matrices
+        call("cb200_gemm_f32_variant", stream.handle, 1, 1, c.buffer.ptr, n, int(ta), int(tb), 1.0, a.buffer.ptr,
+             m, k, a_shape[1], b.buffer.ptr, n, b_shape[1], 0.0)
+        got = ct.to_array(c).reshape(m, n).astype(np.float64)
+    stream.sync()
+
+    def trunc(x):
+        return (x.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32)
+
+    def rna(x):   # round to nearest, ties away: add half an ulp of the 10-bit mantissa, then truncate
+        return ((x.view(np.uint32) + np.uint32(0x1000)) & np.uint32(0xffffe000)).view(np.float32)
+
+    def product(f):
+        a64, b64 = f(A).astype(np.float64), f(B).astype(np.float64)
+        return (a64.T if ta else a64) @ (b64.T if tb else b64)
+
+    err_trunc, err_rna = pc.rel_err(got, product(trunc)), pc.rel_err(got, product(rna))
+    assert err_trunc <= 2e-5, err_trunc
+    assert err_rna >= 20 * err_trunc, (err_trunc, err_rna)
+    for x in (A, B):
+        hi = trunc(x)
+        assert np.array_equal(hi.astype(np.float64) + (x - hi).astype(np.float64), x.astype(np.float64))
