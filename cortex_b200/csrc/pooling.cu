@@ -203,31 +203,55 @@ pooling_forward_vec_kernel(float* out, const float* in, PoolGeom g, int planes, 
     const int seg_x = ox0 * SX;                         // first column of the aligned segment (multiple of 4)
     float* dst = out + ((long long)plane_u * g.out_h + oy) * g.out_w + ox0;
     float res[NX];
-    if (OP == CB200_POOL_MAX && rel_y >= 0 && rel_y + KH <= g.in_h && rel_x >= 0 && rel_x + W_IN <= g.in_w &&
-        seg_x + SEG <= g.in_w) {
-      // every window of this thread lies inside the image: no tests, the fold is compare + select
+    if (rel_y + KH <= g.in_h + g.pad_y && rel_x + W_IN <= g.in_w + g.pad_x && seg_x + SEG <= g.in_w) {
+      // Every window position of this thread is inside the image or in the padding band (which reads 0 and takes
+      // part like any other value): no per-position tests.  Only the halo columns left / right of the aligned
+      // segment and whole rows can be padding.  This is the path of every thread unless a ceil-mode window
+      // reaches past the band, so warps do not diverge into the general code below.
       float v[KH][W_IN];
+      int n_rows = 0;
 #pragma unroll
       for (int ky = 0; ky < KH; ++ky) {
-        const float* row = src + (rel_y + ky) * g.in_w;
+        const int iy = rel_y + ky;
+        const bool row_in = (unsigned)iy < (unsigned)g.in_h;
+        n_rows += row_in ? 1 : 0;
+        const float* row = src + iy * g.in_w;
         float seg[SEG];
 #pragma unroll
         for (int q = 0; q < SEG / 4; ++q) {
-          const float4 t = *reinterpret_cast<const float4*>(row + seg_x + 4 * q);
+          float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (row_in) t = *reinterpret_cast<const float4*>(row + seg_x + 4 * q);
           seg[4 * q] = t.x; seg[4 * q + 1] = t.y; seg[4 * q + 2] = t.z; seg[4 * q + 3] = t.w;
         }
 #pragma unroll
-        for (int c = 0; c < W_IN; ++c) v[ky][c] = (c >= PX && c < PX + SEG) ? seg[c - PX] : row[rel_x + c];
+        for (int c = 0; c < W_IN; ++c) {
+          if (c >= PX && c < PX + SEG) v[ky][c] = seg[c - PX];
+          else v[ky][c] = (row_in && (unsigned)(rel_x + c) < (unsigned)g.in_w) ? row[rel_x + c] : 0.f;
+        }
       }
 #pragma unroll
       for (int o = 0; o < NX; ++o) {
-        float acc = v[0][o * SX];
+        if (OP == CB200_POOL_MAX) {
+          float acc = v[0][o * SX];
 #pragma unroll
-        for (int ky = 0; ky < KH; ++ky)
+          for (int ky = 0; ky < KH; ++ky)
 #pragma unroll
-          for (int kx = 0; kx < KW; ++kx)
-            if (ky + kx > 0) { const float x = v[ky][o * SX + kx]; acc = x > acc ? x : acc; }
-        res[o] = acc;
+            for (int kx = 0; kx < KW; ++kx)
+              if (ky + kx > 0) { const float x = v[ky][o * SX + kx]; acc = x > acc ? x : acc; }
+          res[o] = acc;
+        } else {
+          int n_cols = 0;
+#pragma unroll
+          for (int kx = 0; kx < KW; ++kx) n_cols += (unsigned)(rel_x + o * SX + kx) < (unsigned)g.in_w ? 1 : 0;
+          const double divisor = OP == CB200_POOL_AVG ? (double)(KW * KH) : (double)(n_rows * n_cols);
+          float acc = 0.f;
+          // padding positions add 0 / divisor: the identity, as in the reference's position-by-position sum
+#pragma unroll
+          for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+            for (int kx = 0; kx < KW; ++kx) acc = (float)((double)acc + (double)v[ky][o * SX + kx] / divisor);
+          res[o] = acc;
+        }
       }
     } else {
       bool row_ok[KH], col_ok[W_IN];
