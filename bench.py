@@ -435,6 +435,31 @@ def bench_eltwise(drv, dev, peaks):
         cases["pooling_max_3x3s2"] = (lambda i: stream.pooling_forward(pool_out[i].buffer, pool_out[i].dimensions, 0.0,
                                                                        pool_in[i].buffer, pool_in[i].dimensions, pool_desc),
                                       rows * cols * 4 + rows * cols)
+        # pooling-backward! of that layer (reads input, output, output gradient; writes the input gradient)
+        pool_og = [ct.to_tensor(rng.standard_normal((128, 64, 32, 32), dtype=np.float32)) for _ in range(2)]
+        for i in range(sets):
+            stream.pooling_forward(pool_out[i].buffer, pool_out[i].dimensions, 0.0, pool_in[i].buffer, pool_in[i].dimensions,
+                                   pool_desc)
+        pool_ig = [ct.in_place_reshape(y, [128, 64, 64, 64]) for y in ys]
+        cases["pooling_backward_max_3x3s2"] = (lambda i: ct.pooling_backward(pool_ig[i], 0.0, pool_in[i], pool_out[i],
+                                                                              pool_og[i % 2], pool_desc),
+                                               2 * rows * cols * 4 + 2 * rows * cols)
+        # batch-normalize training half, spatial form [128, 64, 4096]: statistics + apply (input read three times,
+        # output written once) and the gradients (input and output gradient read twice, input gradient written)
+        bn_batch = [ct.new_tensor([64]) for _ in range(2)]
+        bn_run = [ct.to_tensor(np.ones(64, np.float32)) for _ in range(2)]
+        bn_grads = [ct.new_tensor([64]) for _ in range(2)]
+        cases["batch_normalize_update_and_apply_spatial"] = (
+            lambda i: ct.batch_normalize_update_and_apply(bn_out[i], bn_in[i], bn_batch[0], bn_batch[1], bn_run[0], bn_run[1],
+                                                          0.1, bn_stats[2], bn_stats[3], 1e-3), 2 * rows * cols * 4)
+        bn_og = [ct.in_place_reshape(g_, [128, 64, 4096]) for g_ in grads]
+        cases["batch_normalize_gradients_spatial"] = (
+            lambda i: ct.batch_normalize_gradients(bn_out[i], bn_grads[0], bn_grads[1], bn_og[i], bn_out[i], bn_in[i],
+                                                   bn_batch[0], bn_batch[1], bn_stats[2], bn_stats[3], 1e-3),
+            3 * rows * cols * 4)
+        # lrn across channels, n = 5, on [128, 64, 64, 64]
+        lrn_desc = ct.lrn_descriptor(n=5, k=2, alpha=1e-4, beta=0.75)
+        cases["lrn_forward_n5"] = (lambda i: ct.lrn_forward(pool_ig[i], pool_in[i], lrn_desc), 2 * rows * cols * 4)
         # optimiser steps over a flat 64 Mi-parameter buffer (two buffer sets of 4 x 256 MiB: far beyond L2) and rand!
         n_par = 64 << 20
         from cortex_b200 import optimize

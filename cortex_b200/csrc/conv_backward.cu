@@ -330,12 +330,10 @@ int cb200_convolution_backward_data(cb200_stream* s, int dtype, void* in_grad, c
   if (dtype == CB200_FLOAT && rows > 0 && cout > 0 && g.stride_x == 1 && g.stride_y == 1 && g.pad_x <= g.kw - 1 &&
       g.pad_y <= g.kh - 1 &&
       cb200_conv_forward_f32_uses_tma(s, g.batch, cout, g.out_h, g.out_w, g.cin, g.in_h, g.in_w, g.kh, g.kw, 1, 1)) {
-    // the forward launch takes 2 * its input + its re-laid weights (hi and lo, rows padded to whole channel tiles:
-    // its C_out is this layer's C_in) from the head of the stream's workspace: the mirrored filter goes behind that
+    // the forward launch takes (2 * its input + 2 * its weights) floats from the head of the stream's workspace:
+    // the mirrored filter goes behind that
     const size_t og_elems = (size_t)rows * cout, w_elems = (size_t)cout * g.kcols;
-    const int fwd_bn = g.cin > 64 ? 128 : 64;
-    const size_t fwd_w = (size_t)((g.cin + fwd_bn - 1) / fwd_bn) * 2 * fwd_bn * ((size_t)cout * g.kh * g.kw);
-    const size_t head = ((2 * og_elems + (fwd_w > 2 * w_elems ? fwd_w : 2 * w_elems)) * sizeof(float) + 255) & ~(size_t)255;
+    const size_t head = (2 * og_elems + 2 * w_elems) * sizeof(float);
     void* ws = nullptr;
     if ((rc = cb200_scratch(s, head + w_elems * sizeof(float), &ws))) return rc;
     float* wt = (float*)((char*)ws + head);

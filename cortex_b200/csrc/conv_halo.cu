@@ -21,9 +21,7 @@
 //
 // A pre-pass writes the NCHW input as [N][C/4][H][W][4] hi / lo copies (hi = x, lo = x - trunc_tf32(x); one
 // HBM-bound pass), which a 5-d TMA box {4, patch_w, patch_h, 4 channel quads, 1} fetches with out-of-bounds
-// zero fill as the padding.  The weights are permuted to that k order and stored as stacked [W_hi ; W_lo] row
-// blocks per C_out tile, so that one 3-d TMA box brings the B operand of a whole filter row of taps (a W stage:
-// one load, one wait, one commit per kW k-blocks).  Per 3x3 tile the A traffic
+// zero fill as the padding.  The weights are permuted / split as for conv_tma.cu.  Per 3x3 tile the A traffic
 // drops from 9 x 16 KiB to 23 KiB per channel block.  Persistent CTAs, two accumulator buffers in TMEM, warp
 // roles and bounded waits as in conv_tma.cu.
 #include "common.cuh"
@@ -36,6 +34,8 @@ namespace {
 
 constexpr int HBX = 8, HBY = 16;    // output pixels per tile: 8 wide, 16 high = 128 rows
 constexpr int HBK = 16;             // k values per k-block (one tap x 16 channels)
+constexpr int H_EPI_WARPS = 8;
+constexpr int H_THREADS = (H_EPI_WARPS + 4) * 32;
 
 struct HaloParams {
   float* out;
@@ -46,7 +46,6 @@ struct HaloParams {
   int patch_w, patch_h;       // HBX + kw - 1, HBY + kh - 1
   int patch_bytes;            // 4 planes x patch_h x patch_w x 16, rounded up to 128
   int n_patches, w_stages;    // ring depths
-  int taps_per_stage;         // filter taps (k-blocks) one W stage holds; divides kh * kw
   int* status;
 };
 
@@ -65,14 +64,6 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* tmap, int 
       : "memory");
 }
 
-// 3-d tiled load {k within block, row, k-block}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int c0, int c1, int c2, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
-      "l"((uint64_t)tmap), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-      : "memory");
-}
-
 // in [N][C][HW]  ->  hi / lo [N][C/4][HW][4]: thread = (image, channel quad, pixel); reads of a warp are 128
 // contiguous bytes per channel, its writes 512 contiguous bytes
 __global__ void __launch_bounds__(256)
@@ -88,36 +79,30 @@ nchw_to_c4_split_kernel(const float* __restrict__ in, float4* __restrict__ hi, f
   }
 }
 
-// W[cout][c*khkw + t]  ->  stacked [C_out tile][2 BN rows][((c/16)*khkw + t)*16 + c%16]: rows 0 .. BN-1 of a tile are
-// its channels' values (hi), rows BN .. 2BN-1 their lo parts; channels past C_out are zero rows.  One TMA box then
-// brings [W_hi ; W_lo] of a k-block -- the B operand of the stacked MMA -- with one instruction.
+// W[cout][c*khkw + t]  ->  hi / lo [cout][((c/16)*khkw + t)*16 + c%16]
 __global__ void __launch_bounds__(256)
-hconv_prep_weights_kernel(const float* __restrict__ w, float* __restrict__ st, int cout, int cin, int khkw, int BN,
-                          int tiles_n) {
+hconv_prep_weights_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int cout, int cin,
+                          int khkw) {
   const int K = cin * khkw;
-  const long long total = (long long)tiles_n * BN * K;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int row = (int)(i / K), kp = (int)(i - (long long)row * K);      // row = tile * BN + channel within tile
-    const int tile = row / BN, r = row - tile * BN;
+  const int total = cout * K;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int co = i / K, kp = i - co * K;
     const int blk = kp >> 4, c16 = kp & 15;
     const int cb = blk / khkw, t = blk - cb * khkw;
-    const float x = row < cout ? w[(long long)row * K + (cb * 16 + c16) * khkw + t] : 0.f;
-    float* dst = st + ((long long)tile * 2 * BN + r) * K + kp;
-    dst[0] = x;
-    dst[(long long)BN * K] = hconv_lo_part(x);
+    const float x = w[(long long)co * K + (cb * 16 + c16) * khkw + t];
+    hi[i] = x;
+    lo[i] = hconv_lo_part(x);
   }
 }
 
 // Shared memory: [n_patches x (hi patch | lo patch)] [w_stages x (W_hi | W_lo)] [barriers]
-// H_EPI_WARPS: 8 (each warp reads half of a row's accumulator columns) or 4; NBUF: accumulator buffers in TMEM
-// (2: the next tile's MMAs run while this tile is read out); CTAS: resident CTAs per SM the launch is sized for.
-template <int BN, int H_EPI_WARPS, int NBUF, int CTAS>
-__global__ void __launch_bounds__((H_EPI_WARPS + 4) * 32, CTAS)
+template <int BN>
+__global__ void __launch_bounds__(H_THREADS, (BN <= 64 ? 2 : 1))
 conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlo,
-                 const __grid_constant__ CUtensorMap tmW, HaloParams p) {
-  constexpr int W_TILE = 2 * BN * HBK * 4;            // [W_hi ; W_lo] of one k-block
+                 const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmWlo, HaloParams p) {
+  constexpr int B_TILE = BN * HBK * 4;
+  constexpr int W_STAGE = 2 * B_TILE;
   constexpr int MAX_RING = 8;
-  const uint32_t W_STAGE = (uint32_t)p.taps_per_stage * W_TILE;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t patch_pair = 2u * (uint32_t)p.patch_bytes;
@@ -147,7 +132,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(bar_wfull + 8 * s, 1);
       mbar_init(bar_wempty + 8 * s, 1);
     }
-    for (int b = 0; b < NBUF; ++b) {
+    for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, H_EPI_WARPS);
     }
@@ -156,13 +141,13 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     mbar_fence_init();
   }
   if (warp == H_EPI_WARPS + 1) {
-    tmem_alloc(smem_u32(tmem_slot), NBUF * 2 * BN);
+    tmem_alloc(smem_u32(tmem_slot), 4 * BN);
     tmem_relinquish();
   }
   if (lane == 0) {
     if (warp == H_EPI_WARPS) tma_prefetch_desc(&tmA);
     if (warp == H_EPI_WARPS + 2) tma_prefetch_desc(&tmAlo);
-    if (warp == H_EPI_WARPS + 3) tma_prefetch_desc(&tmW);
+    if (warp == H_EPI_WARPS + 3) { tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmWlo); }
   }
   tc_fence_before();
   __syncthreads();
@@ -201,20 +186,22 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (mbar_try_wait(bar_pfull + 8 * (int)(i % p.n_patches), (uint32_t)((i / p.n_patches) & 1))) break;
     }
   } else if (warp == H_EPI_WARPS + 3) {
-    // ---------------- W producer: one box per stage = [W_hi ; W_lo] of taps_per_stage k-blocks ----------------
+    // ---------------- W producer: hi and lo tiles, one pair per (channel block, tap) ----------------
     long long issued = 0;
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    const int n_stages = p.ncb * khkw / p.taps_per_stage;
+    const int nkb = p.ncb * khkw;
     for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-      const int row0 = (tile % tiles_n) * 2 * BN;
-      for (int i = 0; i < n_stages; ++i) {
+      const int n0 = (tile % tiles_n) * BN;
+      for (int i = 0; i < nkb; ++i) {
         if (!mbar_wait(bar_wempty + 8 * s, ph ^ 1, abort_flag, p.status, 1500 + s)) { ok = false; break; }
         const uint32_t full = bar_wfull + 8 * s;
+        const uint32_t dst = smem_base + w_base_off + s * W_STAGE;
         if (elect_one()) {
           mbar_arrive_expect_tx(full, W_STAGE);
-          tma_load_3d(smem_base + w_base_off + s * W_STAGE, &tmW, 0, row0, i * p.taps_per_stage, full);
+          tma_load_2d(dst, &tmW, i * HBK, n0, full);
+          tma_load_2d(dst + B_TILE, &tmWlo, i * HBK, n0, full);
         }
         __syncwarp();
         ++issued;
@@ -244,37 +231,34 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool ok = true;
     int local = 0;
     for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++local) {
-      const int buf = local % NBUF;
-      if (!mbar_wait(bar_acc_empty + 8 * buf, ((local / NBUF) & 1) ^ 1, abort_flag, p.status, 1650)) { ok = false; break; }
+      const int buf = local & 1;
+      if (!mbar_wait(bar_acc_empty + 8 * buf, ((local >> 1) & 1) ^ 1, abort_flag, p.status, 1650)) { ok = false; break; }
       tc_fence_after();
       const uint32_t tmem_main = tmem_base + buf * 2 * BN, tmem_cross = tmem_main + BN;
       uint32_t accumulate = 0;
       for (int cb = 0; ok && cb < p.ncb; ++cb) {
         if (!mbar_wait(bar_pfull + 8 * ps, pph, abort_flag, p.status, 1600 + ps)) { ok = false; break; }
         const uint32_t a_patch = a_low0 + (uint32_t)ps * pair_step;
-        for (int t0 = 0; t0 < khkw; t0 += p.taps_per_stage) {
+        int ky = 0, kx = 0;
+        for (int t = 0; t < khkw; ++t) {
           if (!mbar_wait(bar_wfull + 8 * ws, wph, abort_flag, p.status, 1700 + ws)) { ok = false; break; }
           tc_fence_after();
           if (elect_one()) {
-            uint32_t b_tap = b_low0 + (uint32_t)ws * (W_STAGE >> 4);
-            int ky = t0 / p.kw, kx = t0 - ky * p.kw;
-            for (int tt = 0; tt < p.taps_per_stage; ++tt) {
-              const uint32_t a_tap = a_patch + (uint32_t)(ky * p.patch_w + kx);     // 16 bytes per pixel = 1 unit
+            const uint32_t a_tap = a_patch + (uint32_t)(ky * p.patch_w + kx);     // 16 bytes per pixel = 1 unit
+            const uint32_t b_st = b_low0 + (uint32_t)ws * (W_STAGE >> 4);
 #pragma unroll
-              for (int kk = 0; kk < HBK / 8; ++kk) {
-                const uint32_t al = a_tap + kk * a_kstep, bl = b_tap + kk * 2;
-                // A_hi x [W_hi ; W_lo] -> main | hi x lo;   A_lo x W_hi -> onto the cross columns
-                mma_tf32_ss_words(tmem_main, al, a_hiw, bl, b_hiw, idesc_wide, (kk | tt) ? 1u : accumulate);
-                mma_tf32_ss_words(tmem_cross, al + a_lo_off, a_hiw, bl, b_hiw, idesc, 1);
-              }
-              b_tap += W_TILE >> 4;
-              if (++kx == p.kw) { kx = 0; ++ky; }
+            for (int kk = 0; kk < HBK / 8; ++kk) {
+              const uint32_t al = a_tap + kk * a_kstep, bl = b_st + kk * 2;
+              // A_hi x [W_hi ; W_lo] -> main | hi x lo;   A_lo x W_hi -> onto the cross columns
+              mma_tf32_ss_words(tmem_main, al, a_hiw, bl, b_hiw, idesc_wide, kk ? 1u : accumulate);
+              mma_tf32_ss_words(tmem_cross, al + a_lo_off, a_hiw, bl, b_hiw, idesc, 1);
             }
             mma_commit(bar_wempty + 8 * ws);
-            if (t0 + p.taps_per_stage == khkw) mma_commit(bar_pempty + 8 * ps);   // the patch is free once its last tap retires
+            if (t == khkw - 1) mma_commit(bar_pempty + 8 * ps);       // the patch is free once its last tap retires
           }
           accumulate = 1;
           __syncwarp();
+          if (++kx == p.kw) { kx = 0; ++ky; }
           if (++ws == p.w_stages) { ws = 0; wph ^= 1; }
         }
         if (++ps == p.n_patches) { ps = 0; pph ^= 1; }
@@ -295,12 +279,12 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int row = q * 32 + lane;                      // tile row = TMEM lane: y line row / 8, column row % 8
     const int ly = row >> 3, lx = row & 7;
     const long long hw = (long long)p.out_h * p.out_w;
-    constexpr int COLS_PER_HALF = BN / (H_EPI_WARPS / 4);
+    constexpr int COLS_PER_HALF = BN / 2;
     bool ok = true;
     int local = 0;
     for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++local) {
-      const int buf = local % NBUF;
-      ok = mbar_wait(bar_acc_full + 8 * buf, (local / NBUF) & 1, abort_flag, p.status, 1800);
+      const int buf = local & 1;
+      ok = mbar_wait(bar_acc_full + 8 * buf, (local >> 1) & 1, abort_flag, p.status, 1800);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -344,7 +328,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   if (warp == H_EPI_WARPS + 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, NBUF * 2 * BN);
+    tmem_dealloc(tmem_base, 4 * BN);
   }
 }
 
@@ -384,16 +368,14 @@ int encode_c4(CUtensorMap* tm, const float* base, int CQ, int W, int H, int N, i
   return CB200_OK;
 }
 
-// stacked weights [rows][K] as the 3-d tensor {16, rows, K / 16}; box {16, 2 BN, taps}: taps consecutive K-major
-// 64-byte-swizzled tiles of 2 BN rows
-int encode_hw(CUtensorMap* tm, const float* w, int K, int rows, int BN, int taps) {
+int encode_hw(CUtensorMap* tm, const float* w, int K, int cout, int BN) {
   EncodeTiledFn fn = hconv_encode_fn();
   if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
-  cuuint64_t gdim[3] = {(cuuint64_t)HBK, (cuuint64_t)rows, (cuuint64_t)(K / HBK)};
-  cuuint64_t gstride[2] = {(cuuint64_t)K * 4, (cuuint64_t)HBK * 4};
-  cuuint32_t box[3] = {(cuuint32_t)HBK, (cuuint32_t)(2 * BN), (cuuint32_t)taps};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)w, gdim, gstride, box, estr,
+  cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)cout};
+  cuuint64_t gstride[1] = {(cuuint64_t)K * 4};
+  cuuint32_t box[2] = {(cuuint32_t)HBK, (cuuint32_t)BN};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)w, gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { cb200_set_error("cuTensorMapEncodeTiled failed with %d for the weights", (int)r); return CB200_ERR_CUDA; }
@@ -401,43 +383,40 @@ int encode_hw(CUtensorMap* tm, const float* w, int K, int rows, int BN, int taps
 }
 
 // ring depths that fit the per-CTA shared-memory budget; false if not even the minimum does
-bool halo_plan(int BN, int kh, int kw, int ctas_per_sm, int want_taps, int* patch_bytes, int* n_patches, int* w_stages,
-               int* taps_per_stage, int* smem_bytes) {
+bool halo_plan(int BN, int kh, int kw, int* patch_bytes, int* n_patches, int* w_stages, int* smem_bytes) {
   const int pw = HBX + kw - 1, ph = HBY + kh - 1;
   if (pw > 256 || ph > 256) return false;
   const int pb = (4 * ph * pw * 16 + 127) & ~127;
-  const int w_tile = 2 * BN * HBK * 4;
-  const int budget = (ctas_per_sm == 2 ? 112 : 224) * 1024 - 2048;
-  auto total = [&](int np, int stages, int taps) { return ((np * 2 * pb + 1023) & ~1023) + stages * taps * w_tile + 1024 + 512; };
-  // Two patch pairs are enough (a patch lasts kH*kW k-blocks).  A W stage holds `taps` k-blocks (one load, one wait
-  // and one commit per stage); the ring is as deep as fits (<= 8 stages), and a third patch pair is added only if
-  // room is left.
-  int taps = (want_taps >= 2 && want_taps <= 4 && total(2, 2, want_taps) <= budget) ? want_taps : 1;
+  const int w_stage = 2 * BN * HBK * 4;
+  const int budget = (BN <= 64 ? 112 : 224) * 1024 - 2048;      // two CTAs per SM for 64-channel tiles
+  // two patch pairs are enough (a patch lasts kH*kW k-blocks); the W ring, one stage per k-block, is what
+  // covers the load latency: as deep as fits (<= 8), and a third patch pair only if room is left
   int np = 2, ws = 8;
-  while (total(np, ws, taps) > budget && ws > 2) --ws;
-  if (total(np, ws, taps) > budget || (taps == 1 && ws < 3)) return false;
-  if (total(3, ws, taps) <= budget) np = 3;
-  *patch_bytes = pb; *n_patches = np; *w_stages = ws; *taps_per_stage = taps; *smem_bytes = total(np, ws, taps);
+  auto total = [&](int a, int b) { return ((a * 2 * pb + 1023) & ~1023) + b * w_stage + 1024 + 512; };
+  while (total(np, ws) > budget && ws > 3) --ws;
+  if (total(np, ws) > budget) return false;
+  if (total(3, ws) <= budget) np = 3;
+  *patch_bytes = pb; *n_patches = np; *w_stages = ws; *smem_bytes = total(np, ws);
   return true;
 }
 
-template <int BN, int EPI, int NBUF, int CTAS>
+template <int BN>
 int launch_halo(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmAlo, const CUtensorMap& tmW,
-                const HaloParams& p, int smem_bytes, long long tiles) {
+                const CUtensorMap& tmWlo, const HaloParams& p, int smem_bytes, long long tiles) {
   static std::mutex mu;
   static int configured[64] = {0};
-  constexpr int LIMIT = (CTAS == 2 ? 112 : 224) * 1024;
   {
     std::lock_guard<std::mutex> lock(mu);
-    if (!configured[s->device & 63]) {
-      cudaError_t e = cudaFuncSetAttribute(conv_halo_kernel<BN, EPI, NBUF, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, LIMIT);
+    if (configured[s->device & 63] < smem_bytes) {
+      cudaError_t e = cudaFuncSetAttribute(conv_halo_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (BN <= 64 ? 112 : 224) * 1024);
       if (e != cudaSuccess) return cb200_cuda_fail(e, "cudaFuncSetAttribute", __FILE__, __LINE__);
-      configured[s->device & 63] = 1;
+      configured[s->device & 63] = (BN <= 64 ? 112 : 224) * 1024;
     }
   }
-  const long long slots = (long long)s->sm_count * CTAS;
+  const long long slots = (long long)s->sm_count * (BN <= 64 ? 2 : 1);
   const long long grid = tiles < slots ? tiles : slots;
-  conv_halo_kernel<BN, EPI, NBUF, CTAS><<<(unsigned)grid, (EPI + 4) * 32, smem_bytes, s->stream>>>(tmA, tmAlo, tmW, p);
+  conv_halo_kernel<BN><<<(unsigned)grid, H_THREADS, smem_bytes, s->stream>>>(tmA, tmAlo, tmW, tmWlo, p);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
@@ -451,8 +430,8 @@ bool cb200_conv_halo_eligible(int cin, int cout, int out_w, int out_h, int kh, i
   if (stride_x != 1 || stride_y != 1 || (cin % 16) != 0 || kh * kw < 2 || in_elems >= 2147483647LL) return false;
   const double padded = (double)((out_w + HBX - 1) / HBX) * HBX * ((out_h + HBY - 1) / HBY) * HBY;
   if (padded > 1.35 * (double)out_w * out_h) return false;
-  int pb, np, ws, tp, sm;
-  return halo_plan(cout > 64 ? 128 : 64, kh, kw, cout > 64 ? 1 : 2, kw, &pb, &np, &ws, &tp, &sm);
+  int pb, np, ws, sm;
+  return halo_plan(cout > 64 ? 128 : 64, kh, kw, &pb, &np, &ws, &sm);
 }
 
 int cb200_conv_halo_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
@@ -469,37 +448,35 @@ int cb200_conv_halo_launch(cb200_stream* s, float* out, const float* in, const f
   p.patch_w = HBX + kw - 1;
   p.patch_h = HBY + kh - 1;
   int smem_bytes = 0;
-  const int ctas = BN == 128 ? 1 : 2;
-  // a W stage = one filter row of taps (measured on the 3x3 / 64-channel layer: 7 % faster than one tap per stage;
-  // three resident CTAs per SM with single-buffered accumulators: 7 % slower)
-  if (!halo_plan(BN, kh, kw, ctas, kw, &p.patch_bytes, &p.n_patches, &p.w_stages, &p.taps_per_stage, &smem_bytes)) {
+  if (!halo_plan(BN, kh, kw, &p.patch_bytes, &p.n_patches, &p.w_stages, &smem_bytes)) {
     cb200_set_error("convolution: the %dx%d filter's input patch does not fit shared memory", kw, kh);
     return CB200_ERR_INVALID;
   }
   const int K = cin * kh * kw;
-  const int tiles_n = (cout + BN - 1) / BN;
-  const size_t in_elems = (size_t)batch * cin * in_h * in_w, w_elems = (size_t)tiles_n * 2 * BN * K;
+  const size_t in_elems = (size_t)batch * cin * in_h * in_w, w_elems = (size_t)cout * K;
   void* scratch = nullptr;
-  int rc = cb200_scratch(s, (2 * in_elems + w_elems) * sizeof(float), &scratch);
+  int rc = cb200_scratch(s, (2 * in_elems + 2 * w_elems) * sizeof(float), &scratch);
   if (rc) return rc;
   float* a_hi = (float*)scratch;
   float* a_lo = a_hi + in_elems;
-  float* w_st = a_lo + in_elems;
+  float* w_hi = a_lo + in_elems;
+  float* w_lo = w_hi + w_elems;
   const int hw = in_h * in_w;
   const long long quads = (long long)batch * (cin / 4) * hw;
   long long tb = (quads + 255) / 256;
   if (tb > (long long)s->sm_count * 16) tb = (long long)s->sm_count * 16;
   nchw_to_c4_split_kernel<<<(unsigned)tb, 256, 0, s->stream>>>(in, (float4*)a_hi, (float4*)a_lo, cin / 4, hw, quads);
   CB_LAUNCH_CHECK(s);
-  long long blocks = ((long long)tiles_n * BN * K + 255) / 256;
+  int blocks = (int)((w_elems + 255) / 256);
   if (blocks > s->sm_count * 8) blocks = s->sm_count * 8;
-  hconv_prep_weights_kernel<<<(unsigned)blocks, 256, 0, s->stream>>>(w, w_st, cout, cin, kh * kw, BN, tiles_n);
+  hconv_prep_weights_kernel<<<blocks, 256, 0, s->stream>>>(w, w_hi, w_lo, cout, cin, kh * kw);
   CB_LAUNCH_CHECK(s);
-  CUtensorMap tmA, tmAlo, tmW;
+  CUtensorMap tmA, tmAlo, tmW, tmWlo;
   if ((rc = encode_c4(&tmA, a_hi, cin / 4, in_w, in_h, batch, p.patch_w, p.patch_h))) return rc;
   if ((rc = encode_c4(&tmAlo, a_lo, cin / 4, in_w, in_h, batch, p.patch_w, p.patch_h))) return rc;
-  if ((rc = encode_hw(&tmW, w_st, K, tiles_n * 2 * BN, BN, p.taps_per_stage))) return rc;
-  const long long tiles = (long long)batch * p.tiles_x * p.tiles_y * tiles_n;
-  if (BN == 128) return launch_halo<128, 8, 2, 1>(s, tmA, tmAlo, tmW, p, smem_bytes, tiles);
-  return launch_halo<64, 8, 2, 2>(s, tmA, tmAlo, tmW, p, smem_bytes, tiles);
+  if ((rc = encode_hw(&tmW, w_hi, K, cout, BN))) return rc;
+  if ((rc = encode_hw(&tmWlo, w_lo, K, cout, BN))) return rc;
+  const long long tiles = (long long)batch * p.tiles_x * p.tiles_y * ((cout + BN - 1) / BN);
+  if (BN == 128) return launch_halo<128>(s, tmA, tmAlo, tmW, tmWlo, p, smem_bytes, tiles);
+  return launch_halo<64>(s, tmA, tmAlo, tmW, tmWlo, p, smem_bytes, tiles);
 }
