@@ -444,19 +444,20 @@ def bench_eltwise(drv, dev, peaks):
         cases["pooling_backward_max_3x3s2"] = (lambda i: ct.pooling_backward(pool_ig[i], 0.0, pool_in[i], pool_out[i],
                                                                               pool_og[i % 2], pool_desc),
                                                2 * rows * cols * 4 + 2 * rows * cols)
-        # batch-normalize training half, spatial form [128, 64, 4096]: statistics + apply (input read three times,
-        # output written once) and the gradients (input and output gradient read twice, input gradient written)
+        # batch-normalize training half, spatial form [128, 64, 4096].  Bytes counted as the algorithm's passes: mean,
+        # variance about the rounded mean, apply = input read three times + output written; gradients = input and
+        # output gradient read by the sums pass and again by the input-gradient pass + its write
         bn_batch = [ct.new_tensor([64]) for _ in range(2)]
         bn_run = [ct.to_tensor(np.ones(64, np.float32)) for _ in range(2)]
         bn_grads = [ct.new_tensor([64]) for _ in range(2)]
         cases["batch_normalize_update_and_apply_spatial"] = (
             lambda i: ct.batch_normalize_update_and_apply(bn_out[i], bn_in[i], bn_batch[0], bn_batch[1], bn_run[0], bn_run[1],
-                                                          0.1, bn_stats[2], bn_stats[3], 1e-3), 2 * rows * cols * 4)
+                                                          0.1, bn_stats[2], bn_stats[3], 1e-3), 4 * rows * cols * 4)
         bn_og = [ct.in_place_reshape(g_, [128, 64, 4096]) for g_ in grads]
         cases["batch_normalize_gradients_spatial"] = (
             lambda i: ct.batch_normalize_gradients(bn_out[i], bn_grads[0], bn_grads[1], bn_og[i], bn_out[i], bn_in[i],
                                                    bn_batch[0], bn_batch[1], bn_stats[2], bn_stats[3], 1e-3),
-            3 * rows * cols * 4)
+            5 * rows * cols * 4)
         # lrn across channels, n = 5, on [128, 64, 64, 64]
         lrn_desc = ct.lrn_descriptor(n=5, k=2, alpha=1e-4, beta=0.75)
         cases["lrn_forward_n5"] = (lambda i: ct.lrn_forward(pool_ig[i], pool_in[i], lrn_desc), 2 * rows * cols * 4)

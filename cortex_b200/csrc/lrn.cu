@@ -7,7 +7,7 @@
 //   backward:  dx_c = dy_c * s(c)^-beta - (2 * alpha * beta / n) * x_c * sum_{j in W(c)} dy_j * y_j / s(j)
 // (the backward sum runs over the same window as the forward one, as the library the reference calls does;
 // the reference's literals for n = 2 pin this).  Dense [.., channels, height, width] tensors of rank 3 to 5;
-// evaluated in double, rounded to the element type on store.
+// evaluated in the element type (float tensors in single precision, as the library call the reference makes).
 #include "common.cuh"
 
 namespace {
@@ -20,49 +20,56 @@ struct LrnGeom {
   double k, alpha_over_n, beta;
 };
 
+__device__ __forceinline__ float lrn_pow(float s, float e) { return powf(s, e); }
+__device__ __forceinline__ double lrn_pow(double s, double e) { return pow(s, e); }
+
 template <typename T>
-__device__ __forceinline__ double lrn_scale(const T* x, const LrnGeom& g, long long b, int c, long long p) {
+__device__ __forceinline__ T lrn_scale(const T* x, const LrnGeom& g, long long b, int c, long long p) {
   const int c0 = max(0, c - g.look_behind), c1 = min(g.channels - 1, c + g.look_ahead);
-  double sum = 0.0;
+  T sum = (T)0;
   for (int j = c0; j <= c1; ++j) {
-    const double v = (double)x[(b * g.channels + j) * g.plane + p];
+    const T v = x[(b * g.channels + j) * g.plane + p];
     sum += v * v;
   }
-  return g.k + g.alpha_over_n * sum;
+  return (T)g.k + (T)g.alpha_over_n * sum;
 }
 
 // WRITE_SCALE: store s(c) (backward pre-pass) instead of y
 template <typename T, bool WRITE_SCALE>
 __global__ void __launch_bounds__(256)
-lrn_forward_kernel(T* out, double* scale_out, const T* in, LrnGeom g, long long n_elems) {
+lrn_forward_kernel(T* out, T* scale_out, const T* in, LrnGeom g, long long n_elems) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += (long long)gridDim.x * blockDim.x) {
-    const long long p = i % g.plane;
-    const long long bc = i / g.plane;
-    const int c = (int)(bc % g.channels);
-    const long long b = bc / g.channels;
-    const double s = lrn_scale(in, g, b, c, p);
+    // 32-bit index arithmetic (the entry points limit a tensor to 2^32 - 1 elements)
+    const unsigned iu = (unsigned)i, plane_u = (unsigned)g.plane;
+    const unsigned bc = iu / plane_u;
+    const long long p = iu - bc * plane_u;
+    const long long b = bc / (unsigned)g.channels;
+    const int c = (int)(bc - (unsigned)b * (unsigned)g.channels);
+    const T s = lrn_scale(in, g, b, c, p);
     if (WRITE_SCALE) scale_out[i] = s;
-    else out[i] = (T)((double)in[i] * pow(s, -g.beta));
+    else out[i] = in[i] * lrn_pow(s, (T)-g.beta);
   }
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-lrn_backward_kernel(T* in_grad, const T* out, const T* in, const T* out_grad, const double* scale, LrnGeom g,
+lrn_backward_kernel(T* in_grad, const T* out, const T* in, const T* out_grad, const T* scale, LrnGeom g,
                     long long n_elems) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_elems; i += (long long)gridDim.x * blockDim.x) {
-    const long long p = i % g.plane;
-    const long long bc = i / g.plane;
-    const int c = (int)(bc % g.channels);
-    const long long b = bc / g.channels;
+    // 32-bit index arithmetic (the entry points limit a tensor to 2^32 - 1 elements)
+    const unsigned iu = (unsigned)i, plane_u = (unsigned)g.plane;
+    const unsigned bc = iu / plane_u;
+    const long long p = iu - bc * plane_u;
+    const long long b = bc / (unsigned)g.channels;
+    const int c = (int)(bc - (unsigned)b * (unsigned)g.channels);
     const int c0 = max(0, c - g.look_behind), c1 = min(g.channels - 1, c + g.look_ahead);
-    double sum = 0.0;
+    T sum = (T)0;
     for (int j = c0; j <= c1; ++j) {
       const long long o = (b * g.channels + j) * g.plane + p;
-      sum += (double)out_grad[o] * (double)out[o] / scale[o];
+      sum += out_grad[o] * out[o] / scale[o];
     }
-    const double direct = (double)out_grad[i] * pow(scale[i], -g.beta);
-    in_grad[i] = (T)(direct - 2.0 * g.alpha_over_n * g.beta * (double)in[i] * sum);
+    const T direct = out_grad[i] * lrn_pow(scale[i], (T)-g.beta);
+    in_grad[i] = direct - (T)(2.0 * g.alpha_over_n * g.beta) * in[i] * sum;
   }
 }
 
@@ -89,6 +96,7 @@ int lrn_geom(const cb200_dims* const* all, int count, const cb200_lrn_desc* desc
   g->look_ahead = desc->n - g->look_behind - 1;
   g->k = desc->k; g->alpha_over_n = desc->alpha / (double)desc->n; g->beta = desc->beta;
   *n_elems = g->plane * g->channels * g->batch;
+  CB_REQUIRE(*n_elems < 4294967296LL, "%s: more than 2^32 - 1 elements", what);
   return CB200_OK;
 }
 
@@ -135,15 +143,16 @@ int cb200_lrn_backward(cb200_stream* s, int dtype, void* in_grad, const cb200_di
   if (n == 0) return CB200_OK;
   DeviceGuard guard(s->device);
   void* scratch = nullptr;
-  rc = cb200_scratch(s, (size_t)n * sizeof(double), &scratch);
+  rc = cb200_scratch(s, (size_t)n * cb200_dtype_size(dtype), &scratch);
   if (rc) return rc;
-  double* scale = (double*)scratch;
   if (dtype == CB200_FLOAT) {
+    float* scale = (float*)scratch;
     lrn_forward_kernel<float, true><<<lrn_blocks(s, n), 256, 0, s->stream>>>(nullptr, scale, (const float*)in, g, n);
     CB_LAUNCH_CHECK(s);
     lrn_backward_kernel<float><<<lrn_blocks(s, n), 256, 0, s->stream>>>((float*)in_grad, (const float*)out, (const float*)in,
                                                                          (const float*)out_grad, scale, g, n);
   } else {
+    double* scale = (double*)scratch;
     lrn_forward_kernel<double, true><<<lrn_blocks(s, n), 256, 0, s->stream>>>(nullptr, scale, (const double*)in, g, n);
     CB_LAUNCH_CHECK(s);
     lrn_backward_kernel<double><<<lrn_blocks(s, n), 256, 0, s->stream>>>((double*)in_grad, (const double*)out, (const double*)in,

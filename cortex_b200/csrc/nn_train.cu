@@ -14,8 +14,9 @@
 //
 // The batch-normalisation statistics are sums over (batch x element) per channel.  Elementwise form: one
 // thread per column, rows visited in order (coalesced across threads, and the same summation order as the
-// reference).  Spatial form: one CTA per channel, double-precision tree reduction (the summation order
-// differs from the reference's sequential loop: results agree to rounding of the double sums).
+// reference).  Spatial form: (channel x batch-slab) CTAs write double partial sums, a small kernel combines them
+// in slab order (the summation order differs from the reference's sequential loop: results agree to rounding
+// of the double sums).
 #include "common.cuh"
 
 namespace {
@@ -32,60 +33,91 @@ __device__ __forceinline__ int floor_div(int a, int b) {   // b > 0
   return (a % b != 0 && a < 0) ? q - 1 : q;
 }
 
-template <typename T, int OP>
+// VEC consecutive input columns per thread (VEC = 4 floats / 2 doubles with 16-byte accesses when the rows allow,
+// else 1): the index decomposition and the output-row range are shared, the output / output-gradient values the
+// neighbouring columns read come from the same cache lines.
+template <typename T, int OP, int VEC>
 __global__ void __launch_bounds__(256)
-pooling_backward_kernel(T* in_grad, const T* in, const T* out, const T* out_grad, PoolBwdGeom g, long long n_in,
+pooling_backward_kernel(T* in_grad, const T* in, const T* out, const T* out_grad, PoolBwdGeom g, long long n_groups,
                         double in_grad_alpha) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_in; i += (long long)gridDim.x * blockDim.x) {
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+  const int groups_per_row = g.in_w / VEC;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_groups; i += (long long)gridDim.x * blockDim.x) {
     const unsigned iu = (unsigned)i;
-    const unsigned tq = iu / (unsigned)g.in_w;
-    const int ix = (int)(iu - tq * (unsigned)g.in_w);
+    const unsigned tq = iu / (unsigned)groups_per_row;
+    const int ix0 = (int)(iu - tq * (unsigned)groups_per_row) * VEC;
     const unsigned plane = tq / (unsigned)g.in_h;
     const int iy = (int)(tq - plane * (unsigned)g.in_h);
+    const long long e0 = ((long long)plane * g.in_h + iy) * g.in_w + ix0;
     const long long out_base = (long long)plane * g.out_h * g.out_w;
-    // output rows / columns whose window [o*stride - pad, o*stride - pad + k) holds iy / ix
+    // output rows whose window [o*stride - pad, o*stride - pad + k) holds iy
     const int oy0 = max(0, floor_div(iy + g.pad_y - g.kh + g.stride_y, g.stride_y));   // ceil((iy+pad-kh+1)/stride)
     const int oy1 = min(g.out_h - 1, (iy + g.pad_y) / g.stride_y);
-    const int ox0 = max(0, floor_div(ix + g.pad_x - g.kw + g.stride_x, g.stride_x));
-    const int ox1 = min(g.out_w - 1, (ix + g.pad_x) / g.stride_x);
-    T acc = in_grad_alpha == 0.0 ? (T)0 : (T)(in_grad_alpha * (double)in_grad[i]);
-    const T x = OP == CB200_POOL_MAX ? in[i] : (T)0;
-    for (int oy = oy0; oy <= oy1; ++oy) {
-      int exc_h = 0;
-      if (OP == CB200_POOL_AVG_EXC_PAD) {
-        const int rel_y = oy * g.stride_y - g.pad_y;
-        exc_h = min(rel_y + g.kh, g.in_h) - max(rel_y, 0);
-      }
-      for (int ox = ox0; ox <= ox1; ++ox) {
-        const long long o = out_base + (long long)oy * g.out_w + ox;
-        if (OP == CB200_POOL_MAX) {
-          if (x == out[o]) acc = (T)((double)acc + (double)out_grad[o]);
-        } else if (OP == CB200_POOL_AVG) {
-          acc = (T)((double)acc + (double)out_grad[o] / (double)(g.kw * g.kh));
-        } else {
-          const int rel_x = ox * g.stride_x - g.pad_x;
-          const int exc_w = min(rel_x + g.kw, g.in_w) - max(rel_x, 0);
-          acc = (T)((double)acc + (double)out_grad[o] / (double)(exc_w * exc_h));
+    Pack x, acc;
+    if (OP == CB200_POOL_MAX) x = *reinterpret_cast<const Pack*>(in + e0);
+    if (in_grad_alpha == 0.0) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc.v[e] = (T)0;
+    } else {
+      acc = *reinterpret_cast<const Pack*>(in_grad + e0);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc.v[e] = (T)(in_grad_alpha * (double)acc.v[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const int ix = ix0 + e;
+      const int ox0 = max(0, floor_div(ix + g.pad_x - g.kw + g.stride_x, g.stride_x));
+      const int ox1 = min(g.out_w - 1, (ix + g.pad_x) / g.stride_x);
+      T a = acc.v[e];
+      for (int oy = oy0; oy <= oy1; ++oy) {
+        int exc_h = 0;
+        if (OP == CB200_POOL_AVG_EXC_PAD) {
+          const int rel_y = oy * g.stride_y - g.pad_y;
+          exc_h = min(rel_y + g.kh, g.in_h) - max(rel_y, 0);
+        }
+        for (int ox = ox0; ox <= ox1; ++ox) {
+          const long long o = out_base + (long long)oy * g.out_w + ox;
+          if (OP == CB200_POOL_MAX) {
+            // a + b in the element type IS the rounded exact sum: the reference's double add followed by its cast
+            if (x.v[e] == out[o]) a = a + out_grad[o];
+          } else if (OP == CB200_POOL_AVG) {
+            a = (T)((double)a + (double)out_grad[o] / (double)(g.kw * g.kh));
+          } else {
+            const int rel_x = ox * g.stride_x - g.pad_x;
+            const int exc_w = min(rel_x + g.kw, g.in_w) - max(rel_x, 0);
+            a = (T)((double)a + (double)out_grad[o] / (double)(exc_w * exc_h));
+          }
         }
       }
+      acc.v[e] = a;
     }
-    in_grad[i] = acc;
+    *reinterpret_cast<Pack*>(in_grad + e0) = acc;
   }
+}
+
+template <typename T, int VEC>
+void pooling_backward_launch_v(cb200_stream* s, int op, T* in_grad, const T* in, const T* out, const T* out_grad,
+                               const PoolBwdGeom& g, long long n_in, double alpha) {
+  const long long n_groups = n_in / VEC;
+  long long blocks = (n_groups + 255) / 256;
+  const long long cap = (long long)s->sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  const unsigned b = (unsigned)blocks;
+  if (op == CB200_POOL_MAX)
+    pooling_backward_kernel<T, CB200_POOL_MAX, VEC><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+  else if (op == CB200_POOL_AVG)
+    pooling_backward_kernel<T, CB200_POOL_AVG, VEC><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+  else
+    pooling_backward_kernel<T, CB200_POOL_AVG_EXC_PAD, VEC><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
 }
 
 template <typename T>
 void pooling_backward_launch(cb200_stream* s, int op, T* in_grad, const T* in, const T* out, const T* out_grad,
                              const PoolBwdGeom& g, long long n_in, double alpha) {
-  long long blocks = (n_in + 255) / 256;
-  const long long cap = (long long)s->sm_count * 32;
-  if (blocks > cap) blocks = cap;
-  const unsigned b = (unsigned)blocks;
-  if (op == CB200_POOL_MAX)
-    pooling_backward_kernel<T, CB200_POOL_MAX><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_in, alpha);
-  else if (op == CB200_POOL_AVG)
-    pooling_backward_kernel<T, CB200_POOL_AVG><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_in, alpha);
-  else
-    pooling_backward_kernel<T, CB200_POOL_AVG_EXC_PAD><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_in, alpha);
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const bool vec = (g.in_w % VEC) == 0 && ((((uintptr_t)in_grad) | ((uintptr_t)in)) & 15) == 0;
+  if (vec) pooling_backward_launch_v<T, VEC>(s, op, in_grad, in, out, out_grad, g, n_in, alpha);
+  else pooling_backward_launch_v<T, 1>(s, op, in_grad, in, out, out_grad, g, n_in, alpha);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -208,6 +240,175 @@ bn_gradients_kernel(T* in_grad, T* scale_grad, T* bias_grad, const T* out_grad, 
   }
 }
 
+// ---- spatial form at scale: (channel x batch-slab) CTAs write partial sums, a small kernel combines them ----
+// A row = the `inner` contiguous elements of one (batch entry, channel).  CTA (c, s) walks the rows of channel c
+// whose batch entry lies in slab s with 16-byte loads; partial sums are doubles in the stream's scratch,
+// combined per channel in slab order (deterministic).
+constexpr int BN_SLAB_THREADS = 256;
+
+template <typename T>
+struct BnVec { T v[16 / sizeof(T)]; };
+
+// one value per thread -> CTA total in thread 0 (others: undefined)
+__device__ __forceinline__ double slab_reduce(double v, double* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  double t = 0.0;
+  if (threadIdx.x == 0)
+    for (int w = 0; w < BN_SLAB_THREADS / 32; ++w) t += sh[w];
+  return t;
+}
+
+// NQ sums per (channel, slab).  MODE 0: {x};  1: {(mean - x)^2};  2: the five sums of the gradient pass.
+template <typename T, int MODE, bool VECTOR>
+__global__ void __launch_bounds__(BN_SLAB_THREADS)
+bn_slab_sums_kernel(double* partial, const T* __restrict__ in, const T* out_grad, const T* __restrict__ means,
+                    const T* __restrict__ variances, const T* __restrict__ scale, double epsilon, long long batch,
+                    int channels, int inner, int slabs) {
+  constexpr int NQ = MODE == 2 ? 5 : 1;
+  constexpr int VEC = VECTOR ? 16 / (int)sizeof(T) : 1;
+  __shared__ double red[BN_SLAB_THREADS / 32];
+  const int c = blockIdx.y, slab = blockIdx.x;
+  const long long b0 = batch * slab / slabs, b1 = batch * (slab + 1) / slabs;
+  const double mean = MODE >= 1 ? (double)means[c] : 0.0;
+  double g = 0.0, inv_std = 0.0, d_var = 0.0;
+  if (MODE == 2) {
+    g = (double)scale[c];
+    const double variance = (double)(T)epsilon + (double)variances[c];
+    inv_std = 1.0 / sqrt(variance);
+    d_var = (double)(T)(-0.5 * pow(variance, -1.5));
+  }
+  double acc[NQ];
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) acc[q] = 0.0;
+  const int nvec = inner / VEC;
+  for (long long b = b0; b < b1; ++b) {
+    const long long base = (b * channels + c) * (long long)inner;
+    for (int j = threadIdx.x; j < nvec; j += BN_SLAB_THREADS) {
+      T x[VEC], og[VEC];
+      if (VECTOR) {
+        *reinterpret_cast<BnVec<T>*>(x) = *reinterpret_cast<const BnVec<T>*>(in + base + (long long)j * VEC);
+        if (MODE == 2) *reinterpret_cast<BnVec<T>*>(og) = *reinterpret_cast<const BnVec<T>*>(out_grad + base + (long long)j * VEC);
+      } else {
+        x[0] = in[base + j];
+        if (MODE == 2) og[0] = out_grad[base + j];
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        if (MODE == 0) acc[0] += (double)x[e];
+        else if (MODE == 1) { const double d = mean - (double)x[e]; acc[0] = __dadd_rn(acc[0], __dmul_rn(d, d)); }
+        else {
+          const double o = (double)og[e], centered = (double)x[e] - mean;
+          const double dxhat = (double)(T)__dmul_rn(g, o);
+          acc[0] += o;
+          acc[1] += __dmul_rn(o, __dmul_rn(centered, inv_std));
+          acc[2] += __dmul_rn(__dmul_rn(dxhat, centered), d_var);
+          acc[3] += __dmul_rn(-dxhat, inv_std);
+          acc[4] += __dmul_rn(-2.0, centered);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) {
+    const double t = slab_reduce(acc[q], red);
+    if (threadIdx.x == 0) partial[((long long)q * channels + c) * slabs + slab] = t;
+  }
+}
+
+// STEP 0: batch mean;  1: batch variance + running statistics
+template <typename T, int STEP>
+__global__ void __launch_bounds__(128)
+bn_update_finish_kernel(const double* partial, T* batch_means, T* batch_variances, T* running_means,
+                        T* running_variances, double average_factor, long long count, int channels, int slabs) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  double sum = 0.0;
+  for (int s = 0; s < slabs; ++s) sum += partial[(long long)c * slabs + s];
+  const double n = count > 1 ? (double)count : 1.0;
+  if (STEP == 0) {
+    batch_means[c] = (T)(sum / n);
+  } else {
+    const double factor = (double)(T)average_factor, lerp = (double)(T)1.0 - factor;
+    const double n_running = n - 1.0 > 1.0 ? n - 1.0 : 1.0;
+    const double mean_old = (double)running_means[c], var_old = (double)running_variances[c];
+    const double new_mean = (double)batch_means[c];
+    batch_variances[c] = (T)(sum / n);
+    running_means[c] = (T)(__dmul_rn(mean_old, lerp) + __dmul_rn(new_mean, factor));
+    running_variances[c] = (T)(__dmul_rn(var_old, lerp) + __dmul_rn((double)(T)(sum / n_running), factor));
+  }
+}
+
+// per channel: bias / scale gradient and the coefficients of the input-gradient pass {g, inv_std, mean, d_var_d_out, part3}
+template <typename T>
+__global__ void __launch_bounds__(128)
+bn_gradients_finish_kernel(const double* partial, double* coef, T* scale_grad, T* bias_grad, const T* means,
+                           const T* variances, const T* scale, double epsilon, long long count, int channels, int slabs) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  double sums[5];
+  for (int q = 0; q < 5; ++q) {
+    double t = 0.0;
+    for (int s = 0; s < slabs; ++s) t += partial[((long long)q * channels + c) * slabs + s];
+    sums[q] = t;
+  }
+  const double variance = (double)(T)epsilon + (double)variances[c];
+  const double inv_std = 1.0 / sqrt(variance);
+  bias_grad[c] = (T)sums[0];
+  scale_grad[c] = (T)sums[1];
+  const double d_var_d_out = (double)(T)sums[2];
+  const double d_mean_d_out = (double)(T)(sums[3] + __dmul_rn(d_var_d_out, sums[4] / (double)count));
+  const double one_over_count = 1.0 / (double)count;
+  double* k = coef + (long long)c * 5;
+  k[0] = (double)scale[c]; k[1] = inv_std; k[2] = (double)means[c]; k[3] = d_var_d_out;
+  k[4] = __dmul_rn(d_mean_d_out, one_over_count);
+}
+
+// input gradient: one CTA walks rows (batch entry, channel); the channel's coefficients are uniform per row
+template <typename T, bool VECTOR>
+__global__ void __launch_bounds__(BN_SLAB_THREADS)
+bn_input_gradient_kernel(T* in_grad, const T* out_grad, const T* in, const double* __restrict__ coef, long long n_rows,
+                         int channels, int inner, double one_over_count) {
+  constexpr int VEC = VECTOR ? 16 / (int)sizeof(T) : 1;
+  const int nvec = inner / VEC;
+  for (long long r = blockIdx.x; r < n_rows; r += gridDim.x) {
+    const double* k = coef + (r % channels) * 5;
+    const double g = k[0], inv_std = k[1], mean = k[2], dv2 = __dmul_rn(k[3], 2.0), part3 = k[4];
+    const long long base = r * (long long)inner;
+    for (int j = threadIdx.x; j < nvec; j += BN_SLAB_THREADS) {
+      T x[VEC], og[VEC], res[VEC];
+      if (VECTOR) {
+        *reinterpret_cast<BnVec<T>*>(x) = *reinterpret_cast<const BnVec<T>*>(in + base + (long long)j * VEC);
+        *reinterpret_cast<BnVec<T>*>(og) = *reinterpret_cast<const BnVec<T>*>(out_grad + base + (long long)j * VEC);
+      } else {
+        x[0] = in[base + j];
+        og[0] = out_grad[base + j];
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const double dxhat = (double)(T)__dmul_rn(g, (double)og[e]);
+        const double centered = (double)x[e] - mean;
+        const double part1 = __dmul_rn(dxhat, inv_std);
+        const double part2 = __dmul_rn(__dmul_rn(dv2, centered), one_over_count);
+        res[e] = (T)__dadd_rn(__dadd_rn(part1, part2), part3);
+      }
+      if (VECTOR) *reinterpret_cast<BnVec<T>*>(in_grad + base + (long long)j * VEC) = *reinterpret_cast<BnVec<T>*>(res);
+      else in_grad[base + j] = res[0];
+    }
+  }
+}
+
+static int bn_slab_count(const cb200_stream* s, long long batch, long long channels) {
+  long long slabs = ((long long)s->sm_count * 6 + channels - 1) / channels;
+  if (slabs > batch) slabs = batch;
+  if (slabs < 1) slabs = 1;
+  if (slabs > 1024) slabs = 1024;
+  return (int)slabs;
+}
+
 int bn_train_check(cb200_stream* s, int dtype, int64_t batch, int64_t channels, int64_t inner, const char* what) {
   CB_REQUIRE(s, "%s: null stream", what);
   CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE, "batch-normalization is only defined for float and double tensors");
@@ -222,13 +423,41 @@ int bn_update_launch(cb200_stream* s, const void* in, void* bm, void* bv, void* 
                      int64_t batch, int64_t channels, int64_t inner) {
   DeviceGuard guard(s->device);
   BnShape sh{batch, (int)channels, (int)inner};
-  if (inner == 1)
+  if (inner == 1) {
     bn_update_kernel<T, 1><<<(unsigned)((channels + 127) / 128), 128, 0, s->stream>>>(
         (const T*)in, (T*)bm, (T*)bv, (T*)rm, (T*)rv, factor, sh);
-  else
+    CB_LAUNCH_CHECK(s);
+    return CB200_OK;
+  }
+  if (channels > 65535) {      // grid.y limit: the one-CTA-per-channel kernel
     bn_update_kernel<T, BN_TEAM><<<(unsigned)channels, BN_TEAM, 0, s->stream>>>(
         (const T*)in, (T*)bm, (T*)bv, (T*)rm, (T*)rv, factor, sh);
-  CB_LAUNCH_CHECK(s);
+    CB_LAUNCH_CHECK(s);
+    return CB200_OK;
+  }
+  const int slabs = bn_slab_count(s, batch, channels);
+  void* scratch = nullptr;
+  int rc = cb200_scratch(s, (size_t)channels * slabs * sizeof(double), &scratch);
+  if (rc) return rc;
+  double* partial = (double*)scratch;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const bool vec = (inner % VEC) == 0 && (((uintptr_t)in) & 15) == 0;
+  const dim3 grid((unsigned)slabs, (unsigned)channels, 1);
+  const unsigned fin = (unsigned)((channels + 127) / 128);
+  const long long count = batch * inner;
+  for (int step = 0; step < 2; ++step) {
+    if (step == 0) {
+      if (vec) bn_slab_sums_kernel<T, 0, true><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, nullptr, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs);
+      else bn_slab_sums_kernel<T, 0, false><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, nullptr, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs);
+    } else {
+      if (vec) bn_slab_sums_kernel<T, 1, true><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, (const T*)bm, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs);
+      else bn_slab_sums_kernel<T, 1, false><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, (const T*)bm, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs);
+    }
+    CB_LAUNCH_CHECK(s);
+    if (step == 0) bn_update_finish_kernel<T, 0><<<fin, 128, 0, s->stream>>>(partial, (T*)bm, (T*)bv, (T*)rm, (T*)rv, factor, count, (int)channels, slabs);
+    else bn_update_finish_kernel<T, 1><<<fin, 128, 0, s->stream>>>(partial, (T*)bm, (T*)bv, (T*)rm, (T*)rv, factor, count, (int)channels, slabs);
+    CB_LAUNCH_CHECK(s);
+  }
   return CB200_OK;
 }
 
@@ -258,12 +487,36 @@ int bn_gradients_launch(cb200_stream* s, void* ig, void* sg, void* bg, const voi
                         const void* bv, const void* scale, double epsilon, int64_t batch, int64_t channels, int64_t inner) {
   DeviceGuard guard(s->device);
   BnShape sh{batch, (int)channels, (int)inner};
-  if (inner == 1)
-    bn_gradients_kernel<T, 1><<<(unsigned)((channels + 127) / 128), 128, 0, s->stream>>>(
-        (T*)ig, (T*)sg, (T*)bg, (const T*)og, (const T*)in, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, sh);
-  else
-    bn_gradients_kernel<T, BN_TEAM><<<(unsigned)channels, BN_TEAM, 0, s->stream>>>(
-        (T*)ig, (T*)sg, (T*)bg, (const T*)og, (const T*)in, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, sh);
+  if (inner == 1 || channels > 65535) {
+    if (inner == 1)
+      bn_gradients_kernel<T, 1><<<(unsigned)((channels + 127) / 128), 128, 0, s->stream>>>(
+          (T*)ig, (T*)sg, (T*)bg, (const T*)og, (const T*)in, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, sh);
+    else
+      bn_gradients_kernel<T, BN_TEAM><<<(unsigned)channels, BN_TEAM, 0, s->stream>>>(
+          (T*)ig, (T*)sg, (T*)bg, (const T*)og, (const T*)in, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, sh);
+    CB_LAUNCH_CHECK(s);
+    return CB200_OK;
+  }
+  const int slabs = bn_slab_count(s, batch, channels);
+  void* scratch = nullptr;
+  int rc = cb200_scratch(s, ((size_t)5 * channels * slabs + (size_t)5 * channels) * sizeof(double), &scratch);
+  if (rc) return rc;
+  double* partial = (double*)scratch;
+  double* coef = partial + (size_t)5 * channels * slabs;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const bool vec = (inner % VEC) == 0 && ((((uintptr_t)in) | ((uintptr_t)og) | ((uintptr_t)ig)) & 15) == 0;
+  const dim3 grid((unsigned)slabs, (unsigned)channels, 1);
+  if (vec) bn_slab_sums_kernel<T, 2, true><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, (const T*)og, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, batch, (int)channels, (int)inner, slabs);
+  else bn_slab_sums_kernel<T, 2, false><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, (const T*)og, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, batch, (int)channels, (int)inner, slabs);
+  CB_LAUNCH_CHECK(s);
+  const long long count = batch * inner;
+  bn_gradients_finish_kernel<T><<<(unsigned)((channels + 127) / 128), 128, 0, s->stream>>>(
+      partial, coef, (T*)sg, (T*)bg, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, count, (int)channels, slabs);
+  CB_LAUNCH_CHECK(s);
+  const long long n_rows = batch * channels;
+  long long blocks = n_rows < (long long)s->sm_count * 8 ? n_rows : (long long)s->sm_count * 8;
+  if (vec) bn_input_gradient_kernel<T, true><<<(unsigned)blocks, BN_SLAB_THREADS, 0, s->stream>>>((T*)ig, (const T*)og, (const T*)in, coef, n_rows, (int)channels, (int)inner, 1.0 / (double)count);
+  else bn_input_gradient_kernel<T, false><<<(unsigned)blocks, BN_SLAB_THREADS, 0, s->stream>>>((T*)ig, (const T*)og, (const T*)in, coef, n_rows, (int)channels, (int)inner, 1.0 / (double)count);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }

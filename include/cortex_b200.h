@@ -368,7 +368,7 @@ int cb200_rand(cb200_stream* s, void* dest, const cb200_dims* dest_dims, int dis
  * Dense tensors [.., channels, height, width] of rank 3 to 5, all of one shape.  With
  * W(c) = [c - (n-1)/2, c + n - 1 - (n-1)/2] (integer division, clipped) and s(c) = k + (alpha/n) * sum_{W(c)} x^2:
  *   forward:  y = x * s^-beta;   backward:  dx = dy * s^-beta - (2*alpha*beta/n) * x * sum_{j in W(c)} dy_j*y_j/s(j).
- * The backward call uses 8 bytes of stream scratch per element. */
+ * Float tensors are evaluated in single precision.  The backward call uses one element of stream scratch per element. */
 typedef struct cb200_lrn_desc { int32_t n; double k, alpha, beta; } cb200_lrn_desc;
 int cb200_lrn_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, const void* in,
                       const cb200_dims* in_dims, const cb200_lrn_desc* desc);
