@@ -59,6 +59,13 @@ def workload_config(world, dt="float"):
                   % ((BATCH // max(world, 1)) * WIDTH * 4 >> 20)}
 
 
+def rank_device(local_rank, world, visible):
+    """GPU index a local rank uses: ranks spread evenly over the visible GPUs (stride = visible // world)."""
+    if 1 < world <= visible:
+        return local_rank * (visible // world)
+    return local_rank
+
+
 def threads_in_use():
     """Thread counts the loaded BLAS / OpenMP runtimes report (what the CPU arm really ran on)."""
     try:
@@ -787,7 +794,7 @@ def run_b200(args, rank, world, local_rank):
     # four ranks on GPUs 0-3 upload at 26 GB/s each, two at 54 GB/s each).  With exactly `world` GPUs visible this
     # is the identity.
     visible = torch.cuda.device_count()
-    local_rank = local_rank * max(1, visible // world) if 1 < world <= visible else local_rank
+    local_rank = rank_device(local_rank, world, visible)
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
@@ -974,7 +981,7 @@ def run_b200(args, rank, world, local_rank):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32" if dt == "float" else "f64", "data": "synthetic",
         "config": config, "rows_per_gpu": rows, "row_block": row_block, "kernel_path": kernel_path,
-        "gpu_indices": [r * max(1, visible // world) if 1 < world <= visible else r for r in range(world)],
+        "gpu_indices": [rank_device(r, world, visible) for r in range(world)],
         "tflops": value * FLOPS_PER_SAMPLE / 1e12,
         "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                 "ms_per_step": e2e_ms, "chunk_rows": chunk, "input_slots": pipe.slots,

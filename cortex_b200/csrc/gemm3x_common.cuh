@@ -33,6 +33,11 @@ struct GemmParams {
   int split_from;      // pair kernel only: tiles from this index on are computed as two K halves by two clusters
   float* partials;     // pair kernel only: [tail tile][K half][rank][128][BN] partial accumulators
   int split_block;     // tiles per block of (first halves, second halves) in the grid order
+  // Small problems (fewer tiles than half the SMs): every tile is reduced by ksplit_n CTAs, each over a slice of K.
+  // A CTA parks its raw tile in ksplit_ws[(tile * ksplit_n + slice)][BM][BN]; the one that arrives last (per-tile
+  // counter in tile_flags) sums the slices in slice order and runs the epilogue.  Nobody waits.
+  int ksplit_n;
+  float* ksplit_ws;
   int* tile_flags;
   int* status;
   // Row-major store only: every finished tile is also written to the same (row, column) position of
@@ -88,6 +93,33 @@ __device__ __forceinline__ float4 ld_c4(const float* p, bool partial) {
   return partial ? __ldcg(reinterpret_cast<const float4*>(p)) : *reinterpret_cast<const float4*>(p);
 }
 
+// Park this CTA's raw accumulators (main + cross terms) as a [BM][BN] float tile (K-sliced small problems).
+template <int BN>
+__device__ __forceinline__ void dump_tile(const GemmParams& p, uint32_t tmem_base, float* dst, int warp, int lane) {
+  const int q = warp & 3, half = warp >> 2;
+  constexpr int COLS_PER_HALF = BN / 2;
+  float* row = dst + (long long)(q * 32 + lane) * BN;
+#pragma unroll 1
+  for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
+    const int col0 = half * COLS_PER_HALF + cc * 32;
+    uint32_t r[32];
+    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
+    if (!(p.flags & FLAG_ONE_TERM)) {
+      uint32_t rc[32];
+      tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + col0), rc);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(rc[j]));
+    } else {
+      tmem_ld_wait();
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      __stcg(reinterpret_cast<float4*>(row + col0 + j), make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                    __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
+  }
+}
+
 // `beta_now`: factor applied to what C holds (the caller's beta, or 1 once C holds a partial result).
 // `last_pass`: bias, activation and peer stores join only on the pass that completes the tile.
 // `staging`: shared memory that is free by now (the pipeline stages), 32 x 36 floats per warp: slabs are
@@ -99,7 +131,8 @@ __device__ __forceinline__ float4 ld_c4(const float* p, bool partial) {
 template <int BN, bool WITH_LO = false>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem_base, int m0, int n0, int warp,
                                               int lane, float* staging, float beta_now, bool last_pass, bool c_is_partial,
-                                              const float* part = nullptr) {
+                                              const float* part = nullptr, const float* gather = nullptr,
+                                              int gather_n = 0) {
       float* c_lo = (WITH_LO && last_pass) ? p.C_lo : nullptr;
       const float* e_bias = last_pass ? p.bias : nullptr;
       const int e_act = last_pass ? p.act : 0;
@@ -116,6 +149,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
       for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
         const int col0 = half * COLS_PER_HALF + cc * 32;
         uint32_t r[32];
+        if (gather) {
+          // K slices parked by gather_n CTAs (this one included): summed in slice order, whoever runs this
+          const float* g0 = gather + (long long)(q * 32 + lane) * BN + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 a = __ldcg(reinterpret_cast<const float4*>(g0 + j));
+            for (int sl = 1; sl < gather_n; ++sl) {
+              const float4 b = __ldcg(reinterpret_cast<const float4*>(g0 + (long long)sl * 128 * BN + j));   // [128][BN] per slice
+              a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            }
+            r[j] = __float_as_uint(a.x); r[j + 1] = __float_as_uint(a.y); r[j + 2] = __float_as_uint(a.z); r[j + 3] = __float_as_uint(a.w);
+          }
+        } else {
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
         if (!(p.flags & FLAG_ONE_TERM)) {
           uint32_t rc[32];
@@ -125,6 +171,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(rc[j]));
         } else {
           tmem_ld_wait();
+        }
         }
         if (part) {
 #pragma unroll

@@ -674,6 +674,8 @@ int launch_presplit(cb200_stream* s, float* C, float* C_lo, long long ldc, float
   // reductions of 4096 and more: the main accumulator is folded into partial sums every 2048 k values
   // (the general kernel has to use two K halves per tile for this; here the epilogue warps are free)
   p.k_split = 1;
+  p.ksplit_n = 1;
+  p.ksplit_ws = nullptr;
   p.drain_every = K >= 4096 ? 2048 / BK : 0;
   p.split_block = 2 * s->sm_count;
   p.tile_flags = nullptr;

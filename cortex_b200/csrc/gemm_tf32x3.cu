@@ -81,7 +81,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int tiles_n = (p.N + BN - 1) / BN;
   const int tiles_m = (p.M + BM - 1) / BM;
   const int n_tiles = tiles_m * tiles_n;
-  int k_half = 0, tile_id = (int)blockIdx.x;
+  int k_half = 0, tile_id = (int)blockIdx.x, k_slice = 0;
+  if (p.ksplit_n > 1) {
+    tile_id = (int)blockIdx.x / p.ksplit_n;
+    k_slice = (int)blockIdx.x - tile_id * p.ksplit_n;
+  }
   if (p.k_split == 2) {
     const int blk = (int)blockIdx.x / (2 * p.split_block);
     const int r = (int)blockIdx.x - blk * 2 * p.split_block;
@@ -96,8 +100,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int m0 = tile_m * BM, n0 = tile_n * BN;
   const int nkb_all = (p.K + BK - 1) / BK;
   const int kb_first = p.k_split == 2 ? nkb_all / 2 : nkb_all;       // k-blocks of the first half
-  const int kb_begin = k_half ? kb_first : 0;
-  const int nkb = k_half ? nkb_all - kb_first : kb_first;
+  int kb_begin = k_half ? kb_first : 0;
+  int nkb = k_half ? nkb_all - kb_first : kb_first;
+  if (p.ksplit_n > 1) {
+    kb_begin = (int)((long long)nkb_all * k_slice / p.ksplit_n);
+    nkb = (int)((long long)nkb_all * (k_slice + 1) / p.ksplit_n) - kb_begin;
+  }
 
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bar_full = smem_u32(bars), bar_conv = smem_u32(bars + STAGES), bar_empty = smem_u32(bars + 2 * STAGES),
@@ -300,7 +308,26 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       }
       ok = __all_sync(0xffffffffu, __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0);
     }
-    if (ok) {
+    if (p.ksplit_n > 1) {
+      // K-sliced small problem: park the raw tile; the CTA that arrives last combines the slices and stores.
+      // All eight warps take both barriers whatever their own wait returned (a warp that gave up has raised
+      // the abort flag, which cancels the hand-over for the whole CTA).
+      float* ws_tile = p.ksplit_ws + (long long)tile_id * p.ksplit_n * (BM * BN);
+      if (ok) {
+        dump_tile<BN>(p, tmem_base, ws_tile + (long long)k_slice * (BM * BN), warp, lane);
+        __threadfence();
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(NUM_CONV_WARPS * 32) : "memory");
+      int* arrived = reinterpret_cast<int*>(const_cast<int*>(abort_flag)) + 1;      // a spare shared word
+      if (threadIdx.x == 0) *arrived = *abort_flag ? -1 : atomicAdd(p.tile_flags + tile_id, 1);
+      asm volatile("bar.sync 1, %0;" ::"n"(NUM_CONV_WARPS * 32) : "memory");
+      if (*arrived == p.ksplit_n - 1) {
+        __threadfence();
+        epilogue_tile<BN>(p, tmem_base, m0, n0, warp, lane, reinterpret_cast<float*>(smem), p.beta, true, false, nullptr,
+                          ws_tile, p.ksplit_n);
+        if (threadIdx.x == 0) p.tile_flags[tile_id] = 0;      // left zero for the next launch
+      }
+    } else if (ok) {
       const bool last = p.k_split != 2 || k_half == 1;
       epilogue_tile<BN>(p, tmem_base, m0, n0, warp, lane, reinterpret_cast<float*>(smem), k_half ? 1.f : p.beta, last, k_half == 1);
       if (p.k_split == 2 && k_half == 0) __threadfence();     // this thread's part of C, before the flag below
@@ -374,7 +401,7 @@ int launch_tile(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmB,
     attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
   });
   if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
-  long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.k_split;
+  long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.k_split * p.ksplit_n;
   gemm_tf32x3_kernel<BN, BK><<<(unsigned)tiles, NUM_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmB, p);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
@@ -413,7 +440,15 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   // tiles finish sooner than two wide ones)
   int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
   const long long tiles_m = (M + BM - 1) / BM;
-  while (BN > 64 && tiles_m * ((N + BN - 1) / BN) < s->sm_count) BN >>= 1;
+  // Tile width for problems that do not fill the SMs.  Every column tile re-reads its rows of A, so when A is too
+  // large to stay hot in L2 (>= 24 MB) the widest tile that covers N is kept and the SMs are filled by slicing K
+  // (below).  Otherwise tiles are narrowed while they still fit ONE wave (narrower tiles finish sooner and make
+  // the slices' hand-over cheaper); narrowing into a second, partly empty wave never pays.
+  // Measured (us per call, old rule "narrow until every SM has a tile" -> this rule): 4096x512x4096 232 -> 108,
+  // 2048x1024x4096 220 -> 107, 8192x250x4096 293 -> 204, 8192x125x4096 159 -> 132, 1024x4096x1024 84 -> 60,
+  // 512x512x2048 58 -> 29.
+  const bool big_a = (long long)M * K * 4 >= (24ll << 20);
+  while (BN > 64 && !big_a && tiles_m * ((N + BN / 2 - 1) / (BN / 2)) <= s->sm_count) BN >>= 1;
   const int tiles_n = (N + BN - 1) / BN;
   const long long panel_bytes = (long long)BN * K * 4;          // one column tile's share of B
   // FLAG_SPLIT_K (the fused layer entry points): reductions of 4096 and more are cut in two K halves per
@@ -429,6 +464,27 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   if (p.k_split == 2) {
     int rcf = cb200_tile_flags(s, (size_t)tiles_m * tiles_n, &p.tile_flags);
     if (rcf) return rcf;
+  }
+  // Problems that leave more than half of the SMs without a tile: ksplit_n CTAs per tile, each over a slice of K
+  // (at least 8 k-blocks per slice), combined by the last one to finish.
+  p.ksplit_n = 1;
+  p.ksplit_ws = nullptr;
+  {
+    const long long tiles = tiles_m * tiles_n;
+    const int nkb_all = (K + 15) / 16;
+    long long sl = s->sm_count / (tiles > 0 ? tiles : 1);
+    if (s->opt_gemm_k_slices > 0) sl = s->opt_gemm_k_slices;
+    if (sl > nkb_all / 8) sl = nkb_all / 8;
+    if (sl > 1024 / BN) sl = 1024 / BN;       // the CTA that combines a tile reads slices x 128 x BN floats
+    if (sl > 16) sl = 16;
+    if (p.k_split == 1 && sl >= 2 && !(flags & FLAG_ONE_TERM)) {
+      void* ws = nullptr;
+      int rcs = cb200_partials(s, (size_t)tiles * sl * BM * BN * sizeof(float), &ws);
+      if (rcs) return rcs;
+      if ((rcs = cb200_tile_flags(s, (size_t)tiles, &p.tile_flags))) return rcs;
+      p.ksplit_n = (int)sl;
+      p.ksplit_ws = (float*)ws;
+    }
   }
   p.group_n = tiles_n;
   if (tiles_n * panel_bytes > (40ll << 20)) {

@@ -36,10 +36,15 @@ __device__ __forceinline__ int floor_div(int a, int b) {   // b > 0
 // VEC consecutive input columns per thread (VEC = 4 floats / 2 doubles with 16-byte accesses when the rows allow,
 // else 1): the index decomposition and the output-row range are shared, the output / output-gradient values the
 // neighbouring columns read come from the same cache lines.
-template <typename T, int OP, int VEC>
+// KS / ST: square window size and common stride as compile-time constants (0 = read from the geometry): the
+// divisions by the stride become shifts and the window loops unroll.
+template <typename T, int OP, int VEC, int KS, int ST>
 __global__ void __launch_bounds__(256)
-pooling_backward_kernel(T* in_grad, const T* in, const T* out, const T* out_grad, PoolBwdGeom g, long long n_groups,
+pooling_backward_kernel(T* in_grad, const T* in, const T* out, const T* out_grad, PoolBwdGeom gg, long long n_groups,
                         double in_grad_alpha) {
+  PoolBwdGeom g = gg;
+  if (KS) { g.kw = KS; g.kh = KS; }
+  if (ST) { g.stride_x = ST; g.stride_y = ST; }
   struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   const int groups_per_row = g.in_w / VEC;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_groups; i += (long long)gridDim.x * blockDim.x) {
@@ -95,7 +100,7 @@ pooling_backward_kernel(T* in_grad, const T* in, const T* out, const T* out_grad
   }
 }
 
-template <typename T, int VEC>
+template <typename T, int VEC, int KS, int ST>
 void pooling_backward_launch_v(cb200_stream* s, int op, T* in_grad, const T* in, const T* out, const T* out_grad,
                                const PoolBwdGeom& g, long long n_in, double alpha) {
   const long long n_groups = n_in / VEC;
@@ -104,11 +109,11 @@ void pooling_backward_launch_v(cb200_stream* s, int op, T* in_grad, const T* in,
   if (blocks > cap) blocks = cap;
   const unsigned b = (unsigned)blocks;
   if (op == CB200_POOL_MAX)
-    pooling_backward_kernel<T, CB200_POOL_MAX, VEC><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+    pooling_backward_kernel<T, CB200_POOL_MAX, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
   else if (op == CB200_POOL_AVG)
-    pooling_backward_kernel<T, CB200_POOL_AVG, VEC><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+    pooling_backward_kernel<T, CB200_POOL_AVG, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
   else
-    pooling_backward_kernel<T, CB200_POOL_AVG_EXC_PAD, VEC><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+    pooling_backward_kernel<T, CB200_POOL_AVG_EXC_PAD, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
 }
 
 template <typename T>
@@ -116,8 +121,12 @@ void pooling_backward_launch(cb200_stream* s, int op, T* in_grad, const T* in, c
                              const PoolBwdGeom& g, long long n_in, double alpha) {
   constexpr int VEC = 16 / (int)sizeof(T);
   const bool vec = (g.in_w % VEC) == 0 && ((((uintptr_t)in_grad) | ((uintptr_t)in)) & 15) == 0;
-  if (vec) pooling_backward_launch_v<T, VEC>(s, op, in_grad, in, out, out_grad, g, n_in, alpha);
-  else pooling_backward_launch_v<T, 1>(s, op, in_grad, in, out, out_grad, g, n_in, alpha);
+  const bool square = g.kw == g.kh && g.stride_x == g.stride_y;
+  if (vec && square && g.kw == 3 && g.stride_x == 2) pooling_backward_launch_v<T, VEC, 3, 2>(s, op, in_grad, in, out, out_grad, g, n_in, alpha);
+  else if (vec && square && g.kw == 2 && g.stride_x == 2) pooling_backward_launch_v<T, VEC, 2, 2>(s, op, in_grad, in, out, out_grad, g, n_in, alpha);
+  else if (vec && square && g.kw == 3 && g.stride_x == 1) pooling_backward_launch_v<T, VEC, 3, 1>(s, op, in_grad, in, out, out_grad, g, n_in, alpha);
+  else if (vec) pooling_backward_launch_v<T, VEC, 0, 0>(s, op, in_grad, in, out, out_grad, g, n_in, alpha);
+  else pooling_backward_launch_v<T, 1, 0, 0>(s, op, in_grad, in, out, out_grad, g, n_in, alpha);
 }
 
 // ------------------------------------------------------------------------------------------------------

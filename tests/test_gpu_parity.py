@@ -524,3 +524,32 @@ def test_tensor_core_reads_fp32_words_truncated(b200_driver, ta, tb):
     for x in (A, B):
         hi = trunc(x)
         assert np.array_equal(hi.astype(np.float64) + (x - hi).astype(np.float64), x.astype(np.float64))
+
+
+@pytest.mark.parametrize("M,N,K,act", [(128, 500, 784, "relu"), (128, 10, 500, None), (64, 1000, 2048, "tanh"),
+                                       (300, 72, 1040, None), (8192, 125, 4096, None)])
+def test_small_gemm_is_sliced_over_k(b200_driver, M, N, K, act):
+    """Problems with fewer tiles than half the SMs are reduced by several CTAs per tile, each over a slice of K,
+    combined by whichever finishes last (in slice order: the result does not depend on who that is).  Config 1's
+    two layers, a wide-K case, a ragged one and the 8-way column-sharded head; twice in a row (the per-tile
+    counters must be left clear), fused bias + activation, against float64."""
+    rng = np.random.default_rng(M + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    stream = b200_driver.default_device().create_stream()
+    outs = []
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        a, w, b = ct.to_tensor(A), ct.to_tensor(W), ct.to_tensor(bias)
+        for _ in range(2):
+            c = ct.to_tensor(np.full((M, N), np.nan, np.float32))
+            stream.gemm_bias_act(c.buffer, N, False, True, 1.0, a.buffer, M, K, K, w.buffer, N, K, 0.0, b.buffer, act)
+            outs.append(ct.to_array(c).reshape(M, N))
+    exact = A.astype(np.float64) @ W.astype(np.float64).T + bias
+    if act == "relu":
+        exact = np.maximum(exact, 0.0)
+    elif act == "tanh":
+        exact = np.tanh(exact)
+    assert pc.rel_err(outs[0], exact) <= pc.TOL["float"]
+    assert np.array_equal(outs[0], outs[1])
+    stream.sync()       # raises if a launch reported a status
