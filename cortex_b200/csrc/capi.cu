@@ -206,7 +206,7 @@ int cb200_stream_set_option(cb200_stream* s, int option, int64_t value) {
       s->opt_f64_simple = value != 0;
       return CB200_OK;
     case CB200_OPT_CONV_ROUTE:
-      CB_REQUIRE(value >= 0 && value <= 2, "stream_set_option: convolution route %lld outside [0, 2]", (long long)value);
+      CB_REQUIRE(value >= 0 && value <= 3, "stream_set_option: convolution route %lld outside [0, 3]", (long long)value);
       s->opt_conv_route = (int)value;
       return CB200_OK;
     case CB200_OPT_GEMM_K_SLICES:

@@ -45,11 +45,11 @@ int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const fl
 // channels: every operand tile by TMA -- the input patch kept in shared memory across the filter taps
 // (conv_halo.cu) where the 8 x 16 tiles fit the output, one shifted tile per tap otherwise (conv_tma.cu); the rest:
 // im2col rows gathered by threads (conv_igemm.cu).  opt_conv_route: 0 = by geometry, 1 = always gather, 2 = never
-// the patch kernel.  Also the engine of convolution-backward-data! (conv_backward.cu).
+// the patch kernel, 3 = by geometry, but the patch kernel always behind its layout pre-pass.  Also the engine of convolution-backward-data! (conv_backward.cu).
 bool cb200_conv_forward_f32_uses_tma(const cb200_stream* s, int batch, int cin, int in_h, int in_w, int cout, int out_h,
                                      int out_w, int kh, int kw, int stride_x, int stride_y) {
   const long long in_elems = (long long)batch * cin * in_h * in_w;
-  if (s->opt_conv_route == 0 && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
+  if ((s->opt_conv_route == 0 || s->opt_conv_route == 3) && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
     return true;
   return s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, out_w, out_h, stride_x, stride_y, in_elems);
 }
@@ -58,7 +58,7 @@ int cb200_conv_forward_f32(cb200_stream* s, float* out, const float* in, const f
                            int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y, int stride_x,
                            int stride_y, float out_alpha) {
   const long long in_elems = (long long)batch * cin * in_h * in_w;
-  if (s->opt_conv_route == 0 && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
+  if ((s->opt_conv_route == 0 || s->opt_conv_route == 3) && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
     return cb200_conv_halo_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha);
   if (s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, out_w, out_h, stride_x, stride_y, in_elems))
     return cb200_conv_tma_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha);

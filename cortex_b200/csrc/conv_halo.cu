@@ -64,6 +64,14 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const void* tmap, int 
       : "memory");
 }
 
+// 4-d tiled load {x, y, c, n} of an NCHW tensor; x must be a multiple of 4 elements
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"((uint64_t)tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+
 // in [N][C][HW]  ->  hi / lo [N][C/4][HW][4]: thread = (image, channel quad, pixel); reads of a warp are 128
 // contiguous bytes per channel, its writes 512 contiguous bytes
 __global__ void __launch_bounds__(256)
@@ -332,6 +340,284 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------------------
+// The same kernel fed from the NCHW input directly: no pre-pass over the activations.
+//
+// One TMA box {raw_w, patch_h, 16 channels, 1 image} of the caller's tensor (out-of-image coordinates zero-filled:
+// the padding) lands in a raw staging buffer as [channel][y][x]; four CONVERT warps re-lay it as the
+// [channel quad][y][x][4] hi patch and its lo patch (x - trunc_tf32(x)) in shared memory -- 12 loads and 6 16-byte
+// stores per thread and channel block -- issue a generic->async proxy fence and signal the patch as full.  The box
+// starts at an x that is a multiple of 4 elements (a TMA box must start on a 16-byte boundary): x_lead = pad_x
+// rounded up to 4 columns left of the tile, and the convert step skips x_lead - pad_x columns.
+// Warps: 0-3 epilogue (32 rows x BN columns each), 4-7 convert, 8 raw-patch producer, 9 MMA issuer / TMEM owner,
+// 11 W producer.  Everything downstream of the patch (descriptors, MMAs, accumulators, epilogue) is as above.
+struct DirectExtra {
+  int raw_w, raw_bytes, raw_stages, x_lead;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(H_THREADS, 2)
+conv_halo_direct_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
+                        const __grid_constant__ CUtensorMap tmWlo, HaloParams p, DirectExtra x) {
+  constexpr int B_TILE = BN * HBK * 4;
+  constexpr int W_STAGE = 2 * B_TILE;
+  constexpr int MAX_RING = 8;
+  constexpr int D_EPI_WARPS = 4, D_CONV_WARPS = 4;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t patch_pair = 2u * (uint32_t)p.patch_bytes;
+  const uint32_t raw_base_off = ((uint32_t)p.n_patches * patch_pair + 127u) & ~127u;
+  const uint32_t w_base_off = (raw_base_off + (uint32_t)x.raw_stages * (uint32_t)x.raw_bytes + 1023u) & ~1023u;
+  uint64_t* bars = (uint64_t*)(smem + w_base_off + (uint32_t)p.w_stages * W_STAGE);
+  // bars: [0..8) patch full, [8..16) patch empty, [16..24) W full, [24..32) W empty, [32..34) accumulators ready,
+  // [34..36) accumulators read out, [36] unwinding only, [37..39) raw full, [39..41) raw empty
+  uint32_t* tmem_slot = (uint32_t*)(bars + 41);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (p.cout + BN - 1) / BN;
+  const int per_img = p.tiles_x * p.tiles_y;
+  const int n_tiles = p.batch * per_img * tiles_n;
+  const int khkw = p.kh * p.kw;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t bar_pfull = bar0, bar_pempty = bar0 + 8 * MAX_RING, bar_wfull = bar0 + 16 * MAX_RING,
+                 bar_wempty = bar0 + 24 * MAX_RING, bar_acc_full = bar0 + 32 * MAX_RING, bar_acc_empty = bar_acc_full + 16,
+                 bar_retired = bar_acc_full + 32, bar_rfull = bar_retired + 8, bar_rempty = bar_rfull + 16;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < MAX_RING; ++s) {
+      mbar_init(bar_pfull + 8 * s, D_CONV_WARPS);
+      mbar_init(bar_pempty + 8 * s, 1);
+      mbar_init(bar_wfull + 8 * s, 1);
+      mbar_init(bar_wempty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, D_EPI_WARPS);
+      mbar_init(bar_rfull + 8 * b, 1);
+      mbar_init(bar_rempty + 8 * b, D_CONV_WARPS);
+    }
+    mbar_init(bar_retired, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(tmem_slot), 4 * BN);
+    tmem_relinquish();
+  }
+  if (lane == 0) {
+    if (warp == 8) tma_prefetch_desc(&tmIn);
+    if (warp == 11) { tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmWlo); }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    // ---------------- raw-patch producer: one box per (tile, channel block) ----------------
+    long long issued = 0;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+      const int tm = tile / tiles_n;
+      const int img = tm / per_img, rem = tm - img * per_img;
+      const int y0 = (rem / p.tiles_x) * HBY - p.pad_y, x0 = (rem % p.tiles_x) * HBX - x.x_lead;
+      for (int cb = 0; cb < p.ncb; ++cb) {
+        if (!mbar_wait(bar_rempty + 8 * s, ph ^ 1, abort_flag, p.status, 3400 + s)) { ok = false; break; }
+        const uint32_t full = bar_rfull + 8 * s;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(full, (uint32_t)(16 * p.patch_h * x.raw_w * 4));
+          tma_load_4d(smem_base + raw_base_off + s * x.raw_bytes, &tmIn, x0, y0, cb * 16, img, full);
+        }
+        __syncwarp();
+        ++issued;
+        if (++s == x.raw_stages) { s = 0; ph ^= 1; }
+      }
+    }
+    if (*abort_flag) {
+      for (long long i = issued > x.raw_stages ? issued - x.raw_stages : 0; i < issued; ++i)
+        for (int it = 0; it < (1 << 16); ++it)
+          if (mbar_try_wait(bar_rfull + 8 * (int)(i % x.raw_stages), (uint32_t)((i / x.raw_stages) & 1))) break;
+    }
+  } else if (warp >= D_EPI_WARPS && warp < D_EPI_WARPS + D_CONV_WARPS) {
+    // ---------------- convert warps: raw [c][y][x] -> hi / lo [c/4][y][x][4] ----------------
+    const int ct = (warp - D_EPI_WARPS) * 32 + lane;              // 0 .. 127
+    const int plane_px = p.patch_h * p.patch_w;                    // pixels per channel quad
+    const int n_px = 4 * plane_px;
+    const int raw_plane = p.patch_h * x.raw_w;                     // floats per channel in the raw buffer
+    const int x_skip = x.x_lead - p.pad_x;
+    int rs = 0, ps = 0;
+    uint32_t rph = 0, pph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+      for (int cb = 0; cb < p.ncb; ++cb) {
+        ok = mbar_wait(bar_rfull + 8 * rs, rph, abort_flag, p.status, 3500 + rs) &&
+             mbar_wait(bar_pempty + 8 * ps, pph ^ 1, abort_flag, p.status, 3550 + ps);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float* raw = reinterpret_cast<const float*>(smem + raw_base_off + rs * x.raw_bytes);
+        float4* hi = reinterpret_cast<float4*>(smem + ps * patch_pair);
+        float4* lo = reinterpret_cast<float4*>(smem + ps * patch_pair + p.patch_bytes);
+        for (int i = ct; i < n_px; i += D_CONV_WARPS * 32) {
+          const int q = i / plane_px, r = i - q * plane_px;
+          const int y = r / p.patch_w, px = r - y * p.patch_w;
+          const float* src = raw + (4 * q) * raw_plane + y * x.raw_w + px + x_skip;
+          const float a = src[0], b = src[raw_plane], c = src[2 * raw_plane], d = src[3 * raw_plane];
+          hi[i] = make_float4(a, b, c, d);
+          lo[i] = make_float4(hconv_lo_part(a), hconv_lo_part(b), hconv_lo_part(c), hconv_lo_part(d));
+        }
+        fence_proxy_async_smem();         // these generic-proxy stores -> visible to the tensor core's reads
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar_pfull + 8 * ps);
+          mbar_arrive(bar_rempty + 8 * rs);
+        }
+        if (++rs == x.raw_stages) { rs = 0; rph ^= 1; }
+        if (++ps == p.n_patches) { ps = 0; pph ^= 1; }
+      }
+    }
+  } else if (warp == 11) {
+    // ---------------- W producer: hi and lo tiles, one pair per (channel block, tap) ----------------
+    long long issued = 0;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    const int nkb = p.ncb * khkw;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+      const int n0 = (tile % tiles_n) * BN;
+      for (int i = 0; i < nkb; ++i) {
+        if (!mbar_wait(bar_wempty + 8 * s, ph ^ 1, abort_flag, p.status, 3600 + s)) { ok = false; break; }
+        const uint32_t full = bar_wfull + 8 * s;
+        const uint32_t dst = smem_base + w_base_off + s * W_STAGE;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(full, W_STAGE);
+          tma_load_2d(dst, &tmW, i * HBK, n0, full);
+          tma_load_2d(dst + B_TILE, &tmWlo, i * HBK, n0, full);
+        }
+        __syncwarp();
+        ++issued;
+        if (++s == p.w_stages) { s = 0; ph ^= 1; }
+      }
+    }
+    if (*abort_flag) {
+      for (long long i = issued > p.w_stages ? issued - p.w_stages : 0; i < issued; ++i)
+        for (int it = 0; it < (1 << 16); ++it)
+          if (mbar_try_wait(bar_wfull + 8 * (int)(i % p.w_stages), (uint32_t)((i / p.w_stages) & 1))) break;
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+    const uint32_t idesc = make_idesc_tf32(128, BN, 0, 0);
+    const uint32_t idesc_wide = make_idesc_tf32(128, 2 * BN, 0, 0);
+    const uint32_t line = (uint32_t)p.patch_w * 16u, plane = (uint32_t)p.patch_h * line;
+    const uint64_t d_a = make_smem_desc(smem_base, plane, line, 0);
+    const uint64_t d_b = make_smem_desc(smem_base + w_base_off, 16, 8 * HBK * 4, SWZ_64B);
+    const uint32_t a_hiw = (uint32_t)(d_a >> 32), b_hiw = (uint32_t)(d_b >> 32);
+    const uint32_t a_low0 = (uint32_t)d_a, b_low0 = (uint32_t)d_b;
+    const uint32_t a_lo_off = (uint32_t)p.patch_bytes >> 4, a_kstep = (2u * plane) >> 4, pair_step = patch_pair >> 4;
+    int ps = 0, ws = 0;
+    uint32_t pph = 0, wph = 0;
+    bool ok = true;
+    int local = 0;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      if (!mbar_wait(bar_acc_empty + 8 * buf, ((local >> 1) & 1) ^ 1, abort_flag, p.status, 3650)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tmem_main = tmem_base + buf * 2 * BN, tmem_cross = tmem_main + BN;
+      uint32_t accumulate = 0;
+      for (int cb = 0; ok && cb < p.ncb; ++cb) {
+        if (!mbar_wait(bar_pfull + 8 * ps, pph, abort_flag, p.status, 3700 + ps)) { ok = false; break; }
+        const uint32_t a_patch = a_low0 + (uint32_t)ps * pair_step;
+        int ky = 0, kx = 0;
+        for (int t = 0; t < khkw; ++t) {
+          if (!mbar_wait(bar_wfull + 8 * ws, wph, abort_flag, p.status, 3750 + ws)) { ok = false; break; }
+          tc_fence_after();
+          if (elect_one()) {
+            const uint32_t a_tap = a_patch + (uint32_t)(ky * p.patch_w + kx);     // 16 bytes per pixel = 1 unit
+            const uint32_t b_st = b_low0 + (uint32_t)ws * (W_STAGE >> 4);
+#pragma unroll
+            for (int kk = 0; kk < HBK / 8; ++kk) {
+              const uint32_t al = a_tap + kk * a_kstep, bl = b_st + kk * 2;
+              mma_tf32_ss_words(tmem_main, al, a_hiw, bl, b_hiw, idesc_wide, kk ? 1u : accumulate);
+              mma_tf32_ss_words(tmem_cross, al + a_lo_off, a_hiw, bl, b_hiw, idesc, 1);
+            }
+            mma_commit(bar_wempty + 8 * ws);
+            if (t == khkw - 1) mma_commit(bar_pempty + 8 * ps);       // the patch is free once its last tap retires
+          }
+          accumulate = 1;
+          __syncwarp();
+          if (++kx == p.kw) { kx = 0; ++ky; }
+          if (++ws == p.w_stages) { ws = 0; wph ^= 1; }
+        }
+        if (++ps == p.n_patches) { ps = 0; pph ^= 1; }
+      }
+      if (!ok) break;
+      if (elect_one()) mma_commit(bar_acc_full + 8 * buf);
+      __syncwarp();
+    }
+    if (*abort_flag) {
+      if (elect_one()) mma_commit(bar_retired);
+      __syncwarp();
+      for (int it = 0; it < (1 << 20); ++it)
+        if (mbar_try_wait(bar_retired, 0)) break;
+    }
+  } else if (warp < D_EPI_WARPS) {
+    // ---------------- epilogue (warps 0-3): accumulators -> registers -> NCHW ----------------
+    const int row = warp * 32 + lane;                   // tile row = TMEM lane: y line row / 8, column row % 8
+    const int ly = row >> 3, lx = row & 7;
+    const long long hw = (long long)p.out_h * p.out_w;
+    bool ok = true;
+    int local = 0;
+    for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      ok = mbar_wait(bar_acc_full + 8 * buf, (local >> 1) & 1, abort_flag, p.status, 3800);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tbase = tmem_base + (uint32_t)(buf * 2 * BN) + ((uint32_t)(warp * 32) << 16);
+      const int tm = tile / tiles_n, n0 = (tile % tiles_n) * BN;
+      const int img = tm / per_img, rem = tm - img * per_img;
+      const int oy = (rem / p.tiles_x) * HBY + ly, ox = (rem % p.tiles_x) * HBX + lx;
+      const bool inside = oy < p.out_h && ox < p.out_w;
+      float* obase = p.out + (long long)img * p.cout * hw + (long long)oy * p.out_w + ox;
+      // 32 columns at a time (the buffer is released after the last chunk: the tile after next needs it only a
+      // whole tile of MMAs later)
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        uint32_t r[32], rc[32];
+        tmem_ld_32x32(tbase + cc * 32, r);
+        tmem_ld_32x32(tbase + BN + cc * 32, rc);
+        tmem_ld_wait();
+        if (inside) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = n0 + cc * 32 + j;
+            if (n < p.cout) {
+              float* cp = obase + (long long)n * hw;
+              float o = __uint_as_float(r[j]) + __uint_as_float(rc[j]);
+              if (p.out_alpha != 0.f) o += p.out_alpha * (*cp);
+              *cp = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 4 * BN);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -421,6 +707,70 @@ int launch_halo(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmAl
   return CB200_OK;
 }
 
+// NCHW input as the 4-d tensor {W, H, C, N}; box {raw_w, patch_h, 16, 1}, no swizzle, zero fill outside
+int encode_nchw(CUtensorMap* tm, const float* base, int W, int H, int C, int N, int raw_w, int patch_h) {
+  EncodeTiledFn fn = hconv_encode_fn();
+  if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
+  cuuint64_t gdim[4] = {(cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C, (cuuint64_t)N};
+  cuuint64_t gstride[3] = {(cuuint64_t)W * 4, (cuuint64_t)H * W * 4, (cuuint64_t)C * H * W * 4};
+  cuuint32_t box[4] = {(cuuint32_t)raw_w, (cuuint32_t)patch_h, 16, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)base, gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    cb200_set_error("cuTensorMapEncodeTiled failed with %d for the NCHW input (W %d H %d C %d N %d box %dx%d)", (int)r, W,
+                    H, C, N, raw_w, patch_h);
+    return CB200_ERR_CUDA;
+  }
+  return CB200_OK;
+}
+
+// Shared-memory plan of the direct kernel (64-channel tiles, two CTAs per SM): two patch pairs, one or two raw
+// staging buffers, the W ring as deep as fits (>= 3 stages).
+bool direct_plan(int kh, int kw, int pad_x, HaloParams* p, DirectExtra* x, int* smem_bytes) {
+  const int pw = HBX + kw - 1, ph = HBY + kh - 1;
+  if (pw > 256 || ph > 256) return false;
+  const int pb = (4 * ph * pw * 16 + 127) & ~127;
+  const int x_lead = (pad_x + 3) & ~3;
+  const int raw_w = (x_lead + HBX + kw - 1 - pad_x + 3) & ~3;
+  if (raw_w > 256 || kw - 1 - pad_x < 0) return false;
+  const int raw_bytes = (16 * ph * raw_w * 4 + 127) & ~127;
+  const int w_stage = 2 * 64 * HBK * 4;
+  const int budget = 112 * 1024 - 2048;
+  auto total = [&](int rs, int ws) {
+    const int patches = (2 * 2 * pb + 127) & ~127;
+    return ((patches + rs * raw_bytes + 1023) & ~1023) + ws * w_stage + 1024 + 512;
+  };
+  int rs = 2, ws = 8;
+  while (total(rs, ws) > budget && ws > 6) --ws;
+  if (total(rs, ws) > budget) { rs = 1; ws = 8; while (total(rs, ws) > budget && ws > 3) --ws; }
+  if (total(rs, ws) > budget) return false;
+  p->patch_bytes = pb; p->n_patches = 2; p->w_stages = ws;
+  x->raw_w = raw_w; x->raw_bytes = raw_bytes; x->raw_stages = rs; x->x_lead = x_lead;
+  *smem_bytes = total(rs, ws);
+  return true;
+}
+
+int launch_direct(cb200_stream* s, const CUtensorMap& tmIn, const CUtensorMap& tmW, const CUtensorMap& tmWlo,
+                  const HaloParams& p, const DirectExtra& x, int smem_bytes, long long tiles) {
+  static std::mutex mu;
+  static int configured[64] = {0};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!configured[s->device & 63]) {
+      cudaError_t e = cudaFuncSetAttribute(conv_halo_direct_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+      if (e != cudaSuccess) return cb200_cuda_fail(e, "cudaFuncSetAttribute", __FILE__, __LINE__);
+      configured[s->device & 63] = 1;
+    }
+  }
+  const long long slots = (long long)s->sm_count * 2;
+  const long long grid = tiles < slots ? tiles : slots;
+  conv_halo_direct_kernel<64><<<(unsigned)grid, H_THREADS, smem_bytes, s->stream>>>(tmIn, tmW, tmWlo, p, x);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
 }  // namespace
 
 // Eligible: stride 1, a filter wider than one tap, C_in a multiple of 16, the 8 x 16 tiles cover the output with
@@ -448,11 +798,33 @@ int cb200_conv_halo_launch(cb200_stream* s, float* out, const float* in, const f
   p.patch_w = HBX + kw - 1;
   p.patch_h = HBY + kh - 1;
   int smem_bytes = 0;
+  const int K = cin * kh * kw;
+  // C_out <= 64, rows of the input 16-byte aligned: the kernel that reads the caller's NCHW tensor itself (no
+  // pre-pass over the activations; only the weights are re-laid, 2 x C_out x K floats of the stream's workspace)
+  DirectExtra dx;
+  if (BN == 64 && (in_w % 4) == 0 && (((uintptr_t)in) & 15) == 0 && s->opt_conv_route != 3 &&
+      direct_plan(kh, kw, pad_x, &p, &dx, &smem_bytes)) {
+    const size_t w_elems = (size_t)cout * K;
+    void* scratch = nullptr;
+    int rc = cb200_scratch(s, 2 * w_elems * sizeof(float), &scratch);
+    if (rc) return rc;
+    float* w_hi = (float*)scratch;
+    float* w_lo = w_hi + w_elems;
+    int blocks = (int)((w_elems + 255) / 256);
+    if (blocks > s->sm_count * 8) blocks = s->sm_count * 8;
+    hconv_prep_weights_kernel<<<blocks, 256, 0, s->stream>>>(w, w_hi, w_lo, cout, cin, kh * kw);
+    CB_LAUNCH_CHECK(s);
+    CUtensorMap tmIn, tmW, tmWlo;
+    if ((rc = encode_nchw(&tmIn, in, in_w, in_h, cin, batch, dx.raw_w, p.patch_h))) return rc;
+    if ((rc = encode_hw(&tmW, w_hi, K, cout, BN))) return rc;
+    if ((rc = encode_hw(&tmWlo, w_lo, K, cout, BN))) return rc;
+    const long long tiles = (long long)batch * p.tiles_x * p.tiles_y * ((cout + BN - 1) / BN);
+    return launch_direct(s, tmIn, tmW, tmWlo, p, dx, smem_bytes, tiles);
+  }
   if (!halo_plan(BN, kh, kw, &p.patch_bytes, &p.n_patches, &p.w_stages, &smem_bytes)) {
     cb200_set_error("convolution: the %dx%d filter's input patch does not fit shared memory", kw, kh);
     return CB200_ERR_INVALID;
   }
-  const int K = cin * kh * kw;
   const size_t in_elems = (size_t)batch * cin * in_h * in_w, w_elems = (size_t)cout * K;
   void* scratch = nullptr;
   int rc = cb200_scratch(s, (2 * in_elems + 2 * w_elems) * sizeof(float), &scratch);

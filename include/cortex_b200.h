@@ -460,7 +460,9 @@ enum cb200_stream_option {
   CB200_OPT_CONV_ROUTE = 5,         /* fp32 convolution-forward!: 0 = by geometry (TMA-fed kernels for stride-1 layers
                                        with a multiple of 16 input channels), 1 = always the thread-gathered kernel,
                                        2 = the TMA kernel that loads one tile per filter tap, never the one that
-                                       keeps the input patch in shared memory */
+                                       keeps the input patch in shared memory, 3 = by geometry, but the patch
+                                       kernel always behind its layout pre-pass (never the variant that reads
+                                       the NCHW input itself) */
   CB200_OPT_GEMM_K_SLICES = 6,      /* fp32 tensor-core gemm! on problems with fewer tiles than half the SMs: CTAs per
                                        tile, each over a slice of K: 0 = by size, 1 = never slice, n <= 16 = n slices
                                        when K has at least 8 k-blocks per slice */

@@ -199,12 +199,13 @@ def test_conv_tma_fed_kernels(b200_driver, oracle_driver, args):
     accept).  Against the oracle, float64, and the thread-gathered kernel (route 1), which sums in the same
     k order."""
     run, ref = pc.conv_case("float", bias_scale=0.1, **args)
-    by_geometry = _on(b200_driver, "float", run)
+    by_geometry = _on(b200_driver, "float", run)                       # reads the NCHW input itself where it can
+    behind_prepass = _on(b200_driver, "float", run, {"conv-route": 3}) # the patch kernel behind its layout pre-pass
     per_tap = _on(b200_driver, "float", run, {"conv-route": 2})
     gathered = _on(b200_driver, "float", run, {"conv-route": 1})
     cpu = _on(oracle_driver, "float", run)
     want = ref()
-    for got in (by_geometry, per_tap):
+    for got in (by_geometry, behind_prepass, per_tap):
         assert pc.rel_err(got, cpu) <= pc.TOL["float"]
         assert pc.rel_err(got, want) <= pc.TOL["float"]
         assert pc.rel_err(got, gathered) <= 2e-5
