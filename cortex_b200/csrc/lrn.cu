@@ -20,15 +20,17 @@ struct LrnGeom {
   double k, alpha_over_n, beta;
 };
 
-__device__ __forceinline__ float lrn_pow(float s, float e) { return powf(s, e); }
+// s > 0 (k + a sum of squares): 2^(e * log2 s) with the hardware log2 / exp2 (relative error ~1e-6 for |e| <= 1)
+__device__ __forceinline__ float lrn_pow(float s, float e) { return exp2f(e * __log2f(s)); }
 __device__ __forceinline__ double lrn_pow(double s, double e) { return pow(s, e); }
 
+// `col` points at channel 0 of the element's (batch entry, pixel) column; channels are `plane` elements apart
 template <typename T>
-__device__ __forceinline__ T lrn_scale(const T* x, const LrnGeom& g, long long b, int c, long long p) {
+__device__ __forceinline__ T lrn_scale(const T* col, const LrnGeom& g, unsigned plane, int c) {
   const int c0 = max(0, c - g.look_behind), c1 = min(g.channels - 1, c + g.look_ahead);
   T sum = (T)0;
   for (int j = c0; j <= c1; ++j) {
-    const T v = x[(b * g.channels + j) * g.plane + p];
+    const T v = col[(unsigned)j * plane];
     sum += v * v;
   }
   return (T)g.k + (T)g.alpha_over_n * sum;
@@ -42,10 +44,11 @@ lrn_forward_kernel(T* out, T* scale_out, const T* in, LrnGeom g, long long n_ele
     // 32-bit index arithmetic (the entry points limit a tensor to 2^32 - 1 elements)
     const unsigned iu = (unsigned)i, plane_u = (unsigned)g.plane;
     const unsigned bc = iu / plane_u;
-    const long long p = iu - bc * plane_u;
-    const long long b = bc / (unsigned)g.channels;
-    const int c = (int)(bc - (unsigned)b * (unsigned)g.channels);
-    const T s = lrn_scale(in, g, b, c, p);
+    const unsigned p = iu - bc * plane_u;
+    const unsigned b = bc / (unsigned)g.channels;
+    const int c = (int)(bc - b * (unsigned)g.channels);
+    const unsigned col0 = b * (unsigned)g.channels * plane_u + p;      // channel 0 of this element's column
+    const T s = lrn_scale(in + col0, g, plane_u, c);
     if (WRITE_SCALE) scale_out[i] = s;
     else out[i] = in[i] * lrn_pow(s, (T)-g.beta);
   }
@@ -59,13 +62,14 @@ lrn_backward_kernel(T* in_grad, const T* out, const T* in, const T* out_grad, co
     // 32-bit index arithmetic (the entry points limit a tensor to 2^32 - 1 elements)
     const unsigned iu = (unsigned)i, plane_u = (unsigned)g.plane;
     const unsigned bc = iu / plane_u;
-    const long long p = iu - bc * plane_u;
-    const long long b = bc / (unsigned)g.channels;
-    const int c = (int)(bc - (unsigned)b * (unsigned)g.channels);
+    const unsigned p = iu - bc * plane_u;
+    const unsigned b = bc / (unsigned)g.channels;
+    const int c = (int)(bc - b * (unsigned)g.channels);
+    const unsigned col0 = b * (unsigned)g.channels * plane_u + p;      // channel 0 of this element's column
     const int c0 = max(0, c - g.look_behind), c1 = min(g.channels - 1, c + g.look_ahead);
     T sum = (T)0;
     for (int j = c0; j <= c1; ++j) {
-      const long long o = (b * g.channels + j) * g.plane + p;
+      const unsigned o = col0 + (unsigned)j * plane_u;
       sum += out_grad[o] * out[o] / scale[o];
     }
     const T direct = out_grad[i] * lrn_pow(scale[i], (T)-g.beta);

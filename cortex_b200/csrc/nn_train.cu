@@ -100,6 +100,68 @@ pooling_backward_kernel(T* in_grad, const T* in, const T* out, const T* out_grad
   }
 }
 
+// Square window KS with stride ST known at compile time: an input position lies in at most NW = ceil(KS / ST)
+// windows per dimension, so the candidate windows are a fully unrolled, predicated NW x NW loop (visited in
+// ascending (out-y, out-x) order: the reference's summation order) with 32-bit index arithmetic.
+template <typename T, int OP, int VEC, int KS, int ST>
+__global__ void __launch_bounds__(256)
+pooling_backward_fixed_kernel(T* in_grad, const T* in, const T* out, const T* out_grad, PoolBwdGeom g, long long n_groups,
+                              double in_grad_alpha) {
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
+  constexpr int NW = (KS + ST - 1) / ST;
+  const unsigned groups_per_row = (unsigned)(g.in_w / VEC);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_groups; i += (long long)gridDim.x * blockDim.x) {
+    const unsigned iu = (unsigned)i;
+    const unsigned tq = iu / groups_per_row;
+    const int ix0 = (int)(iu - tq * groups_per_row) * VEC;
+    const unsigned plane = tq / (unsigned)g.in_h;
+    const int iy = (int)(tq - plane * (unsigned)g.in_h);
+    const unsigned e0 = (plane * (unsigned)g.in_h + (unsigned)iy) * (unsigned)g.in_w + (unsigned)ix0;
+    const unsigned out_base = plane * (unsigned)(g.out_h * g.out_w);
+    const int oyh = (iy + g.pad_y) / ST;
+    Pack x, acc;
+    if (OP == CB200_POOL_MAX) x = *reinterpret_cast<const Pack*>(in + e0);
+    if (in_grad_alpha == 0.0) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc.v[e] = (T)0;
+    } else {
+      acc = *reinterpret_cast<const Pack*>(in_grad + e0);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc.v[e] = (T)(in_grad_alpha * (double)acc.v[e]);
+    }
+#pragma unroll
+    for (int dy = NW - 1; dy >= 0; --dy) {
+      const int oy = oyh - dy;
+      const int rel_y = oy * ST - g.pad_y;
+      const bool ok_y = oy >= 0 && oy < g.out_h && iy - rel_y < KS;
+      const int exc_h = min(rel_y + KS, g.in_h) - max(rel_y, 0);
+      const unsigned row_base = out_base + (unsigned)(oy * g.out_w);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const int ix = ix0 + e;
+        const int oxh = (ix + g.pad_x) / ST;
+#pragma unroll
+        for (int dx = NW - 1; dx >= 0; --dx) {
+          const int ox = oxh - dx;
+          const int rel_x = ox * ST - g.pad_x;
+          if (ok_y && ox >= 0 && ox < g.out_w && ix - rel_x < KS) {
+            const unsigned o = row_base + (unsigned)ox;
+            if (OP == CB200_POOL_MAX) {
+              if (x.v[e] == out[o]) acc.v[e] = acc.v[e] + out_grad[o];
+            } else if (OP == CB200_POOL_AVG) {
+              acc.v[e] = (T)((double)acc.v[e] + (double)out_grad[o] / (double)(KS * KS));
+            } else {
+              const int exc_w = min(rel_x + KS, g.in_w) - max(rel_x, 0);
+              acc.v[e] = (T)((double)acc.v[e] + (double)out_grad[o] / (double)(exc_w * exc_h));
+            }
+          }
+        }
+      }
+    }
+    *reinterpret_cast<Pack*>(in_grad + e0) = acc;
+  }
+}
+
 template <typename T, int VEC, int KS, int ST>
 void pooling_backward_launch_v(cb200_stream* s, int op, T* in_grad, const T* in, const T* out, const T* out_grad,
                                const PoolBwdGeom& g, long long n_in, double alpha) {
@@ -108,6 +170,15 @@ void pooling_backward_launch_v(cb200_stream* s, int op, T* in_grad, const T* in,
   const long long cap = (long long)s->sm_count * 32;
   if (blocks > cap) blocks = cap;
   const unsigned b = (unsigned)blocks;
+  if (KS > 0) {
+    if (op == CB200_POOL_MAX)
+      pooling_backward_fixed_kernel<T, CB200_POOL_MAX, VEC, (KS > 0 ? KS : 1), (ST > 0 ? ST : 1)><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+    else if (op == CB200_POOL_AVG)
+      pooling_backward_fixed_kernel<T, CB200_POOL_AVG, VEC, (KS > 0 ? KS : 1), (ST > 0 ? ST : 1)><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+    else
+      pooling_backward_fixed_kernel<T, CB200_POOL_AVG_EXC_PAD, VEC, (KS > 0 ? KS : 1), (ST > 0 ? ST : 1)><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+    return;
+  }
   if (op == CB200_POOL_MAX)
     pooling_backward_kernel<T, CB200_POOL_MAX, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
   else if (op == CB200_POOL_AVG)
