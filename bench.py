@@ -579,7 +579,7 @@ def bench_backward(drv, dev, peaks):
         ms_cd = time_region(stream, lambda: ct.convolution_backward_data(c_gin, 0.0, cog, cw, None, conv.desc, None), 3)
         res["conv_64x64x56x56"] = {"ms": round(ms_c, 3), "backward_weights_ms": round(ms_cw, 3),
                                    "backward_data_ms": round(ms_cd, 3),
-                                   "note": "weights: unroll + one split-reduction launch; data: transpose + one GEMM over all images + roll; work 2 x 1.48e10 flop"}
+                                   "note": "weights: channel-major gradient + transposed unroll + one tensor-core gemm! NT over all pixels (K-sliced) + transpose-add; data: forward patch convolution of the output gradient with the mirrored filter; work 2 x 1.48e10 flop"}
     return res
 
 

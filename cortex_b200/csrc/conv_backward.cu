@@ -21,6 +21,10 @@ int cb200_gemm_no_workspace(cb200_stream* s, int dtype, void* C, long long ldc, 
                             const void* A, long long a_rows, long long a_cols, long long lda, const void* B,
                             long long b_cols, long long ldb, double beta);
 
+int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
+                             const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
+                             float beta, const float* bias, int act, int store_mode, int hw, int flags);
+bool cb200_gemm_tf32x3_eligible(const float* A, long long lda, const float* B, long long ldb, int M, int N, int K);
 bool cb200_conv_forward_f32_uses_tma(const cb200_stream* s, int batch, int cin, int in_h, int in_w, int cout, int out_h,
                                      int out_w, int kh, int kw, int stride_x, int stride_y);
 int cb200_conv_forward_f32(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
@@ -187,6 +191,57 @@ __global__ void __launch_bounds__(256) nchw_to_pixel_rows_kernel(T* out, const T
   }
 }
 
+// Operands of the weight gradient as ONE K-major product over all pixels of the batch (P = batch * hw, pitch ldp):
+//   ogc[co][n*hw + p]               = out_grad[n, co, p]                       (gradient, channel-major)
+//   ut[c*kh*kw + ky*kw + kx][n*hw + p] = in[n, c, oy*sy - py + ky, ox*sx - px + kx]  (the unrolled input, transposed)
+// so that W_grad[co][k] = sum_P ogc[co][P] * ut[k][P] is a gemm! NT whose reduction runs over P.  Both kernels move
+// whole pixel runs: adjacent threads read and write adjacent addresses.
+// one block per (image, channel) run of hw pixels: a plain copy
+__global__ void __launch_bounds__(256)
+og_rows_copy_kernel(float* __restrict__ ogc, const float* __restrict__ og, int batch, int cout, int hw, long long ldp) {
+  const long long runs = (long long)batch * cout;
+  for (long long r = blockIdx.x; r < runs; r += gridDim.x) {
+    const long long n = r / cout;
+    const int co = (int)(r - n * cout);
+    const float* src = og + r * hw;
+    float* dst = ogc + (long long)co * ldp + n * hw;
+    for (int p = threadIdx.x; p < hw; p += blockDim.x) dst[p] = src[p];
+  }
+}
+
+// one block per (image, k row): threads (x = output column, y = output row): no divisions per element; reads are
+// runs of one input row, writes runs of one output row
+__global__ void __launch_bounds__(256)
+unroll_transposed_kernel(float* __restrict__ ut, const float* __restrict__ in, BwdGeom g, long long ldp) {
+  const int hw = g.out_h * g.out_w, taps = g.kh * g.kw;
+  const int k = blockIdx.x, n = blockIdx.y;
+  const int c = k / taps, t = k - c * taps;
+  const int ky = t / g.kw, kx = t - ky * g.kw;
+  const float* plane = in + ((long long)n * g.cin + c) * g.in_h * g.in_w;
+  float* dst = ut + (long long)k * ldp + (long long)n * hw;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int oy = ty; oy < g.out_h; oy += 8) {
+    const int iy = oy * g.stride_y - g.pad_y + ky;
+    const bool row_in = iy >= 0 && iy < g.in_h;
+    const float* src = plane + (long long)iy * g.in_w;
+    for (int ox = tx; ox < g.out_w; ox += 32) {
+      const int ix = ox * g.stride_x - g.pad_x + kx;
+      dst[oy * g.out_w + ox] = (row_in && ix >= 0 && ix < g.in_w) ? src[ix] : 0.f;
+    }
+  }
+}
+
+// wg[co][k] = alpha * wg[co][k] + wt[k][co]   (the GEMM below produces the gradient transposed)
+__global__ void __launch_bounds__(256)
+wgrad_transpose_add_kernel(float* __restrict__ wg, const float* __restrict__ wt, int cout, int kcols, int ldt, float alpha) {
+  const int total = cout * kcols;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int co = i / kcols, k = i - co * kcols;
+    const float v = wt[(long long)k * ldt + co];
+    wg[i] = alpha == 0.f ? v : alpha * wg[i] + v;
+  }
+}
+
 template <typename T> __global__ void scale_kernel(T* p, T alpha, long long n) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     p[i] = alpha * p[i];
@@ -252,10 +307,43 @@ int cb200_convolution_backward_weights(cb200_stream* s, int dtype, void* w_grad,
     // nothing to add: W_grad = alpha * W_grad is the caller's binary-op!; with no images leave it untouched
     return CB200_OK;
   }
+  DeviceGuard guard(s->device);
+  // fp32 with a reduction long enough to pay: ONE tensor-core gemm! NT over all pixels of the batch,
+  // W_grad[C_out, K] = alpha * W_grad + ogc[C_out, P] . ut[K, P]^T, the reduction sliced over the SMs by the GEMM
+  // itself (few output tiles, tens of thousands of k-blocks).  The sum order over P is fixed: deterministic.
+  if (dtype == CB200_FLOAT && rows >= 4096 && g.kcols <= 65535 && g.batch <= 65535) {
+    const long long ldp = (rows + 3) & ~3LL;
+    const int ldt = (cout + 3) & ~3;
+    void* ws = nullptr;
+    const size_t operand_floats = (size_t)(cout + g.kcols) * ldp;
+    if ((rc = cb200_scratch(s, (operand_floats + (size_t)g.kcols * ldt) * sizeof(float), &ws))) return rc;
+    float* ogc = (float*)ws;
+    float* ut = ogc + (size_t)cout * ldp;
+    float* wt = ut + (size_t)g.kcols * ldp;           // the gradient transposed: [K][C_out]
+    if (ldp != rows) CB_CUDA(cudaMemsetAsync(ws, 0, operand_floats * sizeof(float), s->stream));
+    const long long runs = (long long)g.batch * cout;
+    const long long cap16 = (long long)s->sm_count * 16;
+    og_rows_copy_kernel<<<(unsigned)(runs < cap16 ? runs : cap16), 256, 0, s->stream>>>(ogc, (const float*)out_grad, g.batch,
+                                                                                         cout, hw, ldp);
+    CB_LAUNCH_CHECK(s);
+    unroll_transposed_kernel<<<dim3((unsigned)g.kcols, (unsigned)g.batch, 1), 256, 0, s->stream>>>(ut, (const float*)in, g, ldp);
+    CB_LAUNCH_CHECK(s);
+    // computed transposed, wt[K, C_out] = ut . ogc^T: the long dimension (K = C_in*kH*kW rows) fills the 128-row
+    // tiles, C_out is one narrow column tile
+    if (cb200_gemm_tf32x3_eligible(ut, ldp, ogc, ldp, g.kcols, cout, (int)rows)) {
+      rc = cb200_gemm_tf32x3_launch(s, wt, ldt, 0, 1, 1.0f, ut, g.kcols, (int)rows, ldp, ogc, cout, ldp, 0.f, nullptr, 0, 0,
+                                    1, 0);
+      if (rc) return rc;
+      const int n_out = cout * g.kcols;
+      wgrad_transpose_add_kernel<<<(n_out + 255) / 256, 256, 0, s->stream>>>((float*)w_grad, wt, cout, g.kcols, ldt,
+                                                                            (float)w_grad_alpha);
+      CB_LAUNCH_CHECK(s);
+      return CB200_OK;
+    }
+  }
   const long long total = rows * g.ld;
   void* cols = nullptr;
   if ((rc = cb200_scratch(s, (size_t)total * es, &cols))) return rc;
-  DeviceGuard guard(s->device);
   const long long cap = (long long)s->sm_count * 32;
   const long long blocks = rows < cap ? rows : cap;
   if (dtype == CB200_FLOAT)

@@ -447,7 +447,9 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   // Measured (us per call, old rule "narrow until every SM has a tile" -> this rule): 4096x512x4096 232 -> 108,
   // 2048x1024x4096 220 -> 107, 8192x250x4096 293 -> 204, 8192x125x4096 159 -> 132, 1024x4096x1024 84 -> 60,
   // 512x512x2048 58 -> 29.
-  const bool big_a = (long long)M * K * 4 >= (24ll << 20);
+  // (when B is the larger operand, as in a weight gradient whose reduction runs over every pixel of a batch, the
+  // re-reads of A are the smaller cost and narrow tiles are what spreads the work)
+  const bool big_a = (long long)M * K * 4 >= (24ll << 20) && (long long)M >= (long long)N;
   while (BN > 64 && !big_a && tiles_m * ((N + BN / 2 - 1) / (BN / 2)) <= s->sm_count) BN >>= 1;
   const int tiles_n = (N + BN - 1) / BN;
   const long long panel_bytes = (long long)BN * K * 4;          // one column tile's share of B
@@ -477,6 +479,13 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
     if (sl > nkb_all / 8) sl = nkb_all / 8;
     if (sl > 1024 / BN) sl = 1024 / BN;       // the CTA that combines a tile reads slices x 128 x BN floats
     if (sl > 16) sl = 16;
+    // reductions so long that even 16 slices are hundreds of k-blocks each (a weight gradient summed over every
+    // pixel of a batch): the hand-over is amortised, fill the SMs
+    if (s->opt_gemm_k_slices == 0 && nkb_all / 32 >= 256) {
+      long long fill = s->sm_count / (tiles > 0 ? tiles : 1);
+      if (fill > 32) fill = 32;
+      if (fill > sl) sl = fill;
+    }
     if (p.k_split == 1 && sl >= 2 && !(flags & FLAG_ONE_TERM)) {
       void* ws = nullptr;
       int rcs = cb200_partials(s, (size_t)tiles * sl * BM * BN * sizeof(float), &ws);

@@ -158,7 +158,11 @@ def test_conv_backward_matches_oracle(b200_driver, oracle_driver, datatype):
                  # stride 1 and a multiple of 16 output channels: the fp32 data gradient runs as a forward
                  # convolution of the output gradient (mirrored filter, padding k - 1 - pad) on the TMA-fed kernels
                  dict(batch=2, cin=24, hw=16, cout=32, k=3, pad=1), dict(batch=3, cin=8, hw=20, cout=16, k=5, pad=2),
-                 dict(batch=2, cin=16, hw=12, cout=16, k=3, pad=0), dict(batch=2, cin=40, hw=32, cout=48, k=1, pad=0)):
+                 dict(batch=2, cin=16, hw=12, cout=16, k=3, pad=0), dict(batch=2, cin=40, hw=32, cout=48, k=1, pad=0),
+                 # 4096 and more pixels in the batch: the fp32 weight gradient is one tensor-core gemm! over all
+                 # pixels (gradient made channel-major, input unrolled transposed), its reduction sliced over the SMs
+                 dict(batch=8, cin=16, hw=32, cout=24, k=3, pad=1), dict(batch=5, cin=6, hw=31, cout=70, k=5, pad=2, stride=1),
+                 dict(batch=16, cin=8, hw=36, cout=12, k=3, pad=1, stride=2)):
         run, ref = pc.conv_backward_case(datatype, **args)
         gpu, cpu = _on(b200_driver, datatype, run), _on(oracle_driver, datatype, run)
         assert pc.rel_err(gpu, cpu) <= pc.TOL[datatype], args
