@@ -209,8 +209,10 @@ og_rows_copy_kernel(float* __restrict__ ogc, const float* __restrict__ og, int b
   }
 }
 
-// one block per (image, k row): threads (x = output column, y = output row): no divisions per element; reads are
-// runs of one input row, writes runs of one output row
+// one block per (image, k row).  VEC4: four consecutive output columns per thread and one 16-byte store (out_w a
+// multiple of 4, so that a group never straddles two output rows and every store is aligned); else one column per
+// thread.  Reads are runs of one input row, writes runs of one output row.
+template <bool VEC4>
 __global__ void __launch_bounds__(256)
 unroll_transposed_kernel(float* __restrict__ ut, const float* __restrict__ in, BwdGeom g, long long ldp) {
   const int hw = g.out_h * g.out_w, taps = g.kh * g.kw;
@@ -219,14 +221,31 @@ unroll_transposed_kernel(float* __restrict__ ut, const float* __restrict__ in, B
   const int ky = t / g.kw, kx = t - ky * g.kw;
   const float* plane = in + ((long long)n * g.cin + c) * g.in_h * g.in_w;
   float* dst = ut + (long long)k * ldp + (long long)n * hw;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  for (int oy = ty; oy < g.out_h; oy += 8) {
-    const int iy = oy * g.stride_y - g.pad_y + ky;
-    const bool row_in = iy >= 0 && iy < g.in_h;
-    const float* src = plane + (long long)iy * g.in_w;
-    for (int ox = tx; ox < g.out_w; ox += 32) {
-      const int ix = ox * g.stride_x - g.pad_x + kx;
-      dst[oy * g.out_w + ox] = (row_in && ix >= 0 && ix < g.in_w) ? src[ix] : 0.f;
+  if (VEC4) {
+    const int gpr = g.out_w >> 2, groups = g.out_h * gpr;
+    for (int q = threadIdx.x; q < groups; q += blockDim.x) {
+      const int oy = q / gpr, ox0 = (q - oy * gpr) << 2;
+      const int iy = oy * g.stride_y - g.pad_y + ky;
+      const bool row_in = iy >= 0 && iy < g.in_h;
+      const float* src = plane + (long long)iy * g.in_w;
+      float v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int ix = (ox0 + e) * g.stride_x - g.pad_x + kx;
+        v[e] = (row_in && ix >= 0 && ix < g.in_w) ? src[ix] : 0.f;
+      }
+      *reinterpret_cast<float4*>(dst + (q << 2)) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  } else {
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int oy = ty; oy < g.out_h; oy += 8) {
+      const int iy = oy * g.stride_y - g.pad_y + ky;
+      const bool row_in = iy >= 0 && iy < g.in_h;
+      const float* src = plane + (long long)iy * g.in_w;
+      for (int ox = tx; ox < g.out_w; ox += 32) {
+        const int ix = ox * g.stride_x - g.pad_x + kx;
+        dst[oy * g.out_w + ox] = (row_in && ix >= 0 && ix < g.in_w) ? src[ix] : 0.f;
+      }
     }
   }
 }
@@ -326,7 +345,11 @@ int cb200_convolution_backward_weights(cb200_stream* s, int dtype, void* w_grad,
     og_rows_copy_kernel<<<(unsigned)(runs < cap16 ? runs : cap16), 256, 0, s->stream>>>(ogc, (const float*)out_grad, g.batch,
                                                                                          cout, hw, ldp);
     CB_LAUNCH_CHECK(s);
-    unroll_transposed_kernel<<<dim3((unsigned)g.kcols, (unsigned)g.batch, 1), 256, 0, s->stream>>>(ut, (const float*)in, g, ldp);
+    // 16-byte stores when every image's run of the k row starts aligned (hw % 4 == 0 follows from out_w % 4 == 0)
+    if ((g.out_w % 4) == 0)
+      unroll_transposed_kernel<true><<<dim3((unsigned)g.kcols, (unsigned)g.batch, 1), 256, 0, s->stream>>>(ut, (const float*)in, g, ldp);
+    else
+      unroll_transposed_kernel<false><<<dim3((unsigned)g.kcols, (unsigned)g.batch, 1), 256, 0, s->stream>>>(ut, (const float*)in, g, ldp);
     CB_LAUNCH_CHECK(s);
     // computed transposed, wt[K, C_out] = ut . ogc^T: the long dimension (K = C_in*kH*kW rows) fills the 128-row
     // tiles, C_out is one narrow column tile
