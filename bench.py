@@ -1018,6 +1018,7 @@ def run_b200(args, rank, world, local_rank):
         line["mlp_128x784_500_10"] = extra(lambda: bench_mlp_128(drv, dev))
         line["wide_mlp_fp64"] = extra(lambda: bench_mlp_f64(drv, dev))
         line["mnist_convnet_128"] = extra(lambda: bench_mnist_convnet(drv, dev))
+        line["backward"] = extra(lambda: bench_backward(drv, dev, peaks))
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
