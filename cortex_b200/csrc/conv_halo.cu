@@ -356,7 +356,7 @@ struct DirectExtra {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(H_THREADS, 2)
+__global__ void __launch_bounds__(H_THREADS, (BN <= 64 ? 2 : 1))
 conv_halo_direct_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmW,
                         const __grid_constant__ CUtensorMap tmWlo, HaloParams p, DirectExtra x) {
   constexpr int B_TILE = BN * HBK * 4;
@@ -726,9 +726,9 @@ int encode_nchw(CUtensorMap* tm, const float* base, int W, int H, int C, int N, 
   return CB200_OK;
 }
 
-// Shared-memory plan of the direct kernel (64-channel tiles, two CTAs per SM): two patch pairs, one or two raw
-// staging buffers, the W ring as deep as fits (>= 3 stages).
-bool direct_plan(int kh, int kw, int pad_x, HaloParams* p, DirectExtra* x, int* smem_bytes) {
+// Shared-memory plan of the direct kernel (two CTAs per SM for 64-channel tiles, one for 128-channel tiles): two
+// patch pairs, one or two raw staging buffers, the W ring as deep as fits (>= 3 stages).
+bool direct_plan(int BN, int kh, int kw, int pad_x, HaloParams* p, DirectExtra* x, int* smem_bytes) {
   const int pw = HBX + kw - 1, ph = HBY + kh - 1;
   if (pw > 256 || ph > 256) return false;
   const int pb = (4 * ph * pw * 16 + 127) & ~127;
@@ -736,8 +736,8 @@ bool direct_plan(int kh, int kw, int pad_x, HaloParams* p, DirectExtra* x, int* 
   const int raw_w = (x_lead + HBX + kw - 1 - pad_x + 3) & ~3;
   if (raw_w > 256 || kw - 1 - pad_x < 0) return false;
   const int raw_bytes = (16 * ph * raw_w * 4 + 127) & ~127;
-  const int w_stage = 2 * 64 * HBK * 4;
-  const int budget = 112 * 1024 - 2048;
+  const int w_stage = 2 * BN * HBK * 4;
+  const int budget = (BN <= 64 ? 112 : 224) * 1024 - 2048;
   auto total = [&](int rs, int ws) {
     const int patches = (2 * 2 * pb + 127) & ~127;
     return ((patches + rs * raw_bytes + 1023) & ~1023) + ws * w_stage + 1024 + 512;
@@ -752,6 +752,7 @@ bool direct_plan(int kh, int kw, int pad_x, HaloParams* p, DirectExtra* x, int* 
   return true;
 }
 
+template <int BN>
 int launch_direct(cb200_stream* s, const CUtensorMap& tmIn, const CUtensorMap& tmW, const CUtensorMap& tmWlo,
                   const HaloParams& p, const DirectExtra& x, int smem_bytes, long long tiles) {
   static std::mutex mu;
@@ -759,14 +760,15 @@ int launch_direct(cb200_stream* s, const CUtensorMap& tmIn, const CUtensorMap& t
   {
     std::lock_guard<std::mutex> lock(mu);
     if (!configured[s->device & 63]) {
-      cudaError_t e = cudaFuncSetAttribute(conv_halo_direct_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+      cudaError_t e = cudaFuncSetAttribute(conv_halo_direct_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (BN <= 64 ? 112 : 224) * 1024);
       if (e != cudaSuccess) return cb200_cuda_fail(e, "cudaFuncSetAttribute", __FILE__, __LINE__);
       configured[s->device & 63] = 1;
     }
   }
-  const long long slots = (long long)s->sm_count * 2;
+  const long long slots = (long long)s->sm_count * (BN <= 64 ? 2 : 1);
   const long long grid = tiles < slots ? tiles : slots;
-  conv_halo_direct_kernel<64><<<(unsigned)grid, H_THREADS, smem_bytes, s->stream>>>(tmIn, tmW, tmWlo, p, x);
+  conv_halo_direct_kernel<BN><<<(unsigned)grid, H_THREADS, smem_bytes, s->stream>>>(tmIn, tmW, tmWlo, p, x);
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
@@ -799,11 +801,11 @@ int cb200_conv_halo_launch(cb200_stream* s, float* out, const float* in, const f
   p.patch_h = HBY + kh - 1;
   int smem_bytes = 0;
   const int K = cin * kh * kw;
-  // C_out <= 64, rows of the input 16-byte aligned: the kernel that reads the caller's NCHW tensor itself (no
-  // pre-pass over the activations; only the weights are re-laid, 2 x C_out x K floats of the stream's workspace)
+  // Rows of the input 16-byte aligned: the kernel that reads the caller's NCHW tensor itself (no pre-pass over the
+  // activations; only the weights are re-laid, 2 x C_out x K floats of the stream's workspace)
   DirectExtra dx;
-  if (BN == 64 && (in_w % 4) == 0 && (((uintptr_t)in) & 15) == 0 && s->opt_conv_route != 3 &&
-      direct_plan(kh, kw, pad_x, &p, &dx, &smem_bytes)) {
+  if ((in_w % 4) == 0 && (((uintptr_t)in) & 15) == 0 && s->opt_conv_route != 3 &&
+      direct_plan(BN, kh, kw, pad_x, &p, &dx, &smem_bytes)) {
     const size_t w_elems = (size_t)cout * K;
     void* scratch = nullptr;
     int rc = cb200_scratch(s, 2 * w_elems * sizeof(float), &scratch);
@@ -819,7 +821,8 @@ int cb200_conv_halo_launch(cb200_stream* s, float* out, const float* in, const f
     if ((rc = encode_hw(&tmW, w_hi, K, cout, BN))) return rc;
     if ((rc = encode_hw(&tmWlo, w_lo, K, cout, BN))) return rc;
     const long long tiles = (long long)batch * p.tiles_x * p.tiles_y * ((cout + BN - 1) / BN);
-    return launch_direct(s, tmIn, tmW, tmWlo, p, dx, smem_bytes, tiles);
+    if (BN == 128) return launch_direct<128>(s, tmIn, tmW, tmWlo, p, dx, smem_bytes, tiles);
+    return launch_direct<64>(s, tmIn, tmW, tmWlo, p, dx, smem_bytes, tiles);
   }
   if (!halo_plan(BN, kh, kw, &p.patch_bytes, &p.n_patches, &p.w_stages, &smem_bytes)) {
     cb200_set_error("convolution: the %dx%d filter's input patch does not fit shared memory", kw, kh);
