@@ -228,6 +228,10 @@ class Pooling:
     def forward(self, input, output):
         return ct.pooling_forward(output, 0.0, input, self.desc)
 
+    def backward(self, input, output, input_gradient, output_gradient):
+        """PoolingLayer.backward (compute/nn/layers.clj:400-409): pooling-backward! input-gradient 0.0 ..."""
+        return ct.pooling_backward(input_gradient, 0.0, input, output, output_gradient, self.desc)
+
 
 class BatchNormalization:
     """Inference branch of the BatchNormalization layer: batch-normalize! with the running statistics.
@@ -246,6 +250,33 @@ class BatchNormalization:
         else:
             ct.batch_normalize(output, input, self.means, self.variances, self.scale, self.bias, self.epsilon)
         return output
+
+    # --- training branch (compute/nn/layers.clj:228-262) ----------------------------------------
+    @staticmethod
+    def _view(t):
+        shp = t.shape()
+        return ct.in_place_reshape(t, [shp[0], shp[1], shp[2] * shp[3]]) if len(shp) == 4 else t
+
+    def train_forward(self, input, output, average_factor=0.01):
+        """batch-normalize-update-and-apply!: this batch's statistics normalise the output and are folded into the
+        running means / variances.  The very first batch sets the running statistics to the batch's (factor 1.0), as
+        the reference's local-average-factor atom does; later ones interpolate with `average_factor`."""
+        n = self.means.shape()[0]
+        if getattr(self, "batch_means", None) is None:
+            dt = input.get_datatype()
+            self.batch_means, self.batch_variances = ct.new_tensor([n], datatype=dt), ct.new_tensor([n], datatype=dt)
+            self._factor = 1.0
+        ct.batch_normalize_update_and_apply(self._view(output), self._view(input), self.batch_means, self.batch_variances,
+                                            self.means, self.variances, self._factor, self.scale, self.bias, self.epsilon)
+        self._factor = average_factor
+        return output
+
+    def backward(self, input, output, input_gradient, output_gradient, scale_gradient, bias_gradient):
+        """batch-normalize-gradients! with the statistics train_forward left behind."""
+        ct.batch_normalize_gradients(self._view(input_gradient), scale_gradient, bias_gradient, self._view(output_gradient),
+                                     self._view(output), self._view(input), self.batch_means, self.batch_variances,
+                                     self.scale, self.bias, self.epsilon)
+        return input_gradient
 
 
 class ConvNet(_Replayable):
@@ -297,6 +328,82 @@ class ConvNet(_Replayable):
             else:
                 raise ValueError("unknown layer kind %r" % (kind,))
         return cur
+
+    def train_forward_backward(self, x, output_gradient):
+        """One training pass of the layer list (what cortex.nn.execute drives through ComputeLayer.forward /
+        .backward): batch-norm layers use and update batch statistics, every layer keeps its input and output, and the
+        backward sweep returns the loss gradient with respect to x and a list of per-layer parameter gradients
+        ({"weights": .., "bias": ..} for conv / linear, {"scale": .., "bias": ..} for batch-norm, None otherwise).
+        `output_gradient` is the gradient at the network's output; a trailing softmax passes it through (the layer is
+        paired with the cross-entropy loss, whose gradient is already with respect to the softmax input)."""
+        dt = x.get_datatype()
+        new = lambda shape: ct.new_tensor(list(shape), datatype=dt)
+        acts = [x]                      # acts[i] = input of layer i, acts[i + 1] = its output
+        cur = x
+        for spec in self.layers:
+            kind = spec[0]
+            if kind == "conv":
+                conv = spec[1]
+                batch, _c, h, w = cur.shape()
+                od = ct.get_convolution_output_dimensions(conv.desc, h, w)
+                cur = conv.forward(cur, new([batch, conv.desc["out-channels"], od["output-width"], od["output-height"]]))
+            elif kind == "pool":
+                cur = spec[1].forward(cur, new(spec[1].output_shape(cur.shape())))
+            elif kind == "bn":
+                cur = spec[1].train_forward(cur, new(cur.shape()))
+            elif kind == "relu":
+                cur = relu(cur, new(cur.shape()))
+            elif kind == "flatten":
+                cur = ct.as_batch_matrix(cur)
+            elif kind == "linear":
+                lin, act = spec[1], spec[2]
+                cur = lin.forward(cur, new([cur.shape()[0], lin.weights.shape()[0]]))
+                if act is not None:
+                    _ACTIVATIONS[act](cur, cur)
+            elif kind == "softmax":
+                cur = ct.softmax(new(cur.shape()), cur)
+            else:
+                raise ValueError("unknown layer kind %r" % (kind,))
+            acts.append(cur)
+        grads = [None] * len(self.layers)
+        g_out = output_gradient
+        for idx in range(len(self.layers) - 1, -1, -1):
+            spec, inp, out = self.layers[idx], acts[idx], acts[idx + 1]
+            kind = spec[0]
+            if kind == "softmax":
+                g_in = g_out
+            elif kind == "linear":
+                lin, act = spec[1], spec[2]
+                if act is not None:
+                    g_act = new(out.shape())
+                    ct.activation_gradient(g_act, g_out, out, act)
+                    g_out = g_act
+                g_in = new(inp.shape())
+                wg, bg = new(lin.weights.shape()), new(lin.bias.shape())
+                lin.backward(inp, out, g_in, g_out, wg, bg)
+                grads[idx] = {"weights": wg, "bias": bg}
+            elif kind == "flatten":
+                g_in = ct.in_place_reshape(g_out, inp.shape())
+            elif kind == "relu":
+                g_in = new(inp.shape())
+                ct.activation_gradient(g_in, g_out, out, "relu")
+            elif kind == "bn":
+                bn = spec[1]
+                g_in = new(inp.shape())
+                sg, bg = new(bn.scale.shape()), new(bn.bias.shape())
+                bn.backward(inp, out, g_in, g_out, sg, bg)
+                grads[idx] = {"scale": sg, "bias": bg}
+            elif kind == "pool":
+                g_in = new(inp.shape())
+                spec[1].backward(inp, out, g_in, g_out)
+            elif kind == "conv":
+                conv = spec[1]
+                g_in = new(inp.shape()) if idx > 0 else None
+                wg, bg = new(conv.weights.shape()), new(conv.bias.shape())
+                conv.backward(inp, g_in, g_out, wg, bg)
+                grads[idx] = {"weights": wg, "bias": bg}
+            g_out = g_in
+        return acts[-1], g_out, grads
 
 
 class MLP(_Replayable):

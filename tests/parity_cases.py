@@ -359,3 +359,58 @@ def mnist_convnet_case(datatype, batch=32, seed=601):
         return ct.to_array(net.infer(t(X)))
 
     return run
+
+
+def mnist_convnet_training_case(datatype, batch=16, seed=611):
+    """One training pass (forward with batch statistics, backward through every layer) of the same network, with
+    the cross-entropy gradient (softmax output - one-hot labels) / batch at its output.  Returns the output, the
+    updated running statistics of both batch-norm layers and every parameter gradient."""
+    dt = NP[datatype]
+    rng = np.random.default_rng(seed)
+    X = rng.random((batch, 1, 28, 28)).astype(dt)
+    labels = rng.integers(0, 10, size=batch)
+
+    def he(shape, fan_in):
+        return (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(dt)
+
+    W1, b1 = he((20, 25), 25), (rng.standard_normal(20) * 0.1).astype(dt)
+    W2, b2 = he((50, 500), 500), (rng.standard_normal(50) * 0.1).astype(dt)
+    W3, b3 = he((500, 800), 800), (rng.standard_normal(500) * 0.1).astype(dt)
+    W4, b4 = he((10, 500), 500), (rng.standard_normal(10) * 0.1).astype(dt)
+    bn_params = lambda n: [np.zeros(n, dt), np.ones(n, dt), (1 + 0.1 * rng.standard_normal(n)).astype(dt),
+                           (rng.standard_normal(n) * 0.1).astype(dt)]
+    bn1, bn2 = bn_params(20), bn_params(800)
+
+    def run():
+        t = lambda a: ct.to_tensor(a, datatype)
+        bns = [nn.BatchNormalization(*[t(a) for a in bn1], epsilon=1e-3), nn.BatchNormalization(*[t(a) for a in bn2], epsilon=1e-3)]
+        net = nn.ConvNet([
+            ("conv", nn.Convolution(t(W1), t(b1), (5, 5), (0, 0), (1, 1), 1, 20, datatype)),
+            ("pool", nn.Pooling(20, (2, 2), (0, 0), (2, 2), datatype)),
+            ("bn", bns[0]),
+            ("relu",),
+            ("conv", nn.Convolution(t(W2), t(b2), (5, 5), (0, 0), (1, 1), 20, 50, datatype)),
+            ("pool", nn.Pooling(50, (2, 2), (0, 0), (2, 2), datatype)),
+            ("flatten",),
+            ("bn", bns[1]),
+            ("linear", nn.Linear(t(W3), t(b3)), "relu"),
+            ("linear", nn.Linear(t(W4), t(b4)), None),
+            ("softmax",),
+        ], fused=False)
+        x = t(X)
+        probs = ct.to_array(net.infer(x)).reshape(batch, 10)          # only to build a loss gradient of the right size
+        onehot = np.zeros((batch, 10), dt)
+        onehot[np.arange(batch), labels] = 1
+        out_grad = t(((probs - onehot) / batch).astype(dt))
+        out, _g, grads = net.train_forward_backward(x, out_grad)
+        res = {"output": ct.to_array(out)}
+        for i, bn in enumerate(bns):
+            res["bn%d-running-means" % i] = ct.to_array(bn.means)
+            res["bn%d-running-variances" % i] = ct.to_array(bn.variances)
+        for idx, g in enumerate(grads):
+            if g:
+                for name, tensor in g.items():
+                    res["layer%d-%s-gradient" % (idx, name)] = ct.to_array(tensor)
+        return res, out_grad
+
+    return run

@@ -9,6 +9,7 @@ comparison is at 1e-12 relative (double) / 1e-5 (float, bound 1e-4)."""
 import numpy as np
 import pytest
 
+import parity_cases as pc
 from cortex_b200 import tensor as ct
 
 pytestmark = pytest.mark.gpu
@@ -173,3 +174,23 @@ def test_lrn_matches_oracle(b200_driver, oracle_driver, datatype, shape, n):
     (g_out, g_dx), (c_out, c_dx) = _run(b200_driver, datatype, run), _run(oracle_driver, datatype, run)
     assert _rel(g_out, c_out) <= TOL[datatype]
     assert _rel(g_dx, c_dx) <= TOL[datatype]
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
+def test_mnist_convnet_training_pass_matches_oracle(b200_driver, oracle_driver, datatype):
+    """The reference's MNIST network (conv, max-pool, batch-norm, ReLU, conv, max-pool, batch-norm, linear + ReLU,
+    linear, softmax) through one training pass on both backends: output with batch statistics, updated running
+    statistics, and the gradient of every parameter.  The loss gradient fed to the B200 pass is the one the oracle
+    pass built, so both differentiate the same function at the same point."""
+    run = pc.mnist_convnet_training_case(datatype)
+    cpu, _ = _run(oracle_driver, datatype, run)
+    gpu, _ = _run(b200_driver, datatype, run)
+    assert set(cpu) == set(gpu) and len(cpu) >= 15
+    for key in sorted(cpu):
+        if key in ("layer0-bias-gradient", "layer4-bias-gradient"):
+            # a bias in front of a batch-norm layer has gradient zero (the layer removes the mean): both sides hold
+            # rounding noise only
+            assert np.abs(gpu[key]).max() <= (1e-5 if datatype == "float" else 1e-12), key
+            continue
+        err = pc.rel_err(gpu[key], cpu[key])
+        assert err <= (2e-4 if datatype == "float" else 1e-10), (key, err)
