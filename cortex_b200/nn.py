@@ -334,8 +334,9 @@ class ConvNet(_Replayable):
         .backward): batch-norm layers use and update batch statistics, every layer keeps its input and output, and the
         backward sweep returns the loss gradient with respect to x and a list of per-layer parameter gradients
         ({"weights": .., "bias": ..} for conv / linear, {"scale": .., "bias": ..} for batch-norm, None otherwise).
-        `output_gradient` is the gradient at the network's output; a trailing softmax passes it through (the layer is
-        paired with the cross-entropy loss, whose gradient is already with respect to the softmax input)."""
+        `output_gradient` is the gradient at the network's output, or a function of the output tensor returning it; a
+        trailing softmax passes it through (the layer is paired with the cross-entropy loss, whose gradient is already
+        with respect to the softmax input)."""
         dt = x.get_datatype()
         new = lambda shape: ct.new_tensor(list(shape), datatype=dt)
         acts = [x]                      # acts[i] = input of layer i, acts[i + 1] = its output
@@ -366,7 +367,8 @@ class ConvNet(_Replayable):
                 raise ValueError("unknown layer kind %r" % (kind,))
             acts.append(cur)
         grads = [None] * len(self.layers)
-        g_out = output_gradient
+        # a callable gets the network's output (a loss whose gradient depends on this very forward pass)
+        g_out = output_gradient(cur) if callable(output_gradient) else output_gradient
         for idx in range(len(self.layers) - 1, -1, -1):
             spec, inp, out = self.layers[idx], acts[idx], acts[idx + 1]
             kind = spec[0]

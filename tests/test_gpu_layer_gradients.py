@@ -5,7 +5,9 @@ Pooling backward is a gather over the reference's scatter loop in the same visit
 also when it accumulates (input-grad-alpha = 1) onto a non-zero gradient, which is what the CPU backend
 always does.  Batch-normalisation statistics: the elementwise form sums in the reference's order (bit for
 bit up to the power function in the gradient); the spatial form uses a tree reduction in double, so the
-comparison is at 1e-12 relative (double) / 1e-5 (float, bound 1e-4)."""
+comparison is at 1e-12 relative (double) / 1e-5 (float, bound 1e-4).  lrn against the oracle's restatement of the
+published definition.  Then the layers together: one training pass of the reference's MNIST network against the
+oracle's pass, and forty Adam steps on a fixed batch (the loss must fall)."""
 import numpy as np
 import pytest
 
@@ -194,3 +196,57 @@ def test_mnist_convnet_training_pass_matches_oracle(b200_driver, oracle_driver, 
             continue
         err = pc.rel_err(gpu[key], cpu[key])
         assert err <= (2e-4 if datatype == "float" else 1e-10), (key, err)
+
+
+def test_mnist_convnet_learns_a_batch(b200_driver):
+    """End to end on the B200: forward with batch statistics, backward through every layer, Adam steps on every
+    parameter (one optimiser state buffer for the whole network, stepped per layer at its offset, as the reference's
+    compute binding does).  Forty steps on one fixed batch must cut the cross-entropy loss by more than half."""
+    from cortex_b200 import nn, optimize
+    dt, batch = "float", 32
+    rng = np.random.default_rng(77)
+    X = rng.random((batch, 1, 28, 28)).astype(np.float32)
+    labels = rng.integers(0, 10, size=batch)
+    onehot = np.zeros((batch, 10), np.float32)
+    onehot[np.arange(batch), labels] = 1
+    he = lambda shape, fan_in: (rng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+
+    def run():
+        t = lambda a: ct.to_tensor(a, dt)
+        bn = lambda n: nn.BatchNormalization(t(np.zeros(n)), t(np.ones(n)), t(np.ones(n)), t(np.zeros(n)), epsilon=1e-3)
+        layers = [("conv", nn.Convolution(t(he((20, 25), 25)), t(np.zeros(20)), (5, 5), (0, 0), (1, 1), 1, 20, dt)),
+                  ("pool", nn.Pooling(20, (2, 2), (0, 0), (2, 2), dt)), ("bn", bn(20)), ("relu",),
+                  ("conv", nn.Convolution(t(he((50, 500), 500)), t(np.zeros(50)), (5, 5), (0, 0), (1, 1), 20, 50, dt)),
+                  ("pool", nn.Pooling(50, (2, 2), (0, 0), (2, 2), dt)), ("flatten",), ("bn", bn(800)),
+                  ("linear", nn.Linear(t(he((500, 800), 800)), t(np.zeros(500))), "relu"),
+                  ("linear", nn.Linear(t(he((10, 500), 500)), t(np.zeros(10))), None), ("softmax",)]
+        net = nn.ConvNet(layers, fused=False)
+        params = []                                    # (parameter tensor, key of its gradient, layer index)
+        for idx, spec in enumerate(layers):
+            if spec[0] in ("conv", "linear"):
+                params += [(spec[1].weights, "weights", idx), (spec[1].bias, "bias", idx)]
+            elif spec[0] == "bn":
+                params += [(spec[1].scale, "scale", idx), (spec[1].bias, "bias", idx)]
+        total = sum(p.ecount() for p, _k, _i in params)
+        state = {"m": ct.new_tensor([total], datatype=dt), "v": ct.new_tensor([total], datatype=dt)}
+        adam = optimize.Adam(alpha=0.003)
+        x = t(X)
+        losses = []
+
+        def loss_gradient(out):        # cross-entropy on the softmax output: (p - onehot) / batch at the softmax INPUT
+            probs = ct.to_array(out).reshape(batch, 10)
+            losses.append(float(-np.log(np.maximum(probs[np.arange(batch), labels], 1e-30)).mean()))
+            return t((probs - onehot) / batch)
+
+        for _ in range(40):
+            _out, _g, grads = net.train_forward_backward(x, loss_gradient)
+            adam.batch_update()
+            offset = 0
+            for p, key, idx in params:
+                adam.compute_parameters(state, 1.0, offset, grads[idx][key], p)
+                offset += p.ecount()
+        return losses
+
+    losses = _run(b200_driver, dt, run)
+    assert np.isfinite(losses).all()
+    assert losses[-1] < 0.5 * losses[0], (losses[0], losses[-1])
