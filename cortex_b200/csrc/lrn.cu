@@ -54,6 +54,62 @@ lrn_forward_kernel(T* out, T* scale_out, const T* in, LrnGeom g, long long n_ele
   }
 }
 
+// Forward with the window width known at compile time (N <= 8, the common case): one thread owns a (batch entry,
+// pixel) column and walks its channels with the window's N values in registers, so every input element is loaded
+// once (adjacent threads = adjacent pixels: coalesced) and the sum of squares is N multiply-adds in channel order
+// (the same order, hence the same value, as the per-element kernel above).
+template <typename T, int N>
+__global__ void __launch_bounds__(256)
+lrn_forward_columns_kernel(T* out, const T* in, LrnGeom g, long long n_cols) {
+  const unsigned plane = (unsigned)g.plane;
+  const int C = g.channels, lb = g.look_behind, la = N - 1 - lb;
+  for (long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x; col < n_cols; col += (long long)gridDim.x * blockDim.x) {
+    const unsigned cu = (unsigned)col;
+    const unsigned b = cu / plane, p = cu - b * plane;
+    const size_t base = (size_t)b * (unsigned)C * plane + p;
+    const T* x = in + base;
+    T* y = out + base;
+    T win[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int ch = i - lb;
+      win[i] = (ch >= 0 && ch < C) ? x[(unsigned)ch * plane] : (T)0;
+    }
+    for (int c = 0; c < C; ++c) {
+      T sum = (T)0;
+#pragma unroll
+      for (int i = 0; i < N; ++i) sum += win[i] * win[i];
+      const T s = (T)g.k + (T)g.alpha_over_n * sum;
+      y[(unsigned)c * plane] = win[lb] * lrn_pow(s, (T)-g.beta);
+      const int next = c + 1 + la;
+#pragma unroll
+      for (int i = 0; i + 1 < N; ++i) win[i] = win[i + 1];
+      win[N - 1] = next < C ? x[(unsigned)next * plane] : (T)0;
+    }
+  }
+}
+
+template <typename T>
+bool lrn_forward_columns(cb200_stream* s, T* out, const T* in, const LrnGeom& g, int n) {
+  const long long n_cols = g.batch * g.plane;
+  if (n < 1 || n > 8 || n_cols < 4096) return false;      // few columns: the per-element kernel has more threads
+  long long blocks = (n_cols + 255) / 256;
+  const long long cap = (long long)s->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  const unsigned bl = (unsigned)blocks;
+  switch (n) {
+    case 1: lrn_forward_columns_kernel<T, 1><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
+    case 2: lrn_forward_columns_kernel<T, 2><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
+    case 3: lrn_forward_columns_kernel<T, 3><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
+    case 4: lrn_forward_columns_kernel<T, 4><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
+    case 5: lrn_forward_columns_kernel<T, 5><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
+    case 6: lrn_forward_columns_kernel<T, 6><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
+    case 7: lrn_forward_columns_kernel<T, 7><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
+    default: lrn_forward_columns_kernel<T, 8><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
+  }
+  return true;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 lrn_backward_kernel(T* in_grad, const T* out, const T* in, const T* out_grad, const T* scale, LrnGeom g,
@@ -125,10 +181,13 @@ int cb200_lrn_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* o
   if (rc) return rc;
   if (n == 0) return CB200_OK;
   DeviceGuard guard(s->device);
-  if (dtype == CB200_FLOAT)
-    lrn_forward_kernel<float, false><<<lrn_blocks(s, n), 256, 0, s->stream>>>((float*)out, nullptr, (const float*)in, g, n);
-  else
-    lrn_forward_kernel<double, false><<<lrn_blocks(s, n), 256, 0, s->stream>>>((double*)out, nullptr, (const double*)in, g, n);
+  if (dtype == CB200_FLOAT) {
+    if (!lrn_forward_columns<float>(s, (float*)out, (const float*)in, g, desc->n))
+      lrn_forward_kernel<float, false><<<lrn_blocks(s, n), 256, 0, s->stream>>>((float*)out, nullptr, (const float*)in, g, n);
+  } else {
+    if (!lrn_forward_columns<double>(s, (double*)out, (const double*)in, g, desc->n))
+      lrn_forward_kernel<double, false><<<lrn_blocks(s, n), 256, 0, s->stream>>>((double*)out, nullptr, (const double*)in, g, n);
+  }
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }

@@ -156,7 +156,10 @@ def test_batch_normalize_update_normalises(b200_driver, datatype):
 
 @pytest.mark.parametrize("datatype", ["float", "double"])
 @pytest.mark.parametrize("shape,n", [([2, 3, 2, 2], 1), ([2, 3, 2, 2], 2), ([2, 7, 5, 3], 5), ([3, 16, 9, 9], 4),
-                                     ([5, 6, 7], 3), ([2, 2, 4, 3, 3], 9), ([1, 96, 27, 27], 5)],
+                                     ([5, 6, 7], 3), ([2, 2, 4, 3, 3], 9), ([1, 96, 27, 27], 5),
+                                     # 4096 and more (batch entry, pixel) columns: the forward walks each column with the
+                                     # window in registers
+                                     ([16, 24, 20, 20], 5), ([16, 24, 20, 20], 2), ([4, 8, 40, 40], 8), ([8, 3, 32, 32], 1)],
                          ids=lambda v: "x".join(map(str, v)) if isinstance(v, list) else "n%d" % v)
 def test_lrn_matches_oracle(b200_driver, oracle_driver, datatype, shape, n):
     """lrn-forward! / lrn-backward!: both sides evaluate in double and round once; compared at the backend's
