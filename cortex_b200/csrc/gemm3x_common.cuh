@@ -34,7 +34,7 @@ struct GemmParams {
   float* partials;     // pair kernel only: [tail tile][K half][rank][128][BN] partial accumulators
   int split_block;     // tiles per block of (first halves, second halves) in the grid order
   // Small problems (fewer tiles than half the SMs): every tile is reduced by ksplit_n CTAs, each over a slice of K.
-  // A CTA parks its raw tile in ksplit_ws[(tile * ksplit_n + slice)][BM][BN]; the one that arrives last (per-tile
+  // A CTA parks its raw tile in ksplit_ws[(tile * ksplit_n + slice)][BN / 4][BM] float4; the one that arrives last (per-tile
   // counter in tile_flags) sums the slices in slice order and runs the epilogue.  Nobody waits.
   int ksplit_n;
   float* ksplit_ws;
@@ -46,13 +46,16 @@ struct GemmParams {
   float* peers[MAX_PEERS];
 };
 
+// tanh / logistic sit behind a call: inlined next to the cheap cases the compiler evaluated all of them
+// branch-free for every element (about 150 instructions each, measured 4.5 us per 32 x 32 slab of a
+// linear output in the per-element store paths).
+static __device__ __noinline__ float apply_act_transcendental(float v, int act) {
+  return act == CB200_ACT_TANH ? tanhf(v) : 1.f / (1.f + expf(-v));
+}
 __device__ __forceinline__ float apply_act(float v, int act) {
-  switch (act) {
-    case CB200_ACT_RELU: return v > 0.f ? v : 0.f;
-    case CB200_ACT_TANH: return tanhf(v);
-    case CB200_ACT_LOGISTIC: return 1.f / (1.f + expf(-v));
-  }
-  return v;
+  if (act == CB200_ACT_NONE) return v;
+  if (act == CB200_ACT_RELU) return v > 0.f ? v : 0.f;
+  return apply_act_transcendental(v, act);
 }
 
 // lo = x - trunc_tf32(x): exact in fp32; 0 for Inf / NaN so that they propagate through hi alone
@@ -93,12 +96,14 @@ __device__ __forceinline__ float4 ld_c4(const float* p, bool partial) {
   return partial ? __ldcg(reinterpret_cast<const float4*>(p)) : *reinterpret_cast<const float4*>(p);
 }
 
-// Park this CTA's raw accumulators (main + cross terms) as a [BM][BN] float tile (K-sliced small problems).
+// Park this CTA's raw accumulators (main + cross terms) for the CTA that combines the K slices of the tile.
+// A parked tile is BN / 4 column groups of [128 rows] float4: the 32 lanes of a warp (32 consecutive rows)
+// write and read 512 contiguous bytes per instruction.
 template <int BN>
 __device__ __forceinline__ void dump_tile(const GemmParams& p, uint32_t tmem_base, float* dst, int warp, int lane) {
   const int q = warp & 3, half = warp >> 2;
   constexpr int COLS_PER_HALF = BN / 2;
-  float* row = dst + (long long)(q * 32 + lane) * BN;
+  float4* slot = reinterpret_cast<float4*>(dst) + (q * 32 + lane);
 #pragma unroll 1
   for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
     const int col0 = half * COLS_PER_HALF + cc * 32;
@@ -115,8 +120,8 @@ __device__ __forceinline__ void dump_tile(const GemmParams& p, uint32_t tmem_bas
     }
 #pragma unroll
     for (int j = 0; j < 32; j += 4)
-      __stcg(reinterpret_cast<float4*>(row + col0 + j), make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                    __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
+      __stcg(slot + ((col0 + j) >> 2) * 128, make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                         __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])));
   }
 }
 
@@ -150,16 +155,39 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
         const int col0 = half * COLS_PER_HALF + cc * 32;
         uint32_t r[32];
         if (gather) {
-          // K slices parked by gather_n CTAs (this one included): summed in slice order, whoever runs this
-          const float* g0 = gather + (long long)(q * 32 + lane) * BN + col0;
+          // K slices parked by gather_n CTAs (this one included): summed in slice order, whoever runs this.
+          // Two slices (sixteen 16-byte loads) are requested before the first is added: the combine costs
+          // about gather_n / 2 round trips to L2 per 32 columns instead of one per load.
+          constexpr int SLICE4 = 128 * BN / 4;                         // float4 per parked tile
+          const float4* g0 = reinterpret_cast<const float4*>(gather) + (col0 >> 2) * 128 + (q * 32 + lane);
+          float4 a[8];
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            float4 a = __ldcg(reinterpret_cast<const float4*>(g0 + j));
-            for (int sl = 1; sl < gather_n; ++sl) {
-              const float4 b = __ldcg(reinterpret_cast<const float4*>(g0 + (long long)sl * 128 * BN + j));   // [128][BN] per slice
-              a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+          for (int j = 0; j < 8; ++j) a[j] = __ldcg(g0 + j * 128);
+          int sl = 1;
+          for (; sl + 1 < gather_n; sl += 2) {
+            float4 b0[8], b1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              b0[j] = __ldcg(g0 + (long long)sl * SLICE4 + j * 128);
+              b1[j] = __ldcg(g0 + (long long)(sl + 1) * SLICE4 + j * 128);
             }
-            r[j] = __float_as_uint(a.x); r[j + 1] = __float_as_uint(a.y); r[j + 2] = __float_as_uint(a.z); r[j + 3] = __float_as_uint(a.w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              a[j].x += b0[j].x; a[j].y += b0[j].y; a[j].z += b0[j].z; a[j].w += b0[j].w;
+              a[j].x += b1[j].x; a[j].y += b1[j].y; a[j].z += b1[j].z; a[j].w += b1[j].w;
+            }
+          }
+          if (sl < gather_n) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 b = __ldcg(g0 + (long long)sl * SLICE4 + j * 128);
+              a[j].x += b.x; a[j].y += b.y; a[j].z += b.z; a[j].w += b.w;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            r[4 * j] = __float_as_uint(a[j].x); r[4 * j + 1] = __float_as_uint(a[j].y);
+            r[4 * j + 2] = __float_as_uint(a[j].z); r[4 * j + 3] = __float_as_uint(a[j].w);
           }
         } else {
         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
@@ -236,32 +264,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
           __syncwarp();
           continue;
         }
-        if (e_peers > 0 && staging != nullptr && p.store_mode == STORE_ROW_MAJOR) {
+        if (staging != nullptr && p.store_mode == STORE_ROW_MAJOR && !(vec_ok && nb + 32 <= p.N)) {
+          // Ragged or unaligned slab (the last columns of N, a row pitch that is not a multiple of 16 bytes):
+          // transposed through a [32][33]-float shared tile per warp, so that a lane owns a COLUMN and every
+          // load of C, store of C and peer store covers consecutive floats of one row.  (One 4-byte store per
+          // lane per row with lane = row measured 5-8 us per 32 x 32 slab: 32 partly written sectors per
+          // instruction.)  Arithmetic and its order per element are those of the direct paths below.
           float* t = staging + warp * (32 * 36);
-          if (m < p.M && nb < p.N) {
-            const float* crow = p.C + (long long)m * p.ldc + nb;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float o = p.alpha * __uint_as_float(r[j]);
-              if (nb + j < p.N) {
-                if (beta_now != 0.f) o += beta_now * ld_c(crow + j, c_is_partial);
-                if (e_bias) o += e_bias[nb + j];
-                o = apply_act(o, e_act);
-              }
-              t[lane * 33 + j] = o;
-            }
-          }
+          for (int j = 0; j < 32; ++j) t[lane * 33 + j] = p.alpha * __uint_as_float(r[j]);
           __syncwarp();
           const int n = nb + lane;
           if (n < p.N) {
             const int row_base = m0 + q * 32;
+            const float bias_n = e_bias ? e_bias[n] : 0.f;
 #pragma unroll 4
             for (int rr = 0; rr < 32; ++rr) {
               const int mr = row_base + rr;
               if (mr < p.M) {
-                const float v = t[rr * 33 + lane];
                 const long long off = (long long)mr * p.ldc + n;
+                float v = t[rr * 33 + lane];
+                if (beta_now != 0.f) v += beta_now * ld_c(p.C + off, c_is_partial);
+                if (e_bias) v += bias_n;
+                v = apply_act(v, e_act);
                 p.C[off] = v;
+                if (WITH_LO && c_lo) c_lo[off] = lo_part(v);
                 for (int d = 0; d < e_peers; ++d) p.peers[d][off] = v;
               }
             }

@@ -58,8 +58,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   typedef TileCfg<BN, BK> Cfg;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int A_TILE = Cfg::A_TILE;
-  // lo pass by one warp per k-block instead of all warps on each: only where warps and stages pair up
-  constexpr bool WARP_PER_KBLOCK = BN <= 64 && STAGES == NUM_CONV_WARPS;
   // Role loops run either by the whole warp with one elected lane issuing (warp-uniform control
   // flow: cheaper per issued instruction, which narrow tiles and multi-box MN-major loads need) or by
   // lane 0 alone (measured 1-2 % faster for 256-wide tiles fed by two K-major boxes per k-block).
@@ -114,7 +112,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_conv + 8 * s, WARP_PER_KBLOCK ? 1 : NUM_CONV_WARPS);
+      mbar_init(bar_conv + 8 * s, NUM_CONV_WARPS);
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_acc, 1);
@@ -125,6 +123,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  int inject = 0;                 // host-injected fault word: requested here so that its latency hides under the set-up
+  if (warp == NUM_CONV_WARPS) inject = p.status[3];
   if (warp == NUM_CONV_WARPS && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -142,7 +142,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       int issued = 0;
       int s = 0;
       uint32_t ph = 0;
-      const bool withhold = (p.status[3] & 1) != 0;     // host-injected fault: arm nothing, load nothing
+      const bool withhold = (inject & 1) != 0;          // host-injected fault: arm nothing, load nothing
       for (int i = 0; i < nkb; ++i) {
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 100 + s)) break;
         const uint32_t full = bar_full + 8 * s;
@@ -239,31 +239,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // ------------------- hi/lo split, then epilogue (warps 0-7) ---------------
     const int tid = threadIdx.x;
     bool ok = true;
-    if (WARP_PER_KBLOCK) {
-      // Narrow tiles belong to small, latency-bound problems, where a k-block's pass (wait, load,
-      // split, store, proxy fence, arrive) is a serial chain of several hundred cycles: each warp
-      // takes whole k-blocks (i = warp, warp + 8, ...), so eight of those chains overlap.  Warp w
-      // always works on stage w (8 warps, 8 stages), in consecutive phases.
-      for (int i = warp; i < nkb; i += NUM_CONV_WARPS) {
-        const int s = warp, ph = (i / STAGES) & 1;
-        if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 300 + s)) { ok = false; break; }
-        uint8_t* hi = smem + s * Cfg::STAGE;
-        uint8_t* lo = hi + Cfg::RAW;
-        if (!(p.flags & FLAG_ONE_TERM)) {
-#pragma unroll 8
-          for (int c = 0; c < Cfg::RAW / 16 / 32; ++c) {
-            const int off = (lane + c * 32) * 16;
-            const float4 v = *reinterpret_cast<const float4*>(hi + off);
-            float4 l;
-            l.x = lo_part(v.x); l.y = lo_part(v.y); l.z = lo_part(v.z); l.w = lo_part(v.w);
-            *reinterpret_cast<float4*>(lo + off) = l;
-          }
-          fence_proxy_async_smem();
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_conv + 8 * s);
-      }
-    } else {
     for (int i = 0; i < nkb; ++i) {
       const int s = i % STAGES, ph = (i / STAGES) & 1;
       if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 300 + s)) { ok = false; break; }
@@ -282,7 +257,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_conv + 8 * s);   // one arrive per warp
-    }
     }
     if (ok) ok = mbar_wait(bar_acc, 0, abort_flag, p.status, 400);
     ok = __all_sync(0xffffffffu, ok);   // tcgen05.ld below is warp-collective
