@@ -22,7 +22,7 @@ BINARY_OPS = {"+": 0, "-": 1, "*": 2, "/": 3, "min": 4, "max": 5, "bit-and": 6, 
 UNARY_OPS = {"floor": 0, "ceil": 1, "round": 2, "-": 3, "tanh": 4, "logistic": 5, "exp": 6, "sqrt": 7, "noop": 8}
 TERNARY_OPS = {"select": 0}
 REDUCE_OPS = {"max": 0, "min": 1, "sum": 2, "mean": 3, "magnitude": 4, "magnitude-squared": 5}
-ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "tanh": 2, "logistic": 3}
+ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "tanh": 2, "logistic": 3, "softmax": 4}    # softmax: gemm_bias_act only
 DISTRIBUTIONS = {"flat": 0, "gaussian": 1}
 STREAM_OPTIONS = {"gemm-auto-presplit": 0, "presplit-variant": 1, "f64-simple-kernel": 2, "wait-limit-cycles": 3,
                   "inject-fault": 4, "conv-route": 5, "gemm-k-slices": 6}

@@ -109,6 +109,89 @@ int launch_simt(cb200_stream* s, T* C, long long ldc, int ta, int tb, T alpha, c
   return CB200_OK;
 }
 
+// ---- skinny outputs (N <= 16, op(A) row-major, op(B) = B^T row-major: a dense layer's small head) ----
+// A [M, 16]-or-narrower output is one 64-column tensor-core tile per 128 rows with three quarters of it padding,
+// plus the K-slice hand-over: 14.6 us for 128 x 10 x 500.  Here one CTA owns one output row: 128 threads stride
+// over K with up to 16 accumulators each (A read once, coalesced; B's N rows stay in L1 / L2), partial sums are
+// combined by shuffles inside a warp and in warp order across the four warps (fixed order), and lane n of
+// warp 0 finishes column n: alpha, beta, bias, activation -- or the row's softmax, which those lanes hold whole.
+constexpr int SKINNY_MAX_N = 16;
+constexpr int SKINNY_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(SKINNY_THREADS)
+gemm_skinny_nt_kernel(T* C, long long ldc, const T* A, long long lda, const T* B, long long ldb, int M, int N, int K,
+                      T alpha, T beta, const T* bias, int act) {
+  __shared__ T part[SKINNY_THREADS / 32][SKINNY_MAX_N];
+  const int m = (int)blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const T* a = A + (long long)m * lda;
+  T acc[SKINNY_MAX_N];
+#pragma unroll
+  for (int n = 0; n < SKINNY_MAX_N; ++n) acc[n] = (T)0;
+#pragma unroll 2
+  for (int k = (int)threadIdx.x; k < K; k += SKINNY_THREADS) {
+    const T av = a[k];
+#pragma unroll
+    for (int n = 0; n < SKINNY_MAX_N; ++n)
+      if (n < N) acc[n] += av * B[(long long)n * ldb + k];
+  }
+#pragma unroll
+  for (int n = 0; n < SKINNY_MAX_N; ++n) {
+    if (n < N) {
+      T v = acc[n];
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+      if (lane == 0) part[warp][n] = v;
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  const bool live = lane < N;
+  T o = (T)0;
+  if (live) {
+    T sum = part[0][lane];
+#pragma unroll
+    for (int w = 1; w < SKINNY_THREADS / 32; ++w) sum += part[w][lane];
+    o = alpha * sum;
+    if (beta != (T)0) o += beta * C[(long long)m * ldc + lane];
+    if (bias) o += bias[lane];
+    if (act != CB200_ACT_SOFTMAX) o = act_apply<T>(o, act);
+  }
+  if (act == CB200_ACT_SOFTMAX) {
+    // softmax of the row with the CPU backend's roundings (cpu/tensor_math.clj:1037-1088): exp(x - max) evaluated
+    // in double and stored in the element type, the stored values summed in double, the sum rounded, one divide
+    T mt = live ? o : (T)-INFINITY;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const T other = __shfl_xor_sync(0xffffffffu, mt, d);
+      mt = other > mt ? other : mt;
+    }
+    const T et = live ? (T)exp((double)o - (double)mt) : (T)0;
+    double tot = (double)et;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, d);
+    o = et / (T)tot;
+  }
+  if (live) C[(long long)m * ldc + lane] = o;
+}
+
+// Shapes the skinny kernel takes: small heads in the latency-bound regime (the tensor-core path wins back
+// once there are enough rows to fill the SMs with tiles).
+bool skinny_ok(int M, int N, int K, int trans_a, int trans_b, const PeerList* peers) {
+  return !trans_a && trans_b && N >= 1 && N <= SKINNY_MAX_N && M >= 1 && M <= 4096 && K >= 1 && K <= 16384 &&
+         (!peers || peers->n == 0);
+}
+
+template <typename T>
+int launch_skinny(cb200_stream* s, T* C, long long ldc, T alpha, const T* A, int M, int K, long long lda, const T* B, int N,
+                  long long ldb, T beta, const T* bias, int act) {
+  DeviceGuard guard(s->device);
+  gemm_skinny_nt_kernel<T><<<(unsigned)M, SKINNY_THREADS, 0, s->stream>>>(C, ldc, A, lda, B, ldb, M, N, K, alpha, beta, bias, act);
+  CB_LAUNCH_CHECK(s);
+  return CB200_OK;
+}
+
 // tensor-core fp32 path.  (A CTA-pair variant with tcgen05.mma.cta_group::2 and 256 x 256 tiles was
 // built and measured: correct, but 142 vs 210 TFLOP/s at 4096^3 -- the lo pass over shared memory
 // slows to 1000-2000 cycles per k-block while the pair's MMAs stream operands -- so single CTAs stay.)
@@ -131,8 +214,28 @@ int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int
   CB_REQUIRE(ldc >= N, "gemm: ldc %lld smaller than N %d", (long long)ldc, N);
   CB_REQUIRE(lda >= (trans_a ? M : K), "gemm: lda %lld smaller than the stored row of A", (long long)lda);
   CB_REQUIRE(ldb >= (trans_b ? K : N), "gemm: ldb %lld smaller than the stored row of B", (long long)ldb);
-  CB_REQUIRE(act >= CB200_ACT_NONE && act <= CB200_ACT_LOGISTIC, "gemm: unknown activation %d", act);
+  CB_REQUIRE(act >= CB200_ACT_NONE && act <= CB200_ACT_SOFTMAX, "gemm: unknown activation %d", act);
+  CB_REQUIRE(act != CB200_ACT_SOFTMAX || !peers || peers->n == 0, "gemm: the softmax epilogue has no peer-store form");
   if (M == 0 || N == 0) return CB200_OK;
+  if (skinny_ok(M, N, K, trans_a, trans_b, peers)) {
+    if (dtype == CB200_FLOAT)
+      return launch_skinny<float>(s, (float*)C, ldc, (float)alpha, (const float*)A, M, K, lda, (const float*)B, N, ldb,
+                                  (float)beta, (const float*)bias, act);
+    return launch_skinny<double>(s, (double*)C, ldc, alpha, (const double*)A, M, K, lda, (const double*)B, N, ldb, beta,
+                                 (const double*)bias, act);
+  }
+  if (act == CB200_ACT_SOFTMAX) {
+    // wider heads: the layer's kernel, then softmax! over the rows of C in place
+    int rc = gemm_impl(s, dtype, C, ldc, trans_a, trans_b, alpha, A, a_rows, a_cols, lda, B, b_cols, ldb, beta, bias,
+                       CB200_ACT_NONE, peers, layer_stack, allow_workspace);
+    if (rc) return rc;
+    CB_REQUIRE(ldc <= 2147483647LL, "gemm: row pitch of the softmax output over 2^31-1");
+    cb200_dims d;                                    // [M, N] rows of pitch ldc in the wire form (innermost first)
+    for (int i = 0; i < 5; ++i) { d.rev_shape[i] = 1; d.rev_strides[i] = (int32_t)ldc; d.index[i] = nullptr; }
+    d.rev_shape[0] = N; d.rev_strides[0] = 1;
+    d.rev_shape[1] = M;
+    return cb200_softmax_eltwise(s, dtype, C, &d, C, &d);
+  }
   if (dtype == CB200_FLOAT) {
     const float* a = (const float*)A;
     const float* b = (const float*)B;

@@ -484,10 +484,10 @@ class MLP(_Replayable):
                 if trace:
                     trace(idx, "end")
             elif self.fused and act == "softmax":
-                lin.forward_fused(cur, out, None)
+                # one call: heads of up to 16 classes are normalised by the kernel that computes them
+                lin.forward_fused(cur, out, "softmax")
                 if trace:
                     trace(idx, "end")
-                ct.softmax(out, out)
             else:
                 lin.forward(cur, out)
                 if trace:

@@ -60,7 +60,10 @@ enum cb200_reduce_op {
 };
 
 /* epilogue activations of the fused extras (no protocol counterpart) */
-enum cb200_act { CB200_ACT_NONE = 0, CB200_ACT_RELU = 1, CB200_ACT_TANH = 2, CB200_ACT_LOGISTIC = 3 };
+enum cb200_act { CB200_ACT_NONE = 0, CB200_ACT_RELU = 1, CB200_ACT_TANH = 2, CB200_ACT_LOGISTIC = 3,
+                 /* cb200_gemm_bias_act only: softmax! over every output row after bias (a classifier head).  Rows of
+                  * up to 16 columns are normalised by the kernel that computes them, wider ones by a second launch. */
+                 CB200_ACT_SOFTMAX = 4 };
 
 enum cb200_status {
   CB200_OK = 0,

@@ -532,12 +532,12 @@ def test_tensor_core_reads_fp32_words_truncated(b200_driver, ta, tb):
         assert np.array_equal(hi.astype(np.float64) + (x - hi).astype(np.float64), x.astype(np.float64))
 
 
-@pytest.mark.parametrize("M,N,K,act", [(128, 500, 784, "relu"), (128, 10, 500, None), (64, 1000, 2048, "tanh"),
+@pytest.mark.parametrize("M,N,K,act", [(128, 500, 784, "relu"), (128, 24, 500, None), (64, 1000, 2048, "tanh"),
                                        (300, 72, 1040, None), (8192, 125, 4096, None)])
 def test_small_gemm_is_sliced_over_k(b200_driver, M, N, K, act):
     """Problems with fewer tiles than half the SMs are reduced by several CTAs per tile, each over a slice of K,
     combined by whichever finishes last (in slice order: the result does not depend on who that is).  Config 1's
-    two layers, a wide-K case, a ragged one and the 8-way column-sharded head; twice in a row (the per-tile
+    first layer, a 24-column head, a wide-K case, a ragged one and the 8-way column-sharded head; twice in a row (the per-tile
     counters must be left clear), fused bias + activation, against float64."""
     rng = np.random.default_rng(M + N + K)
     A = rng.standard_normal((M, K)).astype(np.float32)
@@ -559,3 +559,41 @@ def test_small_gemm_is_sliced_over_k(b200_driver, M, N, K, act):
     assert pc.rel_err(outs[0], exact) <= pc.TOL["float"]
     assert np.array_equal(outs[0], outs[1])
     stream.sync()       # raises if a launch reported a status
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
+@pytest.mark.parametrize("M,N,K", [(128, 10, 500), (1, 1, 1), (37, 16, 333), (4096, 3, 64), (200, 16, 16384),
+                                   (128, 40, 500), (64, 1000, 256)])
+@pytest.mark.parametrize("act", [None, "relu", "logistic", "softmax"])
+def test_classifier_head_with_fused_softmax(b200_driver, datatype, M, N, K, act):
+    """gemm_bias_act on heads of up to 16 columns runs on the one-CTA-per-row kernel, which also normalises the
+    row when the activation is softmax; wider heads take the layer kernel and a softmax! launch behind the same
+    call.  alpha, beta and a pitched output included; against float64; twice for run-to-run equality."""
+    rng = np.random.default_rng(7 * M + N + K)
+    npdt = pc.NP[datatype]
+    A = rng.standard_normal((M, K)).astype(npdt)
+    W = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(npdt)
+    bias = rng.standard_normal(N).astype(npdt)
+    ldc = N + 3
+    C0 = rng.standard_normal((M, ldc)).astype(npdt)
+    alpha, beta = 1.25, 0.5
+    stream = b200_driver.default_device().create_stream()
+    outs = []
+    with ct.with_stream(stream), ct.with_datatype(datatype):
+        a, w, b = ct.to_tensor(A, datatype), ct.to_tensor(W, datatype), ct.to_tensor(bias, datatype)
+        for _ in range(2):
+            c = ct.to_tensor(C0, datatype)
+            stream.gemm_bias_act(c.buffer, ldc, False, True, alpha, a.buffer, M, K, K, w.buffer, N, K, beta, b.buffer, act)
+            outs.append(ct.to_array(c).reshape(M, ldc))
+    z = alpha * (A.astype(np.float64) @ W.astype(np.float64).T) + beta * C0[:, :N].astype(np.float64) + bias
+    if act == "relu":
+        z = np.maximum(z, 0.0)
+    elif act == "logistic":
+        z = 1.0 / (1.0 + np.exp(-z))
+    elif act == "softmax":
+        e = np.exp(z - z.max(axis=1, keepdims=True))
+        z = e / e.sum(axis=1, keepdims=True)
+    assert pc.rel_err(outs[0][:, :N], z) <= pc.TOL[datatype]
+    assert np.array_equal(outs[0][:, N:], C0[:, N:])          # the pitch padding is not touched
+    assert np.array_equal(outs[0], outs[1])
+    stream.sync()
