@@ -4,10 +4,10 @@
 //
 // Two kernels:
 //  * gemm_f64_pipe_kernel: operands whose base is 16-byte aligned and whose pitch is even.
-//    CTA tile 128 x 128 x 16, 8 warps as 2 (M) x 4 (N), warp tile 64 x 32 = 4 x 4 m16n8k8 tiles.
+//    CTA tile 128 x 128 x 32, 8 warps as 2 (M) x 4 (N), warp tile 64 x 32 = 4 x 4 m16n8k8 tiles.
 //    Operand tiles travel global -> shared by 16-byte cp.async in a 3-stage ring (one barrier per
 //    k-tile, no register staging).  An operand whose K axis is contiguous in memory is kept
-//    [row][k] with a pitch of 20 doubles, the other kind [k][row] with a pitch of 132: both make
+//    [row][k] with a pitch of 36 doubles, the other kind [k][row] with a pitch of 132: both make
 //    the fragment loads of a half-warp hit 16 different 8-byte banks.
 //  * gemm_f64_kernel (below): any alignment, m8n8k4 tiles, register-staged single buffer.
 //
@@ -32,13 +32,14 @@ __device__ __forceinline__ void dmma(double& d0, double& d1, double a, double b)
                : "d"(a), "d"(b));
 }
 
+// tanh / logistic behind a call, so that the epilogue of a layer without them does not evaluate them branch-free
+__device__ __noinline__ double act_f64_transcendental(double v, int act) {
+  return act == CB200_ACT_TANH ? tanh(v) : 1.0 / (1.0 + exp(-v));
+}
 __device__ __forceinline__ double act_f64(double v, int act) {
-  switch (act) {
-    case CB200_ACT_RELU: return v > 0.0 ? v : 0.0;
-    case CB200_ACT_TANH: return tanh(v);
-    case CB200_ACT_LOGISTIC: return 1.0 / (1.0 + exp(-v));
-  }
-  return v;
+  if (act == CB200_ACT_NONE) return v;
+  if (act == CB200_ACT_RELU) return v > 0.0 ? v : 0.0;
+  return act_f64_transcendental(v, act);
 }
 
 __device__ __forceinline__ void dmma_16x8x8(double (&d)[4], const double (&a)[4], const double (&b)[2]) {
@@ -57,8 +58,10 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 }
 
 constexpr int PSTAGES = 3;
-constexpr int KPITCH = 20;                       // [row][k] layout: doubles per row
-constexpr int OPERAND_DOUBLES = 128 * KPITCH;    // >= 16 * DLD
+constexpr int PBK = 32;                          // k-tile of the pipelined kernel (one barrier per 32 k: 16 measured 29.3 TF)
+constexpr int KPITCH = PBK + 4;                  // [row][k] layout: doubles per row (conflict-free per half-warp)
+constexpr int OPERAND_DOUBLES = 128 * KPITCH;    // >= PBK * DLD
+static_assert(OPERAND_DOUBLES >= PBK * DLD, "operand slot too small for the [k][row] layout");
 constexpr int PIPE_SMEM = PSTAGES * 2 * OPERAND_DOUBLES * 8;
 
 // Element (row r, k) of an operand tile in shared memory.
@@ -66,17 +69,17 @@ template <bool K_CONTIG> __device__ __forceinline__ int tile_at(int r, int k) {
   return K_CONTIG ? r * KPITCH + k : k * DLD + r;
 }
 
-// Copy one 128 x 16 operand tile.  K_CONTIG: element (r, k) at g[r*ld + k]; else at g[k*ld + r].
+// Copy one 128 x PBK operand tile.  K_CONTIG: element (r, k) at g[r*ld + k]; else at g[k*ld + r].
 template <bool K_CONTIG>
 __device__ __forceinline__ void load_operand_tile(double* sm, const double* g, long long ld, int r0, int k0, int R,
                                                   int K, int t) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 128 * PBK / 2 / 256; ++i) {
     const int c = t + 256 * i;
     int r, k, left;
     const double* src;
     if (K_CONTIG) {
-      r = c >> 3; k = (c & 7) * 2;
+      r = c / (PBK / 2); k = (c % (PBK / 2)) * 2;
       left = (r0 + r < R) ? (K - (k0 + k)) : 0;
       src = g + (long long)(r0 + r) * ld + k0 + k;
     } else {
@@ -98,7 +101,7 @@ gemm_f64_pipe_kernel(double* C, long long ldc, const double* A, long long lda, c
   const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
   const int m0 = blockIdx.y * DBM, n0 = blockIdx.x * DBN;
   const int g = lane >> 2, tig = lane & 3;
-  const int nk = (K + DBK - 1) / DBK;
+  const int nk = (K + PBK - 1) / PBK;
 
   double acc[4][4][4];
 #pragma unroll
@@ -111,8 +114,8 @@ gemm_f64_pipe_kernel(double* C, long long ldc, const double* A, long long lda, c
   auto issue = [&](int kt) {
     if (kt < nk) {
       double* as = psm + (kt % PSTAGES) * 2 * OPERAND_DOUBLES;
-      load_operand_tile<A_K_CONTIG>(as, A, lda, m0, kt * DBK, M, K, t);
-      load_operand_tile<B_K_CONTIG>(as + OPERAND_DOUBLES, B, ldb, n0, kt * DBK, N, K, t);
+      load_operand_tile<A_K_CONTIG>(as, A, lda, m0, kt * PBK, M, K, t);
+      load_operand_tile<B_K_CONTIG>(as + OPERAND_DOUBLES, B, ldb, n0, kt * PBK, N, K, t);
     }
     cp_async_commit();
   };
@@ -126,7 +129,7 @@ gemm_f64_pipe_kernel(double* C, long long ldc, const double* A, long long lda, c
     const double* as = psm + (kt % PSTAGES) * 2 * OPERAND_DOUBLES;
     const double* bs = as + OPERAND_DOUBLES;
 #pragma unroll
-    for (int kk = 0; kk < DBK / 8; ++kk) {
+    for (int kk = 0; kk < PBK / 8; ++kk) {
       double a[4][4], b[4][2];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
