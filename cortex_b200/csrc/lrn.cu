@@ -58,54 +58,97 @@ lrn_forward_kernel(T* out, T* scale_out, const T* in, LrnGeom g, long long n_ele
 // pixel) column and walks its channels with the window's N values in registers, so every input element is loaded
 // once (adjacent threads = adjacent pixels: coalesced) and the sum of squares is N multiply-adds in channel order
 // (the same order, hence the same value, as the per-element kernel above).
-template <typename T, int N>
+// The channel walk is a chain: the value loaded in one step joins the sum of squares of the next, so AHEAD more
+// values are requested before they are needed and wait in registers behind the window.  A thread owns VEC
+// adjacent pixels (16-byte accesses when the plane size and the base addresses allow): a CTA then moves 4 KB of
+// one channel plane per step instead of 1 KB, which is what the DRAM pages want -- the walk jumps a whole plane
+// between steps (one element per thread measured 1.7 TB/s, with or without the requests ahead; 2.9 TB/s with
+// 16-byte accesses and a shifting window at 120 registers; 4.25 TB/s as a ring at 59).
+template <typename T, int N, int AHEAD, int VEC>
 __global__ void __launch_bounds__(256)
-lrn_forward_columns_kernel(T* out, const T* in, LrnGeom g, long long n_cols) {
+lrn_forward_columns_kernel(T* out, const T* in, LrnGeom g, long long n_groups) {
+  struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   const unsigned plane = (unsigned)g.plane;
-  const int C = g.channels, lb = g.look_behind, la = N - 1 - lb;
-  for (long long col = (long long)blockIdx.x * blockDim.x + threadIdx.x; col < n_cols; col += (long long)gridDim.x * blockDim.x) {
-    const unsigned cu = (unsigned)col;
-    const unsigned b = cu / plane, p = cu - b * plane;
+  const unsigned groups_per_plane = plane / VEC;
+  const int C = g.channels;
+  constexpr int lb = (N - 1) / 2;                // = g.look_behind (lrn_geom)
+  constexpr int W = N + AHEAD;
+  const T k_t = (T)g.k, aon_t = (T)g.alpha_over_n, neg_beta_t = (T)-g.beta;
+  for (long long grp = (long long)blockIdx.x * blockDim.x + threadIdx.x; grp < n_groups; grp += (long long)gridDim.x * blockDim.x) {
+    const unsigned gu = (unsigned)grp;
+    const unsigned b = gu / groups_per_plane, p = (gu - b * groups_per_plane) * VEC;
     const size_t base = (size_t)b * (unsigned)C * plane + p;
     const T* x = in + base;
     T* y = out + base;
-    T win[N];
+    // ring of W channel values: channel ch sits in slot (ch + lb) % W, slots are compile-time constants because
+    // the channel loop is unrolled W-fold (no register moves when the window slides)
+    Pack win[W];
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
+    for (int i = 0; i < W; ++i) {
       const int ch = i - lb;
-      win[i] = (ch >= 0 && ch < C) ? x[(unsigned)ch * plane] : (T)0;
+      if (ch >= 0 && ch < C) {
+        win[i] = *reinterpret_cast<const Pack*>(x + (size_t)ch * plane);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) win[i].v[e] = (T)0;
+      }
     }
-    for (int c = 0; c < C; ++c) {
-      T sum = (T)0;
+    for (int c0 = 0; c0 < C; c0 += W) {
 #pragma unroll
-      for (int i = 0; i < N; ++i) sum += win[i] * win[i];
-      const T s = (T)g.k + (T)g.alpha_over_n * sum;
-      y[(unsigned)c * plane] = win[lb] * lrn_pow(s, (T)-g.beta);
-      const int next = c + 1 + la;
+      for (int r = 0; r < W; ++r) {
+        const int c = c0 + r;
+        if (c < C) {
+          Pack o;
 #pragma unroll
-      for (int i = 0; i + 1 < N; ++i) win[i] = win[i + 1];
-      win[N - 1] = next < C ? x[(unsigned)next * plane] : (T)0;
+          for (int e = 0; e < VEC; ++e) {
+            T sum = (T)0;
+#pragma unroll
+            for (int i = 0; i < N; ++i) sum += win[(r + i) % W].v[e] * win[(r + i) % W].v[e];
+            const T s = k_t + aon_t * sum;
+            // look_behind is (N - 1) / 2 for every descriptor: a constant here
+            o.v[e] = win[(r + (N - 1) / 2) % W].v[e] * lrn_pow(s, neg_beta_t);
+          }
+          *reinterpret_cast<Pack*>(y + (size_t)c * plane) = o;
+          const int next = c + W - lb;
+          if (next < C) {
+            win[r] = *reinterpret_cast<const Pack*>(x + (size_t)next * plane);
+          } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) win[r].v[e] = (T)0;
+          }
+        }
+      }
     }
   }
+}
+
+template <typename T, int N>
+void lrn_forward_columns_launch(cb200_stream* s, T* out, const T* in, const LrnGeom& g) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const long long n_cols = g.batch * g.plane;
+  const bool vec = (g.plane % VEC) == 0 && ((((uintptr_t)out) | ((uintptr_t)in)) & 15) == 0;
+  const long long n_groups = vec ? n_cols / VEC : n_cols;
+  // 128-thread blocks: at 64 registers eight fit an SM, and a shape with a few blocks per SM spreads evenly
+  long long blocks = (n_groups + 127) / 128;
+  const long long cap = (long long)s->sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  if (vec) lrn_forward_columns_kernel<T, N, 6, VEC><<<(unsigned)blocks, 128, 0, s->stream>>>(out, in, g, n_groups);
+  else lrn_forward_columns_kernel<T, N, 6, 1><<<(unsigned)blocks, 128, 0, s->stream>>>(out, in, g, n_groups);
 }
 
 template <typename T>
 bool lrn_forward_columns(cb200_stream* s, T* out, const T* in, const LrnGeom& g, int n) {
   const long long n_cols = g.batch * g.plane;
   if (n < 1 || n > 8 || n_cols < 4096) return false;      // few columns: the per-element kernel has more threads
-  long long blocks = (n_cols + 255) / 256;
-  const long long cap = (long long)s->sm_count * 16;
-  if (blocks > cap) blocks = cap;
-  const unsigned bl = (unsigned)blocks;
   switch (n) {
-    case 1: lrn_forward_columns_kernel<T, 1><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
-    case 2: lrn_forward_columns_kernel<T, 2><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
-    case 3: lrn_forward_columns_kernel<T, 3><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
-    case 4: lrn_forward_columns_kernel<T, 4><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
-    case 5: lrn_forward_columns_kernel<T, 5><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
-    case 6: lrn_forward_columns_kernel<T, 6><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
-    case 7: lrn_forward_columns_kernel<T, 7><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
-    default: lrn_forward_columns_kernel<T, 8><<<bl, 256, 0, s->stream>>>(out, in, g, n_cols); break;
+    case 1: lrn_forward_columns_launch<T, 1>(s, out, in, g); break;
+    case 2: lrn_forward_columns_launch<T, 2>(s, out, in, g); break;
+    case 3: lrn_forward_columns_launch<T, 3>(s, out, in, g); break;
+    case 4: lrn_forward_columns_launch<T, 4>(s, out, in, g); break;
+    case 5: lrn_forward_columns_launch<T, 5>(s, out, in, g); break;
+    case 6: lrn_forward_columns_launch<T, 6>(s, out, in, g); break;
+    case 7: lrn_forward_columns_launch<T, 7>(s, out, in, g); break;
+    default: lrn_forward_columns_launch<T, 8>(s, out, in, g); break;
   }
   return true;
 }

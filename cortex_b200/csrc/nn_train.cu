@@ -100,15 +100,24 @@ pooling_backward_kernel(T* in_grad, const T* in, const T* out, const T* out_grad
   }
 }
 
-// Square window KS with stride ST known at compile time: an input position lies in at most NW = ceil(KS / ST)
-// windows per dimension, so the candidate windows are a fully unrolled, predicated NW x NW loop (visited in
-// ascending (out-y, out-x) order: the reference's summation order) with 32-bit index arithmetic.
-template <typename T, int OP, int VEC, int KS, int ST>
+// Square window KS with stride ST known at compile time, and the horizontal padding's remainder PADP = pad_x % ST
+// (the same for every thread: a thread's first column is a multiple of VEC, itself a multiple of ST).  An input
+// position lies in at most NW = ceil(KS / ST) windows per dimension.  With PADP fixed, WHICH windows element e of
+// a thread's VEC columns belongs to is known at compile time -- column (e + PADP) % ST of window q - dx,
+// q = (e + PADP) / ST, for every dx with (e + PADP) % ST + dx * ST < KS -- so a thread loads each of the NJ
+// distinct (output, output gradient) pairs of a window row once (3 instead of 8 per row for 3 x 3 / 2) and the
+// inner loop is compares and adds only.  Windows are visited in ascending (out-y, out-x) order per element: the
+// reference's summation order.  32-bit index arithmetic.
+template <typename T, int OP, int VEC, int KS, int ST, int PADP>
 __global__ void __launch_bounds__(256)
 pooling_backward_fixed_kernel(T* in_grad, const T* in, const T* out, const T* out_grad, PoolBwdGeom g, long long n_groups,
                               double in_grad_alpha) {
+  static_assert(VEC % ST == 0 && PADP < ST, "a thread's first column must be a multiple of the stride");
   struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
   constexpr int NW = (KS + ST - 1) / ST;
+  constexpr int JMIN = PADP / ST - (NW - 1);          // window offsets (relative to `wbase`) a thread can touch
+  constexpr int JMAX = (VEC - 1 + PADP) / ST;
+  constexpr int NJ = JMAX - JMIN + 1;
   const unsigned groups_per_row = (unsigned)(g.in_w / VEC);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_groups; i += (long long)gridDim.x * blockDim.x) {
     const unsigned iu = (unsigned)i;
@@ -119,6 +128,7 @@ pooling_backward_fixed_kernel(T* in_grad, const T* in, const T* out, const T* ou
     const unsigned e0 = (plane * (unsigned)g.in_h + (unsigned)iy) * (unsigned)g.in_w + (unsigned)ix0;
     const unsigned out_base = plane * (unsigned)(g.out_h * g.out_w);
     const int oyh = (iy + g.pad_y) / ST;
+    const int wbase = (ix0 + g.pad_x - PADP) / ST;    // exact: (ix0 + pad_x) % ST == PADP
     Pack x, acc;
     if (OP == CB200_POOL_MAX) x = *reinterpret_cast<const Pack*>(in + e0);
     if (in_grad_alpha == 0.0) {
@@ -134,25 +144,42 @@ pooling_backward_fixed_kernel(T* in_grad, const T* in, const T* out, const T* ou
       const int oy = oyh - dy;
       const int rel_y = oy * ST - g.pad_y;
       const bool ok_y = oy >= 0 && oy < g.out_h && iy - rel_y < KS;
+      if (!ok_y) continue;
       const int exc_h = min(rel_y + KS, g.in_h) - max(rel_y, 0);
       const unsigned row_base = out_base + (unsigned)(oy * g.out_w);
+      T ov[NJ], gv[NJ];
+      int cnt[NJ];                                     // AVG_EXC_PAD: input positions the window really covers
+      bool ok[NJ];
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const int ox = wbase + JMIN + j;
+        ok[j] = ox >= 0 && ox < g.out_w;
+        ov[j] = (T)0; gv[j] = (T)0; cnt[j] = 1;
+        if (ok[j]) {
+          if (OP == CB200_POOL_MAX) ov[j] = out[row_base + (unsigned)ox];
+          gv[j] = out_grad[row_base + (unsigned)ox];
+          if (OP == CB200_POOL_AVG_EXC_PAD) {
+            const int rel_x = ox * ST - g.pad_x;
+            cnt[j] = (min(rel_x + KS, g.in_w) - max(rel_x, 0)) * exc_h;
+          }
+        }
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        const int ix = ix0 + e;
-        const int oxh = (ix + g.pad_x) / ST;
+        const int r = (e + PADP) % ST, q = (e + PADP) / ST;             // constants once unrolled
 #pragma unroll
         for (int dx = NW - 1; dx >= 0; --dx) {
-          const int ox = oxh - dx;
-          const int rel_x = ox * ST - g.pad_x;
-          if (ok_y && ox >= 0 && ox < g.out_w && ix - rel_x < KS) {
-            const unsigned o = row_base + (unsigned)ox;
-            if (OP == CB200_POOL_MAX) {
-              if (x.v[e] == out[o]) acc.v[e] = acc.v[e] + out_grad[o];
-            } else if (OP == CB200_POOL_AVG) {
-              acc.v[e] = (T)((double)acc.v[e] + (double)out_grad[o] / (double)(KS * KS));
-            } else {
-              const int exc_w = min(rel_x + KS, g.in_w) - max(rel_x, 0);
-              acc.v[e] = (T)((double)acc.v[e] + (double)out_grad[o] / (double)(exc_w * exc_h));
+          if (r + dx * ST < KS) {
+            const int j = q - dx - JMIN;
+            if (ok[j]) {
+              if (OP == CB200_POOL_MAX) {
+                // a + b in the element type IS the rounded exact sum: the reference's double add and its cast
+                if (x.v[e] == ov[j]) acc.v[e] = acc.v[e] + gv[j];
+              } else if (OP == CB200_POOL_AVG) {
+                acc.v[e] = (T)((double)acc.v[e] + (double)gv[j] / (double)(KS * KS));
+              } else {
+                acc.v[e] = (T)((double)acc.v[e] + (double)gv[j] / (double)cnt[j]);
+              }
             }
           }
         }
@@ -160,6 +187,16 @@ pooling_backward_fixed_kernel(T* in_grad, const T* in, const T* out, const T* ou
     }
     *reinterpret_cast<Pack*>(in_grad + e0) = acc;
   }
+}
+
+template <typename T, int OP, int VEC, int KS, int ST>
+void pooling_backward_fixed_launch(cb200_stream* s, unsigned blocks, T* in_grad, const T* in, const T* out, const T* out_grad,
+                                   const PoolBwdGeom& g, long long n_groups, double alpha) {
+  // the padding's remainder modulo the stride is a template constant of the kernel (0 or 1: strides 1 and 2)
+  if (ST == 1 || (g.pad_x % ST) == 0)
+    pooling_backward_fixed_kernel<T, OP, VEC, KS, ST, 0><<<blocks, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+  else
+    pooling_backward_fixed_kernel<T, OP, VEC, KS, ST, (ST > 1 ? 1 : 0)><<<blocks, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
 }
 
 template <typename T, int VEC, int KS, int ST>
@@ -170,21 +207,23 @@ void pooling_backward_launch_v(cb200_stream* s, int op, T* in_grad, const T* in,
   const long long cap = (long long)s->sm_count * 32;
   if (blocks > cap) blocks = cap;
   const unsigned b = (unsigned)blocks;
-  if (KS > 0) {
+  if constexpr (KS > 0) {
+    static_assert(ST == 1 || ST == 2, "fixed-window kernels exist for strides 1 and 2");
     if (op == CB200_POOL_MAX)
-      pooling_backward_fixed_kernel<T, CB200_POOL_MAX, VEC, (KS > 0 ? KS : 1), (ST > 0 ? ST : 1)><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+      pooling_backward_fixed_launch<T, CB200_POOL_MAX, VEC, KS, ST>(s, b, in_grad, in, out, out_grad, g, n_groups, alpha);
     else if (op == CB200_POOL_AVG)
-      pooling_backward_fixed_kernel<T, CB200_POOL_AVG, VEC, (KS > 0 ? KS : 1), (ST > 0 ? ST : 1)><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+      pooling_backward_fixed_launch<T, CB200_POOL_AVG, VEC, KS, ST>(s, b, in_grad, in, out, out_grad, g, n_groups, alpha);
     else
-      pooling_backward_fixed_kernel<T, CB200_POOL_AVG_EXC_PAD, VEC, (KS > 0 ? KS : 1), (ST > 0 ? ST : 1)><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+      pooling_backward_fixed_launch<T, CB200_POOL_AVG_EXC_PAD, VEC, KS, ST>(s, b, in_grad, in, out, out_grad, g, n_groups, alpha);
     return;
+  } else {
+    if (op == CB200_POOL_MAX)
+      pooling_backward_kernel<T, CB200_POOL_MAX, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+    else if (op == CB200_POOL_AVG)
+      pooling_backward_kernel<T, CB200_POOL_AVG, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
+    else
+      pooling_backward_kernel<T, CB200_POOL_AVG_EXC_PAD, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
   }
-  if (op == CB200_POOL_MAX)
-    pooling_backward_kernel<T, CB200_POOL_MAX, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
-  else if (op == CB200_POOL_AVG)
-    pooling_backward_kernel<T, CB200_POOL_AVG, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
-  else
-    pooling_backward_kernel<T, CB200_POOL_AVG_EXC_PAD, VEC, KS, ST><<<b, 256, 0, s->stream>>>(in_grad, in, out, out_grad, g, n_groups, alpha);
 }
 
 template <typename T>

@@ -41,6 +41,9 @@ POOL_GEOMETRIES = (
     (1, 4, 9, 10, 2, 2, 1, 1, 1, 1, "floor"), (3, 2, 11, 13, 3, 3, 1, 1, 2, 1, "ceil"),
     (1, 2, 10, 10, 2, 2, 0, 0, 3, 3, "floor"),       # stride > window: some inputs belong to no window
     (2, 3, 24, 24, 2, 2, 0, 0, 2, 2, "floor"),       # the reference MNIST network's pooling layers
+    # vector-width rows with the window / stride pairs that have their own kernels, every padding remainder
+    (2, 4, 16, 16, 3, 3, 0, 0, 2, 2, "ceil"), (1, 3, 12, 12, 3, 3, 2, 2, 2, 2, "floor"),
+    (2, 3, 8, 8, 3, 3, 1, 1, 1, 1, "floor"), (1, 4, 8, 8, 2, 2, 1, 1, 2, 2, "floor"), (1, 2, 8, 12, 3, 3, 1, 0, 2, 2, "ceil"),
 )
 
 
