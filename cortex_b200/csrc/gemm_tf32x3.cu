@@ -410,21 +410,43 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   p.a_mn_major = trans_a ? 1 : 0;   // op(A)[m][k] = A[k][m]: M is the contiguous axis
   p.b_mn_major = trans_b ? 0 : 1;   // op(B)[k][n] = B[k][n]: N is the contiguous axis
   p.store_mode = store_mode; p.hw = hw > 0 ? hw : 1; p.flags = flags; p.status = s->status_dev;
-  // widest tile that still gives every SM a CTA (small problems are latency-bound: more, narrower
-  // tiles finish sooner than two wide ones)
-  int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  // ---- tile width and K slices --------------------------------------------------------------------
+  // Problems whose tiles (at the widest useful width) do not fill the SMs are latency-bound, and two knobs
+  // trade against each other: narrower tiles and more K slices both put more CTAs to work, but a narrow tile
+  // re-reads more operand bytes per flop from shared memory (a k-block of 16 costs 0.39 / 0.455 / 0.56 us at
+  // 64 / 128 / 256 columns: 1.4x the time for 4x the work) and every slice adds to the hand-over through L2
+  // ((BN / 64) x (1.3 + 0.45 x slices) us).  The pair is chosen by that model, fitted to a sweep of twelve
+  // shapes x three widths x seven slice counts (it predicts each of them within ~10 %):
+  //     t = waves x (5 us + ceil(k-blocks / slices) x c[BN]) + hand-over,    slices > 1 only within one wave.
+  // Against the earlier rule (narrow while one wave holds the tiles, then slice), us per call:
+  //     1024^3 30.9 -> 25.2, 768 x 768 x 3072 46.1 -> 33.2, 1536^3 51.8 -> 43.1, 1024 x 512 x 2048 33.5 -> 25.9,
+  //     256 x 1024 x 4096 34.1 -> 27.2, 640 x 1280 x 1280 36.6 -> 28.4; unchanged where that rule was already best.
+  // Every column tile re-reads its rows of A from DRAM once A no longer stays in L2 (>= 24 MB, and A the larger
+  // operand): the widest tile is kept there whatever the model says (measured: 4096 x 512 x 4096 232 -> 108 us,
+  // 2048 x 1024 x 4096 220 -> 107, 8192 x 125 x 4096 159 -> 132 when that was introduced).
+  const int bn_max = N > 128 ? 256 : (N > 64 ? 128 : 64);
   const long long tiles_m = (M + BM - 1) / BM;
-  // Tile width for problems that do not fill the SMs.  Every column tile re-reads its rows of A, so when A is too
-  // large to stay hot in L2 (>= 24 MB) the widest tile that covers N is kept and the SMs are filled by slicing K
-  // (below).  Otherwise tiles are narrowed while they still fit ONE wave (narrower tiles finish sooner and make
-  // the slices' hand-over cheaper); narrowing into a second, partly empty wave never pays.
-  // Measured (us per call, old rule "narrow until every SM has a tile" -> this rule): 4096x512x4096 232 -> 108,
-  // 2048x1024x4096 220 -> 107, 8192x250x4096 293 -> 204, 8192x125x4096 159 -> 132, 1024x4096x1024 84 -> 60,
-  // 512x512x2048 58 -> 29.
-  // (when B is the larger operand, as in a weight gradient whose reduction runs over every pixel of a batch, the
-  // re-reads of A are the smaller cost and narrow tiles are what spreads the work)
+  const int nkb_model = (K + 15) / 16;
   const bool big_a = (long long)M * K * 4 >= (24ll << 20) && (long long)M >= (long long)N;
-  while (BN > 64 && !big_a && tiles_m * ((N + BN / 2 - 1) / (BN / 2)) <= s->sm_count) BN >>= 1;
+  const bool may_slice = !((flags & FLAG_SPLIT_K) && K >= 4096 && store_mode == STORE_ROW_MAJOR) && !(flags & FLAG_ONE_TERM);
+  int BN = bn_max, model_slices = 1;
+  {
+    double best = 1e30;
+    for (int bn = 256; bn >= 64; bn >>= 1) {
+      if (bn > bn_max) continue;
+      if (s->opt_gemm_tile_n > 0 ? bn != s->opt_gemm_tile_n : (big_a && bn != bn_max)) continue;
+      const double c_kb = bn == 256 ? 0.56 : (bn == 128 ? 0.455 : 0.39);
+      const long long tiles = tiles_m * ((N + bn - 1) / bn);
+      for (int sl = 1; sl <= 32; ++sl) {
+        if (sl > 1 && (!may_slice || tiles * sl > s->sm_count || nkb_model / sl < 4)) break;
+        const long long waves = (tiles * sl + s->sm_count - 1) / s->sm_count;
+        const double t = (double)waves * (5.0 + (double)((nkb_model + sl - 1) / sl) * c_kb) +
+                         (sl > 1 ? (bn / 64) * (1.3 + 0.45 * sl) : 0.0);
+        if (t < best - 1e-9) { best = t; BN = bn; model_slices = sl; }      // ties: the wider tile, fewer slices
+      }
+    }
+    if (s->opt_gemm_tile_n > 0 && s->opt_gemm_tile_n > bn_max) BN = s->opt_gemm_tile_n;   // forced wider than N needs
+  }
   const int tiles_n = (N + BN - 1) / BN;
   const long long panel_bytes = (long long)BN * K * 4;          // one column tile's share of B
   // FLAG_SPLIT_K (the fused layer entry points): reductions of 4096 and more are cut in two K halves per
@@ -441,24 +463,19 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
     int rcf = cb200_tile_flags(s, (size_t)tiles_m * tiles_n, &p.tile_flags);
     if (rcf) return rcf;
   }
-  // Problems that leave more than half of the SMs without a tile: ksplit_n CTAs per tile, each over a slice of K
-  // (at least 8 k-blocks per slice), combined by the last one to finish.
+  // K slices: model_slices CTAs per tile, each over a slice of K, combined by the last one to finish.  The stream
+  // option forces a count (old caps: at least 8 k-blocks per slice, slices x BN <= 1024, at most 16).
   p.ksplit_n = 1;
   p.ksplit_ws = nullptr;
   {
     const long long tiles = tiles_m * tiles_n;
     const int nkb_all = (K + 15) / 16;
-    long long sl = s->sm_count / (tiles > 0 ? tiles : 1);
-    if (s->opt_gemm_k_slices > 0) sl = s->opt_gemm_k_slices;
-    if (sl > nkb_all / 8) sl = nkb_all / 8;
-    if (sl > 1024 / BN) sl = 1024 / BN;       // the CTA that combines a tile reads slices x 128 x BN floats
-    if (sl > 16) sl = 16;
-    // reductions so long that even 16 slices are hundreds of k-blocks each (a weight gradient summed over every
-    // pixel of a batch): the hand-over is amortised, fill the SMs
-    if (s->opt_gemm_k_slices == 0 && nkb_all / 32 >= 256) {
-      long long fill = s->sm_count / (tiles > 0 ? tiles : 1);
-      if (fill > 32) fill = 32;
-      if (fill > sl) sl = fill;
+    long long sl = model_slices;
+    if (s->opt_gemm_k_slices > 0) {
+      sl = s->opt_gemm_k_slices;
+      if (sl > nkb_all / 8) sl = nkb_all / 8;
+      if (sl > 1024 / BN) sl = 1024 / BN;
+      if (sl > 16) sl = 16;
     }
     if (p.k_split == 1 && sl >= 2 && !(flags & FLAG_ONE_TERM)) {
       void* ws = nullptr;
