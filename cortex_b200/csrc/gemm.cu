@@ -11,6 +11,7 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
                                    const float* A, int M, int K, long long lda, const float* B, int N, long long ldb,
                                    float beta, const float* bias, int act, int store_mode, int hw, int flags,
                                    int n_peers, float* const* peers);
+int cb200_gemm_tf32x3_max_slices(const cb200_stream* s, int M, int N);
 bool cb200_gemm_tf32x3_eligible(const float* A, long long lda, const float* B, long long ldb, int M, int N, int K);
 int cb200_gemm_f64_launch(cb200_stream* s, double* C, long long ldc, int trans_a, int trans_b, double alpha,
                           const double* A, int M, int K, long long lda, const double* B, int N, long long ldb,
@@ -256,16 +257,22 @@ int gemm_impl(cb200_stream* s, int dtype, void* C, int64_t ldc, int trans_a, int
       if (K <= K_CHUNK)
         return tc_f32(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, a, M, K, lda, b, N, ldb, (float)beta,
                       (const float*)bias, act, peers, tc_flags);
-      const int n_chunks = (K + K_CHUNK - 1) / K_CHUNK;
+      // A problem with few output tiles gets its K slices inside ONE launch (up to max_sl CTAs per tile, each
+      // over at most K_CHUNK of the reduction, combined in slice order by round-to-nearest adds): a launch then
+      // covers K_CHUNK * max_sl of K instead of K_CHUNK (576 x 64 x 200704: 49 launches, 0.95 ms -> 2 launches).
+      const int max_sl = (layer_stack || (peers && peers->n > 0)) ? 1 : cb200_gemm_tf32x3_max_slices(s, M, N);
+      const long long span = (long long)K_CHUNK * max_sl;
+      const int n_chunks = (int)((K + span - 1) / span);
       const int chunk = ((K + n_chunks - 1) / n_chunks + 15) / 16 * 16;     // even chunks, whole k-blocks
       for (int k0 = 0; k0 < K; k0 += chunk) {
         const int kc = (K - k0 < chunk) ? (K - k0) : chunk;
         const bool last = k0 + kc >= K;
         const float* ak = trans_a ? a + (long long)k0 * lda : a + k0;
         const float* bk = trans_b ? b + k0 : b + (long long)k0 * ldb;
+        const int need = (kc + K_CHUNK - 1) / K_CHUNK;
         int rc = tc_f32(s, (float*)C, ldc, trans_a, trans_b, (float)alpha, ak, M, kc, lda, bk, N, ldb,
                         k0 == 0 ? (float)beta : 1.0f, last ? (const float*)bias : nullptr, last ? act : 0,
-                        last ? peers : nullptr, tc_flags);
+                        last ? peers : nullptr, tc_flags | (need > 1 ? need << 8 : 0));
         if (rc) return rc;
       }
       return CB200_OK;

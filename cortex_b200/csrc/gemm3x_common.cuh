@@ -9,7 +9,7 @@ namespace gemm3x {
 using namespace sm100;
 
 enum { STORE_ROW_MAJOR = 0, STORE_NCHW = 1 };
-enum { FLAG_ONE_TERM = 1, FLAG_SPLIT_K = 2 };
+enum { FLAG_ONE_TERM = 1, FLAG_SPLIT_K = 2, FLAG_MIN_SLICES_SHIFT = 8 };   // bits 8..15: at least that many K slices
 enum { MAX_PEERS = 7 };
 
 struct GemmParams {

@@ -396,6 +396,14 @@ int cb200_gemm_tf32x3_launch(cb200_stream* s, float* C, long long ldc, int trans
                                         store_mode, hw, flags, 0, nullptr);
 }
 
+// Most K slices one launch can give a problem (every tile's slices run side by side in one wave); 1 = none.
+int cb200_gemm_tf32x3_max_slices(const cb200_stream* s, int M, int N) {
+  const int bn_max = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn_max - 1) / bn_max);
+  long long sl = tiles > 0 ? s->sm_count / tiles : 1;
+  return (int)(sl < 1 ? 1 : (sl > 32 ? 32 : sl));
+}
+
 // The same launch with up to MAX_PEERS extra destinations: every output tile is also stored to
 // peers[d] + (the same row-major position), d < n_peers.
 int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int trans_a, int trans_b, float alpha,
@@ -429,7 +437,8 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   const int nkb_model = (K + 15) / 16;
   const bool big_a = (long long)M * K * 4 >= (24ll << 20) && (long long)M >= (long long)N;
   const bool may_slice = !((flags & FLAG_SPLIT_K) && K >= 4096 && store_mode == STORE_ROW_MAJOR) && !(flags & FLAG_ONE_TERM);
-  int BN = bn_max, model_slices = 1;
+  const int min_slices = (flags >> FLAG_MIN_SLICES_SHIFT) & 0xff;      // a long reduction the caller wants cut up
+  int BN = bn_max, model_slices = min_slices > 1 ? min_slices : 1;
   {
     double best = 1e30;
     for (int bn = 256; bn >= 64; bn >>= 1) {
@@ -437,7 +446,7 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
       if (s->opt_gemm_tile_n > 0 ? bn != s->opt_gemm_tile_n : (big_a && bn != bn_max)) continue;
       const double c_kb = bn == 256 ? 0.56 : (bn == 128 ? 0.455 : 0.39);
       const long long tiles = tiles_m * ((N + bn - 1) / bn);
-      for (int sl = 1; sl <= 32; ++sl) {
+      for (int sl = min_slices > 1 ? min_slices : 1; sl <= 32; ++sl) {
         if (sl > 1 && (!may_slice || tiles * sl > s->sm_count || nkb_model / sl < 4)) break;
         const long long waves = (tiles * sl + s->sm_count - 1) / s->sm_count;
         const double t = (double)waves * (5.0 + (double)((nkb_model + sl - 1) / sl) * c_kb) +
@@ -471,7 +480,7 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
     const long long tiles = tiles_m * tiles_n;
     const int nkb_all = (K + 15) / 16;
     long long sl = model_slices;
-    if (s->opt_gemm_k_slices > 0) {
+    if (s->opt_gemm_k_slices > 0 && min_slices <= 1) {
       sl = s->opt_gemm_k_slices;
       if (sl > nkb_all / 8) sl = nkb_all / 8;
       if (sl > 1024 / BN) sl = 1024 / BN;

@@ -598,3 +598,35 @@ def test_classifier_head_with_fused_softmax(b200_driver, datatype, M, N, K, act)
     assert np.array_equal(outs[0][:, N:], C0[:, N:])          # the pitch padding is not touched
     assert np.array_equal(outs[0], outs[1])
     stream.sync()
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb", [(256, 256, 8192, False, True), (300, 72, 50000, False, True),
+                                         (500, 784, 20000, True, False), (64, 24, 140000, False, True),
+                                         (1024, 1024, 8192, False, True)])
+def test_long_reduction_is_cut_inside_one_launch(b200_driver, M, N, K, ta, tb):
+    """gemm! with K above 4096: tcgen05 accumulates with truncation, so the reduction is cut into pieces of at
+    most 4096 joined by round-to-nearest adds.  Problems with few output tiles get the pieces as K slices of one
+    launch (a weight gradient summed over a whole batch), the others as chained launches; all-positive operands
+    are the worst case for the drift.  Against float64, twice for run-to-run equality."""
+    rng = np.random.default_rng(M + N + K)
+    A = (rng.random((K, M) if ta else (M, K)) + 0.5).astype(np.float32)
+    B = (rng.random((N, K) if tb else (K, N)) + 0.5).astype(np.float32)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    stream = b200_driver.default_device().create_stream()
+    outs = []
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        a, b = ct.to_tensor(A), ct.to_tensor(B)
+        for _ in range(2):
+            c = ct.to_tensor(C0)
+            before = stream.launch_count()
+            ct.gemm(c, ta, tb, 0.75, a, b, 0.5)
+            launches = stream.launch_count() - before
+            outs.append(ct.to_array(c).reshape(M, N))
+    opA = A.T.astype(np.float64) if ta else A.astype(np.float64)
+    opB = B.T.astype(np.float64) if tb else B.astype(np.float64)
+    exact = 0.75 * (opA @ opB) + 0.5 * C0
+    assert pc.rel_err(outs[0], exact) <= pc.TOL["float"]
+    assert np.array_equal(outs[0], outs[1])
+    if M * N <= 256 * 256:
+        assert launches <= 2, launches          # slices inside the launch, not one launch per 4096 of K
+    stream.sync()
