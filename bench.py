@@ -885,14 +885,51 @@ def run_b200(args, rank, world, local_rank):
         ms_step = e1.elapsed_ms_since(e0) / args.steps
         gemm_ms = float(np.mean([b.elapsed_ms_since(a) for a, b in gemm_events]))
         # rows of the resident result kept for the parity object below
-        parity_rows = np.random.default_rng(1000 + rank).choice(rows, size=16, replace=False)
-        resident_sample = ct.to_array(resident_out).reshape(rows, CLASSES)[parity_rows].copy()
+        resident_all = ct.to_array(resident_out).reshape(rows, CLASSES).copy()     # this rank's rows [lo, hi)
 
         # ---- end to end: pinned host in -> H2D -> layers -> D2H, every step --------------------
         # chunks of 4096-8192 rows (>= 256 pair tiles each, two waves of the 74 clusters or more), three
         # rotating input slots so that two uploads can be in flight under one chunk's compute
-        chunk = min(8192, max(4096, rows // 2))
+        def chunk_for(n):
+            return min(8192, max(4096, n // 2))
+
+        # Host-fed sharding.  The GPUs of one box do not all get the same host-link bandwidth (measured on an
+        # 8-GPU box of this pool: GPUs 0-3 ~20 GB/s each, GPUs 4-7 ~29 GB/s with all eight uploading), and with
+        # even shards the pass ends when the slowest link ends.  Two calibration steps with even shards, every
+        # rank at once, give each rank's rate (rows / its own device time); the rows are then re-dealt in
+        # proportion, in multiples of 512, unless the rates are within 8 % of each other.  No data moves between
+        # ranks: every rank regenerates the rows of its new range from the seeds.
+        e2e_lo, e2e_hi = lo, hi
+        rates = None
+        if dist is not None and not args.even_shards:
+            cal = BatchPipeline(dev, net, WIDTH, CLASSES, chunk_for(rows), dt, slots=3)
+            cal.run(x_host, y_host, rows)
+            barrier()
+            c0 = cal.compute.create_event(timing=True)
+            for _ in range(2):
+                cal.run(x_host, y_host, rows, wait=False)
+            cal.drain()
+            cal.download.sync()
+            c1 = cal.compute.create_event(timing=True)
+            c1.wait_for_event()
+            my_rate = rows / max(c1.elapsed_ms_since(c0), 1e-6)
+            cal.release()
+            gathered = [torch.zeros(1, device="cuda", dtype=torch.float64) for _ in range(world)]
+            dist.all_gather(gathered, torch.tensor([my_rate], device="cuda", dtype=torch.float64))
+            rates = [float(g_[0]) for g_ in gathered]
+            if args.shard_rates:                       # testing aid: pretend these were the measured rates
+                rates = [float(v) for v in args.shard_rates.split(",")]
+                assert len(rates) == world, "--shard-rates wants one value per rank"
+            from cortex_b200.parallel import weighted_shard_bounds
+            e2e_lo, e2e_hi = weighted_shard_bounds(BATCH, rates, quantum=512, keep_equal_within=0.08)[rank]
+        e2e_rows = e2e_hi - e2e_lo
+        if (e2e_lo, e2e_hi) != (lo, hi):
+            x_host = drv.allocate_host_buffer(e2e_rows * WIDTH, dt, near=dev)
+            x_host.as_numpy()[:] = make_input(e2e_lo, e2e_hi).astype(npdt).reshape(-1)
+            y_host = drv.allocate_host_buffer(e2e_rows * CLASSES, dt, near=dev)
+        chunk = chunk_for(e2e_rows)
         pipe = BatchPipeline(dev, net, WIDTH, CLASSES, chunk, dt, slots=3)
+        resident_rows, rows = rows, e2e_rows          # from here on `rows` is this rank's host-fed row count
         h2d = d2h = 0
         for _ in range(min(args.warmup, 3)):
             pipe.run(x_host, y_host, rows)
@@ -920,11 +957,18 @@ def run_b200(args, rank, world, local_rank):
         probs = y_host.as_numpy().reshape(rows, CLASSES)
         checksum = float(np.abs(probs.sum(axis=1) - 1.0).max())
         # parity of what came back through the pipeline: sampled rows of this rank's shard against float64
+        parity_rows = np.random.default_rng(1000 + rank).choice(rows, size=min(16, rows), replace=False)
         want = fp64_forward(x_host.as_numpy().reshape(rows, WIDTH)[parity_rows], weights)
         parity_err = rel_err(probs[parity_rows], want)
         # host-fed chunks and the resident shard differ in row count, so the GEMM may share the K range of some
-        # tiles differently (same products, another summation order): compared at rounding level, not bit for bit
-        e2e_vs_resident = rel_err(probs[parity_rows], resident_sample.astype(np.float64))
+        # tiles differently (same products, another summation order): compared at rounding level, not bit for bit,
+        # on rows this rank holds in both arms (global rows [lo, hi) resident, [e2e_lo, e2e_hi) host-fed)
+        both_lo, both_hi = max(lo, e2e_lo), min(hi, e2e_hi)
+        if both_hi > both_lo:
+            common = both_lo + np.random.default_rng(2000 + rank).choice(both_hi - both_lo, size=min(16, both_hi - both_lo), replace=False)
+            e2e_vs_resident = rel_err(probs[common - e2e_lo], resident_all[common - lo].astype(np.float64))
+        else:
+            e2e_vs_resident = 0.0
         column_head = bench_column_head(dev, stream, world, rank, dt, dist) if world > 1 else None
 
     # max over ranks
@@ -934,14 +978,18 @@ def run_b200(args, rank, world, local_rank):
         t = torch.tensor([ms_step, e2e_ms, parity_err, e2e_vs_resident], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step, e2e_ms, parity_err, e2e_vs_resident = float(t[0]), float(t[1]), float(t[2]), float(t[3])
-        lt = torch.tensor([launches], device="cuda", dtype=torch.int64)
+        lt = torch.tensor([launches, h2d, d2h], device="cuda", dtype=torch.int64)
         dist.all_reduce(lt, op=dist.ReduceOp.SUM)
-        launches = int(lt[0])
+        launches, h2d_all, d2h_all = int(lt[0]), int(lt[1]), int(lt[2])
+        rows_t = [torch.zeros(1, device="cuda", dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(rows_t, torch.tensor([rows], device="cuda", dtype=torch.int64))
+        e2e_rows_per_rank = [int(r_[0]) for r_ in rows_t]
         gathered = [torch.zeros(4, device="cuda", dtype=torch.float64) for _ in range(world)]
         dist.all_gather(gathered, torch.tensor(rank_stats, device="cuda", dtype=torch.float64))
         all_stats = [[float(v) for v in g] for g in gathered]
     else:
         all_stats = [rank_stats]
+        h2d_all, d2h_all, e2e_rows_per_rank = h2d, d2h, [rows]
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -949,7 +997,7 @@ def run_b200(args, rank, world, local_rank):
 
     value = BATCH / (ms_step / 1000.0)
     e2e_value = BATCH / (e2e_ms / 1000.0)
-    gemm_rows = min(rows, row_block) if row_block else rows
+    gemm_rows = min(resident_rows, row_block) if row_block else resident_rows
     gemm_flops = 2.0 * gemm_rows * WIDTH * WIDTH
     timed_s = ms_step * args.steps / 1000.0
     regime = "sustained" if timed_s >= 1.0 else "burst"
@@ -980,11 +1028,16 @@ def run_b200(args, rank, world, local_rank):
         "metric": "wide_mlp_inference_samples_per_s" + ("" if dt == "float" else "_fp64"), "value": value, "unit": "samples/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32" if dt == "float" else "f64", "data": "synthetic",
-        "config": config, "rows_per_gpu": rows, "row_block": row_block, "kernel_path": kernel_path,
+        "config": config, "rows_per_gpu": resident_rows, "row_block": row_block, "kernel_path": kernel_path,
         "gpu_indices": [rank_device(r, world, visible) for r in range(world)],
         "tflops": value * FLOPS_PER_SAMPLE / 1e12,
-        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+        "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": h2d_all, "d2h_bytes_per_step": d2h_all,
                 "ms_per_step": e2e_ms, "chunk_rows": chunk, "input_slots": pipe.slots,
+                "rows_per_rank": e2e_rows_per_rank,
+                "sharding": ("even" if len(set(e2e_rows_per_rank)) <= 1 else
+                             "rows in proportion to each rank's host-fed rate in two calibration steps with even "
+                             "shards (multiples of 512; even when the rates are within 8 %)"),
+                "calibration_rows_per_ms": [round(r_, 1) for r_ in rates] if rates else None,
                 "host_buffer_numa_node": getattr(x_host, "numa_node", -1),
                 "max_abs_rowsum_minus_1": checksum, "clocks": e2e_clocks,
                 "per_rank": [{"h2d_gbs": round(s_[0], 2), "d2h_gbs": round(s_[1], 2), "forward_ms_per_chunk": round(s_[2], 3),
@@ -1035,6 +1088,11 @@ def main():
     ap.add_argument("--row-block", type=int, default=-1,
                     help="resident arm: run the layer stack depth-first over blocks of this many rows "
                          "(0 = whole shard per layer, -1 = automatic)")
+    ap.add_argument("--even-shards", action="store_true",
+                    help="N > 1: keep the even row split for the host-fed arm (no calibration / re-dealing)")
+    ap.add_argument("--shard-rates", default="",
+                    help="N > 1, testing aid: comma-separated rates to re-deal the host-fed rows by, instead of the "
+                         "calibrated ones (e.g. 1,1.5 on two GPUs exercises the uneven path)")
     ap.add_argument("--no-peaks", action="store_true",
                     help="skip the measurement-only library matmul peaks (rooflines then use the bf16-derived proxy)")
     ap.add_argument("--case", default="mlp", choices=["mlp", "gemm4096", "eltwise", "conv", "gemm4096f64", "mlp128", "mlplayer", "mnistcnn", "backward"],

@@ -32,6 +32,39 @@ def shard_bounds(total, world_size, rank):
     return lo, lo + base + (1 if rank < rem else 0)
 
 
+def weighted_shard_bounds(total, rates, quantum=1, keep_equal_within=0.0):
+    """[lo, hi) for every rank with row counts proportional to `rates` (each rank's measured throughput), in
+    multiples of `quantum` rows (the last rank takes the remainder), every rank keeping at least one quantum.
+    Batch sharding is embarrassingly parallel, so ranks may own different amounts: on a box whose GPUs do not
+    all get the same host-link bandwidth the host-fed pass ends when the slowest link ends, and rows in
+    proportion to the rates make the links end together.  When the rates are within `keep_equal_within`
+    (relative, max over min minus 1) of each other the even split of shard_bounds() is returned."""
+    world = len(rates)
+    total, quantum = int(total), max(1, int(quantum))
+    if world < 1 or any(not (r > 0) for r in rates):
+        raise ValueError("rates must be positive, one per rank")
+    if max(rates) / min(rates) - 1.0 <= keep_equal_within or total < world * quantum:
+        return [shard_bounds(total, world, r) for r in range(world)]
+    units = total // quantum                                   # whole quanta to hand out
+    share = [units * r / float(sum(rates)) for r in rates]
+    counts = [max(1, int(sh)) for sh in share]
+    # largest remainders first until the quanta are used up (or taken back where the floor of 1 overshot)
+    order = sorted(range(world), key=lambda i: share[i] - int(share[i]), reverse=True)
+    i = 0
+    while sum(counts) < units:
+        counts[order[i % world]] += 1
+        i += 1
+    while sum(counts) > units:
+        j = max(range(world), key=lambda k: counts[k])
+        counts[j] -= 1
+    bounds, lo = [], 0
+    for r in range(world):
+        hi = total if r == world - 1 else lo + counts[r] * quantum
+        bounds.append((lo, hi))
+        lo = hi
+    return bounds
+
+
 def shard_rows(array, world_size, rank):
     lo, hi = shard_bounds(array.shape[0], world_size, rank)
     return array[lo:hi]

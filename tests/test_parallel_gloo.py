@@ -92,3 +92,26 @@ def test_two_gloo_ranks_match_single_rank(tmp_path):
         full = np.load(tmp_path / ("full_%d.npy" % r))
         assert np.max(np.abs(full - ref)) <= 1e-5          # identical probabilities on every rank
     assert np.array_equal(np.load(tmp_path / "full_0.npy"), np.load(tmp_path / "full_1.npy"))
+
+
+def test_weighted_shard_bounds():
+    from cortex_b200.parallel import shard_bounds, weighted_shard_bounds
+    # the host-link rates seen on an 8-GPU box: GPUs 0-3 at ~20 GB/s, 4-7 at ~29 GB/s
+    rates = [20.0] * 4 + [29.0] * 4
+    spans = weighted_shard_bounds(65536, rates, quantum=512)
+    assert spans[0][0] == 0 and spans[-1][1] == 65536
+    assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    sizes = [hi - lo for lo, hi in spans]
+    assert all(sz % 512 == 0 and sz > 0 for sz in sizes)
+    assert abs(sizes[0] / 65536 - 20.0 / 196.0) < 0.01 and abs(sizes[7] / 65536 - 29.0 / 196.0) < 0.01
+    # rates within the tolerance: the even split
+    assert weighted_shard_bounds(1000, [1.0, 1.04, 0.99], 8, keep_equal_within=0.08) == [shard_bounds(1000, 3, r) for r in range(3)]
+    # a rank that is almost idle keeps one quantum; the remainder (total not a multiple of the quantum) goes last
+    spans = weighted_shard_bounds(1003, [1e-3, 1.0, 1.0], 8)
+    assert spans[0] == (0, 8) and spans[-1][1] == 1003 and all(hi > lo for lo, hi in spans)
+    for total, rates, q in ((7, [1.0, 2.0], 1), (4096, [3.0, 1.0, 1.0, 1.0], 256), (100, [5.0, 1.0], 64)):
+        spans = weighted_shard_bounds(total, rates, q)
+        assert spans[0][0] == 0 and spans[-1][1] == total and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert all(hi > lo for lo, hi in spans)
+    with pytest.raises(ValueError):
+        weighted_shard_bounds(10, [1.0, 0.0])
