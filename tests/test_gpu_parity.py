@@ -630,3 +630,30 @@ def test_long_reduction_is_cut_inside_one_launch(b200_driver, M, N, K, ta, tb):
     if M * N <= 256 * 256:
         assert launches <= 2, launches          # slices inside the launch, not one launch per 4096 of K
     stream.sync()
+
+
+def test_gemm_tile_width_and_slices_are_interchangeable(b200_driver):
+    """The launch picks the tile width and the number of K slices from a timing model; every pair it could pick
+    (forced here through the stream options) computes the same product within the fp32 bound, ragged edges and
+    alpha / beta included.  Values outside the option's domain are rejected."""
+    M, N, K = 300, 328, 1040
+    rng = np.random.default_rng(77)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((N, K)).astype(np.float32)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    exact = 1.5 * (A.astype(np.float64) @ B.astype(np.float64).T) + 0.5 * C0
+    stream = b200_driver.default_device().create_stream()
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        a, b = ct.to_tensor(A), ct.to_tensor(B)
+        for tile_n in (0, 64, 128, 256):
+            for slices in (0, 1, 2, 4):
+                stream.set_option("gemm-tile-n", tile_n)
+                stream.set_option("gemm-k-slices", slices)
+                c = ct.to_tensor(C0)
+                ct.gemm(c, False, True, 1.5, a, b, 0.5)
+                assert pc.rel_err(ct.to_array(c).reshape(M, N), exact) <= pc.TOL["float"], (tile_n, slices)
+        stream.set_option("gemm-tile-n", 0)
+        stream.set_option("gemm-k-slices", 0)
+        with pytest.raises(Exception):
+            stream.set_option("gemm-tile-n", 96)
+    stream.sync()
