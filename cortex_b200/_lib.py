@@ -100,6 +100,7 @@ SIGNATURES = {
     "cb200_convolution_backward_weights": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
     "cb200_convolution_backward_data": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, _vp, _i64, C.POINTER(ConvDesc)],
     "cb200_convolution_forward_static": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, C.POINTER(ConvDesc)],
+    "cb200_convolution_forward_bias_act": [_vp, _i, _vp, _pd, _d, _vp, _pd, _vp, _pd, C.POINTER(ConvDesc), _vp, _i],
     "cb200_ternary_op": [_vp, _i, _vp, _pd, _vp, _pd, _d, _vp, _pd, _d, _vp, _pd, _d, _i64, _i],
     "cb200_gemv": [_vp, _i, _vp, _i64, _i, _d, _vp, _i64, _i64, _i64, _vp, _i64, _d],
     "cb200_batch_normalize_eltwise": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _d, _i64, _i64],

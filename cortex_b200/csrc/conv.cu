@@ -29,17 +29,17 @@ int cb200_gemm_simt_f32_launch(cb200_stream* s, float* C, long long ldc, int tra
                                float beta);
 int cb200_conv_igemm_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                             int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
-                            int stride_x, int stride_y, float out_alpha);
+                            int stride_x, int stride_y, float out_alpha, const float* bias, int act);
 
 bool cb200_conv_halo_eligible(int cin, int cout, int out_w, int out_h, int kh, int kw, int stride_x, int stride_y,
                               long long in_elems);
 int cb200_conv_halo_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                            int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
-                           float out_alpha);
+                           float out_alpha, const float* bias, int act);
 bool cb200_conv_tma_eligible(int cin, int out_w, int out_h, int stride_x, int stride_y, long long in_elems);
 int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                           int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
-                          float out_alpha);
+                          float out_alpha, const float* bias, int act);
 
 // fp32 forward convolution on dense NCHW tensors, routed by geometry.  Stride-1 layers with a multiple of 16 input
 // channels: every operand tile by TMA -- the input patch kept in shared memory across the filter taps
@@ -54,16 +54,25 @@ bool cb200_conv_forward_f32_uses_tma(const cb200_stream* s, int batch, int cin, 
   return s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, out_w, out_h, stride_x, stride_y, in_elems);
 }
 
+// out = act(conv(in, w) + out_alpha * out + bias[channel]): bias (may be null) and the activation (enum cb200_act)
+// are applied in the epilogue of whichever kernel runs the layer.
+int cb200_conv_forward_f32_bias_act(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin,
+                                    int in_h, int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x,
+                                    int pad_y, int stride_x, int stride_y, float out_alpha, const float* bias, int act) {
+  const long long in_elems = (long long)batch * cin * in_h * in_w;
+  if ((s->opt_conv_route == 0 || s->opt_conv_route == 3) && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
+    return cb200_conv_halo_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha, bias, act);
+  if (s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, out_w, out_h, stride_x, stride_y, in_elems))
+    return cb200_conv_tma_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha, bias, act);
+  return cb200_conv_igemm_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, stride_x,
+                                 stride_y, out_alpha, bias, act);
+}
+
 int cb200_conv_forward_f32(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                            int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y, int stride_x,
                            int stride_y, float out_alpha) {
-  const long long in_elems = (long long)batch * cin * in_h * in_w;
-  if ((s->opt_conv_route == 0 || s->opt_conv_route == 3) && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
-    return cb200_conv_halo_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha);
-  if (s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, out_w, out_h, stride_x, stride_y, in_elems))
-    return cb200_conv_tma_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha);
-  return cb200_conv_igemm_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, stride_x,
-                                 stride_y, out_alpha);
+  return cb200_conv_forward_f32_bias_act(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y,
+                                         stride_x, stride_y, out_alpha, nullptr, 0);
 }
 
 namespace {
@@ -96,6 +105,19 @@ im2col_kernel(T* cols, const T* in, ConvGeom g, long long total) {
   }
 }
 
+// fp64 layers: bias per output channel and activation over the finished NCHW output
+__global__ void __launch_bounds__(256)
+conv_bias_act_f64_kernel(double* out, const double* bias, int act, unsigned hw, unsigned channels, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    double v = out[i];
+    if (bias) v += bias[(unsigned)((i / hw) % channels)];
+    if (act == CB200_ACT_RELU) v = v > 0.0 ? v : 0.0;
+    else if (act == CB200_ACT_TANH) v = tanh(v);
+    else if (act == CB200_ACT_LOGISTIC) v = 1.0 / (1.0 + exp(-v));
+    out[i] = v;
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -108,11 +130,11 @@ int cb200_convolution_workspace_size(const cb200_conv_desc* desc, int in_w, int 
   return CB200_OK;
 }
 
-int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, double out_alpha,
-                              const void* in, const cb200_dims* in_dims, const void* w, const cb200_dims* w_dims,
-                              void* workspace, int64_t workspace_ecount, const cb200_conv_desc* desc) {
-  (void)workspace; (void)workspace_ecount;
+static int convolution_forward_impl(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, double out_alpha,
+                                    const void* in, const cb200_dims* in_dims, const void* w, const cb200_dims* w_dims,
+                                    const cb200_conv_desc* desc, const void* bias, int act) {
   CB_REQUIRE(s && out && out_dims && in && in_dims && w && w_dims && desc, "convolution_forward: null argument");
+  CB_REQUIRE(act >= CB200_ACT_NONE && act <= CB200_ACT_LOGISTIC, "convolution_forward: unknown activation %d", act);
   CB_REQUIRE(dtype == CB200_FLOAT || dtype == CB200_DOUBLE,
              "convolution-forward! is only defined for float and double tensors");
   // input / output are dense [batch, channels, height, width]
@@ -146,8 +168,9 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
   CB_REQUIRE(rows <= 2147483647LL, "convolution_forward: more than 2^31-1 output pixels");
   if (rows == 0 || cout == 0) return CB200_OK;
   if (dtype == CB200_FLOAT)
-    return cb200_conv_forward_f32(s, (float*)out, (const float*)in, (const float*)w, g.batch, g.cin, g.in_h, g.in_w, cout,
-                                  g.out_h, g.out_w, g.kh, g.kw, g.pad_x, g.pad_y, g.stride_x, g.stride_y, (float)out_alpha);
+    return cb200_conv_forward_f32_bias_act(s, (float*)out, (const float*)in, (const float*)w, g.batch, g.cin, g.in_h, g.in_w,
+                                           cout, g.out_h, g.out_w, g.kh, g.kw, g.pad_x, g.pad_y, g.stride_x, g.stride_y,
+                                           (float)out_alpha, (const float*)bias, act);
   const size_t es = 8;
   const long long total = rows * g.ld;
   void* cols = nullptr;
@@ -166,7 +189,29 @@ int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200
                                nullptr, 0, nullptr);
     if (rc) return rc;
   }
+  if (bias || act) {
+    // fp64: one more pass over the output (the per-image GEMMs write whole [C_out, hw] blocks)
+    const long long n_out = rows * cout;
+    long long b2 = (n_out + 255) / 256;
+    if (b2 > cap) b2 = cap;
+    conv_bias_act_f64_kernel<<<(unsigned)b2, 256, 0, s->stream>>>((double*)out, (const double*)bias, act, (unsigned)hw,
+                                                                   (unsigned)cout, n_out);
+    CB_LAUNCH_CHECK(s);
+  }
   return CB200_OK;
+}
+
+int cb200_convolution_forward(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, double out_alpha,
+                              const void* in, const cb200_dims* in_dims, const void* w, const cb200_dims* w_dims,
+                              void* workspace, int64_t workspace_ecount, const cb200_conv_desc* desc) {
+  (void)workspace; (void)workspace_ecount;
+  return convolution_forward_impl(s, dtype, out, out_dims, out_alpha, in, in_dims, w, w_dims, desc, nullptr, CB200_ACT_NONE);
+}
+
+int cb200_convolution_forward_bias_act(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims, double out_alpha,
+                                       const void* in, const cb200_dims* in_dims, const void* w, const cb200_dims* w_dims,
+                                       const cb200_conv_desc* desc, const void* bias, int act) {
+  return convolution_forward_impl(s, dtype, out, out_dims, out_alpha, in, in_dims, w, w_dims, desc, bias, act);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -40,6 +40,8 @@ constexpr int H_THREADS = (H_EPI_WARPS + 4) * 32;
 struct HaloParams {
   float* out;
   float out_alpha;
+  const float* bias;          // [C_out] added after out_alpha * out, or null
+  int act;                    // enum cb200_act applied last
   int batch, cout, out_h, out_w, kh, kw, pad_x, pad_y;
   int tiles_x, tiles_y;       // tiles per image
   int ncb;                    // C_in / 16
@@ -325,7 +327,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             float* cp = obase + (long long)(nb + j) * hw;
             float o = acc[j];
             if (p.out_alpha != 0.f) o += p.out_alpha * (*cp);
-            *cp = o;
+            *cp = conv_bias_act(o, p.bias, p.act, nb + j);
           }
         }
       }
@@ -599,7 +601,7 @@ conv_halo_direct_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_c
               float* cp = obase + (long long)n * hw;
               float o = __uint_as_float(r[j]) + __uint_as_float(rc[j]);
               if (p.out_alpha != 0.f) o += p.out_alpha * (*cp);
-              *cp = o;
+              *cp = conv_bias_act(o, p.bias, p.act, n);
             }
           }
         }
@@ -788,11 +790,11 @@ bool cb200_conv_halo_eligible(int cin, int cout, int out_w, int out_h, int kh, i
 
 int cb200_conv_halo_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                            int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
-                           float out_alpha) {
+                           float out_alpha, const float* bias, int act) {
   DeviceGuard guard(s->device);
   const int BN = cout > 64 ? 128 : 64;
   HaloParams p;
-  p.out = out; p.out_alpha = out_alpha; p.batch = batch; p.cout = cout; p.out_h = out_h; p.out_w = out_w;
+  p.out = out; p.out_alpha = out_alpha; p.batch = batch; p.bias = bias; p.act = act; p.cout = cout; p.out_h = out_h; p.out_w = out_w;
   p.kh = kh; p.kw = kw; p.pad_x = pad_x; p.pad_y = pad_y; p.status = s->status_dev;
   p.tiles_x = (out_w + HBX - 1) / HBX;
   p.tiles_y = (out_h + HBY - 1) / HBY;

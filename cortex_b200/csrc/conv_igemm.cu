@@ -44,6 +44,8 @@ struct ConvParams {
   int batch, cin, in_h, in_w, out_h, out_w, kh, kw, pad_x, pad_y, stride_x, stride_y;
   int cout, K, M;      // K = cin*kh*kw, M = batch*out_h*out_w
   float out_alpha;
+  const float* bias;   // [C_out] added after out_alpha * out, or null
+  int act;             // enum cb200_act applied last
   int* status;
 };
 
@@ -361,7 +363,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               float* cp = obase + (long long)(nb + j) * hw;   // adjacent lanes = adjacent pixels: coalesced
               float o = __uint_as_float(r[j]);
               if (p.out_alpha != 0.f) o += p.out_alpha * (*cp);
-              *cp = o;
+              *cp = conv_bias_act(o, p.bias, p.act, nb + j);
             }
           }
         }
@@ -438,12 +440,12 @@ int encode_weights(CUtensorMap* tm, const float* w, int K, int cout, int BN) {
 // multiple of 4, or an unaligned base -- are copied, zero-padded, into the stream's scratch first).
 int cb200_conv_igemm_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                             int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
-                            int stride_x, int stride_y, float out_alpha) {
+                            int stride_x, int stride_y, float out_alpha, const float* bias, int act) {
   DeviceGuard guard(s->device);
   ConvParams p;
   p.in = in; p.out = out; p.batch = batch; p.cin = cin; p.in_h = in_h; p.in_w = in_w; p.out_h = out_h; p.out_w = out_w;
   p.kh = kh; p.kw = kw; p.pad_x = pad_x; p.pad_y = pad_y; p.stride_x = stride_x; p.stride_y = stride_y;
-  p.cout = cout; p.K = cin * kh * kw; p.M = batch * out_h * out_w; p.out_alpha = out_alpha; p.status = s->status_dev;
+  p.cout = cout; p.K = cin * kh * kw; p.M = batch * out_h * out_w; p.out_alpha = out_alpha; p.status = s->status_dev; p.bias = bias; p.act = act;
   const int BN = cout > 128 ? 256 : (cout > 64 ? 128 : 64);
   CUtensorMap tmW, tmWlo;
   int rc;

@@ -46,6 +46,8 @@ constexpr int T_THREADS = (T_EPI_WARPS + 4) * 32;
 struct TmaConvParams {
   float* out;
   float out_alpha;
+  const float* bias;   // [C_out] added after out_alpha * out, or null
+  int act;             // enum cb200_act applied last
   int batch, cout, out_h, out_w, kh, kw, pad_x, pad_y;
   int bx, by, nbox;         // one box = bx x by output pixels; nbox * bx * by = 128
   int tiles_x, tiles_y;     // boxes per image along x / y
@@ -355,7 +357,7 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             float* cp = obase + (long long)(nb + j) * hw;       // lanes of a box row = adjacent pixels
             float o = acc[j];
             if (p.out_alpha != 0.f) o += p.out_alpha * (*cp);
-            *cp = o;
+            *cp = conv_bias_act(o, p.bias, p.act, nb + j);
           }
         }
       }
@@ -471,10 +473,10 @@ bool cb200_conv_tma_eligible(int cin, int out_w, int out_h, int stride_x, int st
 
 int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                           int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
-                          float out_alpha) {
+                          float out_alpha, const float* bias, int act) {
   DeviceGuard guard(s->device);
   TmaConvParams p;
-  p.out = out; p.out_alpha = out_alpha; p.batch = batch; p.cout = cout; p.out_h = out_h; p.out_w = out_w;
+  p.out = out; p.out_alpha = out_alpha; p.batch = batch; p.bias = bias; p.act = act; p.cout = cout; p.out_h = out_h; p.out_w = out_w;
   p.kh = kh; p.kw = kw; p.pad_x = pad_x; p.pad_y = pad_y; p.status = s->status_dev;
   cb200_conv_tma_plan(out_w, out_h, &p.bx, &p.by, &p.nbox);
   p.tiles_x = (out_w + p.bx - 1) / p.bx;

@@ -101,6 +101,19 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ---- fused bias + activation of the convolution epilogues ---------------------
+// (codes of enum cb200_act; tanh / logistic evaluated in double like the CPU backend, behind a call so that the
+// common cases do not pay for them)
+static __device__ __noinline__ float conv_act_transcendental(float v, int act) {
+  return act == 2 ? (float)tanh((double)v) : (float)(1.0 / (1.0 + exp(-(double)v)));
+}
+__device__ __forceinline__ float conv_bias_act(float o, const float* bias, int act, int channel) {
+  if (bias) o += bias[channel];
+  if (act == 1) o = o > 0.f ? o : 0.f;
+  else if (act > 1) o = conv_act_transcendental(o, act);
+  return o;
+}
+
 // ---- TMA --------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)tmap) : "memory");

@@ -175,6 +175,10 @@ class Convolution:
         ct.binary_op(output, 1.0, output, 1.0, bias, "+")
         return output
 
+    def forward_fused(self, input, output, act=None):
+        """One call: output = act(conv + bias) in the convolution kernel's epilogue (this backend's fused extra)."""
+        return ct.convolution_forward_bias_act(output, 0.0, input, self.weights, self.desc, self.bias, act)
+
     def backward(self, input, input_gradient, output_gradient, weight_gradient, bias_gradient):
         """ConvolutionLayer.backward (compute/nn/layers.clj:320-340): the bias gradient accumulates over batch and
         pixels (destination [C_out 1 1] smaller than the operation), weight and input gradients are overwritten."""
@@ -297,14 +301,26 @@ class ConvNet(_Replayable):
     def infer(self, x):
         dt = x.get_datatype()
         cur = x
+        # fused: a layer's bias and the activation layer right behind it join the producing kernel's epilogue
+        # (convolution + bias [+ ReLU], linear + bias + activation, linear + softmax head)
+        fuse_conv = self.fused and hasattr(ct.check_stream(), "convolution_forward_bias_act")
+        skip = -1
         for idx, spec in enumerate(self.layers):
             kind = spec[0]
+            if idx == skip:
+                continue
+            nxt = self.layers[idx + 1][0] if idx + 1 < len(self.layers) else None
             if kind == "conv":
                 conv = spec[1]
                 batch, _c, h, w = cur.shape()
                 od = ct.get_convolution_output_dimensions(conv.desc, h, w)
                 out = self._buffer(idx, [batch, conv.desc["out-channels"], od["output-width"], od["output-height"]], dt)
-                cur = conv.forward(cur, out)
+                if fuse_conv:
+                    cur = conv.forward_fused(cur, out, "relu" if nxt == "relu" else None)
+                    if nxt == "relu":
+                        skip = idx + 1
+                else:
+                    cur = conv.forward(cur, out)
             elif kind == "pool":
                 out = self._buffer(idx, spec[1].output_shape(cur.shape()), dt)
                 cur = spec[1].forward(cur, out)
@@ -318,6 +334,8 @@ class ConvNet(_Replayable):
                 lin, act = spec[1], spec[2]
                 out = self._buffer(idx, [cur.shape()[0], lin.weights.shape()[0]], dt)
                 if self.fused:
+                    if act is None and nxt == "softmax":
+                        act, skip = "softmax", idx + 1
                     cur = lin.forward_fused(cur, out, act)
                 else:
                     cur = lin.forward(cur, out)

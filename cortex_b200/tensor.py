@@ -859,6 +859,23 @@ def convolution_forward(output, output_alpha, input, weights, workspace, conv_de
     return output
 
 
+def convolution_forward_bias_act(output, output_alpha, input, weights, conv_descriptor, bias=None, act=None):
+    """Fused extra of this backend (no protocol counterpart): convolution-forward!, the layer's bias add and the
+    following activation as one call.  bias: a dense tensor of out-channels elements or None; act: None, "relu",
+    "tanh" or "logistic"."""
+    _external_library_check("convolution-forward!", output, input, weights)
+    _require(len(input.shape()) == 4 and len(output.shape()) == 4, "Input, output must be 4d tensors")
+    _require(act in (None, "none", "relu", "tanh", "logistic"), "convolution epilogue activation must be relu, tanh or logistic")
+    _ensure_conv_io(conv_descriptor, input, output)
+    if bias is not None:
+        _require(bias.ecount() == conv_descriptor["out-channels"] and dense(bias), "bias must be a dense tensor of out-channels elements")
+        _require(bias.get_datatype() == output.get_datatype(), "bias datatype differs from the output's")
+    check_stream().convolution_forward_bias_act(output.buffer, output.dimensions, output_alpha, input.buffer,
+                                                input.dimensions, weights.buffer, weights.dimensions, conv_descriptor,
+                                                bias.buffer if bias is not None else None, act)
+    return output
+
+
 def convolution_backward_weights(weight_gradient, weight_gradient_alpha, output_gradient, input, workspace,
                                  conv_descriptor, algorithms):
     """tensor.clj:1469-1479."""

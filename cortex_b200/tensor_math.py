@@ -108,6 +108,13 @@ class CTensorMath:
                  workspace.ptr if workspace is not None else None, int(workspace_ecount),
                  C.byref(conv_desc_struct(conv_descriptor)))
 
+    def convolution_forward_bias_act(self, output, output_dims, output_alpha, input, input_dims, weights, weight_dims,
+                                     conv_descriptor, bias, act):
+        """Fused extra: act(conv + output_alpha * output + bias[channel]) in the convolution's epilogue."""
+        self._tm("convolution_forward_bias_act", DTYPE_CODE[output.dtype], output.ptr, C.byref(wire(output_dims)),
+                 float(output_alpha), input.ptr, C.byref(wire(input_dims)), weights.ptr, C.byref(wire(weight_dims)),
+                 C.byref(conv_desc_struct(conv_descriptor)), bias.ptr if bias is not None else None, ACTIVATIONS[act])
+
     def convolution_backward_weights(self, weight_gradient, weight_gradient_dims, weight_gradient_alpha,
                                      output_gradient, output_gradient_dims, input, input_dims, workspace,
                                      workspace_ecount, conv_descriptor, algorithms):

@@ -236,6 +236,16 @@ int cb200_convolution_forward_static(cb200_stream* s, int dtype, void* out, cons
                                      double out_alpha, const void* in, const cb200_dims* in_dims,
                                      const void* w, const cb200_dims* w_dims, const cb200_conv_desc* desc);
 
+/* Fused extra (no counterpart in the protocol): what ConvolutionLayer.forward + the following ActivationLayer issue
+ * as three calls (src/cortex/compute/nn/layers.clj:300-318, 91-103) in the convolution's own epilogue:
+ *   out = act(conv(in, w) + out_alpha * out + bias[channel])    bias: [C_out] or NULL; act: enum cb200_act (no softmax)
+ * fp32: bias and activation join the epilogue of whichever tensor-core kernel runs the layer (bit-identical to
+ * the three calls for no activation / ReLU); fp64: one more pass over the output. */
+int cb200_convolution_forward_bias_act(cb200_stream* s, int dtype, void* out, const cb200_dims* out_dims,
+                                       double out_alpha, const void* in, const cb200_dims* in_dims,
+                                       const void* w, const cb200_dims* w_dims, const cb200_conv_desc* desc,
+                                       const void* bias, int act);
+
 /* ---- next to the path: ternary-op! family and gemv! ---------------------------
  * ternary-op! / ternary-op-constant! / ternary-op-constant-constant!
  * (src/cortex/tensor/math.clj:71-98; CPU semantics src/cortex/compute/cpu/tensor_math.clj:465-566):

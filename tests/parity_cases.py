@@ -290,8 +290,9 @@ def conv_backward_case(datatype, batch, cin, hw, cout, k=3, pad=1, stride=1, see
     return run, reference
 
 
-def conv_case(datatype, batch, cin, hw, cout, k=3, pad=1, stride=1, seed=401, bias_scale=0.0):
-    """Config 4: NCHW conv + bias + ReLU."""
+def conv_case(datatype, batch, cin, hw, cout, k=3, pad=1, stride=1, seed=401, bias_scale=0.0, fused=False):
+    """Config 4: NCHW conv + bias + ReLU, as the reference's three calls or (fused) as one call whose epilogue adds
+    the bias and applies the activation."""
     dt = NP[datatype]
     X = np.random.default_rng(seed).standard_normal((batch, cin, hw, hw)).astype(dt)
     W = (np.random.default_rng(seed + 1).standard_normal((cout, cin * k * k)) * np.sqrt(2.0 / (cin * k * k))).astype(dt)
@@ -302,8 +303,11 @@ def conv_case(datatype, batch, cin, hw, cout, k=3, pad=1, stride=1, seed=401, bi
         layer = nn.Convolution(ct.to_tensor(W, datatype), ct.to_tensor(b, datatype), (k, k), (pad, pad),
                                (stride, stride), cin, cout, datatype)
         out = ct.new_tensor([batch, cout, out_hw, out_hw], datatype)
-        layer.forward(ct.to_tensor(X, datatype), out)
-        nn.relu(out, out)
+        if fused:
+            layer.forward_fused(ct.to_tensor(X, datatype), out, "relu")
+        else:
+            layer.forward(ct.to_tensor(X, datatype), out)
+            nn.relu(out, out)
         return ct.to_array(out)
 
     def reference():

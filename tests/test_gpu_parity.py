@@ -657,3 +657,54 @@ def test_gemm_tile_width_and_slices_are_interchangeable(b200_driver):
         with pytest.raises(Exception):
             stream.set_option("gemm-tile-n", 96)
     stream.sync()
+
+
+@pytest.mark.parametrize("datatype", ["float", "double"])
+@pytest.mark.parametrize("args", [
+    dict(batch=2, cin=16, hw=56, cout=64),                       # config 4's geometry: the patch kernel on the NCHW input
+    dict(batch=3, cin=16, hw=13, cout=40, k=5, pad=2),           # patch kernel with overhang
+    dict(batch=2, cin=32, hw=17, cout=130, k=3, pad=1, stride=2),  # strided: the thread-gathered kernel
+    dict(batch=2, cin=3, hw=8, cout=4, k=2, pad=0, stride=2),    # three input channels
+    dict(batch=2, cin=16, hw=30, cout=24, k=3, pad=1),           # rows not a multiple of 4: behind the layout pre-pass
+], ids=lambda a: "x".join(str(v) for v in a.values()))
+def test_conv_bias_relu_in_the_epilogue(b200_driver, oracle_driver, datatype, args):
+    """convolution_forward_bias_act: the layer's bias add and ReLU inside the convolution's epilogue give the bits
+    of the three-call sequence (conv, binary-op! +, ReLU) on every kernel route, and match the oracle's sequence."""
+    fused_run, ref = pc.conv_case(datatype, bias_scale=0.3, fused=True, **args)
+    plain_run, _ = pc.conv_case(datatype, bias_scale=0.3, **args)
+    cpu = _on(oracle_driver, datatype, plain_run)
+    for options in (None, {"conv-route": 1}, {"conv-route": 2}, {"conv-route": 3}):
+        fused = _on(b200_driver, datatype, fused_run, options)
+        plain = _on(b200_driver, datatype, plain_run, options)
+        assert np.array_equal(fused, plain), options
+        assert pc.rel_err(fused, cpu) <= pc.TOL[datatype]
+        assert pc.rel_err(fused, ref()) <= pc.TOL[datatype]
+
+
+def test_conv_epilogue_activations_and_accumulate(b200_driver):
+    """The other epilogue activations and out_alpha: act(conv + out_alpha * out + bias) against float64."""
+    rng = np.random.default_rng(9)
+    batch, cin, hw, cout = 2, 16, 12, 20
+    X = rng.standard_normal((batch, cin, hw, hw)).astype(np.float32)
+    W = (rng.standard_normal((cout, cin * 9)) * 0.1).astype(np.float32)
+    b = rng.standard_normal(cout).astype(np.float32)
+    O0 = rng.standard_normal((batch, cout, hw, hw)).astype(np.float32)
+    xp = np.zeros((batch, cin, hw + 2, hw + 2)); xp[:, :, 1:-1, 1:-1] = X
+    conv = np.zeros((batch, cout, hw, hw))
+    W4 = W.reshape(cout, cin, 3, 3).astype(np.float64)
+    for ky in range(3):
+        for kx in range(3):
+            conv += np.einsum("bchw,oc->bohw", xp[:, :, ky:ky + hw, kx:kx + hw], W4[:, :, ky, kx])
+    z = conv + 0.5 * O0 + b[None, :, None, None]
+    want = {None: z, "relu": np.maximum(z, 0), "tanh": np.tanh(z), "logistic": 1 / (1 + np.exp(-z))}
+    stream = b200_driver.default_device().create_stream()
+    with ct.with_stream(stream), ct.with_datatype("float"):
+        desc = ct.convolution_descriptor("float", cout, cin, 3, 3, 1, 1, 1, 1)
+        x, w, bias = ct.to_tensor(X), ct.to_tensor(W), ct.to_tensor(b)
+        for act, exact in want.items():
+            out = ct.to_tensor(O0)
+            ct.convolution_forward_bias_act(out, 0.5, x, w, desc, bias, act)
+            assert pc.rel_err(ct.to_array(out).reshape(exact.shape), exact) <= pc.TOL["float"], act
+        with pytest.raises(Exception):
+            ct.convolution_forward_bias_act(out, 0.0, x, w, desc, bias, "softmax")
+    stream.sync()
