@@ -220,6 +220,15 @@ class ClockSampler:
 
     def __init__(self, gpu_index):
         self.gpu_index, self.proc, self.lines = gpu_index, None, []
+        self.t_begin = self.t_end = None
+
+    def mark_begin(self):
+        """The timed region starts now (the sampler was started earlier: nvidia-smi needs ~0.1-0.3 s to deliver its
+        first line, longer than a short timed region lasts)."""
+        self.t_begin = time.monotonic()
+
+    def mark_end(self):
+        self.t_end = time.monotonic()
 
     def start(self):
         try:
@@ -233,7 +242,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
     def stop(self):
         if self.proc is None:
@@ -244,7 +253,16 @@ class ClockSampler:
         except Exception:
             pass
         sm, mx, reasons = [], [], set()
-        for line in self.lines:
+        lines = self.lines
+        if self.t_begin is not None and self.t_end is not None:
+            # samples that arrived inside the marked region (a line describes the ~20 ms before it arrived)
+            inside = [ln for ln in lines if self.t_begin <= ln[0] <= self.t_end + 0.025]
+            if not inside and lines:
+                # region shorter than the sampling period: the sample nearest to it
+                mid = 0.5 * (self.t_begin + self.t_end)
+                inside = [min(lines, key=lambda ln: abs(ln[0] - mid))]
+            lines = inside
+        for _t, line in lines:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
@@ -874,18 +892,20 @@ def run_b200(args, rank, world, local_rank):
         def step(record=False):
             return net.infer(x, row_block=row_block, trace=trace if record else None)
 
+        sampler = ClockSampler(local_rank)      # started before the warm-up so that it is delivering by the timed region
+        if rank == 0:
+            sampler.start()
         for _ in range(args.warmup):
             resident_out = step()
         barrier()
-        sampler = ClockSampler(local_rank)
-        if rank == 0:
-            sampler.start()
+        sampler.mark_begin()
         launches0 = stream.launch_count()
         e0 = stream.create_event(timing=True)
         for _ in range(args.steps):
             step(record=True)
         e1 = stream.create_event(timing=True)
         e1.wait_for_event()
+        sampler.mark_end()
         barrier()
         clocks = sampler.stop() if rank == 0 else None
         launches = stream.launch_count() - launches0
@@ -938,12 +958,13 @@ def run_b200(args, rank, world, local_rank):
         pipe = BatchPipeline(dev, net, WIDTH, CLASSES, chunk, dt, slots=3)
         resident_rows, rows = rows, e2e_rows          # from here on `rows` is this rank's host-fed row count
         h2d = d2h = 0
-        for _ in range(min(args.warmup, 3)):
-            pipe.run(x_host, y_host, rows)
-        barrier()
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
+        for _ in range(min(args.warmup, 3)):
+            pipe.run(x_host, y_host, rows)
+        barrier()
+        sampler.mark_begin()
         t0 = pipe.compute.create_event(timing=True)
         for _ in range(args.steps):
             h2d, d2h = pipe.run(x_host, y_host, rows, wait=False)    # steps stream back to back, drained once
@@ -951,6 +972,7 @@ def run_b200(args, rank, world, local_rank):
         pipe.download.sync()
         t1 = pipe.compute.create_event(timing=True)
         t1.wait_for_event()
+        sampler.mark_end()
         barrier()
         e2e_ms = t1.elapsed_ms_since(t0) / args.steps
         e2e_clocks = sampler.stop() if rank == 0 else None
