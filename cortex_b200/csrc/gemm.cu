@@ -24,13 +24,15 @@ int cb200_gemm_presplit_auto_launch(cb200_stream* s, float* C, long long ldc, in
 
 namespace {
 
+// tanh / logistic (evaluated in double like the CPU backend) behind a call: next to the cheap cases the compiler
+// evaluated them branch-free for every element
+static __device__ __noinline__ double act_transcendental(double v, int act) {
+  return act == CB200_ACT_TANH ? tanh(v) : 1.0 / (1.0 + exp(-v));
+}
 template <typename T> __device__ __forceinline__ T act_apply(T v, int act) {
-  switch (act) {
-    case CB200_ACT_RELU: return v > (T)0 ? v : (T)0;
-    case CB200_ACT_TANH: return (T)tanh((double)v);
-    case CB200_ACT_LOGISTIC: return (T)(1.0 / (1.0 + exp(-(double)v)));
-  }
-  return v;
+  if (act == CB200_ACT_NONE) return v;
+  if (act == CB200_ACT_RELU) return v > (T)0 ? v : (T)0;
+  return (T)act_transcendental((double)v, act);
 }
 
 // 64x64 tile, 16x16 threads, 4x4 per thread.  Element (m,k) of op(A) is
