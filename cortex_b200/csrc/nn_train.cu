@@ -381,15 +381,60 @@ __device__ __forceinline__ double slab_reduce(double v, double* sh) {
   return t;
 }
 
+// What the CTA that completes a channel's sums writes (the other slabs' CTAs have parked theirs): the statistics of
+// the update pass, or the gradients of scale / bias and the five coefficients of the input-gradient pass.
+template <typename T>
+struct BnFinish {
+  T* batch_means; T* batch_variances; T* running_means; T* running_variances;   // MODE 0 / 1
+  double average_factor;
+  double* coef; T* scale_grad; T* bias_grad;                                    // MODE 2
+  long long count;
+  int* counters;            // one per channel, zero between launches
+};
+
+// MODE 0: batch mean;  1: batch variance + running statistics;  2: per channel bias / scale gradient and the
+// coefficients {g, inv_std, mean, d_var_d_out, part3} of the input-gradient pass
+template <typename T, int MODE>
+__device__ __forceinline__ void bn_finish_channel(const double* sums, int c, const BnFinish<T>& f, const T* means,
+                                                  const T* variances, const T* scale, double epsilon) {
+  const double n = f.count > 1 ? (double)f.count : 1.0;
+  if (MODE == 0) {
+    f.batch_means[c] = (T)(sums[0] / n);
+  } else if (MODE == 1) {
+    const double factor = (double)(T)f.average_factor, lerp = (double)(T)1.0 - factor;
+    const double n_running = n - 1.0 > 1.0 ? n - 1.0 : 1.0;
+    const double mean_old = (double)f.running_means[c], var_old = (double)f.running_variances[c];
+    const double new_mean = (double)f.batch_means[c];
+    f.batch_variances[c] = (T)(sums[0] / n);
+    f.running_means[c] = (T)(__dmul_rn(mean_old, lerp) + __dmul_rn(new_mean, factor));
+    f.running_variances[c] = (T)(__dmul_rn(var_old, lerp) + __dmul_rn((double)(T)(sums[0] / n_running), factor));
+  } else {
+    const double variance = (double)(T)epsilon + (double)variances[c];
+    const double inv_std = 1.0 / sqrt(variance);
+    f.bias_grad[c] = (T)sums[0];
+    f.scale_grad[c] = (T)sums[1];
+    const double d_var_d_out = (double)(T)sums[2];
+    const double d_mean_d_out = (double)(T)(sums[3] + __dmul_rn(d_var_d_out, sums[4] / (double)f.count));
+    const double one_over_count = 1.0 / (double)f.count;
+    double* k = f.coef + (long long)c * 5;
+    k[0] = (double)scale[c]; k[1] = inv_std; k[2] = (double)means[c]; k[3] = d_var_d_out;
+    k[4] = __dmul_rn(d_mean_d_out, one_over_count);
+  }
+}
+
 // NQ sums per (channel, slab).  MODE 0: {x};  1: {(mean - x)^2};  2: the five sums of the gradient pass.
+// Every CTA parks its sums and takes a ticket of its channel's counter; the CTA that takes the last one adds the
+// parked sums in slab order (a warp loads them side by side, lane 0 adds them in order: the same value whichever
+// CTA that is) and writes the channel's results -- no separate finishing launch, and nobody waits.
 template <typename T, int MODE, bool VECTOR>
 __global__ void __launch_bounds__(BN_SLAB_THREADS)
 bn_slab_sums_kernel(double* partial, const T* __restrict__ in, const T* out_grad, const T* __restrict__ means,
                     const T* __restrict__ variances, const T* __restrict__ scale, double epsilon, long long batch,
-                    int channels, int inner, int slabs) {
+                    int channels, int inner, int slabs, BnFinish<T> fin) {
   constexpr int NQ = MODE == 2 ? 5 : 1;
   constexpr int VEC = VECTOR ? 16 / (int)sizeof(T) : 1;
   __shared__ double red[BN_SLAB_THREADS / 32];
+  __shared__ int is_last;
   const int c = blockIdx.y, slab = blockIdx.x;
   const long long b0 = batch * slab / slabs, b1 = batch * (slab + 1) / slabs;
   const double mean = MODE >= 1 ? (double)means[c] : 0.0;
@@ -436,54 +481,31 @@ bn_slab_sums_kernel(double* partial, const T* __restrict__ in, const T* out_grad
     const double t = slab_reduce(acc[q], red);
     if (threadIdx.x == 0) partial[((long long)q * channels + c) * slabs + slab] = t;
   }
-}
-
-// STEP 0: batch mean;  1: batch variance + running statistics
-template <typename T, int STEP>
-__global__ void __launch_bounds__(128)
-bn_update_finish_kernel(const double* partial, T* batch_means, T* batch_variances, T* running_means,
-                        T* running_variances, double average_factor, long long count, int channels, int slabs) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
-  double sum = 0.0;
-  for (int s = 0; s < slabs; ++s) sum += partial[(long long)c * slabs + s];
-  const double n = count > 1 ? (double)count : 1.0;
-  if (STEP == 0) {
-    batch_means[c] = (T)(sum / n);
-  } else {
-    const double factor = (double)(T)average_factor, lerp = (double)(T)1.0 - factor;
-    const double n_running = n - 1.0 > 1.0 ? n - 1.0 : 1.0;
-    const double mean_old = (double)running_means[c], var_old = (double)running_variances[c];
-    const double new_mean = (double)batch_means[c];
-    batch_variances[c] = (T)(sum / n);
-    running_means[c] = (T)(__dmul_rn(mean_old, lerp) + __dmul_rn(new_mean, factor));
-    running_variances[c] = (T)(__dmul_rn(var_old, lerp) + __dmul_rn((double)(T)(sum / n_running), factor));
+  if (threadIdx.x == 0) {
+    __threadfence();                                   // this CTA's sums, before its ticket
+    is_last = atomicAdd(fin.counters + c, 1) == slabs - 1;
   }
-}
-
-// per channel: bias / scale gradient and the coefficients of the input-gradient pass {g, inv_std, mean, d_var_d_out, part3}
-template <typename T>
-__global__ void __launch_bounds__(128)
-bn_gradients_finish_kernel(const double* partial, double* coef, T* scale_grad, T* bias_grad, const T* means,
-                           const T* variances, const T* scale, double epsilon, long long count, int channels, int slabs) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
-  double sums[5];
-  for (int q = 0; q < 5; ++q) {
-    double t = 0.0;
-    for (int s = 0; s < slabs; ++s) t += partial[((long long)q * channels + c) * slabs + s];
-    sums[q] = t;
+  __syncthreads();
+  if (!is_last || threadIdx.x >= 32) return;
+  __threadfence();
+  const int lane = threadIdx.x;
+  double tot[NQ];
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) tot[q] = 0.0;
+  for (int s0 = 0; s0 < slabs; s0 += 32) {
+    double v[NQ];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q)
+      v[q] = s0 + lane < slabs ? __ldcg(partial + ((long long)q * channels + c) * slabs + s0 + lane) : 0.0;
+    const int nn = min(32, slabs - s0);
+    for (int l = 0; l < nn; ++l)
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) tot[q] += __shfl_sync(0xffffffffu, v[q], l);
   }
-  const double variance = (double)(T)epsilon + (double)variances[c];
-  const double inv_std = 1.0 / sqrt(variance);
-  bias_grad[c] = (T)sums[0];
-  scale_grad[c] = (T)sums[1];
-  const double d_var_d_out = (double)(T)sums[2];
-  const double d_mean_d_out = (double)(T)(sums[3] + __dmul_rn(d_var_d_out, sums[4] / (double)count));
-  const double one_over_count = 1.0 / (double)count;
-  double* k = coef + (long long)c * 5;
-  k[0] = (double)scale[c]; k[1] = inv_std; k[2] = (double)means[c]; k[3] = d_var_d_out;
-  k[4] = __dmul_rn(d_mean_d_out, one_over_count);
+  if (lane == 0) {
+    bn_finish_channel<T, MODE>(tot, c, fin, means, variances, scale, epsilon);
+    fin.counters[c] = 0;                               // left zero for the next launch
+  }
 }
 
 // input gradient: one CTA walks rows (batch entry, channel); the channel's coefficients are uniform per row
@@ -559,24 +581,21 @@ int bn_update_launch(cb200_stream* s, const void* in, void* bm, void* bv, void* 
   int rc = cb200_scratch(s, (size_t)channels * slabs * sizeof(double), &scratch);
   if (rc) return rc;
   double* partial = (double*)scratch;
+  BnFinish<T> fin;
+  fin.batch_means = (T*)bm; fin.batch_variances = (T*)bv; fin.running_means = (T*)rm; fin.running_variances = (T*)rv;
+  fin.average_factor = factor; fin.coef = nullptr; fin.scale_grad = nullptr; fin.bias_grad = nullptr;
+  fin.count = batch * inner;
+  if ((rc = cb200_tile_flags(s, (size_t)channels, &fin.counters))) return rc;
   constexpr int VEC = 16 / (int)sizeof(T);
   const bool vec = (inner % VEC) == 0 && (((uintptr_t)in) & 15) == 0;
   const dim3 grid((unsigned)slabs, (unsigned)channels, 1);
-  const unsigned fin = (unsigned)((channels + 127) / 128);
-  const long long count = batch * inner;
-  for (int step = 0; step < 2; ++step) {
-    if (step == 0) {
-      if (vec) bn_slab_sums_kernel<T, 0, true><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, nullptr, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs);
-      else bn_slab_sums_kernel<T, 0, false><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, nullptr, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs);
-    } else {
-      if (vec) bn_slab_sums_kernel<T, 1, true><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, (const T*)bm, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs);
-      else bn_slab_sums_kernel<T, 1, false><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, (const T*)bm, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs);
-    }
-    CB_LAUNCH_CHECK(s);
-    if (step == 0) bn_update_finish_kernel<T, 0><<<fin, 128, 0, s->stream>>>(partial, (T*)bm, (T*)bv, (T*)rm, (T*)rv, factor, count, (int)channels, slabs);
-    else bn_update_finish_kernel<T, 1><<<fin, 128, 0, s->stream>>>(partial, (T*)bm, (T*)bv, (T*)rm, (T*)rv, factor, count, (int)channels, slabs);
-    CB_LAUNCH_CHECK(s);
-  }
+  // mean pass, then the variance pass (which reads the mean the first one's last CTAs wrote): two launches
+  if (vec) bn_slab_sums_kernel<T, 0, true><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, nullptr, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs, fin);
+  else bn_slab_sums_kernel<T, 0, false><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, nullptr, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs, fin);
+  CB_LAUNCH_CHECK(s);
+  if (vec) bn_slab_sums_kernel<T, 1, true><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, (const T*)bm, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs, fin);
+  else bn_slab_sums_kernel<T, 1, false><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, nullptr, (const T*)bm, nullptr, nullptr, 0.0, batch, (int)channels, (int)inner, slabs, fin);
+  CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
 
@@ -625,12 +644,13 @@ int bn_gradients_launch(cb200_stream* s, void* ig, void* sg, void* bg, const voi
   constexpr int VEC = 16 / (int)sizeof(T);
   const bool vec = (inner % VEC) == 0 && ((((uintptr_t)in) | ((uintptr_t)og) | ((uintptr_t)ig)) & 15) == 0;
   const dim3 grid((unsigned)slabs, (unsigned)channels, 1);
-  if (vec) bn_slab_sums_kernel<T, 2, true><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, (const T*)og, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, batch, (int)channels, (int)inner, slabs);
-  else bn_slab_sums_kernel<T, 2, false><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, (const T*)og, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, batch, (int)channels, (int)inner, slabs);
-  CB_LAUNCH_CHECK(s);
   const long long count = batch * inner;
-  bn_gradients_finish_kernel<T><<<(unsigned)((channels + 127) / 128), 128, 0, s->stream>>>(
-      partial, coef, (T*)sg, (T*)bg, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, count, (int)channels, slabs);
+  BnFinish<T> fin;
+  fin.batch_means = nullptr; fin.batch_variances = nullptr; fin.running_means = nullptr; fin.running_variances = nullptr;
+  fin.average_factor = 0.0; fin.coef = coef; fin.scale_grad = (T*)sg; fin.bias_grad = (T*)bg; fin.count = count;
+  if ((rc = cb200_tile_flags(s, (size_t)channels, &fin.counters))) return rc;
+  if (vec) bn_slab_sums_kernel<T, 2, true><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, (const T*)og, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, batch, (int)channels, (int)inner, slabs, fin);
+  else bn_slab_sums_kernel<T, 2, false><<<grid, BN_SLAB_THREADS, 0, s->stream>>>(partial, (const T*)in, (const T*)og, (const T*)bm, (const T*)bv, (const T*)scale, epsilon, batch, (int)channels, (int)inner, slabs, fin);
   CB_LAUNCH_CHECK(s);
   const long long n_rows = batch * channels;
   long long blocks = n_rows < (long long)s->sm_count * 8 ? n_rows : (long long)s->sm_count * 8;
