@@ -16,7 +16,7 @@ class DimensionError(ValueError):
 
 
 def _is_number(x):
-    return isinstance(x, int) and not isinstance(x, bool)
+    return type(x) is int or (isinstance(x, int) and not isinstance(x, bool))
 
 
 def _prod(seq):
@@ -25,13 +25,16 @@ def _prod(seq):
 
 def disambiguate_shape_entry(entry):
     """dimensions.clj:46-52 -- an index tensor counts as its element count."""
+    if type(entry) is int:
+        return entry
     if _is_number(entry):
         return int(entry)
     return int(entry.ecount())
 
 
 def disambiguate_shape(shape):
-    return [disambiguate_shape_entry(e) for e in shape]
+    # the common case (every entry a plain int) without a call per entry: this runs on every tensor operation
+    return [e if type(e) is int else disambiguate_shape_entry(e) for e in shape]
 
 
 def direct_shape(shape):
