@@ -38,7 +38,10 @@ def disambiguate_shape(shape):
 
 
 def direct_shape(shape):
-    return all(_is_number(e) for e in shape)
+    for e in shape:                      # a plain loop: this runs several times per tensor operation
+        if type(e) is not int and not _is_number(e):
+            return False
+    return True
 
 
 def extend_strides(shape, strides=None):
@@ -127,7 +130,12 @@ def direct(dims):
 def access_increasing(dims):
     """dimensions.clj:204-211 -- strides non-increasing and no index tensors."""
     st = dims["strides"]
-    return direct_shape(dims["shape"]) and all(st[i] >= st[i + 1] for i in range(len(st) - 1))
+    if not direct_shape(dims["shape"]):
+        return False
+    for i in range(len(st) - 1):
+        if st[i] < st[i + 1]:
+            return False
+    return True
 
 
 def elem_idx_to_addr(rev_shape, rev_strides, rev_max_shape, arg, index_value=None):
