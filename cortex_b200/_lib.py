@@ -25,7 +25,7 @@ REDUCE_OPS = {"max": 0, "min": 1, "sum": 2, "mean": 3, "magnitude": 4, "magnitud
 ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "tanh": 2, "logistic": 3, "softmax": 4}    # softmax: gemm_bias_act only
 DISTRIBUTIONS = {"flat": 0, "gaussian": 1}
 STREAM_OPTIONS = {"gemm-auto-presplit": 0, "presplit-variant": 1, "f64-simple-kernel": 2, "wait-limit-cycles": 3,
-                  "inject-fault": 4, "conv-route": 5, "gemm-k-slices": 6, "gemm-tile-n": 7}
+                  "inject-fault": 4, "conv-route": 5, "gemm-k-slices": 6, "gemm-tile-n": 7, "gemm-slice-handover": 8}
 
 
 class Dims(C.Structure):

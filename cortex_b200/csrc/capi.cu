@@ -160,7 +160,7 @@ int cb200_stream_create(int device, cb200_stream** out) {
   s->launches.store(0);
   s->capture_start = -1;
   s->live_graphs = std::make_shared<std::atomic<int>>(0);
-  s->opt_gemm_auto_presplit = s->opt_presplit_variant = s->opt_f64_simple = s->opt_conv_route = s->opt_gemm_k_slices = s->opt_gemm_tile_n = 0;
+  s->opt_gemm_auto_presplit = s->opt_presplit_variant = s->opt_f64_simple = s->opt_conv_route = s->opt_gemm_k_slices = s->opt_gemm_tile_n = s->opt_gemm_slice_handover = 0;
   cudaError_t e = cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, device);
   if (e == cudaSuccess) e = cudaMalloc((void**)&s->status_dev, 4 * sizeof(int));
@@ -212,6 +212,10 @@ int cb200_stream_set_option(cb200_stream* s, int option, int64_t value) {
     case CB200_OPT_GEMM_K_SLICES:
       CB_REQUIRE(value >= 0 && value <= 16, "stream_set_option: K slices %lld outside [0, 16]", (long long)value);
       s->opt_gemm_k_slices = (int)value;
+      return CB200_OK;
+    case CB200_OPT_GEMM_SLICE_HANDOVER:
+      CB_REQUIRE(value == 0 || value == 1, "stream_set_option: slice hand-over %lld outside [0, 1]", (long long)value);
+      s->opt_gemm_slice_handover = (int)value;
       return CB200_OK;
     case CB200_OPT_GEMM_TILE_N:
       CB_REQUIRE(value == 0 || value == 64 || value == 128 || value == 256,

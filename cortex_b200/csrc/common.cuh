@@ -30,7 +30,7 @@ struct cb200_stream {
   std::shared_ptr<std::atomic<int>> live_graphs;
   std::vector<void*> retired;
   // per-stream routing options (cb200_stream_set_option); 0 = automatic
-  int opt_gemm_auto_presplit, opt_presplit_variant, opt_f64_simple, opt_conv_route, opt_gemm_k_slices, opt_gemm_tile_n;
+  int opt_gemm_auto_presplit, opt_presplit_variant, opt_f64_simple, opt_conv_route, opt_gemm_k_slices, opt_gemm_tile_n, opt_gemm_slice_handover;
 };
 
 // A captured sequence of this library's launches on one stream, replayable with one call.

@@ -37,6 +37,7 @@ struct GemmParams {
   // A CTA parks its raw tile in ksplit_ws[(tile * ksplit_n + slice)][BN / 4][BM] float4; the one that arrives last (per-tile
   // counter in tile_flags) sums the slices in slice order and runs the epilogue.  Nobody waits.
   int ksplit_n;
+  int ksplit_cluster;  // 1: the slices of a tile are the CTAs of one thread-block cluster and meet in shared memory
   float* ksplit_ws;
   int* tile_flags;
   int* status;
@@ -125,6 +126,33 @@ __device__ __forceinline__ void dump_tile(const GemmParams& p, uint32_t tmem_bas
   }
 }
 
+// The same parked tile ([BN / 4][128 rows] float4) in this CTA's own shared memory: the cluster form of the hand-over.
+template <int BN>
+__device__ __forceinline__ void dump_tile_smem(const GemmParams& p, uint32_t tmem_base, float* dst, int warp, int lane) {
+  const int q = warp & 3, half = warp >> 2;
+  constexpr int COLS_PER_HALF = BN / 2;
+  float4* slot = reinterpret_cast<float4*>(dst) + (q * 32 + lane);
+#pragma unroll 1
+  for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
+    const int col0 = half * COLS_PER_HALF + cc * 32;
+    uint32_t r[32];
+    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col0, r);
+    if (!(p.flags & FLAG_ONE_TERM)) {
+      uint32_t rc[32];
+      tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(BN + col0), rc);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(rc[j]));
+    } else {
+      tmem_ld_wait();
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)       // plain stores: the cache-hinted form of dump_tile is for global memory only
+      slot[((col0 + j) >> 2) * 128] = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+  }
+}
+
 // `beta_now`: factor applied to what C holds (the caller's beta, or 1 once C holds a partial result).
 // `last_pass`: bias, activation and peer stores join only on the pass that completes the tile.
 // `staging`: shared memory that is free by now (the pipeline stages), 32 x 36 floats per warp: slabs are
@@ -137,24 +165,64 @@ template <int BN, bool WITH_LO = false>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem_base, int m0, int n0, int warp,
                                               int lane, float* staging, float beta_now, bool last_pass, bool c_is_partial,
                                               const float* part = nullptr, const float* gather = nullptr,
-                                              int gather_n = 0) {
+                                              int gather_n = 0, uint32_t cluster_src = 0, int item = -1) {
       float* c_lo = (WITH_LO && last_pass) ? p.C_lo : nullptr;
       const float* e_bias = last_pass ? p.bias : nullptr;
       const int e_act = last_pass ? p.act : 0;
       const int e_peers = last_pass ? p.n_peers : 0;
-      const int q = warp & 3, half = warp >> 2;
+      // `item` >= 0 (cluster hand-over): this warp finishes the 32 x 32 slab (q, half, cc) = (item & 3,
+      // (item >> 2) & 1, item >> 3) whatever its own index is -- the values come from shared memory, not from
+      // the warp's TMEM lanes; `warp` still names its staging slot.
+      const int sel = item >= 0 ? item : warp;
+      const int q = sel & 3, half = (sel >> 2) & 1;
       const int m = m0 + q * 32 + lane;
       constexpr int COLS_PER_HALF = BN / 2;
+      const int cc_lo = item >= 0 ? item >> 3 : 0, cc_hi = item >= 0 ? (item >> 3) + 1 : COLS_PER_HALF / 32;
       constexpr int CHUNK = COLS_PER_HALF < 32 ? COLS_PER_HALF : 32;
       static_assert(CHUNK == 32, "BN must be >= 64");
       bool vec_ok = p.store_mode == STORE_ROW_MAJOR && (p.ldc % 4) == 0 && (((uintptr_t)p.C) & 15) == 0;
       for (int d = 0; d < e_peers; ++d) vec_ok = vec_ok && (((uintptr_t)p.peers[d]) & 15) == 0;
       const bool vec8_ok = vec_ok && e_peers == 0 && (p.ldc % 8) == 0 && (((uintptr_t)p.C) & 31) == 0;
 #pragma unroll 1
-      for (int cc = 0; cc < COLS_PER_HALF / 32; ++cc) {
+      for (int cc = cc_lo; cc < cc_hi; ++cc) {
         const int col0 = half * COLS_PER_HALF + cc * 32;
         uint32_t r[32];
-        if (gather) {
+        if (cluster_src) {
+          // K slices parked in the shared memory of the gather_n CTAs of this cluster (rank = slice): summed in
+          // slice order through distributed shared memory, two slices requested per round trip
+          const uint32_t off = cluster_src + (uint32_t)(((col0 >> 2) * 128 + (q * 32 + lane)) * 16);
+          float4 a[8];
+          {
+            const uint32_t b0 = mapa(off, 0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] = ld_dsmem_v4(b0 + j * 2048);
+          }
+          int sl = 1;
+          for (; sl + 1 < gather_n; sl += 2) {
+            const uint32_t b0 = mapa(off, (uint32_t)sl), b1 = mapa(off, (uint32_t)sl + 1);
+            float4 v0[8], v1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { v0[j] = ld_dsmem_v4(b0 + j * 2048); v1[j] = ld_dsmem_v4(b1 + j * 2048); }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              a[j].x += v0[j].x; a[j].y += v0[j].y; a[j].z += v0[j].z; a[j].w += v0[j].w;
+              a[j].x += v1[j].x; a[j].y += v1[j].y; a[j].z += v1[j].z; a[j].w += v1[j].w;
+            }
+          }
+          if (sl < gather_n) {
+            const uint32_t b0 = mapa(off, (uint32_t)sl);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 b = ld_dsmem_v4(b0 + j * 2048);
+              a[j].x += b.x; a[j].y += b.y; a[j].z += b.z; a[j].w += b.w;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            r[4 * j] = __float_as_uint(a[j].x); r[4 * j + 1] = __float_as_uint(a[j].y);
+            r[4 * j + 2] = __float_as_uint(a[j].z); r[4 * j + 3] = __float_as_uint(a[j].w);
+          }
+        } else if (gather) {
           // K slices parked by gather_n CTAs (this one included): summed in slice order, whoever runs this.
           // Two slices (sixteen 16-byte loads) are requested before the first is added: the combine costs
           // about gather_n / 2 round trips to L2 per 32 columns instead of one per load.

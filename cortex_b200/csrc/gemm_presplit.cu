@@ -675,6 +675,7 @@ int launch_presplit(cb200_stream* s, float* C, float* C_lo, long long ldc, float
   // (the general kernel has to use two K halves per tile for this; here the epilogue warps are free)
   p.k_split = 1;
   p.ksplit_n = 1;
+  p.ksplit_cluster = 0;
   p.ksplit_ws = nullptr;
   p.drain_every = K >= 4096 ? 2048 / BK : 0;
   p.split_block = 2 * s->sm_count;

@@ -282,7 +282,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       }
       ok = __all_sync(0xffffffffu, __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0);
     }
-    if (p.ksplit_n > 1) {
+    if (p.ksplit_n > 1 && p.ksplit_cluster) {
+      // K slices as the CTAs of one cluster: park the raw tile in this CTA's own shared memory (the pipeline
+      // stages are free by now); the slices meet after the cluster barrier below
+      if (ok) dump_tile_smem<BN>(p, tmem_base, reinterpret_cast<float*>(smem), warp, lane);
+    } else if (p.ksplit_n > 1) {
       // K-sliced small problem: park the raw tile; the CTA that arrives last combines the slices and stores.
       // All eight warps take both barriers whatever their own wait returned (a warp that gave up has raised
       // the abort flag, which cancels the hand-over for the whole CTA).
@@ -310,6 +314,23 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
+  if (p.ksplit_n > 1 && p.ksplit_cluster) {
+    // Every thread of every CTA of the cluster takes both barriers, whatever happened before (a CTA whose waits
+    // ran out has raised its abort flag and reported the status; its parked tile is then undefined, like the
+    // output of a failed launch).  Between them each CTA finishes its share of the tile's 32 x 32 slabs: slab i
+    // belongs to CTA i % n, the CTA's slabs go round its eight warps; the values are summed in slice order from
+    // the n CTAs' shared memory, so the result does not depend on which CTA or warp does it.
+    cluster_sync_all();
+    if (warp < NUM_CONV_WARPS && !*abort_flag) {
+      const int n = p.ksplit_n, rank = (int)cluster_ctarank();
+      constexpr int ITEMS = 8 * (BN / 64);
+      float* staging = reinterpret_cast<float*>(smem + 128 * BN * 4);       // behind the parked tile
+      for (int i = rank + n * warp; i < ITEMS; i += n * NUM_CONV_WARPS)
+        epilogue_tile<BN>(p, tmem_base, m0, n0, warp, lane, staging, p.beta, true, false, nullptr, nullptr, n,
+                          smem_u32(smem), i);
+    }
+    cluster_sync_all();
+  }
   if (p.k_split == 2 && threadIdx.x == 0 && !*abort_flag) {
     // first half: publish "C holds the partial tile"; second half: leave the flag zero for the next launch
     int* flag = p.tile_flags + tile_id;
@@ -366,17 +387,74 @@ int make_tmap(CUtensorMap* tm, const float* base, long long rows, long long cols
 }
 
 template <int BN, int BK>
-int launch_tile(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p) {
+cudaError_t tile_kernel_attributes(int dev) {
   typedef TileCfg<BN, BK> Cfg;
   static std::once_flag once[64];
-  int dev = s->device;
-  cudaError_t attr_err = cudaSuccess;
+  static cudaError_t result[64];
   std::call_once(once[dev & 63], [&] {
-    attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    result[dev & 63] = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
   });
+  return result[dev & 63];
+}
+
+// How many clusters of `cluster` CTAs of this kernel the device holds at once (the CTAs of a cluster must sit in one
+// GPC, so this is less than SMs / cluster); 0 when the query fails.  Cached per device and cluster size.
+template <int BN, int BK>
+int max_active_clusters(cb200_stream* s, int cluster) {
+  typedef TileCfg<BN, BK> Cfg;
+  static std::mutex mu;
+  static int cache[64][9];
+  static bool have[64][9];
+  const int dev = s->device & 63;
+  if (cluster < 1 || cluster > 8) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!have[dev][cluster]) {
+    int n = 0;
+    if (tile_kernel_attributes<BN, BK>(s->device) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)cluster, 1, 1);
+      cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+      cfg.dynamicSmemBytes = Cfg::SMEM;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = (unsigned)cluster;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tf32x3_kernel<BN, BK>, &cfg) != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+    }
+    cache[dev][cluster] = n;
+    have[dev][cluster] = true;
+  }
+  return cache[dev][cluster];
+}
+
+template <int BN, int BK>
+int launch_tile(cb200_stream* s, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p) {
+  typedef TileCfg<BN, BK> Cfg;
+  cudaError_t attr_err = tile_kernel_attributes<BN, BK>(s->device);
   if (attr_err != cudaSuccess) return cb200_cuda_fail(attr_err, "cudaFuncSetAttribute", __FILE__, __LINE__);
   long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.k_split * p.ksplit_n;
-  gemm_tf32x3_kernel<BN, BK><<<(unsigned)tiles, NUM_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmB, p);
+  if (p.ksplit_n > 1 && p.ksplit_cluster) {
+    // the slices of a tile (consecutive block indices) as one thread-block cluster
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)tiles, 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = s->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)p.ksplit_n;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tf32x3_kernel<BN, BK>, tmA, tmB, p);
+    if (e != cudaSuccess) return cb200_cuda_fail(e, "cudaLaunchKernelEx(gemm_tf32x3_kernel)", __FILE__, __LINE__);
+  } else {
+    gemm_tf32x3_kernel<BN, BK><<<(unsigned)tiles, NUM_THREADS, Cfg::SMEM, s->stream>>>(tmA, tmB, p);
+  }
   CB_LAUNCH_CHECK(s);
   return CB200_OK;
 }
@@ -475,6 +553,7 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   // K slices: model_slices CTAs per tile, each over a slice of K, combined by the last one to finish.  The stream
   // option forces a count (old caps: at least 8 k-blocks per slice, slices x BN <= 1024, at most 16).
   p.ksplit_n = 1;
+  p.ksplit_cluster = 0;
   p.ksplit_ws = nullptr;
   {
     const long long tiles = tiles_m * tiles_n;
@@ -487,12 +566,24 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
       if (sl > 16) sl = 16;
     }
     if (p.k_split == 1 && sl >= 2 && !(flags & FLAG_ONE_TERM)) {
-      void* ws = nullptr;
-      int rcs = cb200_partials(s, (size_t)tiles * sl * BM * BN * sizeof(float), &ws);
-      if (rcs) return rcs;
-      if ((rcs = cb200_tile_flags(s, (size_t)tiles, &p.tile_flags))) return rcs;
       p.ksplit_n = (int)sl;
-      p.ksplit_ws = (float*)ws;
+      // up to 8 slices (the portable cluster size): the slices of a tile are launched as one cluster and hand
+      // their partial tiles over through distributed shared memory; more slices go through L2
+      int fit = 0;
+      if (sl <= 8 && s->opt_gemm_slice_handover != 1) {
+        DeviceGuard guard_q(s->device);
+        fit = BN == 256 ? max_active_clusters<256, 16>(s, (int)sl)
+                        : (BN == 128 ? max_active_clusters<128, 16>(s, (int)sl) : max_active_clusters<64, 16>(s, (int)sl));
+      }
+      if (fit >= tiles) {          // every tile's cluster resident at once; otherwise a second wave would cost more than L2
+        p.ksplit_cluster = 1;
+      } else {
+        void* ws = nullptr;
+        int rcs = cb200_partials(s, (size_t)tiles * sl * BM * BN * sizeof(float), &ws);
+        if (rcs) return rcs;
+        if ((rcs = cb200_tile_flags(s, (size_t)tiles, &p.tile_flags))) return rcs;
+        p.ksplit_ws = (float*)ws;
+      }
     }
   }
   p.group_n = tiles_n;

@@ -480,6 +480,8 @@ enum cb200_stream_option {
                                        tile, each over a slice of K: 0 = by size, 1 = never slice, n <= 16 = n slices
                                        when K has at least 8 k-blocks per slice */
   CB200_OPT_GEMM_TILE_N = 7,        /* fp32 tensor-core gemm!: output tile width, 0 = by size, else 64, 128 or 256 */
+  CB200_OPT_GEMM_SLICE_HANDOVER = 8, /* K-sliced fp32 gemm!: 0 = up to 8 slices meet in distributed shared memory (the
+                                       slices of a tile are one thread-block cluster), more through L2; 1 = always L2 */
   CB200_OPT_INJECT_FAULT = 4        /* bit 0: the TMA producers of the fp32 tensor-core GEMM issue no loads, so
                                        the consumers' waits run out -> CB200_ERR_TIMEOUT from cb200_stream_sync.
                                        The failure is made on the host side of the barrier protocol; the kernel

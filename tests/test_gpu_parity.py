@@ -535,7 +535,8 @@ def test_tensor_core_reads_fp32_words_truncated(b200_driver, ta, tb):
 
 @pytest.mark.parametrize("M,N,K,act", [(128, 500, 784, "relu"), (128, 24, 500, None), (64, 1000, 2048, "tanh"),
                                        (300, 72, 1040, None), (8192, 125, 4096, None)])
-def test_small_gemm_is_sliced_over_k(b200_driver, M, N, K, act):
+@pytest.mark.parametrize("handover", [0, 1])
+def test_small_gemm_is_sliced_over_k(b200_driver, M, N, K, act, handover):
     """Problems with fewer tiles than half the SMs are reduced by several CTAs per tile, each over a slice of K,
     combined by whichever finishes last (in slice order: the result does not depend on who that is).  Config 1's
     first layer, a 24-column head, a wide-K case, a ragged one and the 8-way column-sharded head; twice in a row (the per-tile
@@ -545,6 +546,8 @@ def test_small_gemm_is_sliced_over_k(b200_driver, M, N, K, act):
     W = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
     bias = rng.standard_normal(N).astype(np.float32)
     stream = b200_driver.default_device().create_stream()
+    # 0: up to 8 slices meet in distributed shared memory (the slices of a tile launched as one cluster); 1: through L2
+    stream.set_option("gemm-slice-handover", handover)
     outs = []
     with ct.with_stream(stream), ct.with_datatype("float"):
         a, w, b = ct.to_tensor(A), ct.to_tensor(W), ct.to_tensor(bias)
@@ -647,13 +650,19 @@ def test_gemm_tile_width_and_slices_are_interchangeable(b200_driver):
         a, b = ct.to_tensor(A), ct.to_tensor(B)
         for tile_n in (0, 64, 128, 256):
             for slices in (0, 1, 2, 4):
-                stream.set_option("gemm-tile-n", tile_n)
-                stream.set_option("gemm-k-slices", slices)
-                c = ct.to_tensor(C0)
-                ct.gemm(c, False, True, 1.5, a, b, 0.5)
-                assert pc.rel_err(ct.to_array(c).reshape(M, N), exact) <= pc.TOL["float"], (tile_n, slices)
+                outs = []
+                for handover in (0, 1):      # slices meeting in distributed shared memory (one cluster per tile) / through L2
+                    stream.set_option("gemm-tile-n", tile_n)
+                    stream.set_option("gemm-k-slices", slices)
+                    stream.set_option("gemm-slice-handover", handover)
+                    c = ct.to_tensor(C0)
+                    ct.gemm(c, False, True, 1.5, a, b, 0.5)
+                    outs.append(ct.to_array(c).reshape(M, N))
+                    assert pc.rel_err(outs[-1], exact) <= pc.TOL["float"], (tile_n, slices, handover)
+                assert np.array_equal(outs[0], outs[1]), (tile_n, slices)     # both sum the slices in slice order
         stream.set_option("gemm-tile-n", 0)
         stream.set_option("gemm-k-slices", 0)
+        stream.set_option("gemm-slice-handover", 0)
         with pytest.raises(Exception):
             stream.set_option("gemm-tile-n", 96)
     stream.sync()
