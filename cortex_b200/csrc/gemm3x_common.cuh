@@ -332,7 +332,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
           __syncwarp();
           continue;
         }
-        if (staging != nullptr && p.store_mode == STORE_ROW_MAJOR && !(vec_ok && nb + 32 <= p.N)) {
+        // 16-byte stores also serve a last slab that ends on a multiple of 4 columns (N = 500): the same code as
+        // every other slab with a predicate per store, instead of the transposed path below -- that path costs
+        // ~2.7 us whatever it stores (it runs once, in one warp, from a cold instruction cache)
+        const bool vec4_slab = vec_ok && (nb + 32 <= p.N || (p.N & 3) == 0);
+        if (staging != nullptr && p.store_mode == STORE_ROW_MAJOR && !vec4_slab) {
           // Ragged or unaligned slab (the last columns of N, a row pitch that is not a multiple of 16 bytes):
           // transposed through a [32][33]-float shared tile per warp, so that a lane owns a COLUMN and every
           // load of C, store of C and peer store covers consecutive floats of one row.  (One 4-byte store per
@@ -346,19 +350,20 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
           if (n < p.N) {
             const int row_base = m0 + q * 32;
             const float bias_n = e_bias ? e_bias[n] : 0.f;
-#pragma unroll 4
+            // a compact loop on purpose: this path runs once per launch for one or two warps, straight from a cold
+            // instruction cache -- fully unrolled (32 rows) it measured 4 us slower than as a loop
+#pragma unroll 1
             for (int rr = 0; rr < 32; ++rr) {
               const int mr = row_base + rr;
-              if (mr < p.M) {
-                const long long off = (long long)mr * p.ldc + n;
-                float v = t[rr * 33 + lane];
-                if (beta_now != 0.f) v += beta_now * ld_c(p.C + off, c_is_partial);
-                if (e_bias) v += bias_n;
-                v = apply_act(v, e_act);
-                p.C[off] = v;
-                if (WITH_LO && c_lo) c_lo[off] = lo_part(v);
-                for (int d = 0; d < e_peers; ++d) p.peers[d][off] = v;
-              }
+              if (mr >= p.M) break;
+              const long long off = (long long)mr * p.ldc + n;
+              float v = t[rr * 33 + lane];
+              if (beta_now != 0.f) v += beta_now * ld_c(p.C + off, c_is_partial);
+              if (e_bias) v += bias_n;
+              v = apply_act(v, e_act);
+              p.C[off] = v;
+              if (WITH_LO && c_lo) c_lo[off] = lo_part(v);
+              for (int d = 0; d < e_peers; ++d) p.peers[d][off] = v;
             }
           }
           __syncwarp();
@@ -396,9 +401,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                   st_global_v8(c_lo + (long long)m * p.ldc + nb + j, l);
                 }
               }
-            } else if (vec_ok && nb + 32 <= p.N) {
+            } else if (vec4_slab) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
+                if (nb + j >= p.N) break;            // N is a multiple of 4 here whenever the slab is cut short
                 float4 o;
                 o.x = p.alpha * __uint_as_float(r[j]);
                 o.y = p.alpha * __uint_as_float(r[j + 1]);
