@@ -527,8 +527,9 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
       for (int sl = min_slices > 1 ? min_slices : 1; sl <= 32; ++sl) {
         if (sl > 1 && (!may_slice || tiles * sl > s->sm_count || nkb_model / sl < 4)) break;
         const long long waves = (tiles * sl + s->sm_count - 1) / s->sm_count;
+        // (up to 8 slices meet in distributed shared memory, measured at about three quarters of the L2 cost)
         const double t = (double)waves * (5.0 + (double)((nkb_model + sl - 1) / sl) * c_kb) +
-                         (sl > 1 ? (bn / 64) * (1.3 + 0.45 * sl) : 0.0);
+                         (sl > 1 ? (sl <= 8 ? 0.75 : 1.0) * (bn / 64) * (1.3 + 0.45 * sl) : 0.0);
         if (t < best - 1e-9) { best = t; BN = bn; model_slices = sl; }      // ties: the wider tile, fewer slices
       }
     }
