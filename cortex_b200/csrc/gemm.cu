@@ -129,10 +129,15 @@ gemm_skinny_nt_kernel(T* C, long long ldc, const T* A, long long lda, const T* B
   const int m = (int)blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const T* a = A + (long long)m * lda;
+  // requested now, used after the reduction: the epilogue lanes' bias and C values would otherwise cost a memory
+  // round trip each at the very end of a kernel that is nothing but latency
+  const bool epi_lane = warp == 0 && lane < N;
+  const T bias_v = (epi_lane && bias) ? bias[lane] : (T)0;
+  const T c_old = (epi_lane && beta != (T)0) ? C[(long long)m * ldc + lane] : (T)0;
   T acc[SKINNY_MAX_N];
 #pragma unroll
   for (int n = 0; n < SKINNY_MAX_N; ++n) acc[n] = (T)0;
-#pragma unroll 2
+#pragma unroll 4
   for (int k = (int)threadIdx.x; k < K; k += SKINNY_THREADS) {
     const T av = a[k];
 #pragma unroll
@@ -157,8 +162,8 @@ gemm_skinny_nt_kernel(T* C, long long ldc, const T* A, long long lda, const T* B
 #pragma unroll
     for (int w = 1; w < SKINNY_THREADS / 32; ++w) sum += part[w][lane];
     o = alpha * sum;
-    if (beta != (T)0) o += beta * C[(long long)m * ldc + lane];
-    if (bias) o += bias[lane];
+    if (beta != (T)0) o += beta * c_old;
+    if (bias) o += bias_v;
     if (act != CB200_ACT_SOFTMAX) o = act_apply<T>(o, act);
   }
   if (act == CB200_ACT_SOFTMAX) {

@@ -514,18 +514,28 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   const long long tiles_m = (M + BM - 1) / BM;
   const int nkb_model = (K + 15) / 16;
   const bool big_a = (long long)M * K * 4 >= (24ll << 20) && (long long)M >= (long long)N;
-  const bool may_slice = !((flags & FLAG_SPLIT_K) && K >= 4096 && store_mode == STORE_ROW_MAJOR) && !(flags & FLAG_ONE_TERM);
-  const int min_slices = (flags >> FLAG_MIN_SLICES_SHIFT) & 0xff;      // a long reduction the caller wants cut up
+  // FLAG_SPLIT_K (the fused layer entry points, K >= 4096): the reduction must be cut at least in two.  Where the
+  // tiles leave room, two or more K slices do that (and fill the SMs); otherwise the two-halves form below.
+  const bool want_halves = (flags & FLAG_SPLIT_K) && K >= 4096 && store_mode == STORE_ROW_MAJOR;
+  const bool may_slice = !(flags & FLAG_ONE_TERM);
+  int min_slices = (flags >> FLAG_MIN_SLICES_SHIFT) & 0xff;            // a long reduction the caller wants cut up
+  if (want_halves && may_slice && min_slices < 2 && s->opt_gemm_k_slices != 1) min_slices = 2;
   int BN = bn_max, model_slices = min_slices > 1 ? min_slices : 1;
-  {
+  bool sliced_instead_of_halves = false;
+  for (int attempt = 0; attempt < 2; ++attempt) {
     double best = 1e30;
+    if (attempt == 1) {                  // no room for the slices: one CTA per tile (and K halves where wanted)
+      min_slices = (flags >> FLAG_MIN_SLICES_SHIFT) & 0xff;
+      model_slices = min_slices > 1 ? min_slices : 1;
+    }
+    const bool slices_allowed = may_slice && !(attempt == 1 && want_halves);
     for (int bn = 256; bn >= 64; bn >>= 1) {
       if (bn > bn_max) continue;
       if (s->opt_gemm_tile_n > 0 ? bn != s->opt_gemm_tile_n : (big_a && bn != bn_max)) continue;
       const double c_kb = bn == 256 ? 0.56 : (bn == 128 ? 0.455 : 0.39);
       const long long tiles = tiles_m * ((N + bn - 1) / bn);
       for (int sl = min_slices > 1 ? min_slices : 1; sl <= 32; ++sl) {
-        if (sl > 1 && (!may_slice || tiles * sl > s->sm_count || nkb_model / sl < 4)) break;
+        if (sl > 1 && (!slices_allowed || tiles * sl > s->sm_count || nkb_model / sl < 4)) break;
         const long long waves = (tiles * sl + s->sm_count - 1) / s->sm_count;
         // (up to 8 slices meet in distributed shared memory, measured at about three quarters of the L2 cost)
         const double t = (double)waves * (5.0 + (double)((nkb_model + sl - 1) / sl) * c_kb) +
@@ -534,6 +544,8 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
       }
     }
     if (s->opt_gemm_tile_n > 0 && s->opt_gemm_tile_n > bn_max) BN = s->opt_gemm_tile_n;   // forced wider than N needs
+    if (best < 1e29) { sliced_instead_of_halves = want_halves && attempt == 0; break; }
+    if (!(want_halves && attempt == 0)) break;      // nothing to retry (a forced minimum that does not fit runs as asked)
   }
   const int tiles_n = (N + BN - 1) / BN;
   const long long panel_bytes = (long long)BN * K * 4;          // one column tile's share of B
@@ -542,7 +554,7 @@ int cb200_gemm_tf32x3_launch_peers(cb200_stream* s, float* C, long long ldc, int
   // 7e-9 * K (relative: 2.9e-5 at K = 4096, inside the 1e-4 bound of one gemm!), the same for every
   // output, so it compounds through a stack of layers (five 4096-wide layers: 1.4e-4 on the softmax
   // output); two 2048-long halves joined by a round-to-nearest add halve that, at 8-12 % of the speed.
-  p.k_split = ((flags & FLAG_SPLIT_K) && K >= 4096 && store_mode == STORE_ROW_MAJOR) ? 2 : 1;
+  p.k_split = (want_halves && !sliced_instead_of_halves) ? 2 : 1;
   p.C_lo = nullptr;
   p.drain_every = 0;
   p.tile_flags = nullptr;

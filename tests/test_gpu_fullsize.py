@@ -163,16 +163,19 @@ def test_wide_mlp_full_width_sampled_rows(b200_driver, datatype, rows, presplit)
 
 @pytest.mark.parametrize("M,N,K", [(300, 200, 4096), (128, 1000, 4112), (513, 260, 8200), (4096, 4096, 4096)])
 @pytest.mark.parametrize("beta", [0.0, 0.75])
-def test_fused_layer_long_reduction(b200_driver, M, N, K, beta):
-    """gemm_bias_act with K >= 4096: every output tile is reduced in two K halves by two CTAs of one
-    launch (and in host-chained launches past 4096); alpha, beta, bias and ReLU must come out as for
-    one reduction.  Sampled entries against float64."""
+@pytest.mark.parametrize("never_slice", [False, True])
+def test_fused_layer_long_reduction(b200_driver, M, N, K, beta, never_slice):
+    """gemm_bias_act with K >= 4096: the reduction of every output tile is cut at least in two -- K slices
+    where the tiles leave SMs free (the small shapes here), otherwise, or with slicing switched off, two K
+    halves by two CTAs of one launch (and host-chained launches past 4096); alpha, beta, bias and ReLU must
+    come out as for one reduction.  Sampled entries against float64."""
     rng = np.random.default_rng(K + M)
     A = rng.standard_normal((M, K)).astype(np.float32)
     W = (rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)
     C0 = rng.standard_normal((M, N)).astype(np.float32)
     bias = rng.standard_normal(N).astype(np.float32)
     stream = _stream(b200_driver)
+    stream.set_option("gemm-k-slices", 1 if never_slice else 0)
     with ct.with_stream(stream), ct.with_datatype("float"):
         a, w, c, b = ct.to_tensor(A), ct.to_tensor(W), ct.to_tensor(C0), ct.to_tensor(bias)
         for _ in range(2):      # twice: the per-tile flags must be left clean by the first launch
