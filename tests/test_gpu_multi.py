@@ -27,7 +27,11 @@ def _rel_err(got, want):
 
 @pytest.mark.parametrize("datatype,tol", [("float", 1e-4), ("double", 1e-12)])
 @pytest.mark.parametrize("M,K,N,ld,col0,n_peers", [(300, 256, 200, 1000, 400, 2), (128, 64, 125, 1000, 125, 3),
-                                                   (512, 512, 256, 1024, 512, 7), (100, 30, 17, 53, 5, 1)])
+                                                   (512, 512, 256, 1024, 512, 7), (100, 30, 17, 53, 5, 1),
+                                                   # few tiles, long reductions: the K slices of a tile (one
+                                                   # cluster, or through L2) finish the peer stores as well
+                                                   (1024, 4096, 125, 1000, 125, 3), (1024, 4096, 248, 1000, 248, 2),
+                                                   (256, 2048, 64, 256, 64, 2)])
 def test_gemm_epilogue_stores_to_every_destination(datatype, tol, M, K, N, ld, col0, n_peers):
     """All destinations on ONE device: the epilogue writes the same window of each, and nothing else."""
     from cortex_b200 import tensor as ct
