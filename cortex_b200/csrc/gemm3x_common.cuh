@@ -33,7 +33,7 @@ struct GemmParams {
   int split_from;      // pair kernel only: tiles from this index on are computed as two K halves by two clusters
   float* partials;     // pair kernel only: [tail tile][K half][rank][128][BN] partial accumulators
   int split_block;     // tiles per block of (first halves, second halves) in the grid order
-  // Small problems (fewer tiles than half the SMs): every tile is reduced by ksplit_n CTAs, each over a slice of K.
+  // Problems whose tiles leave SMs free: every tile is reduced by ksplit_n CTAs, each over a slice of K.
   // A CTA parks its raw tile in ksplit_ws[(tile * ksplit_n + slice)][BN / 4][BM] float4; the one that arrives last (per-tile
   // counter in tile_flags) sums the slices in slice order and runs the epilogue.  Nobody waits.
   int ksplit_n;

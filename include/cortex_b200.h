@@ -476,9 +476,9 @@ enum cb200_stream_option {
                                        keeps the input patch in shared memory, 3 = by geometry, but the patch
                                        kernel always behind its layout pre-pass (never the variant that reads
                                        the NCHW input itself) */
-  CB200_OPT_GEMM_K_SLICES = 6,      /* fp32 tensor-core gemm! on problems with fewer tiles than half the SMs: CTAs per
-                                       tile, each over a slice of K: 0 = by size, 1 = never slice, n <= 16 = n slices
-                                       when K has at least 8 k-blocks per slice */
+  CB200_OPT_GEMM_K_SLICES = 6,      /* fp32 tensor-core gemm! on problems whose tiles leave SMs free: CTAs per tile, each
+                                       over a slice of K: 0 = chosen with the tile width by a timing model, 1 = never
+                                       slice, n <= 16 = n slices when K has at least 8 k-blocks per slice */
   CB200_OPT_GEMM_TILE_N = 7,        /* fp32 tensor-core gemm!: output tile width, 0 = by size, else 64, 128 or 256 */
   CB200_OPT_GEMM_SLICE_HANDOVER = 8, /* K-sliced fp32 gemm!: 0 = up to 8 slices meet in distributed shared memory (the
                                        slices of a tile are one thread-block cluster), more through L2; 1 = always L2 */
