@@ -166,7 +166,11 @@ reduce_rows_vec(T* out, const T* in, Operand oo, Operand oi, Geometry go, Geomet
       for (; j + (U - 1) * nthreads < nvec; j += U * nthreads) {
         RVec<T, VEC> v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = row[j + u * nthreads];
+        for (int u = 0; u < U; ++u) {
+          // read-once stream: evict-first loads (16 bytes whatever the element type)
+          const float4 raw = __ldcs(reinterpret_cast<const float4*>(row + j + u * nthreads));
+          v[u] = *reinterpret_cast<const RVec<T, VEC>*>(&raw);
+        }
 #pragma unroll
         for (int u = 0; u < U; ++u) red_vec_accum<T, A, FAST>(op, acc, facc, fsum, v[u], alpha, unit);
       }
