@@ -36,14 +36,16 @@ bool cb200_conv_halo_eligible(int cin, int cout, int out_w, int out_h, int kh, i
 int cb200_conv_halo_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                            int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
                            float out_alpha, const float* bias, int act);
-bool cb200_conv_tma_eligible(int cin, int out_w, int out_h, int stride_x, int stride_y, long long in_elems);
+bool cb200_conv_tma_eligible(int cin, int cout, int kh, int kw, int out_w, int out_h, int stride_x, int stride_y,
+                             long long in_elems);
 int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                           int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
-                          float out_alpha, const float* bias, int act);
+                          int stride_x, int stride_y, float out_alpha, const float* bias, int act);
 
-// fp32 forward convolution on dense NCHW tensors, routed by geometry.  Stride-1 layers with a multiple of 16 input
-// channels: every operand tile by TMA -- the input patch kept in shared memory across the filter taps
-// (conv_halo.cu) where the 8 x 16 tiles fit the output, one shifted tile per tap otherwise (conv_tma.cu); the rest:
+// fp32 forward convolution on dense NCHW tensors, routed by geometry.  Layers with a multiple of 16 input
+// channels: every operand tile by TMA -- stride 1: the input patch kept in shared memory across the filter taps
+// (conv_halo.cu) where the 8 x 16 tiles fit the output, one shifted tile per tap otherwise (conv_tma.cu, which also
+// takes stride-2 layers with enough products per input element through the tensor map's traversal stride); the rest:
 // im2col rows gathered by threads (conv_igemm.cu).  opt_conv_route: 0 = by geometry, 1 = always gather, 2 = never
 // the patch kernel, 3 = by geometry, but the patch kernel always behind its layout pre-pass.  Also the engine of convolution-backward-data! (conv_backward.cu).
 bool cb200_conv_forward_f32_uses_tma(const cb200_stream* s, int batch, int cin, int in_h, int in_w, int cout, int out_h,
@@ -51,7 +53,7 @@ bool cb200_conv_forward_f32_uses_tma(const cb200_stream* s, int batch, int cin, 
   const long long in_elems = (long long)batch * cin * in_h * in_w;
   if ((s->opt_conv_route == 0 || s->opt_conv_route == 3) && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
     return true;
-  return s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, out_w, out_h, stride_x, stride_y, in_elems);
+  return s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, cout, kh, kw, out_w, out_h, stride_x, stride_y, in_elems);
 }
 
 // out = act(conv(in, w) + out_alpha * out + bias[channel]): bias (may be null) and the activation (enum cb200_act)
@@ -62,8 +64,8 @@ int cb200_conv_forward_f32_bias_act(cb200_stream* s, float* out, const float* in
   const long long in_elems = (long long)batch * cin * in_h * in_w;
   if ((s->opt_conv_route == 0 || s->opt_conv_route == 3) && cb200_conv_halo_eligible(cin, cout, out_w, out_h, kh, kw, stride_x, stride_y, in_elems))
     return cb200_conv_halo_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha, bias, act);
-  if (s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, out_w, out_h, stride_x, stride_y, in_elems))
-    return cb200_conv_tma_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, out_alpha, bias, act);
+  if (s->opt_conv_route != 1 && cb200_conv_tma_eligible(cin, cout, kh, kw, out_w, out_h, stride_x, stride_y, in_elems))
+    return cb200_conv_tma_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, stride_x, stride_y, out_alpha, bias, act);
   return cb200_conv_igemm_launch(s, out, in, w, batch, cin, in_h, in_w, cout, out_h, out_w, kh, kw, pad_x, pad_y, stride_x,
                                  stride_y, out_alpha, bias, act);
 }

@@ -49,6 +49,7 @@ struct TmaConvParams {
   const float* bias;   // [C_out] added after out_alpha * out, or null
   int act;             // enum cb200_act applied last
   int batch, cout, out_h, out_w, kh, kw, pad_x, pad_y;
+  int stride_x, stride_y;   // 1 or 2: the boxes walk the input with the TMA's traversal stride
   int bx, by, nbox;         // one box = bx x by output pixels; nbox * bx * by = 128
   int tiles_x, tiles_y;     // boxes per image along x / y
   int n_boxes;              // batch * tiles_x * tiles_y
@@ -206,8 +207,8 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int id = box0 + b;
         const int img = id / per_img, rem = id - img * per_img;
         bn[b] = img;
-        by0[b] = (rem / p.tiles_x) * p.by - p.pad_y;
-        bx0[b] = (rem % p.tiles_x) * p.bx - p.pad_x;
+        by0[b] = (rem / p.tiles_x) * p.by * p.stride_y - p.pad_y;
+        bx0[b] = (rem % p.tiles_x) * p.bx * p.stride_x - p.pad_x;
       }
       int cb = 0, ky = 0, kx = 0;
       for (int i = 0; i < p.nkb; ++i) {
@@ -389,14 +390,16 @@ EncodeTiledFn tconv_encode_fn() {
   return fn;
 }
 
-// NHWC activations [N][H][W][C] as the 4-d tensor {C, W, H, N}; box {16, bx, by, 1}
-int encode_nhwc(CUtensorMap* tm, const float* base, int C, int W, int H, int N, int bx, int by) {
+// NHWC activations [N][H][W][C] as the 4-d tensor {C, W, H, N}; box {16, bx, by, 1} output pixels.  A strided layer
+// reads every sx-th column and sy-th row: the map's traversal strides do that (to deliver n elements along a
+// dimension with traversal stride s the box extent is n * s), so the tile in shared memory is the same bx x by x 16.
+int encode_nhwc(CUtensorMap* tm, const float* base, int C, int W, int H, int N, int bx, int by, int sx, int sy) {
   EncodeTiledFn fn = tconv_encode_fn();
   if (!fn) { cb200_set_error("cuTensorMapEncodeTiled is not available from this driver"); return CB200_ERR_CUDA; }
   cuuint64_t gdim[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
   cuuint64_t gstride[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
-  cuuint32_t box[4] = {(cuuint32_t)TBK, (cuuint32_t)bx, (cuuint32_t)by, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
+  cuuint32_t box[4] = {(cuuint32_t)TBK, (cuuint32_t)(bx * sx), (cuuint32_t)(by * sy), 1};
+  cuuint32_t estr[4] = {1, (cuuint32_t)sx, (cuuint32_t)sy, 1};
   CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)base, gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -463,19 +466,26 @@ double cb200_conv_tma_plan(int out_w, int out_h, int* bx_out, int* by_out, int* 
   return best;
 }
 
-// Eligible: stride 1, C_in a multiple of 16, the output tiles with <= 35 % overhang.
-bool cb200_conv_tma_eligible(int cin, int out_w, int out_h, int stride_x, int stride_y, long long in_elems) {
-  if (stride_x != 1 || stride_y != 1 || (cin % 16) != 0 || in_elems >= 2147483647LL) return false;
+// Eligible: stride 1 or 2, C_in a multiple of 16, the output tiles with <= 35 % overhang (and a box whose extent
+// times the stride stays within the 256 elements a tensor-map box may span).
+// Strided layers pay the same layout pre-pass over the whole input for a fraction of the products: they come here
+// only when every input element feeds at least ~400 multiply-adds (measured: 64 x 64 x 56 x 56 -> 128, 3 x 3 / 2:
+// 93 us here, 85 us on the gather kernel; 1 x 1 / 2: 62 against 31; 32 x 128 x 28 x 28 -> 256, 3 x 3 / 2: 40 against 58).
+bool cb200_conv_tma_eligible(int cin, int cout, int kh, int kw, int out_w, int out_h, int stride_x, int stride_y,
+                             long long in_elems) {
+  if (stride_x < 1 || stride_x > 2 || stride_y < 1 || stride_y > 2 || (cin % 16) != 0 || in_elems >= 2147483647LL) return false;
+  if (stride_x * stride_y > 1 && (long long)cout * kh * kw < 400ll * stride_x * stride_y) return false;
   int bx, by, nbox;
   const double ratio = cb200_conv_tma_plan(out_w, out_h, &bx, &by, &nbox);
-  return ratio > 0.0 && ratio <= 1.35;
+  return ratio > 0.0 && ratio <= 1.35 && bx * stride_x <= 256 && by * stride_y <= 256;
 }
 
 int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const float* w, int batch, int cin, int in_h,
                           int in_w, int cout, int out_h, int out_w, int kh, int kw, int pad_x, int pad_y,
-                          float out_alpha, const float* bias, int act) {
+                          int stride_x, int stride_y, float out_alpha, const float* bias, int act) {
   DeviceGuard guard(s->device);
   TmaConvParams p;
+  p.stride_x = stride_x; p.stride_y = stride_y;
   p.out = out; p.out_alpha = out_alpha; p.batch = batch; p.bias = bias; p.act = act; p.cout = cout; p.out_h = out_h; p.out_w = out_w;
   p.kh = kh; p.kw = kw; p.pad_x = pad_x; p.pad_y = pad_y; p.status = s->status_dev;
   cb200_conv_tma_plan(out_w, out_h, &p.bx, &p.by, &p.nbox);
@@ -503,8 +513,8 @@ int cb200_conv_tma_launch(cb200_stream* s, float* out, const float* in, const fl
   CB_LAUNCH_CHECK(s);
   const int BN = cout > 64 ? 128 : 64;       // wider layers take several 128-channel tiles
   CUtensorMap tmA, tmAlo, tmW, tmWlo;
-  if ((rc = encode_nhwc(&tmA, a_hi, cin, in_w, in_h, batch, p.bx, p.by))) return rc;
-  if ((rc = encode_nhwc(&tmAlo, a_lo, cin, in_w, in_h, batch, p.bx, p.by))) return rc;
+  if ((rc = encode_nhwc(&tmA, a_hi, cin, in_w, in_h, batch, p.bx, p.by, stride_x, stride_y))) return rc;
+  if ((rc = encode_nhwc(&tmAlo, a_lo, cin, in_w, in_h, batch, p.bx, p.by, stride_x, stride_y))) return rc;
   if ((rc = encode_w(&tmW, w_hi, K, cout, BN))) return rc;
   if ((rc = encode_w(&tmWlo, w_lo, K, cout, BN))) return rc;
   if (BN == 128) return launch_tconv<128>(s, tmA, tmAlo, tmW, tmWlo, p);

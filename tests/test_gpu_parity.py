@@ -196,6 +196,11 @@ def test_conv_matches_oracle(b200_driver, oracle_driver, datatype):
     dict(batch=1, cin=16, hw=40, cout=64, k=7, pad=3),           # 7 x 7 filter: 14 x 22 patch
     dict(batch=2, cin=48, hw=24, cout=20, k=2, pad=0),           # even filter, output 23 x 23 (overhang)
     dict(batch=40, cin=32, hw=32, cout=48),                      # 320 tiles on 296 slots: the 24 tiles of the last round are shared over the channel blocks
+    # stride 2: the per-tap kernel's boxes walk the input with the tensor map's traversal stride
+    # (layers with at least ~400 products per input element; the others stay on the gather kernel)
+    dict(batch=3, cin=32, hw=32, cout=200, k=3, pad=1, stride=2),
+    dict(batch=2, cin=16, hw=56, cout=72, k=5, pad=2, stride=2),
+    dict(batch=2, cin=16, hw=56, cout=64, k=1, pad=0, stride=2),      # too little work per element: gather kernel
 ], ids=lambda a: "x".join(str(v) for v in a.values()))
 def test_conv_tma_fed_kernels(b200_driver, oracle_driver, args):
     """Stride-1 fp32 convolutions with a multiple of 16 input channels run kernels whose operand tiles all arrive
